@@ -1,0 +1,70 @@
+"""ctypes loaders for the in-tree native libraries.
+
+`kernels()` returns the sm_100a CUDA kernel library, `host()` the C++ host-policy library. Both are
+built by `inference_b200/_native/build.py`; a missing library is an error (there is no silent PyTorch
+fallback for a kernel on a GPU box).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from pathlib import Path
+
+_DIR = Path(__file__).resolve().parent
+_KERNELS = None
+_HOST = None
+
+
+class NativeLibraryMissing(RuntimeError):
+    pass
+
+
+def _load(name: str, builder: str):
+    path = _DIR / name
+    if not path.exists():
+        if os.environ.get("SWB_NO_AUTOBUILD"):
+            raise NativeLibraryMissing(f"{path} is missing; run `python -m inference_b200._native.build`")
+        from . import build as _build
+
+        getattr(_build, builder)()
+    if not path.exists():
+        raise NativeLibraryMissing(f"{path} could not be built")
+    return ctypes.CDLL(str(path), mode=ctypes.RTLD_GLOBAL)
+
+
+def kernels() -> ctypes.CDLL:
+    global _KERNELS
+    if _KERNELS is None:
+        _KERNELS = _load("libswb200_kernels.so", "build_kernels")
+        _declare_kernels(_KERNELS)
+    return _KERNELS
+
+
+def host() -> ctypes.CDLL:
+    global _HOST
+    if _HOST is None:
+        _HOST = _load("libswb200_host.so", "build_host")
+    return _HOST
+
+
+c_int = ctypes.c_int
+c_void_p = ctypes.c_void_p
+c_size_t = ctypes.c_size_t
+c_float = ctypes.c_float
+c_ll = ctypes.c_longlong
+
+
+def _declare_kernels(lib: ctypes.CDLL) -> None:
+    def sig(name, argtypes, restype=c_int):
+        fn = getattr(lib, name, None)
+        if fn is not None:
+            fn.argtypes = argtypes
+            fn.restype = restype
+
+    sig("swb_status_read", [ctypes.POINTER(c_int)])
+    sig("swb_status_clear", [])
+    sig("swb_set_wait_limit_ns", [ctypes.c_ulonglong])
+    sig("swb_sm_count", [])
+    sig("swb_gemm_workspace_min", [], c_size_t)
+    sig("swb_gemm_bf16", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                          c_int, c_int, c_int, c_void_p, c_size_t, c_int, c_int, c_int, c_void_p])

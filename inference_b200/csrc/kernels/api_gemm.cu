@@ -1,0 +1,36 @@
+// extern "C" entry points for the dense GEMM.
+#include "gemm_tcgen05.cuh"
+
+extern "C" {
+
+int swb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* D, int ldd, int T, int N, int K,
+                  const void* bias, const void* residual, int ld_res, int act, int out_fp32, void* workspace,
+                  size_t workspace_bytes, int force_mode, int force_block_n, int force_splits, void* stream) {
+  swb::GemmArgs a;
+  a.A = A;
+  a.lda = lda;
+  a.W = W;
+  a.ldw = ldw;
+  a.D = D;
+  a.ldd = ldd;
+  a.T = T;
+  a.N = N;
+  a.K = K;
+  a.bias = bias;
+  a.residual = residual;
+  a.ld_res = ld_res;
+  a.act = act;
+  a.out_fp32 = out_fp32;
+  a.workspace = workspace;
+  a.workspace_bytes = workspace_bytes;
+  a.force_mode = force_mode;
+  a.force_block_n = force_block_n;
+  a.force_splits = force_splits;
+  return swb::gemm_bf16_launch(a, reinterpret_cast<cudaStream_t>(stream));
+}
+
+size_t swb_gemm_workspace_min(void) { return swb::SWB_GEMM_COUNTER_BYTES + (size_t)(8u << 20); }
+
+int swb_sm_count(void) { return swb::device_sm_count(); }
+
+}  // extern "C"

@@ -1,0 +1,572 @@
+// bf16 GEMM for sm_100a: D[T, N] = act(A[T, K] * W[N, K]^T + bias) + residual.
+//
+// Replaces the reference's cuBLAS-backed `linear` (candle-llm/src/primitives/nn.rs:14-19 and every
+// dense projection in models/llama.rs) with a hand-written Blackwell kernel:
+//   * operands staged global -> shared by TMA (128-byte swizzle, one 64-wide K slab per stage),
+//   * tcgen05.mma (kind::f16, M=128, N=16..256) issued by one thread, accumulating fp32 in TMEM,
+//   * a 4..8 stage mbarrier pipeline, two TMEM accumulator stages so the epilogue of tile i overlaps
+//     the mainloop of tile i+1, persistent CTAs (one per SM),
+//   * fused epilogue (bias, SiLU / tanh-GELU, residual add, bf16 or fp32 output),
+//   * token counts <= 256 run "swapped": the weight is the M=128 operand and tokens the N operand, so
+//     decode-sized batches waste no tensor-core rows; small problems are split along K across CTAs and
+//     the last-arriving CTA of a tile reduces the fp32 partials in a fixed order (deterministic).
+// Warp roles: warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..5 = epilogue.
+#include "common.cuh"
+#include "gemm_tcgen05.cuh"
+
+#include <cudaTypedefs.h>
+
+#include <mutex>
+#include <unordered_map>
+
+namespace swb {
+
+SWB_REGISTER_STATUS_UNIT(gemm);
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int GEMM_THREADS = 192;
+constexpr int GROUP_M = 8;
+
+template <int BLOCK_N>
+struct GemmCfg {
+  static constexpr int STAGES = BLOCK_N >= 256 ? 4 : (BLOCK_N >= 128 ? 6 : 8);
+  static constexpr uint32_t A_BYTES = BM * BK * 2;
+  static constexpr uint32_t B_BYTES = BLOCK_N * BK * 2;
+  static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr uint32_t TMEM_COLS = (2 * BLOCK_N < 32) ? 32 : 2 * BLOCK_N;
+  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+};
+
+struct UnitCoord {
+  int tile, split, tm, tn;
+};
+
+__device__ __forceinline__ UnitCoord decode_unit(const GemmParams& p, int u) {
+  UnitCoord c;
+  c.tile = u / p.splits;
+  c.split = u - c.tile * p.splits;
+  const int per_group = GROUP_M * p.tiles_n;
+  const int g = c.tile / per_group;
+  const int first_m = g * GROUP_M;
+  const int gsize = min(GROUP_M, p.tiles_m - first_m);
+  const int r = c.tile - g * per_group;
+  c.tm = first_m + r % gsize;
+  c.tn = r / gsize;
+  return c;
+}
+
+__device__ __forceinline__ float apply_act(float x, int act) {
+  if (act == SWB_ACT_SILU) return silu_f(x);
+  if (act == SWB_ACT_GELU_TANH) return gelu_tanh_f(x);
+  return x;
+}
+
+// One thread's 16 consecutive accumulator columns -> global memory.
+// Normal layout: row = token, columns = features. Transposed (swapped operands): row = feature, columns = tokens.
+template <bool TRANSPOSED>
+__device__ __forceinline__ void epilogue_store16(const GemmParams& p, float* v, int row, int col0) {
+  if (row >= p.M) return;
+  const int nvalid = min(16, p.N - col0);
+  if (nvalid <= 0) return;
+  if constexpr (!TRANSPOSED) {
+    const size_t off = (size_t)row * p.ldd + col0;
+    if (p.vec_ok && nvalid == 16) {
+      if (p.bias) {
+        const uint4* bp = reinterpret_cast<const uint4*>(p.bias + col0);
+        uint4 b0 = __ldg(bp), b1 = __ldg(bp + 1);
+        const bf16* bb0 = reinterpret_cast<const bf16*>(&b0);
+        const bf16* bb1 = reinterpret_cast<const bf16*>(&b1);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          v[j] += __bfloat162float(bb0[j]);
+          v[8 + j] += __bfloat162float(bb1[j]);
+        }
+      }
+      if (p.act != SWB_ACT_NONE) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = apply_act(v[j], p.act);
+      }
+      if (p.residual) {
+        const uint4* rp = reinterpret_cast<const uint4*>(p.residual + (size_t)row * p.ld_res + col0);
+        uint4 r0 = rp[0], r1 = rp[1];
+        const bf16* rr0 = reinterpret_cast<const bf16*>(&r0);
+        const bf16* rr1 = reinterpret_cast<const bf16*>(&r1);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          v[j] += __bfloat162float(rr0[j]);
+          v[8 + j] += __bfloat162float(rr1[j]);
+        }
+      }
+      if (p.out_fp32) {
+        float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + off);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) op[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+      } else {
+        uint4 o[2];
+        __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ob[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+        uint4* op = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + off);
+        op[0] = o[0];
+        op[1] = o[1];
+      }
+    } else {
+      for (int j = 0; j < nvalid; ++j) {
+        float x = v[j];
+        if (p.bias) x += __bfloat162float(p.bias[col0 + j]);
+        x = apply_act(x, p.act);
+        if (p.residual) x += __bfloat162float(p.residual[(size_t)row * p.ld_res + col0 + j]);
+        if (p.out_fp32)
+          reinterpret_cast<float*>(p.out)[off + j] = x;
+        else
+          reinterpret_cast<bf16*>(p.out)[off + j] = __float2bfloat16(x);
+      }
+    }
+  } else {
+    const float b = p.bias ? __bfloat162float(p.bias[row]) : 0.f;
+#pragma unroll 4
+    for (int j = 0; j < nvalid; ++j) {
+      const int tok = col0 + j;
+      float x = apply_act(v[j] + b, p.act);
+      if (p.residual) x += __bfloat162float(p.residual[(size_t)tok * p.ld_res + row]);
+      const size_t off = (size_t)tok * p.ldd + row;
+      if (p.out_fp32)
+        reinterpret_cast<float*>(p.out)[off] = x;
+      else
+        reinterpret_cast<bf16*>(p.out)[off] = __float2bfloat16(x);
+    }
+  }
+}
+
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <int BLOCK_N, bool TRANSPOSED>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                         const GemmParams p) {
+  using Cfg = GemmCfg<BLOCK_N>;
+  constexpr int STAGES = Cfg::STAGES;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* bar_empty = bar_full + STAGES;
+  uint64_t* bar_tfull = bar_empty + STAGES;
+  uint64_t* bar_tempty = bar_tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 2);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* s_last = s_abort + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&bar_full[s], 1);
+      mbar_init(&bar_empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&bar_tfull[a], 1);
+      mbar_init(&bar_tempty[a], 4);
+    }
+    *s_abort = 0;
+    *s_last = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_units = p.tiles_m * p.tiles_n * p.splits;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      const uint64_t pol_a = p.stream_a ? l2_policy_evict_first() : l2_policy_evict_last();
+      const uint64_t pol_b = l2_policy_evict_last();
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t outstanding = 0;       // stages whose TMA was issued and not yet known consumed
+      uint32_t issue_phase_bits = 0;  // parity each outstanding stage's full barrier will complete
+      bool ok = true;
+      for (int u = blockIdx.x; ok && u < total_units; u += gridDim.x) {
+        const UnitCoord c = decode_unit(p, u);
+        const int kb0 = c.split * p.kblocks_per_split;
+        const int kb1 = min(kb0 + p.kblocks_per_split, p.kblocks_total);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          ok = mbar_wait(&bar_empty[stage], phase ^ 1, s_abort, 100 + stage);
+          if (!ok) break;
+          outstanding &= ~(1u << stage);
+          uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
+          uint8_t* sb = sa + Cfg::A_BYTES;
+          mbar_arrive_expect_tx(&bar_full[stage], Cfg::STAGE_BYTES);
+          tma_load_2d_hint(sa, &tmap_a, &bar_full[stage], kb * BK, c.tm * BM, pol_a);
+          tma_load_2d_hint(sb, &tmap_b, &bar_full[stage], kb * BK, c.tn * BLOCK_N, pol_b);
+          outstanding |= 1u << stage;
+          issue_phase_bits = (issue_phase_bits & ~(1u << stage)) | (phase << stage);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (*s_abort) {
+        // Drain: let every copy this thread issued land before the CTA's shared memory is released.
+        for (int s = 0; s < STAGES; ++s) {
+          if (outstanding & (1u << s)) {
+            const uint32_t par = (issue_phase_bits >> s) & 1u;
+            for (int it = 0; it < (1 << 20); ++it)
+              if (mbar_try_wait(&bar_full[s], par)) break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, BLOCK_N);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; ok && u < total_units; u += gridDim.x) {
+        const UnitCoord c = decode_unit(p, u);
+        const int kb0 = c.split * p.kblocks_per_split;
+        const int kb1 = min(kb0 + p.kblocks_per_split, p.kblocks_total);
+        ok = mbar_wait(&bar_tempty[acc], acc_phase ^ 1, s_abort, 200 + acc);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BLOCK_N);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          ok = mbar_wait(&bar_full[stage], phase, s_abort, 300 + stage);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+          const uint64_t adesc = umma_desc_kmajor_sw128(sa);
+          const uint64_t bdesc = umma_desc_kmajor_sw128(sa + Cfg::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // advance 16 bf16 = 32 bytes along K inside the 128-byte swizzle atom: +2 in 16-byte units
+            umma_f16_ss(tmem_d, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                        (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&bar_empty[stage]);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&bar_tfull[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (warps 2..5) ------------------------------
+    const int quarter = warp & 3;           // TMEM lane quarter this warp may access
+    const int row_in_tile = quarter * 32 + lane;
+    const int epi_tid = (warp - 2) * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; ok && u < total_units; u += gridDim.x) {
+      const UnitCoord c = decode_unit(p, u);
+      ok = mbar_wait(&bar_tfull[acc], acc_phase, s_abort, 400 + acc);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BLOCK_N);
+      const int row = c.tm * BM + row_in_tile;
+      const int col_base = c.tn * BLOCK_N;
+      if (p.splits == 1) {
+#pragma unroll 1
+        for (int ch = 0; ch < BLOCK_N / 16; ++ch) {
+          float v[16];
+          tmem_ld_32x32b_x16(taddr + ch * 16, v);
+          epilogue_store16<TRANSPOSED>(p, v, row, col_base + ch * 16);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_tempty[acc]);
+      } else {
+        float* ws_mine = p.workspace + ((size_t)c.tile * p.splits + c.split) * (size_t)(BLOCK_N * BM);
+#pragma unroll 1
+        for (int ch = 0; ch < BLOCK_N / 16; ++ch) {
+          float v[16];
+          tmem_ld_32x32b_x16(taddr + ch * 16, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) __stcg(&ws_mine[(ch * 16 + j) * BM + row_in_tile], v[j]);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_tempty[acc]);
+        __threadfence();
+        epi_bar_sync();
+        if (epi_tid == 0) {
+          const int old = atomicAdd(&p.counters[c.tile], 1);
+          const int last = (old == p.splits - 1) ? 1 : 0;
+          if (last) p.counters[c.tile] = 0;  // ready for the next launch
+          *s_last = last;
+        }
+        epi_bar_sync();
+        if (*s_last) {
+          __threadfence();
+          const float* ws_tile = p.workspace + (size_t)c.tile * p.splits * (size_t)(BLOCK_N * BM);
+#pragma unroll 1
+          for (int ch = 0; ch < BLOCK_N / 16; ++ch) {
+            float v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = 0.f;
+            for (int s = 0; s < p.splits; ++s) {
+              const float* wsp = ws_tile + (size_t)s * (BLOCK_N * BM) + (ch * 16) * BM + row_in_tile;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] += __ldcg(&wsp[j * BM]);
+            }
+            epilogue_store16<TRANSPOSED>(p, v, row, col_base + ch * 16);
+          }
+        }
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  int rows, cols, ld, box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    h = h * 1000003u ^ (size_t)k.rows;
+    h = h * 1000003u ^ (size_t)k.cols;
+    h = h * 1000003u ^ (size_t)k.ld;
+    h = h * 1000003u ^ (size_t)k.box_rows;
+    return h;
+  }
+};
+
+}  // namespace
+
+// 2-D bf16 row-major [rows, cols] (row stride ld elements), box = 64 columns x box_rows rows, 128B swizzle.
+int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  MapKey key{ptr, rows, cols, ld, box_rows};
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return 0;
+    }
+  }
+  auto encode = get_encode_fn();
+  if (!encode) return -1;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return -(int)r - 1000;
+  std::lock_guard<std::mutex> g(mu);
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, *out);
+  return 0;
+}
+
+int device_sm_count() {
+  static int sms[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return 148;
+  if (sms[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    sms[dev] = n;
+  }
+  return sms[dev];
+}
+
+namespace {
+
+template <int BLOCK_N, bool TRANSPOSED>
+int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
+  using Cfg = GemmCfg<BLOCK_N>;
+  auto kern = gemm_bf16_tcgen05_kernel<BLOCK_N, TRANSPOSED>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return -(int)e;
+    configured[dev] = true;
+  }
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
+template <bool TRANSPOSED>
+int launch_bn(int block_n, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
+              cudaStream_t stream) {
+  switch (block_n) {
+    case 16: return launch_cfg<16, TRANSPOSED>(ta, tb, p, grid, stream);
+    case 32: return launch_cfg<32, TRANSPOSED>(ta, tb, p, grid, stream);
+    case 64: return launch_cfg<64, TRANSPOSED>(ta, tb, p, grid, stream);
+    case 128: return launch_cfg<128, TRANSPOSED>(ta, tb, p, grid, stream);
+    case 256: return launch_cfg<256, TRANSPOSED>(ta, tb, p, grid, stream);
+  }
+  return -2;
+}
+
+int pick_splits(int tiles, int kblocks, int sms, int max_splits) {
+  if (tiles >= sms || kblocks < 8) return 1;
+  int best = 1;
+  double best_eff = 0.0;
+  const int smax = std::min(max_splits, kblocks / 4);
+  for (int s = 1; s <= smax; ++s) {
+    const int kps = (kblocks + s - 1) / s;
+    const int real = (kblocks + kps - 1) / kps;
+    if (real != s) continue;
+    const long units = (long)tiles * s;
+    const long waves = (units + sms - 1) / sms;
+    // each wave costs kps k-blocks plus a fixed per-unit overhead of roughly 3 k-blocks (fill + epilogue)
+    const double cost = (double)waves * (kps + 3.0);
+    const double eff = 1.0 / cost;
+    if (eff > best_eff * 1.03) {
+      best_eff = eff;
+      best = s;
+    }
+  }
+  return best;
+}
+
+}  // namespace
+
+int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
+  if (a.T <= 0 || a.N <= 0 || a.K <= 0) return 0;
+  if ((a.K % 8) != 0 || (a.lda % 8) != 0 || (a.ldw % 8) != 0) return -3;
+  if ((reinterpret_cast<uintptr_t>(a.A) & 15) || (reinterpret_cast<uintptr_t>(a.W) & 15)) return -3;
+  const int sms = device_sm_count();
+
+  int swapped = a.force_mode;
+  if (swapped < 0) swapped = (a.T <= 256) ? 1 : 0;
+
+  GemmParams p{};
+  p.K = a.K;
+  p.kblocks_total = (a.K + BK - 1) / BK;
+  p.ldd = a.ldd;
+  p.out = a.D;
+  p.out_fp32 = a.out_fp32;
+  p.bias = reinterpret_cast<const bf16*>(a.bias);
+  p.residual = reinterpret_cast<const bf16*>(a.residual);
+  p.ld_res = a.ld_res;
+  p.act = a.act;
+  p.status = nullptr;
+
+  int block_n;
+  CUtensorMap ta, tb;
+  if (swapped) {
+    if (a.T > 256) return -4;
+    block_n = a.T <= 16 ? 16 : a.T <= 32 ? 32 : a.T <= 64 ? 64 : a.T <= 128 ? 128 : 256;
+    if (a.force_block_n > 0) block_n = a.force_block_n;
+    if (block_n < a.T) return -4;
+    p.M = a.N;
+    p.N = a.T;
+    p.transposed = 1;
+    p.stream_a = 1;
+    p.tiles_m = (a.N + BM - 1) / BM;
+    p.tiles_n = 1;
+    int r = make_tmap_bf16_2d(&ta, a.W, a.N, a.K, a.ldw, BM);
+    if (r) return r;
+    r = make_tmap_bf16_2d(&tb, a.A, a.T, a.K, a.lda, block_n);
+    if (r) return r;
+    p.vec_ok = 0;
+  } else {
+    block_n = a.N >= 256 ? 256 : a.N >= 128 ? 128 : a.N >= 64 ? 64 : a.N >= 32 ? 32 : 16;
+    if (a.force_block_n > 0) block_n = a.force_block_n;
+    p.M = a.T;
+    p.N = a.N;
+    p.transposed = 0;
+    p.stream_a = 0;
+    p.tiles_m = (a.T + BM - 1) / BM;
+    p.tiles_n = (a.N + block_n - 1) / block_n;
+    int r = make_tmap_bf16_2d(&ta, a.A, a.T, a.K, a.lda, BM);
+    if (r) return r;
+    r = make_tmap_bf16_2d(&tb, a.W, a.N, a.K, a.ldw, block_n);
+    if (r) return r;
+    const size_t esz = a.out_fp32 ? 4 : 2;
+    p.vec_ok = ((a.ldd * esz) % 16 == 0) && ((reinterpret_cast<uintptr_t>(a.D) & 15) == 0) &&
+               (!a.bias || (reinterpret_cast<uintptr_t>(a.bias) & 15) == 0) &&
+               (!a.residual || (((reinterpret_cast<uintptr_t>(a.residual) & 15) == 0) && (a.ld_res % 8 == 0)));
+  }
+
+  const int tiles = p.tiles_m * p.tiles_n;
+  const size_t counter_bytes = SWB_GEMM_COUNTER_BYTES;
+  const size_t tile_bytes = (size_t)block_n * BM * sizeof(float);
+  int max_splits = 0;
+  if (a.workspace && a.workspace_bytes > counter_bytes && tiles <= (int)(counter_bytes / sizeof(int))) {
+    const size_t cap = (a.workspace_bytes - counter_bytes) / tile_bytes;
+    max_splits = (int)std::min<size_t>(16, cap / (size_t)tiles);
+  }
+  int splits = 1;
+  if (a.force_splits > 0)
+    splits = std::min(a.force_splits, std::max(1, max_splits));
+  else if (max_splits > 1)
+    splits = pick_splits(tiles, p.kblocks_total, sms, max_splits);
+  splits = std::max(1, std::min(splits, p.kblocks_total));
+  int kps = (p.kblocks_total + splits - 1) / splits;
+  splits = (p.kblocks_total + kps - 1) / kps;
+  p.splits = splits;
+  p.kblocks_per_split = kps;
+  p.counters = reinterpret_cast<int*>(a.workspace);
+  p.workspace = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a.workspace) + counter_bytes);
+
+  const int units = tiles * splits;
+  const int grid = std::min(units, sms);
+  return swapped ? launch_bn<true>(block_n, ta, tb, p, grid, stream) : launch_bn<false>(block_n, ta, tb, p, grid, stream);
+}
+
+}  // namespace swb

@@ -1,0 +1,61 @@
+// Parameter blocks for the tcgen05 bf16 GEMM (kernel in gemm_tcgen05.cu).
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace swb {
+
+enum GemmAct : int { SWB_ACT_NONE = 0, SWB_ACT_SILU = 1, SWB_ACT_GELU_TANH = 2 };
+
+// The first SWB_GEMM_COUNTER_BYTES of a GEMM workspace hold per-tile arrival counters (zero between
+// launches: the caller zeroes them once, the kernel restores zero); fp32 split-K partials follow.
+constexpr size_t SWB_GEMM_COUNTER_BYTES = 64 * 1024;
+
+// Kernel-level problem: D[M, N] = A[M, K] * B[N, K]^T, possibly stored transposed.
+struct GemmParams {
+  int M, N, K;
+  int tiles_m, tiles_n, splits, kblocks_per_split, kblocks_total;
+  int transposed;  // 1: rows of the tile are output features, columns are tokens
+  int stream_a;    // 1: A is a weight read once (L2 evict-first)
+  int vec_ok;      // 16-byte vector epilogue accesses are legal
+  int ldd;
+  void* out;
+  int out_fp32;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  int ld_res;
+  int act;
+  float* workspace;
+  int* counters;
+  int* status;
+};
+
+// User-level problem: D[T, N] = act(A[T, K] * W[N, K]^T + bias[N]) + residual[T, N].
+struct GemmArgs {
+  const void* A;
+  int lda;
+  const void* W;
+  int ldw;
+  void* D;
+  int ldd;
+  int T, N, K;
+  const void* bias;
+  const void* residual;
+  int ld_res;
+  int act;
+  int out_fp32;
+  void* workspace;
+  size_t workspace_bytes;
+  int force_mode;     // -1 auto, 0 tokens-as-M, 1 swapped (weights-as-M)
+  int force_block_n;  // 0 auto
+  int force_splits;   // 0 auto
+};
+
+int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream);
+int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows);
+int device_sm_count();
+
+}  // namespace swb

@@ -1,0 +1,57 @@
+// Host-side registry of per-translation-unit device status words.
+#include "common.cuh"
+
+#include <mutex>
+#include <vector>
+
+namespace swb {
+namespace {
+std::vector<StatusUnit>& units() {
+  static std::vector<StatusUnit> u;
+  return u;
+}
+std::mutex& units_mu() {
+  static std::mutex m;
+  return m;
+}
+}  // namespace
+
+void register_status_unit(const StatusUnit& u) {
+  std::lock_guard<std::mutex> g(units_mu());
+  units().push_back(u);
+}
+}  // namespace swb
+
+extern "C" {
+
+// Reads the first non-zero status word among all kernel units into out8 (8 ints); returns its code.
+int swb_status_read(int* out8) {
+  std::lock_guard<std::mutex> g(swb::units_mu());
+  for (int i = 0; i < 8; ++i) out8[i] = 0;
+  for (auto& u : swb::units()) {
+    int tmp[8];
+    if (u.read(tmp) != 0) return -1;
+    if (tmp[0] != 0) {
+      for (int i = 0; i < 8; ++i) out8[i] = tmp[i];
+      return tmp[0];
+    }
+  }
+  return 0;
+}
+
+int swb_status_clear() {
+  std::lock_guard<std::mutex> g(swb::units_mu());
+  int rc = 0;
+  for (auto& u : swb::units()) rc |= u.clear();
+  return rc;
+}
+
+// Budget of every bounded device-side wait, in nanoseconds (default 2 s).
+int swb_set_wait_limit_ns(unsigned long long ns) {
+  std::lock_guard<std::mutex> g(swb::units_mu());
+  int rc = 0;
+  for (auto& u : swb::units()) rc |= u.set_limit(ns);
+  return rc;
+}
+
+}  // extern "C"

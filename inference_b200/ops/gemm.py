@@ -1,0 +1,57 @@
+"""Dense bf16 GEMM on tcgen05 (replaces the reference's cuBLAS `linear`, candle-llm/src/primitives/nn.rs:14-19)."""
+from __future__ import annotations
+
+import torch
+
+from .._native import kernels
+from .runtime import check, ptr, require_cuda, stream_ptr
+
+ACT = {None: 0, "none": 0, "silu": 1, "gelu_tanh": 2}
+_WORKSPACES: dict[tuple[int, int], torch.Tensor] = {}
+WORKSPACE_BYTES = 64 * 1024 + (96 << 20)
+
+
+def gemm_workspace(device: torch.device, slot: int = 0) -> torch.Tensor:
+    """Per-(device, slot) split-K scratch. Launches sharing a slot must be ordered on one stream."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    key = (idx, slot)
+    ws = _WORKSPACES.get(key)
+    if ws is None:
+        ws = torch.zeros(WORKSPACE_BYTES, dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = ws
+    return ws
+
+
+def gemm_bf16(a: torch.Tensor, w: torch.Tensor, *, bias: torch.Tensor | None = None,
+              residual: torch.Tensor | None = None, act: str | None = None, out: torch.Tensor | None = None,
+              out_dtype: torch.dtype = torch.bfloat16, mode: int = -1, block_n: int = 0, splits: int = 0,
+              workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """out[T, N] = act(a[T, K] @ w[N, K]^T + bias) + residual. a and w are bf16 with contiguous rows."""
+    require_cuda(a, w)
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    assert a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1]
+    assert a.stride(1) == 1 and w.stride(1) == 1
+    T, K = a.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty((T, N), dtype=out_dtype, device=a.device)
+    assert out.shape == (T, N) and out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
+    if residual is not None:
+        assert residual.dtype == torch.bfloat16 and residual.shape == (T, N) and residual.stride(1) == 1
+    if bias is not None:
+        assert bias.dtype == torch.bfloat16 and bias.numel() == N and bias.is_contiguous()
+    if workspace is None:
+        workspace = gemm_workspace(a.device)
+    rc = kernels().swb_gemm_bf16(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
+                                 T, N, K, ptr(bias), ptr(residual), residual.stride(0) if residual is not None else 0,
+                                 ACT[act], 1 if out.dtype == torch.float32 else 0, workspace.data_ptr(),
+                                 workspace.numel(), mode, block_n, splits, stream_ptr())
+    check(rc, "swb_gemm_bf16")
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, **kw) -> torch.Tensor:
+    """`x @ w^T (+ bias)` over the last dimension of x."""
+    lead = x.shape[:-1]
+    y = gemm_bf16(x.reshape(-1, x.shape[-1]), w, bias=bias, **kw)
+    return y.reshape(*lead, w.shape[0])

@@ -1,0 +1,83 @@
+"""tcgen05 GEMM against a plain PyTorch fp32 reference of the same op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, w, bias, residual, act):
+    y = a.float() @ w.float().t()
+    if bias is not None:
+        y = y + bias.float()
+    if act == "silu":
+        y = torch.nn.functional.silu(y)
+    elif act == "gelu_tanh":
+        y = torch.nn.functional.gelu(y, approximate="tanh")
+    if residual is not None:
+        y = y + residual.float()
+    return y
+
+
+def _check(T, N, K, *, mode=-1, block_n=0, splits=0, bias=False, residual=False, act=None, out_dtype=torch.bfloat16):
+    from inference_b200 import ops
+
+    g = torch.Generator(device="cuda").manual_seed(T * 7919 + N * 31 + K)
+    a = (torch.randn(T, K, device="cuda", generator=g) * 0.5).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).bfloat16()
+    b = (torch.randn(N, device="cuda", generator=g) * 0.1).bfloat16() if bias else None
+    r = (torch.randn(T, N, device="cuda", generator=g) * 0.5).bfloat16() if residual else None
+    y = ops.gemm_bf16(a, w, bias=b, residual=r, act=act, mode=mode, block_n=block_n, splits=splits,
+                      out_dtype=out_dtype)
+    ops.check_status()
+    ref = _ref(a, w, b, r, act)
+    err = (y.float() - ref).abs().max().item()
+    scale = ref.abs().max().item() + 1e-6
+    tol = 2e-2 if out_dtype == torch.bfloat16 else 2e-3
+    assert err / scale < tol, f"T={T} N={N} K={K} mode={mode} bn={block_n} splits={splits}: err {err} scale {scale}"
+    return y
+
+
+@pytest.mark.parametrize("T", [1, 5, 16, 33, 64, 128, 200, 256])
+def test_swapped_small_tokens(T):
+    _check(T, 512, 256)
+    _check(T, 384, 1024, bias=True, residual=True)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 8])
+def test_split_k_deterministic(splits):
+    y0 = _check(8, 1024, 2048, mode=1, splits=splits, bias=True, act="silu")
+    y1 = _check(8, 1024, 2048, mode=1, splits=splits, bias=True, act="silu")
+    assert torch.equal(y0, y1)
+
+
+@pytest.mark.parametrize("shape", [(300, 256, 128), (512, 1024, 512), (1000, 776, 328), (129, 4096, 4096)])
+@pytest.mark.parametrize("block_n", [0, 64, 128])
+def test_tokens_as_m(shape, block_n):
+    T, N, K = shape
+    _check(T, N, K, mode=0, block_n=block_n)
+    _check(T, N, K, mode=0, block_n=block_n, bias=True, residual=True, act="gelu_tanh")
+
+
+def test_fp32_out_and_ragged_edges():
+    _check(77, 1000, 264, mode=0, out_dtype=torch.float32)
+    _check(7, 1000, 264, mode=1, out_dtype=torch.float32, bias=True)
+    _check(40, 136, 72, mode=1)
+    _check(260, 136, 72)
+
+
+def test_llama_shapes():
+    for T in (1, 8, 64):
+        _check(T, 6144, 4096)
+        _check(T, 4096, 14336, residual=True)
+    _check(1024, 6144, 4096)
+    _check(1024, 4096, 14336, residual=True)
+
+
+def test_strided_views():
+    from inference_b200 import ops
+
+    a = (torch.randn(48, 1024, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(256, 512, device="cuda") * 0.05).bfloat16()
+    y = ops.gemm_bf16(a[:, 512:], w)
+    ref = a[:, 512:].float() @ w.float().t()
+    assert (y.float() - ref).abs().max().item() < 0.05 * ref.abs().max().item()
