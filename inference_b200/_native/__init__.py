@@ -68,3 +68,22 @@ def _declare_kernels(lib: ctypes.CDLL) -> None:
     sig("swb_gemm_workspace_min", [], c_size_t)
     sig("swb_gemm_bf16", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                           c_int, c_int, c_int, c_void_p, c_size_t, c_int, c_int, c_int, c_void_p])
+    sig("swb_rmsnorm", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float,
+                        c_void_p])
+    sig("swb_layernorm_mod", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                              c_int, c_int, c_float, c_void_p])
+    sig("swb_rope_kv_write", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                              c_void_p, c_float, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                              c_void_p])
+    sig("swb_gated_act_mul", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    sig("swb_embedding", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    sig("swb_gated_residual", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p])
+    sig("swb_attn_decode_workspace_bytes", [c_int, c_int, c_int], c_size_t)
+    sig("swb_attn_paged", [c_void_p, c_ll, c_int, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int,
+                           c_int, c_void_p, c_size_t, c_void_p])
+    sig("swb_attn_dense", [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int,
+                           c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    sig("swb_argmax", [c_void_p, c_int, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    sig("swb_spec_verify_greedy", [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    sig("swb_rep_penalty", [c_void_p, c_ll, c_int, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p])

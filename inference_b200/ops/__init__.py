@@ -1,3 +1,6 @@
 """Python wrappers over the sm_100a kernel library (tensors in, tensors out, current CUDA stream)."""
-from .gemm import gemm_bf16, linear, gemm_workspace  # noqa: F401
-from .runtime import check_status, device_status, KernelError  # noqa: F401
+from .attention import dense_attention, paged_attention  # noqa: F401
+from .gemm import gemm_bf16, gemm_workspace, linear  # noqa: F401
+from .llm import (argmax, embedding, gated_act_mul, gated_residual, layernorm_mod, rmsnorm, rope_kv_write,  # noqa: F401
+                  spec_verify_greedy)
+from .runtime import KernelError, check_status, device_status  # noqa: F401

@@ -1,0 +1,65 @@
+"""Paged and dense attention wrappers (head_dim 128)."""
+from __future__ import annotations
+
+import torch
+
+from .._native import kernels
+from .runtime import check, ptr, require_cuda, stream_ptr
+
+_DECODE_WS: dict[int, torch.Tensor] = {}
+
+
+def decode_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _DECODE_WS.get(idx)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 16 << 20), dtype=torch.uint8, device=device)
+        _DECODE_WS[idx] = ws
+    return ws
+
+
+def paged_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
+                    kv_lens: torch.Tensor, *, cu_q: torch.Tensor | None, max_q_len: int, scale: float,
+                    causal: bool = True, decode: bool = False, num_splits: int = 1, softcap: float = 0.0,
+                    out: torch.Tensor | None = None, workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """q: [T, Hq, 128] (any token/head strides, unit inner stride); caches [blocks, Hkv, block_size, 128];
+    block_table int32 [num_seqs, max_blocks]; kv_lens int32 [num_seqs] (context length including the new
+    tokens); cu_q int32 [num_seqs + 1] or None when every sequence has exactly max_q_len query tokens.
+    Bottom-right aligned causal mask like the reference SDPA (candle-llm/src/primitives/attention.rs:154-186)."""
+    require_cuda(q, kcache, vcache, block_table, kv_lens)
+    T, Hq, D = q.shape
+    Hkv, bs = kcache.shape[1], kcache.shape[2]
+    assert q.stride(2) == 1 and kcache.is_contiguous() and vcache.is_contiguous()
+    assert block_table.dtype == torch.int32 and kv_lens.dtype == torch.int32 and block_table.stride(1) == 1
+    num_seqs = kv_lens.numel()
+    if out is None:
+        out = torch.empty((T, Hq * D), dtype=q.dtype, device=q.device)
+    ws_ptr, ws_bytes = None, 0
+    if decode and num_splits > 1:
+        need = kernels().swb_attn_decode_workspace_bytes(num_seqs, Hkv, num_splits)
+        if workspace is None:
+            workspace = decode_workspace(q.device, need)
+        ws_ptr, ws_bytes = workspace.data_ptr(), workspace.numel()
+    rc = kernels().swb_attn_paged(q.data_ptr(), q.stride(0), q.stride(1), out.data_ptr(), out.stride(0),
+                                  kcache.data_ptr(), vcache.data_ptr(), block_table.data_ptr(), block_table.stride(0),
+                                  bs, ptr(cu_q), kv_lens.data_ptr(), num_seqs, max_q_len, Hq, Hkv, D, scale, softcap,
+                                  1 if causal else 0, 1 if decode else 0, num_splits, ws_ptr, ws_bytes, stream_ptr())
+    check(rc, "swb_attn_paged")
+    return out
+
+
+def dense_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float, causal: bool = False,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+    """q [B, Sq, Hq, 128], k/v [B, Skv, Hkv, 128] (k and v share strides) -> out [B, Sq, Hq*128]."""
+    require_cuda(q, k, v)
+    B, Sq, Hq, D = q.shape
+    Skv, Hkv = k.shape[1], k.shape[2]
+    assert q.stride(3) == 1 and k.stride(3) == 1 and k.stride() == v.stride()
+    assert q.stride(0) == Sq * q.stride(1) and k.stride(0) == Skv * k.stride(1)
+    if out is None:
+        out = torch.empty((B, Sq, Hq * D), dtype=q.dtype, device=q.device)
+    rc = kernels().swb_attn_dense(q.data_ptr(), q.stride(1), q.stride(2), k.data_ptr(), v.data_ptr(), k.stride(1),
+                                  k.stride(2), out.data_ptr(), out.stride(1), B, Sq, Skv, Hq, Hkv, D, scale,
+                                  1 if causal else 0, stream_ptr())
+    check(rc, "swb_attn_dense")
+    return out
