@@ -1,0 +1,185 @@
+"""Model runner: turns host-side sequence state into device step inputs and executes the forward.
+
+Decode steps are captured once per (batch, attention-splits) shape into a CUDA graph over static input
+buffers; each step then costs one pinned host->device copy of the step metadata, one graph launch and
+one device->host copy of the sampled tokens. The reference launches ~45 small kernels plus 7 library
+GEMMs per layer per token with no graph capture (candle-llm/README.md:165-168 calls decode launch-bound).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..models.llama import LlamaGpu, StepInputs
+from .kv_pool import PagedKvPool, PagedSequence
+
+
+def _splits_for(batch: int, kv_heads: int, max_kv: int, sms: int = 148) -> int:
+    tiles = max(1, (max_kv + 63) // 64)
+    want = max(1, (2 * sms) // max(1, batch * kv_heads))
+    s = 1
+    while s * 2 <= min(want, tiles, 32):
+        s *= 2
+    return s
+
+
+@dataclass
+class _DecodeGraph:
+    graph: torch.cuda.CUDAGraph
+    tokens_out: torch.Tensor
+    logits_out: torch.Tensor | None
+    launches: int
+
+
+class ModelRunner:
+    def __init__(self, model: LlamaGpu, pool: PagedKvPool, max_batch: int = 64, max_seq_len: int = 8192,
+                 use_graphs: bool = True):
+        self.model, self.pool = model, pool
+        self.max_batch, self.max_seq_len = max_batch, max_seq_len
+        self.max_blocks = (max_seq_len + pool.block_size - 1) // pool.block_size
+        self.use_graphs = use_graphs
+        dev = model.device
+        model.ensure_rope(max_seq_len + 64)
+        # static decode-step buffers; one packed int64 staging area so a step is a single H2D copy
+        self._n_meta = max_batch * 4 + max_batch * self.max_blocks
+        self._host_meta = torch.zeros(self._n_meta, dtype=torch.int32).pin_memory() if dev.type == "cuda" else \
+            torch.zeros(self._n_meta, dtype=torch.int32)
+        self._host_np = self._host_meta.numpy()
+        self._host_table_np = self._host_np[4 * max_batch:].reshape(max_batch, self.max_blocks)
+        self._row_state: list[tuple[int, int, int]] = [(0, 0, 0)] * max_batch  # (uid, epoch, blocks written)
+        self._dev_meta = torch.zeros(self._n_meta, dtype=torch.int32, device=dev)
+        self._ids = torch.zeros(max_batch, dtype=torch.int64, device=dev)
+        self._pos = torch.zeros(max_batch, dtype=torch.int32, device=dev)
+        self._slots = torch.zeros(max_batch, dtype=torch.int64, device=dev)
+        self._kvl = torch.zeros(max_batch, dtype=torch.int32, device=dev)
+        self._table = torch.zeros((max_batch, self.max_blocks), dtype=torch.int32, device=dev)
+        self._host_tokens = torch.zeros(max_batch, dtype=torch.int64).pin_memory() if dev.type == "cuda" else \
+            torch.zeros(max_batch, dtype=torch.int64)
+        self._graphs: dict[tuple[int, int, bool], _DecodeGraph] = {}
+        self.h2d_bytes_last = 0
+        self.d2h_bytes_last = 0
+        self.launches_last = 0
+
+    # ---- prefill (eager, ragged) ------------------------------------------------------------------
+    def prefill(self, seqs: list[PagedSequence], new_tokens: list[list[int]], *, want_logits: bool = False,
+                all_positions: bool = False):
+        """Appends new_tokens[i] to seqs[i] (any mix of lengths, including chunked / prefix-seeded sequences)
+        and returns greedy next tokens [num_seqs] (or fp32 logits when want_logits)."""
+        dev = self.model.device
+        ids, pos, slots, cu, kvl, rows = [], [], [], [0], [], []
+        for s, toks in zip(seqs, new_tokens):
+            start = s.length
+            sl = s.reserve(len(toks))
+            ids += toks
+            pos += list(range(start, start + len(toks)))
+            slots += sl
+            cu.append(cu[-1] + len(toks))
+            kvl.append(s.length)
+            rows.append(cu[-1] - 1)
+        maxb = max(len(s.blocks) for s in seqs)
+        table = torch.zeros((len(seqs), maxb), dtype=torch.int32)
+        for i, s in enumerate(seqs):
+            table[i, : len(s.blocks)] = torch.tensor(s.blocks, dtype=torch.int32)
+        max_q = max(len(t) for t in new_tokens)
+        G = self.model.cfg.groups
+        decode = max_q * G <= 16 and all(len(t) == max_q for t in new_tokens)
+        inp = StepInputs(
+            input_ids=torch.tensor(ids, dtype=torch.int64, device=dev),
+            positions=torch.tensor(pos, dtype=torch.int32, device=dev),
+            slot_mapping=torch.tensor(slots, dtype=torch.int64, device=dev),
+            block_table=table.to(dev), kv_lens=torch.tensor(kvl, dtype=torch.int32, device=dev),
+            cu_q=None if decode else torch.tensor(cu, dtype=torch.int32, device=dev), max_q_len=max_q,
+            num_seqs=len(seqs), decode=decode,
+            attn_splits=_splits_for(len(seqs), self.model.hkv, max(kvl)) if decode else 1,
+            logits_rows=None if all_positions else torch.tensor(rows, dtype=torch.int64, device=dev))
+        hidden = self.model.forward_hidden(inp, self.pool.data)
+        self.launches_last = self.model.launches
+        if want_logits or all_positions:
+            return self.model.logits(hidden)
+        return self.model.greedy_tokens(hidden)
+
+    # ---- decode (graph-captured, one token per sequence) ---------------------------------------------
+    def _fill_decode_meta(self, seqs: list[PagedSequence], tokens: list[int]) -> int:
+        MB = self.max_batch
+        h, table = self._host_np, self._host_table_np
+        max_kv = 0
+        for i, s in enumerate(seqs):
+            p = s.length
+            slot = s.reserve(1)[0]
+            h[i] = tokens[i]
+            h[MB + i] = p
+            h[2 * MB + i] = slot
+            h[3 * MB + i] = p + 1
+            if p + 1 > max_kv:
+                max_kv = p + 1
+            owner, epoch, written = self._row_state[i]
+            nb = len(s.blocks)
+            if owner != s.uid or epoch != s.epoch or written > nb:
+                table[i, :nb] = s.blocks
+                self._row_state[i] = (s.uid, s.epoch, nb)
+            elif written < nb:
+                table[i, written:nb] = s.blocks[written:nb]
+                self._row_state[i] = (s.uid, s.epoch, nb)
+        return max_kv
+
+    def _unpack_meta(self, B: int) -> None:
+        MB, mb = self.max_batch, self.max_blocks
+        m = self._dev_meta
+        self._ids[:B].copy_(m[:B])
+        self._pos[:B].copy_(m[MB:MB + B])
+        self._slots[:B].copy_(m[2 * MB:2 * MB + B])
+        self._kvl[:B].copy_(m[3 * MB:3 * MB + B])
+        self._table[:B].copy_(m[4 * MB:4 * MB + B * mb].view(B, mb))
+
+    def _decode_body(self, B: int, splits: int, want_logits: bool):
+        self._unpack_meta(B)
+        inp = StepInputs(input_ids=self._ids[:B], positions=self._pos[:B], slot_mapping=self._slots[:B],
+                         block_table=self._table[:B], kv_lens=self._kvl[:B], cu_q=None, max_q_len=1, num_seqs=B,
+                         decode=True, attn_splits=splits, logits_rows=None)
+        hidden = self.model.forward_hidden(inp, self.pool.data)
+        if want_logits:
+            return None, self.model.logits(hidden)
+        return self.model.greedy_tokens(hidden), None
+
+    def decode(self, seqs: list[PagedSequence], tokens: list[int], *, want_logits: bool = False):
+        """One decode step: feeds tokens[i] at the end of seqs[i]; returns next greedy tokens as a pinned
+        host tensor [B] (after a stream sync) or device fp32 logits [B, vocab]."""
+        B = len(seqs)
+        assert B <= self.max_batch
+        max_kv = self._fill_decode_meta(seqs, tokens)
+        self._dev_meta.copy_(self._host_meta, non_blocking=True)
+        self.h2d_bytes_last = self._host_meta.numel() * 4
+        splits = _splits_for(B, self.model.hkv, max_kv)
+        key = (B, splits, want_logits)
+        if not self.use_graphs or self.model.device.type != "cuda":
+            toks, logits = self._decode_body(B, splits, want_logits)
+            self.launches_last = self.model.launches + 5
+        else:
+            g = self._graphs.get(key)
+            if g is None:
+                g = self._capture(B, splits, want_logits)
+                self._graphs[key] = g
+            g.graph.replay()
+            toks, logits = g.tokens_out, g.logits_out
+            self.launches_last = g.launches
+        if want_logits:
+            return logits
+        self._host_tokens[:B].copy_(toks, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.d2h_bytes_last = B * 8
+        return self._host_tokens[:B]
+
+    def _capture(self, B: int, splits: int, want_logits: bool) -> _DecodeGraph:
+        # warm-up on a side stream (sets kernel attributes, fills the tensor-map cache), then capture
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                self._decode_body(B, splits, want_logits)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            toks, logits = self._decode_body(B, splits, want_logits)
+        return _DecodeGraph(graph, toks, logits, self.model.launches + 5)

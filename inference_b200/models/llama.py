@@ -1,0 +1,266 @@
+"""Llama-family decoder on sm_100a kernels with a paged KV cache and tensor parallelism.
+
+The capability target is the reference's generic `CausalLm` (candle-llm/src/models/llama.rs:31-1488):
+config-dispatched Llama / Mistral / Qwen2 / Qwen3 / Phi-3 / Gemma-2 / GLM-4 decoders. The execution
+design differs: weights are stored in tensor-parallel layout (column-parallel fused QKV and gate/up,
+row-parallel o_proj and down_proj, vocab-parallel head) even at P = 1, every projection is a tcgen05
+GEMM, norms / RoPE / KV writes / activations are fused kernels, attention reads the paged cache through
+the block table, and one step consumes a flat ragged token batch so prefill, chunked prefill, decode and
+speculative verify all share one forward.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .. import ops
+from ..contracts.errors import LoadError, Unsupported
+from ..parallel.comm import Communicator, single
+from .config import Architecture, ModelConfig, build_rope
+from .oracle import canonical_weights
+
+
+@dataclass
+class StepInputs:
+    """One engine step over a flat token batch (all tensors on the model's device)."""
+    input_ids: torch.Tensor            # int64 [T]
+    positions: torch.Tensor            # int32 [T]
+    slot_mapping: torch.Tensor         # int64 [T] flat cache slot per token (-1 = do not cache)
+    block_table: torch.Tensor          # int32 [num_seqs, max_blocks]
+    kv_lens: torch.Tensor              # int32 [num_seqs] context length including this step's tokens
+    cu_q: torch.Tensor | None          # int32 [num_seqs + 1]; None => every sequence has max_q_len tokens
+    max_q_len: int
+    num_seqs: int
+    decode: bool = False               # q_len * gqa_group <= 16 for every sequence
+    attn_splits: int = 1
+    logits_rows: torch.Tensor | None = None  # int64 rows of the hidden state to project; None => all rows
+
+
+@dataclass
+class LayerWeights:
+    ln1: torch.Tensor
+    qkv: torch.Tensor
+    qkv_bias: torch.Tensor | None
+    q_norm: torch.Tensor | None
+    k_norm: torch.Tensor | None
+    o: torch.Tensor
+    post_attn_ln: torch.Tensor | None   # sandwich: norm of the attention output
+    ln2: torch.Tensor
+    gate_up: torch.Tensor
+    down: torch.Tensor
+    post_mlp_ln: torch.Tensor | None    # sandwich: norm of the MLP output
+
+
+def _shard_rows(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    n = t.shape[0] // world
+    return t[rank * n:(rank + 1) * n]
+
+
+def _shard_cols(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    n = t.shape[1] // world
+    return t[:, rank * n:(rank + 1) * n]
+
+
+class LlamaGpu:
+    def __init__(self, cfg: ModelConfig, comm: Communicator | None = None, device: torch.device | None = None):
+        if cfg.mla is not None or cfg.moe is not None or cfg.architecture is Architecture.QWEN35:
+            raise Unsupported(f"{cfg.architecture.value}: served by the fp32 oracle path, not the sm_100a decoder")
+        if cfg.head_dim != 128:
+            raise Unsupported("the sm_100a attention kernels are built for head_dim 128")
+        self.cfg = cfg
+        self.comm = comm or single(device)
+        self.device = device or self.comm.device
+        P = self.comm.world
+        if cfg.num_heads % P or cfg.num_kv_heads % P or cfg.intermediate_size % P or cfg.vocab_size % P:
+            raise Unsupported(f"tensor parallel degree {P} does not divide heads/kv-heads/ffn/vocab")
+        self.hq = cfg.num_heads // P
+        self.hkv = cfg.num_kv_heads // P
+        self.ffn = cfg.intermediate_size // P
+        self.vocab_local = cfg.vocab_size // P
+        self.layers: list[LayerWeights] = []
+        self.embed: torch.Tensor | None = None      # full table on every rank (gather is local)
+        self.norm: torch.Tensor | None = None
+        self.lm_head: torch.Tensor | None = None    # [vocab / P, hidden]
+        rope = build_rope(cfg)
+        self.rot_dim, self.rope_interleaved = rope.dim, rope.interleaved
+        self._inv_freq = torch.tensor(rope.inv_freq, dtype=torch.float64)
+        self.cos = self.sin = None
+        self.max_positions = 0
+        self.launches = 0  # kernels launched by the last forward (for accounting)
+
+    # ---- weights --------------------------------------------------------------------------------
+    def ensure_rope(self, max_positions: int) -> None:
+        if max_positions <= self.max_positions:
+            return
+        ang = torch.arange(max_positions, dtype=torch.float64)[:, None] * self._inv_freq[None, :]
+        self.cos = ang.cos().float().to(self.device).contiguous()
+        self.sin = ang.sin().float().to(self.device).contiguous()
+        self.max_positions = max_positions
+
+    def load_state_dict(self, weights: dict[str, torch.Tensor]) -> "LlamaGpu":
+        """Takes full (unsharded) HF-named tensors and keeps this rank's tensor-parallel slice in bf16."""
+        cfg, r, P, dev = self.cfg, self.comm.rank, self.comm.world, self.device
+        w = canonical_weights(weights, cfg)
+        D = cfg.head_dim
+
+        def get(k: str) -> torch.Tensor:
+            if k not in w:
+                raise LoadError(f"missing tensor {k}")
+            return w[k]
+
+        def dev16(t: torch.Tensor) -> torch.Tensor:
+            return t.to(device=dev, dtype=torch.bfloat16).contiguous()
+
+        self.embed = dev16(get("model.embed_tokens.weight"))
+        self.norm = dev16(get("model.norm.weight"))
+        head = w.get("lm_head.weight", w["model.embed_tokens.weight"])
+        self.lm_head = dev16(_shard_rows(head, r, P))
+        self.layers = []
+        for i in range(cfg.num_layers):
+            p = f"model.layers.{i}"
+            q = _shard_rows(get(f"{p}.self_attn.q_proj.weight"), r, P)
+            k = _shard_rows(get(f"{p}.self_attn.k_proj.weight"), r, P)
+            v = _shard_rows(get(f"{p}.self_attn.v_proj.weight"), r, P)
+            qkv_bias = None
+            if f"{p}.self_attn.q_proj.bias" in w:
+                qkv_bias = dev16(torch.cat([_shard_rows(get(f"{p}.self_attn.{n}_proj.bias"), r, P) for n in "qkv"]))
+            gate = _shard_rows(get(f"{p}.mlp.gate_proj.weight"), r, P)
+            up = _shard_rows(get(f"{p}.mlp.up_proj.weight"), r, P)
+            arch = cfg.architecture
+            if arch is Architecture.GEMMA2:
+                post_attn, ln2, post_mlp = (get(f"{p}.post_attention_layernorm.weight"),
+                                            get(f"{p}.pre_feedforward_layernorm.weight"),
+                                            get(f"{p}.post_feedforward_layernorm.weight"))
+            elif arch is Architecture.GLM4:
+                post_attn, ln2, post_mlp = (get(f"{p}.post_self_attn_layernorm.weight"),
+                                            get(f"{p}.post_attention_layernorm.weight"),
+                                            get(f"{p}.post_mlp_layernorm.weight"))
+            else:
+                post_attn, ln2, post_mlp = None, get(f"{p}.post_attention_layernorm.weight"), None
+            qn = w.get(f"{p}.self_attn.q_norm.weight")
+            kn = w.get(f"{p}.self_attn.k_norm.weight")
+            self.layers.append(LayerWeights(
+                ln1=dev16(get(f"{p}.input_layernorm.weight")), qkv=dev16(torch.cat([q, k, v])), qkv_bias=qkv_bias,
+                q_norm=dev16(qn) if qn is not None else None, k_norm=dev16(kn) if kn is not None else None,
+                o=dev16(_shard_cols(get(f"{p}.self_attn.o_proj.weight"), r, P)),
+                post_attn_ln=dev16(post_attn) if post_attn is not None else None, ln2=dev16(ln2),
+                gate_up=dev16(torch.cat([gate, up])), down=dev16(_shard_cols(get(f"{p}.mlp.down_proj.weight"), r, P)),
+                post_mlp_ln=dev16(post_mlp) if post_mlp is not None else None))
+        assert D == 128
+        return self
+
+    def init_random(self, seed: int = 0, std: float = 0.02) -> "LlamaGpu":
+        """Random N(0, std) weights generated directly on the device in this rank's shard shapes."""
+        cfg, dev = self.cfg, self.device
+        g = torch.Generator(device=dev).manual_seed(seed * 1000 + self.comm.rank)
+        H, D = cfg.hidden_size, cfg.head_dim
+
+        def rnd(*shape):
+            t = torch.empty(*shape, dtype=torch.bfloat16, device=dev)
+            t.normal_(0.0, std, generator=g)
+            return t
+
+        one = 0.0 if cfg.architecture is Architecture.GEMMA2 else 1.0
+
+        def ones(n):
+            return torch.full((n,), one, dtype=torch.bfloat16, device=dev)
+
+        ge = torch.Generator(device=dev).manual_seed(seed * 1000 + 999)  # shared across ranks
+        self.embed = torch.empty(cfg.vocab_size, H, dtype=torch.bfloat16, device=dev).normal_(0.0, std, generator=ge)
+        self.norm = ones(H)
+        if cfg.tie_word_embeddings:
+            self.lm_head = self.embed[self.comm.rank * self.vocab_local:(self.comm.rank + 1) * self.vocab_local]
+        else:
+            self.lm_head = rnd(self.vocab_local, H)
+        sandwich = cfg.architecture.sandwich_norms
+        self.layers = []
+        for _ in range(cfg.num_layers):
+            self.layers.append(LayerWeights(
+                ln1=ones(H), qkv=rnd((self.hq + 2 * self.hkv) * D, H), qkv_bias=None,
+                q_norm=torch.ones(D, dtype=torch.bfloat16, device=dev) if cfg.architecture.has_qk_norm else None,
+                k_norm=torch.ones(D, dtype=torch.bfloat16, device=dev) if cfg.architecture.has_qk_norm else None,
+                o=rnd(H, self.hq * D), post_attn_ln=ones(H) if sandwich else None, ln2=ones(H),
+                gate_up=rnd(2 * self.ffn, H), down=rnd(H, self.ffn), post_mlp_ln=ones(H) if sandwich else None))
+        return self
+
+    def weight_bytes(self) -> int:
+        n = self.embed.numel() + self.norm.numel()
+        if self.lm_head.data_ptr() != self.embed.data_ptr() and not self.cfg.tie_word_embeddings:
+            n += self.lm_head.numel()
+        for L in self.layers:
+            n += L.qkv.numel() + L.o.numel() + L.gate_up.numel() + L.down.numel() + 2 * L.ln1.numel()
+        return n * 2
+
+    # ---- forward --------------------------------------------------------------------------------
+    def forward_hidden(self, inp: StepInputs, kv_pool: torch.Tensor) -> torch.Tensor:
+        """Runs the decoder stack; kv_pool is [layers, 2, blocks, Hkv_local, block_size, 128]. Returns the
+        final (un-normed) branch output and residual folded together: rows of normed hidden states [T, H]."""
+        cfg = self.cfg
+        D = cfg.head_dim
+        eps, woff = cfg.rms_norm_eps, cfg.norm_weight_offset
+        T = inp.input_ids.numel()
+        res = ops.embedding(inp.input_ids, self.embed, scale=cfg.embed_scale)
+        branch = None
+        block_size = kv_pool.shape[4]
+        q_cols = self.hq * D
+        n = 1
+        for li, L in enumerate(self.layers):
+            h = ops.rmsnorm(res, L.ln1, eps, w_offset=woff) if branch is None else \
+                ops.rmsnorm(branch, L.ln1, eps, residual=res, w_offset=woff)
+            qkv = ops.gemm_bf16(h, L.qkv, bias=L.qkv_bias)
+            ops.rope_kv_write(qkv, inp.positions, inp.slot_mapping, self.cos, self.sin, kv_pool[li, 0], kv_pool[li, 1],
+                              self.hq, self.hkv, D, rot_dim=self.rot_dim, interleaved=self.rope_interleaved,
+                              q_norm=L.q_norm, k_norm=L.k_norm, norm_eps=eps, norm_w_offset=woff,
+                              block_size=block_size)
+            q = qkv[:, :q_cols].view(T, self.hq, D)
+            attn = ops.paged_attention(q, kv_pool[li, 0], kv_pool[li, 1], inp.block_table, inp.kv_lens, cu_q=inp.cu_q,
+                                       max_q_len=inp.max_q_len, scale=cfg.attn_scale, causal=True, decode=inp.decode,
+                                       num_splits=inp.attn_splits, softcap=cfg.attn_logit_softcap or 0.0)
+            branch = ops.gemm_bf16(attn, L.o)
+            branch = self.comm.all_reduce(branch)
+            if L.post_attn_ln is not None:
+                branch = ops.rmsnorm(branch, L.post_attn_ln, eps, w_offset=woff)
+                n += 1
+            h = ops.rmsnorm(branch, L.ln2, eps, residual=res, w_offset=woff)
+            gu = ops.gemm_bf16(h, L.gate_up)
+            act = ops.gated_act_mul(gu, cfg.mlp_activation)
+            branch = ops.gemm_bf16(act, L.down)
+            branch = self.comm.all_reduce(branch)
+            if L.post_mlp_ln is not None:
+                branch = ops.rmsnorm(branch, L.post_mlp_ln, eps, w_offset=woff)
+                n += 1
+            n += 9 if inp.attn_splits == 1 or not inp.decode else 10
+        self.launches = n
+        if inp.logits_rows is not None:
+            # fold the last branch into the residual first, then pick the rows to project
+            tmp = ops.rmsnorm(branch, self.norm, eps, residual=res, w_offset=woff)
+            self.launches += 1
+            return tmp.index_select(0, inp.logits_rows)
+        self.launches += 1
+        return ops.rmsnorm(branch, self.norm, eps, residual=res, w_offset=woff)
+
+    def logits_local(self, hidden: torch.Tensor) -> torch.Tensor:
+        """fp32 logits of this rank's vocabulary shard: [R, vocab / P]."""
+        self.launches += 1
+        logits = ops.gemm_bf16(hidden, self.lm_head, out_dtype=torch.float32)
+        c = self.cfg.final_logit_softcap
+        return torch.tanh(logits / c) * c if c else logits
+
+    def logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        local = self.logits_local(hidden)
+        return self.comm.all_gather(local, dim=1) if self.comm.is_parallel else local
+
+    def greedy_tokens(self, hidden: torch.Tensor) -> torch.Tensor:
+        """Vocab-parallel lm_head + argmax: each rank reduces its shard, then a tiny (value, index) exchange."""
+        local = self.logits_local(hidden)
+        self.launches += 1
+        if not self.comm.is_parallel:
+            return ops.argmax(local)
+        vals = local.max(dim=-1)
+        idx = vals.indices + self.comm.rank * self.vocab_local
+        packed = torch.stack((vals.values.double(), idx.double()), dim=-1)  # [R, 2]
+        allp = self.comm.all_gather(packed[None], dim=0)                     # [P, R, 2]
+        best = allp[..., 0].max(dim=0)
+        # ties across ranks resolve to the lowest rank (= lowest global index), like a single-device argmax
+        return allp[best.indices, torch.arange(allp.shape[1], device=allp.device), 1].long()
