@@ -123,24 +123,28 @@ class ModelRunner:
                 self._row_state[i] = (s.uid, s.epoch, nb)
         return max_kv
 
-    def _unpack_meta(self, B: int) -> None:
+    def _unpack_meta(self, B: int, skip_ids: bool = False) -> None:
         MB, mb = self.max_batch, self.max_blocks
         m = self._dev_meta
-        self._ids[:B].copy_(m[:B])
+        if not skip_ids:
+            self._ids[:B].copy_(m[:B])
         self._pos[:B].copy_(m[MB:MB + B])
         self._slots[:B].copy_(m[2 * MB:2 * MB + B])
         self._kvl[:B].copy_(m[3 * MB:3 * MB + B])
         self._table[:B].copy_(m[4 * MB:4 * MB + B * mb].view(B, mb))
 
-    def _decode_body(self, B: int, splits: int, want_logits: bool):
-        self._unpack_meta(B)
+    def _decode_body(self, B: int, splits: int, want_logits: bool, feedback: bool = False):
+        self._unpack_meta(B, skip_ids=feedback)
         inp = StepInputs(input_ids=self._ids[:B], positions=self._pos[:B], slot_mapping=self._slots[:B],
                          block_table=self._table[:B], kv_lens=self._kvl[:B], cu_q=None, max_q_len=1, num_seqs=B,
                          decode=True, attn_splits=splits, logits_rows=None)
         hidden = self.model.forward_hidden(inp, self.pool.data)
         if want_logits:
             return None, self.model.logits(hidden)
-        return self.model.greedy_tokens(hidden), None
+        toks = self.model.greedy_tokens(hidden)
+        if feedback:
+            self._ids[:B].copy_(toks)  # the next replay consumes these without a host round trip
+        return toks, None
 
     def decode(self, seqs: list[PagedSequence], tokens: list[int], *, want_logits: bool = False):
         """One decode step: feeds tokens[i] at the end of seqs[i]; returns next greedy tokens as a pinned
@@ -154,7 +158,7 @@ class ModelRunner:
         key = (B, splits, want_logits)
         if not self.use_graphs or self.model.device.type != "cuda":
             toks, logits = self._decode_body(B, splits, want_logits)
-            self.launches_last = self.model.launches + 5
+            self.launches_last = self.model.launches
         else:
             g = self._graphs.get(key)
             if g is None:
@@ -170,16 +174,54 @@ class ModelRunner:
         self.d2h_bytes_last = B * 8
         return self._host_tokens[:B]
 
-    def _capture(self, B: int, splits: int, want_logits: bool) -> _DecodeGraph:
+    def decode_multi(self, seqs: list[PagedSequence], tokens: list[int], n_steps: int) -> torch.Tensor:
+        """n_steps greedy decode steps with the sampled token fed back on the device: the host uploads the
+        metadata of all steps once, then only enqueues one small device copy and one graph launch per step.
+        Returns the generated tokens [n_steps, B] on the device (no synchronisation is performed)."""
+        B = len(seqs)
+        dev = self.model.device
+        n_meta = self._n_meta
+        host_all = torch.empty((n_steps, n_meta), dtype=torch.int32)
+        if dev.type == "cuda":
+            host_all = host_all.pin_memory()
+        max_kv = 0
+        for k in range(n_steps):
+            max_kv = self._fill_decode_meta(seqs, tokens if k == 0 else [0] * B)
+            host_all[k].copy_(self._host_meta)
+        dev_all = host_all.to(dev, non_blocking=True)
+        self.h2d_bytes_last = host_all.numel() * 4
+        splits = _splits_for(B, self.model.hkv, max_kv)
+        out = torch.empty((n_steps, B), dtype=torch.int64, device=dev)
+        self._ids[:B].copy_(torch.tensor(tokens, dtype=torch.int64).to(dev, non_blocking=True))
+        key = (B, splits, "feedback")
+        g = self._graphs.get(key)
+        if g is None and self.use_graphs and dev.type == "cuda":
+            self._dev_meta.copy_(dev_all[0])
+            saved = self._ids[:B].clone()
+            g = self._capture(B, splits, False, feedback=True)
+            self._ids[:B].copy_(saved)
+            self._graphs[key] = g
+        for k in range(n_steps):
+            self._dev_meta.copy_(dev_all[k], non_blocking=True)
+            if g is not None:
+                g.graph.replay()
+                out[k].copy_(g.tokens_out)
+            else:
+                toks, _ = self._decode_body(B, splits, False, feedback=True)
+                out[k].copy_(toks)
+        self.launches_last = (g.launches if g is not None else self.model.launches) * n_steps
+        return out
+
+    def _capture(self, B: int, splits: int, want_logits: bool, feedback: bool = False) -> _DecodeGraph:
         # warm-up on a side stream (sets kernel attributes, fills the tensor-map cache), then capture
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
             for _ in range(2):
-                self._decode_body(B, splits, want_logits)
+                self._decode_body(B, splits, want_logits, feedback)
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            toks, logits = self._decode_body(B, splits, want_logits)
-        return _DecodeGraph(graph, toks, logits, self.model.launches + 5)
+            toks, logits = self._decode_body(B, splits, want_logits, feedback)
+        return _DecodeGraph(graph, toks, logits, self.model.launches)
