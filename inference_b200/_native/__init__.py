@@ -79,7 +79,7 @@ def _declare_kernels(lib: ctypes.CDLL) -> None:
     sig("swb_embedding", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p])
     sig("swb_gated_residual", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p])
     sig("swb_attn_decode_workspace_bytes", [c_int, c_int, c_int], c_size_t)
-    sig("swb_attn_paged", [c_void_p, c_ll, c_int, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_int,
+    sig("swb_attn_paged", [c_void_p, c_ll, c_int, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int,
                            c_int, c_void_p, c_size_t, c_void_p])
     sig("swb_attn_dense", [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int,

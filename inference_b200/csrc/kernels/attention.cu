@@ -11,69 +11,13 @@
 // The KV cache layout is [block, kv_head, block_size, head_dim] so one head's tokens of a block are
 // contiguous. Replaces the reference's gather(index_select) + repeat_kv + FlashAttention-2 varlen /
 // eager SDPA path (candle-llm/src/primitives/attention.rs:59-68,136-302; paged_kv_cache.rs:248-283).
-#include "common.cuh"
+#include "attention_common.cuh"
+#include "gemm_tcgen05.cuh"
 
 namespace swb {
+using namespace attn;
 namespace {
 
-constexpr int HD = 128;
-constexpr int KV_TILE = 64;
-constexpr int TILE_BYTES = KV_TILE * HD * 2;  // 16 KB
-
-struct AttnParams {
-  const bf16* q;
-  long long q_stride_tok;
-  int q_stride_head;
-  bf16* out;
-  long long out_stride_tok;
-  const bf16* k;
-  const bf16* v;
-  const int* block_table;  // non-null => paged
-  int max_blocks;
-  int block_size;
-  long long kv_stride_tok;  // dense layout strides (elements)
-  int kv_stride_head;
-  const int* cu_q;     // [num_seqs + 1] or null (uniform_q_len)
-  const int* cu_k;     // dense only: [num_seqs + 1] or null (uniform_kv_len)
-  const int* kv_lens;  // [num_seqs] or null (uniform_kv_len)
-  int uniform_q_len, uniform_kv_len;
-  int num_seqs, Hq, Hkv, G;
-  float scale;
-  float softcap;
-  int causal;
-  int num_splits;
-  float* part_o;
-  float* part_ml;
-};
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-               : "r"(addr));
-}
-__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-               : "r"(addr));
-}
-__device__ __forceinline__ void mma_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
 // byte offset of 16-byte chunk `c` of row `r` in a [rows][128 bf16] tile with an XOR swizzle
 __device__ __forceinline__ uint32_t tile_off(int r, int c) { return (uint32_t)(r * 256 + ((c ^ (r & 7)) << 4)); }
 
@@ -101,12 +45,6 @@ __device__ __forceinline__ void load_kv_tile(const AttnParams& p, int seq, int k
     cp_async16(sK + off, kr, valid ? 16u : 0u);
     cp_async16(sV + off, vr, valid ? 16u : 0u);
   }
-}
-
-__device__ __forceinline__ float score_transform(float s, float scale, float softcap) {
-  // returns the score in log2 units
-  if (softcap > 0.f) return softcap * tanhf(s * scale / softcap) * 1.4426950408889634f;
-  return s * (scale * 1.4426950408889634f);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -522,6 +460,9 @@ inline int last_err() {
 }
 
 }  // namespace
+
+int attn_decode_tma_launch(const AttnParams& p, int num_blocks, cudaStream_t stream);
+
 }  // namespace swb
 
 extern "C" {
@@ -535,7 +476,7 @@ size_t swb_attn_decode_workspace_bytes(int num_seqs, int Hkv, int num_splits) {
 // mode 0 = prefill (any q_len per sequence, max_q_len bounds the grid); mode 1 = decode (q_len * G <= 16).
 int swb_attn_paged(const void* q, long long q_stride_tok, int q_stride_head, void* out, long long out_stride_tok,
                    const void* kcache, const void* vcache, const int* block_table, int max_blocks, int block_size,
-                   const int* cu_q, const int* kv_lens, int num_seqs, int max_q_len, int Hq, int Hkv, int D,
+                   int num_blocks, const int* cu_q, const int* kv_lens, int num_seqs, int max_q_len, int Hq, int Hkv, int D,
                    float scale, float softcap, int causal, int mode, int num_splits, void* workspace,
                    size_t workspace_bytes, void* stream) {
   using namespace swb;
@@ -579,9 +520,14 @@ int swb_attn_paged(const void* q, long long q_stride_tok, int q_stride_head, voi
     p.part_ml = p.part_o + (size_t)num_seqs * Hkv * num_splits * 16 * HD;
   }
   p.num_splits = num_splits;
-  dim3 grid(num_splits, Hkv, num_seqs);
-  attn_decode_kernel<<<grid, 128, DECODE_SMEM, s>>>(p);
-  rc = last_err();
+  if (block_size == 16 && num_blocks > 0 && kv_lens != nullptr) {
+    // TMA-fed warp-specialised kernel (the cp.async kernel below serves other block sizes)
+    rc = attn_decode_tma_launch(p, num_blocks, s);
+  } else {
+    dim3 grid(num_splits, Hkv, num_seqs);
+    attn_decode_kernel<<<grid, 128, DECODE_SMEM, s>>>(p);
+    rc = last_err();
+  }
   if (rc || num_splits == 1) return rc;
   attn_merge_kernel<<<dim3(Hkv, num_seqs), 128, 0, s>>>(p);
   return last_err();

@@ -21,7 +21,8 @@ def decode_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
 def paged_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
                     kv_lens: torch.Tensor, *, cu_q: torch.Tensor | None, max_q_len: int, scale: float,
                     causal: bool = True, decode: bool = False, num_splits: int = 1, softcap: float = 0.0,
-                    out: torch.Tensor | None = None, workspace: torch.Tensor | None = None) -> torch.Tensor:
+                    out: torch.Tensor | None = None, workspace: torch.Tensor | None = None,
+                    use_tma: bool = True) -> torch.Tensor:
     """q: [T, Hq, 128] (any token/head strides, unit inner stride); caches [blocks, Hkv, block_size, 128];
     block_table int32 [num_seqs, max_blocks]; kv_lens int32 [num_seqs] (context length including the new
     tokens); cu_q int32 [num_seqs + 1] or None when every sequence has exactly max_q_len query tokens.
@@ -42,7 +43,7 @@ def paged_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
         ws_ptr, ws_bytes = workspace.data_ptr(), workspace.numel()
     rc = kernels().swb_attn_paged(q.data_ptr(), q.stride(0), q.stride(1), out.data_ptr(), out.stride(0),
                                   kcache.data_ptr(), vcache.data_ptr(), block_table.data_ptr(), block_table.stride(0),
-                                  bs, ptr(cu_q), kv_lens.data_ptr(), num_seqs, max_q_len, Hq, Hkv, D, scale, softcap,
+                                  bs, kcache.shape[0] if use_tma else 0, ptr(cu_q), kv_lens.data_ptr(), num_seqs, max_q_len, Hq, Hkv, D, scale, softcap,
                                   1 if causal else 0, 1 if decode else 0, num_splits, ws_ptr, ws_bytes, stream_ptr())
     check(rc, "swb_attn_paged")
     return out

@@ -190,9 +190,10 @@ def test_paged_prefill(Hq, Hkv):
         o += n
 
 
+@pytest.mark.parametrize("use_tma", [True, False])
 @pytest.mark.parametrize("splits", [1, 3, 8])
 @pytest.mark.parametrize("q_len", [1, 3])
-def test_paged_decode(splits, q_len):
+def test_paged_decode(splits, q_len, use_tma):
     from inference_b200 import ops
 
     D, Hq, Hkv = 128, 16, 4
@@ -203,7 +204,8 @@ def test_paged_decode(splits, q_len):
     kvl = torch.tensor(kv_lens, dtype=torch.int32, device="cuda")
     scale = 1 / math.sqrt(D)
     out = ops.paged_attention(q, kc, vc, table, kvl, cu_q=None, max_q_len=q_len, scale=scale, causal=True,
-                              decode=True, num_splits=splits)
+                              decode=True, num_splits=splits, use_tma=use_tma)
+    ops.check_status()
     for i in range(B):
         ref = _ref_attn(q[i * q_len:(i + 1) * q_len], ks[i], vs[i], scale, True)
         err = (out[i * q_len:(i + 1) * q_len].float() - ref).abs().max().item()
