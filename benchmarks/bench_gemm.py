@@ -17,10 +17,23 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from inference_b200 import ops
 
 
-def bench(fn, iters):
+def bench(fn, iters, graph=False):
     for _ in range(3):
         fn(0)
     torch.cuda.synchronize()
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(iters):
+                fn(i)
+        g.replay()
+        torch.cuda.synchronize()
+        st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        st.record()
+        g.replay()
+        en.record()
+        torch.cuda.synchronize()
+        return st.elapsed_time(en) / iters
     st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     st.record()
     for i in range(iters):
@@ -37,7 +50,8 @@ def main():
     ap.add_argument("--shapes", default="llama")
     ap.add_argument("--mode", type=int, default=-1)
     ap.add_argument("--block-n", type=int, default=0)
-    ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--ctas", type=int, default=0)
+    ap.add_argument("--graph", action="store_true", help="time a CUDA graph of the iterations (no launch overhead)")
     args = ap.parse_args()
     peaks = {}
     p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
@@ -64,7 +78,7 @@ def main():
         a = (torch.randn(T, K, device="cuda") * 0.5).bfloat16()
         out = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
         ms = bench(lambda i: ops.gemm_bf16(a, ws[i % copies], out=out, mode=args.mode, block_n=args.block_n,
-                                           splits=args.splits), args.iters)
+                                           ctas=args.ctas), args.iters, args.graph)
         ops.check_status()
         flops = 2.0 * T * N * K
         byts = (N * K + T * K + T * N) * 2
@@ -74,7 +88,7 @@ def main():
             row["frac_tflops_of_measured"] = round(row["tflops"] / peaks["bf16_tflops"], 3)
             row["frac_hbm_of_measured"] = round(row["gbs"] / peaks["hbm_gbs"], 3)
         if args.torch:
-            ms_t = bench(lambda i: torch.matmul(a, ws[i % copies].t(), out=out), args.iters)
+            ms_t = bench(lambda i: torch.matmul(a, ws[i % copies].t(), out=out), args.iters, args.graph)
             row["torch_ms"] = round(ms_t, 4)
         rows.append(row)
         print(json.dumps(row), flush=True)

@@ -27,10 +27,10 @@ int swb_sm_count(void);
  * D bf16 or fp32 (out_fp32). act: 0 none, 1 SiLU, 2 tanh-GELU.
  * workspace: >= swb_gemm_workspace_min() bytes, zero-filled once by the caller; it lets small problems
  * split K across CTAs. Calls that share a workspace must be ordered on one stream.
- * force_mode: -1 auto, 0 tokens-as-M, 1 weights-as-M (T <= 256). force_block_n / force_splits: 0 auto. */
+ * force_mode: -1 auto, 0 tokens-as-M, 1 weights-as-M (T <= 256). force_block_n: 0 auto. force_ctas: 0 auto, > 0 stream-K over that many CTAs, < 0 whole tiles only. */
 int swb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* D, int ldd, int T, int N, int K,
                   const void* bias, const void* residual, int ld_res, int act, int out_fp32, void* workspace,
-                  size_t workspace_bytes, int force_mode, int force_block_n, int force_splits,
+                  size_t workspace_bytes, int force_mode, int force_block_n, int force_ctas,
                   swb_stream_t stream);
 size_t swb_gemm_workspace_min(void);
 

@@ -5,7 +5,7 @@ extern "C" {
 
 int swb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* D, int ldd, int T, int N, int K,
                   const void* bias, const void* residual, int ld_res, int act, int out_fp32, void* workspace,
-                  size_t workspace_bytes, int force_mode, int force_block_n, int force_splits, void* stream) {
+                  size_t workspace_bytes, int force_mode, int force_block_n, int force_ctas, void* stream) {
   swb::GemmArgs a;
   a.A = A;
   a.lda = lda;
@@ -25,7 +25,7 @@ int swb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* D, int l
   a.workspace_bytes = workspace_bytes;
   a.force_mode = force_mode;
   a.force_block_n = force_block_n;
-  a.force_splits = force_splits;
+  a.force_ctas = force_ctas;
   return swb::gemm_bf16_launch(a, reinterpret_cast<cudaStream_t>(stream));
 }
 

@@ -51,6 +51,8 @@ __device__ __forceinline__ void load_kv_tile(const AttnParams& p, int seq, int k
 // prefill / dense attention
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t sQ = smem_u32(smem);
   const uint32_t sKV = sQ + TILE_BYTES;  // stage s: K at sKV + s*2*TILE, V at + TILE
@@ -222,6 +224,8 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnParams p) {
 // decode attention (<= 16 packed rows = query tokens x GQA group heads)
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t sQ = smem_u32(smem);           // 16 rows x 256 B = 4 KB
   const uint32_t sKV = sQ + 16 * 256;            // 2 stages x (K, V)
@@ -413,6 +417,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
 }
 
 __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int kvh = blockIdx.x;
   const int seq = blockIdx.y;
   const int q_start = p.cu_q ? p.cu_q[seq] : seq * p.uniform_q_len;
@@ -454,10 +460,8 @@ int configure_once() {
   return 0;
 }
 
-inline int last_err() {
-  cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? 0 : -(int)e;
-}
+static thread_local int launch_rc = 0;
+inline int last_err() { return launch_rc; }
 
 }  // namespace
 
@@ -509,7 +513,7 @@ int swb_attn_paged(const void* q, long long q_stride_tok, int q_stride_head, voi
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (mode == 0) {
     dim3 grid((max_q_len + 63) / 64, Hq, num_seqs);
-    attn_prefill_kernel<<<grid, 128, PREFILL_SMEM, s>>>(p);
+    launch_rc = launch_kernel(attn_prefill_kernel, dim3(grid), dim3(128), PREFILL_SMEM, s, p);
     return last_err();
   }
   if (max_q_len * p.G > 16) return -4;
@@ -525,11 +529,11 @@ int swb_attn_paged(const void* q, long long q_stride_tok, int q_stride_head, voi
     rc = attn_decode_tma_launch(p, num_blocks, s);
   } else {
     dim3 grid(num_splits, Hkv, num_seqs);
-    attn_decode_kernel<<<grid, 128, DECODE_SMEM, s>>>(p);
+    launch_rc = launch_kernel(attn_decode_kernel, dim3(grid), dim3(128), DECODE_SMEM, s, p);
     rc = last_err();
   }
   if (rc || num_splits == 1) return rc;
-  attn_merge_kernel<<<dim3(Hkv, num_seqs), 128, 0, s>>>(p);
+  launch_rc = launch_kernel(attn_merge_kernel, dim3(dim3(Hkv, num_seqs)), dim3(128), 0, s, p);
   return last_err();
 }
 
@@ -565,7 +569,7 @@ int swb_attn_dense(const void* q, long long q_stride_tok, int q_stride_head, con
   p.causal = causal;
   p.num_splits = 1;
   dim3 grid((q_len + 63) / 64, Hq, batch);
-  attn_prefill_kernel<<<grid, 128, PREFILL_SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  launch_rc = launch_kernel(attn_prefill_kernel, dim3(grid), dim3(128), PREFILL_SMEM, reinterpret_cast<cudaStream_t>(stream), p);
   return last_err();
 }
 

@@ -36,6 +36,7 @@ __device__ __forceinline__ uint32_t q_off(int r, int c) { return (uint32_t)(r * 
 __global__ void __launch_bounds__(160) attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap_k,
                                                               const __grid_constant__ CUtensorMap tmap_v,
                                                               const AttnParams p) {
+  pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
@@ -51,16 +52,6 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(const __grid_const
   const int seq = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  const int q_start = p.cu_q ? p.cu_q[seq] : seq * p.uniform_q_len;
-  const int q_len = p.cu_q ? p.cu_q[seq + 1] - q_start : p.uniform_q_len;
-  const int kv_len = p.kv_lens[seq];
-  const int nrows = min(16, q_len * p.G);
-  const int causal_shift = kv_len - q_len;
-  const int total_tiles = (kv_len + KV_TILE - 1) / KV_TILE;
-  const int per = (total_tiles + p.num_splits - 1) / p.num_splits;
-  const int t0 = split * per;
-  const int n_tiles = max(0, min(total_tiles, t0 + per) - t0);
-
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&bar_full[s], 1);
@@ -71,6 +62,18 @@ __global__ void __launch_bounds__(160) attn_decode_tma_kernel(const __grid_const
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
   }
+  pdl_wait();  // everything below reads what the preceding kernels wrote (q, the newest K/V, kv_lens)
+
+  const int q_start = p.cu_q ? p.cu_q[seq] : seq * p.uniform_q_len;
+  const int q_len = p.cu_q ? p.cu_q[seq + 1] - q_start : p.uniform_q_len;
+  const int kv_len = p.kv_lens[seq];
+  const int nrows = min(16, q_len * p.G);
+  const int causal_shift = kv_len - q_len;
+  const int total_tiles = (kv_len + KV_TILE - 1) / KV_TILE;
+  const int per = (total_tiles + p.num_splits - 1) / p.num_splits;
+  const int t0 = split * per;
+  const int n_tiles = max(0, min(total_tiles, t0 + per) - t0);
+
   // Q rows -> shared (row r = query token r / G, head kvh * G + r % G), zero rows past nrows
   for (int idx = threadIdx.x; idx < 256; idx += blockDim.x) {
     const int row = idx >> 4, c = idx & 15;
@@ -296,9 +299,7 @@ int attn_decode_tma_launch(const AttnParams& p, int num_blocks, cudaStream_t str
   rc = make_tmap_bf16_2d(&tv, p.v, rows, HD, HD, 16);
   if (rc) return rc;
   dim3 grid(p.num_splits, p.Hkv, p.num_seqs);
-  attn_decode_tma_kernel<<<grid, 160, SMEM_BYTES, stream>>>(tk, tv, p);
-  cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? 0 : -(int)e;
+  return launch_kernel(attn_decode_tma_kernel, grid, dim3(160), SMEM_BYTES, stream, tk, tv, p);
 }
 
 }  // namespace swb

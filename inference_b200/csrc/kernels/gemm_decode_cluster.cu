@@ -1,0 +1,350 @@
+// Decode-sized bf16 GEMM (tokens <= 64) as a thread-block-cluster split-K kernel for sm_100a.
+//
+// out[T, N] = act(x[T, K] * W[N, K]^T + bias) + residual with T <= 64 is pure weight streaming: the
+// roofline is HBM bandwidth, and one 128-row weight tile per CTA leaves most SMs idle (N = 4096 gives 32
+// tiles for 148 SMs). Here a cluster of 2/4/8 CTAs shares one weight tile and splits K between its
+// members; each member streams its K range by TMA into a small ring (two CTAs fit per SM), accumulates
+// with tcgen05.mma into TMEM (weights as the M = 128 operand, tokens as N), then the partial tiles are
+// reduce-scattered through distributed shared memory: member r receives every member's columns
+// [r * BLOCK_N / C, (r + 1) * BLOCK_N / C) by st.shared::cluster, sums them in a fixed order
+// (deterministic) and runs the fused epilogue for its slice. No global workspace, atomics or fences.
+// The weight operand does not depend on the preceding kernel, so its first stages are requested before
+// the programmatic-dependent-launch wait.
+#include "common.cuh"
+#include "gemm_tcgen05.cuh"
+
+namespace swb {
+
+SWB_REGISTER_STATUS_UNIT(gemm_decode_cluster);
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int THREADS = 192;
+
+template <int BLOCK_N>
+struct DecCfg {
+  static constexpr int STAGES = BLOCK_N >= 64 ? 3 : 4;
+  static constexpr uint32_t A_BYTES = BM * BK * 2;
+  static constexpr uint32_t B_BYTES = BLOCK_N * BK * 2;
+  static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr uint32_t RECV_BYTES = BM * BLOCK_N * 4;  // CLUSTER slots of [128][BLOCK_N / CLUSTER] fp32
+  static constexpr uint32_t TMEM_COLS = BLOCK_N < 32 ? 32 : BLOCK_N;
+  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + RECV_BYTES + 1024 + 256;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32x4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+__device__ __forceinline__ void st_cluster_f32x2(uint32_t addr, float a, float b) {
+  asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(a), "f"(b) : "memory");
+}
+
+__device__ __forceinline__ float act_apply(float x, int act) {
+  if (act == SWB_ACT_SILU) return silu_f(x);
+  if (act == SWB_ACT_GELU_TANH) return gelu_tanh_f(x);
+  return x;
+}
+
+template <int BLOCK_N, int CLUSTER>
+__global__ void __launch_bounds__(THREADS, 2)
+gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                           const GemmParams p) {
+  using Cfg = DecCfg<BLOCK_N>;
+  constexpr int STAGES = Cfg::STAGES;
+  constexpr int SL = BLOCK_N / CLUSTER;  // columns (tokens) owned by each cluster member
+  constexpr int VEC = SL >= 4 ? 4 : SL;
+  static_assert(SL >= 2, "slice too narrow");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  float* recv = reinterpret_cast<float*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES + Cfg::RECV_BYTES);
+  uint64_t* bar_empty = bar_full + STAGES;
+  uint64_t* bar_tfull = bar_empty + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tfull + 1);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t crank = CLUSTER > 1 ? cluster_ctarank() : 0u;
+  const int tile_m = (int)blockIdx.x / CLUSTER;
+  const int kps = (p.kblocks_total + CLUSTER - 1) / CLUSTER;
+  const int kb0 = (int)crank * kps;
+  const int kb1 = min(p.kblocks_total, kb0 + kps);
+  const int nkb = max(0, kb1 - kb0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&bar_full[s], 1);
+      mbar_init(&bar_empty[s], 1);
+    }
+    mbar_init(bar_tfull, 1);
+    *s_abort = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  if (CLUSTER > 1) cluster_arrive();  // phase 1: "my shared memory is live" (waited on before remote stores)
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint64_t pol_w = l2_policy_evict_first();
+      const uint64_t pol_x = l2_policy_evict_last();
+      const int pre = min(STAGES, nkb);
+      for (int i = 0; i < pre; ++i) {
+        mbar_arrive_expect_tx(&bar_full[i], Cfg::STAGE_BYTES);
+        tma_load_2d_hint(smem + i * Cfg::STAGE_BYTES, &tmap_w, &bar_full[i], (kb0 + i) * BK, tile_m * BM, pol_w);
+      }
+      pdl_wait();
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t outstanding = (pre >= 32) ? 0xffffffffu : ((1u << pre) - 1u);
+      uint32_t issue_phase_bits = 0;
+      for (int i = 0; i < nkb; ++i) {
+        uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
+        uint8_t* sb = sa + Cfg::A_BYTES;
+        if (i >= pre) {
+          if (!mbar_wait(&bar_empty[stage], phase ^ 1, s_abort, 700 + stage)) break;
+          mbar_arrive_expect_tx(&bar_full[stage], Cfg::STAGE_BYTES);
+          tma_load_2d_hint(sa, &tmap_w, &bar_full[stage], (kb0 + i) * BK, tile_m * BM, pol_w);
+          outstanding |= 1u << stage;
+          issue_phase_bits = (issue_phase_bits & ~(1u << stage)) | (phase << stage);
+        }
+        tma_load_2d_hint(sb, &tmap_x, &bar_full[stage], (kb0 + i) * BK, 0, pol_x);
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (*s_abort) {
+        for (int s = 0; s < STAGES; ++s)
+          if (outstanding & (1u << s))
+            for (int it = 0; it < (1 << 20); ++it)
+              if (mbar_try_wait(&bar_full[s], (issue_phase_bits >> s) & 1u)) break;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, BLOCK_N);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int i = 0; i < nkb; ++i) {
+        ok = mbar_wait(&bar_full[stage], phase, s_abort, 800 + stage);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+        const uint64_t adesc = umma_desc_kmajor_sw128(sa);
+        const uint64_t bdesc = umma_desc_kmajor_sw128(sa + Cfg::A_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k)
+          umma_f16_ss(tmem_base, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (i > 0 || k > 0) ? 1u : 0u);
+        umma_commit(&bar_empty[stage]);
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (ok && nkb > 0) umma_commit(bar_tfull);
+    }
+  }
+
+  // ---- all threads: make sure every member's shared memory is live before any remote store ----
+  __syncwarp();
+  if (CLUSTER > 1) cluster_wait();
+
+  if (warp >= 2) {
+    pdl_wait();
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    bool have = nkb > 0;
+    if (have) have = mbar_wait(bar_tfull, 0, s_abort, 900);
+    have = __all_sync(0xffffffffu, have);  // warp-uniform: tcgen05.ld is warp-collective
+    tc_fence_after_sync();
+    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t recv_local = smem_u32(recv);
+#pragma unroll 1
+    for (int ch = 0; ch < BLOCK_N / 16; ++ch) {
+      float v[16];
+      if (have) {
+        tmem_ld_32x32b_x16(taddr + ch * 16, v);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 16; j += VEC) {
+        const int col = ch * 16 + j;
+        const uint32_t dest = (uint32_t)(col / SL);
+        // slot `crank` of the destination's receive buffer, [row][SL] fp32
+        const uint32_t off = (uint32_t)(((crank * BM + row) * SL + (col % SL)) * 4);
+        const uint32_t addr = CLUSTER > 1 ? map_to_cta(recv_local + off, dest) : recv_local + off;
+        if (VEC == 4)
+          st_cluster_f32x4(addr, v[j], v[j + 1], v[j + 2], v[j + 3]);
+        else
+          st_cluster_f32x2(addr, v[j], v[j + 1]);
+      }
+    }
+    tc_fence_before_sync();
+  }
+
+  // ---- phase 2: every partial slice has been delivered ----
+  __syncwarp();
+  if (CLUSTER > 1) {
+    cluster_arrive();
+    cluster_wait();
+  } else {
+    __syncthreads();
+  }
+
+  if (warp >= 2) {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int feat = tile_m * BM + row;
+    if (feat < p.M) {
+      const float b = p.bias ? __bfloat162float(p.bias[feat]) : 0.f;
+#pragma unroll
+      for (int c = 0; c < SL; ++c) {
+        const int tok = (int)crank * SL + c;
+        if (tok >= p.N) break;
+        float acc = 0.f;
+#pragma unroll
+        for (int src = 0; src < CLUSTER; ++src) acc += recv[(src * BM + row) * SL + c];
+        float x = act_apply(acc + b, p.act);
+        if (p.residual) x += __bfloat162float(p.residual[(size_t)tok * p.ld_res + feat]);
+        const size_t off = (size_t)tok * p.ldd + feat;
+        if (p.out_fp32)
+          reinterpret_cast<float*>(p.out)[off] = x;
+        else
+          reinterpret_cast<bf16*>(p.out)[off] = __float2bfloat16(x);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+template <int BLOCK_N, int CLUSTER>
+int launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
+  using Cfg = DecCfg<BLOCK_N>;
+  auto kern = gemm_decode_cluster_kernel<BLOCK_N, CLUSTER>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return -(int)e;
+    configured[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.tiles_m * CLUSTER);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (CLUSTER > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = CLUSTER;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  if (pdl_enabled()) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, tx, p);
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
+template <int BLOCK_N>
+int launch_cluster(int cluster, const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t s) {
+  switch (cluster) {
+    case 1: return launch_one<BLOCK_N, 1>(tw, tx, p, s);
+    case 2: return launch_one<BLOCK_N, 2>(tw, tx, p, s);
+    case 4: return launch_one<BLOCK_N, 4>(tw, tx, p, s);
+    case 8: return launch_one<BLOCK_N, 8>(tw, tx, p, s);
+  }
+  return -2;
+}
+
+}  // namespace
+
+// Returns 1 when the cluster kernel takes this problem (T <= 64), 0 when the caller should use the general kernel.
+int gemm_decode_cluster_supported(int T) { return T >= 1 && T <= 64; }
+
+int gemm_decode_cluster_launch(const GemmArgs& a, int force_cluster, cudaStream_t stream) {
+  const int sms = device_sm_count();
+  const int block_n = a.T <= 16 ? 16 : a.T <= 32 ? 32 : 64;
+  GemmParams p{};
+  p.M = a.N;
+  p.N = a.T;
+  p.K = a.K;
+  p.kblocks_total = (a.K + BK - 1) / BK;
+  p.tiles_m = (a.N + BM - 1) / BM;
+  p.tiles_n = 1;
+  p.transposed = 1;
+  p.stream_a = 1;
+  p.ldd = a.ldd;
+  p.out = a.D;
+  p.out_fp32 = a.out_fp32;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(a.bias);
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(a.residual);
+  p.ld_res = a.ld_res;
+  p.act = a.act;
+  // two CTAs are resident per SM: take the largest power-of-two cluster that keeps one resident wave
+  int cluster = 1;
+  while (cluster < 8 && (long)p.tiles_m * (cluster * 2) <= 2L * sms && p.kblocks_total / (cluster * 2) >= 4) cluster *= 2;
+  if (force_cluster > 0) cluster = force_cluster;
+  while (cluster > 1 && (block_n / cluster) < 2) cluster /= 2;
+  CUtensorMap tw, tx;
+  int r = make_tmap_bf16_2d(&tw, a.W, a.N, a.K, a.ldw, BM);
+  if (r) return r;
+  r = make_tmap_bf16_2d(&tx, a.A, a.T, a.K, a.lda, block_n);
+  if (r) return r;
+  switch (block_n) {
+    case 16: return launch_cluster<16>(cluster, tw, tx, p, stream);
+    case 32: return launch_cluster<32>(cluster, tw, tx, p, stream);
+    default: return launch_cluster<64>(cluster, tw, tx, p, stream);
+  }
+}
+
+}  // namespace swb

@@ -30,9 +30,15 @@ constexpr int BK = 64;
 constexpr int GEMM_THREADS = 192;
 constexpr int GROUP_M = 8;
 
-template <int BLOCK_N>
+// Decode-sized (swapped) problems are bandwidth bound: their pipelines are sized so two CTAs share an
+// SM, which lets a dependent kernel's CTAs (programmatic dependent launch) become resident and prefetch
+// weights while the predecessor drains. Large problems take the whole SM for one deep pipeline.
+template <int BLOCK_N, bool SWAPPED>
 struct GemmCfg {
-  static constexpr int STAGES = BLOCK_N >= 256 ? 4 : (BLOCK_N >= 128 ? 6 : 8);
+  static constexpr bool TWO_PER_SM = false;  // (decode-sized problems that want two CTAs per SM use the cluster kernel)
+  static constexpr int STAGES = TWO_PER_SM ? (BLOCK_N >= 128 ? 3 : (BLOCK_N >= 64 ? 4 : 5))
+                                           : (BLOCK_N >= 256 ? 4 : (BLOCK_N >= 128 ? 6 : 8));
+  static constexpr int MIN_CTAS = TWO_PER_SM ? 2 : 1;
   static constexpr uint32_t A_BYTES = BM * BK * 2;
   static constexpr uint32_t B_BYTES = BLOCK_N * BK * 2;
   static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -40,23 +46,52 @@ struct GemmCfg {
   static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
-struct UnitCoord {
-  int tile, split, tm, tn;
+// One contiguous run of k-blocks of one output tile, as processed by one CTA.
+struct Seg {
+  int tile, tm, tn, kb0, kb1;
+  bool first;  // first segment of this CTA (selects the partial-sum slot)
 };
 
-__device__ __forceinline__ UnitCoord decode_unit(const GemmParams& p, int u) {
-  UnitCoord c;
-  c.tile = u / p.splits;
-  c.split = u - c.tile * p.splits;
-  const int per_group = GROUP_M * p.tiles_n;
-  const int g = c.tile / per_group;
-  const int first_m = g * GROUP_M;
-  const int gsize = min(GROUP_M, p.tiles_m - first_m);
-  const int r = c.tile - g * per_group;
-  c.tm = first_m + r % gsize;
-  c.tn = r / gsize;
-  return c;
-}
+// Work decomposition shared by the three warp roles so they walk identical segment sequences.
+//  * data parallel: CTA c owns whole tiles c, c + grid, ...
+//  * stream-K: the tiles x k-blocks iteration space is cut into equal contiguous ranges, one per CTA; a
+//    CTA's range may start and end inside a tile, those partial tiles are reduced through the workspace.
+struct SegIter {
+  const GemmParams& p;
+  int it, it_end, next_tile, nseg;
+  __device__ explicit SegIter(const GemmParams& pp) : p(pp), nseg(0) {
+    it = (int)blockIdx.x * p.iters_per_cta;
+    it_end = min(it + p.iters_per_cta, p.tiles_m * p.tiles_n * p.kblocks_total);
+    next_tile = (int)blockIdx.x;
+  }
+  __device__ __forceinline__ void coords(Seg& s) const {
+    const int per_group = GROUP_M * p.tiles_n;
+    const int g = s.tile / per_group;
+    const int first_m = g * GROUP_M;
+    const int gsize = min(GROUP_M, p.tiles_m - first_m);
+    const int r = s.tile - g * per_group;
+    s.tm = first_m + r % gsize;
+    s.tn = r / gsize;
+  }
+  __device__ __forceinline__ bool next(Seg& s) {
+    if (p.stream_k) {
+      if (it >= it_end) return false;
+      s.tile = it / p.kblocks_total;
+      s.kb0 = it - s.tile * p.kblocks_total;
+      s.kb1 = min(p.kblocks_total, s.kb0 + (it_end - it));
+      it += s.kb1 - s.kb0;
+    } else {
+      if (next_tile >= p.tiles_m * p.tiles_n) return false;
+      s.tile = next_tile;
+      s.kb0 = 0;
+      s.kb1 = p.kblocks_total;
+      next_tile += (int)gridDim.x;
+    }
+    s.first = (nseg++ == 0);
+    coords(s);
+    return true;
+  }
+};
 
 __device__ __forceinline__ float apply_act(float x, int act) {
   if (act == SWB_ACT_SILU) return silu_f(x);
@@ -144,10 +179,10 @@ __device__ __forceinline__ void epilogue_store16(const GemmParams& p, float* v, 
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 template <int BLOCK_N, bool TRANSPOSED>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS, (GemmCfg<BLOCK_N, TRANSPOSED>::MIN_CTAS))
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          const GemmParams p) {
-  using Cfg = GemmCfg<BLOCK_N>;
+  using Cfg = GemmCfg<BLOCK_N, TRANSPOSED>;
   constexpr int STAGES = Cfg::STAGES;
 
   extern __shared__ uint8_t smem_raw[];
@@ -187,8 +222,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-
-  const int total_units = p.tiles_m * p.tiles_n * p.splits;
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -200,16 +234,41 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       uint32_t outstanding = 0;       // stages whose TMA was issued and not yet known consumed
       uint32_t issue_phase_bits = 0;  // parity each outstanding stage's full barrier will complete
       bool ok = true;
-      for (int u = blockIdx.x; ok && u < total_units; u += gridDim.x) {
-        const UnitCoord c = decode_unit(p, u);
-        const int kb0 = c.split * p.kblocks_per_split;
-        const int kb1 = min(kb0 + p.kblocks_per_split, p.kblocks_total);
-        for (int kb = kb0; kb < kb1; ++kb) {
+      Seg c;
+      // A static weight operand does not depend on the predecessor kernel: start streaming it into the
+      // (still empty) ring before waiting on the programmatic dependency.
+      int prefetched = 0;
+      if (p.stream_a) {
+        SegIter pre(p);
+        while (prefetched < STAGES && pre.next(c)) {
+          for (int kb = c.kb0; kb < c.kb1 && prefetched < STAGES; ++kb) {
+            uint8_t* sa = smem + prefetched * Cfg::STAGE_BYTES;
+            mbar_arrive_expect_tx(&bar_full[prefetched], Cfg::STAGE_BYTES);
+            tma_load_2d_hint(sa, &tmap_a, &bar_full[prefetched], kb * BK, c.tm * BM, pol_a);
+            outstanding |= 1u << prefetched;
+            ++prefetched;
+          }
+        }
+      }
+      pdl_wait();
+      int issued = 0;
+      SegIter iter(p);
+      while (ok && iter.next(c)) {
+        for (int kb = c.kb0; kb < c.kb1; ++kb, ++issued) {
+          uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
+          uint8_t* sb = sa + Cfg::A_BYTES;
+          if (issued < prefetched) {
+            // the A half of this stage is already in flight (first pass over the ring: stage == issued)
+            tma_load_2d_hint(sb, &tmap_b, &bar_full[stage], kb * BK, c.tn * BLOCK_N, pol_b);
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1;
+            }
+            continue;
+          }
           ok = mbar_wait(&bar_empty[stage], phase ^ 1, s_abort, 100 + stage);
           if (!ok) break;
           outstanding &= ~(1u << stage);
-          uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
-          uint8_t* sb = sa + Cfg::A_BYTES;
           mbar_arrive_expect_tx(&bar_full[stage], Cfg::STAGE_BYTES);
           tma_load_2d_hint(sa, &tmap_a, &bar_full[stage], kb * BK, c.tm * BM, pol_a);
           tma_load_2d_hint(sb, &tmap_b, &bar_full[stage], kb * BK, c.tn * BLOCK_N, pol_b);
@@ -241,10 +300,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int u = blockIdx.x; ok && u < total_units; u += gridDim.x) {
-        const UnitCoord c = decode_unit(p, u);
-        const int kb0 = c.split * p.kblocks_per_split;
-        const int kb1 = min(kb0 + p.kblocks_per_split, p.kblocks_total);
+      SegIter iter(p);
+      Seg c;
+      pdl_wait();
+      while (ok && iter.next(c)) {
+        const int kb0 = c.kb0, kb1 = c.kb1;
         ok = mbar_wait(&bar_tempty[acc], acc_phase ^ 1, s_abort, 200 + acc);
         if (!ok) break;
         tc_fence_after_sync();
@@ -282,15 +342,18 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int u = blockIdx.x; ok && u < total_units; u += gridDim.x) {
-      const UnitCoord c = decode_unit(p, u);
+    SegIter iter(p);
+    Seg c;
+    pdl_wait();
+    while (ok && iter.next(c)) {
       ok = mbar_wait(&bar_tfull[acc], acc_phase, s_abort, 400 + acc);
       if (!ok) break;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BLOCK_N);
       const int row = c.tm * BM + row_in_tile;
       const int col_base = c.tn * BLOCK_N;
-      if (p.splits == 1) {
+      const bool whole = (c.kb0 == 0 && c.kb1 == p.kblocks_total);
+      if (whole) {
 #pragma unroll 1
         for (int ch = 0; ch < BLOCK_N / 16; ++ch) {
           float v[16];
@@ -301,7 +364,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar_tempty[acc]);
       } else {
-        float* ws_mine = p.workspace + ((size_t)c.tile * p.splits + c.split) * (size_t)(BLOCK_N * BM);
+        // partial tile: park fp32 partial sums in this CTA's slot, the last contributor reduces them
+        constexpr size_t SLOT = (size_t)BLOCK_N * BM;
+        float* ws_mine = p.workspace + ((size_t)blockIdx.x * 2 + (c.first ? 0 : 1)) * SLOT;
 #pragma unroll 1
         for (int ch = 0; ch < BLOCK_N / 16; ++ch) {
           float v[16];
@@ -312,25 +377,30 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar_tempty[acc]);
+        const int tile_it0 = c.tile * p.kblocks_total;
+        const int first_cta = tile_it0 / p.iters_per_cta;
+        const int last_cta = (tile_it0 + p.kblocks_total - 1) / p.iters_per_cta;
+        const int contributors = last_cta - first_cta + 1;
         __threadfence();
         epi_bar_sync();
         if (epi_tid == 0) {
           const int old = atomicAdd(&p.counters[c.tile], 1);
-          const int last = (old == p.splits - 1) ? 1 : 0;
+          const int last = (old == contributors - 1) ? 1 : 0;
           if (last) p.counters[c.tile] = 0;  // ready for the next launch
           *s_last = last;
         }
         epi_bar_sync();
         if (*s_last) {
           __threadfence();
-          const float* ws_tile = p.workspace + (size_t)c.tile * p.splits * (size_t)(BLOCK_N * BM);
 #pragma unroll 1
           for (int ch = 0; ch < BLOCK_N / 16; ++ch) {
             float v[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = 0.f;
-            for (int s = 0; s < p.splits; ++s) {
-              const float* wsp = ws_tile + (size_t)s * (BLOCK_N * BM) + (ch * 16) * BM + row_in_tile;
+            for (int cta = first_cta; cta <= last_cta; ++cta) {
+              // a contributor whose range starts inside this tile used slot 0, otherwise slot 1
+              const int slot = (cta * p.iters_per_cta >= tile_it0) ? 0 : 1;
+              const float* wsp = p.workspace + ((size_t)cta * 2 + slot) * SLOT + (ch * 16) * BM + row_in_tile;
 #pragma unroll
               for (int j = 0; j < 16; ++j) v[j] += __ldcg(&wsp[j * BM]);
             }
@@ -433,7 +503,7 @@ namespace {
 
 template <int BLOCK_N, bool TRANSPOSED>
 int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
-  using Cfg = GemmCfg<BLOCK_N>;
+  using Cfg = GemmCfg<BLOCK_N, TRANSPOSED>;
   auto kern = gemm_bf16_tcgen05_kernel<BLOCK_N, TRANSPOSED>;
   static bool configured[64] = {false};
   int dev = 0;
@@ -443,9 +513,7 @@ int launch_cfg(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p
     if (e != cudaSuccess) return -(int)e;
     configured[dev] = true;
   }
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta, tb, p);
-  cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? 0 : -(int)e;
+  return launch_kernel(kern, dim3(grid), dim3(GEMM_THREADS), Cfg::SMEM_BYTES, stream, ta, tb, p);
 }
 
 template <bool TRANSPOSED>
@@ -461,28 +529,6 @@ int launch_bn(int block_n, const CUtensorMap& ta, const CUtensorMap& tb, const G
   return -2;
 }
 
-int pick_splits(int tiles, int kblocks, int sms, int max_splits) {
-  if (tiles >= sms || kblocks < 8) return 1;
-  int best = 1;
-  double best_eff = 0.0;
-  const int smax = std::min(max_splits, kblocks / 4);
-  for (int s = 1; s <= smax; ++s) {
-    const int kps = (kblocks + s - 1) / s;
-    const int real = (kblocks + kps - 1) / kps;
-    if (real != s) continue;
-    const long units = (long)tiles * s;
-    const long waves = (units + sms - 1) / sms;
-    // each wave costs kps k-blocks plus a fixed per-unit overhead of roughly 3 k-blocks (fill + epilogue)
-    const double cost = (double)waves * (kps + 3.0);
-    const double eff = 1.0 / cost;
-    if (eff > best_eff * 1.03) {
-      best_eff = eff;
-      best = s;
-    }
-  }
-  return best;
-}
-
 }  // namespace
 
 int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
@@ -493,6 +539,13 @@ int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
 
   int swapped = a.force_mode;
   if (swapped < 0) swapped = (a.T <= 256) ? 1 : 0;
+  // decode-sized problems with fewer weight tiles than SMs: cluster split-K with a DSMEM reduction
+  if (a.force_mode == 2 || (a.force_mode < 0 && gemm_decode_cluster_supported(a.T) && (a.N + BM - 1) / BM < sms &&
+                            (a.K + BK - 1) / BK >= 8)) {
+    if (!gemm_decode_cluster_supported(a.T)) return -4;
+    return gemm_decode_cluster_launch(a, a.force_mode == 2 ? a.force_ctas : 0, stream);
+  }
+  if (swapped > 1) swapped = 1;
 
   GemmParams p{};
   p.K = a.K;
@@ -545,27 +598,33 @@ int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
 
   const int tiles = p.tiles_m * p.tiles_n;
   const size_t counter_bytes = SWB_GEMM_COUNTER_BYTES;
-  const size_t tile_bytes = (size_t)block_n * BM * sizeof(float);
-  int max_splits = 0;
-  if (a.workspace && a.workspace_bytes > counter_bytes && tiles <= (int)(counter_bytes / sizeof(int))) {
-    const size_t cap = (a.workspace_bytes - counter_bytes) / tile_bytes;
-    max_splits = (int)std::min<size_t>(16, cap / (size_t)tiles);
+  const size_t slot_bytes = (size_t)block_n * BM * sizeof(float);
+  const long total_iters = (long)tiles * p.kblocks_total;
+  // stream-K needs two partial slots per CTA and one counter per tile
+  const bool ws_ok = a.workspace && a.workspace_bytes >= counter_bytes + (size_t)4 * sms * slot_bytes &&
+                     tiles <= (int)(counter_bytes / sizeof(int));
+  int grid;
+  // decode-sized (swapped) problems are bandwidth bound and rarely fill a wave of whole tiles: balance them
+  // exactly; large token counts keep whole tiles per CTA (no partial-tile reduction traffic)
+  bool stream_k = ws_ok && a.force_ctas >= 0 && swapped && (tiles % sms != 0) && total_iters >= 2;
+  if (a.force_ctas > 0 && ws_ok) stream_k = true;
+  if (stream_k) {
+    const int per_sm = 1;
+    int want = a.force_ctas > 0 ? std::min(a.force_ctas, per_sm * sms) : per_sm * sms;
+    // keep at least 4 k-blocks per CTA so the pipeline fill is amortised
+    want = (int)std::max<long>(1, std::min<long>(want, total_iters / 4 > 0 ? total_iters / 4 : 1));
+    const int per = (int)((total_iters + want - 1) / want);
+    grid = (int)((total_iters + per - 1) / per);
+    p.iters_per_cta = per;
+    p.stream_k = 1;
+  } else {
+    grid = std::min(tiles, sms);
+    p.iters_per_cta = p.kblocks_total;
+    p.stream_k = 0;
   }
-  int splits = 1;
-  if (a.force_splits > 0)
-    splits = std::min(a.force_splits, std::max(1, max_splits));
-  else if (max_splits > 1)
-    splits = pick_splits(tiles, p.kblocks_total, sms, max_splits);
-  splits = std::max(1, std::min(splits, p.kblocks_total));
-  int kps = (p.kblocks_total + splits - 1) / splits;
-  splits = (p.kblocks_total + kps - 1) / kps;
-  p.splits = splits;
-  p.kblocks_per_split = kps;
   p.counters = reinterpret_cast<int*>(a.workspace);
-  p.workspace = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a.workspace) + counter_bytes);
-
-  const int units = tiles * splits;
-  const int grid = std::min(units, sms);
+  p.workspace = a.workspace ? reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(a.workspace) + counter_bytes)
+                            : nullptr;
   return swapped ? launch_bn<true>(block_n, ta, tb, p, grid, stream) : launch_bn<false>(block_n, ta, tb, p, grid, stream);
 }
 

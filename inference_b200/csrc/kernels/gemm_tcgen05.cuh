@@ -17,7 +17,9 @@ constexpr size_t SWB_GEMM_COUNTER_BYTES = 64 * 1024;
 // Kernel-level problem: D[M, N] = A[M, K] * B[N, K]^T, possibly stored transposed.
 struct GemmParams {
   int M, N, K;
-  int tiles_m, tiles_n, splits, kblocks_per_split, kblocks_total;
+  int tiles_m, tiles_n, kblocks_total;
+  int stream_k;       // 1: contiguous (tile, k-block) ranges per CTA; 0: whole tiles, strided over CTAs
+  int iters_per_cta;  // stream-K range length in k-block iterations
   int transposed;  // 1: rows of the tile are output features, columns are tokens
   int stream_a;    // 1: A is a weight read once (L2 evict-first)
   int vec_ok;      // 16-byte vector epilogue accesses are legal
@@ -49,12 +51,14 @@ struct GemmArgs {
   int out_fp32;
   void* workspace;
   size_t workspace_bytes;
-  int force_mode;     // -1 auto, 0 tokens-as-M, 1 swapped (weights-as-M)
+  int force_mode;     // -1 auto, 0 tokens-as-M, 1 swapped (weights-as-M), 2 cluster split-K (T <= 64; force_ctas = cluster size)
   int force_block_n;  // 0 auto
-  int force_splits;   // 0 auto
+  int force_ctas;     // 0 auto; > 0 stream-K over that many CTAs; < 0 whole tiles only
 };
 
 int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream);
+int gemm_decode_cluster_supported(int T);
+int gemm_decode_cluster_launch(const GemmArgs& a, int force_cluster, cudaStream_t stream);
 int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows);
 int device_sm_count();
 

@@ -44,6 +44,8 @@ template <int THREADS, int VPT>
 __global__ void __launch_bounds__(THREADS) rmsnorm_kernel(const bf16* __restrict__ x, int ldx, bf16* residual,
                                                          int ldr, const bf16* __restrict__ w, bf16* out, int ldo,
                                                          int H, float eps, float w_offset) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[32];
   const int row = blockIdx.x;
   const int nvec = H / 8;
@@ -94,6 +96,8 @@ __global__ void __launch_bounds__(THREADS) layernorm_mod_kernel(const bf16* __re
                                                                int rows_per_batch, const bf16* __restrict__ gamma,
                                                                const bf16* __restrict__ beta, bf16* out, int ldo, int H,
                                                                float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[32];
   const int row = blockIdx.x;
   const int nvec = H / 8;
@@ -168,6 +172,8 @@ __global__ void __launch_bounds__(256) rope_kv_write_kernel(
     const float* __restrict__ cos_tab, const float* __restrict__ sin_tab, int rot_dim, int interleaved,
     const bf16* __restrict__ q_norm_w, const bf16* __restrict__ k_norm_w, float norm_eps, float norm_w_offset,
     bf16* kcache, bf16* vcache, int block_size, int T, int Hq, int Hkv, int D) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float rope_smem[8 * 256];
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -265,6 +271,8 @@ __global__ void __launch_bounds__(256) rope_kv_write_kernel(
 // out[t, f] = act(gu[t, f]) * gu[t, F + f]; act 1 = SiLU (SwiGLU), 2 = tanh-GELU (GeGLU).
 __global__ void __launch_bounds__(256) gated_act_mul_kernel(const bf16* __restrict__ gu, int ld_gu, bf16* out,
                                                            int ldo, int T, int F, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int nvec = F / 8;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)T * nvec) return;
@@ -281,6 +289,8 @@ __global__ void __launch_bounds__(256) gated_act_mul_kernel(const bf16* __restri
 __global__ void __launch_bounds__(256) embedding_kernel(const long long* __restrict__ ids, const bf16* __restrict__ table,
                                                        bf16* out, int T, int H, int vocab_start, int vocab_end,
                                                        float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int nvec = H / 8;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)T * nvec) return;
@@ -305,6 +315,8 @@ __global__ void __launch_bounds__(256) embedding_kernel(const long long* __restr
 __global__ void __launch_bounds__(256) gated_residual_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b,
                                                             const bf16* __restrict__ gate, int ld_gate,
                                                             int rows_per_batch, bf16* out, int T, int H) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int nvec = H / 8;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)T * nvec) return;
@@ -337,10 +349,8 @@ int launch_norm(int H, F&& f) {
   return -3;
 }
 
-inline int last_err() {
-  cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? 0 : -(int)e;
-}
+static thread_local int launch_rc = 0;
+inline int last_err() { return launch_rc; }
 
 }  // namespace
 }  // namespace swb
@@ -355,7 +365,7 @@ int swb_rmsnorm(const void* x, int ldx, void* residual, int ldr, const void* w, 
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   return launch_norm(H, [&](auto TH, auto VP) {
     constexpr int THREADS = decltype(TH)::value, VPT = decltype(VP)::value;
-    rmsnorm_kernel<THREADS, VPT><<<T, THREADS, 0, s>>>(reinterpret_cast<const bf16*>(x), ldx,
+    launch_rc = launch_kernel(rmsnorm_kernel<THREADS, VPT>, dim3(T), dim3(THREADS), 0, s, reinterpret_cast<const bf16*>(x), ldx,
                                                         reinterpret_cast<bf16*>(residual), ldr,
                                                         reinterpret_cast<const bf16*>(w), reinterpret_cast<bf16*>(out),
                                                         ldo, H, eps, w_offset);
@@ -372,8 +382,7 @@ int swb_layernorm_mod(const void* x, int ldx, const void* scale, const void* shi
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   return launch_norm(H, [&](auto TH, auto VP) {
     constexpr int THREADS = decltype(TH)::value, VPT = decltype(VP)::value;
-    layernorm_mod_kernel<THREADS, VPT><<<T, THREADS, 0, s>>>(
-        reinterpret_cast<const bf16*>(x), ldx, reinterpret_cast<const bf16*>(scale),
+    launch_rc = launch_kernel(layernorm_mod_kernel<THREADS, VPT>, dim3(T), dim3(THREADS), 0, s, reinterpret_cast<const bf16*>(x), ldx, reinterpret_cast<const bf16*>(scale),
         reinterpret_cast<const bf16*>(shift), ld_mod, rows_per_batch, reinterpret_cast<const bf16*>(gamma),
         reinterpret_cast<const bf16*>(beta), reinterpret_cast<bf16*>(out), ldo, H, eps);
     return last_err();
@@ -390,8 +399,7 @@ int swb_rope_kv_write(void* qkv, int ld_qkv, const int* positions, const long lo
   const long long warps = (long long)T * (Hq + 2 * Hkv);
   const int wpb = 8;
   const long long blocks = (warps + wpb - 1) / wpb;
-  rope_kv_write_kernel<<<(unsigned)blocks, wpb * 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<bf16*>(qkv), ld_qkv, positions, slot_mapping, cos_tab, sin_tab, rot_dim, interleaved,
+  launch_rc = launch_kernel(rope_kv_write_kernel, dim3((unsigned)blocks), dim3(wpb * 32), 0, reinterpret_cast<cudaStream_t>(stream), reinterpret_cast<bf16*>(qkv), ld_qkv, positions, slot_mapping, cos_tab, sin_tab, rot_dim, interleaved,
       reinterpret_cast<const bf16*>(q_norm_w), reinterpret_cast<const bf16*>(k_norm_w), norm_eps, norm_w_offset,
       reinterpret_cast<bf16*>(kcache), reinterpret_cast<bf16*>(vcache), block_size, T, Hq, Hkv, D);
   return last_err();
@@ -402,8 +410,7 @@ int swb_gated_act_mul(const void* gate_up, int ld_gu, void* out, int ldo, int T,
   if (T <= 0) return 0;
   if (F % 8 != 0 || ld_gu % 8 != 0 || ldo % 8 != 0) return -3;
   const long long n = (long long)T * (F / 8);
-  gated_act_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const bf16*>(gate_up), ld_gu, reinterpret_cast<bf16*>(out), ldo, T, F, act);
+  launch_rc = launch_kernel(gated_act_mul_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), reinterpret_cast<const bf16*>(gate_up), ld_gu, reinterpret_cast<bf16*>(out), ldo, T, F, act);
   return last_err();
 }
 
@@ -413,8 +420,7 @@ int swb_embedding(const long long* ids, const void* table, void* out, int T, int
   if (T <= 0) return 0;
   if (H % 8 != 0) return -3;
   const long long n = (long long)T * (H / 8);
-  embedding_kernel<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      ids, reinterpret_cast<const bf16*>(table), reinterpret_cast<bf16*>(out), T, H, vocab_start, vocab_end, scale);
+  launch_rc = launch_kernel(embedding_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), ids, reinterpret_cast<const bf16*>(table), reinterpret_cast<bf16*>(out), T, H, vocab_start, vocab_end, scale);
   return last_err();
 }
 
@@ -424,8 +430,7 @@ int swb_gated_residual(const void* a, const void* b, const void* gate, int ld_ga
   if (T <= 0) return 0;
   if (H % 8 != 0 || (gate && ld_gate % 8 != 0)) return -3;
   const long long n = (long long)T * (H / 8);
-  gated_residual_kernel<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const bf16*>(a), reinterpret_cast<const bf16*>(b), reinterpret_cast<const bf16*>(gate), ld_gate,
+  launch_rc = launch_kernel(gated_residual_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), reinterpret_cast<const bf16*>(a), reinterpret_cast<const bf16*>(b), reinterpret_cast<const bf16*>(gate), ld_gate,
       rows_per_batch, reinterpret_cast<bf16*>(out), T, H);
   return last_err();
 }

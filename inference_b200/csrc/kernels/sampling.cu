@@ -29,6 +29,8 @@ template <typename T>
 __global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ logits, long long ld, int V,
                                                       const uint8_t* __restrict__ allow, long long* out_ids,
                                                       float* out_vals) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ ArgMax red[32];
   const int row = blockIdx.x;
   const T* x = logits + (size_t)row * ld;
@@ -66,6 +68,8 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ logi
 // target_ids[i] == draft[i]) and the bonus/correction token target_ids[n_accepted].
 __global__ void spec_verify_greedy_kernel(const long long* __restrict__ target_ids, const long long* __restrict__ draft,
                                           int k, int num_seqs, int* n_accepted, long long* next_token) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int s = blockIdx.x * blockDim.x + threadIdx.x;
   if (s >= num_seqs) return;
   const long long* t = target_ids + (size_t)s * (k + 1);
@@ -79,6 +83,8 @@ __global__ void spec_verify_greedy_kernel(const long long* __restrict__ target_i
 // In-place repetition penalty on fp32 logits: for each id in history[row, :len[row]] once.
 __global__ void rep_penalty_kernel(float* logits, long long ld, int V, const long long* __restrict__ history,
                                    int hist_ld, const int* __restrict__ hist_len, float penalty) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   const int n = hist_len[row];
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
@@ -96,10 +102,8 @@ __global__ void rep_penalty_kernel(float* logits, long long ld, int V, const lon
   }
 }
 
-inline int last_err() {
-  cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? 0 : -(int)e;
-}
+static thread_local int launch_rc = 0;
+inline int last_err() { return launch_rc; }
 
 }  // namespace
 }  // namespace swb
@@ -112,11 +116,11 @@ int swb_argmax(const void* logits, int is_fp32, long long ld, int rows, int V, c
   if (rows <= 0) return 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (is_fp32)
-    argmax_kernel<float><<<rows, 1024, 0, s>>>(reinterpret_cast<const float*>(logits), ld, V,
-                                               reinterpret_cast<const uint8_t*>(allow_mask), out_ids, out_vals);
+    launch_rc = launch_kernel(argmax_kernel<float>, dim3(rows), dim3(1024), 0, s, reinterpret_cast<const float*>(logits),
+                              ld, V, reinterpret_cast<const uint8_t*>(allow_mask), out_ids, out_vals);
   else
-    argmax_kernel<bf16><<<rows, 1024, 0, s>>>(reinterpret_cast<const bf16*>(logits), ld, V,
-                                              reinterpret_cast<const uint8_t*>(allow_mask), out_ids, out_vals);
+    launch_rc = launch_kernel(argmax_kernel<bf16>, dim3(rows), dim3(1024), 0, s, reinterpret_cast<const bf16*>(logits),
+                              ld, V, reinterpret_cast<const uint8_t*>(allow_mask), out_ids, out_vals);
   return last_err();
 }
 
@@ -124,8 +128,7 @@ int swb_spec_verify_greedy(const long long* target_ids, const long long* draft, 
                            long long* next_token, void* stream) {
   using namespace swb;
   if (num_seqs <= 0) return 0;
-  spec_verify_greedy_kernel<<<(num_seqs + 127) / 128, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      target_ids, draft, k, num_seqs, n_accepted, next_token);
+  launch_rc = launch_kernel(spec_verify_greedy_kernel, dim3((num_seqs + 127) / 128), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream), target_ids, draft, k, num_seqs, n_accepted, next_token);
   return last_err();
 }
 
@@ -133,7 +136,7 @@ int swb_rep_penalty(float* logits, long long ld, int rows, int V, const long lon
                     const int* hist_len, float penalty, void* stream) {
   using namespace swb;
   if (rows <= 0) return 0;
-  rep_penalty_kernel<<<rows, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(logits, ld, V, history, hist_ld,
+  launch_rc = launch_kernel(rep_penalty_kernel, dim3(rows), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), logits, ld, V, history, hist_ld,
                                                                                hist_len, penalty);
   return last_err();
 }

@@ -1,6 +1,7 @@
 // Host-side registry of per-translation-unit device status words.
 #include "common.cuh"
 
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 
@@ -15,6 +16,17 @@ std::mutex& units_mu() {
   return m;
 }
 }  // namespace
+
+namespace {
+int g_pdl = -1;
+}
+bool pdl_enabled() {
+  if (g_pdl < 0) {
+    const char* e = getenv("SWB_PDL");
+    g_pdl = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_pdl == 1;
+}
 
 void register_status_unit(const StatusUnit& u) {
   std::lock_guard<std::mutex> g(units_mu());
@@ -53,5 +65,8 @@ int swb_set_wait_limit_ns(unsigned long long ns) {
   for (auto& u : swb::units()) rc |= u.set_limit(ns);
   return rc;
 }
+
+// Programmatic dependent launch on (1) / off (0) for every kernel of this library.
+void swb_set_pdl(int on) { swb::g_pdl = on ? 1 : 0; }
 
 }  // extern "C"

@@ -24,7 +24,7 @@ def gemm_workspace(device: torch.device, slot: int = 0) -> torch.Tensor:
 
 def gemm_bf16(a: torch.Tensor, w: torch.Tensor, *, bias: torch.Tensor | None = None,
               residual: torch.Tensor | None = None, act: str | None = None, out: torch.Tensor | None = None,
-              out_dtype: torch.dtype = torch.bfloat16, mode: int = -1, block_n: int = 0, splits: int = 0,
+              out_dtype: torch.dtype = torch.bfloat16, mode: int = -1, block_n: int = 0, ctas: int = 0,
               workspace: torch.Tensor | None = None) -> torch.Tensor:
     """out[T, N] = act(a[T, K] @ w[N, K]^T + bias) + residual. a and w are bf16 with contiguous rows."""
     require_cuda(a, w)
@@ -45,7 +45,7 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, *, bias: torch.Tensor | None = N
     rc = kernels().swb_gemm_bf16(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
                                  T, N, K, ptr(bias), ptr(residual), residual.stride(0) if residual is not None else 0,
                                  ACT[act], 1 if out.dtype == torch.float32 else 0, workspace.data_ptr(),
-                                 workspace.numel(), mode, block_n, splits, stream_ptr())
+                                 workspace.numel(), mode, block_n, ctas, stream_ptr())
     check(rc, "swb_gemm_bf16")
     return out
 

@@ -18,7 +18,7 @@ def _ref(a, w, bias, residual, act):
     return y
 
 
-def _check(T, N, K, *, mode=-1, block_n=0, splits=0, bias=False, residual=False, act=None, out_dtype=torch.bfloat16):
+def _check(T, N, K, *, mode=-1, block_n=0, ctas=0, bias=False, residual=False, act=None, out_dtype=torch.bfloat16):
     from inference_b200 import ops
 
     g = torch.Generator(device="cuda").manual_seed(T * 7919 + N * 31 + K)
@@ -26,14 +26,14 @@ def _check(T, N, K, *, mode=-1, block_n=0, splits=0, bias=False, residual=False,
     w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).bfloat16()
     b = (torch.randn(N, device="cuda", generator=g) * 0.1).bfloat16() if bias else None
     r = (torch.randn(T, N, device="cuda", generator=g) * 0.5).bfloat16() if residual else None
-    y = ops.gemm_bf16(a, w, bias=b, residual=r, act=act, mode=mode, block_n=block_n, splits=splits,
+    y = ops.gemm_bf16(a, w, bias=b, residual=r, act=act, mode=mode, block_n=block_n, ctas=ctas,
                       out_dtype=out_dtype)
     ops.check_status()
     ref = _ref(a, w, b, r, act)
     err = (y.float() - ref).abs().max().item()
     scale = ref.abs().max().item() + 1e-6
     tol = 2e-2 if out_dtype == torch.bfloat16 else 2e-3
-    assert err / scale < tol, f"T={T} N={N} K={K} mode={mode} bn={block_n} splits={splits}: err {err} scale {scale}"
+    assert err / scale < tol, f"T={T} N={N} K={K} mode={mode} bn={block_n} ctas={ctas}: err {err} scale {scale}"
     return y
 
 
@@ -43,11 +43,12 @@ def test_swapped_small_tokens(T):
     _check(T, 384, 1024, bias=True, residual=True)
 
 
-@pytest.mark.parametrize("splits", [1, 2, 3, 8])
-def test_split_k_deterministic(splits):
-    y0 = _check(8, 1024, 2048, mode=1, splits=splits, bias=True, act="silu")
-    y1 = _check(8, 1024, 2048, mode=1, splits=splits, bias=True, act="silu")
+@pytest.mark.parametrize("ctas", [-1, 3, 7, 20, 148])
+def test_stream_k_deterministic(ctas):
+    y0 = _check(8, 1024, 2048, mode=1, ctas=ctas, bias=True, act="silu")
+    y1 = _check(8, 1024, 2048, mode=1, ctas=ctas, bias=True, act="silu")
     assert torch.equal(y0, y1)
+    _check(300, 640, 1024, mode=0, ctas=ctas, residual=True)
 
 
 @pytest.mark.parametrize("shape", [(300, 256, 128), (512, 1024, 512), (1000, 776, 328), (129, 4096, 4096)])
@@ -81,3 +82,12 @@ def test_strided_views():
     y = ops.gemm_bf16(a[:, 512:], w)
     ref = a[:, 512:].float() @ w.float().t()
     assert (y.float() - ref).abs().max().item() < 0.05 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("cluster", [1, 2, 4, 8])
+@pytest.mark.parametrize("T", [1, 7, 16, 31, 64])
+def test_cluster_split_k_decode(T, cluster):
+    y0 = _check(T, 1024, 2048, mode=2, ctas=cluster, bias=True, residual=True, act="silu")
+    y1 = _check(T, 1024, 2048, mode=2, ctas=cluster, bias=True, residual=True, act="silu")
+    assert torch.equal(y0, y1)
+    _check(T, 1000, 1096, mode=2, ctas=cluster, out_dtype=torch.float32)
