@@ -4,6 +4,8 @@
 // (longest matching prefix of draft tokens against target argmaxes, candle-llm/src/decode/speculative.rs:399-421).
 #include "common.cuh"
 
+#include <algorithm>
+
 namespace swb {
 namespace {
 
@@ -25,17 +27,24 @@ __device__ __forceinline__ float to_f<bf16>(bf16 x) { return __bfloat162float(x)
 
 // allow: optional uint8 [V] (1 = allowed). penalty_ids: optional [n_pen] token ids whose logit is divided
 // (positive) or multiplied (negative) by `penalty` before the comparison.
+// grid (rows, chunks): each CTA reduces one contiguous vocabulary chunk of one row. With chunks == 1 the
+// result goes straight to out_ids; otherwise (value, index) partials go to `part` and argmax_merge_kernel
+// finishes the row, so a 128k vocabulary at batch 1..64 still fills the GPU.
 template <typename T>
 __global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ logits, long long ld, int V,
                                                       const uint8_t* __restrict__ allow, long long* out_ids,
-                                                      float* out_vals) {
+                                                      float* out_vals, float* part_val, long long* part_idx) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ ArgMax red[32];
   const int row = blockIdx.x;
+  const int chunks = gridDim.y;
+  const int per = (V + chunks - 1) / chunks;
+  const int v0 = blockIdx.y * per;
+  const int v1 = min(V, v0 + per);
   const T* x = logits + (size_t)row * ld;
   ArgMax best{-INFINITY, (long long)V};
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+  for (int i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
     if (allow && !allow[i]) continue;
     float v = to_f<T>(x[i]);
     if (v != v) continue;  // NaN never wins
@@ -57,9 +66,34 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ logi
       best = better(best, other);
     }
     if (lane == 0) {
-      out_ids[row] = best.i < V ? best.i : 0;
-      if (out_vals) out_vals[row] = best.v;
+      if (chunks == 1) {
+        out_ids[row] = best.i < V ? best.i : 0;
+        if (out_vals) out_vals[row] = best.v;
+      } else {
+        part_val[row * chunks + blockIdx.y] = best.v;
+        part_idx[row * chunks + blockIdx.y] = best.i;
+      }
     }
+  }
+}
+
+__global__ void __launch_bounds__(32) argmax_merge_kernel(const float* __restrict__ part_val,
+                                                         const long long* __restrict__ part_idx, int chunks, int V,
+                                                         long long* out_ids, float* out_vals) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x;
+  ArgMax best{-INFINITY, (long long)V};
+  for (int c = threadIdx.x; c < chunks; c += 32)
+    best = better(best, ArgMax{part_val[row * chunks + c], part_idx[row * chunks + c]});
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgMax other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, other);
+  }
+  if (threadIdx.x == 0) {
+    out_ids[row] = best.i < V ? best.i : 0;
+    if (out_vals) out_vals[row] = best.v;
   }
 }
 
@@ -110,18 +144,30 @@ inline int last_err() { return launch_rc; }
 
 extern "C" {
 
+// scratch: >= rows * 32 * 12 bytes when rows * V is large enough to be chunked (may be null: single pass).
 int swb_argmax(const void* logits, int is_fp32, long long ld, int rows, int V, const void* allow_mask,
-               long long* out_ids, float* out_vals, void* stream) {
+               long long* out_ids, float* out_vals, void* scratch, size_t scratch_bytes, void* stream) {
   using namespace swb;
   if (rows <= 0) return 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  int chunks = 1;
+  if (scratch && V >= 16384) {
+    chunks = std::min(32, std::max(1, 296 / rows));
+    while (chunks > 1 && (size_t)rows * chunks * 12 > scratch_bytes) chunks /= 2;
+  }
+  float* pv = reinterpret_cast<float*>(scratch);
+  long long* pi = reinterpret_cast<long long*>(reinterpret_cast<uint8_t*>(scratch) + (size_t)rows * chunks * 4 +
+                                               ((8 - ((size_t)rows * chunks * 4) % 8) % 8));
+  const uint8_t* allow = reinterpret_cast<const uint8_t*>(allow_mask);
   if (is_fp32)
-    launch_rc = launch_kernel(argmax_kernel<float>, dim3(rows), dim3(1024), 0, s, reinterpret_cast<const float*>(logits),
-                              ld, V, reinterpret_cast<const uint8_t*>(allow_mask), out_ids, out_vals);
+    launch_rc = launch_kernel(argmax_kernel<float>, dim3(rows, chunks), dim3(1024), 0, s,
+                              reinterpret_cast<const float*>(logits), ld, V, allow, out_ids, out_vals, pv, pi);
   else
-    launch_rc = launch_kernel(argmax_kernel<bf16>, dim3(rows), dim3(1024), 0, s, reinterpret_cast<const bf16*>(logits),
-                              ld, V, reinterpret_cast<const uint8_t*>(allow_mask), out_ids, out_vals);
-  return last_err();
+    launch_rc = launch_kernel(argmax_kernel<bf16>, dim3(rows, chunks), dim3(1024), 0, s,
+                              reinterpret_cast<const bf16*>(logits), ld, V, allow, out_ids, out_vals, pv, pi);
+  if (launch_rc || chunks == 1) return launch_rc;
+  launch_rc = launch_kernel(argmax_merge_kernel, dim3(rows), dim3(32), 0, s, pv, pi, chunks, V, out_ids, out_vals);
+  return launch_rc;
 }
 
 int swb_spec_verify_greedy(const long long* target_ids, const long long* draft, int k, int num_seqs, int* n_accepted,

@@ -118,6 +118,18 @@ def gated_residual(a: torch.Tensor, b: torch.Tensor, gate: torch.Tensor | None =
     return out.reshape(a.shape)
 
 
+_ARGMAX_SCRATCH: dict[int, torch.Tensor] = {}
+
+
+def _argmax_scratch(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _ARGMAX_SCRATCH.get(idx)
+    if t is None:
+        t = torch.empty(1 << 20, dtype=torch.uint8, device=device)
+        _ARGMAX_SCRATCH[idx] = t
+    return t
+
+
 def argmax(logits: torch.Tensor, allow_mask: torch.Tensor | None = None, out: torch.Tensor | None = None
            ) -> torch.Tensor:
     """Row-wise argmax (ties -> lowest index) of fp32/bf16 logits; allow_mask: optional uint8 [V]."""
@@ -126,8 +138,10 @@ def argmax(logits: torch.Tensor, allow_mask: torch.Tensor | None = None, out: to
     assert l2.stride(1) == 1 and l2.dtype in (torch.float32, torch.bfloat16)
     if out is None:
         out = torch.empty(l2.shape[0], dtype=torch.int64, device=logits.device)
+    scratch = _argmax_scratch(logits.device)
     rc = kernels().swb_argmax(l2.data_ptr(), 1 if l2.dtype == torch.float32 else 0, l2.stride(0), l2.shape[0],
-                              l2.shape[1], ptr(allow_mask), out.data_ptr(), None, stream_ptr())
+                              l2.shape[1], ptr(allow_mask), out.data_ptr(), None, scratch.data_ptr(), scratch.numel(),
+                              stream_ptr())
     check(rc, "swb_argmax")
     return out
 
