@@ -1,10 +1,8 @@
-"""Refcounted paged-KV block allocator policy (dense ids, LIFO recycle, copy-on-write sharing).
-
-Behavioural parity: core-llm/src/paging.rs:42-127 — `alloc` pops the most recently freed id or mints the
-next dense id, `retain` adds a sharer, `release` frees at refcount 0, and the accounting exposes live,
-shared and peak-live counts.
-"""
+"""Refcounted paged-KV block allocator policy (dense ids, LIFO recycle, copy-on-write sharing), backed by the
+C++ host library. Behavioural parity: core-llm/src/paging.rs:42-127."""
 from __future__ import annotations
+
+from ._lib import lib
 
 
 class OutOfBlocks(RuntimeError):
@@ -13,51 +11,41 @@ class OutOfBlocks(RuntimeError):
 
 class BlockAllocator:
     def __init__(self, capacity: int | None = None):
+        self._lib = lib()
+        self._h = self._lib.swb_alloc_new(-1 if capacity is None else capacity)
         self.capacity = capacity
-        self._refs: list[int] = []
-        self._free: list[int] = []
-        self._live = 0
-        self._peak = 0
+
+    def __del__(self):
+        try:
+            self._lib.swb_alloc_free(self._h)
+        except Exception:
+            pass
 
     def alloc(self) -> int:
-        if self._free:
-            b = self._free.pop()
-        else:
-            if self.capacity is not None and len(self._refs) >= self.capacity:
-                raise OutOfBlocks(f"KV block pool exhausted ({self.capacity} blocks)")
-            b = len(self._refs)
-            self._refs.append(0)
-        self._refs[b] = 1
-        self._live += 1
-        self._peak = max(self._peak, self._live)
+        b = self._lib.swb_alloc_alloc(self._h)
+        if b < 0:
+            raise OutOfBlocks(f"KV block pool exhausted ({self.capacity} blocks)")
         return b
 
     def retain(self, block: int) -> None:
-        if self._refs[block] <= 0:
+        if self._lib.swb_alloc_retain(self._h, block) != 0:
             raise ValueError(f"retain of free block {block}")
-        self._refs[block] += 1
 
     def release(self, block: int) -> None:
-        if self._refs[block] <= 0:
+        if self._lib.swb_alloc_release(self._h, block) != 0:
             raise ValueError(f"release of free block {block}")
-        self._refs[block] -= 1
-        if self._refs[block] == 0:
-            self._free.append(block)
-            self._live -= 1
 
     def refcount(self, block: int) -> int:
-        return self._refs[block] if 0 <= block < len(self._refs) else 0
+        return self._lib.swb_alloc_refcount(self._h, block)
 
     def live_blocks(self) -> int:
-        return self._live
+        return self._lib.swb_alloc_live(self._h)
 
     def shared_blocks(self) -> int:
-        return sum(1 for r in self._refs if r > 1)
+        return self._lib.swb_alloc_shared(self._h)
 
     def peak_live_blocks(self) -> int:
-        return self._peak
+        return self._lib.swb_alloc_peak(self._h)
 
     def free_blocks(self) -> int | None:
-        if self.capacity is None:
-            return None
-        return self.capacity - self._live
+        return None if self.capacity is None else self.capacity - self.live_blocks()
