@@ -1,0 +1,322 @@
+"""Text-LLM providers over the decode backends: `b200-llama` (sm_100a kernels, paged KV, tensor parallel) and
+`cpu-llama` (fp32 oracle). Capability target: candle-llm/src/provider.rs:39-1285 (`candle-llama`): load an HF
+snapshot directory or a GGUF file, render the chat template, tokenize, optional JSON constraint mask, thinking /
+tool-call segmentation, stop strings, incremental detokenisation, typed cancel, usage accounting."""
+from __future__ import annotations
+
+import json
+from pathlib import Path
+from typing import Callable
+
+import numpy as np
+import torch
+
+from ..contracts.core_llm import (Canceled, Channel, ChatMlTemplate, ChatTemplate, Constraint, DoneEvent,
+                                  FinishReason, IncrementalDetok, JinjaChatTemplate, JsonConstraint, Llama3Template,
+                                  LoadError, LoadSpec, Quantize, RenderOptions, StopMatcher, StreamEvent,
+                                  TextLlm, TextLlmCapabilities, TextLlmDescriptor, TextLlmOutput,
+                                  TextLlmRegistration, TextLlmRequest, ThinkingSegmenter, TokenEvent, Tokenizer,
+                                  ToolCallSegmenter, Unsupported, Usage)
+from ..io import gguf as gguf_io
+from ..io import gguf_quants as gq
+from ..io.safetensors_io import load_dir
+from ..models.config import Architecture, ModelConfig
+from ..models.oracle import OracleLlama
+from ..policy.sampler import SamplingParams
+from .backend import DecodeBackend, GpuBackend, OracleBackend
+from .decode import GenerationConfig, generate
+
+BACKEND_GPU = "b200"
+BACKEND_CPU = "cpu"
+_STOP_NAMES = ("<|eot_id|>", "<|end_of_text|>", "<|im_end|>", "<|endoftext|>", "</s>", "<end_of_turn>", "<|user|>")
+_PROJ_SUFFIXES = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight", "gate_proj.weight",
+                  "up_proj.weight", "down_proj.weight", "qkv_proj.weight", "gate_up_proj.weight")
+
+
+def quantize_roundtrip(w: torch.Tensor, bits: int) -> torch.Tensor:
+    """Projection weight -> GGML Q4_K (bits 4) or Q8_0 (bits 8) blocks -> dense again: the numerics of a model
+    quantised on load (candle-llm/src/primitives/projection.rs:15-53 maps Q4 -> Q4K, Q8 -> Q8_0)."""
+    k = w.shape[-1]
+    block = 256 if bits == 4 else 32
+    if k % block:
+        return w
+    x = w.detach().float().cpu().numpy()
+    raw = gq.quantize_q4_k(x) if bits == 4 else gq.quantize_q8_0(x)
+    y = gq.dequantize(raw, "Q4_K" if bits == 4 else "Q8_0", x.size).reshape(x.shape)
+    return torch.from_numpy(y.copy()).to(w.dtype)
+
+
+def _read_json(p: Path) -> dict:
+    try:
+        return json.loads(p.read_text())
+    except (OSError, json.JSONDecodeError):
+        return {}
+
+
+def _supported_on_gpu(cfg: ModelConfig) -> bool:
+    return (cfg.head_dim == 128 and cfg.moe is None and cfg.mla is None and
+            cfg.architecture not in (Architecture.QWEN35, Architecture.DEEPSEEK_V2, Architecture.QWEN2_MOE))
+
+
+def probe_config(spec: LoadSpec) -> ModelConfig | None:
+    """Weightless probe: config.json of a snapshot directory or the metadata of a GGUF file."""
+    p = Path(spec.source)
+    try:
+        if p.is_dir() and (p / "config.json").is_file():
+            return ModelConfig.from_dir(p)
+        if p.is_file() and (p.suffix == ".gguf" or p.read_bytes()[:4] == b"GGUF"):
+            ck = gguf_io.GgufCheckpoint(p)
+            cfg = ModelConfig.from_json(ck.config())
+            ck.file.close()
+            return cfg
+    except Exception:
+        return None
+    return None
+
+
+class LlamaProvider(TextLlm):
+    def __init__(self, descriptor: TextLlmDescriptor, backend: DecodeBackend, tokenizer: Tokenizer,
+                 template: ChatTemplate, stop_tokens: list[int], cfg: ModelConfig):
+        self._descriptor = descriptor
+        self.backend = backend
+        self.tokenizer = tokenizer
+        self.template = template
+        self.stop_tokens = stop_tokens
+        self.cfg = cfg
+        self._constraint_table = None
+
+    # ---- loading ------------------------------------------------------------------------------------
+    @staticmethod
+    def load(spec: LoadSpec, provider_id: str, backend_name: str, comm=None) -> "LlamaProvider":
+        p = Path(spec.source)
+        if p.is_dir():
+            cfg = ModelConfig.from_dir(p)
+            weights = load_dir(p)
+            tok_path = p / "tokenizer.json"
+            if not tok_path.is_file():
+                raise LoadError(f"{p}: tokenizer.json not found")
+            tokenizer = Tokenizer.from_file(tok_path)
+            tcfg = _read_json(p / "tokenizer_config.json")
+            template, thinking, tools = _pick_template(tcfg.get("chat_template") and tcfg, cfg)
+            extra_eos = _eos_ids(_read_json(p / "config.json")) | _eos_ids(_read_json(p / "generation_config.json"))
+        elif p.is_file():
+            ck = gguf_io.GgufCheckpoint(p)
+            cfg = ModelConfig.from_json(ck.config())
+            weights = ck.tensors()
+            tj = ck.tokenizer_json()
+            if tj is None:
+                raise Unsupported(f"{p}: GGUF tokenizer model {ck.file.metadata.get('tokenizer.ggml.model')!r} "
+                                  "cannot be reconstructed (byte-level BPE only)")
+            tokenizer = Tokenizer.from_json(tj)
+            ct = ck.chat_template()
+            template, thinking, tools = _pick_template({"chat_template": ct} if ct else None, cfg)
+            extra_eos = _eos_ids(ck.config())
+        else:
+            raise LoadError(f"model source '{spec.source}' is neither a snapshot directory nor a GGUF file")
+        bits = spec.quantize.value if spec.quantize is not None else cfg.quantization_bits
+        if bits in (4, 8):
+            weights = {k: (quantize_roundtrip(v, bits) if k.endswith(_PROJ_SUFFIXES) else v) for k, v in weights.items()}
+        stop = sorted(extra_eos | {i for n in _STOP_NAMES if (i := tokenizer.token_to_id(n)) is not None})
+        backend = _build_backend(cfg, weights, backend_name, comm)
+        caps = TextLlmCapabilities(max_context_tokens=backend.max_context, max_new_tokens=0, supports_system_prompt=True,
+                                   supports_vision=False, supports_video=False, supports_thinking=thinking,
+                                   supports_tools=tools, supported_constraints=[Constraint.JSON])
+        d = TextLlmDescriptor(provider_id, cfg.architecture.family, backend_name, caps)
+        return LlamaProvider(d, backend, tokenizer, template, stop, cfg)
+
+    # ---- contract ---------------------------------------------------------------------------------------
+    def descriptor(self) -> TextLlmDescriptor:
+        return self._descriptor
+
+    def validate(self, req: TextLlmRequest) -> None:
+        self._descriptor.capabilities.validate_request(self._descriptor.id, req)
+
+    def generate(self, req: TextLlmRequest, on_event: Callable[[StreamEvent], None]) -> TextLlmOutput:
+        self.validate(req)
+        if req.cancel.is_cancelled():
+            raise Canceled()
+        prompt = self.template.render_with(req.messages, RenderOptions(True, req.enable_thinking_kwarg(), req.tools))
+        prompt_ids = self.tokenizer.encode(prompt, add_special_tokens=False)
+        if len(prompt_ids) + 1 > self.backend.max_context:
+            from ..contracts.core_llm import InvalidRequest
+            raise InvalidRequest(f"[{self._descriptor.id}] prompt of {len(prompt_ids)} tokens exceeds the context "
+                                 f"window {self.backend.max_context}")
+        s = req.sampling
+        cfg = GenerationConfig(max_new_tokens=req.max_new_tokens,
+                               sampling=SamplingParams(s.temperature, s.top_p, s.top_k, s.repetition_penalty,
+                                                       s.repetition_context),
+                               seed=req.seed if req.seed is not None else 0, stop_tokens=tuple(self.stop_tokens),
+                               cancel=req.cancel)
+        mask = self._json_mask() if req.constraint is Constraint.JSON else None
+        caps = self._descriptor.capabilities
+        seg = ThinkingSegmenter() if caps.supports_thinking else None
+        if seg is not None and prompt.rstrip().endswith("<think>"):
+            seg.push("<think>")
+        tool_seg = ToolCallSegmenter(req.tools) if caps.supports_tools and req.tools else None
+        stopper = StopMatcher(req.stop)
+        st = _StreamState(on_event)
+        acc: list[int] = []
+        detok = IncrementalDetok()
+
+        string_stop = [False]
+
+        def route_content(text: str, tid: int) -> bool:
+            pieces = tool_seg.push(text) if tool_seg is not None else [text]
+            for piece in pieces:
+                chunk = stopper.push(piece)
+                if chunk.emit:
+                    st.emit(tid, chunk.emit, Channel.CONTENT)
+                if chunk.stop:
+                    string_stop[0] = True
+                    return False
+            return True
+
+        def sink(tok: int) -> bool:
+            acc.append(tok)
+            delta = detok.push(self.tokenizer.decode(acc, skip_special_tokens=True))
+            if delta is None:
+                return True
+            if seg is None:
+                return route_content(delta, tok)
+            for span in seg.push(delta):
+                if span.channel is Channel.THINKING:
+                    st.emit(tok, span.text, Channel.THINKING)
+                elif not route_content(span.text, tok):
+                    return False
+            return True
+
+        res = generate(self.backend, prompt_ids, cfg, sink, mask)
+        if not string_stop[0]:
+            # end-of-generation tails, in pipeline order: reasoning segmenter, tool segmenter, stop matcher
+            if seg is not None:
+                for span in seg.flush():
+                    if span.channel is Channel.THINKING:
+                        st.emit(st.last_id, span.text, Channel.THINKING)
+                    else:
+                        route_content(span.text, st.last_id)
+            if tool_seg is not None and not string_stop[0]:
+                for piece in tool_seg.flush():
+                    c = stopper.push(piece)
+                    if c.emit:
+                        st.emit(st.last_id, c.emit, Channel.CONTENT)
+            tail = stopper.flush()
+            if tail and not string_stop[0]:
+                st.emit(st.last_id, tail, Channel.CONTENT)
+        usage = Usage(len(prompt_ids), len(res.tokens))
+        on_event(DoneEvent(res.finish_reason, usage))
+        return TextLlmOutput(text=st.content, thinking=st.thinking or None,
+                             tool_calls=tool_seg.take_calls() if tool_seg is not None else [], usage=usage,
+                             finish_reason=res.finish_reason)
+
+    def _json_mask(self):
+        if self._constraint_table is None:
+            self._constraint_table = self.tokenizer.constraint_decode_table()
+        jc = JsonConstraint(self._constraint_table)
+        consumed = [0]
+        stops = self.stop_tokens
+
+        def mask(generated: list[int]):
+            while consumed[0] < len(generated):
+                jc.accept(generated[consumed[0]])
+                consumed[0] += 1
+            allowed = np.asarray(jc.allowed(), dtype=np.uint8)
+            if jc.can_stop():
+                for s in stops:
+                    if s < allowed.size:
+                        allowed[s] = 1
+            if not allowed.any():           # nothing extends the value: only stopping remains
+                for s in stops:
+                    if s < allowed.size:
+                        allowed[s] = 1
+            return allowed
+
+        return mask
+
+
+class _StreamState:
+    def __init__(self, on_event):
+        self.on_event = on_event
+        self.index = 0
+        self.last_id = 0
+        self.content = ""
+        self.thinking = ""
+
+    def emit(self, tid: int, text: str, channel: Channel) -> None:
+        if channel is Channel.CONTENT:
+            self.content += text
+        else:
+            self.thinking += text
+        self.last_id = tid
+        self.on_event(TokenEvent(tid, text, self.index, channel))
+        self.index += 1
+
+
+def _eos_ids(cfg: dict) -> set[int]:
+    e = cfg.get("eos_token_id")
+    if isinstance(e, int):
+        return {e}
+    if isinstance(e, list):
+        return {int(x) for x in e if isinstance(x, int)}
+    return set()
+
+
+def _pick_template(tokenizer_config: dict | None, cfg: ModelConfig) -> tuple[ChatTemplate, bool, bool]:
+    """Jinja template from the tokenizer config when present, else a built-in layout by family. The template
+    source decides whether thinking (`enable_thinking`) and tools (`tool_call`) are advertised."""
+    if tokenizer_config:
+        try:
+            t = JinjaChatTemplate.from_tokenizer_config(tokenizer_config)
+            return t, "enable_thinking" in t.source, "tool_call" in t.source
+        except Exception:
+            pass
+    if cfg.architecture in (Architecture.QWEN3, Architecture.QWEN3_VL, Architecture.QWEN2_MOE):
+        return ChatMlTemplate(), False, False
+    return Llama3Template(), False, False
+
+
+def _build_backend(cfg: ModelConfig, weights: dict, backend_name: str, comm=None) -> DecodeBackend:
+    if backend_name == BACKEND_GPU:
+        if not torch.cuda.is_available():
+            raise LoadError("the b200 backend needs a CUDA device (use the cpu runtime bundle on hosts without one)")
+        if not _supported_on_gpu(cfg):
+            raise Unsupported(f"{cfg.architecture.value} (head_dim {cfg.head_dim}) is not served by the sm_100a "
+                              "decoder; load it through the cpu-llama provider")
+        from ..models.llama import LlamaGpu
+        from .kv_pool import PagedKvPool
+        from .runner import ModelRunner
+
+        dev = comm.device if comm is not None else torch.device("cuda", torch.cuda.current_device())
+        model = LlamaGpu(cfg, comm=comm, device=dev).load_state_dict(weights)
+        ctx = min(cfg.max_position_embeddings or 8192, 32768)
+        max_batch = 16
+        free, _total = torch.cuda.mem_get_info(dev)
+        per_block = cfg.num_layers * 2 * model.hkv * 16 * cfg.head_dim * 2
+        want = max_batch * ((ctx + 15) // 16) + 64
+        nblocks = max(64, min(want, int(free * 0.6) // per_block))
+        pool = PagedKvPool(cfg.num_layers, nblocks, model.hkv, cfg.head_dim, 16, device=dev)
+        return GpuBackend(ModelRunner(model, pool, max_batch=max_batch, max_seq_len=ctx))
+    return OracleBackend(OracleLlama(cfg, weights, dtype=torch.float32, device="cpu"),
+                         max_context=cfg.max_position_embeddings or 8192)
+
+
+# ---- registrations ------------------------------------------------------------------------------------------
+def _descriptor(pid: str, backend: str) -> TextLlmDescriptor:
+    return TextLlmDescriptor(pid, "llama", backend, TextLlmCapabilities(
+        max_context_tokens=0, max_new_tokens=0, supports_system_prompt=True, supports_vision=False,
+        supports_video=False, supports_thinking=False, supports_tools=False, supported_constraints=[Constraint.JSON]))
+
+
+def _can_load_gpu(spec: LoadSpec) -> bool:
+    cfg = probe_config(spec)
+    return cfg is not None and _supported_on_gpu(cfg)
+
+
+def _can_load_cpu(spec: LoadSpec) -> bool:
+    cfg = probe_config(spec)
+    return cfg is not None and cfg.mla is None and cfg.architecture is not Architecture.QWEN35
+
+
+B200_LLAMA = TextLlmRegistration(lambda: _descriptor("b200-llama", BACKEND_GPU),
+                                 lambda spec: LlamaProvider.load(spec, "b200-llama", BACKEND_GPU), _can_load_gpu)
+CPU_LLAMA = TextLlmRegistration(lambda: _descriptor("cpu-llama", BACKEND_CPU),
+                                lambda spec: LlamaProvider.load(spec, "cpu-llama", BACKEND_CPU), _can_load_cpu)
