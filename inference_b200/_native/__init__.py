@@ -84,6 +84,12 @@ def _declare_kernels(lib: ctypes.CDLL) -> None:
                            c_int, c_void_p, c_size_t, c_void_p])
     sig("swb_attn_dense", [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int,
                            c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    sig("swb_comm_max_ctas", [])
+    sig("swb_comm_flag_words", [])
+    sig("swb_allreduce_rmsnorm", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                                  c_void_p, c_float, c_float, c_void_p, c_int, c_void_p])
+    sig("swb_flag_wait", [c_void_p, ctypes.c_uint, c_void_p, c_void_p])
+    sig("swb_set_pdl", [c_int], None)
     sig("swb_argmax", [c_void_p, c_int, c_ll, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p])
     sig("swb_spec_verify_greedy", [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p])
     sig("swb_rep_penalty", [c_void_p, c_ll, c_int, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p])

@@ -1,0 +1,254 @@
+// One-shot all-reduce over NVLink peer memory fused with residual add and RMSNorm (tensor-parallel decode).
+//
+// Every rank's row-parallel GEMM writes its partial [T, H] tile straight into a symmetric-memory buffer. This
+// kernel then (1) runs a flag barrier with every peer (release store of an epoch into the peer's flag word,
+// bounded acquire spin on its own), (2) pulls the P partial rows with 16-byte peer loads, sums them in fp32 in
+// rank order (so every rank produces bit-identical results), (3) adds the residual stream and writes it back,
+// (4) applies RMSNorm and writes the normalised activations for the next column-parallel GEMM.
+// It replaces ncclAllReduce + residual add + rms_norm (the reference has no collective at all: its only
+// multi-GPU path copies the hidden state between devices, candle-llm/src/models/llama.rs:690-707).
+// Buffers are double-buffered by the caller, so no trailing barrier is needed: a buffer is rewritten only after
+// the next call's leading barrier proved that every peer finished reading it.
+// Waits are bounded: on expiry the CTA records {where, rank, peer} in the status word and skips the reduction.
+#include "common.cuh"
+
+#include <type_traits>
+
+namespace swb {
+
+SWB_REGISTER_STATUS_UNIT(comm_allreduce);
+
+namespace {
+
+constexpr int MAX_RANKS = 8;
+constexpr int MAX_CTAS = 256;
+
+struct ArParams {
+  const bf16* peer_data[MAX_RANKS];
+  uint32_t* peer_flags[MAX_RANKS];  // [MAX_CTAS][MAX_RANKS] per rank
+  uint32_t* epochs;                 // local, [MAX_CTAS]
+  int rank, world, T, H, ld_data;
+  bf16* residual;
+  int ldr;
+  const bf16* weight;
+  float eps, w_offset;
+  bf16* out;
+  int ldo;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_peer16(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void unpack8(const uint4& u, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return u;
+}
+
+// Flag barrier of CTA `blockIdx.x` with the same CTA on every peer. Returns false on timeout.
+__device__ __forceinline__ bool peer_barrier(const ArParams& p, uint32_t epoch, int* s_ok) {
+  if (threadIdx.x == 0) *s_ok = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < p.world) {
+    const int peer = threadIdx.x;
+    __threadfence_system();
+    st_release_sys(p.peer_flags[peer] + (size_t)blockIdx.x * MAX_RANKS + p.rank, epoch);
+    const uint32_t* mine = p.peer_flags[p.rank] + (size_t)blockIdx.x * MAX_RANKS + peer;
+    uint64_t t0 = 0;
+    for (uint32_t it = 0;; ++it) {
+      if ((int32_t)(ld_acquire_sys(mine) - epoch) >= 0) break;
+      if ((it & 0x3F) == 0x3F) {
+        const uint64_t now = global_timer_ns();
+        if (t0 == 0) t0 = now;
+        if (now - t0 > g_wait_limit_ns) {
+          report_error(SWB_ERR_PEER_TIMEOUT, 1000 + (int)blockIdx.x, p.rank, peer);
+          *s_ok = 0;
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  return *s_ok != 0;
+}
+
+template <int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS) allreduce_rmsnorm_kernel(const ArParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[32];
+  __shared__ int s_ok;
+  const uint32_t epoch = p.epochs[blockIdx.x] + 1u;
+  const bool ok = peer_barrier(p, epoch, &s_ok);
+  if (threadIdx.x == 0) p.epochs[blockIdx.x] = epoch;
+  if (!ok) return;
+
+  const int nvec = p.H / 8;
+  for (int row = blockIdx.x; row < p.T; row += gridDim.x) {
+    float vals[VPT][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = threadIdx.x + i * THREADS;
+      if (v < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) vals[i][j] = 0.f;
+        uint4 part[MAX_RANKS];
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r)
+          if (r < p.world) part[r] = ld_peer16(p.peer_data[r] + (size_t)row * p.ld_data + v * 8);
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r) {
+          if (r < p.world) {
+            float f[8];
+            unpack8(part[r], f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) vals[i][j] += f[j];
+          }
+        }
+        if (p.residual) {
+          float rf[8];
+          unpack8(*reinterpret_cast<const uint4*>(p.residual + (size_t)row * p.ldr + v * 8), rf);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) vals[i][j] += rf[j];
+          uint4 s = pack8(vals[i]);
+          *reinterpret_cast<uint4*>(p.residual + (size_t)row * p.ldr + v * 8) = s;
+          unpack8(s, vals[i]);
+        } else if (p.weight) {
+          uint4 s = pack8(vals[i]);  // normalise the bf16-rounded sum, like a separate all-reduce would
+          unpack8(s, vals[i]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+      }
+    }
+    float inv = 1.f;
+    if (p.weight) {
+      ss = warp_sum(ss);
+      const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+      if (lane == 0) red[warp] = ss;
+      __syncthreads();
+      float t = (lane < THREADS / 32) ? red[lane] : 0.f;
+      t = warp_sum(t);
+      __syncthreads();
+      inv = rsqrtf(t / (float)p.H + p.eps);
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = threadIdx.x + i * THREADS;
+      if (v < nvec) {
+        float o[8];
+        if (p.weight) {
+          float wf[8];
+          unpack8(__ldg(reinterpret_cast<const uint4*>(p.weight + v * 8)), wf);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * inv * (wf[j] + p.w_offset);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = vals[i][j];
+        }
+        *reinterpret_cast<uint4*>(p.out + (size_t)row * p.ldo + v * 8) = pack8(o);
+      }
+    }
+  }
+}
+
+// A stand-alone wait used by the timeout test: spins on one local flag word that nothing sets.
+__global__ void flag_wait_kernel(const uint32_t* flag, uint32_t expected, int* result) {
+  uint64_t t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    if ((int32_t)(ld_acquire_sys(flag) - expected) >= 0) {
+      *result = 1;
+      return;
+    }
+    if ((it & 0x3F) == 0x3F) {
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > g_wait_limit_ns) {
+        report_error(SWB_ERR_PEER_TIMEOUT, 2000, 0, 0);
+        *result = 0;
+        return;
+      }
+    }
+  }
+}
+
+}  // namespace
+}  // namespace swb
+
+extern "C" {
+
+int swb_comm_max_ctas(void) { return swb::MAX_CTAS; }
+int swb_comm_flag_words(void) { return swb::MAX_CTAS * swb::MAX_RANKS; }
+
+// out = rmsnorm(sum_r data_r [+ residual]) * (weight + w_offset); residual (if given) becomes the sum.
+// weight == null: out = sum (+ residual). peer_data / peer_flags: `world` device pointers each.
+int swb_allreduce_rmsnorm(const void* const* peer_data, void* const* peer_flags, void* epochs, int rank, int world,
+                          int T, int H, int ld_data, void* residual, int ldr, const void* weight, float eps,
+                          float w_offset, void* out, int ldo, void* stream) {
+  using namespace swb;
+  if (T <= 0) return 0;
+  if (world < 1 || world > MAX_RANKS || H % 8 != 0 || ld_data % 8 != 0 || ldo % 8 != 0) return -3;
+  ArParams p{};
+  for (int r = 0; r < world; ++r) {
+    p.peer_data[r] = reinterpret_cast<const bf16*>(peer_data[r]);
+    p.peer_flags[r] = reinterpret_cast<uint32_t*>(peer_flags[r]);
+  }
+  p.epochs = reinterpret_cast<uint32_t*>(epochs);
+  p.rank = rank;
+  p.world = world;
+  p.T = T;
+  p.H = H;
+  p.ld_data = ld_data;
+  p.residual = reinterpret_cast<bf16*>(residual);
+  p.ldr = ldr;
+  p.weight = reinterpret_cast<const bf16*>(weight);
+  p.eps = eps;
+  p.w_offset = w_offset;
+  p.out = reinterpret_cast<bf16*>(out);
+  p.ldo = ldo;
+  const int grid = T < MAX_CTAS ? T : MAX_CTAS;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int nvec = H / 8;
+  if (nvec <= 128) return launch_kernel(allreduce_rmsnorm_kernel<128, 1>, dim3(grid), dim3(128), 0, s, p);
+  if (nvec <= 256) return launch_kernel(allreduce_rmsnorm_kernel<256, 1>, dim3(grid), dim3(256), 0, s, p);
+  if (nvec <= 512) return launch_kernel(allreduce_rmsnorm_kernel<512, 1>, dim3(grid), dim3(512), 0, s, p);
+  if (nvec <= 1024) return launch_kernel(allreduce_rmsnorm_kernel<512, 2>, dim3(grid), dim3(512), 0, s, p);
+  if (nvec <= 2048) return launch_kernel(allreduce_rmsnorm_kernel<512, 4>, dim3(grid), dim3(512), 0, s, p);
+  return -3;
+}
+
+// Bounded wait on a flag nothing sets (health / timeout self-test): result[0] = 1 if the flag reached
+// `expected`, 0 if the wait budget ran out (the status word then holds SWB_ERR_PEER_TIMEOUT).
+int swb_flag_wait(const void* flag, unsigned expected, int* result, void* stream) {
+  swb::flag_wait_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint32_t*>(flag), expected, result);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
+}  // extern "C"

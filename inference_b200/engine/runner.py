@@ -222,6 +222,11 @@ class ModelRunner:
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
+        fused = self.model.comm.fused
+        if fused is not None:
+            fused.begin_capture()
         with torch.cuda.graph(graph):
             toks, logits = self._decode_body(B, splits, want_logits, feedback)
+        if fused is not None:
+            fused.end_capture()
         return _DecodeGraph(graph, toks, logits, self.model.launches)

@@ -87,6 +87,11 @@ class LlamaGpu:
         self._inv_freq = torch.tensor(rope.inv_freq, dtype=torch.float64)
         self.cos = self.sin = None
         self.max_positions = 0
+        pending = getattr(self.comm, "_fused_pending", None)
+        if pending and self.comm.fused is None:
+            from ..parallel.symm import attach_fused
+
+            attach_fused(self.comm, cfg.hidden_size, pending)
         self.launches = 0  # kernels launched by the last forward (for accounting)
 
     # ---- weights --------------------------------------------------------------------------------
@@ -205,9 +210,14 @@ class LlamaGpu:
         block_size = kv_pool.shape[4]
         q_cols = self.hq * D
         n = 1
+        pending_h = None
         for li, L in enumerate(self.layers):
-            h = ops.rmsnorm(res, L.ln1, eps, w_offset=woff) if branch is None else \
-                ops.rmsnorm(branch, L.ln1, eps, residual=res, w_offset=woff)
+            if pending_h is not None:
+                h = pending_h           # already all-reduced, added to the residual and normed with this ln1
+            elif branch is None:
+                h = ops.rmsnorm(res, L.ln1, eps, w_offset=woff)
+            else:
+                h = ops.rmsnorm(branch, L.ln1, eps, residual=res, w_offset=woff)
             qkv = ops.gemm_bf16(h, L.qkv, bias=L.qkv_bias)
             ops.rope_kv_write(qkv, inp.positions, inp.slot_mapping, self.cos, self.sin, kv_pool[li, 0], kv_pool[li, 1],
                               self.hq, self.hkv, D, rot_dim=self.rot_dim, interleaved=self.rope_interleaved,
@@ -217,28 +227,39 @@ class LlamaGpu:
             attn = ops.paged_attention(q, kv_pool[li, 0], kv_pool[li, 1], inp.block_table, inp.kv_lens, cu_q=inp.cu_q,
                                        max_q_len=inp.max_q_len, scale=cfg.attn_scale, causal=True, decode=inp.decode,
                                        num_splits=inp.attn_splits, softcap=cfg.attn_logit_softcap or 0.0)
-            branch = ops.gemm_bf16(attn, L.o)
-            branch = self.comm.all_reduce(branch)
-            if L.post_attn_ln is not None:
-                branch = ops.rmsnorm(branch, L.post_attn_ln, eps, w_offset=woff)
-                n += 1
-            h = ops.rmsnorm(branch, L.ln2, eps, residual=res, w_offset=woff)
+            fused = self.comm.fused if (self.comm.fused is not None and T <= self.comm.fused.max_tokens and
+                                        L.post_attn_ln is None) else None
+            if fused is not None:
+                h = fused.gemm_allreduce_rmsnorm(attn, L.o, res, L.ln2, eps, woff)
+            else:
+                branch = ops.gemm_bf16(attn, L.o)
+                branch = self.comm.all_reduce(branch)
+                if L.post_attn_ln is not None:
+                    branch = ops.rmsnorm(branch, L.post_attn_ln, eps, w_offset=woff)
+                    n += 1
+                h = ops.rmsnorm(branch, L.ln2, eps, residual=res, w_offset=woff)
             gu = ops.gemm_bf16(h, L.gate_up)
             act = ops.gated_act_mul(gu, cfg.mlp_activation)
-            branch = ops.gemm_bf16(act, L.down)
-            branch = self.comm.all_reduce(branch)
-            if L.post_mlp_ln is not None:
-                branch = ops.rmsnorm(branch, L.post_mlp_ln, eps, w_offset=woff)
-                n += 1
+            if fused is not None and L.post_mlp_ln is None:
+                # the down-projection's all-reduce fuses with the NEXT norm (next layer's ln1 or the final norm)
+                nxt = self.layers[li + 1].ln1 if li + 1 < len(self.layers) else self.norm
+                pending_h = fused.gemm_allreduce_rmsnorm(act, L.down, res, nxt, eps, woff)
+                branch = None
+            else:
+                pending_h = None
+                branch = ops.gemm_bf16(act, L.down)
+                branch = self.comm.all_reduce(branch)
+                if L.post_mlp_ln is not None:
+                    branch = ops.rmsnorm(branch, L.post_mlp_ln, eps, w_offset=woff)
+                    n += 1
             n += 9 if inp.attn_splits == 1 or not inp.decode else 10
         self.launches = n
-        if inp.logits_rows is not None:
-            # fold the last branch into the residual first, then pick the rows to project
-            tmp = ops.rmsnorm(branch, self.norm, eps, residual=res, w_offset=woff)
-            self.launches += 1
-            return tmp.index_select(0, inp.logits_rows)
+        final = pending_h if pending_h is not None else ops.rmsnorm(branch, self.norm, eps, residual=res,
+                                                                    w_offset=woff)
         self.launches += 1
-        return ops.rmsnorm(branch, self.norm, eps, residual=res, w_offset=woff)
+        if inp.logits_rows is not None:
+            return final.index_select(0, inp.logits_rows)
+        return final
 
     def logits_local(self, hidden: torch.Tensor) -> torch.Tensor:
         """fp32 logits of this rank's vocabulary shard: [R, vocab / P]."""

@@ -1,0 +1,97 @@
+"""Worker for the multi-GPU tensor-parallel tests (launched by torch.distributed.run, one rank per GPU)."""
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+    from inference_b200 import ops
+    from inference_b200.engine.kv_pool import PagedKvPool, PagedSequence
+    from inference_b200.engine.runner import ModelRunner
+    from inference_b200.models import ModelConfig
+    from inference_b200.models.llama import LlamaGpu
+    from inference_b200.models.oracle import OracleLlama, random_llama_weights
+    from inference_b200.parallel import init_distributed
+    from inference_b200.parallel.symm import FusedCollectives
+
+    mode = sys.argv[1] if len(sys.argv) > 1 else "fused"
+    comm = init_distributed()
+    dev = comm.device
+    P, r = comm.world, comm.rank
+
+    # 1. fused all-reduce + residual + rmsnorm against a torch reference
+    H = 1024
+    fc = FusedCollectives(comm, H, max_tokens=64)
+    g = torch.Generator(device=dev).manual_seed(100 + r)
+    for T in (1, 7, 64):
+        for it in range(3):
+            part = (torch.randn(T, H, device=dev, generator=g) * 0.5).bfloat16()
+            allp = comm.all_gather(part[None], dim=0).float()           # [P, T, H]
+            res = (torch.randn(T, H, device=dev, generator=torch.Generator(device=dev).manual_seed(7 + it)) * 0.5) \
+                .bfloat16()
+            w = (torch.rand(H, device=dev, generator=torch.Generator(device=dev).manual_seed(9)) + 0.5).bfloat16()
+            buf, i = fc.exchange_buffer(T)
+            buf.copy_(part)
+            res_k = res.clone()
+            out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+            fc._launch(i, T, res_k, w, 1e-5, 0.0, out)
+            torch.cuda.synchronize()
+            s = (allp.sum(0) + res.float()).bfloat16()
+            assert torch.equal(res_k, s), f"rank {r}: residual mismatch T={T}"
+            sf = s.float()
+            ref = sf * torch.rsqrt(sf.pow(2).mean(-1, keepdim=True) + 1e-5) * w.float()
+            assert (out.float() - ref).abs().max().item() < 3e-2, f"rank {r}: norm mismatch T={T}"
+            t2 = part.clone()
+            fc.all_reduce(t2)
+            torch.cuda.synchronize()
+            assert (t2.float() - allp.sum(0)).abs().max().item() < 2e-2
+    fc.check()
+
+    # 2. TP=k model == TP=1 oracle within bf16 tolerance, through prefill and graph decode
+    cfg = ModelConfig.from_json({"hidden_size": 1024, "intermediate_size": 2048, "num_hidden_layers": 2,
+                                 "num_attention_heads": 8, "num_key_value_heads": 8, "head_dim": 128,
+                                 "vocab_size": 4096, "rope_theta": 10000.0})
+    w = {k: v.bfloat16().float() for k, v in random_llama_weights(cfg, seed=1, std=0.05).items()}
+    oracle = OracleLlama(cfg, w, dtype=torch.float32, device=dev)
+    if mode == "fused":
+        from inference_b200.parallel.symm import attach_fused
+
+        attach_fused(comm)
+    model = LlamaGpu(cfg, comm=comm, device=dev).load_state_dict(w)
+    assert (comm.fused is not None) == (mode == "fused")
+    pool = PagedKvPool(cfg.num_layers, 64, model.hkv, cfg.head_dim, 16, device=dev)
+    runner = ModelRunner(model, pool, max_batch=4, max_seq_len=256)
+    prompts = [list(range(3, 40)), list(range(100, 109))]
+    seqs = [PagedSequence(pool) for _ in prompts]
+    logits = runner.prefill(seqs, prompts, want_logits=True)
+    caches = []
+    for i, p in enumerate(prompts):
+        c = oracle.make_cache()
+        ref = oracle.decode_logits(torch.tensor([p], device=dev), c, 0)[0]
+        caches.append(c)
+        assert (logits[i] - ref).abs().max().item() < 0.08 * max(1.0, ref.abs().max().item()), f"prefill seq {i}"
+    toks = [int(logits[i].argmax()) for i in range(2)]
+    for step in range(4):
+        lg = runner.decode(seqs, toks, want_logits=True)
+        for i in range(2):
+            ref = oracle.decode_logits(torch.tensor([[toks[i]]], device=dev), caches[i], caches[i].offset)[0]
+            assert (lg[i] - ref).abs().max().item() < 0.08 * max(1.0, ref.abs().max().item()), f"decode {step} {i}"
+        toks = [int(lg[i].argmax()) for i in range(2)]
+    got = runner.decode(seqs, toks).tolist()
+    allg = comm.all_gather(torch.tensor([got], device=dev), dim=0)
+    assert all(torch.equal(allg[0], allg[k]) for k in range(P)), "ranks disagree on sampled tokens"
+    ops.check_status()
+    comm.barrier()
+    if r == 0:
+        print(f"TP_WORKER_OK world={P} mode={mode}")
+
+
+if __name__ == "__main__":
+    main()
+    import torch.distributed as dist
+
+    if dist.is_initialized():
+        dist.destroy_process_group()
