@@ -101,6 +101,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--prompt-len", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
+    ap.add_argument("--emulate-tp", type=int, default=0,
+                    help="debug only: run ONE rank's tensor-parallel shard shapes without communication (invalid run)")
     ap.add_argument("--no-extra", action="store_true", help="skip the TTFT / batch-1 / batch-8 side measurements")
     args = ap.parse_args()
 
@@ -126,6 +128,13 @@ def main() -> int:
     if args.layers:
         cfg.num_layers = args.layers
         invalid = f"debug run with {args.layers} layers"
+    if args.emulate_tp > 1:
+        P = args.emulate_tp
+        cfg.num_heads //= P
+        cfg.num_kv_heads //= P
+        cfg.intermediate_size //= P
+        cfg.vocab_size //= P
+        invalid = (invalid or "") + f" single-rank shard shapes of tp{P}"
 
     if world > 1 and os.environ.get("SWB_COMM", "auto") != "nccl":
         try:

@@ -1,7 +1,19 @@
 // extern "C" entry points for the dense GEMM.
 #include "gemm_tcgen05.cuh"
 
+namespace swb {
+namespace {
+unsigned long long* g_trace = nullptr;
+}
+unsigned long long* gemm_trace_buffer() { return g_trace; }
+}  // namespace swb
+
 extern "C" {
+
+// Profiling aid: when set to a device buffer of at least grid * 8 uint64, decode GEMM CTAs record globaltimer
+// stamps of their phases (start, setup done, dependency satisfied, accumulator complete, partials delivered,
+// cluster barrier passed, outputs stored, end). Pass null to switch it off.
+void swb_gemm_set_trace(void* device_buffer) { swb::g_trace = reinterpret_cast<unsigned long long*>(device_buffer); }
 
 int swb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* D, int ldd, int T, int N, int K,
                   const void* bias, const void* residual, int ld_res, int act, int out_fp32, void* workspace,

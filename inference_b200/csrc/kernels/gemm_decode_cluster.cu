@@ -31,7 +31,7 @@ struct DecCfg {
   static constexpr uint32_t A_BYTES = BM * BK * 2;
   static constexpr uint32_t B_BYTES = BLOCK_N * BK * 2;
   static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr uint32_t RECV_BYTES = (BM + 8) * BLOCK_N * 4;  // CLUSTER slots of [rows per member][BLOCK_N] fp32
+  static constexpr uint32_t RECV_BYTES = (BM + 16) * BLOCK_N * 4;  // CLUSTER slots of [BLOCK_N][rows per member] fp32
   static constexpr uint32_t TMEM_COLS = BLOCK_N < 32 ? 32 : BLOCK_N;
   static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + RECV_BYTES + 1024 + 256;
 };
@@ -72,8 +72,9 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
                            const GemmParams p) {
   using Cfg = DecCfg<BLOCK_N>;
   constexpr int STAGES = Cfg::STAGES;
-  constexpr int R = (BM + CLUSTER - 1) / CLUSTER;  // output-feature rows owned by each cluster member
-  constexpr int NV = BLOCK_N / 4;                  // float4 groups per row (power of two)
+  // output-feature rows owned by each cluster member, rounded up to 8 so the final store is 16-byte vectors
+  constexpr int R = (((BM + CLUSTER - 1) / CLUSTER) + 7) / 8 * 8;
+  static_assert(CLUSTER * R * BLOCK_N * 4 <= (int)Cfg::RECV_BYTES, "receive buffer too small for this cluster size");
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -87,6 +88,8 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  unsigned long long* tr = p.trace ? p.trace + (size_t)blockIdx.x * 8 : nullptr;
+  if (tr && threadIdx.x == 0) tr[0] = global_timer_ns();
   const uint32_t crank = CLUSTER > 1 ? cluster_ctarank() : 0u;
   const int tile_m = (int)blockIdx.x / CLUSTER;
   const int kps = (p.kblocks_total + CLUSTER - 1) / CLUSTER;
@@ -114,6 +117,7 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   pdl_launch_dependents();
+  if (tr && threadIdx.x == 0) tr[1] = global_timer_ns();   // setup done
   if (CLUSTER > 1) cluster_arrive();  // phase 1: "my shared memory is live" (waited on before remote stores)
 
   if (warp == 0) {
@@ -126,6 +130,7 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
         tma_load_2d_hint(smem + i * Cfg::STAGE_BYTES, &tmap_w, &bar_full[i], (kb0 + i) * BK, tile_m * BM, pol_w);
       }
       pdl_wait();
+      if (tr) tr[2] = global_timer_ns();                   // dependency satisfied
       int stage = 0;
       uint32_t phase = 0;
       uint32_t outstanding = (pre >= 32) ? 0xffffffffu : ((1u << pre) - 1u);
@@ -189,15 +194,17 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
     const int row = quarter * 32 + lane;
     bool have = nkb > 0;
     if (have) have = mbar_wait(bar_tfull, 0, s_abort, 900);
-    have = __all_sync(0xffffffffu, have);  // warp-uniform: tcgen05.ld is warp-collective
+    have = __all_sync(0xffffffffu, have);
+    if (tr && threadIdx.x == 64) tr[3] = global_timer_ns();  // accumulator complete  // warp-uniform: tcgen05.ld is warp-collective
     tc_fence_after_sync();
     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const uint32_t recv_local = smem_u32(recv);
     const uint32_t owner = (uint32_t)(row / R);
     const int lr = row - (int)owner * R;
-    // slot `crank` of the owner's receive buffer: [R rows][BLOCK_N] fp32, float4 groups XOR-swizzled by row
-    const uint32_t row_base = recv_local + (uint32_t)(((crank * R + lr) * BLOCK_N) * 4);
-    const uint32_t remote_row = CLUSTER > 1 ? map_to_cta(row_base, owner) : row_base;
+    // slot `crank` of the owner's receive buffer, laid out [token][R rows] fp32: a warp's 32 consecutive rows
+    // store 128 contiguous bytes per token, and the owner later reads 8 consecutive rows as two float4
+    const uint32_t col_base = recv_local + (uint32_t)((crank * BLOCK_N * R + lr) * 4);
+    const uint32_t remote = CLUSTER > 1 ? map_to_cta(col_base, owner) : col_base;
 #pragma unroll 1
     for (int ch = 0; ch < BLOCK_N / 16; ++ch) {
       float v[16];
@@ -208,12 +215,14 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
         for (int j = 0; j < 16; ++j) v[j] = 0.f;
       }
 #pragma unroll
-      for (int j = 0; j < 16; j += 4) {
-        const int c4 = (ch * 4 + j / 4) ^ (lr & (NV - 1));
-        st_cluster_f32x4(remote_row + (uint32_t)(c4 * 16), v[j], v[j + 1], v[j + 2], v[j + 3]);
+      for (int j = 0; j < 16; ++j) {
+        if (ch * 16 + j < p.N)   // tokens past the batch are never read back
+          asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + (uint32_t)((ch * 16 + j) * R * 4)), "f"(v[j])
+                       : "memory");
       }
     }
     tc_fence_before_sync();
+    if (tr && threadIdx.x == 64) tr[4] = global_timer_ns();  // partials delivered
   }
 
   // ---- phase 2: every partial slice has been delivered ----
@@ -225,34 +234,86 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
     __syncthreads();
   }
 
+  if (tr && threadIdx.x == 64) tr[5] = global_timer_ns();    // cluster barrier passed
   if (warp >= 2) {
     const int et = (warp - 2) * 32 + lane;  // 0..127
-    for (int idx = et; idx < R * BLOCK_N; idx += 128) {
-      const int lr = idx % R;          // consecutive threads -> consecutive features: coalesced stores
-      const int tok = idx / R;
-      const int row = (int)crank * R + lr;
+    constexpr int R8 = R / 8;
+    for (int idx = et; idx < R8 * BLOCK_N; idx += 128) {
+      const int f8 = idx % R8;         // consecutive threads -> consecutive 16-byte feature groups of one token
+      const int tok = idx / R8;
+      const int row = (int)crank * R + f8 * 8;
       const int feat = tile_m * BM + row;
       if (row >= BM || feat >= p.M || tok >= p.N) continue;
-      const int c4 = (tok >> 2) ^ (lr & (NV - 1));
-      float acc = 0.f;
+      float acc[8];
 #pragma unroll
-      for (int src = 0; src < CLUSTER; ++src) acc += recv[(src * R + lr) * BLOCK_N + c4 * 4 + (tok & 3)];
-      float x = act_apply(acc + (p.bias ? __bfloat162float(p.bias[feat]) : 0.f), p.act);
-      if (p.residual) x += __bfloat162float(p.residual[(size_t)tok * p.ld_res + feat]);
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+      for (int src = 0; src < CLUSTER; ++src) {
+        const float4* rp = reinterpret_cast<const float4*>(recv + ((size_t)src * BLOCK_N + tok) * R + f8 * 8);
+        const float4 a0 = rp[0], a1 = rp[1];
+        acc[0] += a0.x; acc[1] += a0.y; acc[2] += a0.z; acc[3] += a0.w;
+        acc[4] += a1.x; acc[5] += a1.y; acc[6] += a1.z; acc[7] += a1.w;
+      }
+      const int nvalid = min(8, p.M - feat);
       const size_t off = (size_t)tok * p.ldd + feat;
-      if (p.out_fp32)
-        reinterpret_cast<float*>(p.out)[off] = x;
-      else
-        reinterpret_cast<bf16*>(p.out)[off] = __float2bfloat16(x);
+      const bool vec = p.vec_ok && nvalid == 8 && ((p.ldd & 7) == 0) && ((feat & 7) == 0) && (!p.residual || (p.ld_res & 7) == 0);
+      if (vec) {
+        if (p.bias) {
+          const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + feat));
+          const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 t = __bfloat1622float2(bh[j]);
+            acc[2 * j] += t.x;
+            acc[2 * j + 1] += t.y;
+          }
+        }
+        if (p.act != SWB_ACT_NONE) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = act_apply(acc[j], p.act);
+        }
+        if (p.residual) {
+          const uint4 r = *reinterpret_cast<const uint4*>(p.residual + (size_t)tok * p.ld_res + feat);
+          const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 t = __bfloat1622float2(rh[j]);
+            acc[2 * j] += t.x;
+            acc[2 * j + 1] += t.y;
+          }
+        }
+        if (p.out_fp32) {
+          float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + off);
+          op[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+          op[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+        } else {
+          uint4 o;
+          __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+          *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + off) = o;
+        }
+      } else {
+        for (int j = 0; j < nvalid; ++j) {
+          float x = act_apply(acc[j] + (p.bias ? __bfloat162float(p.bias[feat + j]) : 0.f), p.act);
+          if (p.residual) x += __bfloat162float(p.residual[(size_t)tok * p.ld_res + feat + j]);
+          if (p.out_fp32)
+            reinterpret_cast<float*>(p.out)[off + j] = x;
+          else
+            reinterpret_cast<bf16*>(p.out)[off + j] = __float2bfloat16(x);
+        }
+      }
     }
   }
 
+  if (tr && threadIdx.x == 64) tr[6] = global_timer_ns();    // outputs stored
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
+  if (tr && threadIdx.x == 0) tr[7] = global_timer_ns();
 }
 
 template <int BLOCK_N, int CLUSTER>
@@ -299,9 +360,7 @@ int launch_cluster(int cluster, const CUtensorMap& tw, const CUtensorMap& tx, co
     case 2: return launch_one<BLOCK_N, 2>(tw, tx, p, s);
     case 3: return launch_one<BLOCK_N, 3>(tw, tx, p, s);
     case 4: return launch_one<BLOCK_N, 4>(tw, tx, p, s);
-    case 5: return launch_one<BLOCK_N, 5>(tw, tx, p, s);
     case 6: return launch_one<BLOCK_N, 6>(tw, tx, p, s);
-    case 7: return launch_one<BLOCK_N, 7>(tw, tx, p, s);
     case 8: return launch_one<BLOCK_N, 8>(tw, tx, p, s);
   }
   return -2;
@@ -331,15 +390,20 @@ int gemm_decode_cluster_launch(const GemmArgs& a, int force_cluster, cudaStream_
   p.residual = reinterpret_cast<const __nv_bfloat16*>(a.residual);
   p.ld_res = a.ld_res;
   p.act = a.act;
+  p.trace = gemm_trace_buffer();
+  p.vec_ok = ((reinterpret_cast<uintptr_t>(a.D) & 15) == 0) && (!a.bias || (reinterpret_cast<uintptr_t>(a.bias) & 15) == 0) &&
+             (!a.residual || (reinterpret_cast<uintptr_t>(a.residual) & 15) == 0) && (!a.out_fp32 || (a.ldd % 4) == 0);
   // Two CTAs can be resident per SM. Measured on B200 over Llama-3-8B projections: the fastest member count is
   // the largest one that keeps the grid under ~1.75 CTAs per SM with at least 6 k-blocks per member.
   int cluster = 1;
-  for (int c = 2; c <= 8; ++c) {
+  for (int c : {2, 3, 4, 6, 8}) {
     if ((long)p.tiles_m * c * 4 > 7L * sms) break;
-    if (p.kblocks_total / c < 6) break;
+    if (p.kblocks_total / c < 2) break;
     cluster = c;
   }
   if (force_cluster > 0) cluster = std::min(8, force_cluster);
+  if (cluster == 5) cluster = 4;
+  if (cluster == 7) cluster = 6;
   CUtensorMap tw, tx;
   int r = make_tmap_bf16_2d(&tw, a.W, a.N, a.K, a.ldw, BM);
   if (r) return r;

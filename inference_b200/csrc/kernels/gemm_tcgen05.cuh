@@ -33,6 +33,7 @@ struct GemmParams {
   float* workspace;
   int* counters;
   int* status;
+  unsigned long long* trace;  // optional [grid][8] globaltimer stamps of kernel phases (profiling aid)
 };
 
 // User-level problem: D[T, N] = act(A[T, K] * W[N, K]^T + bias[N]) + residual[T, N].
@@ -61,5 +62,6 @@ int gemm_decode_cluster_supported(int T);
 int gemm_decode_cluster_launch(const GemmArgs& a, int force_cluster, cudaStream_t stream);
 int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows);
 int device_sm_count();
+unsigned long long* gemm_trace_buffer();
 
 }  // namespace swb
