@@ -84,6 +84,12 @@ def _declare_kernels(lib: ctypes.CDLL) -> None:
                            c_int, c_void_p, c_size_t, c_void_p])
     sig("swb_attn_dense", [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_ll, c_int, c_void_p, c_ll, c_int, c_int,
                            c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    sig("swb_axpy", [c_void_p, c_void_p, c_void_p, c_ll, c_float, c_float, c_int, c_void_p])
+    sig("swb_groupnorm", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int,
+                          c_void_p])
+    sig("swb_upsample2x", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    sig("swb_softmax_rows", [c_void_p, c_void_p, c_int, c_int, c_ll, c_ll, c_float, c_void_p])
+    sig("swb_rgb8", [c_void_p, c_void_p, c_ll, c_int, c_void_p])
     sig("swb_comm_max_ctas", [])
     sig("swb_comm_flag_words", [])
     sig("swb_allreduce_rmsnorm", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,

@@ -194,7 +194,8 @@ __global__ void __launch_bounds__(256) rope_kv_write_kernel(
     v[i] = (i < epl && d < D) ? __bfloat162float(src[d]) : 0.f;
   }
   bf16* dst = src;
-  if (!is_q) {
+  if (!is_q && (is_k ? kcache : vcache) != nullptr) {
+    // with a cache the k / v heads go to their slot (in-place otherwise: dense attention reads qkv directly)
     const long long slot = slot_mapping ? slot_mapping[t] : -1;
     if (slot < 0) {
       dst = nullptr;  // padding token: nothing to cache

@@ -1,0 +1,61 @@
+"""Wrappers for the media kernels: sampler axpy, GroupNorm(+SiLU), nearest upsample, row softmax, RGB8."""
+from __future__ import annotations
+
+import torch
+
+from .._native import kernels
+from .runtime import check, require_cuda, stream_ptr
+
+
+def axpy(a: float, x: torch.Tensor, b: float, y: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out = a * x + b * y (the flow-matching Euler update is axpy(1, x, dt, v))."""
+    require_cuda(x, y)
+    assert x.shape == y.shape and x.dtype == y.dtype and x.is_contiguous() and y.is_contiguous()
+    if out is None:
+        out = torch.empty_like(x)
+    rc = kernels().swb_axpy(x.data_ptr(), y.data_ptr(), out.data_ptr(), x.numel(), a, b,
+                            1 if x.dtype == torch.float32 else 0, stream_ptr())
+    check(rc, "swb_axpy")
+    return out
+
+
+def groupnorm_nhwc(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, groups: int = 32, eps: float = 1e-6,
+                   silu: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
+    """x: [N, H, W, C] bf16 channels-last. GroupNorm with optional fused SiLU."""
+    require_cuda(x)
+    N, H, W, C = x.shape
+    assert x.is_contiguous() and x.dtype == torch.bfloat16
+    if out is None:
+        out = torch.empty_like(x)
+    stats = torch.empty((N, groups, 2), dtype=torch.float32, device=x.device)
+    rc = kernels().swb_groupnorm(x.data_ptr(), stats.data_ptr(), gamma.data_ptr(), beta.data_ptr(), out.data_ptr(), N,
+                                 H * W, C, groups, eps, 1 if silu else 0, stream_ptr())
+    check(rc, "swb_groupnorm")
+    return out
+
+
+def upsample2x_nhwc(x: torch.Tensor) -> torch.Tensor:
+    require_cuda(x)
+    N, H, W, C = x.shape
+    out = torch.empty((N, 2 * H, 2 * W, C), dtype=x.dtype, device=x.device)
+    check(kernels().swb_upsample2x(x.data_ptr(), out.data_ptr(), N, H, W, C, stream_ptr()), "swb_upsample2x")
+    return out
+
+
+def softmax_rows(scores: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """fp32 [R, C] -> bf16 probabilities softmax(scale * scores)."""
+    require_cuda(scores)
+    assert scores.dtype == torch.float32 and scores.stride(1) == 1
+    out = torch.empty(scores.shape, dtype=torch.bfloat16, device=scores.device)
+    check(kernels().swb_softmax_rows(scores.data_ptr(), out.data_ptr(), scores.shape[0], scores.shape[1],
+                                     scores.stride(0), out.stride(0), scale, stream_ptr()), "swb_softmax_rows")
+    return out
+
+
+def rgb8_nhwc(x: torch.Tensor) -> torch.Tensor:
+    """[N, H, W, C>=3] bf16 in [-1, 1] -> uint8 [N, H, W, 3] (round half to even)."""
+    require_cuda(x)
+    N, H, W, C = x.shape
+    out = torch.empty((N, H, W, 3), dtype=torch.uint8, device=x.device)
+    check(kernels().swb_rgb8(x.data_ptr(), out.data_ptr(), N * H * W, C, stream_ptr()), "swb_rgb8")
+    return out

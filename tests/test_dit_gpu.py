@@ -1,0 +1,76 @@
+"""FLUX-style DiT on sm_100a kernels vs the fp32 oracle (small head_dim-128 config), plus the media kernels."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_media_kernels():
+    from inference_b200 import ops
+
+    x = torch.randn(1000, 64, device="cuda").bfloat16()
+    y = torch.randn(1000, 64, device="cuda").bfloat16()
+    z = ops.axpy(1.0, x, -0.3, y)
+    assert torch.allclose(z.float(), x.float() - 0.3 * y.float(), atol=2e-2)
+    zf = ops.axpy(0.5, x.float(), 2.0, y.float())
+    assert torch.allclose(zf, 0.5 * x.float() + 2.0 * y.float(), atol=1e-5)
+    a = torch.randn(2, 24, 20, 64, device="cuda").bfloat16()
+    g = (torch.rand(64, device="cuda") + 0.5).bfloat16()
+    b = (torch.randn(64, device="cuda") * 0.1).bfloat16()
+    for silu in (False, True):
+        out = ops.groupnorm_nhwc(a, g, b, groups=8, eps=1e-6, silu=silu)
+        ref = torch.nn.functional.group_norm(a.float().permute(0, 3, 1, 2), 8, g.float(), b.float(), 1e-6)
+        if silu:
+            ref = torch.nn.functional.silu(ref)
+        assert torch.allclose(out.float(), ref.permute(0, 2, 3, 1), atol=4e-2, rtol=2e-2)
+    up = ops.upsample2x_nhwc(a)
+    ref = torch.nn.functional.interpolate(a.float().permute(0, 3, 1, 2), scale_factor=2, mode="nearest")
+    assert torch.equal(up.float(), ref.permute(0, 2, 3, 1))
+    s = torch.randn(37, 1000, device="cuda")
+    p = ops.softmax_rows(s, 0.5)
+    assert torch.allclose(p.float(), torch.softmax(s * 0.5, -1), atol=2e-3)
+    img = (torch.rand(1, 16, 16, 8, device="cuda") * 2.4 - 1.2).bfloat16()
+    u8 = ops.rgb8_nhwc(img)
+    ref = torch.round((img[..., :3].float().clamp(-1, 1) + 1) * 127.5).to(torch.uint8)
+    assert torch.equal(u8, ref)
+
+
+def test_rope_in_place_updates_k_without_cache():
+    from inference_b200 import ops
+
+    T, H, D = 6, 2, 128
+    qkv = torch.randn(T, 3 * H * D, device="cuda").bfloat16()
+    before = qkv.clone()
+    pos = torch.arange(T, device="cuda", dtype=torch.int32)
+    ang = torch.arange(T, dtype=torch.float32)[:, None] * (1.0 / 10000 ** (torch.arange(0, D, 2) / D))[None]
+    cos, sin = ang.cos().cuda().contiguous(), ang.sin().cuda().contiguous()
+    ops.rope_kv_write(qkv, pos, None, cos, sin, None, None, H, H, D, interleaved=True)
+    k_before = before[:, H * D:2 * H * D].float().view(T, H, D)
+    x0, x1 = k_before[..., 0::2], k_before[..., 1::2]
+    ref = torch.stack((x0 * cos[:, None] - x1 * sin[:, None], x1 * cos[:, None] + x0 * sin[:, None]), -1).flatten(-2)
+    got = qkv[:, H * D:2 * H * D].float().view(T, H, D)
+    assert torch.allclose(got, ref, atol=3e-2)
+    assert torch.equal(qkv[:, 2 * H * D:], before[:, 2 * H * D:])
+
+
+@pytest.mark.parametrize("batch", [1, 2])
+def test_flux_dit_matches_oracle(batch):
+    from inference_b200.models.dit_flux import FluxConfig, FluxDiTGpu, OracleFluxDiT, make_ids, random_flux_weights
+
+    cfg = FluxConfig(in_channels=64, vec_in_dim=64, context_in_dim=128, hidden_size=256, num_heads=2, depth=2,
+                     depth_single=2)
+    w = {k: v.bfloat16().float() for k, v in random_flux_weights(cfg, seed=0, std=0.05).items()}
+    oracle = OracleFluxDiT(cfg, w, device="cuda")
+    model = FluxDiTGpu(cfg, device=torch.device("cuda")).load_state_dict(w)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    hh, ww, St = 6, 5, 19
+    img = torch.randn(batch, hh * ww, 64, device="cuda", generator=g).bfloat16()
+    txt = torch.randn(batch, St, 128, device="cuda", generator=g).bfloat16()
+    y = torch.randn(batch, 64, device="cuda", generator=g).bfloat16()
+    t = torch.full((batch,), 0.7, device="cuda")
+    gd = torch.full((batch,), 3.5, device="cuda")
+    txt_ids, img_ids = make_ids(hh, ww, St, "cuda")
+    ref = oracle.forward(img.float(), img_ids, txt.float(), txt_ids, t, y.float(), gd)
+    out = model.forward(img, img_ids, txt, txt_ids, t, y, gd)
+    err = (out.float() - ref).abs().max().item()
+    assert err < 0.06 * max(1.0, ref.abs().max().item()), err
