@@ -17,6 +17,7 @@ def main():
     ap.add_argument("--depth", type=int, default=19)
     ap.add_argument("--depth-single", type=int, default=38)
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--vae", action="store_true", help="also time the VAE decode of the final latents")
     args = ap.parse_args()
     from inference_b200.contracts.gen_core.sampling import build_flow_sigmas, compute_mu, image_seq_len
     from inference_b200 import ops
@@ -57,11 +58,26 @@ def main():
     flops_double = 2 * S * H * (3 * H + H + 2 * M) + 4 * S * S * H
     flops_single = 2 * S * H * (3 * H + M) + 2 * S * (H + M) * H + 4 * S * S * H
     tflop = (cfg.depth * flops_double + cfg.depth_single * flops_single) / 1e12
+    vae_ms = None
+    if args.vae:
+        from inference_b200.models.vae import VaeConfig, VaeDecoderGpu
+
+        vae = VaeDecoderGpu(VaeConfig(), dev).init_random(1)
+        z = torch.randn(1, 16, args.size // 8, args.size // 8, device=dev, generator=g)
+        vae.decode_rgb8(z)
+        torch.cuda.synchronize()
+        e0.record()
+        img = vae.decode_rgb8(z)
+        e1.record()
+        torch.cuda.synchronize()
+        vae_ms = round(e0.elapsed_time(e1), 2)
+        assert img.shape == (1, args.size, args.size, 3)
     ops.check_status()
     print(json.dumps({"metric": "flux_dit_ms_per_step", "ms_per_step": round(ms / args.steps, 3),
                       "s_per_image_dit_only": round(ms / 1e3, 3), "steps": args.steps, "size": args.size,
                       "tflop_per_step": round(tflop, 2), "achieved_tflops": round(tflop / (ms / args.steps) * 1e3, 1),
-                      "launches_per_step": model.launches, "weights_gb": round(model.weight_bytes() / 1e9, 2)}))
+                      "launches_per_step": model.launches, "weights_gb": round(model.weight_bytes() / 1e9, 2), "vae_decode_ms": vae_ms,
+                      "s_per_image": round((ms + (vae_ms or 0.0)) / 1e3, 3)}))
 
 
 if __name__ == "__main__":

@@ -93,6 +93,42 @@ __global__ void __launch_bounds__(256) groupnorm_stats_kernel(const bf16* __rest
   }
 }
 
+// Narrow groups (C / G in {1, 2, 4}: a 16-byte vector spans several groups). One CTA covers `chunk` pixels of one
+// sample over all channels; thread t owns vector column t % (C/8) and walks pixels with stride 256 / (C/8).
+// Requires C/8 to divide 256 and G <= 512.
+__global__ void __launch_bounds__(256) groupnorm_stats_narrow_kernel(const bf16* __restrict__ x, float* stats, int HW,
+                                                                    int C, int G, int chunk) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float acc[2 * 512];
+  for (int i = threadIdx.x; i < 2 * G; i += blockDim.x) acc[i] = 0.f;
+  __syncthreads();
+  const int n = blockIdx.y;
+  const int c8 = C / 8, cpg = C / G;
+  const int v = threadIdx.x % c8, lane_p = threadIdx.x / c8, stride_p = 256 / c8;
+  const int p0 = blockIdx.x * chunk, p1 = min(HW, p0 + chunk);
+  float s[8], ss[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s[j] = ss[j] = 0.f;
+  for (int p = p0 + lane_p; p < p1; p += stride_p) {
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(x + ((size_t)n * HW + p) * C + v * 8), f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      s[j] += f[j];
+      ss[j] += f[j] * f[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int g = (v * 8 + j) / cpg;
+    atomicAdd(&acc[2 * g], s[j]);
+    atomicAdd(&acc[2 * g + 1], ss[j]);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 2 * G; i += blockDim.x) atomicAdd(&stats[(size_t)n * G * 2 + i], acc[i]);
+}
+
 // y = silu?((x - mean) * rstd * gamma + beta), NHWC bf16, 8 channels per thread.
 __global__ void __launch_bounds__(256) groupnorm_apply_kernel(const bf16* __restrict__ x, const float* __restrict__ stats,
                                                              const bf16* __restrict__ gamma,
@@ -107,18 +143,27 @@ __global__ void __launch_bounds__(256) groupnorm_apply_kernel(const bf16* __rest
   const long long pix = i / c8;
   const int n = (int)(pix / HW);
   const int cpg = C / G;
-  const int g = c / cpg;
   const float cnt = (float)HW * cpg;
-  const float mean = stats[((size_t)n * G + g) * 2] / cnt;
-  const float var = fmaxf(stats[((size_t)n * G + g) * 2 + 1] / cnt - mean * mean, 0.f);
-  const float rstd = rsqrtf(var + eps);
+  float mean[8], rstd[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int g = (c + j) / cpg;
+    if (j == 0 || (cpg < 8 && (c + j) % cpg == 0)) {
+      mean[j] = stats[((size_t)n * G + g) * 2] / cnt;
+      const float var = fmaxf(stats[((size_t)n * G + g) * 2 + 1] / cnt - mean[j] * mean[j], 0.f);
+      rstd[j] = rsqrtf(var + eps);
+    } else {
+      mean[j] = mean[j - 1];
+      rstd[j] = rstd[j - 1];
+    }
+  }
   float f[8], ga[8], be[8], o[8];
   unpack8(reinterpret_cast<const uint4*>(x)[i], f);
   unpack8(__ldg(reinterpret_cast<const uint4*>(gamma + c)), ga);
   unpack8(__ldg(reinterpret_cast<const uint4*>(beta + c)), be);
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    const float v = (f[j] - mean) * rstd * ga[j] + be[j];
+    const float v = (f[j] - mean[j]) * rstd[j] * ga[j] + be[j];
     o[j] = silu ? silu_f(v) : v;
   }
   reinterpret_cast<uint4*>(out)[i] = pack8(o);
@@ -186,6 +231,31 @@ __global__ void __launch_bounds__(256) rgb8_kernel(const bf16* __restrict__ x, u
   out[i] = (uint8_t)__float2int_rn((v + 1.f) * 127.5f);
 }
 
+// 3x3, stride 1, zero-padding 1 patch gather over NHWC bf16: out[(n, h, w), (kh, kw, c)] = x[n, h+kh-1, w+kw-1, c].
+// The result feeds the tcgen05 GEMM against weights laid out [C_out, (kh, kw, c)].
+__global__ void __launch_bounds__(256) im2col3x3_kernel(const bf16* __restrict__ x, bf16* out, int N, int H, int W,
+                                                       int C) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int c8 = C / 8;
+  const long long total = (long long)N * H * W * 9 * c8;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int v = (int)(i % c8);
+  long long r = i / c8;
+  const int tap = (int)(r % 9);
+  r /= 9;
+  const int w = (int)(r % W);
+  r /= W;
+  const int h = (int)(r % H);
+  const int n = (int)(r / H);
+  const int ih = h + tap / 3 - 1, iw = w + tap % 3 - 1;
+  uint4 val = make_uint4(0, 0, 0, 0);
+  if (ih >= 0 && ih < H && iw >= 0 && iw < W)
+    val = reinterpret_cast<const uint4*>(x)[(((size_t)n * H + ih) * W + iw) * c8 + v];
+  reinterpret_cast<uint4*>(out)[i] = val;
+}
+
 inline int blocks_for(long long n) { return (int)((n + 255) / 256); }
 
 }  // namespace
@@ -205,19 +275,25 @@ int swb_axpy(const void* x, const void* y, void* out, long long n, float a, floa
                        reinterpret_cast<const bf16*>(y), reinterpret_cast<bf16*>(out), n / 8, a, b);
 }
 
-// stats: fp32 [N, G, 2] scratch. x, out: NHWC bf16 [N, H*W, C]; C / G must be a multiple of 8.
+// stats: fp32 [N, G, 2] scratch. x, out: NHWC bf16 [N, H*W, C]; C / G a multiple of 8, or one of 1, 2, 4 (then
+// C/8 must divide 256 and G <= 512).
 int swb_groupnorm(const void* x, void* stats, const void* gamma, const void* beta, void* out, int N, int HW, int C,
                   int G, float eps, int silu, void* stream) {
   using namespace swb;
   if (N <= 0 || HW <= 0) return 0;
-  if (C % G != 0 || (C / G) % 8 != 0) return -3;
+  if (C % G != 0 || C % 8 != 0) return -3;
+  const int cpg = C / G;
+  const bool narrow = cpg % 8 != 0;
+  if (narrow && (8 % cpg != 0 || 256 % (C / 8) != 0 || G > 512)) return -3;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   cudaError_t e = cudaMemsetAsync(stats, 0, (size_t)N * G * 2 * sizeof(float), s);
   if (e != cudaSuccess) return -(int)e;
   const int chunk = 1024;
   dim3 grid((HW + chunk - 1) / chunk, G, N);
-  int rc = launch_kernel(groupnorm_stats_kernel, grid, dim3(256), 0, s, reinterpret_cast<const bf16*>(x),
-                         reinterpret_cast<float*>(stats), HW, C, G, chunk);
+  int rc = narrow ? launch_kernel(groupnorm_stats_narrow_kernel, dim3((HW + chunk - 1) / chunk, N), dim3(256), 0, s,
+                                  reinterpret_cast<const bf16*>(x), reinterpret_cast<float*>(stats), HW, C, G, chunk)
+                  : launch_kernel(groupnorm_stats_kernel, grid, dim3(256), 0, s, reinterpret_cast<const bf16*>(x),
+                                  reinterpret_cast<float*>(stats), HW, C, G, chunk);
   if (rc) return rc;
   const long long n8 = (long long)N * HW * C / 8;
   return launch_kernel(groupnorm_apply_kernel, dim3(blocks_for(n8)), dim3(256), 0, s, reinterpret_cast<const bf16*>(x),
@@ -230,6 +306,17 @@ int swb_upsample2x(const void* x, void* out, int N, int H, int W, int C, void* s
   if (C % 8) return -3;
   const long long total = (long long)N * 4 * H * W * (C / 8);
   return launch_kernel(upsample2x_kernel, dim3(blocks_for(total)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+                       reinterpret_cast<const bf16*>(x), reinterpret_cast<bf16*>(out), N, H, W, C);
+}
+
+int swb_im2col3x3(const void* x, void* out, int N, int H, int W, int C, void* stream) {
+  using namespace swb;
+  if (C % 8) return -3;
+  const long long total = (long long)N * H * W * 9 * (C / 8);
+  if (total <= 0) return 0;
+  const long long blocks = (total + 255) / 256;
+  if (blocks > 0x7fffffffLL) return -4;
+  return launch_kernel(im2col3x3_kernel, dim3((unsigned)blocks), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
                        reinterpret_cast<const bf16*>(x), reinterpret_cast<bf16*>(out), N, H, W, C);
 }
 

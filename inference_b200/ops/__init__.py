@@ -4,4 +4,4 @@ from .gemm import gemm_bf16, gemm_workspace, linear  # noqa: F401
 from .llm import (argmax, embedding, gated_act_mul, gated_residual, layernorm_mod, rmsnorm, rope_kv_write,  # noqa: F401
                   spec_verify_greedy)
 from .runtime import KernelError, check_status, device_status  # noqa: F401
-from .dit import axpy, groupnorm_nhwc, rgb8_nhwc, softmax_rows, upsample2x_nhwc  # noqa: E402,F401
+from .dit import axpy, groupnorm_nhwc, im2col3x3_nhwc, rgb8_nhwc, softmax_rows, upsample2x_nhwc  # noqa: E402,F401

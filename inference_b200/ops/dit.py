@@ -59,3 +59,13 @@ def rgb8_nhwc(x: torch.Tensor) -> torch.Tensor:
     out = torch.empty((N, H, W, 3), dtype=torch.uint8, device=x.device)
     check(kernels().swb_rgb8(x.data_ptr(), out.data_ptr(), N * H * W, C, stream_ptr()), "swb_rgb8")
     return out
+
+
+def im2col3x3_nhwc(x: torch.Tensor) -> torch.Tensor:
+    """[N, H, W, C] bf16 -> [N*H*W, 9*C] patches (stride 1, zero padding 1), column order (kh, kw, c)."""
+    require_cuda(x)
+    N, H, W, C = x.shape
+    assert x.is_contiguous() and x.dtype == torch.bfloat16
+    out = torch.empty((N * H * W, 9 * C), dtype=x.dtype, device=x.device)
+    check(kernels().swb_im2col3x3(x.data_ptr(), out.data_ptr(), N, H, W, C, stream_ptr()), "swb_im2col3x3")
+    return out

@@ -23,6 +23,19 @@ def test_media_kernels():
         if silu:
             ref = torch.nn.functional.silu(ref)
         assert torch.allclose(out.float(), ref.permute(0, 2, 3, 1), atol=4e-2, rtol=2e-2)
+    for C, G in ((128, 32), (64, 32), (32, 32)):      # groups narrower than one 16-byte vector
+        a2 = torch.randn(2, 9, 7, C, device="cuda").bfloat16()
+        g2 = (torch.rand(C, device="cuda") + 0.5).bfloat16()
+        b2 = (torch.randn(C, device="cuda") * 0.1).bfloat16()
+        out = ops.groupnorm_nhwc(a2, g2, b2, groups=G, eps=1e-6, silu=True)
+        ref = torch.nn.functional.silu(torch.nn.functional.group_norm(a2.float().permute(0, 3, 1, 2), G, g2.float(),
+                                                                      b2.float(), 1e-6))
+        assert torch.allclose(out.float(), ref.permute(0, 2, 3, 1), atol=4e-2, rtol=2e-2)
+    a3 = torch.randn(1, 5, 6, 16, device="cuda").bfloat16()
+    cols = ops.im2col3x3_nhwc(a3)
+    ref = torch.nn.functional.unfold(a3.float().permute(0, 3, 1, 2), 3, padding=1)      # [1, C*9, L], (c, kh, kw)
+    ref = ref.view(1, 16, 9, 30).permute(0, 3, 2, 1).reshape(30, 144)
+    assert torch.equal(cols.float(), ref)
     up = ops.upsample2x_nhwc(a)
     ref = torch.nn.functional.interpolate(a.float().permute(0, 3, 1, 2), scale_factor=2, mode="nearest")
     assert torch.equal(up.float(), ref.permute(0, 2, 3, 1))
@@ -74,3 +87,20 @@ def test_flux_dit_matches_oracle(batch):
     out = model.forward(img, img_ids, txt, txt_ids, t, y, gd)
     err = (out.float() - ref).abs().max().item()
     assert err < 0.06 * max(1.0, ref.abs().max().item()), err
+
+
+def test_vae_decoder_matches_oracle():
+    from inference_b200.models.vae import OracleVaeDecoder, VaeConfig, VaeDecoderGpu, random_vae_weights
+
+    cfg = VaeConfig(ch=64, ch_mult=(1, 2), num_res_blocks=1)
+    w = {k: v.bfloat16().float() for k, v in random_vae_weights(cfg, seed=0).items()}
+    oracle = OracleVaeDecoder(cfg, w, device="cuda")
+    gpu = VaeDecoderGpu(cfg, torch.device("cuda")).load_state_dict(w)
+    z = torch.randn(1, 16, 12, 10, device="cuda") * 0.5
+    ref = oracle.decode(z)                                  # [1, 3, 24, 20]
+    out = gpu.decode(z)[..., :3].permute(0, 3, 1, 2).float()
+    assert out.shape == ref.shape
+    err = (out - ref).abs().max().item()
+    assert err < 0.06 * max(1.0, ref.abs().max().item()), err
+    u8 = gpu.decode_rgb8(z)
+    assert u8.shape == (1, 24, 20, 3) and u8.dtype == torch.uint8
