@@ -129,6 +129,15 @@ def save_file(tensors: dict[str, torch.Tensor], path: str | Path, metadata: dict
             f.write(b)
 
 
+def load_file(path: str | Path, dtype: torch.dtype | None = None) -> dict[str, torch.Tensor]:
+    """Every tensor of one .safetensors file (copied out of the mapping)."""
+    f = SafetensorsFile(path)
+    try:
+        return {k: (f.get(k).to(dtype) if dtype is not None else f.get(k).clone()) for k in f.keys()}
+    finally:
+        f.close()
+
+
 def shard_files(directory: str | Path) -> list[Path]:
     d = Path(directory)
     files = sorted(p for p in d.iterdir() if p.suffix == ".safetensors") if d.is_dir() else [d]

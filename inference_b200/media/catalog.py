@@ -1,0 +1,13 @@
+"""The media provider catalog of one backend (parity: candle-gen-catalog's `provider_registry()`): an explicit list,
+no global state and no import-time discovery."""
+from __future__ import annotations
+
+from ..contracts.gen_core.registry import ProviderRegistry, ProviderRegistryBuilder
+
+
+def provider_registry(backend: str = "b200") -> ProviderRegistry:
+    from . import flux
+
+    b = ProviderRegistryBuilder()
+    b.register_generators(flux.registrations(backend))
+    return b.build()

@@ -1,0 +1,311 @@
+"""FLUX.1 text-to-image providers: `flux1_dev` / `flux1_schnell` on the sm_100a kernels and `cpu_flux1_*` on the
+fp32 oracle (parity: candle-gen-flux/src/lib.rs:130-374, pipeline.rs:101-126,622-723,878-970).
+
+generate(): validate -> residency.run(encode text -> for each image: seeded CPU noise -> patchify 2x2 -> flow
+schedule with resolution-dependent shift (dev) -> sampler loop calling the DiT once per step (guidance is an
+embedding input, no CFG batch) -> unpatchify -> VAE decode -> RGB8 on the host).
+
+Snapshot layout: `<transformer_file>` (BFL key names) + `ae.safetensors`; an optional `swb_config.json`
+({"dit": {...FluxConfig fields}, "vae": {...VaeConfig fields}, "text": "hash"}) overrides the fixed FLUX.1
+dimensions - used by synthetic snapshots so conformance suites run in seconds."""
+from __future__ import annotations
+
+import enum
+import json
+from dataclasses import dataclass
+from pathlib import Path
+from typing import Any, Callable
+
+import torch
+
+from ..contracts.errors import Canceled, InferenceError, LoadError, Unsupported
+from ..contracts.gen_core.generator import (Capabilities, GenerationOutput, GenerationRequest, Generator, Modality,
+                                            ModelDescriptor)
+from ..contracts.gen_core.media import Image
+from ..contracts.gen_core.registry import PerComponentBytes, Registration
+from ..contracts.gen_core.traits import reject_unknown_components
+from ..contracts.gen_core.runtime import LoadSpec, OffloadPolicy, ProgressDecoding, ProgressStep
+from ..contracts.gen_core.sampling import (SCHEDULERS, SOLVERS, FlowModelSampling, TorchLatentOps, build_flow_sigmas,
+                                           compute_mu, denoise, get_solver, image_seq_len, schedule_sigmas)
+from ..models.dit_flux import FluxConfig, OracleFluxDiT, make_ids, rope_table
+from ..models.vae import OracleVaeDecoder, VaeConfig
+from .residency import Residency
+from .seed import default_seed, for_each_image_seed, seeded_noise_nchw
+from .text_encoders import HashTextEncoders, TextConditioning
+
+SIZE_MULTIPLE = 16
+FLUX1_DEV_ID, FLUX1_SCHNELL_ID = "flux1_dev", "flux1_schnell"
+
+
+class Variant(enum.Enum):
+    SCHNELL = "schnell"
+    DEV = "dev"
+
+    @property
+    def model_id(self) -> str:
+        return FLUX1_DEV_ID if self is Variant.DEV else FLUX1_SCHNELL_ID
+
+    @property
+    def default_steps(self) -> int:
+        return 25 if self is Variant.DEV else 4
+
+    @property
+    def supports_guidance(self) -> bool:
+        return self is Variant.DEV
+
+    @property
+    def default_guidance(self) -> float:
+        return 3.5
+
+    @property
+    def t5_max_len(self) -> int:
+        return 512 if self is Variant.DEV else 256
+
+    @property
+    def transformer_file(self) -> str:
+        return "flux1-dev.safetensors" if self is Variant.DEV else "flux1-schnell.safetensors"
+
+
+def flux_descriptor(variant: Variant, backend: str, prefix: str = "") -> ModelDescriptor:
+    return ModelDescriptor(
+        id=prefix + variant.model_id, family="flux", backend=backend, modality=Modality.IMAGE,
+        capabilities=Capabilities(
+            supports_negative_prompt=False, supports_guidance=variant.supports_guidance, supports_true_cfg=False,
+            conditioning=[], supports_lora=False, supports_lokr=False, samplers=list(SOLVERS),
+            schedulers=list(SCHEDULERS), supported_guidance_methods=[], min_size=256, max_size=2048, max_count=8,
+            supports_sequential_offload=True),
+        required_components=[])
+
+
+def patchify(z: torch.Tensor) -> torch.Tensor:
+    """[1, 16, h, w] -> [1, (h/2)(w/2), 64], channel-major inside a patch (c, ph, pw)."""
+    b, c, h, w = z.shape
+    return z.view(b, c, h // 2, 2, w // 2, 2).permute(0, 2, 4, 1, 3, 5).reshape(b, (h // 2) * (w // 2), c * 4)
+
+
+def unpatchify(x: torch.Tensor, h: int, w: int) -> torch.Tensor:
+    b, _, d = x.shape
+    c = d // 4
+    return x.view(b, h // 2, w // 2, c, 2, 2).permute(0, 3, 1, 4, 2, 5).reshape(b, c, h, w)
+
+
+def flux_schedule(variant: Variant, steps: int, width: int, height: int) -> list[float]:
+    """steps+1 sigmas from 1 to 0; dev shifts time by mu(image sequence length) (pipeline.rs:101-126)."""
+    if variant is Variant.DEV:
+        return build_flow_sigmas(steps, compute_mu(image_seq_len(width, height), steps))
+    return [1.0 - i / steps for i in range(steps + 1)]
+
+
+@dataclass
+class _Heavy:
+    dit: Any
+    vae: Any
+    device: torch.device
+    dtype: torch.dtype
+
+
+class FluxPipeline:
+    """Paths and configuration only; components are built by the residency owner when first needed."""
+
+    def __init__(self, variant: Variant, root: Path, backend: str, device: torch.device):
+        self.variant, self.root, self.backend, self.device = variant, Path(root), backend, device
+        self.dit_cfg = FluxConfig(guidance_embed=variant.supports_guidance)
+        self.vae_cfg = VaeConfig()
+        self.text_kind = "t5_clip"
+        cfg_path = self.root / "swb_config.json"
+        if cfg_path.exists():
+            raw = json.loads(cfg_path.read_text())
+            if "dit" in raw:
+                d = dict(raw["dit"])
+                if "axes_dim" in d:
+                    d["axes_dim"] = tuple(d["axes_dim"])
+                self.dit_cfg = FluxConfig(**d)
+            if "vae" in raw:
+                v = dict(raw["vae"])
+                if "ch_mult" in v:
+                    v["ch_mult"] = tuple(v["ch_mult"])
+                self.vae_cfg = VaeConfig(**v)
+            self.text_kind = raw.get("text", self.text_kind)
+        self.dtype = torch.bfloat16 if backend == "b200" else torch.float32
+
+    # ---- loaders -------------------------------------------------------------------------------------
+    def load_text(self):
+        if self.text_kind == "hash":
+            return HashTextEncoders(self.dit_cfg.context_in_dim, self.dit_cfg.vec_in_dim, self.device, self.dtype)
+        from .t5_clip import load_t5_clip
+
+        return load_t5_clip(self.root, self.backend, self.device)
+
+    def load_heavy(self) -> _Heavy:
+        from ..io.safetensors_io import load_file
+
+        tf = self.root / self.variant.transformer_file
+        ae = self.root / "ae.safetensors"
+        for p in (tf, ae):
+            if not p.exists():
+                raise LoadError(f"{self.variant.model_id}: missing weight file {p}")
+        dit_w, vae_w = load_file(tf), load_file(ae)
+        if self.backend == "b200":
+            from ..models.dit_flux import FluxDiTGpu
+            from ..models.vae import VaeDecoderGpu
+
+            dit = FluxDiTGpu(self.dit_cfg, device=self.device).load_state_dict(dit_w)
+            vae = VaeDecoderGpu(self.vae_cfg, self.device).load_state_dict(vae_w)
+        else:
+            dit = OracleFluxDiT(self.dit_cfg, dit_w, device=self.device)
+            vae = OracleVaeDecoder(self.vae_cfg, vae_w, device=self.device)
+        return _Heavy(dit, vae, self.device, self.dtype)
+
+    # ---- phases --------------------------------------------------------------------------------------
+    def encode(self, text, prompt: str) -> TextConditioning:
+        return text.encode(prompt, self.variant.t5_max_len)
+
+    def render(self, heavy: _Heavy, cond: TextConditioning, req: GenerationRequest, on_progress) -> list[Image]:
+        v = self.variant
+        steps = req.steps or v.default_steps
+        guidance = (req.guidance if req.guidance is not None else v.default_guidance) if v.supports_guidance else None
+        base_seed = req.seed if req.seed is not None else default_seed()
+        lh, lw = req.height // 8, req.width // 8
+        dev, dt = heavy.device, heavy.dtype
+        txt = cond.txt.to(dev, dt)
+        pooled = cond.pooled.to(dev, dt)
+        txt_ids, img_ids = make_ids(lh // 2, lw // 2, txt.shape[1], dev)
+        rope = rope_table(torch.cat([txt_ids, img_ids], 0), self.dit_cfg.axes_dim, self.dit_cfg.theta)
+        ms = FlowModelSampling()
+        if req.scheduler is None:
+            sigmas = flux_schedule(v, steps, req.width, req.height)
+        else:
+            sigmas = schedule_sigmas(req.scheduler, FlowModelSampling(mu=req.scheduler_shift or 0.0), steps)
+        solver = get_solver(req.sampler or "euler")
+        ops = TorchLatentOps()
+        gvec = torch.full((1,), float(guidance), device=dev) if guidance is not None else None
+        c_lat = self.vae_cfg.z_channels
+
+        def one_image(seed: int) -> Image:
+            noise = seeded_noise_nchw(seed, c_lat, lh, lw)                    # CPU draw -> device
+            x = patchify(noise).to(dev, dt).contiguous()
+            state = {"step": 0}
+
+            def run_model(x_in, t):
+                if req.cancel.is_cancelled():
+                    raise Canceled(f"{v.model_id}: cancelled at step {state['step']}")
+                tt = torch.full((1,), float(t), device=dev)
+                if self.backend == "b200":
+                    out = heavy.dit.forward(x_in, img_ids, txt, txt_ids, tt, pooled, gvec, rope=rope)
+                else:
+                    out = heavy.dit.forward(x_in, img_ids, txt, txt_ids, tt, pooled, gvec)
+                state["step"] += 1
+                if state["step"] <= steps:          # multi-evaluation solvers still report `steps` events
+                    on_progress(ProgressStep(state["step"], steps))
+                return out.to(dt).contiguous()
+
+            x = solver.sample(ops, ms, lambda xx, s: denoise(ops, ms, xx, s, run_model), x, sigmas, seed)
+            while state["step"] < steps:            # solvers that skip the final evaluation at sigma 0
+                state["step"] += 1
+                on_progress(ProgressStep(state["step"], steps))
+            if req.cancel.is_cancelled():
+                raise Canceled(f"{v.model_id}: cancelled before decode")
+            on_progress(ProgressDecoding())
+            z = unpatchify(x.float(), lh, lw)
+            if self.backend == "b200":
+                u8 = heavy.vae.decode_rgb8(z)[0]                               # [H, W, 3] uint8 on device
+                host = u8.cpu()
+            else:
+                img = heavy.vae.decode(z)[0].permute(1, 2, 0)
+                host = torch.round((img.clamp(-1, 1) + 1) * 127.5).to(torch.uint8).cpu()
+            return Image(width=req.width, height=req.height, pixels=host.contiguous().numpy().tobytes())
+
+        return for_each_image_seed(base_seed, req.count, one_image)
+
+
+class FluxGenerator(Generator):
+    def __init__(self, variant: Variant, pipe: FluxPipeline, descriptor: ModelDescriptor, policy: OffloadPolicy):
+        self.variant, self.pipe, self._descriptor = variant, pipe, descriptor
+        sync = torch.cuda.synchronize if pipe.backend == "b200" else (lambda: None)
+        self.residency = Residency.from_policy(policy, pipe.load_text, pipe.load_heavy, sync)
+
+    def descriptor(self) -> ModelDescriptor:
+        return self._descriptor
+
+    def validate(self, req: GenerationRequest) -> None:
+        mid = self._descriptor.id
+        self._descriptor.capabilities.validate_request(mid, req)
+        if not req.prompt:
+            raise InferenceError(f"{mid}: prompt must not be empty")
+        if req.steps == 0:
+            raise InferenceError(f"{mid}: steps must be >= 1 (an explicit 0 renders undenoised noise)")
+        if req.width % SIZE_MULTIPLE or req.height % SIZE_MULTIPLE:
+            raise InferenceError(f"{mid}: width/height must be multiples of {SIZE_MULTIPLE} "
+                                 f"(got {req.width}x{req.height})")
+
+    def generate(self, req: GenerationRequest, on_progress: Callable = lambda p: None) -> GenerationOutput:
+        self.validate(req)
+        images = self.residency.run(req.cancel, on_progress, lambda text: self.pipe.encode(text, req.prompt),
+                                    lambda heavy, cond: self.pipe.render(heavy, cond, req, on_progress))
+        return GenerationOutput(images=images)
+
+
+def _load(variant: Variant, backend: str, prefix: str) -> Callable[[LoadSpec], FluxGenerator]:
+    def load(spec: LoadSpec) -> FluxGenerator:
+        mid = prefix + variant.model_id
+        if spec.weights is None or spec.weights.is_file:
+            raise Unsupported(f"{mid}: needs a snapshot directory (single-file checkpoints are not supported)")
+        if spec.quantize is not None:
+            raise Unsupported(f"{mid}: quantised loading ({spec.quantize.name}) is not supported")
+        reject_unknown_components(spec.components, [], mid)
+        if spec.adapters or spec.control or spec.extra_controls or spec.ip_adapter:
+            raise Unsupported(f"{mid}: adapters / control branches are not supported by this provider")
+        if backend == "b200":
+            if not torch.cuda.is_available():
+                raise LoadError(f"{mid}: no CUDA device")
+            device = torch.device("cuda", torch.cuda.current_device())
+        else:
+            device = torch.device("cpu")
+        pipe = FluxPipeline(variant, Path(spec.weights.path), backend, device)    # lazy: paths only
+        return FluxGenerator(variant, pipe, flux_descriptor(variant, backend, prefix), spec.offload_policy)
+    return load
+
+
+def _footprint(variant: Variant) -> Callable[[LoadSpec], PerComponentBytes | None]:
+    def footprint(spec: LoadSpec) -> PerComponentBytes | None:
+        if spec.weights is None or spec.weights.is_file:
+            return None
+        root = Path(spec.weights.path)
+        out = {}
+        for name, rel in (("transformer", variant.transformer_file), ("vae", "ae.safetensors")):
+            f = root / rel
+            if f.exists():
+                out[name] = f.stat().st_size
+        te = PerComponentBytes.from_root_subdirs(root, {"text_encoder": "text_encoder", "text_encoder_2":
+                                                        "text_encoder_2"})
+        out.update(te.components)
+        return PerComponentBytes(out)
+    return footprint
+
+
+def registrations(backend: str = "b200") -> list[Registration]:
+    """`flux1_schnell` + `flux1_dev` for the sm_100a backend, `cpu_flux1_*` for the fp32 oracle backend."""
+    prefix = "" if backend == "b200" else "cpu_"
+    return [Registration(descriptor=(lambda v=v: flux_descriptor(v, backend, prefix)), load=_load(v, backend, prefix),
+                         footprint=_footprint(v)) for v in (Variant.SCHNELL, Variant.DEV)]
+
+
+def write_synthetic_snapshot(root, variant: Variant = Variant.DEV, seed: int = 0) -> Path:
+    """A tiny random FLUX-shaped snapshot (2+2 blocks, hidden 256) with the hash text encoder."""
+    from ..io.safetensors_io import save_file
+    from ..models.dit_flux import random_flux_weights
+    from ..models.vae import random_vae_weights
+
+    root = Path(root)
+    root.mkdir(parents=True, exist_ok=True)
+    dit = FluxConfig(in_channels=64, vec_in_dim=32, context_in_dim=64, hidden_size=256, num_heads=2, depth=2,
+                     depth_single=2, guidance_embed=variant.supports_guidance)
+    vae = VaeConfig(ch=32, ch_mult=(1, 2, 2, 2), num_res_blocks=1)
+    save_file({k: v.bfloat16() for k, v in random_flux_weights(dit, seed).items()}, root / variant.transformer_file)
+    save_file({k: v.bfloat16() for k, v in random_vae_weights(vae, seed + 1).items()}, root / "ae.safetensors")
+    (root / "swb_config.json").write_text(json.dumps({
+        "dit": {**{k: getattr(dit, k) for k in ("in_channels", "vec_in_dim", "context_in_dim", "hidden_size",
+                                                "num_heads", "depth", "depth_single", "guidance_embed")},
+                "axes_dim": list(dit.axes_dim)},
+        "vae": {"ch": vae.ch, "ch_mult": list(vae.ch_mult), "num_res_blocks": vae.num_res_blocks}, "text": "hash"}))
+    return root
