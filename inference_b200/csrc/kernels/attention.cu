@@ -15,6 +15,7 @@
 #include "gemm_tcgen05.cuh"
 
 namespace swb {
+int g_dense_impl = 0;
 using namespace attn;
 namespace {
 
@@ -537,6 +538,9 @@ int swb_attn_paged(const void* q, long long q_stride_tok, int q_stride_head, voi
   return last_err();
 }
 
+// 0: pick the tcgen05 kernel whenever it supports the problem; 1: always the mma.sync kernel (comparison runs).
+void swb_attn_dense_set_impl(int impl) { swb::g_dense_impl = impl; }
+
 // Dense attention over q/k/v laid out [batch * seq, heads, 128] (arbitrary element strides), uniform lengths.
 int swb_attn_dense(const void* q, long long q_stride_tok, int q_stride_head, const void* k, const void* v,
                    long long kv_stride_tok, int kv_stride_head, void* out, long long out_stride_tok, int batch,
@@ -544,6 +548,12 @@ int swb_attn_dense(const void* q, long long q_stride_tok, int q_stride_head, con
   using namespace swb;
   if (batch <= 0 || q_len <= 0) return 0;
   if (D != HD || Hq % Hkv != 0) return -3;
+  if (kv_len <= 0) return -3;
+  if (g_dense_impl == 0 && attn_dense_tcgen05_supported(q, k, v, q_stride_tok, q_stride_head, kv_stride_tok,
+                                                        kv_stride_head, out_stride_tok, D, causal))
+    return attn_dense_tcgen05_launch(q, q_stride_tok, q_stride_head, k, v, kv_stride_tok, kv_stride_head, out,
+                                     out_stride_tok, batch, q_len, kv_len, Hq, Hkv, scale,
+                                     reinterpret_cast<cudaStream_t>(stream));
   int rc = configure_once();
   if (rc) return rc;
   AttnParams p{};

@@ -71,4 +71,12 @@ __device__ __forceinline__ float score_transform(float s, float scale, float sof
 }
 
 }  // namespace attn
+
+// attention_tcgen05.cu
+int attn_dense_tcgen05_supported(const void* q, const void* k, const void* v, long long q_stride_tok, int q_stride_head,
+                                 long long kv_stride_tok, int kv_stride_head, long long out_stride_tok, int D,
+                                 int causal);
+int attn_dense_tcgen05_launch(const void* q, long long q_stride_tok, int q_stride_head, const void* k, const void* v,
+                              long long kv_stride_tok, int kv_stride_head, void* out, long long out_stride_tok,
+                              int batch, int q_len, int kv_len, int Hq, int Hkv, float scale, cudaStream_t stream);
 }  // namespace swb

@@ -64,3 +64,8 @@ def dense_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale:
                                   1 if causal else 0, stream_ptr())
     check(rc, "swb_attn_dense")
     return out
+
+
+def set_dense_impl(legacy: bool) -> None:
+    """Comparison runs only: True forces the mma.sync kernel for dense attention, False restores the tcgen05 kernel."""
+    kernels().swb_attn_dense_set_impl(1 if legacy else 0)

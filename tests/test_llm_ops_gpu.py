@@ -223,3 +223,34 @@ def test_dense_attention_noncausal():
     for b in range(B):
         ref = _ref_attn(q[b], k[b], v[b], scale, False)
         assert (out[b].float() - ref).abs().max().item() < 3e-2
+
+
+@pytest.mark.parametrize("B,Sq,Skv,Hq,Hkv,qmul", [(1, 4608, 4608, 4, 4, 1.0), (2, 300, 1000, 8, 2, 1.0),
+                                                   (1, 1024, 2048, 2, 1, 6.0), (1, 129, 257, 2, 2, 1.0),
+                                                   (1, 256, 128, 1, 1, 12.0)])
+def test_dense_attention_tcgen05(B, Sq, Skv, Hq, Hkv, qmul):
+    """tcgen05 kernel against fp32 math and against the mma.sync kernel; qmul > 1 spreads the logits so that the
+    running maximum keeps growing and the lazy accumulator rescale is exercised."""
+    from inference_b200 import ops
+    from inference_b200.ops.attention import set_dense_impl
+
+    g = torch.Generator(device="cuda").manual_seed(Sq * 31 + Skv)
+    q = (torch.randn(B, Sq, Hq, 128, device="cuda", generator=g) * qmul).bfloat16()
+    k = torch.randn(B, Skv, Hkv, 128, device="cuda", generator=g).bfloat16()
+    v = torch.randn(B, Skv, Hkv, 128, device="cuda", generator=g).bfloat16()
+    if qmul > 1:   # keys later in the sequence score higher on average
+        k = (k.float() + q.float().mean(1, keepdim=True)[:, :, :Hkv] * torch.linspace(
+            0, 0.05, Skv, device="cuda")[None, :, None, None]).bfloat16()
+    scale = 1 / math.sqrt(128)
+    out = ops.dense_attention(q, k, v, scale=scale)
+    ops.check_status()
+    set_dense_impl(True)
+    try:
+        legacy = ops.dense_attention(q, k, v, scale=scale)
+    finally:
+        set_dense_impl(False)
+    for b in range(B):
+        ref = _ref_attn(q[b], k[b], v[b], scale, False)
+        err = (out[b].float() - ref).abs().max().item()
+        assert err < 3e-2, (b, err)
+        assert (out[b].float() - legacy[b].float()).abs().max().item() < 3e-2
