@@ -17,15 +17,19 @@ def main():
     ap.add_argument("--depth", type=int, default=19)
     ap.add_argument("--depth-single", type=int, default=38)
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--eager", action="store_true", help="launch every kernel from Python instead of replaying a graph")
     ap.add_argument("--vae", action="store_true", help="also time the VAE decode of the final latents")
     args = ap.parse_args()
     from inference_b200.contracts.gen_core.sampling import build_flow_sigmas, compute_mu, image_seq_len
     from inference_b200 import ops
     from inference_b200.models.dit_flux import FluxConfig, FluxDiTGpu, make_ids, rope_table
 
-    dev = torch.device("cuda")
+    from inference_b200.parallel import init_distributed
+
+    comm = init_distributed()          # world 1 unless launched by torch.distributed.run (then sequence parallel)
+    dev = comm.device
     cfg = FluxConfig(depth=args.depth, depth_single=args.depth_single)
-    model = FluxDiTGpu(cfg, device=dev).init_random(0)
+    model = FluxDiTGpu(cfg, comm=comm, device=dev).init_random(0)
     ht = args.size // 16
     Si, St = ht * ht, 512
     g = torch.Generator(device=dev).manual_seed(0)
@@ -41,25 +45,27 @@ def main():
         lat = x
         for i in range(n_steps):
             t = torch.full((1,), sigmas[i], device=dev)
-            v = model.forward(lat, img_ids, txt, txt_ids, t, y, gd, rope=rope)
+            fwd = model.forward if args.eager else model.forward_graphed
+            v = fwd(lat, img_ids, txt, txt_ids, t, y, gd, rope=rope)
             lat = ops.axpy(1.0, lat, sigmas[i + 1] - sigmas[i], v.contiguous())
         return lat
 
     run(args.warmup)
+    comm.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     run(args.steps)
     e1.record()
     torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
+    ms = comm.max_over_ranks(e0.elapsed_time(e1))
     S = Si + St
     H, M = cfg.hidden_size, cfg.mlp_hidden
     flops_double = 2 * S * H * (3 * H + H + 2 * M) + 4 * S * S * H
     flops_single = 2 * S * H * (3 * H + M) + 2 * S * (H + M) * H + 4 * S * S * H
     tflop = (cfg.depth * flops_double + cfg.depth_single * flops_single) / 1e12
     vae_ms = None
-    if args.vae:
+    if args.vae and comm.rank == 0:
         from inference_b200.models.vae import VaeConfig, VaeDecoderGpu
 
         vae = VaeDecoderGpu(VaeConfig(), dev).init_random(1)
@@ -73,7 +79,12 @@ def main():
         vae_ms = round(e0.elapsed_time(e1), 2)
         assert img.shape == (1, args.size, args.size, 3)
     ops.check_status()
-    print(json.dumps({"metric": "flux_dit_ms_per_step", "ms_per_step": round(ms / args.steps, 3),
+    comm.barrier()
+    if comm.rank != 0:
+        return
+    import os as _os
+    print(json.dumps({"n_gpus": comm.world, "sp_impl": _os.environ.get("SWB_SP", "fused") if comm.world > 1 else None,
+                      "metric": "flux_dit_ms_per_step", "cuda_graph": not args.eager, "ms_per_step": round(ms / args.steps, 3),
                       "s_per_image_dit_only": round(ms / 1e3, 3), "steps": args.steps, "size": args.size,
                       "tflop_per_step": round(tflop, 2), "achieved_tflops": round(tflop / (ms / args.steps) * 1e3, 1),
                       "launches_per_step": model.launches, "weights_gb": round(model.weight_bytes() / 1e9, 2), "vae_decode_ms": vae_ms,

@@ -69,7 +69,7 @@ def main():
                 shapes.append((T, N, K))
     else:
         for s in args.shapes.split(";"):
-            shapes.append(tuple(int(x) for x in s.split(",")))
+            shapes.append(tuple(int(x) for x in s.replace("x", ",").split(",")))
     rows = []
     for T, N, K in shapes:
         wbytes = N * K * 2

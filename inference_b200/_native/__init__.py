@@ -89,6 +89,12 @@ def _declare_kernels(lib: ctypes.CDLL) -> None:
                           c_void_p])
     sig("swb_upsample2x", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
     sig("swb_attn_dense_set_impl", [c_int], None)
+    sig("swb_attn_dense_scatter", [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_ll, c_int, c_void_p, c_int,
+                                   c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                   c_void_p])
+    sig("swb_gemm_bf16_scatter", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
+                                  c_int, c_int, c_int, c_int, c_int, c_void_p])
+    sig("swb_peer_barrier", [c_void_p, c_void_p, c_int, c_int, c_void_p])
     sig("swb_im2col3x3", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
     sig("swb_softmax_rows", [c_void_p, c_void_p, c_int, c_int, c_ll, c_ll, c_float, c_void_p])
     sig("swb_rgb8", [c_void_p, c_void_p, c_ll, c_int, c_void_p])

@@ -41,6 +41,37 @@ int swb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* D, int l
   return swb::gemm_bf16_launch(a, reinterpret_cast<cudaStream_t>(stream));
 }
 
+// GEMM whose epilogue dispatches the output head-sharded to peers (see GemmScatter): D is not written locally.
+// peers: `world` device pointers to every rank's receive buffer [global rows, N / (heads * 128), heads_per_rank, 128].
+int swb_gemm_bf16_scatter(const void* A, int lda, const void* W, int ldw, int T, int N, int K, const void* bias,
+                          int act, void* const* peers, int world, int heads, int row_split, int row_off0,
+                          int row_off1, void* stream) {
+  if (world < 1 || world > 8 || heads % world != 0 || N % (heads * 128) != 0) return -3;
+  swb::GemmScatter sc{};
+  for (int r = 0; r < world; ++r) sc.peer[r] = reinterpret_cast<__nv_bfloat16*>(peers[r]);
+  sc.hd_total = heads * 128;
+  sc.heads_per_rank = heads / world;
+  sc.ld = (N / sc.hd_total) * sc.heads_per_rank * 128;
+  sc.row_split = row_split;
+  sc.row_off0 = row_off0;
+  sc.row_off1 = row_off1;
+  swb::GemmArgs a{};
+  a.A = A;
+  a.lda = lda;
+  a.W = W;
+  a.ldw = ldw;
+  a.D = nullptr;
+  a.ldd = 16;
+  a.T = T;
+  a.N = N;
+  a.K = K;
+  a.bias = bias;
+  a.act = act;
+  a.force_mode = 0;
+  a.scatter = &sc;
+  return swb::gemm_bf16_launch(a, reinterpret_cast<cudaStream_t>(stream));
+}
+
 size_t swb_gemm_workspace_min(void) { return swb::SWB_GEMM_COUNTER_BYTES + (size_t)(8u << 20); }
 
 int swb_sm_count(void) { return swb::device_sm_count(); }

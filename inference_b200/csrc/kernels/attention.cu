@@ -538,6 +538,22 @@ int swb_attn_paged(const void* q, long long q_stride_tok, int q_stride_head, voi
   return last_err();
 }
 
+// Dense non-causal attention (tcgen05 kernel only, batch 1) whose epilogue returns every output row to the rank
+// that owns the token: see OutScatter in attention_tcgen05.cu. peers: `world` pointers to [local rows, out_stride_tok].
+int swb_attn_dense_scatter(const void* q, long long q_stride_tok, int q_stride_head, const void* k, const void* v,
+                           long long kv_stride_tok, int kv_stride_head, void* const* peers, int world,
+                           long long out_stride_tok, int col_offset, int row_split, int n0, int n1, int q_len,
+                           int kv_len, int Hq, int Hkv, float scale, void* stream) {
+  using namespace swb;
+  if (q_len <= 0 || kv_len <= 0 || Hq % Hkv != 0) return -3;
+  if (!attn_dense_tcgen05_supported(q, k, v, q_stride_tok, q_stride_head, kv_stride_tok, kv_stride_head, out_stride_tok,
+                                    128, 0))
+    return -3;
+  return attn_dense_tcgen05_launch(q, q_stride_tok, q_stride_head, k, v, kv_stride_tok, kv_stride_head, nullptr,
+                                   out_stride_tok, 1, q_len, kv_len, Hq, Hkv, scale,
+                                   reinterpret_cast<cudaStream_t>(stream), peers, world, row_split, n0, n1, col_offset);
+}
+
 // 0: pick the tcgen05 kernel whenever it supports the problem; 1: always the mma.sync kernel (comparison runs).
 void swb_attn_dense_set_impl(int impl) { swb::g_dense_impl = impl; }
 

@@ -45,7 +45,16 @@ constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_S0 = 0, COL_O0 = 128, COL_S1 = 256, COL_O1 = 384;
 constexpr float RESCALE_THRESHOLD = 8.f;           // in log2 units
 
+// Sequence-parallel return path: query row g (global token index, batch 1) belongs to rank
+// (g < split ? g / n0 : (g - split) / n1) at local row (g < split ? g % n0 : n0 + (g - split) % n1); the output row is
+// stored straight into that rank's buffer at column col_offset + head * 128.
+struct OutScatter {
+  bf16* peer[8];
+  int enabled, split, n0, n1, col_offset;
+};
+
 struct FaParams {
+  OutScatter scatter;
   bf16* out;
   long long out_stride_tok;   // elements; token index = b * q_len + s
   int q_len, kv_len, Hq, Hkv;
@@ -338,6 +347,13 @@ attn_dense_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       tc_fence_after_sync();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       bf16* dst = p.out + ((long long)batch * p.q_len + row) * p.out_stride_tok + (long long)head * HD;
+      if (p.scatter.enabled && row < p.q_len) {
+        const OutScatter& sc = p.scatter;
+        const int g2 = row - sc.split;
+        const int rk = row < sc.split ? row / sc.n0 : g2 / sc.n1;
+        const int local = row < sc.split ? row % sc.n0 : sc.n0 + g2 % sc.n1;
+        dst = sc.peer[rk] + (long long)local * p.out_stride_tok + sc.col_offset + head * HD;
+      }
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t o[32];
@@ -436,7 +452,8 @@ int attn_dense_tcgen05_supported(const void* q, const void* k, const void* v, lo
 
 int attn_dense_tcgen05_launch(const void* q, long long q_stride_tok, int q_stride_head, const void* k, const void* v,
                               long long kv_stride_tok, int kv_stride_head, void* out, long long out_stride_tok,
-                              int batch, int q_len, int kv_len, int Hq, int Hkv, float scale, cudaStream_t stream) {
+                              int batch, int q_len, int kv_len, int Hq, int Hkv, float scale, cudaStream_t stream,
+                              void* const* peers, int world, int split, int n0, int n1, int col_offset) {
   CUtensorMap tq, tk, tv;
   int rc = make_tmap_heads(&tq, q, Hq, q_len, batch, q_stride_head, q_stride_tok, q_stride_tok * q_len);
   if (rc) return rc;
@@ -461,6 +478,15 @@ int attn_dense_tcgen05_launch(const void* q, long long q_stride_tok, int q_strid
   p.Hq = Hq;
   p.Hkv = Hkv;
   p.scale_log2 = scale * 1.4426950408889634f;
+  if (peers) {
+    if (world < 1 || world > 8 || batch != 1 || n1 <= 0 || (split > 0 && n0 <= 0) || (col_offset % 8) != 0) return -3;
+    for (int r = 0; r < world; ++r) p.scatter.peer[r] = reinterpret_cast<bf16*>(peers[r]);
+    p.scatter.enabled = 1;
+    p.scatter.split = split;
+    p.scatter.n0 = n0 > 0 ? n0 : 1;
+    p.scatter.n1 = n1;
+    p.scatter.col_offset = col_offset;
+  }
   dim3 grid((q_len + 2 * BM - 1) / (2 * BM), Hq, batch);
   return launch_kernel(attn_dense_tcgen05_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, tq, tk, tv, p);
 }

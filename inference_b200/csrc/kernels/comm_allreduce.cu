@@ -177,6 +177,17 @@ __global__ void __launch_bounds__(THREADS) allreduce_rmsnorm_kernel(const ArPara
   }
 }
 
+// Barrier across ranks between two kernels of a stream (everything this rank's earlier kernels wrote to peers is
+// visible to a peer once that peer's barrier returns). One CTA; flag row `blockIdx.x` = 0 of its own flag pad.
+__global__ void __launch_bounds__(32) peer_barrier_kernel(const ArParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ int s_ok;
+  const uint32_t epoch = p.epochs[0] + 1u;
+  peer_barrier(p, epoch, &s_ok);
+  if (threadIdx.x == 0) p.epochs[0] = epoch;
+}
+
 // A stand-alone wait used by the timeout test: spins on one local flag word that nothing sets.
 __global__ void flag_wait_kernel(const uint32_t* flag, uint32_t expected, int* result) {
   uint64_t t0 = 0;
@@ -240,6 +251,18 @@ int swb_allreduce_rmsnorm(const void* const* peer_data, void* const* peer_flags,
   if (nvec <= 1024) return launch_kernel(allreduce_rmsnorm_kernel<512, 2>, dim3(grid), dim3(512), 0, s, p);
   if (nvec <= 2048) return launch_kernel(allreduce_rmsnorm_kernel<512, 4>, dim3(grid), dim3(512), 0, s, p);
   return -3;
+}
+
+// peer_flags: `world` pointers to flag pads of at least MAX_RANKS words; epochs: one local word.
+int swb_peer_barrier(void* const* peer_flags, void* epochs, int rank, int world, void* stream) {
+  using namespace swb;
+  if (world < 1 || world > MAX_RANKS) return -3;
+  ArParams p{};
+  for (int r = 0; r < world; ++r) p.peer_flags[r] = reinterpret_cast<uint32_t*>(peer_flags[r]);
+  p.epochs = reinterpret_cast<uint32_t*>(epochs);
+  p.rank = rank;
+  p.world = world;
+  return launch_kernel(peer_barrier_kernel, dim3(1), dim3(32), 0, reinterpret_cast<cudaStream_t>(stream), p);
 }
 
 // Bounded wait on a flag nothing sets (health / timeout self-test): result[0] = 1 if the flag reached

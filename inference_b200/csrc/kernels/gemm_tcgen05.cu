@@ -145,6 +145,16 @@ __device__ __forceinline__ void epilogue_store16(const GemmParams& p, float* v, 
 #pragma unroll
         for (int j = 0; j < 8; ++j) ob[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
         uint4* op = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + off);
+        if (p.scatter.enabled) {   // a 16-column chunk never straddles a head (128 columns)
+          const GemmScatter& sc = p.scatter;
+          const int which = col0 / sc.hd_total;
+          const int rem = col0 - which * sc.hd_total;
+          const int h = rem >> 7;
+          const int r = h / sc.heads_per_rank;
+          const int grow = row + (row < sc.row_split ? sc.row_off0 : sc.row_off1);
+          op = reinterpret_cast<uint4*>(sc.peer[r] + (size_t)grow * sc.ld +
+                                        (which * sc.heads_per_rank + (h - r * sc.heads_per_rank)) * 128 + (rem & 127));
+        }
         op[0] = o[0];
         op[1] = o[1];
       }
@@ -538,10 +548,15 @@ int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
   const int sms = device_sm_count();
 
   int swapped = a.force_mode;
+  if (a.scatter) {
+    if (a.out_fp32 || a.residual || (a.N % 16) != 0 || (a.scatter->ld % 8) != 0 || a.scatter->hd_total % 128 != 0)
+      return -3;
+    swapped = 0;
+  }
   if (swapped < 0) swapped = (a.T <= 256) ? 1 : 0;
   // decode-sized problems with fewer weight tiles than SMs: cluster split-K with a DSMEM reduction
-  if (a.force_mode == 2 || (a.force_mode < 0 && gemm_decode_cluster_supported(a.T) && (a.N + BM - 1) / BM < sms &&
-                            (a.K + BK - 1) / BK >= 8)) {
+  if (!a.scatter && (a.force_mode == 2 || (a.force_mode < 0 && gemm_decode_cluster_supported(a.T) && (a.N + BM - 1) / BM < sms &&
+                            (a.K + BK - 1) / BK >= 8))) {
     if (!gemm_decode_cluster_supported(a.T)) return -4;
     return gemm_decode_cluster_launch(a, a.force_mode == 2 ? a.force_ctas : 0, stream);
   }
@@ -558,6 +573,10 @@ int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
   p.ld_res = a.ld_res;
   p.act = a.act;
   p.status = nullptr;
+  if (a.scatter) {
+    p.scatter = *a.scatter;
+    p.scatter.enabled = 1;
+  }
 
   int block_n;
   CUtensorMap ta, tb;
@@ -579,6 +598,17 @@ int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
     p.vec_ok = 0;
   } else {
     block_n = a.N >= 256 ? 256 : a.N >= 128 ? 128 : a.N >= 64 ? 64 : a.N >= 32 ? 32 : 16;
+    if (block_n == 256) {
+      // wave quantisation: with few row tiles a 128-wide tile can fill the SMs better than a 256-wide one does,
+      // at roughly 0.85 of its per-SM rate
+      const long tm = (a.T + BM - 1) / BM;
+      auto fill = [&](int bn) {
+        const long tiles = tm * ((a.N + bn - 1) / bn);
+        const long waves = (tiles + sms - 1) / sms;
+        return (double)tiles / (double)(waves * sms);
+      };
+      if (fill(128) * 0.85 > fill(256) * 1.02) block_n = 128;
+    }
     if (a.force_block_n > 0) block_n = a.force_block_n;
     p.M = a.T;
     p.N = a.N;
@@ -594,6 +624,7 @@ int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
     p.vec_ok = ((a.ldd * esz) % 16 == 0) && ((reinterpret_cast<uintptr_t>(a.D) & 15) == 0) &&
                (!a.bias || (reinterpret_cast<uintptr_t>(a.bias) & 15) == 0) &&
                (!a.residual || (((reinterpret_cast<uintptr_t>(a.residual) & 15) == 0) && (a.ld_res % 8 == 0)));
+    if (a.scatter && !p.vec_ok) return -3;
   }
 
   const int tiles = p.tiles_m * p.tiles_n;

@@ -14,6 +14,19 @@ enum GemmAct : int { SWB_ACT_NONE = 0, SWB_ACT_SILU = 1, SWB_ACT_GELU_TANH = 2 }
 // launches: the caller zeroes them once, the kernel restores zero); fp32 split-K partials follow.
 constexpr size_t SWB_GEMM_COUNTER_BYTES = 64 * 1024;
 
+// Head-sharded dispatch of the output to peers (sequence-parallel attention): output columns are laid out
+// [which (q/k/v...)][head][128]; head h belongs to rank h / heads_per_rank, whose buffer is
+// [global rows, which, heads_per_rank, 128] with row stride `ld`. Local row r lands at global row
+// (r < row_split ? row_off0 : row_off1) + r. Only the tokens-as-M kernel with 16-byte stores supports it.
+struct GemmScatter {
+  __nv_bfloat16* peer[8];
+  int enabled;
+  int hd_total;        // heads * 128: width of one `which` block
+  int heads_per_rank;
+  int ld;
+  int row_split, row_off0, row_off1;
+};
+
 // Kernel-level problem: D[M, N] = A[M, K] * B[N, K]^T, possibly stored transposed.
 struct GemmParams {
   int M, N, K;
@@ -34,6 +47,7 @@ struct GemmParams {
   int* counters;
   int* status;
   unsigned long long* trace;  // optional [grid][8] globaltimer stamps of kernel phases (profiling aid)
+  GemmScatter scatter;
 };
 
 // User-level problem: D[T, N] = act(A[T, K] * W[N, K]^T + bias[N]) + residual[T, N].
@@ -55,6 +69,7 @@ struct GemmArgs {
   int force_mode;     // -1 auto, 0 tokens-as-M, 1 swapped (weights-as-M), 2 cluster split-K (T <= 64; force_ctas = cluster size)
   int force_block_n;  // 0 auto
   int force_ctas;     // 0 auto; > 0 stream-K over that many CTAs; < 0 whole tiles only
+  const GemmScatter* scatter = nullptr;
 };
 
 int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream);

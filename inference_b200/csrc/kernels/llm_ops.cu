@@ -269,6 +269,84 @@ __global__ void __launch_bounds__(256) rope_kv_write_kernel(
   }
 }
 
+// Head dim 128 with full rotary width: every lane owns four elements so that both members of each rotation pair are
+// lane-local (interleaved: elements 4l..4l+3; half-split: 2l, 2l+1, 64+2l, 65+2l) and all accesses are 4- or 8-byte
+// vectors. V heads are only touched when they have to be copied into a cache.
+template <bool INTERLEAVED>
+__global__ void __launch_bounds__(256) rope_kv_write_d128_kernel(
+    bf16* qkv, int ld_qkv, const int* __restrict__ positions, const long long* __restrict__ slot_mapping,
+    const float* __restrict__ cos_tab, const float* __restrict__ sin_tab, const bf16* __restrict__ q_norm_w,
+    const bf16* __restrict__ k_norm_w, float norm_eps, float norm_w_offset, bf16* kcache, bf16* vcache, int block_size,
+    int T, int Hq, int Hkv, int heads_active) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int D = 128;
+  const int lane = threadIdx.x & 31;
+  const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (gw >= (long long)T * heads_active) return;
+  const int t = (int)(gw / heads_active);
+  const int h = (int)(gw % heads_active);
+  bf16* src = qkv + (size_t)t * ld_qkv + (size_t)h * D;
+  const bool is_q = h < Hq;
+  const bool is_k = !is_q && h < Hq + Hkv;
+  const int e0 = INTERLEAVED ? 4 * lane : 2 * lane;         // first element of the low pair block
+  const int e1 = INTERLEAVED ? 4 * lane + 2 : 64 + 2 * lane;  // first element of the second block
+  float v[4];
+  {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + e0));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + e1));
+    v[0] = a.x, v[1] = a.y, v[2] = b.x, v[3] = b.y;
+  }
+  bf16* dst = src;
+  if (!is_q && (is_k ? kcache : vcache) != nullptr) {
+    const long long slot = slot_mapping ? slot_mapping[t] : -1;
+    if (slot < 0) {
+      dst = nullptr;
+    } else {
+      const long long blk = slot / block_size;
+      const int off = (int)(slot % block_size);
+      const int kvh = is_k ? (h - Hq) : (h - Hq - Hkv);
+      dst = (is_k ? kcache : vcache) + (((size_t)blk * Hkv + kvh) * block_size + off) * (size_t)D;
+    }
+  }
+  if (is_q || is_k) {
+    const bf16* nw = is_q ? q_norm_w : k_norm_w;
+    if (nw) {
+      float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+      ss = warp_sum(ss);
+      const float inv = rsqrtf(ss / (float)D + norm_eps);
+      const float2 wa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(nw + e0));
+      const float2 wb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(nw + e1));
+      // round through bf16 like an unfused norm would before the rotation
+      v[0] = __bfloat162float(__float2bfloat16(v[0] * inv * (wa.x + norm_w_offset)));
+      v[1] = __bfloat162float(__float2bfloat16(v[1] * inv * (wa.y + norm_w_offset)));
+      v[2] = __bfloat162float(__float2bfloat16(v[2] * inv * (wb.x + norm_w_offset)));
+      v[3] = __bfloat162float(__float2bfloat16(v[3] * inv * (wb.y + norm_w_offset)));
+    }
+    const int pos = positions[t];
+    const float2 c = *reinterpret_cast<const float2*>(cos_tab + (size_t)pos * 64 + 2 * lane);
+    const float2 sn = *reinterpret_cast<const float2*>(sin_tab + (size_t)pos * 64 + 2 * lane);
+    float o[4];
+    if (INTERLEAVED) {   // pairs (v0, v1) with angle 2l and (v2, v3) with angle 2l + 1
+      o[0] = v[0] * c.x - v[1] * sn.x;
+      o[1] = v[1] * c.x + v[0] * sn.x;
+      o[2] = v[2] * c.y - v[3] * sn.y;
+      o[3] = v[3] * c.y + v[2] * sn.y;
+    } else {             // pairs (v0, v2) with angle 2l and (v1, v3) with angle 2l + 1
+      o[0] = v[0] * c.x - v[2] * sn.x;
+      o[2] = v[2] * c.x + v[0] * sn.x;
+      o[1] = v[1] * c.y - v[3] * sn.y;
+      o[3] = v[3] * c.y + v[1] * sn.y;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = o[i];
+  }
+  if (dst) {
+    *reinterpret_cast<__nv_bfloat162*>(dst + e0) = __floats2bfloat162_rn(v[0], v[1]);
+    *reinterpret_cast<__nv_bfloat162*>(dst + e1) = __floats2bfloat162_rn(v[2], v[3]);
+  }
+}
+
 // out[t, f] = act(gu[t, f]) * gu[t, F + f]; act 1 = SiLU (SwiGLU), 2 = tanh-GELU (GeGLU).
 __global__ void __launch_bounds__(256) gated_act_mul_kernel(const bf16* __restrict__ gu, int ld_gu, bf16* out,
                                                            int ldo, int T, int F, int act) {
@@ -397,8 +475,19 @@ int swb_rope_kv_write(void* qkv, int ld_qkv, const int* positions, const long lo
   using namespace swb;
   if (T <= 0) return 0;
   if (D > 256 || rot_dim > D || (rot_dim & 1)) return -3;
-  const long long warps = (long long)T * (Hq + 2 * Hkv);
   const int wpb = 8;
+  if (D == 128 && rot_dim == 128 && (ld_qkv % 2) == 0 && (reinterpret_cast<uintptr_t>(qkv) & 3) == 0) {
+    const int heads_active = Hq + Hkv + (vcache ? Hkv : 0);   // V stays where it is unless it goes to a cache
+    const long long nblk = ((long long)T * heads_active + wpb - 1) / wpb;
+    auto kern = interleaved ? rope_kv_write_d128_kernel<true> : rope_kv_write_d128_kernel<false>;
+    launch_rc = launch_kernel(kern, dim3((unsigned)nblk), dim3(wpb * 32), 0, reinterpret_cast<cudaStream_t>(stream),
+                              reinterpret_cast<bf16*>(qkv), ld_qkv, positions, slot_mapping, cos_tab, sin_tab,
+                              reinterpret_cast<const bf16*>(q_norm_w), reinterpret_cast<const bf16*>(k_norm_w),
+                              norm_eps, norm_w_offset, reinterpret_cast<bf16*>(kcache), reinterpret_cast<bf16*>(vcache),
+                              block_size, T, Hq, Hkv, heads_active);
+    return last_err();
+  }
+  const long long warps = (long long)T * (Hq + 2 * Hkv);
   const long long blocks = (warps + wpb - 1) / wpb;
   launch_rc = launch_kernel(rope_kv_write_kernel, dim3((unsigned)blocks), dim3(wpb * 32), 0, reinterpret_cast<cudaStream_t>(stream), reinterpret_cast<bf16*>(qkv), ld_qkv, positions, slot_mapping, cos_tab, sin_tab, rot_dim, interleaved,
       reinterpret_cast<const bf16*>(q_norm_w), reinterpret_cast<const bf16*>(k_norm_w), norm_eps, norm_w_offset,

@@ -251,7 +251,12 @@ class FluxDiTGpu:
 
     @torch.no_grad()
     def forward(self, img, img_ids, txt, txt_ids, timesteps, y, guidance=None, rope=None):
-        """img [B, S_img, C_in], txt [B, S_txt, C_ctx] bf16 -> velocity [B, S_img, C_in] bf16."""
+        """img [B, S_img, C_in], txt [B, S_txt, C_ctx] bf16 -> velocity [B, S_img, C_in] bf16. With a parallel
+        communicator every rank passes the full inputs and receives the full velocity; the work in between is
+        sequence-parallel (each rank owns 1/P of the text and of the image tokens, and 1/P of the heads inside
+        attention)."""
+        if self.comm.world > 1:
+            return self._forward_sp(img, img_ids, txt, txt_ids, timesteps, y, guidance, rope)
         cfg = self.cfg
         H, D, NH, M = cfg.hidden_size, cfg.head_dim, cfg.num_heads, cfg.mlp_hidden
         B, Si, _ = img.shape
@@ -336,3 +341,164 @@ class FluxDiTGpu:
         xm = ops.layernorm_mod(x_img, scale=m[:, H:], shift=m[:, :H], rows_per_batch=Si)
         self.launches += 1
         return self._lin(xm.view(B * Si, H), "final_layer.linear").view(B, Si, -1)
+
+    # ---------------------------------------------------------------------------------------------------------
+    # CUDA-graph replay (the forward has static shapes: one capture per (image tokens, text tokens) pair)
+    # ---------------------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def forward_graphed(self, img, img_ids, txt, txt_ids, timesteps, y, guidance=None, rope=None):
+        """Same result as forward(); the first call for a shape runs eagerly once (allocations, tensor maps,
+        symmetric-memory rendezvous) and captures, later calls copy the inputs into static buffers and replay."""
+        key = (tuple(img.shape), tuple(txt.shape), guidance is not None)
+        st = getattr(self, "_graphs", None)
+        if st is None:
+            st = self._graphs = {}
+        g = st.get(key)
+        if g is None:
+            if rope is None:
+                rope = rope_table(torch.cat([txt_ids, img_ids], 0).to(img.device), self.cfg.axes_dim, self.cfg.theta)
+            static = {"img": img.clone(), "txt": txt.clone(), "t": timesteps.clone(), "y": y.clone(),
+                      "g": guidance.clone() if guidance is not None else None, "rope": rope,
+                      "img_ids": img_ids, "txt_ids": txt_ids}
+            run = lambda: self.forward(static["img"], static["img_ids"], static["txt"], static["txt_ids"],  # noqa: E731
+                                       static["t"], static["y"], static["g"], rope=static["rope"])
+            side = torch.cuda.Stream(device=img.device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                run()                       # warm-up on the capture stream
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            if self.comm.world > 1:
+                self.comm.barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                static["out"] = run()
+            static["launches"] = self.launches
+            g = st[key] = (graph, static)
+        graph, static = g
+        static["img"].copy_(img)
+        static["txt"].copy_(txt)
+        static["t"].copy_(timesteps)
+        static["y"].copy_(y)
+        if guidance is not None:
+            static["g"].copy_(guidance)
+        graph.replay()
+        self.launches = static["launches"]
+        return static["out"]
+
+    # ---------------------------------------------------------------------------------------------------------
+    # sequence parallel
+    # ---------------------------------------------------------------------------------------------------------
+    def _sp_context(self, S: int, St: int):
+        from ..parallel.sp import UlyssesContext
+
+        key = (S, St)
+        if getattr(self, "_sp_key", None) != key:
+            self._sp_ctx = UlyssesContext(self.comm, S, St, self.cfg.num_heads, self.cfg.hidden_size,
+                                          self.cfg.mlp_hidden)
+            self._sp_key = key
+        return self._sp_ctx
+
+    def _forward_sp(self, img, img_ids, txt, txt_ids, timesteps, y, guidance, rope):
+        import os
+
+        cfg, comm = self.cfg, self.comm
+        H, D, NH, M = cfg.hidden_size, cfg.head_dim, cfg.num_heads, cfg.mlp_hidden
+        P, r = comm.world, comm.rank
+        B, Si, _ = img.shape
+        assert B == 1, "sequence-parallel forward handles one image per call"
+        St = txt.shape[1]
+        S = St + Si
+        dev = img.device
+        self.launches = 0
+        fused = os.environ.get("SWB_SP", "fused") != "nccl"
+        if rope is None:
+            rope = rope_table(torch.cat([txt_ids, img_ids], 0).to(dev), cfg.axes_dim, cfg.theta)
+        cos, sin = rope
+        St_l, Si_l = St // P, Si // P
+        S_l, Hl = St_l + Si_l, NH // P
+        scale = D ** -0.5
+        sv = self.conditioning_vector(timesteps, y, guidance)
+        x_txt = self._lin(txt[0, r * St_l:(r + 1) * St_l], "txt_in")          # [St_l, H]
+        x_img = self._lin(img[0, r * Si_l:(r + 1) * Si_l], "img_in")          # [Si_l, H]
+        positions = torch.arange(S, dtype=torch.int32, device=dev)
+        # global positions of this rank's local rows ([txt_l | img_l])
+        local_pos = torch.cat([positions[r * St_l:(r + 1) * St_l], positions[St + r * Si_l:St + (r + 1) * Si_l]])
+        if fused:
+            ctx = self._sp_context(S, St)
+            buf2 = ctx.attn                                                     # [S_l, H + M], peers write [:, :H]
+        else:
+            buf2 = torch.empty((S_l, H + M), dtype=torch.bfloat16, device=dev)
+            qkv_l = torch.empty((S_l, 3 * H), dtype=torch.bfloat16, device=dev)
+
+        def exchange_and_attend(norms):
+            """norms: [(row_lo, row_hi, q_norm, k_norm)] in GLOBAL rows (fused) or LOCAL rows (baseline)."""
+            if fused:
+                ctx.barrier()                                   # every peer's QKV tiles have landed
+                for lo, hi, qn, kn in norms:
+                    ops.rope_kv_write(ctx.qkv[lo:hi], positions[lo:hi], None, cos, sin, None, None, Hl, Hl, D,
+                                      rot_dim=D, interleaved=True, q_norm=qn, k_norm=kn, norm_eps=1e-6)
+                ctx.attn_scatter(scale)
+                ctx.barrier()                                   # every peer's attention rows have landed
+                self.launches += 3 + len(norms)
+                return
+            for lo, hi, qn, kn in norms:
+                ops.rope_kv_write(qkv_l[lo:hi], local_pos[lo:hi], None, cos, sin, None, None, NH, NH, D, rot_dim=D,
+                                  interleaved=True, q_norm=qn, k_norm=kn, norm_eps=1e-6)
+            g = comm.all_to_all(qkv_l.view(S_l, 3, NH, D), split_dim=2, cat_dim=0)       # [P*S_l, 3, Hl, D]
+            o = ops.dense_attention(g[None, :, 0], g[None, :, 1], g[None, :, 2], scale=scale)[0]  # [P*S_l, Hl*D]
+            back = comm.all_to_all(o.contiguous(), split_dim=0, cat_dim=1)               # [S_l, H]
+            buf2[:, :H].copy_(back)
+            self.launches += 2 + len(norms)
+
+        for i in range(cfg.depth):
+            mods, norms = {}, []
+            for s in ("img", "txt"):
+                m = self._lin(sv, f"double_blocks.{i}.{s}_mod.lin")
+                mods[s] = [m[:, j * H:(j + 1) * H] for j in range(6)]
+            for s, x, lo_l, n_l, lo_g, n_g in (("txt", x_txt, 0, St_l, 0, St), ("img", x_img, St_l, Si_l, St, Si)):
+                xm = ops.layernorm_mod(x[None], scale=mods[s][1], shift=mods[s][0], rows_per_batch=n_l)[0]
+                name = f"double_blocks.{i}.{s}_attn.qkv"
+                if fused:
+                    ctx.gemm_scatter(xm, self.w[name + ".weight"], self.w[name + ".bias"], s)
+                    self.launches += 1
+                else:
+                    self._lin(xm, name, out=qkv_l[lo_l:lo_l + n_l])
+                nw = (self.w[f"double_blocks.{i}.{s}_attn.norm.query_norm.scale"],
+                      self.w[f"double_blocks.{i}.{s}_attn.norm.key_norm.scale"])
+                norms.append((lo_g, lo_g + n_g, *nw) if fused else (lo_l, lo_l + n_l, *nw))
+            exchange_and_attend(norms)
+            new = {}
+            for s, x, lo_l, n_l in (("txt", x_txt, 0, St_l), ("img", x_img, St_l, Si_l)):
+                proj = self._lin(buf2[lo_l:lo_l + n_l, :H], f"double_blocks.{i}.{s}_attn.proj")
+                x = ops.gated_residual(x[None], proj[None], mods[s][2], rows_per_batch=n_l)
+                hm = ops.layernorm_mod(x, scale=mods[s][4], shift=mods[s][3], rows_per_batch=n_l)
+                h1 = self._lin(hm[0], f"double_blocks.{i}.{s}_mlp.0", act="gelu_tanh")
+                h2 = self._lin(h1, f"double_blocks.{i}.{s}_mlp.2")
+                new[s] = ops.gated_residual(x, h2[None], mods[s][5], rows_per_batch=n_l)[0]
+                self.launches += 3
+            x_img, x_txt = new["img"], new["txt"]
+
+        x = torch.cat([x_txt, x_img], 0).contiguous()                           # [S_l, H] local joint
+        for i in range(cfg.depth_single):
+            p = f"single_blocks.{i}"
+            m = self._lin(sv, p + ".modulation.lin")
+            sh, sc, g = m[:, :H], m[:, H:2 * H], m[:, 2 * H:]
+            xm = ops.layernorm_mod(x[None], scale=sc, shift=sh, rows_per_batch=S_l)[0]
+            nw = (self.w[p + ".norm.query_norm.scale"], self.w[p + ".norm.key_norm.scale"])
+            if fused:
+                ctx.gemm_scatter(xm, self.w[p + ".linear1_qkv.weight"], self.w[p + ".linear1_qkv.bias"], "joint")
+                self.launches += 1
+            else:
+                self._lin(xm, p + ".linear1_qkv", out=qkv_l)
+            self._lin(xm, p + ".linear1_mlp", act="gelu_tanh", out=buf2[:, H:])
+            exchange_and_attend([(0, S, *nw)] if fused else [(0, S_l, *nw)])
+            out = self._lin(buf2, p + ".linear2")
+            x = ops.gated_residual(x[None], out[None], g, rows_per_batch=S_l)[0]
+            self.launches += 2
+        x_img = x[St_l:].contiguous()
+        m = self._lin(sv, "final_layer.adaLN_modulation.1")
+        xm = ops.layernorm_mod(x_img[None], scale=m[:, H:], shift=m[:, :H], rows_per_batch=Si_l)[0]
+        v_local = self._lin(xm, "final_layer.linear")                           # [Si_l, C]
+        self.launches += 2
+        return comm.all_gather(v_local, dim=0)[None]

@@ -87,6 +87,12 @@ def test_flux_dit_matches_oracle(batch):
     out = model.forward(img, img_ids, txt, txt_ids, t, y, gd)
     err = (out.float() - ref).abs().max().item()
     assert err < 0.06 * max(1.0, ref.abs().max().item()), err
+    # graph replay: first call captures, second replays with new inputs
+    for scale_in in (1.0, 0.5):
+        img2 = (img.float() * scale_in).bfloat16()
+        eager = model.forward(img2, img_ids, txt, txt_ids, t, y, gd).clone()
+        replay = model.forward_graphed(img2, img_ids, txt, txt_ids, t, y, gd)
+        assert torch.equal(eager, replay)
 
 
 def test_vae_decoder_matches_oracle():

@@ -11,12 +11,25 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run(nproc, mode, port):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+def _run(nproc, mode, port, worker="_tp_worker.py", marker="TP_WORKER_OK", extra_env=None):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **(extra_env or {}))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
-           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "_tp_worker.py"), mode]
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, worker), mode]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
-    assert r.returncode == 0 and "TP_WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0 and marker in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.parametrize("mode", ["fused", "nccl"])
+def test_sequence_parallel_dit_2gpu(mode):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    _run(2, mode, 29551 if mode == "fused" else 29552, "_sp_worker.py", "SP_WORKER_OK", {"SWB_SP": mode})
+
+
+def test_sequence_parallel_dit_4gpu():
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs 4 GPUs")
+    _run(4, "fused", 29553, "_sp_worker.py", "SP_WORKER_OK", {"SWB_SP": "fused"})
 
 
 @pytest.mark.parametrize("mode", ["fused", "nccl"])
