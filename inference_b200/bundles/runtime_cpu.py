@@ -1,0 +1,35 @@
+"""The CPU runtime bundle (the role of crates/bundles/runtime-cpu): fp32 PyTorch oracle models: one call composes the
+media provider registry, the text-LLM registry and the snapshot preparers of the CPU backend into a validated
+catalog. Nothing is discovered at import time; the lists below are the shipped surface."""
+from __future__ import annotations
+
+from ..contracts.core_llm.prepare import SnapshotPreparerRegistry, SnapshotPreparerRegistryBuilder
+from ..contracts.core_llm.registry import TextLlmRegistry, TextLlmRegistryBuilder
+from ..contracts.gen_core.registry import ProviderRegistry
+from .catalog import RuntimeCatalog
+
+PLATFORM = "cpu"
+BACKEND = "cpu"
+
+
+def provider_registry() -> ProviderRegistry:
+    from ..media.catalog import provider_registry as media_registry
+
+    return media_registry(BACKEND)
+
+
+def text_registry() -> TextLlmRegistry:
+    from ..engine.provider import CPU_LLAMA
+
+    return TextLlmRegistryBuilder().register(CPU_LLAMA).build()
+
+
+def snapshot_preparer_registry() -> SnapshotPreparerRegistry:
+    from ..io.prepare import registration
+
+    return SnapshotPreparerRegistryBuilder().register(registration(BACKEND)).build()
+
+
+def catalog() -> RuntimeCatalog:
+    return RuntimeCatalog.try_new(PLATFORM, BACKEND, provider_registry(), text_registry(),
+                                  snapshot_preparer_registry())
