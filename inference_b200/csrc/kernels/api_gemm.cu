@@ -49,6 +49,7 @@ int swb_gemm_bf16_scatter(const void* A, int lda, const void* W, int ldw, int T,
   if (world < 1 || world > 8 || heads % world != 0 || N % (heads * 128) != 0) return -3;
   swb::GemmScatter sc{};
   for (int r = 0; r < world; ++r) sc.peer[r] = reinterpret_cast<__nv_bfloat16*>(peers[r]);
+  sc.enabled = 1;
   sc.hd_total = heads * 128;
   sc.heads_per_rank = heads / world;
   sc.ld = (N / sc.hd_total) * sc.heads_per_rank * 128;
@@ -67,6 +68,34 @@ int swb_gemm_bf16_scatter(const void* A, int lda, const void* W, int ldw, int T,
   a.K = K;
   a.bias = bias;
   a.act = act;
+  a.force_mode = 0;
+  a.scatter = &sc;
+  return swb::gemm_bf16_launch(a, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// Row-parallel GEMM whose epilogue performs the scatter half of a reduce-scatter: this rank's partial sums for token
+// row t go to rank t / rows_per_rank, slot `rank` of its [world, rows_per_rank, N] buffer (peers[r]).
+int swb_gemm_bf16_scatter_rows(const void* A, int lda, const void* W, int ldw, int T, int N, int K, void* const* peers,
+                               int world, int rank, int rows_per_rank, void* stream) {
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || rows_per_rank <= 0 ||
+      (long long)rows_per_rank * world < T)
+    return -3;
+  swb::GemmScatter sc{};
+  for (int r = 0; r < world; ++r) sc.peer[r] = reinterpret_cast<__nv_bfloat16*>(peers[r]);
+  sc.enabled = 2;
+  sc.ld = N;
+  sc.rows_per_rank = rows_per_rank;
+  sc.src_rank = rank;
+  swb::GemmArgs a{};
+  a.A = A;
+  a.lda = lda;
+  a.W = W;
+  a.ldw = ldw;
+  a.D = nullptr;
+  a.ldd = 16;
+  a.T = T;
+  a.N = N;
+  a.K = K;
   a.force_mode = 0;
   a.scatter = &sc;
   return swb::gemm_bf16_launch(a, reinterpret_cast<cudaStream_t>(stream));

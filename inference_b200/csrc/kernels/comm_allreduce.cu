@@ -177,6 +177,90 @@ __global__ void __launch_bounds__(THREADS) allreduce_rmsnorm_kernel(const ArPara
   }
 }
 
+// Second half of the fused reduce-scatter, joined with the all-gather that feeds the next column-parallel GEMM
+// (sequence-parallel tensor parallelism for prefill). This rank owns `rows` token rows. Peers' row-parallel GEMM
+// epilogues have stored their bf16 partial sums into the local slot buffer [world, rows_per_rank, H]. Per row:
+// barrier (first), fp32 sum over the slots in rank order (+ the local residual shard, which is updated in place),
+// RMSNorm, and the normed row is stored into EVERY rank's gathered activation buffer at its global row.
+// n_src == 0 skips the slots (first layer: norm of the residual only).
+struct RsAgParams {
+  ArParams ar;                 // peer_flags / epochs / rank / world / H / residual / weight / eps ... (data unused)
+  const bf16* slots;           // local [world, rows_per_rank, H]
+  bf16* gather[MAX_RANKS];     // every rank's [T, ld_gather] buffer
+  int n_src, rows, rows_per_rank, row_offset, ld_gather;
+};
+
+template <int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS) reduce_norm_gather_kernel(const RsAgParams q) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const ArParams& p = q.ar;
+  __shared__ float red[32];
+  __shared__ int s_ok;
+  const uint32_t epoch = p.epochs[blockIdx.x] + 1u;
+  const bool ok = peer_barrier(p, epoch, &s_ok);
+  if (threadIdx.x == 0) p.epochs[blockIdx.x] = epoch;
+  if (!ok) return;
+  const int nvec = p.H / 8;
+  for (int row = blockIdx.x; row < q.rows; row += gridDim.x) {
+    float vals[VPT][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = threadIdx.x + i * THREADS;
+      if (v < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) vals[i][j] = 0.f;
+        for (int r = 0; r < q.n_src; ++r) {
+          float f[8];
+          unpack8(__ldcg(reinterpret_cast<const uint4*>(q.slots + ((size_t)r * q.rows_per_rank + row) * p.H + v * 8)), f);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) vals[i][j] += f[j];
+        }
+        if (p.residual) {
+          uint4* rp = reinterpret_cast<uint4*>(p.residual + (size_t)row * p.ldr + v * 8);
+          if (q.n_src > 0) {
+            float rf[8];
+            unpack8(*rp, rf);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) vals[i][j] += rf[j];
+            const uint4 s = pack8(vals[i]);
+            *rp = s;
+            unpack8(s, vals[i]);
+          } else {
+            unpack8(*rp, vals[i]);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+      }
+    }
+    ss = warp_sum(ss);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    float t = (lane < THREADS / 32) ? red[lane] : 0.f;
+    t = warp_sum(t);
+    __syncthreads();
+    const float inv = rsqrtf(t / (float)p.H + p.eps);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = threadIdx.x + i * THREADS;
+      if (v < nvec) {
+        float o[8], wf[8];
+        unpack8(__ldg(reinterpret_cast<const uint4*>(p.weight + v * 8)), wf);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * inv * (wf[j] + p.w_offset);
+        const uint4 packed = pack8(o);
+        const size_t off = (size_t)(q.row_offset + row) * q.ld_gather + v * 8;
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r)
+          if (r < p.world) *reinterpret_cast<uint4*>(q.gather[r] + off) = packed;
+      }
+    }
+  }
+}
+
 // Barrier across ranks between two kernels of a stream (everything this rank's earlier kernels wrote to peers is
 // visible to a peer once that peer's barrier returns). One CTA; flag row `blockIdx.x` = 0 of its own flag pad.
 __global__ void __launch_bounds__(32) peer_barrier_kernel(const ArParams p) {
@@ -250,6 +334,46 @@ int swb_allreduce_rmsnorm(const void* const* peer_data, void* const* peer_flags,
   if (nvec <= 512) return launch_kernel(allreduce_rmsnorm_kernel<512, 1>, dim3(grid), dim3(512), 0, s, p);
   if (nvec <= 1024) return launch_kernel(allreduce_rmsnorm_kernel<512, 2>, dim3(grid), dim3(512), 0, s, p);
   if (nvec <= 2048) return launch_kernel(allreduce_rmsnorm_kernel<512, 4>, dim3(grid), dim3(512), 0, s, p);
+  return -3;
+}
+
+// See reduce_norm_gather_kernel. slots: local [world, rows_per_rank, H]; gather: `world` pointers to [T, ld_gather];
+// residual: local [rows, ldr] (updated in place when n_src > 0); rows: rows this rank owns (may be 0: the rank still
+// takes part in the barrier). peer_flags as for swb_allreduce_rmsnorm (pads of MAX_CTAS * MAX_RANKS words).
+int swb_reduce_norm_gather(const void* slots, int n_src, void* residual, int ldr, const void* weight, float eps,
+                           float w_offset, void* const* gather, int ld_gather, int row_offset, int rows,
+                           int rows_per_rank, int H, void* const* peer_flags, void* epochs, int rank, int world,
+                           void* stream) {
+  using namespace swb;
+  if (world < 1 || world > MAX_RANKS || H % 8 != 0 || ld_gather % 8 != 0 || !weight || !residual) return -3;
+  RsAgParams q{};
+  for (int r = 0; r < world; ++r) {
+    q.ar.peer_flags[r] = reinterpret_cast<uint32_t*>(peer_flags[r]);
+    q.gather[r] = reinterpret_cast<bf16*>(gather[r]);
+  }
+  q.ar.epochs = reinterpret_cast<uint32_t*>(epochs);
+  q.ar.rank = rank;
+  q.ar.world = world;
+  q.ar.H = H;
+  q.ar.residual = reinterpret_cast<bf16*>(residual);
+  q.ar.ldr = ldr;
+  q.ar.weight = reinterpret_cast<const bf16*>(weight);
+  q.ar.eps = eps;
+  q.ar.w_offset = w_offset;
+  q.slots = reinterpret_cast<const bf16*>(slots);
+  q.n_src = n_src;
+  q.rows = rows;
+  q.rows_per_rank = rows_per_rank;
+  q.row_offset = row_offset;
+  q.ld_gather = ld_gather;
+  // every rank launches the same grid so that CTA b meets CTA b of its peers at the barrier
+  const int grid = rows_per_rank < MAX_CTAS ? (rows_per_rank > 0 ? rows_per_rank : 1) : MAX_CTAS;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int nvec = H / 8;
+  if (nvec <= 256) return launch_kernel(reduce_norm_gather_kernel<256, 1>, dim3(grid), dim3(256), 0, s, q);
+  if (nvec <= 512) return launch_kernel(reduce_norm_gather_kernel<512, 1>, dim3(grid), dim3(512), 0, s, q);
+  if (nvec <= 1024) return launch_kernel(reduce_norm_gather_kernel<512, 2>, dim3(grid), dim3(512), 0, s, q);
+  if (nvec <= 2048) return launch_kernel(reduce_norm_gather_kernel<512, 4>, dim3(grid), dim3(512), 0, s, q);
   return -3;
 }
 

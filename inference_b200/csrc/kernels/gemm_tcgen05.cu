@@ -145,7 +145,7 @@ __device__ __forceinline__ void epilogue_store16(const GemmParams& p, float* v, 
 #pragma unroll
         for (int j = 0; j < 8; ++j) ob[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
         uint4* op = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + off);
-        if (p.scatter.enabled) {   // a 16-column chunk never straddles a head (128 columns)
+        if (p.scatter.enabled == 1) {   // a 16-column chunk never straddles a head (128 columns)
           const GemmScatter& sc = p.scatter;
           const int which = col0 / sc.hd_total;
           const int rem = col0 - which * sc.hd_total;
@@ -154,6 +154,12 @@ __device__ __forceinline__ void epilogue_store16(const GemmParams& p, float* v, 
           const int grow = row + (row < sc.row_split ? sc.row_off0 : sc.row_off1);
           op = reinterpret_cast<uint4*>(sc.peer[r] + (size_t)grow * sc.ld +
                                         (which * sc.heads_per_rank + (h - r * sc.heads_per_rank)) * 128 + (rem & 127));
+        } else if (p.scatter.enabled == 2) {
+          const GemmScatter& sc = p.scatter;
+          const int r = row / sc.rows_per_rank;
+          op = reinterpret_cast<uint4*>(sc.peer[r] +
+                                        ((size_t)sc.src_rank * sc.rows_per_rank + (row - r * sc.rows_per_rank)) * sc.ld +
+                                        col0);
         }
         op[0] = o[0];
         op[1] = o[1];
@@ -549,8 +555,9 @@ int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
 
   int swapped = a.force_mode;
   if (a.scatter) {
-    if (a.out_fp32 || a.residual || (a.N % 16) != 0 || (a.scatter->ld % 8) != 0 || a.scatter->hd_total % 128 != 0)
-      return -3;
+    if (a.out_fp32 || a.residual || (a.N % 16) != 0 || (a.scatter->ld % 8) != 0) return -3;
+    if (a.scatter->enabled == 1 && a.scatter->hd_total % 128 != 0) return -3;
+    if (a.scatter->enabled == 2 && a.scatter->rows_per_rank <= 0) return -3;
     swapped = 0;
   }
   if (swapped < 0) swapped = (a.T <= 256) ? 1 : 0;
@@ -575,7 +582,6 @@ int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
   p.status = nullptr;
   if (a.scatter) {
     p.scatter = *a.scatter;
-    p.scatter.enabled = 1;
   }
 
   int block_n;

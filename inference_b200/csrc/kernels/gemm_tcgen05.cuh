@@ -14,10 +14,12 @@ enum GemmAct : int { SWB_ACT_NONE = 0, SWB_ACT_SILU = 1, SWB_ACT_GELU_TANH = 2 }
 // launches: the caller zeroes them once, the kernel restores zero); fp32 split-K partials follow.
 constexpr size_t SWB_GEMM_COUNTER_BYTES = 64 * 1024;
 
-// Head-sharded dispatch of the output to peers (sequence-parallel attention): output columns are laid out
-// [which (q/k/v...)][head][128]; head h belongs to rank h / heads_per_rank, whose buffer is
-// [global rows, which, heads_per_rank, 128] with row stride `ld`. Local row r lands at global row
-// (r < row_split ? row_off0 : row_off1) + r. Only the tokens-as-M kernel with 16-byte stores supports it.
+// Dispatch of the output to peers from the epilogue (tokens-as-M kernel, 16-byte stores only).
+// enabled == 1, head-sharded (sequence-parallel attention): output columns are laid out [which (q/k/v...)][head][128];
+//   head h belongs to rank h / heads_per_rank, whose buffer is [global rows, which, heads_per_rank, 128] with row
+//   stride `ld`. Local row r lands at global row (r < row_split ? row_off0 : row_off1) + r.
+// enabled == 2, row-sharded (reduce-scatter of a row-parallel GEMM): row t belongs to rank t / rows_per_rank, whose
+//   buffer is [source rank, rows_per_rank, ld]; this rank's partial sums go to slot `src_rank`.
 struct GemmScatter {
   __nv_bfloat16* peer[8];
   int enabled;
@@ -25,6 +27,7 @@ struct GemmScatter {
   int heads_per_rank;
   int ld;
   int row_split, row_off0, row_off1;
+  int rows_per_rank, src_rank;
 };
 
 // Kernel-level problem: D[M, N] = A[M, K] * B[N, K]^T, possibly stored transposed.

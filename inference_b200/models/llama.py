@@ -205,6 +205,8 @@ class LlamaGpu:
         D = cfg.head_dim
         eps, woff = cfg.rms_norm_eps, cfg.norm_weight_offset
         T = inp.input_ids.numel()
+        if self._use_tp_prefill(T):
+            return self._forward_hidden_tp_prefill(inp, kv_pool)
         res = ops.embedding(inp.input_ids, self.embed, scale=cfg.embed_scale)
         branch = None
         block_size = kv_pool.shape[4]
@@ -260,6 +262,66 @@ class LlamaGpu:
         if inp.logits_rows is not None:
             return final.index_select(0, inp.logits_rows)
         return final
+
+    # ---- prefill with fused reduce-scatter / all-gather -----------------------------------------------------
+    def _use_tp_prefill(self, T: int) -> bool:
+        import os
+
+        f = self.comm.fused
+        if f is None or not self.comm.is_parallel or T <= f.max_tokens or os.environ.get("SWB_TP_PREFILL") == "nccl":
+            return False
+        if any(L.post_attn_ln is not None or L.post_mlp_ln is not None for L in self.layers):
+            return False
+        return T <= self.tp_prefill_max_tokens
+
+    tp_prefill_max_tokens = 8192
+
+    def _tp_prefill_context(self):
+        if getattr(self, "_tp_ctx", None) is None:
+            from ..parallel.tp_prefill import TpPrefillContext
+
+            self._tp_ctx = TpPrefillContext(self.comm, self.cfg.hidden_size, self.tp_prefill_max_tokens)
+        return self._tp_ctx
+
+    def _forward_hidden_tp_prefill(self, inp: StepInputs, kv_pool: torch.Tensor) -> torch.Tensor:
+        """Same math as forward_hidden; the residual stream is sharded by token rows, each row-parallel GEMM scatters
+        its partial sums to the row owners from its epilogue, and the owners' reduce + norm kernel gathers the normed
+        rows on every rank for the next column-parallel GEMM."""
+        cfg = self.cfg
+        D = cfg.head_dim
+        eps, woff = cfg.rms_norm_eps, cfg.norm_weight_offset
+        T = inp.input_ids.numel()
+        ctx = self._tp_prefill_context()
+        lo, n_rows = ctx.my_rows(T)
+        block_size = kv_pool.shape[4]
+        q_cols = self.hq * D
+        ids_l = inp.input_ids[lo:lo + n_rows]
+        res = (ops.embedding(ids_l, self.embed, scale=cfg.embed_scale) if n_rows > 0 else
+               torch.zeros((1, cfg.hidden_size), dtype=torch.bfloat16, device=self.device))
+        h = ctx.reduce_norm_gather(T, res, self.layers[0].ln1, eps, woff, reduce=False)
+        n = 3
+        for li, L in enumerate(self.layers):
+            qkv = ops.gemm_bf16(h, L.qkv, bias=L.qkv_bias)
+            ops.rope_kv_write(qkv, inp.positions, inp.slot_mapping, self.cos, self.sin, kv_pool[li, 0], kv_pool[li, 1],
+                              self.hq, self.hkv, D, rot_dim=self.rot_dim, interleaved=self.rope_interleaved,
+                              q_norm=L.q_norm, k_norm=L.k_norm, norm_eps=eps, norm_w_offset=woff,
+                              block_size=block_size)
+            q = qkv[:, :q_cols].view(T, self.hq, D)
+            attn = ops.paged_attention(q, kv_pool[li, 0], kv_pool[li, 1], inp.block_table, inp.kv_lens, cu_q=inp.cu_q,
+                                       max_q_len=inp.max_q_len, scale=cfg.attn_scale, causal=True, decode=inp.decode,
+                                       num_splits=inp.attn_splits, softcap=cfg.attn_logit_softcap or 0.0)
+            ctx.gemm_scatter_rows(attn, L.o)
+            h = ctx.reduce_norm_gather(T, res, L.ln2, eps, woff)
+            gu = ops.gemm_bf16(h, L.gate_up)
+            act = ops.gated_act_mul(gu, cfg.mlp_activation)
+            ctx.gemm_scatter_rows(act, L.down)
+            nxt = self.layers[li + 1].ln1 if li + 1 < len(self.layers) else self.norm
+            h = ctx.reduce_norm_gather(T, res, nxt, eps, woff)
+            n += 11
+        self.launches = n
+        if inp.logits_rows is not None:
+            return h.index_select(0, inp.logits_rows)
+        return h.clone()
 
     def logits_local(self, hidden: torch.Tensor) -> torch.Tensor:
         """fp32 logits of this rank's vocabulary shard: [R, vocab / P]."""

@@ -83,6 +83,25 @@ def main():
     got = runner.decode(seqs, toks).tolist()
     allg = comm.all_gather(torch.tensor([got], device=dev), dim=0)
     assert all(torch.equal(allg[0], allg[k]) for k in range(P)), "ranks disagree on sampled tokens"
+    for s_ in seqs:
+        s_.release()
+    # 3. prompts longer than the decode-sized exchange buffers: fused reduce-scatter / all-gather prefill path
+    #    (odd total length so the row shards are uneven) against the oracle
+    pool2 = PagedKvPool(cfg.num_layers, 128, model.hkv, cfg.head_dim, 16, device=dev)
+    runner2 = ModelRunner(model, pool2, max_batch=4, max_seq_len=1024)
+    long_prompts = [[(7 * i + 3) % cfg.vocab_size for i in range(301)], [(5 * i + 11) % cfg.vocab_size for i in range(170)]]
+    seqs2 = [PagedSequence(pool2) for _ in long_prompts]
+    if mode == "fused":
+        assert model._use_tp_prefill(sum(len(p) for p in long_prompts))
+    for rep in range(2):
+        lg2 = runner2.prefill(seqs2, long_prompts, want_logits=True)
+        for i, p in enumerate(long_prompts):
+            ref = oracle.decode_logits(torch.tensor([p], device=dev), oracle.make_cache(), 0)[0]
+            err = (lg2[i] - ref).abs().max().item()
+            assert err < 0.1 * max(1.0, ref.abs().max().item()), f"long prefill seq {i} rep {rep} err {err}"
+        for s_ in seqs2:
+            s_.release()
+        seqs2 = [PagedSequence(pool2) for _ in long_prompts]
     ops.check_status()
     comm.barrier()
     if r == 0:
