@@ -5,6 +5,7 @@ with cudaProfilerStart/Stop so that `ncu --profile-from-start off` sees only tho
   --what dit      one FLUX-shaped DiT denoise step (1024x1024) at reduced depth (--depth / --depth-single)
   --what gemm     one tcgen05 GEMM, T x N x K from --shape (operands larger than L2 by default)
   --what cluster  one decode GEMM through the cluster split-K kernel (T=64, N=4096, K=14336)
+  --what quant    one Q4_K dequant-GEMM (T from --shape "Tx..", N=28672, K=4096: the gate/up projection)
   --what attn     one split-KV decode attention launch (batch 64, 8 KV heads, context 2048)
   --what attn_dense one dense non-causal attention launch (S=4608, 24 heads)
 """
@@ -50,6 +51,18 @@ def main():
         def fn():
             flush.zero_()
             ops.gemm_bf16(a, w)
+        window(fn, reps=args.reps)
+    elif args.what == "quant":
+        from inference_b200.ops import quant
+
+        T, (N, K) = int(args.shape.split("x")[0]) if "x" in args.shape and args.shape != "8192x4096x4096" else 1, (28672, 4096)
+        a = (torch.randn(T, K, device=dev, generator=g) * 0.5).bfloat16()
+        qw = quant.quantize_weight(torch.randn(N, K) * 0.02, "Q4_K").to(dev)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+        def fn():
+            flush.zero_()
+            quant.linear_quant(a, qw)
         window(fn, reps=args.reps)
     elif args.what == "attn":
         B, Hq, Hkv, ctx, bs = 64, 32, 8, 2048, 16

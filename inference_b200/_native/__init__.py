@@ -98,6 +98,9 @@ def _declare_kernels(lib: ctypes.CDLL) -> None:
                                        c_int, c_void_p])
     sig("swb_reduce_norm_gather", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_float, c_void_p, c_int, c_int,
                                    c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    sig("swb_gemm_quant", [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                           c_void_p, c_void_p, ctypes.c_size_t, c_int, c_void_p])
+    sig("swb_dequant_rows", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
     sig("swb_peer_barrier", [c_void_p, c_void_p, c_int, c_int, c_void_p])
     sig("swb_im2col3x3", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
     sig("swb_softmax_rows", [c_void_p, c_void_p, c_int, c_int, c_ll, c_ll, c_float, c_void_p])

@@ -502,6 +502,53 @@ int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, int rows, int cols, int
   return 0;
 }
 
+// Cached 2-D map over 16-bit elements (packed quantised weights are moved as opaque 16-bit words):
+// [rows, cols] with a row pitch in bytes, box = box_cols x box_rows, optional 128-byte swizzle.
+int make_tmap_u16_2d(CUtensorMap* out, const void* ptr, long long cols, long long rows, long long row_pitch_bytes,
+                     int box_cols, int box_rows, int swizzle128) {
+  struct Key {
+    const void* ptr;
+    long long cols, rows, pitch;
+    int bc, br, sw;
+    bool operator==(const Key& o) const {
+      return ptr == o.ptr && cols == o.cols && rows == o.rows && pitch == o.pitch && bc == o.bc && br == o.br && sw == o.sw;
+    }
+  };
+  struct KeyHash {
+    size_t operator()(const Key& k) const {
+      size_t h = reinterpret_cast<size_t>(k.ptr);
+      for (long long v : {k.cols, k.rows, k.pitch, (long long)k.bc, (long long)k.br, (long long)k.sw})
+        h = h * 1000003u ^ (size_t)v;
+      return h;
+    }
+  };
+  static std::mutex mu;
+  static std::unordered_map<Key, CUtensorMap, KeyHash> cache;
+  const Key key{ptr, cols, rows, row_pitch_bytes, box_cols, box_rows, swizzle128};
+  {
+    std::lock_guard<std::mutex> g(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return 0;
+    }
+  }
+  auto encode = get_encode_fn();
+  if (!encode) return -1;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)row_pitch_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return -(int)r - 1000;
+  std::lock_guard<std::mutex> g(mu);
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, *out);
+  return 0;
+}
+
 int device_sm_count() {
   static int sms[64] = {0};
   int dev = 0;
