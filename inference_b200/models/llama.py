@@ -189,13 +189,32 @@ class LlamaGpu:
                 gate_up=rnd(2 * self.ffn, H), down=rnd(H, self.ffn), post_mlp_ln=ones(H) if sandwich else None))
         return self
 
+    def quantize_(self, fmt: str = "Q4_K") -> "LlamaGpu":
+        """Replace the projection weights of every layer by packed `fmt` weights (quantise-on-load, the role of
+        candle-llm's Q4_K / Q8_0 quantise-on-load: candle-llm/src/quant.rs); embeddings and the output head stay bf16.
+        Decode-sized steps then run the fused dequant-GEMM; the prefill tensor-parallel scatter paths need dense
+        weights and stay off."""
+        from ..ops.quant import quantize_on_device
+
+        for L in self.layers:
+            for name in ("qkv", "o", "gate_up", "down"):
+                w = getattr(L, name)
+                if isinstance(w, torch.Tensor) and w.shape[1] % 256 == 0:
+                    setattr(L, name, quantize_on_device(w, fmt))
+        self.quant_format = fmt
+        return self
+
+    quant_format: str | None = None
+
     def weight_bytes(self) -> int:
-        n = self.embed.numel() + self.norm.numel()
+        n, q = self.embed.numel() + self.norm.numel(), 0
         if self.lm_head.data_ptr() != self.embed.data_ptr() and not self.cfg.tie_word_embeddings:
             n += self.lm_head.numel()
         for L in self.layers:
-            n += L.qkv.numel() + L.o.numel() + L.gate_up.numel() + L.down.numel() + 2 * L.ln1.numel()
-        return n * 2
+            n += 2 * L.ln1.numel()
+            for t in (L.qkv, L.o, L.gate_up, L.down):
+                q += t.nbytes if not isinstance(t, torch.Tensor) else 2 * t.numel()
+        return n * 2 + q
 
     # ---- forward --------------------------------------------------------------------------------
     def forward_hidden(self, inp: StepInputs, kv_pool: torch.Tensor) -> torch.Tensor:
@@ -220,7 +239,7 @@ class LlamaGpu:
                 h = ops.rmsnorm(res, L.ln1, eps, w_offset=woff)
             else:
                 h = ops.rmsnorm(branch, L.ln1, eps, residual=res, w_offset=woff)
-            qkv = ops.gemm_bf16(h, L.qkv, bias=L.qkv_bias)
+            qkv = ops.linear_any(h, L.qkv, bias=L.qkv_bias)
             ops.rope_kv_write(qkv, inp.positions, inp.slot_mapping, self.cos, self.sin, kv_pool[li, 0], kv_pool[li, 1],
                               self.hq, self.hkv, D, rot_dim=self.rot_dim, interleaved=self.rope_interleaved,
                               q_norm=L.q_norm, k_norm=L.k_norm, norm_eps=eps, norm_w_offset=woff,
@@ -234,13 +253,13 @@ class LlamaGpu:
             if fused is not None:
                 h = fused.gemm_allreduce_rmsnorm(attn, L.o, res, L.ln2, eps, woff)
             else:
-                branch = ops.gemm_bf16(attn, L.o)
+                branch = ops.linear_any(attn, L.o)
                 branch = self.comm.all_reduce(branch)
                 if L.post_attn_ln is not None:
                     branch = ops.rmsnorm(branch, L.post_attn_ln, eps, w_offset=woff)
                     n += 1
                 h = ops.rmsnorm(branch, L.ln2, eps, residual=res, w_offset=woff)
-            gu = ops.gemm_bf16(h, L.gate_up)
+            gu = ops.linear_any(h, L.gate_up)
             act = ops.gated_act_mul(gu, cfg.mlp_activation)
             if fused is not None and L.post_mlp_ln is None:
                 # the down-projection's all-reduce fuses with the NEXT norm (next layer's ln1 or the final norm)
@@ -249,7 +268,7 @@ class LlamaGpu:
                 branch = None
             else:
                 pending_h = None
-                branch = ops.gemm_bf16(act, L.down)
+                branch = ops.linear_any(act, L.down)
                 branch = self.comm.all_reduce(branch)
                 if L.post_mlp_ln is not None:
                     branch = ops.rmsnorm(branch, L.post_mlp_ln, eps, w_offset=woff)
@@ -269,6 +288,8 @@ class LlamaGpu:
 
         f = self.comm.fused
         if f is None or not self.comm.is_parallel or T <= f.max_tokens or os.environ.get("SWB_TP_PREFILL") == "nccl":
+            return False
+        if self.quant_format is not None:
             return False
         if any(L.post_attn_ln is not None or L.post_mlp_ln is not None for L in self.layers):
             return False
@@ -301,7 +322,7 @@ class LlamaGpu:
         h = ctx.reduce_norm_gather(T, res, self.layers[0].ln1, eps, woff, reduce=False)
         n = 3
         for li, L in enumerate(self.layers):
-            qkv = ops.gemm_bf16(h, L.qkv, bias=L.qkv_bias)
+            qkv = ops.linear_any(h, L.qkv, bias=L.qkv_bias)
             ops.rope_kv_write(qkv, inp.positions, inp.slot_mapping, self.cos, self.sin, kv_pool[li, 0], kv_pool[li, 1],
                               self.hq, self.hkv, D, rot_dim=self.rot_dim, interleaved=self.rope_interleaved,
                               q_norm=L.q_norm, k_norm=L.k_norm, norm_eps=eps, norm_w_offset=woff,
@@ -312,7 +333,7 @@ class LlamaGpu:
                                        num_splits=inp.attn_splits, softcap=cfg.attn_logit_softcap or 0.0)
             ctx.gemm_scatter_rows(attn, L.o)
             h = ctx.reduce_norm_gather(T, res, L.ln2, eps, woff)
-            gu = ops.gemm_bf16(h, L.gate_up)
+            gu = ops.linear_any(h, L.gate_up)
             act = ops.gated_act_mul(gu, cfg.mlp_activation)
             ctx.gemm_scatter_rows(act, L.down)
             nxt = self.layers[li + 1].ln1 if li + 1 < len(self.layers) else self.norm

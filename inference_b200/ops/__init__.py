@@ -5,3 +5,4 @@ from .llm import (argmax, embedding, gated_act_mul, gated_residual, layernorm_mo
                   spec_verify_greedy)
 from .runtime import KernelError, check_status, device_status  # noqa: F401
 from .dit import axpy, groupnorm_nhwc, im2col3x3_nhwc, rgb8_nhwc, softmax_rows, upsample2x_nhwc  # noqa: E402,F401
+from .quant import QuantWeight, dequantize, linear_any, linear_quant, quantize_weight  # noqa: E402,F401

@@ -103,3 +103,66 @@ def linear_quant(a: torch.Tensor, qw: QuantWeight, bias: torch.Tensor | None = N
                                   ws.data_ptr(), ws.numel(), splits, stream_ptr())
     check(rc, "swb_gemm_quant")
     return out
+
+
+def linear_any(a: torch.Tensor, w, bias: torch.Tensor | None = None, out: torch.Tensor | None = None, **kw
+               ) -> torch.Tensor:
+    """a @ w^T for a dense bf16 weight or a QuantWeight (the projections of a model may be either)."""
+    if isinstance(w, QuantWeight):
+        assert not kw or set(kw) <= {"out_dtype"} and kw.get("out_dtype") in (None, torch.bfloat16)
+        return linear_quant(a, w, bias=bias, out=out)
+    return gemm_bf16(a, w, bias=bias, out=out, **kw)
+
+
+def _q8_0_torch(w: torch.Tensor) -> torch.Tensor:
+    N, K = w.shape
+    g = w.float().reshape(N, K // 32, 32)
+    d = (g.abs().amax(-1, keepdim=True) / 127.0).half()
+    inv = torch.where(d.float() > 0, 1.0 / d.float(), torch.zeros_like(d, dtype=torch.float32))
+    q = (g * inv).round().clamp(-127, 127).to(torch.int8)
+    out = torch.empty((N, K // 32, 34), dtype=torch.uint8, device=w.device)
+    out[..., :2] = d.view(torch.uint8).reshape(N, K // 32, 2)
+    out[..., 2:] = q.view(torch.uint8)
+    return out.reshape(N, -1)
+
+
+def _q4_k_torch(w: torch.Tensor) -> torch.Tensor:
+    """Min/max Q4_K on the device: per 32-weight sub-block scale = (max - min) / 15 and offset = -min (clamped at 0),
+    both quantised to 6 bits against the super-block's largest scale / offset (fp16 d / dmin)."""
+    N, K = w.shape
+    g = w.float().reshape(N, K // 256, 8, 32)
+    lo = g.amin(-1).clamp_max(0.0)
+    hi = g.amax(-1)
+    scale = ((hi - lo) / 15.0).clamp_min(0.0)
+    mn = -lo
+    d = (scale.amax(-1, keepdim=True) / 63.0).half()
+    dmin = (mn.amax(-1, keepdim=True) / 63.0).half()
+    inv_d = torch.where(d.float() > 0, 1.0 / d.float(), torch.zeros_like(d, dtype=torch.float32))
+    inv_dm = torch.where(dmin.float() > 0, 1.0 / dmin.float(), torch.zeros_like(dmin, dtype=torch.float32))
+    sc = (scale * inv_d).round().clamp(0, 63).to(torch.int32)          # [N, B, 8]
+    m = (mn * inv_dm).round().clamp(0, 63).to(torch.int32)
+    eff_s = d.float() * sc.float()
+    eff_m = dmin.float() * m.float()
+    inv_s = torch.where(eff_s > 0, 1.0 / eff_s, torch.zeros_like(eff_s))
+    q = ((g + eff_m[..., None]) * inv_s[..., None]).round().clamp(0, 15).to(torch.int32)   # [N, B, 8, 32]
+    out = torch.empty((N, K // 256, 144), dtype=torch.uint8, device=w.device)
+    out[..., 0:2] = d.view(torch.uint8).reshape(N, K // 256, 2)
+    out[..., 2:4] = dmin.view(torch.uint8).reshape(N, K // 256, 2)
+    s_lo, s_hi, m_lo, m_hi = sc[..., :4], sc[..., 4:], m[..., :4], m[..., 4:]
+    out[..., 4:8] = (s_lo | ((s_hi >> 4) << 6)).to(torch.uint8)
+    out[..., 8:12] = (m_lo | ((m_hi >> 4) << 6)).to(torch.uint8)
+    out[..., 12:16] = ((s_hi & 0xF) | ((m_hi & 0xF) << 4)).to(torch.uint8)
+    pairs = q.reshape(N, K // 256, 4, 2, 32)                            # pair p: sub-blocks 2p (low nibbles), 2p+1 (high)
+    out[..., 16:] = (pairs[:, :, :, 0] | (pairs[:, :, :, 1] << 4)).to(torch.uint8).reshape(N, K // 256, 128)
+    return out.reshape(N, -1)
+
+
+def quantize_on_device(w: torch.Tensor, fmt: str) -> QuantWeight:
+    """Quantise a bf16 / fp32 [N, K] tensor where it lives (used for quantise-on-load of whole models)."""
+    N, K = w.shape
+    assert K % 256 == 0
+    if fmt == "Q8_0":
+        return QuantWeight(fmt, _q8_0_torch(w).contiguous(), N, K)
+    if fmt == "Q4_K":
+        return QuantWeight(fmt, _q4_k_torch(w).contiguous(), N, K)
+    return quantize_weight(w.float(), fmt)

@@ -94,7 +94,7 @@ class FusedCollectives:
         """normed = rmsnorm(allreduce(a @ w^T) + residual) with the residual updated in place."""
         T = a.shape[0]
         buf, i = self.exchange_buffer(T)
-        ops.gemm_bf16(a, w, out=buf)
+        ops.linear_any(a, w, out=buf)
         out = torch.empty((T, self.hidden), dtype=torch.bfloat16, device=a.device)
         self._launch(i, T, residual, norm_w, eps, w_offset, out)
         return out

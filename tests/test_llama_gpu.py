@@ -82,3 +82,41 @@ def test_greedy_decode_matches_oracle_tokens():
         if a != b:
             assert margins[i] < 0.05, f"diverged at step {i} with margin {margins[i]}"
             break
+
+
+@pytest.mark.parametrize("fmt", ["Q4_K", "Q8_0"])
+def test_quantised_model_matches_oracle_on_dequantised_weights(fmt):
+    """quantize_() swaps the projections for packed weights; logits must match the fp32 oracle run on the very
+    weights those packed bytes decode to (prefill uses the expand + dense GEMM path, decode the fused dequant-GEMM)."""
+    from inference_b200.engine.kv_pool import PagedKvPool, PagedSequence
+    from inference_b200.engine.runner import ModelRunner
+    from inference_b200.models.llama import LlamaGpu
+    from inference_b200.models.oracle import OracleLlama, random_llama_weights
+    from inference_b200.ops import quant
+
+    cfg = _small_cfg()
+    w = {k: v.bfloat16().float() for k, v in random_llama_weights(cfg, seed=2, std=0.05).items()}
+    proj = ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj")
+    wq = {k: (quant.dequantize_reference(quant.quantize_on_device(v, fmt)) if any(p in k for p in proj) else v)
+          for k, v in w.items()}
+    oracle = OracleLlama(cfg, wq, dtype=torch.float32, device="cuda")
+    model = LlamaGpu(cfg, device=torch.device("cuda")).load_state_dict(w).quantize_(fmt)
+    assert model.quant_format == fmt and not isinstance(model.layers[0].qkv, torch.Tensor)
+    pool = PagedKvPool(cfg.num_layers, 256, model.hkv, cfg.head_dim, 16, device="cuda")
+    runner = ModelRunner(model, pool, max_batch=4, max_seq_len=512)
+    prompts = [list(range(5, 90)), list(range(300, 312))]
+    seqs = [PagedSequence(pool) for _ in prompts]
+    logits = runner.prefill(seqs, prompts, want_logits=True)
+    caches = []
+    for i, p in enumerate(prompts):
+        c = oracle.make_cache()
+        ref = oracle.decode_logits(torch.tensor([p], device="cuda"), c, 0)[0]
+        caches.append(c)
+        assert (logits[i] - ref).abs().max().item() < 0.1 * max(1.0, ref.abs().max().item())
+    toks = [int(logits[i].argmax()) for i in range(2)]
+    for step in range(3):
+        lg = runner.decode(seqs, toks, want_logits=True)
+        for i in range(2):
+            ref = oracle.decode_logits(torch.tensor([[toks[i]]], device="cuda"), caches[i], caches[i].offset)[0]
+            assert (lg[i] - ref).abs().max().item() < 0.1 * max(1.0, ref.abs().max().item()), (fmt, step, i)
+        toks = [int(lg[i].argmax()) for i in range(2)]
