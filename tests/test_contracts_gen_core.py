@@ -1,0 +1,176 @@
+"""Tensor-free media contracts: request validation floor, registry builder, sampler framework (schedules, solvers
+converging on an analytic denoiser), guidance math, tiling plans and the memory-adaptation ladder."""
+import math
+
+import pytest
+
+from inference_b200.contracts.errors import InferenceError, Unsupported
+from inference_b200.contracts.gen_core import (Capabilities, Conditioning, ConditioningKind, GenerationRequest,
+                                               LoadSpec, Modality, ModelDescriptor, ProviderRegistryBuilder, Quant,
+                                               Registration, TilingConfig, WeightsSource, apg, budgeted_plan, cfg,
+                                               cfg_rescale, model_descriptor_errors, plan_memory_adaptation,
+                                               plan_tiles, reject_unknown_components, require_component,
+                                               trapezoidal_mask)
+from inference_b200.contracts.gen_core.sampling import (SCHEDULERS, SOLVERS, CpuLatentOps, DiscreteModelSampling,
+                                                        EdmModelSampling, FlowMatchPolicy, FlowModelSampling,
+                                                        build_flow_sigmas, compute_mu, denoise, get_solver,
+                                                        image_seq_len, schedule_sigmas)
+
+
+def _caps(**kw):
+    base = dict(min_size=256, max_size=1024, max_count=4, samplers=["euler"], schedulers=["simple"])
+    base.update(kw)
+    return Capabilities(**base)
+
+
+def test_request_validation_floor():
+    caps = _caps(supports_guidance=True)
+    caps.validate_request("m", GenerationRequest(prompt="a", width=512, height=512, guidance=3.0, sampler="euler"))
+    bad = [dict(count=0), dict(count=5), dict(steps=0), dict(steps=1_000_000), dict(width=128), dict(height=2048),
+           dict(negative_prompt="x"), dict(true_cfg=2.0), dict(sampler="heun"), dict(scheduler="karras"),
+           dict(guidance=float("inf")), dict(strength=float("nan")), dict(guidance_method="apg"),
+           dict(conditioning=[Conditioning(kind=ConditioningKind.DEPTH)])]
+    for kw in bad:
+        with pytest.raises(InferenceError):
+            caps.validate_request("m", GenerationRequest(**{"prompt": "a", "width": 512, "height": 512, **kw}))
+    # unsupported surface is the typed Unsupported, malformed values are plain errors
+    with pytest.raises(Unsupported):
+        caps.validate_request("m", GenerationRequest(prompt="a", width=512, height=512, negative_prompt="x"))
+    try:
+        caps.validate_request("m", GenerationRequest(prompt="a", width=512, height=512, count=0))
+    except Unsupported:
+        pytest.fail("a range error must not be reported as Unsupported")
+    except InferenceError:
+        pass
+    caps.validate_request_skip_size("m", GenerationRequest(prompt="a", width=64, height=64))
+
+
+def _desc(mid="gen_a", backend="b200", **kw):
+    return ModelDescriptor(id=mid, family="fam", backend=backend, modality=Modality.IMAGE, capabilities=_caps(**kw))
+
+
+def test_registry_builder_and_descriptor_sweep():
+    loaded = []
+    reg = (ProviderRegistryBuilder()
+           .register_generators([Registration(lambda: _desc("gen_a"), lambda s: loaded.append(("a", s)) or "A"),
+                                 Registration(lambda: _desc("gen_b"), lambda s: "B")])
+           .reject_quant(Quant.NVFP4, "no block-scaled path on this backend").build())
+    assert reg.ids() == ["gen_a", "gen_b"] and reg.descriptor_conformance_errors() == []
+    assert reg.load("gen_a", LoadSpec.from_dir("/x")) == "A" and loaded
+    with pytest.raises(InferenceError):
+        reg.load("nope", LoadSpec.from_dir("/x"))
+    with pytest.raises(Unsupported):
+        reg.load("gen_b", LoadSpec(weights=WeightsSource.dir("/x"), quantize=Quant.NVFP4))
+    with pytest.raises(InferenceError):      # duplicate id within a kind
+        ProviderRegistryBuilder().register_generators([Registration(lambda: _desc("d"), lambda s: 0),
+                                                       Registration(lambda: _desc("d"), lambda s: 0)]).build()
+    errs = model_descriptor_errors(_desc(" padded", samplers=["eu ler", "euler", "euler"], max_count=0))
+    for needle in ("empty or padded", "whitespace", "duplicate", "max_count is 0"):
+        assert any(needle in e for e in errs), (needle, errs)
+    assert model_descriptor_errors(_desc()) == []
+
+
+def test_component_gates():
+    comps = {"vae": WeightsSource.dir("/v")}
+    assert require_component(comps, "vae", "m").path.name == "v"
+    with pytest.raises(InferenceError):
+        require_component(comps, "text_encoder", "m")
+    reject_unknown_components(comps, ["vae", "unet"], "m")
+    with pytest.raises(InferenceError):
+        reject_unknown_components(comps, ["unet"], "m")
+
+
+def test_flow_schedule_and_policy():
+    assert image_seq_len(1024, 1024) == 4096 and image_seq_len(512, 768) == 32 * 48
+    mu_small, mu_big = compute_mu(256, 28), compute_mu(4096, 28)
+    assert mu_big > mu_small > 0
+    s = build_flow_sigmas(28, mu_big)
+    assert len(s) == 29 and s[0] == pytest.approx(1.0) and s[-1] == 0.0 and all(a > b for a, b in zip(s, s[1:]))
+    lin = build_flow_sigmas(4, 0.0)
+    assert lin == pytest.approx([1.0, 0.75, 0.5, 0.25, 0.0])
+    pol = FlowMatchPolicy(s)
+    c = pol.coeffs(3)
+    assert pol.num_steps() == 28 and c.timestep == s[3] and c.a_out == pytest.approx(s[4] - s[3]) and c.a_noise == 0.0
+
+
+@pytest.mark.parametrize("ms", [FlowModelSampling(), FlowModelSampling(mu=1.15), DiscreteModelSampling(),
+                                EdmModelSampling()])
+def test_every_scheduler_is_monotone(ms):
+    for name in SCHEDULERS:
+        sig = schedule_sigmas(name, ms, 12)
+        if name in ("ddim_uniform", "beta", "beta57"):   # index-striding / de-duplicating schedules vary in length
+            assert 2 <= len(sig) <= 14 and sig[-1] == 0.0, name
+        else:
+            assert len(sig) == 13 and sig[-1] == 0.0, name
+        assert all(a >= b for a, b in zip(sig, sig[1:])) and sig[0] > 0, name
+        assert all(math.isfinite(x) for x in sig)
+    with pytest.raises(KeyError):
+        schedule_sigmas("nope", ms, 4)
+
+
+@pytest.mark.parametrize("name", sorted(SOLVERS))
+def test_solvers_recover_the_clean_sample(name):
+    """With a perfect flow model (velocity = noise - x0) every solver must land on x0 from pure noise."""
+    ops, ms = CpuLatentOps(), FlowModelSampling()
+    x0 = [0.3, -1.2, 0.7, 2.0]
+    noise = [1.0, 0.5, -0.8, 0.1]
+    x = [n for n in noise]                               # sigma = 1: pure noise
+
+    def model(x_in, t):                                  # v = noise_hat - x0 with noise_hat inferred from x_t, t
+        if t >= 1.0:
+            return [n - c for n, c in zip(x_in, x0)]
+        return [((xi - (1 - t) * c) / t if t > 0 else 0.0) - c for xi, c in zip(x_in, x0)]
+
+    sig = build_flow_sigmas(12, 0.0)
+    out = get_solver(name).sample(ops, ms, lambda xx, s: denoise(ops, ms, xx, s, model), x, sig, seed=3)
+    assert all(abs(a - b) < 1e-3 for a, b in zip(out, x0)), (name, out)
+    with pytest.raises(KeyError):
+        get_solver("nope")
+
+
+def test_guidance_math():
+    ops = CpuLatentOps()
+    cond, unc = [1.0, 2.0, -1.0, 0.5], [0.5, 1.0, 0.0, 0.0]
+    assert cfg(ops, cond, unc, 1.0) == pytest.approx(cond)
+    assert cfg(ops, cond, unc, 3.0) == pytest.approx([u + 3 * (c - u) for c, u in zip(cond, unc)])
+    g = cfg_rescale(ops, cond, unc, 5.0, rescale=1.0)
+
+    def std(v):
+        m = sum(v) / len(v)
+        return math.sqrt(sum((t - m) ** 2 for t in v) / len(v))
+    assert std(g) == pytest.approx(std(cond), rel=1e-6)
+    # APG with eta = 1 and no clipping is plain CFG; eta = 0 removes the component parallel to cond
+    assert apg(ops, cond, unc, 4.0, eta=1.0) == pytest.approx(cfg(ops, cond, unc, 4.0))
+    a0 = apg(ops, cond, unc, 4.0, eta=0.0)
+    delta = [a - c for a, c in zip(a0, cond)]
+    assert abs(sum(d * c for d, c in zip(delta, cond))) < 1e-9
+
+
+def test_tiling_and_memory_ladder():
+    plan = plan_tiles(128, 160, TilingConfig(64, 16))
+    assert not plan.is_single() and plan.tiles[0].y0 == 0 and plan.tiles[-1].y1 == 128 and plan.tiles[-1].x1 == 160
+    covered = [[0] * 160 for _ in range(128)]
+    for t in plan.tiles:
+        for y in range(t.y0, t.y1):
+            for x in range(t.x0, t.x1):
+                covered[y][x] += 1
+    assert min(min(r) for r in covered) >= 1
+    assert plan_tiles(32, 32, TilingConfig(64, 16)).is_single()
+    up, down = trapezoidal_mask(10, 4, 0), trapezoidal_mask(10, 0, 4)
+    assert up[-1] == 1.0 and down[0] == 1.0 and up[0] < up[3] < 1.0
+    # complementary ramps across an overlap sum to one
+    ramp_in, ramp_out = trapezoidal_mask(8, 4, 0)[:4], trapezoidal_mask(8, 0, 4)[-4:]
+    assert [a + b for a, b in zip(ramp_in, ramp_out)] == pytest.approx([1.0] * 4)
+    big = budgeted_plan(256, 256, TilingConfig(128, 16), bytes_per_latent_pixel=1 << 20, budget_bytes=1 << 32)
+    small = budgeted_plan(256, 256, TilingConfig(128, 16), bytes_per_latent_pixel=1 << 20, budget_bytes=1 << 30)
+    assert len(small.tiles) > len(big.tiles)
+    args = (10 << 30, 24 << 30, 1 << 30, 2 << 30, 16 << 30)   # text encoder, transformer, vae, activations, vae act.
+    roomy = plan_memory_adaptation(200 << 30, *args)
+    assert roomy.fits and not roomy.sequential_offload and not roomy.vae_tiling and roomy.scale_resolution == 1.0
+    seq = plan_memory_adaptation(42 << 30, *args)              # 24 + 1 + 16 = 41 GB heavy phase fits only alone
+    assert seq.fits and seq.sequential_offload and not seq.vae_tiling
+    tiled = plan_memory_adaptation(30 << 30, *args)
+    assert tiled.fits and tiled.vae_tiling and not tiled.quantize_branch
+    quant = plan_memory_adaptation(12 << 30, *args)
+    assert quant.fits and quant.quantize_branch
+    assert not plan_memory_adaptation(1 << 30, *args).fits
