@@ -87,8 +87,17 @@ def build_host(force: bool = False) -> Path:
     return lib
 
 
+def build_capi(force: bool = False) -> Path:
+    """The contracts C ABI (embeds / joins a Python interpreter at run time; links no libpython)."""
+    src = CSRC / "capi" / "capi.cpp"
+    lib = OUT / "libswb200_capi.so"
+    if force or _newer(src, lib, [CSRC / "include" / "swb200_contracts.h"]):
+        _run([CXX, *CXX_FLAGS, "-shared", "-o", str(lib), str(src), "-ldl", "-lpthread"])
+    return lib
+
+
 def build_all(force: bool = False) -> dict[str, Path]:
-    return {"kernels": build_kernels(force), "host": build_host(force)}
+    return {"kernels": build_kernels(force), "host": build_host(force), "capi": build_capi(force)}
 
 
 if __name__ == "__main__":
