@@ -608,8 +608,9 @@ int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
     swapped = 0;
   }
   if (swapped < 0) swapped = (a.T <= 256) ? 1 : 0;
-  // decode-sized problems with fewer weight tiles than SMs: cluster split-K with a DSMEM reduction
-  if (!a.scatter && (a.force_mode == 2 || (a.force_mode < 0 && gemm_decode_cluster_supported(a.T) && (a.N + BM - 1) / BM < sms &&
+  // decode-sized problems with at most two weight tiles per SM: the two-CTAs-per-SM cluster kernel (split-K over a
+  // cluster with a DSMEM reduction when tiles are few, plain whole tiles otherwise)
+  if (!a.scatter && (a.force_mode == 2 || (a.force_mode < 0 && gemm_decode_cluster_supported(a.T) && (a.N + BM - 1) / BM <= 2 * sms &&
                             (a.K + BK - 1) / BK >= 8))) {
     if (!gemm_decode_cluster_supported(a.T)) return -4;
     return gemm_decode_cluster_launch(a, a.force_mode == 2 ? a.force_ctas : 0, stream);
