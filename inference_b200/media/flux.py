@@ -290,8 +290,10 @@ def registrations(backend: str = "b200") -> list[Registration]:
                          footprint=_footprint(v)) for v in (Variant.SCHNELL, Variant.DEV)]
 
 
-def write_synthetic_snapshot(root, variant: Variant = Variant.DEV, seed: int = 0) -> Path:
-    """A tiny random FLUX-shaped snapshot (2+2 blocks, hidden 256) with the hash text encoder."""
+def write_synthetic_snapshot(root, variant: Variant = Variant.DEV, seed: int = 0, text: str = "hash") -> Path:
+    """A tiny random FLUX-shaped snapshot (2+2 blocks, hidden 256). text="hash" uses the weight-free prompt encoder;
+    text="t5_clip" also writes tiny random T5 / CLIP encoders with real tokenizer files (a SentencePiece model trained
+    on a toy corpus, a toy CLIP BPE vocabulary) in the Hugging Face directory layout."""
     from ..io.safetensors_io import save_file
     from ..models.dit_flux import random_flux_weights
     from ..models.vae import random_vae_weights
@@ -307,5 +309,78 @@ def write_synthetic_snapshot(root, variant: Variant = Variant.DEV, seed: int = 0
         "dit": {**{k: getattr(dit, k) for k in ("in_channels", "vec_in_dim", "context_in_dim", "hidden_size",
                                                 "num_heads", "depth", "depth_single", "guidance_embed")},
                 "axes_dim": list(dit.axes_dim)},
-        "vae": {"ch": vae.ch, "ch_mult": list(vae.ch_mult), "num_res_blocks": vae.num_res_blocks}, "text": "hash"}))
+        "vae": {"ch": vae.ch, "ch_mult": list(vae.ch_mult), "num_res_blocks": vae.num_res_blocks}, "text": text}))
+    if text == "t5_clip":
+        _write_synthetic_text_encoders(root, dit.context_in_dim, dit.vec_in_dim, seed)
     return root
+
+
+def _write_synthetic_text_encoders(root: Path, context_dim: int, vec_dim: int, seed: int) -> None:
+    import sentencepiece as spm
+
+    from ..io.safetensors_io import save_file
+
+    g = torch.Generator().manual_seed(seed + 7)
+    rnd = lambda *shape: torch.randn(*shape, generator=g) * 0.05   # noqa: E731
+    # ---- T5 (2 layers, d_model = context_dim) --------------------------------------------------------------
+    (root / "tokenizer_2").mkdir(exist_ok=True)
+    corpus = root / "tokenizer_2" / "corpus.txt"
+    words = "a fox cat dog red blue green big small runs jumps over the lazy quick brown photo of in on".split()
+    corpus.write_text("\n".join(" ".join(words[(i * 7 + j) % len(words)] for j in range(6)) for i in range(200)))
+    spm.SentencePieceTrainer.train(input=str(corpus), model_prefix=str(root / "tokenizer_2" / "spiece"), vocab_size=64,
+                                   model_type="unigram", pad_id=0, eos_id=1, unk_id=2, bos_id=-1,
+                                   minloglevel=2, hard_vocab_limit=False)
+    corpus.unlink()
+    t5 = {"vocab_size": 64, "d_model": context_dim, "d_kv": 16, "d_ff": 96, "num_layers": 2, "num_heads": 4,
+          "relative_attention_num_buckets": 8, "relative_attention_max_distance": 32}
+    tw = {"shared.weight": rnd(64, context_dim), "encoder.final_layer_norm.weight": torch.ones(context_dim),
+          "encoder.block.0.layer.0.SelfAttention.relative_attention_bias.weight": rnd(8, 4)}
+    for i in range(2):
+        p = f"encoder.block.{i}.layer"
+        for n in "qkv":
+            tw[f"{p}.0.SelfAttention.{n}.weight"] = rnd(64, context_dim)
+        tw[f"{p}.0.SelfAttention.o.weight"] = rnd(context_dim, 64)
+        tw[f"{p}.0.layer_norm.weight"] = torch.ones(context_dim)
+        tw[f"{p}.1.layer_norm.weight"] = torch.ones(context_dim)
+        tw[f"{p}.1.DenseReluDense.wi_0.weight"] = rnd(96, context_dim)
+        tw[f"{p}.1.DenseReluDense.wi_1.weight"] = rnd(96, context_dim)
+        tw[f"{p}.1.DenseReluDense.wo.weight"] = rnd(context_dim, 96)
+    (root / "text_encoder_2").mkdir(exist_ok=True)
+    (root / "text_encoder_2" / "config.json").write_text(json.dumps(t5))
+    save_file(tw, root / "text_encoder_2" / "model.safetensors")
+    # ---- CLIP (2 layers, hidden = vec_dim) ------------------------------------------------------------------
+    from .text_models import _bytes_to_unicode
+
+    chars = sorted(set(_bytes_to_unicode().values()))
+    vocab = {}
+    for c in chars:
+        vocab[c] = len(vocab)
+    for c in chars:
+        vocab[c + "</w>"] = len(vocab)
+    merges = [("f", "o"), ("fo", "x</w>"), ("c", "a"), ("ca", "t</w>"), ("d", "o"), ("do", "g</w>")]
+    for a, b in merges:
+        vocab[a + b] = len(vocab)
+    vocab["<|startoftext|>"] = len(vocab)
+    vocab["<|endoftext|>"] = len(vocab)
+    (root / "tokenizer").mkdir(exist_ok=True)
+    (root / "tokenizer" / "vocab.json").write_text(json.dumps(vocab), encoding="utf-8")
+    (root / "tokenizer" / "merges.txt").write_text("#version: 0.2\n" + "\n".join(f"{a} {b}" for a, b in merges),
+                                                   encoding="utf-8")
+    V, Hc = len(vocab), vec_dim
+    clip = {"vocab_size": V, "hidden_size": Hc, "intermediate_size": 2 * Hc, "num_hidden_layers": 2,
+            "num_attention_heads": 2, "max_position_embeddings": 24, "eos_token_id": vocab["<|endoftext|>"],
+            "hidden_act": "quick_gelu"}
+    cw = {"text_model.embeddings.token_embedding.weight": rnd(V, Hc),
+          "text_model.embeddings.position_embedding.weight": rnd(24, Hc),
+          "text_model.final_layer_norm.weight": torch.ones(Hc), "text_model.final_layer_norm.bias": torch.zeros(Hc)}
+    for i in range(2):
+        lp = f"text_model.encoder.layers.{i}."
+        for n in ("q_proj", "k_proj", "v_proj", "out_proj"):
+            cw[f"{lp}self_attn.{n}.weight"], cw[f"{lp}self_attn.{n}.bias"] = rnd(Hc, Hc), rnd(Hc)
+        for n in ("layer_norm1", "layer_norm2"):
+            cw[f"{lp}{n}.weight"], cw[f"{lp}{n}.bias"] = torch.ones(Hc), torch.zeros(Hc)
+        cw[lp + "mlp.fc1.weight"], cw[lp + "mlp.fc1.bias"] = rnd(2 * Hc, Hc), rnd(2 * Hc)
+        cw[lp + "mlp.fc2.weight"], cw[lp + "mlp.fc2.bias"] = rnd(Hc, 2 * Hc), rnd(Hc)
+    (root / "text_encoder").mkdir(exist_ok=True)
+    (root / "text_encoder" / "config.json").write_text(json.dumps(clip))
+    save_file(cw, root / "text_encoder" / "model.safetensors")

@@ -1,0 +1,168 @@
+"""T5 (v1.1, encoder only) and CLIP text encoders: the two prompt encoders of FLUX-family pipelines
+(candle-gen-flux/src/pipeline.rs:552-620 encodes with T5-XXL [1, L, 4096] and takes CLIP-L's pooled vector [1, 768]).
+
+Both are written once over torch tensors; `linear` routes every projection through the tcgen05 GEMM when the weights
+are bf16 on a CUDA device and through a plain matmul otherwise (CPU oracle backend). Attention runs on small
+[heads, L, L] score tensors (L <= 512, head dim 64) and stays in torch. Weight names follow the Hugging Face
+checkpoints (`encoder.block.N.layer.0.SelfAttention.q.weight`, `text_model.encoder.layers.N.self_attn.q_proj.weight`)."""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None = None) -> torch.Tensor:
+    if x.is_cuda and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0:
+        from .. import ops
+
+        lead = x.shape[:-1]
+        y = ops.gemm_bf16(x.reshape(-1, x.shape[-1]).to(torch.bfloat16).contiguous(), w, bias=b)
+        return y.reshape(*lead, w.shape[0])
+    y = x.to(w.dtype) @ w.t()
+    return y + b if b is not None else y
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# T5 encoder
+# ---------------------------------------------------------------------------------------------------------------
+@dataclass
+class T5Config:
+    vocab_size: int = 32128
+    d_model: int = 4096
+    d_kv: int = 64
+    d_ff: int = 10240
+    num_layers: int = 24
+    num_heads: int = 64
+    relative_attention_num_buckets: int = 32
+    relative_attention_max_distance: int = 128
+    layer_norm_epsilon: float = 1e-6
+
+    @staticmethod
+    def from_json(j: dict) -> "T5Config":
+        keys = T5Config.__dataclass_fields__
+        return T5Config(**{k: j[k] for k in keys if k in j})
+
+
+def _t5_bucket(rel: torch.Tensor, num_buckets: int, max_distance: int) -> torch.Tensor:
+    """Bidirectional bucketing of relative positions (memory - query)."""
+    nb = num_buckets // 2
+    out = (rel > 0).long() * nb
+    n = rel.abs()
+    max_exact = nb // 2
+    large = max_exact + (torch.log(n.float().clamp_min(1) / max_exact) / math.log(max_distance / max_exact)
+                         * (nb - max_exact)).long()
+    large = torch.minimum(large, torch.full_like(large, nb - 1))
+    return out + torch.where(n < max_exact, n, large)
+
+
+class T5Encoder:
+    def __init__(self, cfg: T5Config, weights: dict[str, torch.Tensor], device="cpu", dtype=torch.float32):
+        self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
+        self.w = {k: v.to(device=self.device, dtype=dtype).contiguous() for k, v in weights.items()
+                  if k.startswith(("encoder.", "shared."))}
+        if "shared.weight" not in self.w and "encoder.embed_tokens.weight" in self.w:
+            self.w["shared.weight"] = self.w["encoder.embed_tokens.weight"]
+
+    def _norm(self, x, name):
+        v = x.float().pow(2).mean(-1, keepdim=True)
+        return (x.float() * torch.rsqrt(v + self.cfg.layer_norm_epsilon)).to(self.dtype) * self.w[name]
+
+    @torch.no_grad()
+    def encode(self, ids: torch.Tensor, mask: torch.Tensor | None = None) -> torch.Tensor:
+        """ids [B, L] int64 -> last hidden state [B, L, d_model]. `mask` [B, L] (1 = attend); FLUX passes none and
+        attends the padding too."""
+        cfg = self.cfg
+        B, L = ids.shape
+        H, D = cfg.num_heads, cfg.d_kv
+        x = self.w["shared.weight"][ids.to(self.device)]
+        pos = torch.arange(L, device=self.device)
+        buckets = _t5_bucket(pos[None, :] - pos[:, None], cfg.relative_attention_num_buckets,
+                             cfg.relative_attention_max_distance)
+        table = self.w["encoder.block.0.layer.0.SelfAttention.relative_attention_bias.weight"]      # [buckets, H]
+        bias = table[buckets].permute(2, 0, 1)[None].float()                                          # [1, H, L, L]
+        if mask is not None:
+            bias = bias + (1.0 - mask.to(self.device).float())[:, None, None, :] * torch.finfo(torch.float32).min
+        for i in range(cfg.num_layers):
+            p = f"encoder.block.{i}.layer"
+            h = self._norm(x, f"{p}.0.layer_norm.weight")
+            q, k, v = (linear(h, self.w[f"{p}.0.SelfAttention.{n}.weight"]).view(B, L, H, D).transpose(1, 2)
+                       for n in "qkv")
+            s = q.float() @ k.float().transpose(-1, -2) + bias          # T5 does not scale by sqrt(d)
+            a = (torch.softmax(s, -1) @ v.float()).transpose(1, 2).reshape(B, L, H * D).to(self.dtype)
+            x = x + linear(a, self.w[f"{p}.0.SelfAttention.o.weight"])
+            h = self._norm(x, f"{p}.1.layer_norm.weight")
+            g = F.gelu(linear(h, self.w[f"{p}.1.DenseReluDense.wi_0.weight"]).float(), approximate="tanh")
+            u = linear(h, self.w[f"{p}.1.DenseReluDense.wi_1.weight"]).float()
+            x = x + linear((g * u).to(self.dtype), self.w[f"{p}.1.DenseReluDense.wo.weight"])
+        return self._norm(x, "encoder.final_layer_norm.weight")
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# CLIP text encoder
+# ---------------------------------------------------------------------------------------------------------------
+@dataclass
+class ClipTextConfig:
+    vocab_size: int = 49408
+    hidden_size: int = 768
+    intermediate_size: int = 3072
+    num_hidden_layers: int = 12
+    num_attention_heads: int = 12
+    max_position_embeddings: int = 77
+    layer_norm_eps: float = 1e-5
+    hidden_act: str = "quick_gelu"
+    eos_token_id: int = 49407
+
+    @staticmethod
+    def from_json(j: dict) -> "ClipTextConfig":
+        j = j.get("text_config", j)
+        keys = ClipTextConfig.__dataclass_fields__
+        return ClipTextConfig(**{k: j[k] for k in keys if k in j})
+
+
+class ClipTextEncoder:
+    def __init__(self, cfg: ClipTextConfig, weights: dict[str, torch.Tensor], device="cpu", dtype=torch.float32):
+        self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
+        self.w = {k: v.to(device=self.device, dtype=dtype).contiguous() for k, v in weights.items()
+                  if k.startswith("text_model.")}
+
+    def _ln(self, x, name):
+        return F.layer_norm(x.float(), (x.shape[-1],), self.w[name + ".weight"].float(), self.w[name + ".bias"].float(),
+                            self.cfg.layer_norm_eps).to(self.dtype)
+
+    def _act(self, x):
+        x = x.float()
+        if self.cfg.hidden_act == "quick_gelu":
+            return x * torch.sigmoid(1.702 * x)
+        return F.gelu(x)
+
+    @torch.no_grad()
+    def encode(self, ids: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """ids [B, L <= 77] -> (last hidden state [B, L, hidden], pooled [B, hidden] = state at the first EOS token)."""
+        cfg = self.cfg
+        B, L = ids.shape
+        H = cfg.num_attention_heads
+        D = cfg.hidden_size // H
+        ids = ids.to(self.device)
+        p = "text_model."
+        x = self.w[p + "embeddings.token_embedding.weight"][ids] + self.w[p + "embeddings.position_embedding.weight"][:L]
+        causal = torch.full((L, L), float("-inf"), device=self.device).triu(1)
+        for i in range(cfg.num_hidden_layers):
+            lp = f"{p}encoder.layers.{i}."
+            h = self._ln(x, lp + "layer_norm1")
+            q, k, v = (linear(h, self.w[f"{lp}self_attn.{n}_proj.weight"], self.w[f"{lp}self_attn.{n}_proj.bias"])
+                       .view(B, L, H, D).transpose(1, 2).float() for n in "qkv")
+            s = q @ k.transpose(-1, -2) * D ** -0.5 + causal
+            a = (torch.softmax(s, -1) @ v).transpose(1, 2).reshape(B, L, H * D).to(self.dtype)
+            x = x + linear(a, self.w[lp + "self_attn.out_proj.weight"], self.w[lp + "self_attn.out_proj.bias"])
+            h = self._ln(x, lp + "layer_norm2")
+            h = self._act(linear(h, self.w[lp + "mlp.fc1.weight"], self.w[lp + "mlp.fc1.bias"])).to(self.dtype)
+            x = x + linear(h, self.w[lp + "mlp.fc2.weight"], self.w[lp + "mlp.fc2.bias"])
+        x = self._ln(x, p + "final_layer_norm")
+        if cfg.eos_token_id == 2:                     # legacy checkpoints: the EOS has the largest id
+            eos = ids.argmax(-1)
+        else:
+            eos = (ids == cfg.eos_token_id).int().argmax(-1)
+        return x, x[torch.arange(B, device=self.device), eos]

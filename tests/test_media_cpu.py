@@ -103,3 +103,26 @@ def test_seed_and_patch_helpers():
     assert len(s) == 5 and s[0] == 1.0 and s[-1] == 0.0 and all(x > y for x, y in zip(s, s[1:]))
     assert s[2] > 0.5                                # the dev shift pushes time toward the noisy end
     assert flux_schedule(Variant.SCHNELL, 4, 512, 512) == [1.0, 0.75, 0.5, 0.25, 0.0]
+
+
+def test_flux_with_t5_and_clip_text_encoders(tmp_path):
+    """The full pipeline with real (tiny, random) T5 + CLIP encoders and tokenizer files."""
+    from inference_b200.media.text_models import ClipBpeTokenizer, T5ClipEncoders
+
+    snap = write_synthetic_snapshot(tmp_path / "flux_te", Variant.SCHNELL, text="t5_clip")
+    tok = ClipBpeTokenizer.from_dir(snap / "tokenizer", 24)
+    ids = tok.encode("A  Fox, a cat")
+    assert len(ids) == 24 and ids[0] == tok.bos and ids[-1] == tok.eos
+    assert tok.vocab["fox</w>"] in ids and tok.vocab["cat</w>"] in ids            # merges applied, lower-cased
+    enc = T5ClipEncoders.from_snapshot(snap, "cpu", "cpu")
+    a, b = enc.encode("a fox", 32), enc.encode("a dog", 32)
+    assert a.txt.shape == (1, 32, 64) and a.pooled.shape == (1, 32)
+    assert not torch.allclose(a.txt, b.txt) and not torch.allclose(a.pooled, b.pooled)
+    g = provider_registry("cpu").load("cpu_flux1_schnell", LoadSpec.from_dir(snap))
+    req = dict(width=256, height=256, steps=1, seed=4)
+    x = g.generate(GenerationRequest(prompt="a fox", **req), lambda e: None)
+    y = g.generate(GenerationRequest(prompt="a fox", **req), lambda e: None)
+    z = g.generate(GenerationRequest(prompt="a big red dog", **req), lambda e: None)
+    assert x.images[0].pixels == y.images[0].pixels and x.images[0].pixels != z.images[0].pixels
+    fp = provider_registry("cpu").footprint("cpu_flux1_schnell", LoadSpec.from_dir(snap))
+    assert fp.components["text_encoder"] > 0 and fp.components["text_encoder_2"] > 0
