@@ -112,6 +112,7 @@ class FluxPipeline:
         self.dit_cfg = FluxConfig(guidance_embed=variant.supports_guidance)
         self.vae_cfg = VaeConfig()
         self.text_kind = "t5_clip"
+        self.random_init = None
         cfg_path = self.root / "swb_config.json"
         if cfg_path.exists():
             raw = json.loads(cfg_path.read_text())
@@ -126,6 +127,7 @@ class FluxPipeline:
                     v["ch_mult"] = tuple(v["ch_mult"])
                 self.vae_cfg = VaeConfig(**v)
             self.text_kind = raw.get("text", self.text_kind)
+            self.random_init = raw.get("random_init")      # seed: build random weights on the device, read no files
         self.dtype = torch.bfloat16 if backend == "b200" else torch.float32
 
     # ---- loaders -------------------------------------------------------------------------------------
@@ -139,6 +141,13 @@ class FluxPipeline:
     def load_heavy(self) -> _Heavy:
         from ..io.safetensors_io import load_file
 
+        if self.random_init is not None and self.backend == "b200":
+            from ..models.dit_flux import FluxDiTGpu
+            from ..models.vae import VaeDecoderGpu
+
+            seed = int(self.random_init)
+            return _Heavy(FluxDiTGpu(self.dit_cfg, device=self.device).init_random(seed),
+                          VaeDecoderGpu(self.vae_cfg, self.device).init_random(seed + 1), self.device, self.dtype)
         tf = self.root / self.variant.transformer_file
         ae = self.root / "ae.safetensors"
         for p in (tf, ae):
@@ -191,7 +200,7 @@ class FluxPipeline:
                     raise Canceled(f"{v.model_id}: cancelled at step {state['step']}")
                 tt = torch.full((1,), float(t), device=dev)
                 if self.backend == "b200":
-                    out = heavy.dit.forward(x_in, img_ids, txt, txt_ids, tt, pooled, gvec, rope=rope)
+                    out = heavy.dit.forward_graphed(x_in, img_ids, txt, txt_ids, tt, pooled, gvec, rope=rope)
                 else:
                     out = heavy.dit.forward(x_in, img_ids, txt, txt_ids, tt, pooled, gvec)
                 state["step"] += 1
