@@ -112,6 +112,13 @@ def attach_fused(comm: Communicator, hidden: int | None = None, max_tokens: int 
     otherwise leave the NCCL baseline in place (health = degraded). SWB_COMM=nccl forces the baseline."""
     if not comm.is_parallel or comm.backend != "nccl" or os.environ.get("SWB_COMM", "auto") == "nccl":
         return False
+    from .health import FaultPlan
+
+    if FaultPlan.from_env().denies("peer"):      # test seam: behave as if peer access were unavailable
+        comm.fused = None
+        comm.health = "degraded"
+        comm.fused_error = "peer access denied by the fault plan"  # type: ignore[attr-defined]
+        return False
     if hidden is None:
         comm._fused_pending = max_tokens  # type: ignore[attr-defined]  (created lazily by the model with its width)
         return True
