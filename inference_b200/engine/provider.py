@@ -54,8 +54,8 @@ def _read_json(p: Path) -> dict:
 
 
 def _supported_on_gpu(cfg: ModelConfig) -> bool:
-    return (cfg.head_dim == 128 and cfg.moe is None and cfg.mla is None and
-            cfg.architecture not in (Architecture.QWEN35, Architecture.DEEPSEEK_V2, Architecture.QWEN2_MOE))
+    return (cfg.head_dim == 128 and cfg.mla is None and
+            cfg.architecture not in (Architecture.QWEN35, Architecture.DEEPSEEK_V2))
 
 
 def probe_config(spec: LoadSpec) -> ModelConfig | None:

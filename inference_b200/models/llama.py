@@ -50,6 +50,19 @@ class LayerWeights:
     gate_up: torch.Tensor
     down: torch.Tensor
     post_mlp_ln: torch.Tensor | None    # sandwich: norm of the MLP output
+    moe: "MoeWeights | None" = None     # sparse FFN (then gate_up / down are unused)
+
+
+@dataclass
+class MoeWeights:
+    """Top-k routed experts with an optional (sigmoid-gated) shared expert (Qwen2-MoE: candle-llm models/llama.rs
+    MoE FFN). Expert FFNs are sharded like the dense one: gate/up by rows, down by columns."""
+    router: torch.Tensor                      # [E, H], replicated
+    gate_up: list[torch.Tensor]               # E x [2 * F_local, H]
+    down: list[torch.Tensor]                  # E x [H, F_local]
+    shared_gate_up: torch.Tensor | None
+    shared_down: torch.Tensor | None
+    shared_gate: torch.Tensor | None          # [1, H]
 
 
 def _shard_rows(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
@@ -64,7 +77,7 @@ def _shard_cols(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
 
 class LlamaGpu:
     def __init__(self, cfg: ModelConfig, comm: Communicator | None = None, device: torch.device | None = None):
-        if cfg.mla is not None or cfg.moe is not None or cfg.architecture is Architecture.QWEN35:
+        if cfg.mla is not None or cfg.architecture is Architecture.QWEN35:
             raise Unsupported(f"{cfg.architecture.value}: served by the fp32 oracle path, not the sm_100a decoder")
         if cfg.head_dim != 128:
             raise Unsupported("the sm_100a attention kernels are built for head_dim 128")
@@ -130,8 +143,28 @@ class LlamaGpu:
             qkv_bias = None
             if f"{p}.self_attn.q_proj.bias" in w:
                 qkv_bias = dev16(torch.cat([_shard_rows(get(f"{p}.self_attn.{n}_proj.bias"), r, P) for n in "qkv"]))
-            gate = _shard_rows(get(f"{p}.mlp.gate_proj.weight"), r, P)
-            up = _shard_rows(get(f"{p}.mlp.up_proj.weight"), r, P)
+            moe = None
+            if f"{p}.mlp.gate.weight" in w:
+                E = cfg.moe.num_experts
+
+                def gu(prefix):
+                    return dev16(torch.cat([_shard_rows(get(f"{prefix}.gate_proj.weight"), r, P),
+                                            _shard_rows(get(f"{prefix}.up_proj.weight"), r, P)]))
+                has_shared = f"{p}.mlp.shared_expert.gate_proj.weight" in w
+                sg = w.get(f"{p}.mlp.shared_expert_gate.weight")
+                moe = MoeWeights(
+                    router=dev16(get(f"{p}.mlp.gate.weight")),
+                    gate_up=[gu(f"{p}.mlp.experts.{e}") for e in range(E)],
+                    down=[dev16(_shard_cols(get(f"{p}.mlp.experts.{e}.down_proj.weight"), r, P)) for e in range(E)],
+                    shared_gate_up=gu(f"{p}.mlp.shared_expert") if has_shared else None,
+                    shared_down=dev16(_shard_cols(get(f"{p}.mlp.shared_expert.down_proj.weight"), r, P))
+                    if has_shared else None,
+                    shared_gate=dev16(torch.cat([sg, torch.zeros(7, sg.shape[1])])) if sg is not None else None)
+                gate = up = torch.zeros(8, cfg.hidden_size)
+                w[f"{p}.mlp.down_proj.weight"] = torch.zeros(cfg.hidden_size, 8 * P)
+            else:
+                gate = _shard_rows(get(f"{p}.mlp.gate_proj.weight"), r, P)
+                up = _shard_rows(get(f"{p}.mlp.up_proj.weight"), r, P)
             arch = cfg.architecture
             if arch is Architecture.GEMMA2:
                 post_attn, ln2, post_mlp = (get(f"{p}.post_attention_layernorm.weight"),
@@ -151,7 +184,7 @@ class LlamaGpu:
                 o=dev16(_shard_cols(get(f"{p}.self_attn.o_proj.weight"), r, P)),
                 post_attn_ln=dev16(post_attn) if post_attn is not None else None, ln2=dev16(ln2),
                 gate_up=dev16(torch.cat([gate, up])), down=dev16(_shard_cols(get(f"{p}.mlp.down_proj.weight"), r, P)),
-                post_mlp_ln=dev16(post_mlp) if post_mlp is not None else None))
+                post_mlp_ln=dev16(post_mlp) if post_mlp is not None else None, moe=moe))
         assert D == 128
         return self
 
@@ -259,6 +292,11 @@ class LlamaGpu:
                     branch = ops.rmsnorm(branch, L.post_attn_ln, eps, w_offset=woff)
                     n += 1
                 h = ops.rmsnorm(branch, L.ln2, eps, residual=res, w_offset=woff)
+            if L.moe is not None:
+                pending_h = None
+                branch = self.comm.all_reduce(self._moe_ffn(h, L.moe))
+                n += 9 if inp.attn_splits == 1 or not inp.decode else 10
+                continue
             gu = ops.linear_any(h, L.gate_up)
             act = ops.gated_act_mul(gu, cfg.mlp_activation)
             if fused is not None and L.post_mlp_ln is None:
@@ -282,6 +320,37 @@ class LlamaGpu:
             return final.index_select(0, inp.logits_rows)
         return final
 
+    def _moe_ffn(self, h: torch.Tensor, m: MoeWeights) -> torch.Tensor:
+        """Sparse FFN on this rank's shard (partial sums; the caller all-reduces). The routing is data dependent
+        (experts are visited by a host loop over those that received tokens), so models with MoE layers decode
+        eagerly instead of replaying a CUDA graph."""
+        moe = self.cfg.moe
+        act = self.cfg.mlp_activation
+        logits = ops.gemm_bf16(h, m.router, out_dtype=torch.float32)
+        probs = torch.softmax(logits, dim=-1)
+        topv, topi = probs.topk(moe.num_experts_per_tok, dim=-1)
+        if moe.norm_topk_prob:
+            topv = topv / topv.sum(-1, keepdim=True)
+        topv = topv * moe.routed_scaling_factor
+        out = torch.zeros(h.shape, dtype=torch.float32, device=h.device)
+        for e in torch.unique(topi).tolist():
+            sel = topi == e
+            rows = sel.any(-1).nonzero().flatten()
+            wgt = (topv * sel).sum(-1).index_select(0, rows)
+            x = h.index_select(0, rows)
+            y = ops.gemm_bf16(ops.gated_act_mul(ops.gemm_bf16(x, m.gate_up[e]), act), m.down[e])
+            out.index_add_(0, rows, y.float() * wgt[:, None])
+        if m.shared_gate_up is not None:
+            y = ops.gemm_bf16(ops.gated_act_mul(ops.gemm_bf16(h, m.shared_gate_up), act), m.shared_down).float()
+            if m.shared_gate is not None:
+                y = y * torch.sigmoid(ops.gemm_bf16(h, m.shared_gate, out_dtype=torch.float32)[:, :1])
+            out += y
+        return out.to(torch.bfloat16)
+
+    @property
+    def has_moe(self) -> bool:
+        return any(L.moe is not None for L in self.layers)
+
     # ---- prefill with fused reduce-scatter / all-gather -----------------------------------------------------
     def _use_tp_prefill(self, T: int) -> bool:
         import os
@@ -291,7 +360,7 @@ class LlamaGpu:
             return False
         if self.quant_format is not None:
             return False
-        if any(L.post_attn_ln is not None or L.post_mlp_ln is not None for L in self.layers):
+        if any(L.post_attn_ln is not None or L.post_mlp_ln is not None or L.moe is not None for L in self.layers):
             return False
         return T <= self.tp_prefill_max_tokens
 
