@@ -10,4 +10,7 @@ def provider_registry(backend: str = "b200") -> ProviderRegistry:
 
     b = ProviderRegistryBuilder()
     b.register_generators(flux.registrations(backend))
+    from .train import trainer_registration
+
+    b.register("trainer", trainer_registration(backend))
     return b.build()

@@ -1,0 +1,226 @@
+"""LoRA adapter training for flow-matching DiTs and adapter merging at load time (the role of
+candle-gen/src/train/flow_match.rs:296-680 and train/lora.rs: cached latents + text embeddings, frozen DiT with
+low-rank adapters on the attention / MLP projections, logit-normal timestep sampling, x_t = (1 - t) x0 + t eps,
+target velocity eps - x0, AdamW with gradient accumulation and clipping, periodic checkpoints with resume, PEFT-style
+adapter files).
+
+Training differentiates through the plain-PyTorch model (`OracleFluxDiT.forward_grad`) on whatever device its weights
+live on; it is outside the serving hot path. Dataset: a directory of `*.safetensors` items with `latent`
+[16, h, w] (already scaled VAE latents), `txt` [L, context_dim] and `pooled` [vec_dim]."""
+from __future__ import annotations
+
+import json
+import math
+from pathlib import Path
+from typing import Callable
+
+import torch
+
+from ..contracts.errors import Canceled, InferenceError, LoadError
+from ..contracts.gen_core.traits import SimpleDescriptor, Trainer, TrainingConfig, TrainingProgress
+from ..io.safetensors_io import load_file, save_file
+from ..models.dit_flux import FluxConfig, OracleFluxDiT, make_ids
+from .flux import patchify
+
+TARGET_SUFFIXES = ("img_attn.qkv", "img_attn.proj", "txt_attn.qkv", "txt_attn.proj", "linear1", "linear2")
+
+
+def lr_at(schedule: str, step: int, total: int, warmup: int, base: float) -> float:
+    """constant | linear | cosine, each with linear warm-up (gen-core/src/train/schedule.rs:12-59)."""
+    if warmup > 0 and step < warmup:
+        return base * (step + 1) / warmup
+    if schedule == "constant":
+        return base
+    frac = (step - warmup) / max(1, total - warmup)
+    if schedule == "linear":
+        return base * max(0.0, 1.0 - frac)
+    if schedule == "cosine":
+        return base * 0.5 * (1.0 + math.cos(math.pi * min(1.0, frac)))
+    raise InferenceError(f"unknown lr_schedule {schedule!r} (constant | linear | cosine)")
+
+
+def lora_targets(weights: dict[str, torch.Tensor]) -> list[str]:
+    names = sorted({k[: -len(".weight")] for k in weights if k.endswith(".weight") and weights[k].dim() == 2})
+    return [n for n in names if n.endswith(TARGET_SUFFIXES)]
+
+
+def merge_lora(weights: dict[str, torch.Tensor], adapter: dict[str, torch.Tensor], scale: float = 1.0,
+               prefix: str = "transformer.") -> dict[str, torch.Tensor]:
+    """W += scale * (alpha / r) * B A for every `<prefix><module>.lora_A.weight` / `.lora_B.weight` pair; a per-module
+    `<module>.alpha` scalar (kohya style) overrides alpha = r."""
+    out = dict(weights)
+    mods = sorted({k[len(prefix): -len(".lora_A.weight")] for k in adapter if k.startswith(prefix) and
+                   k.endswith(".lora_A.weight")})
+    for m in mods:
+        a, b = adapter[f"{prefix}{m}.lora_A.weight"].float(), adapter[f"{prefix}{m}.lora_B.weight"].float()
+        key = m + ".weight"
+        if key not in out:
+            raise LoadError(f"adapter targets '{m}', which the model does not have")
+        r = a.shape[0]
+        alpha = float(adapter[f"{prefix}{m}.alpha"]) if f"{prefix}{m}.alpha" in adapter else float(r)
+        w = out[key]
+        out[key] = (w.float() + (b @ a) * (scale * alpha / r)).to(w.dtype)
+    return out
+
+
+class FluxLoraTrainer(Trainer):
+    def __init__(self, cfg: FluxConfig, weights: dict[str, torch.Tensor], backend: str = "cpu", device="cpu"):
+        self.cfg, self.backend, self.device = cfg, backend, torch.device(device)
+        self.model = OracleFluxDiT(cfg, weights, dtype=torch.float32, device=self.device)
+        for t in self.model.w.values():
+            t.requires_grad_(False)
+
+    def descriptor(self) -> SimpleDescriptor:
+        return SimpleDescriptor("flux1_lora_trainer" if self.backend != "cpu" else "cpu_flux1_lora_trainer", "flux",
+                                self.backend, {"adapters": ["lora"], "targets": list(TARGET_SUFFIXES)})
+
+    def validate(self, c: TrainingConfig) -> None:
+        if c.adapter != "lora":
+            raise InferenceError(f"adapter kind {c.adapter!r} is not supported (lora)")
+        if c.dataset_dir is None or not Path(c.dataset_dir).is_dir():
+            raise InferenceError("dataset_dir must be an existing directory of cached items")
+        if c.output_dir is None:
+            raise InferenceError("output_dir is required")
+        if c.steps < 1 or c.rank < 1 or c.batch_size != 1 or c.grad_accum < 1 or c.learning_rate <= 0:
+            raise InferenceError("steps, rank, grad_accum must be >= 1, batch_size == 1, learning_rate > 0")
+        lr_at(c.lr_schedule, 0, c.steps, c.warmup_steps, c.learning_rate)
+
+    # ---- pieces ------------------------------------------------------------------------------------------
+    def _items(self, d: Path) -> list[dict[str, torch.Tensor]]:
+        files = sorted(Path(d).glob("*.safetensors"))
+        if not files:
+            raise InferenceError(f"{d}: no dataset items (*.safetensors with latent / txt / pooled)")
+        items = []
+        for f in files:
+            t = load_file(f)
+            if not {"latent", "txt", "pooled"} <= set(t):
+                raise InferenceError(f"{f}: needs tensors latent, txt, pooled")
+            items.append({k: v.float().to(self.device) for k, v in t.items()})
+        return items
+
+    def _init_adapters(self, rank: int, gen: torch.Generator) -> dict[str, list[torch.Tensor]]:
+        ad = {}
+        for name in lora_targets(self.model.w):
+            w = self.model.w[name + ".weight"]
+            a = (torch.randn(rank, w.shape[1], generator=gen) / math.sqrt(w.shape[1])).to(self.device).requires_grad_()
+            b = torch.zeros(w.shape[0], rank, device=self.device, requires_grad=True)
+            ad[name] = [a, b]
+        return ad
+
+    def loss_on(self, item, t: float, noise: torch.Tensor) -> torch.Tensor:
+        """Flow-matching loss of one item at time t with the given noise: || v_theta(x_t, t) - (eps - x0) ||^2."""
+        x0 = patchify(item["latent"][None])
+        eps = patchify(noise[None])
+        xt = (1.0 - t) * x0 + t * eps
+        lh, lw = item["latent"].shape[1] // 2, item["latent"].shape[2] // 2
+        txt_ids, img_ids = make_ids(lh, lw, item["txt"].shape[0], self.device)
+        g = torch.full((1,), 3.5, device=self.device) if self.cfg.guidance_embed else None
+        v = self.model.forward_grad(xt, img_ids, item["txt"][None], txt_ids, torch.full((1,), t, device=self.device),
+                                    item["pooled"][None], g)
+        return torch.mean((v - (eps - x0)) ** 2)
+
+    # ---- contract ------------------------------------------------------------------------------------------
+    def train(self, c: TrainingConfig, on_progress: Callable[[TrainingProgress], None] = lambda p: None) -> Path:
+        self.validate(c)
+        out_dir = Path(c.output_dir)
+        out_dir.mkdir(parents=True, exist_ok=True)
+        items = self._items(Path(c.dataset_dir))
+        gen = torch.Generator().manual_seed(c.seed)
+        adapters = self._init_adapters(c.rank, gen)
+        params = [p for ab in adapters.values() for p in ab]
+        opt = torch.optim.AdamW(params, lr=c.learning_rate, weight_decay=0.0)
+        start = 0
+        if c.resume is not None:
+            start = self._load_checkpoint(Path(c.resume), adapters, opt, gen)
+        scale = c.alpha / c.rank
+        self.model.lora = {n: (a, b, scale) for n, (a, b) in adapters.items()}
+        last = None
+        try:
+            for step in range(start, c.steps):
+                if c.cancel.is_cancelled():
+                    raise Canceled(f"training cancelled at step {step}")
+                lr = lr_at(c.lr_schedule, step, c.steps, c.warmup_steps, c.learning_rate)
+                for gparam in opt.param_groups:
+                    gparam["lr"] = lr
+                opt.zero_grad(set_to_none=True)
+                total = 0.0
+                for micro in range(c.grad_accum):
+                    item = items[(step * c.grad_accum + micro) % len(items)]
+                    u = torch.randn(1, generator=gen).item()
+                    t = 1.0 / (1.0 + math.exp(-u))                      # logit-normal(0, 1)
+                    noise = torch.randn(item["latent"].shape, generator=gen).to(self.device)
+                    loss = self.loss_on(item, t, noise) / c.grad_accum
+                    loss.backward()
+                    total += float(loss.detach())
+                torch.nn.utils.clip_grad_norm_(params, 1.0)
+                opt.step()
+                ck = None
+                if c.save_every and (step + 1) % c.save_every == 0 and step + 1 < c.steps:
+                    ck = self._save(out_dir / f"adapter-step{step + 1:06d}.safetensors", adapters, c, step + 1, opt, gen)
+                on_progress(TrainingProgress(step + 1, c.steps, total, lr, ck))
+            last = self._save(out_dir / "adapter.safetensors", adapters, c, c.steps, opt, gen)
+        finally:
+            self.model.lora = None
+        return last
+
+    # ---- checkpoints ---------------------------------------------------------------------------------------
+    def _save(self, path: Path, adapters, c: TrainingConfig, step: int, opt, gen) -> Path:
+        t = {}
+        for n, (a, b) in adapters.items():
+            t[f"transformer.{n}.lora_A.weight"] = a.detach().cpu().contiguous()
+            t[f"transformer.{n}.lora_B.weight"] = b.detach().cpu().contiguous()
+        save_file(t, path, metadata={"format": "peft-lora", "rank": str(c.rank), "alpha": str(c.alpha),
+                                     "step": str(step), "base": "flux"})
+        state = {"rng": gen.get_state()}
+        for i, p in enumerate(opt.param_groups[0]["params"]):
+            st = opt.state.get(p, {})
+            if st:
+                state[f"exp_avg.{i}"] = st["exp_avg"].detach().cpu().contiguous()
+                state[f"exp_avg_sq.{i}"] = st["exp_avg_sq"].detach().cpu().contiguous()
+                state[f"step.{i}"] = st["step"].detach().cpu().reshape(1).float() if torch.is_tensor(st["step"]) \
+                    else torch.tensor([float(st["step"])])
+        save_file(state, path.with_suffix(".state.safetensors"), metadata={"step": str(step)})
+        return path
+
+    def _load_checkpoint(self, path: Path, adapters, opt, gen) -> int:
+        from ..io.safetensors_io import SafetensorsFile
+
+        if not path.is_file():
+            raise LoadError(f"resume checkpoint {path} not found")
+        t = load_file(path)
+        for n, (a, b) in adapters.items():
+            a.data.copy_(t[f"transformer.{n}.lora_A.weight"])
+            b.data.copy_(t[f"transformer.{n}.lora_B.weight"])
+        sp = path.with_suffix(".state.safetensors")
+        f = SafetensorsFile(sp)
+        step = int(f.metadata.get("step", "0")) if hasattr(f, "metadata") else 0
+        f.close()
+        st = load_file(sp)
+        gen.set_state(st["rng"].to(torch.uint8))
+        for i, p in enumerate(opt.param_groups[0]["params"]):
+            if f"exp_avg.{i}" in st:
+                opt.state[p] = {"exp_avg": st[f"exp_avg.{i}"].to(p.device), "exp_avg_sq": st[f"exp_avg_sq.{i}"].to(p.device),
+                                "step": st[f"step.{i}"].reshape(()).to(torch.float32)}
+        return step
+
+
+def trainer_registration(backend: str):
+    """`flux1_lora_trainer` (kind "trainer"): loads the DiT of a FLUX snapshot directory and trains adapters on it."""
+    from ..contracts.gen_core.registry import Registration
+    from ..contracts.gen_core.runtime import LoadSpec
+
+    tid = "flux1_lora_trainer" if backend != "cpu" else "cpu_flux1_lora_trainer"
+
+    def load(spec: LoadSpec) -> FluxLoraTrainer:
+        from .flux import FluxPipeline, Variant
+
+        if spec.weights is None or spec.weights.is_file:
+            raise InferenceError(f"{tid}: needs a snapshot directory")
+        device = torch.device("cuda", torch.cuda.current_device()) if backend != "cpu" else torch.device("cpu")
+        pipe = FluxPipeline(Variant.DEV, Path(spec.weights.path), "cpu", device)
+        f = Path(spec.weights.path) / Variant.DEV.transformer_file
+        if not f.is_file():
+            raise LoadError(f"{tid}: missing {f}")
+        return FluxLoraTrainer(pipe.dit_cfg, load_file(f), backend, device)
+
+    return Registration(descriptor=lambda: SimpleDescriptor(tid, "flux", backend, {"adapters": ["lora"]}), load=load)

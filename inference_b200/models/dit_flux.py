@@ -124,8 +124,14 @@ class OracleFluxDiT:
         self.cfg = cfg
         self.w = {k: v.to(device=device, dtype=dtype) for k, v in weights.items()}
 
+    lora: dict | None = None     # {module name: (A [r, in], B [out, r], scale)}: low-rank deltas added on the fly
+
     def _lin(self, x, name):
-        return F.linear(x, self.w[name + ".weight"], self.w[name + ".bias"])
+        y = F.linear(x, self.w[name + ".weight"], self.w[name + ".bias"])
+        if self.lora is not None and name in self.lora:
+            a, b, scale = self.lora[name]
+            y = y + F.linear(F.linear(x, a), b) * scale
+        return y
 
     def _mlp_embed(self, x, name):
         return self._lin(F.silu(self._lin(x, name + ".in_layer")), name + ".out_layer")
@@ -156,6 +162,10 @@ class OracleFluxDiT:
 
     @torch.no_grad()
     def forward(self, img, img_ids, txt, txt_ids, timesteps, y, guidance=None):
+        return self.forward_grad(img, img_ids, txt, txt_ids, timesteps, y, guidance)
+
+    def forward_grad(self, img, img_ids, txt, txt_ids, timesteps, y, guidance=None):
+        """The same computation with autograd enabled (adapter training differentiates through it)."""
         cfg = self.cfg
         Hs = cfg.hidden_size
         cos, sin = rope_table(torch.cat([txt_ids, img_ids], 0), cfg.axes_dim, cfg.theta)
