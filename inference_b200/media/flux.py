@@ -24,7 +24,7 @@ from ..contracts.gen_core.generator import (Capabilities, GenerationOutput, Gene
 from ..contracts.gen_core.media import Image
 from ..contracts.gen_core.registry import PerComponentBytes, Registration
 from ..contracts.gen_core.traits import reject_unknown_components
-from ..contracts.gen_core.runtime import LoadSpec, OffloadPolicy, ProgressDecoding, ProgressStep
+from ..contracts.gen_core.runtime import AdapterKind, LoadSpec, OffloadPolicy, ProgressDecoding, ProgressStep
 from ..contracts.gen_core.sampling import (SCHEDULERS, SOLVERS, FlowModelSampling, TorchLatentOps, build_flow_sigmas,
                                            compute_mu, denoise, get_solver, image_seq_len, schedule_sigmas)
 from ..models.dit_flux import FluxConfig, OracleFluxDiT, make_ids, rope_table
@@ -71,7 +71,7 @@ def flux_descriptor(variant: Variant, backend: str, prefix: str = "") -> ModelDe
         id=prefix + variant.model_id, family="flux", backend=backend, modality=Modality.IMAGE,
         capabilities=Capabilities(
             supports_negative_prompt=False, supports_guidance=variant.supports_guidance, supports_true_cfg=False,
-            conditioning=[], supports_lora=False, supports_lokr=False, samplers=list(SOLVERS),
+            conditioning=[], supports_lora=True, supports_lokr=False, samplers=list(SOLVERS),
             schedulers=list(SCHEDULERS), supported_guidance_methods=[], min_size=256, max_size=2048, max_count=8,
             supports_sequential_offload=True),
         required_components=[])
@@ -113,6 +113,7 @@ class FluxPipeline:
         self.vae_cfg = VaeConfig()
         self.text_kind = "t5_clip"
         self.random_init = None
+        self.adapters: list = []
         cfg_path = self.root / "swb_config.json"
         if cfg_path.exists():
             raw = json.loads(cfg_path.read_text())
@@ -154,6 +155,12 @@ class FluxPipeline:
             if not p.exists():
                 raise LoadError(f"{self.variant.model_id}: missing weight file {p}")
         dit_w, vae_w = load_file(tf), load_file(ae)
+        for ad in self.adapters:                         # low-rank adapters are merged into the weights at load
+            from .train import merge_lora
+
+            if not Path(ad.path).is_file():
+                raise LoadError(f"{self.variant.model_id}: adapter file {ad.path} not found")
+            dit_w = merge_lora(dit_w, load_file(ad.path), ad.scale if ad.scale is not None else 1.0)
         if self.backend == "b200":
             from ..models.dit_flux import FluxDiTGpu
             from ..models.vae import VaeDecoderGpu
@@ -262,8 +269,11 @@ def _load(variant: Variant, backend: str, prefix: str) -> Callable[[LoadSpec], F
         if spec.quantize is not None:
             raise Unsupported(f"{mid}: quantised loading ({spec.quantize.name}) is not supported")
         reject_unknown_components(spec.components, [], mid)
-        if spec.adapters or spec.control or spec.extra_controls or spec.ip_adapter:
-            raise Unsupported(f"{mid}: adapters / control branches are not supported by this provider")
+        if spec.control or spec.extra_controls or spec.ip_adapter:
+            raise Unsupported(f"{mid}: control branches / IP adapters are not supported by this provider")
+        for ad in spec.adapters:
+            if ad.kind is not AdapterKind.LORA:
+                raise Unsupported(f"{mid}: adapter kind {ad.kind.value} is not supported (lora)")
         if backend == "b200":
             if not torch.cuda.is_available():
                 raise LoadError(f"{mid}: no CUDA device")
@@ -271,6 +281,7 @@ def _load(variant: Variant, backend: str, prefix: str) -> Callable[[LoadSpec], F
         else:
             device = torch.device("cpu")
         pipe = FluxPipeline(variant, Path(spec.weights.path), backend, device)    # lazy: paths only
+        pipe.adapters = list(spec.adapters)
         return FluxGenerator(variant, pipe, flux_descriptor(variant, backend, prefix), spec.offload_policy)
     return load
 

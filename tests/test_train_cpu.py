@@ -79,3 +79,34 @@ def test_validation_and_cancellation(dataset, tmp_path):
     with pytest.raises(Canceled):
         tr.train(cfg, cancel_after_one)
     assert tr.model.lora is None
+
+
+def test_adapter_is_applied_by_the_generator(tmp_path):
+    """An adapter file named in LoadSpec.adapters changes the generated image; scale 0 leaves it unchanged."""
+    from inference_b200.contracts.gen_core import AdapterKind, AdapterSpec, GenerationRequest, LoadSpec, WeightsSource
+    from inference_b200.media import provider_registry
+    from inference_b200.media.flux import Variant, write_synthetic_snapshot
+
+    snap = write_synthetic_snapshot(tmp_path / "snap", Variant.SCHNELL)
+    base_w = load_file(snap / Variant.SCHNELL.transformer_file)
+    g = torch.Generator().manual_seed(0)
+    ad = {}
+    for name in lora_targets(base_w)[:3]:
+        w = base_w[name + ".weight"]
+        ad[f"transformer.{name}.lora_A.weight"] = torch.randn(4, w.shape[1], generator=g) * 0.3
+        ad[f"transformer.{name}.lora_B.weight"] = torch.randn(w.shape[0], 4, generator=g) * 0.3
+    save_file(ad, tmp_path / "ad.safetensors")
+    reg = provider_registry("cpu")
+    req = lambda: GenerationRequest(prompt="a fox", width=256, height=256, steps=1, seed=2)   # noqa: E731
+
+    def run(scale):
+        spec = LoadSpec(weights=WeightsSource.dir(snap),
+                        adapters=[] if scale is None else [AdapterSpec(path=tmp_path / "ad.safetensors", scale=scale,
+                                                                       kind=AdapterKind.LORA)])
+        return reg.load("cpu_flux1_schnell", spec).generate(req(), lambda e: None).images[0].pixels
+    plain = run(None)
+    assert run(0.0) == plain and run(1.0) != plain
+    with pytest.raises(InferenceError):
+        bad = LoadSpec(weights=WeightsSource.dir(snap), adapters=[AdapterSpec(path=tmp_path / "nope.safetensors", scale=1.0,
+                                                                              kind=AdapterKind.LORA)])
+        reg.load("cpu_flux1_schnell", bad).generate(req(), lambda e: None)
