@@ -237,7 +237,48 @@ class FluxDiTGpu:
             W, b = self.w.pop(p + ".weight"), self.w.pop(p + ".bias")
             self.w[p + "_qkv.weight"], self.w[p + "_mlp.weight"] = W[: 3 * H].contiguous(), W[3 * H:].contiguous()
             self.w[p + "_qkv.bias"], self.w[p + "_mlp.bias"] = b[: 3 * H].contiguous(), b[3 * H:].contiguous()
+        self._build_modulation_table()
         return self
+
+    def _mod_names(self) -> list[str]:
+        names = []
+        for i in range(self.cfg.depth):
+            names += [f"double_blocks.{i}.img_mod.lin", f"double_blocks.{i}.txt_mod.lin"]
+        names += [f"single_blocks.{i}.modulation.lin" for i in range(self.cfg.depth_single)]
+        return names + ["final_layer.adaLN_modulation.1"]
+
+    def _build_modulation_table(self) -> None:
+        """Every adaLN modulation is a linear map of the same conditioning vector, so all of them (344 x hidden output
+        rows for FLUX.1) are one GEMM per step. The per-block weights become views into the concatenated matrix; with
+        a parallel communicator each rank computes a contiguous share of the rows and the shares are all-gathered."""
+        names = self._mod_names()
+        sizes = [self.w[n + ".weight"].shape[0] for n in names]
+        total = sum(sizes)
+        P = self.comm.world
+        pad = (-total) % (8 * P)
+        big_w = torch.empty((total + pad, self.cfg.hidden_size), dtype=torch.bfloat16, device=self.device)
+        big_b = torch.zeros(total + pad, dtype=torch.bfloat16, device=self.device)
+        off = 0
+        self._mod_slices = {}
+        for n, sz in zip(names, sizes):
+            big_w[off:off + sz].copy_(self.w.pop(n + ".weight"))
+            big_b[off:off + sz].copy_(self.w.pop(n + ".bias"))
+            self.w[n + ".weight"], self.w[n + ".bias"] = big_w[off:off + sz], big_b[off:off + sz]
+            self._mod_slices[n] = (off, sz)
+            off += sz
+        if pad:
+            big_w[total:].zero_()
+        self._mod_w, self._mod_b = big_w, big_b
+
+    def _all_modulations(self, sv: torch.Tensor) -> dict[str, torch.Tensor]:
+        """sv [B, H] -> {modulation name: [B, rows]} from one GEMM (plus an all-gather when parallel)."""
+        P, r = self.comm.world, self.comm.rank
+        n = self._mod_w.shape[0] // P
+        out = ops.gemm_bf16(sv, self._mod_w[r * n:(r + 1) * n], bias=self._mod_b[r * n:(r + 1) * n])
+        self.launches += 1
+        if P > 1:
+            out = self.comm.all_gather(out, dim=1)
+        return {name: out[:, off:off + sz] for name, (off, sz) in self._mod_slices.items()}
 
     def init_random(self, seed: int = 0, std: float = 0.02) -> "FluxDiTGpu":
         return self.load_state_dict(random_flux_weights(self.cfg, seed, std, torch.bfloat16, self.device))
@@ -279,6 +320,7 @@ class FluxDiTGpu:
         cos, sin = rope
         positions = torch.arange(S, dtype=torch.int32, device=dev).repeat(B)
         sv = self.conditioning_vector(timesteps, y, guidance)
+        mod = self._all_modulations(sv)
         x_img = self._lin(img.reshape(B * Si, -1), "img_in").view(B, Si, H)
         x_txt = self._lin(txt.reshape(B * St, -1), "txt_in").view(B, St, H)
         scale = D ** -0.5
@@ -298,7 +340,7 @@ class FluxDiTGpu:
         for i in range(cfg.depth):
             mods = {}
             for s in ("img", "txt"):
-                m = self._lin(sv, f"double_blocks.{i}.{s}_mod.lin")           # [B, 6H]
+                m = mod[f"double_blocks.{i}.{s}_mod.lin"]                      # [B, 6H]
                 mods[s] = [m[:, j * H:(j + 1) * H] for j in range(6)]
             for s, x, lo, n in (("txt", x_txt, 0, St), ("img", x_img, St, Si)):
                 xm = ops.layernorm_mod(x, scale=mods[s][1], shift=mods[s][0], rows_per_batch=n)
@@ -336,7 +378,7 @@ class FluxDiTGpu:
         buf2 = torch.empty((B, S, H + M), dtype=torch.bfloat16, device=dev)
         for i in range(cfg.depth_single):
             p = f"single_blocks.{i}"
-            m = self._lin(sv, p + ".modulation.lin")
+            m = mod[p + ".modulation.lin"]
             sh, sc, g = m[:, :H], m[:, H:2 * H], m[:, 2 * H:]
             xm = ops.layernorm_mod(x, scale=sc, shift=sh, rows_per_batch=S).view(B * S, H)
             self._lin(xm, p + ".linear1_qkv", out=qkv.view(B * S, 3 * H))
@@ -347,7 +389,7 @@ class FluxDiTGpu:
             x = ops.gated_residual(x, out, g, rows_per_batch=S)
             self.launches += 2
         x_img = x[:, St:].contiguous()
-        m = self._lin(sv, "final_layer.adaLN_modulation.1")
+        m = mod["final_layer.adaLN_modulation.1"]
         xm = ops.layernorm_mod(x_img, scale=m[:, H:], shift=m[:, :H], rows_per_batch=Si)
         self.launches += 1
         return self._lin(xm.view(B * Si, H), "final_layer.linear").view(B, Si, -1)
@@ -429,6 +471,7 @@ class FluxDiTGpu:
         S_l, Hl = St_l + Si_l, NH // P
         scale = D ** -0.5
         sv = self.conditioning_vector(timesteps, y, guidance)
+        mod = self._all_modulations(sv)
         x_txt = self._lin(txt[0, r * St_l:(r + 1) * St_l], "txt_in")          # [St_l, H]
         x_img = self._lin(img[0, r * Si_l:(r + 1) * Si_l], "img_in")          # [Si_l, H]
         positions = torch.arange(S, dtype=torch.int32, device=dev)
@@ -464,7 +507,7 @@ class FluxDiTGpu:
         for i in range(cfg.depth):
             mods, norms = {}, []
             for s in ("img", "txt"):
-                m = self._lin(sv, f"double_blocks.{i}.{s}_mod.lin")
+                m = mod[f"double_blocks.{i}.{s}_mod.lin"]
                 mods[s] = [m[:, j * H:(j + 1) * H] for j in range(6)]
             for s, x, lo_l, n_l, lo_g, n_g in (("txt", x_txt, 0, St_l, 0, St), ("img", x_img, St_l, Si_l, St, Si)):
                 xm = ops.layernorm_mod(x[None], scale=mods[s][1], shift=mods[s][0], rows_per_batch=n_l)[0]
@@ -492,7 +535,7 @@ class FluxDiTGpu:
         x = torch.cat([x_txt, x_img], 0).contiguous()                           # [S_l, H] local joint
         for i in range(cfg.depth_single):
             p = f"single_blocks.{i}"
-            m = self._lin(sv, p + ".modulation.lin")
+            m = mod[p + ".modulation.lin"]
             sh, sc, g = m[:, :H], m[:, H:2 * H], m[:, 2 * H:]
             xm = ops.layernorm_mod(x[None], scale=sc, shift=sh, rows_per_batch=S_l)[0]
             nw = (self.w[p + ".norm.query_norm.scale"], self.w[p + ".norm.key_norm.scale"])
@@ -507,7 +550,7 @@ class FluxDiTGpu:
             x = ops.gated_residual(x[None], out[None], g, rows_per_batch=S_l)[0]
             self.launches += 2
         x_img = x[St_l:].contiguous()
-        m = self._lin(sv, "final_layer.adaLN_modulation.1")
+        m = mod["final_layer.adaLN_modulation.1"]
         xm = ops.layernorm_mod(x_img[None], scale=m[:, H:], shift=m[:, :H], rows_per_batch=Si_l)[0]
         v_local = self._lin(xm, "final_layer.linear")                           # [Si_l, C]
         self.launches += 2
