@@ -26,8 +26,12 @@ def main():
     out = torch.empty(B, S, H * 128, device="cuda", dtype=torch.bfloat16)
     flops = 4.0 * B * H * S * S * 128
     res = {}
-    for name, legacy in (("tcgen05", False), ("mma_sync", True)):
+    from inference_b200._native import kernels
+
+    for name, legacy, tiles in (("tcgen05", False, 0), ("tcgen05_1tile", False, 1), ("tcgen05_2tile", False, 2),
+                                ("mma_sync", True, 0)):
         set_dense_impl(legacy)
+        kernels().swb_attn_dense_set_tiles(tiles)
 
         def run(i):
             t = qkv[i % copies]
@@ -44,6 +48,7 @@ def main():
         ms = e0.elapsed_time(e1) / args.iters
         res[name] = {"ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1)}
     set_dense_impl(False)
+    kernels().swb_attn_dense_set_tiles(0)
     ops.check_status()
     print(json.dumps({"shape": {"batch": B, "seq": S, "heads": H, "head_dim": 128}, **res}))
 

@@ -80,11 +80,17 @@ def main():
         assert img.shape == (1, args.size, args.size, 3)
     ops.check_status()
     comm.barrier()
+    phases = None
+    if os.environ.get("SWB_SP_TRACE") == "1" and comm.world > 1:
+        t = torch.full((1,), 0.5, device=dev)
+        model.forward(x, img_ids, txt, txt_ids, t, y, gd, rope=rope)     # eager, with phase events
+        phases = getattr(model, "sp_phase_ms", None)
+    comm.barrier()
     if comm.rank != 0:
         return
     import os as _os
     print(json.dumps({"n_gpus": comm.world, "sp_impl": _os.environ.get("SWB_SP", "fused") if comm.world > 1 else None,
-                      "metric": "flux_dit_ms_per_step", "cuda_graph": not args.eager, "ms_per_step": round(ms / args.steps, 3),
+                      "metric": "flux_dit_ms_per_step", "cuda_graph": not args.eager, "sp_phase_ms": phases, "ms_per_step": round(ms / args.steps, 3),
                       "s_per_image_dit_only": round(ms / 1e3, 3), "steps": args.steps, "size": args.size,
                       "tflop_per_step": round(tflop, 2), "achieved_tflops": round(tflop / (ms / args.steps) * 1e3, 1),
                       "launches_per_step": model.launches, "weights_gb": round(model.weight_bytes() / 1e9, 2), "vae_decode_ms": vae_ms,

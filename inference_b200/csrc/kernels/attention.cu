@@ -556,6 +556,8 @@ int swb_attn_dense_scatter(const void* q, long long q_stride_tok, int q_stride_h
 
 // 0: pick the tcgen05 kernel whenever it supports the problem; 1: always the mma.sync kernel (comparison runs).
 void swb_attn_dense_set_impl(int impl) { swb::g_dense_impl = impl; }
+// 0: pick the number of query tiles per CTA per problem; 1 / 2: fixed (comparison runs).
+void swb_attn_dense_set_tiles(int tiles) { swb::attn_dense_tcgen05_set_tiles(tiles); }
 
 // Dense attention over q/k/v laid out [batch * seq, heads, 128] (arbitrary element strides), uniform lengths.
 int swb_attn_dense(const void* q, long long q_stride_tok, int q_stride_head, const void* k, const void* v,

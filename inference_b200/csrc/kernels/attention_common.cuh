@@ -73,6 +73,7 @@ __device__ __forceinline__ float score_transform(float s, float scale, float sof
 }  // namespace attn
 
 // attention_tcgen05.cu
+void attn_dense_tcgen05_set_tiles(int tiles);
 int attn_dense_tcgen05_supported(const void* q, const void* k, const void* v, long long q_stride_tok, int q_stride_head,
                                  long long kv_stride_tok, int kv_stride_head, long long out_stride_tok, int D,
                                  int causal);

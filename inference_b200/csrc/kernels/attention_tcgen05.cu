@@ -59,6 +59,7 @@ struct FaParams {
   long long out_stride_tok;   // elements; token index = b * q_len + s
   int q_len, kv_len, Hq, Hkv;
   float scale_log2;
+  int tiles;   // query tiles per CTA: 2 (MMAs of one tile overlap the softmax of the other) or 1 (twice the CTAs)
 };
 
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* tmap, uint64_t* bar, int c0, int c1, int c2,
@@ -148,7 +149,7 @@ attn_dense_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Barriers* bars = reinterpret_cast<Barriers*>(smem + SMEM_BAR);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q_base = blockIdx.x * (2 * BM);
+  const int q_base = blockIdx.x * (p.tiles * BM);
   const int head = blockIdx.y, batch = blockIdx.z;
   const int kv_head = head / (p.Hq / p.Hkv);
   const int n_tiles = (p.kv_len + BN - 1) / BN;
@@ -189,8 +190,8 @@ attn_dense_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      mbar_arrive_expect_tx(&bars->q_full, 2 * TILE_BYTES);
-      for (int q = 0; q < 2; ++q)
+      mbar_arrive_expect_tx(&bars->q_full, p.tiles * TILE_BYTES);
+      for (int q = 0; q < p.tiles; ++q)
         for (int a = 0; a < 2; ++a)
           tma_load_4d(smem + SMEM_Q + q * TILE_BYTES + a * ATOM_BYTES, &tmap_q, &bars->q_full, a * 64, head,
                       q_base + q * BM, batch);
@@ -246,7 +247,7 @@ attn_dense_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       if (ok) {
         tc_fence_after_sync();
         issue_qk(0, 0);
-        issue_qk(1, 0);
+        if (p.tiles == 2) issue_qk(1, 0);
         umma_commit(&bars->k_empty[0]);
       }
       for (int j = 0; j < n_tiles && ok; ++j) {
@@ -254,7 +255,7 @@ attn_dense_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         const uint32_t ph = (j / KV_STAGES) & 1, phn = ((j + 1) / KV_STAGES) & 1;
         ok = mbar_wait(&bars->v_full[s], ph, abort_flag, 22);
         if (ok && j + 1 < n_tiles) ok = mbar_wait(&bars->k_full[sn], phn, abort_flag, 23);
-        for (int q = 0; q < 2 && ok; ++q) {
+        for (int q = 0; q < p.tiles && ok; ++q) {
           ok = mbar_wait(&bars->p_full[q], j & 1, abort_flag, 24 + q);
           if (!ok) break;
           tc_fence_after_sync();
@@ -262,10 +263,11 @@ attn_dense_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
           for (int k = 0; k < BN / 16; ++k)
             umma_f16_ts(tmem + col_o[q], tmem + col_s[q] + k * 8,
                         umma_desc_mnmajor_sw128(v_addr + s * TILE_BYTES + k * 2048), IDESC_PV, (j > 0) || (k > 0));
-          if (q == 1) umma_commit(&bars->v_empty[s]);
+          const bool last_q = (q == p.tiles - 1);
+          if (last_q) umma_commit(&bars->v_empty[s]);
           if (j + 1 < n_tiles) {
             issue_qk(q, sn);
-            if (q == 1) umma_commit(&bars->k_empty[sn]);
+            if (last_q) umma_commit(&bars->k_empty[sn]);
           }
         }
       }
@@ -278,13 +280,14 @@ attn_dense_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
   } else {
     // ------------------------------------------------------------------ softmax warpgroups (thread = query row)
     const int q = warp >> 2;
+    const int my_tiles = (q < p.tiles) ? n_tiles : 0;   // the second warpgroup idles in one-tile mode
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t t_s = tmem + lane_base + (q ? COL_S1 : COL_S0);
     const uint32_t t_o = tmem + lane_base + (q ? COL_O1 : COL_O0);
     const int row = q_base + q * BM + (warp & 3) * 32 + lane;
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
+    for (int j = 0; j < my_tiles; ++j) {
       ok = mbar_wait(&bars->s_full[q], j & 1, abort_flag, 30 + q);
       if (!ok) break;
       tc_fence_after_sync();
@@ -342,33 +345,46 @@ attn_dense_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       tc_fence_before_sync();
       mbar_arrive(&bars->p_full[q]);
     }
-    if (ok) ok = mbar_wait(&bars->o_final, 0, abort_flag, 32 + q);
-    if (ok) {
+    if (ok && my_tiles > 0) ok = mbar_wait(&bars->o_final, 0, abort_flag, 32 + q);
+    if (ok && my_tiles > 0) {
       tc_fence_after_sync();
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      bf16* dst = p.out + ((long long)batch * p.q_len + row) * p.out_stride_tok + (long long)head * HD;
-      if (p.scatter.enabled && row < p.q_len) {
-        const OutScatter& sc = p.scatter;
-        const int g2 = row - sc.split;
-        const int rk = row < sc.split ? row / sc.n0 : g2 / sc.n1;
-        const int local = row < sc.split ? row % sc.n0 : sc.n0 + g2 % sc.n1;
-        dst = sc.peer[rk] + (long long)local * p.out_stride_tok + sc.col_offset + head * HD;
-      }
+      // Stage this warp's 32 rows x 128 columns in the (now idle) Q region, then write every row's 256 bytes with
+      // 16 lanes x 16 bytes: contiguous runs for local stores and for stores that cross NVLink alike.
+      // 16-byte chunk c of row r sits at c ^ (r & 7).
+      uint8_t* slab = smem + SMEM_Q + warp * (32 * 256);
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t o[32];
         tmem_ld_x32(t_o + c * 32, o);
         tmem_ld_wait();
-        if (row < p.q_len) {
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint4 u;
-            u.x = pack_bf16x2(__uint_as_float(o[v * 8 + 0]) * inv, __uint_as_float(o[v * 8 + 1]) * inv);
-            u.y = pack_bf16x2(__uint_as_float(o[v * 8 + 2]) * inv, __uint_as_float(o[v * 8 + 3]) * inv);
-            u.z = pack_bf16x2(__uint_as_float(o[v * 8 + 4]) * inv, __uint_as_float(o[v * 8 + 5]) * inv);
-            u.w = pack_bf16x2(__uint_as_float(o[v * 8 + 6]) * inv, __uint_as_float(o[v * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = u;
+        for (int v = 0; v < 4; ++v) {
+          uint4 u;
+          u.x = pack_bf16x2(__uint_as_float(o[v * 8 + 0]) * inv, __uint_as_float(o[v * 8 + 1]) * inv);
+          u.y = pack_bf16x2(__uint_as_float(o[v * 8 + 2]) * inv, __uint_as_float(o[v * 8 + 3]) * inv);
+          u.z = pack_bf16x2(__uint_as_float(o[v * 8 + 4]) * inv, __uint_as_float(o[v * 8 + 5]) * inv);
+          u.w = pack_bf16x2(__uint_as_float(o[v * 8 + 6]) * inv, __uint_as_float(o[v * 8 + 7]) * inv);
+          *reinterpret_cast<uint4*>(slab + lane * 256 + (((c * 4 + v) ^ (lane & 7)) << 4)) = u;
+        }
+      }
+      __syncwarp();
+      const int row0 = q_base + q * BM + (warp & 3) * 32;
+#pragma unroll 4
+      for (int it = 0; it < 16; ++it) {
+        const int r = 2 * it + (lane >> 4), ch = lane & 15;
+        const int grow = row0 + r;
+        if (grow < p.q_len) {
+          const uint4 val = *reinterpret_cast<const uint4*>(slab + r * 256 + ((ch ^ (r & 7)) << 4));
+          bf16* dst = p.out + ((long long)batch * p.q_len + grow) * p.out_stride_tok + (long long)head * HD;
+          if (p.scatter.enabled) {
+            const OutScatter& sc = p.scatter;
+            const int g2 = grow - sc.split;
+            const int rk = grow < sc.split ? grow / sc.n0 : g2 / sc.n1;
+            const int local = grow < sc.split ? grow % sc.n0 : sc.n0 + g2 % sc.n1;
+            dst = sc.peer[rk] + (long long)local * p.out_stride_tok + sc.col_offset + head * HD;
           }
+          *reinterpret_cast<uint4*>(dst + ch * 8) = val;
         }
       }
     }
@@ -440,6 +456,9 @@ int make_tmap_heads(CUtensorMap* out, const void* ptr, int heads, int tokens, in
 
 }  // namespace
 
+int g_force_tiles = 0;   // 0: choose per problem; 1 / 2: fixed query tiles per CTA (comparison runs)
+void attn_dense_tcgen05_set_tiles(int tiles) { g_force_tiles = tiles; }
+
 // Returns 1 when the tcgen05 kernel handles this problem, 0 otherwise.
 int attn_dense_tcgen05_supported(const void* q, const void* k, const void* v, long long q_stride_tok, int q_stride_head,
                                  long long kv_stride_tok, int kv_stride_head, long long out_stride_tok, int D,
@@ -487,7 +506,12 @@ int attn_dense_tcgen05_launch(const void* q, long long q_stride_tok, int q_strid
     p.scatter.n1 = n1;
     p.scatter.col_offset = col_offset;
   }
-  dim3 grid((q_len + 2 * BM - 1) / (2 * BM), Hq, batch);
+  // one-tile CTAs when that shortens the schedule: a one-tile CTA takes ~0.6 of a two-tile CTA's time
+  const int sms = 148;
+  const long c2 = (long)((q_len + 2 * BM - 1) / (2 * BM)) * Hq * batch, c1 = (long)((q_len + BM - 1) / BM) * Hq * batch;
+  const double t2 = (double)((c2 + sms - 1) / sms), t1 = 0.6 * (double)((c1 + sms - 1) / sms);
+  p.tiles = (g_force_tiles == 1 || g_force_tiles == 2) ? g_force_tiles : (t1 < t2 ? 1 : 2);
+  dim3 grid((q_len + p.tiles * BM - 1) / (p.tiles * BM), Hq, batch);
   return launch_kernel(attn_dense_tcgen05_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, tq, tk, tv, p);
 }
 

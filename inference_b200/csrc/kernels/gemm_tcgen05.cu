@@ -43,7 +43,9 @@ struct GemmCfg {
   static constexpr uint32_t B_BYTES = BLOCK_N * BK * 2;
   static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr uint32_t TMEM_COLS = (2 * BLOCK_N < 32) ? 32 : 2 * BLOCK_N;
-  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+  // staging slabs of the coalescing epilogue: 4 warps x 32 rows x 128 bf16 columns (tokens-as-M, wide tiles only)
+  static constexpr uint32_t EPI_BYTES = (!SWAPPED && BLOCK_N >= 128) ? 4 * 32 * 256 : 0;
+  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ + EPI_BYTES;
 };
 
 // One contiguous run of k-blocks of one output tile, as processed by one CTA.
@@ -193,6 +195,84 @@ __device__ __forceinline__ void epilogue_store16(const GemmParams& p, float* v, 
 }
 
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Destination of the 8 bf16 at (row, col0 .. col0 + 7) under the peer dispatch modes of GemmScatter.
+__device__ __forceinline__ bf16* scatter_dst(const GemmScatter& sc, int row, int col0) {
+  if (sc.enabled == 1) {
+    const int which = col0 / sc.hd_total;
+    const int rem = col0 - which * sc.hd_total;
+    const int h = rem >> 7;
+    const int r = h / sc.heads_per_rank;
+    const int grow = row + (row < sc.row_split ? sc.row_off0 : sc.row_off1);
+    return sc.peer[r] + (size_t)grow * sc.ld + (which * sc.heads_per_rank + (h - r * sc.heads_per_rank)) * 128 +
+           (rem & 127);
+  }
+  const int r = row / sc.rows_per_rank;
+  return sc.peer[r] + ((size_t)sc.src_rank * sc.rows_per_rank + (row - r * sc.rows_per_rank)) * sc.ld + col0;
+}
+
+// Coalescing epilogue for peer dispatch: every epilogue warp stages its 32 rows x 128 columns (bf16, bias and
+// activation applied) in shared memory, then writes each row's 256 bytes with 16 lanes x 16 bytes, so what crosses
+// NVLink are 256-byte contiguous runs instead of 32-byte fragments. 16-byte chunk c of row r is stored at c ^ (r & 7).
+template <int BLOCK_N>
+__device__ __forceinline__ void epilogue_scatter_staged(const GemmParams& p, uint32_t taddr, uint8_t* slab, int lane,
+                                                        int row0, int col_base) {
+#pragma unroll 1
+  for (int sl = 0; sl < BLOCK_N / 128; ++sl) {
+#pragma unroll 1
+    for (int ch = 0; ch < 8; ++ch) {
+      float v[16];
+      tmem_ld_32x32b_x16(taddr + sl * 128 + ch * 16, v);
+      const int col0 = col_base + sl * 128 + ch * 16;
+      if (p.bias && col0 < p.N) {
+        const uint4* bp = reinterpret_cast<const uint4*>(p.bias + col0);
+        const uint4 b0 = __ldg(bp), b1 = __ldg(bp + 1);
+        const bf16* bb0 = reinterpret_cast<const bf16*>(&b0);
+        const bf16* bb1 = reinterpret_cast<const bf16*>(&b1);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          v[j] += __bfloat162float(bb0[j]);
+          v[8 + j] += __bfloat162float(bb1[j]);
+        }
+      }
+      if (p.act != SWB_ACT_NONE) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = apply_act(v[j], p.act);
+      }
+      if (p.residual && row0 + lane < p.M && col0 < p.N) {
+        const uint4* rp = reinterpret_cast<const uint4*>(p.residual + (size_t)(row0 + lane) * p.ld_res + col0);
+        const uint4 r0 = rp[0], r1 = rp[1];
+        const bf16* rr0 = reinterpret_cast<const bf16*>(&r0);
+        const bf16* rr1 = reinterpret_cast<const bf16*>(&r1);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          v[j] += __bfloat162float(rr0[j]);
+          v[8 + j] += __bfloat162float(rr1[j]);
+        }
+      }
+      uint4 o[2];
+      __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(o);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ob[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+      uint8_t* rowp = slab + lane * 256;
+      *reinterpret_cast<uint4*>(rowp + (((2 * ch) ^ (lane & 7)) << 4)) = o[0];
+      *reinterpret_cast<uint4*>(rowp + (((2 * ch + 1) ^ (lane & 7)) << 4)) = o[1];
+    }
+    __syncwarp();
+#pragma unroll 4
+    for (int it = 0; it < 16; ++it) {
+      const int r = 2 * it + (lane >> 4), c = lane & 15;
+      const uint4 val = *reinterpret_cast<const uint4*>(slab + r * 256 + ((c ^ (r & 7)) << 4));
+      const int row = row0 + r, col0 = col_base + sl * 128 + c * 8;
+      if (row < p.M && col0 < p.N) {
+        bf16* dst = p.scatter.enabled ? scatter_dst(p.scatter, row, col0)
+                                      : reinterpret_cast<bf16*>(p.out) + (size_t)row * p.ldd + col0;
+        *reinterpret_cast<uint4*>(dst) = val;
+      }
+    }
+    __syncwarp();
+  }
+}
 
 template <int BLOCK_N, bool TRANSPOSED>
 __global__ void __launch_bounds__(GEMM_THREADS, (GemmCfg<BLOCK_N, TRANSPOSED>::MIN_CTAS))
@@ -370,11 +450,25 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       const int col_base = c.tn * BLOCK_N;
       const bool whole = (c.kb0 == 0 && c.kb1 == p.kblocks_total);
       if (whole) {
+        if constexpr (Cfg::EPI_BYTES > 0) {
+          if (p.scatter.enabled || p.staged_epilogue) {
+            uint8_t* slab = smem + STAGES * Cfg::STAGE_BYTES + 256 + (warp - 2) * (32 * 256);
+            epilogue_scatter_staged<BLOCK_N>(p, taddr, slab, lane, c.tm * BM + quarter * 32, col_base);
+          } else {
 #pragma unroll 1
-        for (int ch = 0; ch < BLOCK_N / 16; ++ch) {
-          float v[16];
-          tmem_ld_32x32b_x16(taddr + ch * 16, v);
-          epilogue_store16<TRANSPOSED>(p, v, row, col_base + ch * 16);
+            for (int ch = 0; ch < BLOCK_N / 16; ++ch) {
+              float v[16];
+              tmem_ld_32x32b_x16(taddr + ch * 16, v);
+              epilogue_store16<TRANSPOSED>(p, v, row, col_base + ch * 16);
+            }
+          }
+        } else {
+#pragma unroll 1
+          for (int ch = 0; ch < BLOCK_N / 16; ++ch) {
+            float v[16];
+            tmem_ld_32x32b_x16(taddr + ch * 16, v);
+            epilogue_store16<TRANSPOSED>(p, v, row, col_base + ch * 16);
+          }
         }
         tc_fence_before_sync();
         __syncwarp();
@@ -631,6 +725,11 @@ int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
   if (a.scatter) {
     p.scatter = *a.scatter;
   }
+  static const int staged_default = [] {
+    const char* e = getenv("SWB_GEMM_STAGED");
+    return e ? atoi(e) : 0;
+  }();
+  p.staged_epilogue = staged_default;
 
   int block_n;
   CUtensorMap ta, tb;
@@ -679,6 +778,7 @@ int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
                (!a.bias || (reinterpret_cast<uintptr_t>(a.bias) & 15) == 0) &&
                (!a.residual || (((reinterpret_cast<uintptr_t>(a.residual) & 15) == 0) && (a.ld_res % 8 == 0)));
     if (a.scatter && !p.vec_ok) return -3;
+    if (!p.vec_ok || a.out_fp32 || (a.N % 16) != 0) p.staged_epilogue = 0;
   }
 
   const int tiles = p.tiles_m * p.tiles_n;

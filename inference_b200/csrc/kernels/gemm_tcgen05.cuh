@@ -51,6 +51,7 @@ struct GemmParams {
   int* status;
   unsigned long long* trace;  // optional [grid][8] globaltimer stamps of kernel phases (profiling aid)
   GemmScatter scatter;
+  int staged_epilogue;   // tokens-as-M, bf16 output: stage rows in shared memory and store 256-byte runs
 };
 
 // User-level problem: D[T, N] = act(A[T, K] * W[N, K]^T + bias[N]) + residual[T, N].

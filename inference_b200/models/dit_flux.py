@@ -454,6 +454,15 @@ class FluxDiTGpu:
     def _forward_sp(self, img, img_ids, txt, txt_ids, timesteps, y, guidance, rope):
         import os
 
+        trace = os.environ.get("SWB_SP_TRACE") == "1" and not torch.cuda.is_current_stream_capturing()
+        marks: list = []
+
+        def mark(name):      # phase boundaries as CUDA events (profiling aid; eager mode only)
+            if trace:
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                marks.append((name, e))
+
         cfg, comm = self.cfg, self.comm
         H, D, NH, M = cfg.hidden_size, cfg.head_dim, cfg.num_heads, cfg.mlp_hidden
         P, r = comm.world, comm.rank
@@ -487,12 +496,17 @@ class FluxDiTGpu:
         def exchange_and_attend(norms):
             """norms: [(row_lo, row_hi, q_norm, k_norm)] in GLOBAL rows (fused) or LOCAL rows (baseline)."""
             if fused:
+                mark("qkv_gemm_scatter")
                 ctx.barrier()                                   # every peer's QKV tiles have landed
+                mark("barrier_a")
                 for lo, hi, qn, kn in norms:
                     ops.rope_kv_write(ctx.qkv[lo:hi], positions[lo:hi], None, cos, sin, None, None, Hl, Hl, D,
                                       rot_dim=D, interleaved=True, q_norm=qn, k_norm=kn, norm_eps=1e-6)
+                mark("rope")
                 ctx.attn_scatter(scale)
+                mark("attn_scatter")
                 ctx.barrier()                                   # every peer's attention rows have landed
+                mark("barrier_b")
                 self.launches += 3 + len(norms)
                 return
             for lo, hi, qn, kn in norms:
@@ -504,11 +518,13 @@ class FluxDiTGpu:
             buf2[:, :H].copy_(back)
             self.launches += 2 + len(norms)
 
+        mark("prologue")
         for i in range(cfg.depth):
             mods, norms = {}, []
             for s in ("img", "txt"):
                 m = mod[f"double_blocks.{i}.{s}_mod.lin"]
                 mods[s] = [m[:, j * H:(j + 1) * H] for j in range(6)]
+            mark("rest")
             for s, x, lo_l, n_l, lo_g, n_g in (("txt", x_txt, 0, St_l, 0, St), ("img", x_img, St_l, Si_l, St, Si)):
                 xm = ops.layernorm_mod(x[None], scale=mods[s][1], shift=mods[s][0], rows_per_batch=n_l)[0]
                 name = f"double_blocks.{i}.{s}_attn.qkv"
@@ -537,6 +553,7 @@ class FluxDiTGpu:
             p = f"single_blocks.{i}"
             m = mod[p + ".modulation.lin"]
             sh, sc, g = m[:, :H], m[:, H:2 * H], m[:, 2 * H:]
+            mark("rest")
             xm = ops.layernorm_mod(x[None], scale=sc, shift=sh, rows_per_batch=S_l)[0]
             nw = (self.w[p + ".norm.query_norm.scale"], self.w[p + ".norm.key_norm.scale"])
             if fused:
@@ -554,4 +571,12 @@ class FluxDiTGpu:
         xm = ops.layernorm_mod(x_img[None], scale=m[:, H:], shift=m[:, :H], rows_per_batch=Si_l)[0]
         v_local = self._lin(xm, "final_layer.linear")                           # [Si_l, C]
         self.launches += 2
-        return comm.all_gather(v_local, dim=0)[None]
+        out = comm.all_gather(v_local, dim=0)[None]
+        if trace:
+            mark("rest")
+            torch.cuda.synchronize()
+            tot: dict = {}
+            for (_, e0), (name, e1) in zip(marks, marks[1:]):
+                tot[name] = tot.get(name, 0.0) + e0.elapsed_time(e1)
+            self.sp_phase_ms = {k: round(v, 3) for k, v in tot.items()}
+        return out

@@ -249,8 +249,20 @@ def test_dense_attention_tcgen05(B, Sq, Skv, Hq, Hkv, qmul):
         legacy = ops.dense_attention(q, k, v, scale=scale)
     finally:
         set_dense_impl(False)
+    from inference_b200._native import kernels
+
+    forced = []
+    try:
+        for tiles in (1, 2):          # both schedules: one query tile per CTA, two with softmax / MMA overlap
+            kernels().swb_attn_dense_set_tiles(tiles)
+            forced.append(ops.dense_attention(q, k, v, scale=scale))
+            ops.check_status()
+    finally:
+        kernels().swb_attn_dense_set_tiles(0)
     for b in range(B):
         ref = _ref_attn(q[b], k[b], v[b], scale, False)
         err = (out[b].float() - ref).abs().max().item()
         assert err < 3e-2, (b, err)
         assert (out[b].float() - legacy[b].float()).abs().max().item() < 3e-2
+        for f in forced:
+            assert (f[b].float() - ref).abs().max().item() < 3e-2
