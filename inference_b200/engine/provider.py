@@ -313,7 +313,7 @@ def _can_load_gpu(spec: LoadSpec) -> bool:
 
 def _can_load_cpu(spec: LoadSpec) -> bool:
     cfg = probe_config(spec)
-    return cfg is not None and cfg.mla is None and cfg.architecture is not Architecture.QWEN35
+    return cfg is not None and cfg.architecture is not Architecture.QWEN35
 
 
 B200_LLAMA = TextLlmRegistration(lambda: _descriptor("b200-llama", BACKEND_GPU),

@@ -196,7 +196,20 @@ class ModelConfig:
                             bool(v.get("norm_topk_prob", False)), real("routed_scaling_factor") or 1.0,
                             max(0, integer("first_k_dense_replace") or 0))
 
+        # newer Hugging Face configs nest theta and the scaling block in `rope_parameters`
+        rp = v.get("rope_parameters") if isinstance(v.get("rope_parameters"), dict) else None
         rs = v.get("rope_scaling") if isinstance(v.get("rope_scaling"), dict) else None
+        theta = real("rope_theta")
+        prf = real("partial_rotary_factor")
+        if rp is not None:
+            if theta is None and isinstance(rp.get("rope_theta"), (int, float)):
+                theta = float(rp["rope_theta"])
+            if prf is None and isinstance(rp.get("partial_rotary_factor"), (int, float)):
+                prf = float(rp["partial_rotary_factor"])
+            if rs is None and rp.get("rope_type", rp.get("type", "default")) not in (None, "default"):
+                rs = rp
+            elif rs is None and isinstance(rp.get("mrope_section"), list):
+                rs = rp
         yarn, scaling, mrope = None, None, None
         if rs is not None:
             ty = rs.get("type", rs.get("rope_type"))
@@ -210,7 +223,7 @@ class ModelConfig:
                                   rf("original_max_position_embeddings", 4096.0), rf("mscale", 1.0),
                                   rf("mscale_all_dim", 0.0))
             ty2 = rs.get("rope_type", rs.get("type"))
-            if ty2 is None or ty2 == "llama3":  # a bare factor block is treated as llama3
+            if (ty2 is None and "factor" in rs) or ty2 == "llama3":  # a bare factor block is treated as llama3
                 scaling = RopeScaling(rf("factor", 1.0), rf("low_freq_factor", 1.0), rf("high_freq_factor", 4.0),
                                       rf("original_max_position_embeddings", 8192.0))
             ms = rs.get("mrope_section")
@@ -220,12 +233,12 @@ class ModelConfig:
         return ModelConfig(
             hidden_size=hidden, intermediate_size=inter, num_layers=req("num_hidden_layers"), num_heads=heads,
             num_kv_heads=integer("num_key_value_heads") or heads, head_dim=head_dim, vocab_size=req("vocab_size"),
-            rms_norm_eps=real("rms_norm_eps") or 1e-5, rope_theta=real("rope_theta") or 500000.0,
+            rms_norm_eps=real("rms_norm_eps") or 1e-5, rope_theta=theta or 500000.0,
             rope_scaling=scaling, tie_word_embeddings=tie, architecture=arch,
             max_position_embeddings=integer("max_position_embeddings") or 0, quantization_bits=qbits,
             quantization_group_size=qgroup, moe=moe, attn_logit_softcap=real("attn_logit_softcapping"),
             final_logit_softcap=real("final_logit_softcapping"), query_pre_attn_scalar=integer("query_pre_attn_scalar"),
-            partial_rotary_factor=real("partial_rotary_factor") or 1.0, mla=mla, yarn=yarn, mrope_section=mrope,
+            partial_rotary_factor=prf or 1.0, mla=mla, yarn=yarn, mrope_section=mrope,
             raw=dict(top))
 
     @staticmethod

@@ -136,6 +136,18 @@ def _split_packed(weights: dict[str, torch.Tensor], cfg: ModelConfig) -> dict[st
             t = out.pop(key)
             half = t.shape[0] // 2
             out[f"{base}gate_proj.weight"], out[f"{base}up_proj.weight"] = t[:half], t[half:]
+        elif key.endswith("mlp.experts.gate_up_proj") and weights[key].dim() == 3:
+            # stacked experts of newer checkpoints: [E, 2F, H] and [E, H, F] -> per-expert projections
+            base = key[: -len("gate_up_proj")]
+            t = out.pop(key)
+            half = t.shape[1] // 2
+            for e in range(t.shape[0]):
+                out[f"{base}{e}.gate_proj.weight"], out[f"{base}{e}.up_proj.weight"] = t[e, :half], t[e, half:]
+        elif key.endswith("mlp.experts.down_proj") and weights[key].dim() == 3:
+            base = key[: -len("down_proj")]
+            t = out.pop(key)
+            for e in range(t.shape[0]):
+                out[f"{base}{e}.down_proj.weight"] = t[e]
     return out
 
 
@@ -158,7 +170,7 @@ class OracleLlama:
 
     def __init__(self, cfg: ModelConfig, weights: dict[str, torch.Tensor], dtype: torch.dtype = torch.float32,
                  device: str | torch.device = "cpu"):
-        if cfg.mla is not None or cfg.architecture in (Architecture.QWEN35,):
+        if cfg.architecture in (Architecture.QWEN35,):
             raise LoadError(f"{cfg.architecture.value} is served by its own model class")
         self.cfg = cfg
         self.dtype = dtype
@@ -200,7 +212,15 @@ class OracleLlama:
         xf = x.reshape(-1, shape[-1])
         logits = xf @ self.w[p + ".gate.weight"].t()
         probs = torch.softmax(logits.float(), dim=-1)
-        topv, topi = probs.topk(moe.num_experts_per_tok, dim=-1)
+        raw = self.cfg.raw
+        if raw.get("topk_method") == "group_limited_greedy" and raw.get("n_group", 1) > 1:
+            g, tg = int(raw["n_group"]), int(raw.get("topk_group", 1))      # keep only the best `topk_group` groups
+            gs = probs.view(probs.shape[0], g, -1).amax(-1)
+            keep = torch.zeros_like(gs).scatter_(1, gs.topk(tg, dim=-1).indices, 1.0)
+            probs_sel = probs.masked_fill(keep.repeat_interleave(probs.shape[1] // g, 1) == 0, 0.0)
+            topv, topi = probs_sel.topk(moe.num_experts_per_tok, dim=-1)
+        else:
+            topv, topi = probs.topk(moe.num_experts_per_tok, dim=-1)
         if moe.norm_topk_prob:
             topv = topv / topv.sum(-1, keepdim=True)
         topv = topv * moe.routed_scaling_factor
@@ -212,6 +232,8 @@ class OracleLlama:
                 continue
             wgt = (topv * sel).sum(-1)[rows].to(x.dtype)
             out[rows] += self._mlp(xf[rows], f"{p}.experts.{e}") * wgt[:, None]
+        if (p + ".shared_experts.gate_proj.weight") in self.w:      # DeepSeek: ungated shared experts
+            out = out + self._mlp(xf, p + ".shared_experts")
         if (p + ".shared_expert.gate_proj.weight") in self.w:
             sh = self._mlp(xf, p + ".shared_expert")
             gate_key = p + ".shared_expert_gate.weight"
@@ -226,9 +248,40 @@ class OracleLlama:
             return self._moe(x, p)
         return self._mlp(x, p)
 
+    def _attention_mla(self, x, layer, cos, sin, cache, causal, additive_mask) -> torch.Tensor:
+        """Multi-head latent attention (DeepSeek-V2; candle-llm models/llama.rs MLA path): queries optionally through
+        a low-rank bottleneck, keys / values expanded from a shared compressed latent plus one rotary key head."""
+        cfg, m = self.cfg, self.cfg.mla
+        p = f"model.layers.{layer}.self_attn"
+        B, S, _ = x.shape
+        H = cfg.num_heads
+        if (p + ".q_a_proj.weight") in self.w:
+            q = self._lin(rms_norm(self._lin(x, p + ".q_a_proj"), self.w[p + ".q_a_layernorm.weight"], cfg.rms_norm_eps),
+                          p + ".q_b_proj")
+        else:
+            q = self._lin(x, p + ".q_proj")
+        q = q.view(B, S, H, m.q_head_dim)
+        q_nope, q_pe = q[..., : m.qk_nope_head_dim], q[..., m.qk_nope_head_dim:]
+        ckv = self._lin(x, p + ".kv_a_proj_with_mqa")
+        c, k_pe = ckv[..., : m.kv_lora_rank], ckv[..., m.kv_lora_rank:].view(B, S, 1, m.qk_rope_head_dim)
+        kv = self._lin(rms_norm(c, self.w[p + ".kv_a_layernorm.weight"], cfg.rms_norm_eps), p + ".kv_b_proj")
+        kv = kv.view(B, S, H, m.qk_nope_head_dim + m.v_head_dim)
+        k_nope, v = kv[..., : m.qk_nope_head_dim], kv[..., m.qk_nope_head_dim:]
+        q_pe = apply_rope(q_pe, cos, sin, m.qk_rope_head_dim, True)
+        k_pe = apply_rope(k_pe, cos, sin, m.qk_rope_head_dim, True)
+        q = torch.cat((q_nope, q_pe), -1).transpose(1, 2)
+        k = torch.cat((k_nope, k_pe.expand(B, S, H, m.qk_rope_head_dim)), -1).transpose(1, 2)
+        v = v.transpose(1, 2)
+        if cache is not None:
+            k, v = cache.update(layer, k, v)
+        o = sdpa(q, k, v, cfg.attn_scale, causal, additive_mask, None)
+        return self._lin(o.transpose(1, 2).reshape(B, S, H * m.v_head_dim), p + ".o_proj")
+
     def _attention(self, x: torch.Tensor, layer: int, cos, sin, cache: ContiguousKvCache | None, causal: bool,
                    additive_mask) -> torch.Tensor:
         cfg = self.cfg
+        if cfg.mla is not None:
+            return self._attention_mla(x, layer, cos, sin, cache, causal, additive_mask)
         p = f"model.layers.{layer}.self_attn"
         B, S, _ = x.shape
         q = self._lin(x, p + ".q_proj").view(B, S, cfg.num_heads, cfg.head_dim)
