@@ -726,8 +726,8 @@ int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
     p.scatter = *a.scatter;
   }
   static const int staged_default = [] {
-    const char* e = getenv("SWB_GEMM_STAGED");
-    return e ? atoi(e) : 0;
+    const char* e = getenv("SWB_GEMM_STAGED");   // 0 restores the row-per-thread stores (comparison runs)
+    return e ? atoi(e) : 1;
   }();
   p.staged_epilogue = staged_default;
 
