@@ -90,6 +90,8 @@ def _declare_kernels(lib: ctypes.CDLL) -> None:
     sig("swb_upsample2x", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
     sig("swb_attn_dense_set_impl", [c_int], None)
     sig("swb_attn_dense_set_tiles", [c_int], None)
+    sig("swb_attn_varlen_causal", [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_ll, c_int, c_void_p, c_ll, c_void_p, c_int,
+                                   c_int, c_int, c_int, c_int, c_float, c_void_p])
     sig("swb_attn_dense_scatter", [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_ll, c_int, c_void_p, c_int,
                                    c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                    c_void_p])

@@ -554,6 +554,24 @@ int swb_attn_dense_scatter(const void* q, long long q_stride_tok, int q_stride_h
                                    reinterpret_cast<cudaStream_t>(stream), peers, world, row_split, n0, n1, col_offset);
 }
 
+// Causal self-attention over a packed batch of fresh sequences (no earlier context): sequence s covers tokens
+// [cu_q[s], cu_q[s + 1]) of q / k / v / out, which share one flat token axis (prefill straight from the QKV
+// projection output). cu_q: device int32 [num_seqs + 1]. tcgen05 kernel only (head dim 128).
+int swb_attn_varlen_causal(const void* q, long long q_stride_tok, int q_stride_head, const void* k, const void* v,
+                           long long kv_stride_tok, int kv_stride_head, void* out, long long out_stride_tok,
+                           const int* cu_q, int num_seqs, int max_q_len, int total_tokens, int Hq, int Hkv, float scale,
+                           void* stream) {
+  using namespace swb;
+  if (num_seqs <= 0 || total_tokens <= 0) return 0;
+  if (!cu_q || max_q_len <= 0 || Hq % Hkv != 0) return -3;
+  if (!attn_dense_tcgen05_supported(q, k, v, q_stride_tok, q_stride_head, kv_stride_tok, kv_stride_head, out_stride_tok,
+                                    128, 1))
+    return -3;
+  return attn_dense_tcgen05_launch(q, q_stride_tok, q_stride_head, k, v, kv_stride_tok, kv_stride_head, out,
+                                   out_stride_tok, num_seqs, max_q_len, max_q_len, Hq, Hkv, scale,
+                                   reinterpret_cast<cudaStream_t>(stream), nullptr, 0, 0, 0, 0, 0, 1, cu_q, total_tokens);
+}
+
 // 0: pick the tcgen05 kernel whenever it supports the problem; 1: always the mma.sync kernel (comparison runs).
 void swb_attn_dense_set_impl(int impl) { swb::g_dense_impl = impl; }
 // 0: pick the number of query tiles per CTA per problem; 1 / 2: fixed (comparison runs).
@@ -567,11 +585,12 @@ int swb_attn_dense(const void* q, long long q_stride_tok, int q_stride_head, con
   if (batch <= 0 || q_len <= 0) return 0;
   if (D != HD || Hq % Hkv != 0) return -3;
   if (kv_len <= 0) return -3;
-  if (g_dense_impl == 0 && attn_dense_tcgen05_supported(q, k, v, q_stride_tok, q_stride_head, kv_stride_tok,
-                                                        kv_stride_head, out_stride_tok, D, causal))
+  if (g_dense_impl == 0 && (!causal || q_len == kv_len) &&
+      attn_dense_tcgen05_supported(q, k, v, q_stride_tok, q_stride_head, kv_stride_tok, kv_stride_head, out_stride_tok, D,
+                                   causal))
     return attn_dense_tcgen05_launch(q, q_stride_tok, q_stride_head, k, v, kv_stride_tok, kv_stride_head, out,
                                      out_stride_tok, batch, q_len, kv_len, Hq, Hkv, scale,
-                                     reinterpret_cast<cudaStream_t>(stream));
+                                     reinterpret_cast<cudaStream_t>(stream), nullptr, 0, 0, 0, 0, 0, causal);
   int rc = configure_once();
   if (rc) return rc;
   AttnParams p{};

@@ -60,6 +60,8 @@ struct FaParams {
   int q_len, kv_len, Hq, Hkv;
   float scale_log2;
   int tiles;   // query tiles per CTA: 2 (MMAs of one tile overlap the softmax of the other) or 1 (twice the CTAs)
+  int causal;  // key j attends to query i only if j <= i (sequences start at position 0: fresh prefill)
+  const int* cu_q;   // optional [num_seqs + 1] token offsets: blockIdx.z is then a sequence of a packed batch
 };
 
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* tmap, uint64_t* bar, int c0, int c1, int c2,
@@ -150,9 +152,16 @@ attn_dense_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
   Barriers* bars = reinterpret_cast<Barriers*>(smem + SMEM_BAR);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q_base = blockIdx.x * (p.tiles * BM);
-  const int head = blockIdx.y, batch = blockIdx.z;
+  const int head = blockIdx.y;
+  // packed variable-length batch: this CTA's sequence covers tokens [tok0, tok0 + q_len) of one flat token axis
+  const int tok0 = p.cu_q ? p.cu_q[blockIdx.z] : 0;
+  const int q_len = p.cu_q ? p.cu_q[blockIdx.z + 1] - tok0 : p.q_len;
+  const int kv_len = p.cu_q ? q_len : p.kv_len;
+  const int batch = p.cu_q ? 0 : blockIdx.z;
+  if (q_base >= q_len) return;   // uniform for the whole CTA, before any barrier or TMEM allocation
   const int kv_head = head / (p.Hq / p.Hkv);
-  const int n_tiles = (p.kv_len + BN - 1) / BN;
+  const int kv_end = p.causal ? min(kv_len, q_base + p.tiles * BM) : kv_len;
+  const int n_tiles = (kv_end + BN - 1) / BN;
   volatile int* abort_flag = &bars->abort;
 
   if (threadIdx.x == 0) {
@@ -194,7 +203,7 @@ attn_dense_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       for (int q = 0; q < p.tiles; ++q)
         for (int a = 0; a < 2; ++a)
           tma_load_4d(smem + SMEM_Q + q * TILE_BYTES + a * ATOM_BYTES, &tmap_q, &bars->q_full, a * 64, head,
-                      q_base + q * BM, batch);
+                      tok0 + q_base + q * BM, batch);
       bool ok = true;
       int issued_k = 0, issued_v = 0;
       for (int j = 0; j < n_tiles && ok; ++j) {
@@ -205,14 +214,14 @@ attn_dense_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         mbar_arrive_expect_tx(&bars->k_full[s], TILE_BYTES);
         for (int a = 0; a < 2; ++a)
           tma_load_4d(smem + SMEM_K + s * TILE_BYTES + a * ATOM_BYTES, &tmap_k, &bars->k_full[s], a * 64, kv_head,
-                      j * BN, batch);
+                      tok0 + j * BN, batch);
         issued_k = j + 1;
         ok = mbar_wait(&bars->v_empty[s], ph ^ 1, abort_flag, 11);
         if (!ok) break;
         mbar_arrive_expect_tx(&bars->v_full[s], TILE_BYTES);
         for (int a = 0; a < 2; ++a)
           tma_load_4d(smem + SMEM_V + s * TILE_BYTES + a * ATOM_BYTES, &tmap_v, &bars->v_full[s], a * 64, kv_head,
-                      j * BN, batch);
+                      tok0 + j * BN, batch);
         issued_v = j + 1;
       }
       if (!ok) {
@@ -295,10 +304,13 @@ attn_dense_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) tmem_ld_x32(t_s + c * 32, s + c * 32);
       tmem_ld_wait();
-      if ((j + 1) * BN > p.kv_len) {   // ragged last tile: keys past kv_len were zero-filled by TMA
+      // keys past the sequence (zero fill, or the next sequence of a packed batch) and, when causal, keys after the
+      // query position never contribute
+      if ((j + 1) * BN > kv_len || (p.causal && (j + 1) * BN > q_base + q * BM)) {
+        const int last_key = p.causal ? min(kv_len - 1, row) : kv_len - 1;
 #pragma unroll
         for (int i = 0; i < BN; ++i)
-          if (j * BN + i >= p.kv_len) s[i] = __float_as_uint(-INFINITY);
+          if (j * BN + i > last_key) s[i] = __float_as_uint(-INFINITY);
       }
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
@@ -374,9 +386,9 @@ attn_dense_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       for (int it = 0; it < 16; ++it) {
         const int r = 2 * it + (lane >> 4), ch = lane & 15;
         const int grow = row0 + r;
-        if (grow < p.q_len) {
+        if (grow < q_len) {
           const uint4 val = *reinterpret_cast<const uint4*>(slab + r * 256 + ((ch ^ (r & 7)) << 4));
-          bf16* dst = p.out + ((long long)batch * p.q_len + grow) * p.out_stride_tok + (long long)head * HD;
+          bf16* dst = p.out + ((long long)batch * p.q_len + tok0 + grow) * p.out_stride_tok + (long long)head * HD;
           if (p.scatter.enabled) {
             const OutScatter& sc = p.scatter;
             const int g2 = grow - sc.split;
@@ -463,7 +475,8 @@ void attn_dense_tcgen05_set_tiles(int tiles) { g_force_tiles = tiles; }
 int attn_dense_tcgen05_supported(const void* q, const void* k, const void* v, long long q_stride_tok, int q_stride_head,
                                  long long kv_stride_tok, int kv_stride_head, long long out_stride_tok, int D,
                                  int causal) {
-  if (D != HD || causal) return 0;
+  if (D != HD) return 0;
+  (void)causal;   // causal problems are supported when queries and keys cover the same positions (checked by callers)
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) return 0;
   if ((q_stride_tok | q_stride_head | kv_stride_tok | kv_stride_head | out_stride_tok) % 8) return 0;
   return 1;
@@ -472,13 +485,19 @@ int attn_dense_tcgen05_supported(const void* q, const void* k, const void* v, lo
 int attn_dense_tcgen05_launch(const void* q, long long q_stride_tok, int q_stride_head, const void* k, const void* v,
                               long long kv_stride_tok, int kv_stride_head, void* out, long long out_stride_tok,
                               int batch, int q_len, int kv_len, int Hq, int Hkv, float scale, cudaStream_t stream,
-                              void* const* peers, int world, int split, int n0, int n1, int col_offset) {
+                              void* const* peers, int world, int split, int n0, int n1, int col_offset, int causal,
+                              const int* cu_q, int total_tokens) {
   CUtensorMap tq, tk, tv;
-  int rc = make_tmap_heads(&tq, q, Hq, q_len, batch, q_stride_head, q_stride_tok, q_stride_tok * q_len);
+  // packed batches address one flat token axis (batch = the number of sequences only sizes the grid)
+  const int map_q_tokens = cu_q ? total_tokens : q_len, map_kv_tokens = cu_q ? total_tokens : kv_len;
+  const int map_batch = cu_q ? 1 : batch;
+  int rc = make_tmap_heads(&tq, q, Hq, map_q_tokens, map_batch, q_stride_head, q_stride_tok, q_stride_tok * map_q_tokens);
   if (rc) return rc;
-  rc = make_tmap_heads(&tk, k, Hkv, kv_len, batch, kv_stride_head, kv_stride_tok, kv_stride_tok * kv_len);
+  rc = make_tmap_heads(&tk, k, Hkv, map_kv_tokens, map_batch, kv_stride_head, kv_stride_tok,
+                       kv_stride_tok * map_kv_tokens);
   if (rc) return rc;
-  rc = make_tmap_heads(&tv, v, Hkv, kv_len, batch, kv_stride_head, kv_stride_tok, kv_stride_tok * kv_len);
+  rc = make_tmap_heads(&tv, v, Hkv, map_kv_tokens, map_batch, kv_stride_head, kv_stride_tok,
+                       kv_stride_tok * map_kv_tokens);
   if (rc) return rc;
   static bool configured[64] = {false};
   int dev = 0;
@@ -497,6 +516,9 @@ int attn_dense_tcgen05_launch(const void* q, long long q_stride_tok, int q_strid
   p.Hq = Hq;
   p.Hkv = Hkv;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.causal = causal;
+  p.cu_q = cu_q;
+  if (cu_q) p.q_len = 0;   // rows are addressed by their flat token index
   if (peers) {
     if (world < 1 || world > 8 || batch != 1 || n1 <= 0 || (split > 0 && n0 <= 0) || (col_offset % 8) != 0) return -3;
     for (int r = 0; r < world; ++r) p.scatter.peer[r] = reinterpret_cast<bf16*>(peers[r]);

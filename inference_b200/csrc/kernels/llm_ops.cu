@@ -267,6 +267,13 @@ __global__ void __launch_bounds__(256) rope_kv_write_kernel(
       if (i < epl && d < D) dst[d] = __float2bfloat16(v[i]);
     }
   }
+  if (is_k && dst != src) {   // the rotated key also stays in the projection buffer
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int d = lane + i * 32;
+      if (i < epl && d < D) src[d] = __float2bfloat16(v[i]);
+    }
+  }
 }
 
 // Head dim 128 with full rotary width: every lane owns four elements so that both members of each rotation pair are
@@ -344,6 +351,10 @@ __global__ void __launch_bounds__(256) rope_kv_write_d128_kernel(
   if (dst) {
     *reinterpret_cast<__nv_bfloat162*>(dst + e0) = __floats2bfloat162_rn(v[0], v[1]);
     *reinterpret_cast<__nv_bfloat162*>(dst + e1) = __floats2bfloat162_rn(v[2], v[3]);
+  }
+  if (is_k && dst != src) {   // the rotated key also stays in the projection buffer (prefill attention reads it there)
+    *reinterpret_cast<__nv_bfloat162*>(src + e0) = __floats2bfloat162_rn(v[0], v[1]);
+    *reinterpret_cast<__nv_bfloat162*>(src + e1) = __floats2bfloat162_rn(v[2], v[3]);
   }
 }
 

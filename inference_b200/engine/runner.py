@@ -68,6 +68,7 @@ class ModelRunner:
         and returns greedy next tokens [num_seqs] (or fp32 logits when want_logits)."""
         dev = self.model.device
         ids, pos, slots, cu, kvl, rows = [], [], [], [0], [], []
+        fresh = all(s.length == 0 for s in seqs)     # no earlier context: attention can read K / V from the QKV buffer
         for s, toks in zip(seqs, new_tokens):
             start = s.length
             sl = s.reserve(len(toks))
@@ -90,7 +91,7 @@ class ModelRunner:
             slot_mapping=torch.tensor(slots, dtype=torch.int64, device=dev),
             block_table=table.to(dev), kv_lens=torch.tensor(kvl, dtype=torch.int32, device=dev),
             cu_q=None if decode else torch.tensor(cu, dtype=torch.int32, device=dev), max_q_len=max_q,
-            num_seqs=len(seqs), decode=decode,
+            num_seqs=len(seqs), decode=decode, fresh_prefill=fresh and not decode,
             attn_splits=_splits_for(len(seqs), self.model.hkv, max(kvl)) if decode else 1,
             logits_rows=None if all_positions else torch.tensor(rows, dtype=torch.int64, device=dev))
         hidden = self.model.forward_hidden(inp, self.pool.data)

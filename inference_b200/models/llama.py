@@ -35,6 +35,7 @@ class StepInputs:
     decode: bool = False               # q_len * gqa_group <= 16 for every sequence
     attn_splits: int = 1
     logits_rows: torch.Tensor | None = None  # int64 rows of the hidden state to project; None => all rows
+    fresh_prefill: bool = False        # every sequence starts at position 0 (context == this step's tokens)
 
 
 @dataclass
@@ -238,6 +239,7 @@ class LlamaGpu:
         return self
 
     quant_format: str | None = None
+    dense_prefill: bool = True      # False: always read K / V back from the paged cache (comparison runs)
 
     def weight_bytes(self) -> int:
         n, q = self.embed.numel() + self.norm.numel(), 0
@@ -278,9 +280,17 @@ class LlamaGpu:
                               q_norm=L.q_norm, k_norm=L.k_norm, norm_eps=eps, norm_w_offset=woff,
                               block_size=block_size)
             q = qkv[:, :q_cols].view(T, self.hq, D)
-            attn = ops.paged_attention(q, kv_pool[li, 0], kv_pool[li, 1], inp.block_table, inp.kv_lens, cu_q=inp.cu_q,
-                                       max_q_len=inp.max_q_len, scale=cfg.attn_scale, causal=True, decode=inp.decode,
-                                       num_splits=inp.attn_splits, softcap=cfg.attn_logit_softcap or 0.0)
+            if inp.fresh_prefill and inp.cu_q is not None and not cfg.attn_logit_softcap and self.dense_prefill:
+                # no earlier context: causal attention straight from the projection output on the tcgen05 kernel
+                kv_cols = self.hkv * D
+                attn = ops.varlen_causal_attention(q, qkv[:, q_cols:q_cols + kv_cols].view(T, self.hkv, D),
+                                                   qkv[:, q_cols + kv_cols:].view(T, self.hkv, D), inp.cu_q,
+                                                   inp.max_q_len, scale=cfg.attn_scale)
+            else:
+                attn = ops.paged_attention(q, kv_pool[li, 0], kv_pool[li, 1], inp.block_table, inp.kv_lens,
+                                           cu_q=inp.cu_q, max_q_len=inp.max_q_len, scale=cfg.attn_scale, causal=True,
+                                           decode=inp.decode, num_splits=inp.attn_splits,
+                                           softcap=cfg.attn_logit_softcap or 0.0)
             fused = self.comm.fused if (self.comm.fused is not None and T <= self.comm.fused.max_tokens and
                                         L.post_attn_ln is None) else None
             if fused is not None:
@@ -397,9 +407,17 @@ class LlamaGpu:
                               q_norm=L.q_norm, k_norm=L.k_norm, norm_eps=eps, norm_w_offset=woff,
                               block_size=block_size)
             q = qkv[:, :q_cols].view(T, self.hq, D)
-            attn = ops.paged_attention(q, kv_pool[li, 0], kv_pool[li, 1], inp.block_table, inp.kv_lens, cu_q=inp.cu_q,
-                                       max_q_len=inp.max_q_len, scale=cfg.attn_scale, causal=True, decode=inp.decode,
-                                       num_splits=inp.attn_splits, softcap=cfg.attn_logit_softcap or 0.0)
+            if inp.fresh_prefill and inp.cu_q is not None and not cfg.attn_logit_softcap and self.dense_prefill:
+                # no earlier context: causal attention straight from the projection output on the tcgen05 kernel
+                kv_cols = self.hkv * D
+                attn = ops.varlen_causal_attention(q, qkv[:, q_cols:q_cols + kv_cols].view(T, self.hkv, D),
+                                                   qkv[:, q_cols + kv_cols:].view(T, self.hkv, D), inp.cu_q,
+                                                   inp.max_q_len, scale=cfg.attn_scale)
+            else:
+                attn = ops.paged_attention(q, kv_pool[li, 0], kv_pool[li, 1], inp.block_table, inp.kv_lens,
+                                           cu_q=inp.cu_q, max_q_len=inp.max_q_len, scale=cfg.attn_scale, causal=True,
+                                           decode=inp.decode, num_splits=inp.attn_splits,
+                                           softcap=cfg.attn_logit_softcap or 0.0)
             ctx.gemm_scatter_rows(attn, L.o)
             h = ctx.reduce_norm_gather(T, res, L.ln2, eps, woff)
             gu = ops.linear_any(h, L.gate_up)

@@ -69,3 +69,20 @@ def dense_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale:
 def set_dense_impl(legacy: bool) -> None:
     """Comparison runs only: True forces the mma.sync kernel for dense attention, False restores the tcgen05 kernel."""
     kernels().swb_attn_dense_set_impl(1 if legacy else 0)
+
+
+def varlen_causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_q: torch.Tensor, max_q_len: int, *,
+                            scale: float, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal self-attention over a packed batch of fresh sequences on the tcgen05 kernel. q [T, Hq, 128], k / v
+    [T, Hkv, 128] (views into one QKV buffer are fine), cu_q int32 [num_seqs + 1] -> out [T, Hq * 128]."""
+    require_cuda(q, k, v, cu_q)
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    assert D == 128 and q.stride(2) == 1 and k.stride(2) == 1 and k.stride() == v.stride() and cu_q.dtype == torch.int32
+    if out is None:
+        out = torch.empty((T, Hq * D), dtype=q.dtype, device=q.device)
+    rc = kernels().swb_attn_varlen_causal(q.data_ptr(), q.stride(0), q.stride(1), k.data_ptr(), v.data_ptr(), k.stride(0),
+                                          k.stride(1), out.data_ptr(), out.stride(0), cu_q.data_ptr(), cu_q.numel() - 1,
+                                          max_q_len, T, Hq, Hkv, scale, stream_ptr())
+    check(rc, "swb_attn_varlen_causal")
+    return out

@@ -266,3 +266,26 @@ def test_dense_attention_tcgen05(B, Sq, Skv, Hq, Hkv, qmul):
         assert (out[b].float() - legacy[b].float()).abs().max().item() < 3e-2
         for f in forced:
             assert (f[b].float() - ref).abs().max().item() < 3e-2
+
+
+@pytest.mark.parametrize("lens,Hq,Hkv", [([300, 17, 1024, 129], 8, 2), ([64], 4, 4), ([1000, 1000], 2, 1)])
+def test_varlen_causal_attention_tcgen05(lens, Hq, Hkv):
+    """Packed fresh-prefill attention straight from a QKV buffer (strided views) against fp32 causal attention."""
+    from inference_b200 import ops
+
+    T = sum(lens)
+    g = torch.Generator(device="cuda").manual_seed(T)
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * 128, device="cuda", generator=g).bfloat16()
+    q = qkv[:, : Hq * 128].view(T, Hq, 128)
+    k = qkv[:, Hq * 128:(Hq + Hkv) * 128].view(T, Hkv, 128)
+    v = qkv[:, (Hq + Hkv) * 128:].view(T, Hkv, 128)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    scale = 1 / math.sqrt(128)
+    out = ops.varlen_causal_attention(q, k, v, cu, max(lens), scale=scale)
+    ops.check_status()
+    lo = 0
+    for n in lens:
+        ref = _ref_attn(q[lo:lo + n], k[lo:lo + n], v[lo:lo + n], scale, True)
+        err = (out[lo:lo + n].float() - ref).abs().max().item()
+        assert err < 3e-2, (n, err)
+        lo += n
