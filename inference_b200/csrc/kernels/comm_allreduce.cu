@@ -75,7 +75,8 @@ __device__ __forceinline__ bool peer_barrier(const ArParams& p, uint32_t epoch, 
   __syncthreads();
   if ((int)threadIdx.x < p.world) {
     const int peer = threadIdx.x;
-    __threadfence_system();
+    // The release store alone orders everything this rank wrote before the barrier: earlier kernels' writes are
+    // visible to this thread at the kernel boundary and a system-scope release is cumulative over them.
     st_release_sys(p.peer_flags[peer] + (size_t)blockIdx.x * MAX_RANKS + p.rank, epoch);
     const uint32_t* mine = p.peer_flags[p.rank] + (size_t)blockIdx.x * MAX_RANKS + peer;
     uint64_t t0 = 0;
