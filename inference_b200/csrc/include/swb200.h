@@ -34,6 +34,11 @@ int swb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* D, int l
                   swb_stream_t stream);
 size_t swb_gemm_workspace_min(void);
 
+/* Grouped GEMM (mixture of experts): rows [128 i, 128 i + 128) of A [T, K] multiply group group_of_mtile[i] of the
+ * stacked weight W [groups * N, K]; negative entries skip the tile. T is a multiple of 128; the table is device memory. */
+int swb_gemm_bf16_grouped(const void* A, int lda, const void* W, int ldw, int groups, const int* group_of_mtile, void* D,
+                          int ldd, int T, int N, int K, int act, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -101,6 +101,30 @@ int swb_gemm_bf16_scatter_rows(const void* A, int lda, const void* W, int ldw, i
   return swb::gemm_bf16_launch(a, reinterpret_cast<cudaStream_t>(stream));
 }
 
+// Grouped GEMM for mixture-of-experts layers: rows [128 * i, 128 * i + 128) of A multiply weight group
+// group_of_mtile[i] of the stacked W [groups * N, K]; tiles whose entry is negative are skipped (their output rows
+// are left untouched). T must be a multiple of 128; the table lives in device memory, so routing never touches the host.
+int swb_gemm_bf16_grouped(const void* A, int lda, const void* W, int ldw, int groups, const int* group_of_mtile, void* D,
+                          int ldd, int T, int N, int K, int act, void* stream) {
+  if (groups <= 0 || !group_of_mtile || T % 128 != 0) return -3;
+  swb::GemmArgs a{};
+  a.A = A;
+  a.lda = lda;
+  a.W = W;
+  a.ldw = ldw;
+  a.D = D;
+  a.ldd = ldd;
+  a.T = T;
+  a.N = N;
+  a.K = K;
+  a.act = act;
+  a.force_mode = 0;
+  a.force_ctas = -1;
+  a.group_of_mtile = group_of_mtile;
+  a.groups = groups;
+  return swb::gemm_bf16_launch(a, reinterpret_cast<cudaStream_t>(stream));
+}
+
 size_t swb_gemm_workspace_min(void) { return swb::SWB_GEMM_COUNTER_BYTES + (size_t)(8u << 20); }
 
 int swb_sm_count(void) { return swb::device_sm_count(); }

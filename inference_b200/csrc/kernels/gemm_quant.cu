@@ -16,6 +16,7 @@
 #include "gemm_tcgen05.cuh"
 
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 #include <algorithm>
 
@@ -44,6 +45,9 @@ struct QParams {
   const bf16* bias;
   float* workspace;            // [tiles * splits][BLOCK_N * 128] fp32
   int* counters;               // [tiles]
+  const uint8_t* sf;           // NVFP4 only: unsigned E4M3 block scales in 128 x 4 atoms (see DqNvfp4)
+  int sf_m_atoms;              // NVFP4 only: row atoms of the scale tensor = ceil(N / 128)
+  float gscale;                // NVFP4 only: per-tensor fp32 scale
 };
 
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
@@ -200,6 +204,58 @@ struct DqAffine {   // groups of 64: packed uint32 little-endian fields, w = sca
         out[c * 2] = make_uint4(o[0], o[1], o[2], o[3]);
         out[c * 2 + 1] = make_uint4(o[4], o[5], o[6], o[7]);
       }
+    }
+  }
+};
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
+// NVFP4 (the reference's container: candle-gen/src/quant/nvfp4.rs:90-358): E2M1 codes, two per byte (even column in
+// the low nibble), one unsigned E4M3 scale per 16 columns and one fp32 scale per tensor; w = e2m1 * e4m3 * global.
+// The scale bytes sit in 128-row x 4-block atoms: atom (row / 128) + m_atoms * (block / 4), byte
+// (row % 32) * 16 + (row % 128 / 32) * 4 + block % 4 - so the four scales of a 64-column group are one aligned word.
+struct DqNvfp4 {
+  static constexpr int RAW_ROW = 128, RAW_STAGES = 4, BOXES = 1;
+  static constexpr bool SWIZZLED = true;
+  // eight E2M1 codes (nibble i = column i) -> eight bf16 in column order, times the block scale. The magnitude bits
+  // index two 8-byte tables (high and low bytes of 0, .5, 1, 1.5, 2, 3, 4, 6 in bf16) through prmt; the sign bits
+  // reach bit 7 of each high byte through prmt's sign-replication mode.
+  static __device__ __forceinline__ uint4 decode8(uint32_t x, uint32_t s2) {
+    const uint32_t HL = 0x3F3F3F00u, HH = 0x40404040u, LL = 0xC0800000u, LH = 0xC0804000u;
+    const uint32_t sel = x & 0x77777777u, selb = sel >> 16, xs = x << 4;
+    uint32_t hiA = prmt(HL, HH, sel), loA = prmt(LL, LH, sel), hiB = prmt(HL, HH, selb), loB = prmt(LL, LH, selb);
+    hiA |= prmt(xs, x, 0xD9C8u) & 0x80808080u;
+    hiB |= prmt(xs, x, 0xFBEAu) & 0x80808080u;
+    return make_uint4(mul_bf16x2(prmt(loA, hiA, 0x5140u), s2), mul_bf16x2(prmt(loA, hiA, 0x7362u), s2),
+                      mul_bf16x2(prmt(loB, hiB, 0x5140u), s2), mul_bf16x2(prmt(loB, hiB, 0x7362u), s2));
+  }
+  template <bool SWZ>
+  static __device__ __forceinline__ void run(const uint8_t* blk, int srow, const QParams& p, int grow, int kb, int g,
+                                             uint4* out) {
+    const size_t atom = (size_t)(grow >> 7) + (size_t)p.sf_m_atoms * (size_t)(kb * 4 + g);
+    const uint32_t sfw = *reinterpret_cast<const uint32_t*>(p.sf + atom * 512 + (grow & 31) * 16 + ((grow & 127) >> 5) * 4);
+    const __half2_raw h01 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(sfw & 0xFFFFu), __NV_E4M3);
+    const __half2_raw h23 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(sfw >> 16), __NV_E4M3);
+    const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&h01));
+    const float2 f23 = __half22float2(*reinterpret_cast<const __half2*>(&h23));
+    const uint32_t s2[4] = {dup_bf16(f01.x * p.gscale), dup_bf16(f01.y * p.gscale), dup_bf16(f23.x * p.gscale),
+                            dup_bf16(f23.y * p.gscale)};
+    const int x7 = SWZ ? (srow & 7) : 0;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {   // the 64-column group is 32 bytes: chunks 2g, 2g + 1 of the 128-byte row
+      const uint4 q = *reinterpret_cast<const uint4*>(blk + (((2 * g + c) ^ x7) << 4));
+      out[c * 4 + 0] = decode8(q.x, s2[c * 2]);
+      out[c * 4 + 1] = decode8(q.y, s2[c * 2]);
+      out[c * 4 + 2] = decode8(q.z, s2[c * 2 + 1]);
+      out[c * 4 + 3] = decode8(q.w, s2[c * 2 + 1]);
     }
   }
 };
@@ -492,7 +548,7 @@ int launch_fmt(int block_n, const CUtensorMap& ta, const QParams& p, int tiles, 
 }
 
 long long row_bytes_for(int fmt, int K) {
-  return fmt == 0 ? (long long)K / 256 * 144 : fmt == 1 ? (long long)K / 32 * 34 : fmt == 2 ? K / 2 : K;
+  return fmt == 0 ? (long long)K / 256 * 144 : fmt == 1 ? (long long)K / 32 * 34 : (fmt == 2 || fmt == 4) ? K / 2 : K;
 }
 
 }  // namespace
@@ -501,12 +557,15 @@ long long row_bytes_for(int fmt, int K) {
 extern "C" {
 
 // Packed [N, K] weights (formats as for swb_gemm_quant) -> dense bf16 [N, K].
-int swb_dequant_rows(int fmt, const void* Wq, const void* scales, const void* biases, void* out, int N, int K,
-                     void* stream) {
+static int dequant_rows_impl(int fmt, const void* Wq, const void* scales, const void* biases, float gscale, void* out,
+                             int N, int K, void* stream) {
   using namespace swb;
   if (N <= 0) return 0;
-  if (K <= 0 || K % QBK != 0 || fmt < 0 || fmt > 3) return -3;
+  if (K <= 0 || K % QBK != 0 || fmt < 0 || fmt > 4) return -3;
   QParams p{};
+  p.sf = reinterpret_cast<const uint8_t*>(scales);
+  p.sf_m_atoms = (N + 127) / 128;
+  p.gscale = gscale;
   p.w = reinterpret_cast<const uint8_t*>(Wq);
   p.scales = reinterpret_cast<const bf16*>(scales);
   p.biases = reinterpret_cast<const bf16*>(biases);
@@ -520,23 +579,41 @@ int swb_dequant_rows(int fmt, const void* Wq, const void* scales, const void* bi
     case 0: return launch_dequant<DqQ4K>(p, o, s);
     case 1: return launch_dequant<DqQ80>(p, o, s);
     case 2: return launch_dequant<DqAffine<4>>(p, o, s);
-    default: return launch_dequant<DqAffine<8>>(p, o, s);
+    case 3: return launch_dequant<DqAffine<8>>(p, o, s);
+    default: return launch_dequant<DqNvfp4>(p, o, s);
   }
+}
+
+int swb_dequant_rows(int fmt, const void* Wq, const void* scales, const void* biases, void* out, int N, int K,
+                     void* stream) {
+  if (fmt > 3) return -3;
+  return dequant_rows_impl(fmt, Wq, scales, biases, 1.f, out, N, K, stream);
+}
+
+// NVFP4 weights -> dense bf16 [N, K]. packed: [N, K / 2] bytes; sf: swizzled unsigned E4M3 scales
+// (ceil(N / 128) * 128 x ceil(K / 64) * 4 bytes, 16-byte aligned); global_scale: the tensor's fp32 scale.
+int swb_dequant_nvfp4(const void* packed, const void* sf, float global_scale, void* out, int N, int K, void* stream) {
+  if (!sf || (reinterpret_cast<uintptr_t>(sf) & 3)) return -3;
+  return dequant_rows_impl(4, packed, sf, nullptr, global_scale, out, N, K, stream);
 }
 
 // fmt: 0 Q4_K, 1 Q8_0, 2 affine 4-bit (group 64), 3 affine 8-bit (group 64). A: bf16 [T <= 64, K] (lda elements);
 // Wq: packed [N rows]; scales / biases: bf16 [N, K/64] for fmt 2 / 3 (null otherwise); D: bf16 [T, N] (ldd).
 // K must be a multiple of 256. workspace: as for swb_gemm_bf16 (counters zeroed once, then fp32 partial tiles).
-int swb_gemm_quant(int fmt, const void* A, int lda, const void* Wq, const void* scales, const void* biases, void* D,
-                   int ldd, int T, int N, int K, const void* bias, void* workspace, size_t workspace_bytes,
-                   int force_splits, void* stream) {
+static int gemm_quant_impl(int fmt, const void* A, int lda, const void* Wq, const void* scales, const void* biases,
+                           float gscale, void* D, int ldd, int T, int N, int K, const void* bias, void* workspace,
+                           size_t workspace_bytes, int force_splits, void* stream) {
   using namespace swb;
   if (T <= 0 || N <= 0) return 0;
   if (T > 64 || K <= 0 || K % QBK != 0 || (lda % 8) != 0 || (reinterpret_cast<uintptr_t>(A) & 15) ||
-      (reinterpret_cast<uintptr_t>(Wq) & 15) || fmt < 0 || fmt > 3)
+      (reinterpret_cast<uintptr_t>(Wq) & 15) || fmt < 0 || fmt > 4)
     return -3;
   if ((fmt == 2 || fmt == 3) && (!scales || !biases)) return -3;
+  if (fmt == 4 && (!scales || (reinterpret_cast<uintptr_t>(scales) & 3))) return -3;
   QParams p{};
+  p.sf = reinterpret_cast<const uint8_t*>(scales);
+  p.sf_m_atoms = (N + 127) / 128;
+  p.gscale = gscale;
   p.w = reinterpret_cast<const uint8_t*>(Wq);
   p.scales = reinterpret_cast<const bf16*>(scales);
   p.biases = reinterpret_cast<const bf16*>(biases);
@@ -567,8 +644,26 @@ int swb_gemm_quant(int fmt, const void* A, int lda, const void* Wq, const void* 
     case 0: return launch_fmt<DqQ4K>(block_n, tm, p, tiles, s);
     case 1: return launch_fmt<DqQ80>(block_n, tm, p, tiles, s);
     case 2: return launch_fmt<DqAffine<4>>(block_n, tm, p, tiles, s);
-    default: return launch_fmt<DqAffine<8>>(block_n, tm, p, tiles, s);
+    case 3: return launch_fmt<DqAffine<8>>(block_n, tm, p, tiles, s);
+    default: return launch_fmt<DqNvfp4>(block_n, tm, p, tiles, s);
   }
+}
+
+int swb_gemm_quant(int fmt, const void* A, int lda, const void* Wq, const void* scales, const void* biases, void* D,
+                   int ldd, int T, int N, int K, const void* bias, void* workspace, size_t workspace_bytes,
+                   int force_splits, void* stream) {
+  if (fmt > 3) return -3;
+  return gemm_quant_impl(fmt, A, lda, Wq, scales, biases, 1.f, D, ldd, T, N, K, bias, workspace, workspace_bytes,
+                         force_splits, stream);
+}
+
+// D[T <= 64, N] = A[T, K] * dequant(NVFP4 W[N, K])^T + bias: weight-only FP4 with bf16 activations (the reference's
+// W4A16 regime, candle-gen/src/quant/nvfp4_linear.rs:80-88). Operands as for swb_dequant_nvfp4.
+int swb_gemm_nvfp4(const void* A, int lda, const void* packed, const void* sf, float global_scale, void* D, int ldd,
+                   int T, int N, int K, const void* bias, void* workspace, size_t workspace_bytes, int force_splits,
+                   void* stream) {
+  return gemm_quant_impl(4, A, lda, packed, sf, nullptr, global_scale, D, ldd, T, N, K, bias, workspace,
+                         workspace_bytes, force_splits, stream);
 }
 
 }  // extern "C"

@@ -83,11 +83,18 @@ struct SegIter {
       s.kb1 = min(p.kblocks_total, s.kb0 + (it_end - it));
       it += s.kb1 - s.kb0;
     } else {
-      if (next_tile >= p.tiles_m * p.tiles_n) return false;
-      s.tile = next_tile;
+      // grouped mode: tiles of row blocks without a weight group are passed over; every role walks the
+      // same table, so the sequences stay identical
+      for (;;) {
+        if (next_tile >= p.tiles_m * p.tiles_n) return false;
+        s.tile = next_tile;
+        next_tile += (int)gridDim.x;
+        if (!p.group_of_mtile) break;
+        coords(s);
+        if (__ldg(p.group_of_mtile + s.tm) >= 0) break;
+      }
       s.kb0 = 0;
       s.kb1 = p.kblocks_total;
-      next_tile += (int)gridDim.x;
     }
     s.first = (nseg++ == 0);
     coords(s);
@@ -350,12 +357,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       int issued = 0;
       SegIter iter(p);
       while (ok && iter.next(c)) {
+        const int b_row = c.tn * BLOCK_N + (p.group_of_mtile ? __ldg(p.group_of_mtile + c.tm) * p.group_rows : 0);
         for (int kb = c.kb0; kb < c.kb1; ++kb, ++issued) {
           uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
           uint8_t* sb = sa + Cfg::A_BYTES;
           if (issued < prefetched) {
             // the A half of this stage is already in flight (first pass over the ring: stage == issued)
-            tma_load_2d_hint(sb, &tmap_b, &bar_full[stage], kb * BK, c.tn * BLOCK_N, pol_b);
+            tma_load_2d_hint(sb, &tmap_b, &bar_full[stage], kb * BK, b_row, pol_b);
             if (++stage == STAGES) {
               stage = 0;
               phase ^= 1;
@@ -367,7 +375,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           outstanding &= ~(1u << stage);
           mbar_arrive_expect_tx(&bar_full[stage], Cfg::STAGE_BYTES);
           tma_load_2d_hint(sa, &tmap_a, &bar_full[stage], kb * BK, c.tm * BM, pol_a);
-          tma_load_2d_hint(sb, &tmap_b, &bar_full[stage], kb * BK, c.tn * BLOCK_N, pol_b);
+          tma_load_2d_hint(sb, &tmap_b, &bar_full[stage], kb * BK, b_row, pol_b);
           outstanding |= 1u << stage;
           issue_phase_bits = (issue_phase_bits & ~(1u << stage)) | (phase << stage);
           if (++stage == STAGES) {
@@ -701,10 +709,14 @@ int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
     if (a.scatter->enabled == 2 && a.scatter->rows_per_rank <= 0) return -3;
     swapped = 0;
   }
+  if (a.group_of_mtile) {
+    if (a.scatter || a.groups <= 0 || a.bias || a.residual) return -3;
+    swapped = 0;
+  }
   if (swapped < 0) swapped = (a.T <= 256) ? 1 : 0;
   // decode-sized problems with at most two weight tiles per SM: the two-CTAs-per-SM cluster kernel (split-K over a
   // cluster with a DSMEM reduction when tiles are few, plain whole tiles otherwise)
-  if (!a.scatter && (a.force_mode == 2 || (a.force_mode < 0 && gemm_decode_cluster_supported(a.T) && (a.N + BM - 1) / BM <= 2 * sms &&
+  if (!a.scatter && !a.group_of_mtile && (a.force_mode == 2 || (a.force_mode < 0 && gemm_decode_cluster_supported(a.T) && (a.N + BM - 1) / BM <= 2 * sms &&
                             (a.K + BK - 1) / BK >= 8))) {
     if (!gemm_decode_cluster_supported(a.T)) return -4;
     return gemm_decode_cluster_launch(a, a.force_mode == 2 ? a.force_ctas : 0, stream);
@@ -771,8 +783,10 @@ int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
     p.tiles_n = (a.N + block_n - 1) / block_n;
     int r = make_tmap_bf16_2d(&ta, a.A, a.T, a.K, a.lda, BM);
     if (r) return r;
-    r = make_tmap_bf16_2d(&tb, a.W, a.N, a.K, a.ldw, block_n);
+    r = make_tmap_bf16_2d(&tb, a.W, a.group_of_mtile ? a.groups * a.N : a.N, a.K, a.ldw, block_n);
     if (r) return r;
+    p.group_of_mtile = a.group_of_mtile;
+    p.group_rows = a.N;
     const size_t esz = a.out_fp32 ? 4 : 2;
     p.vec_ok = ((a.ldd * esz) % 16 == 0) && ((reinterpret_cast<uintptr_t>(a.D) & 15) == 0) &&
                (!a.bias || (reinterpret_cast<uintptr_t>(a.bias) & 15) == 0) &&
@@ -793,6 +807,7 @@ int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
   // exactly; large token counts keep whole tiles per CTA (no partial-tile reduction traffic)
   bool stream_k = ws_ok && a.force_ctas >= 0 && swapped && (tiles % sms != 0) && total_iters >= 2;
   if (a.force_ctas > 0 && ws_ok) stream_k = true;
+  if (a.group_of_mtile) stream_k = false;   // whole tiles only: the skip table is indexed by row tile
   if (stream_k) {
     const int per_sm = 1;
     int want = a.force_ctas > 0 ? std::min(a.force_ctas, per_sm * sms) : per_sm * sms;

@@ -52,6 +52,10 @@ struct GemmParams {
   unsigned long long* trace;  // optional [grid][8] globaltimer stamps of kernel phases (profiling aid)
   GemmScatter scatter;
   int staged_epilogue;   // tokens-as-M, bf16 output: stage rows in shared memory and store 256-byte runs
+  // grouped (mixture-of-experts) mode: row tile tm multiplies weight group group_of_mtile[tm] (rows
+  // [g * group_rows, g * group_rows + N) of the stacked weight); a negative entry skips the tile
+  const int* group_of_mtile;
+  int group_rows;
 };
 
 // User-level problem: D[T, N] = act(A[T, K] * W[N, K]^T + bias[N]) + residual[T, N].
@@ -74,6 +78,8 @@ struct GemmArgs {
   int force_block_n;  // 0 auto
   int force_ctas;     // 0 auto; > 0 stream-K over that many CTAs; < 0 whole tiles only
   const GemmScatter* scatter = nullptr;
+  const int* group_of_mtile = nullptr;   // device [ceil(T / 128)]: weight group per 128-row tile, < 0 = skip
+  int groups = 0;                        // W is [groups * N, K] when group_of_mtile is set
 };
 
 int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream);

@@ -24,6 +24,16 @@ def _splits_for(batch: int, kv_heads: int, max_kv: int, sms: int = 148) -> int:
     return s
 
 
+def _bucket(batch: int, max_batch: int) -> int:
+    """Batch size a decode graph is captured for: exact up to 8 rows, then the next multiple of 8 (of 16
+    above 64). A continuous-batching job whose lanes drain one by one then replays a handful of graphs
+    instead of capturing one per live-lane count."""
+    if batch <= 8:
+        return batch
+    step = 8 if batch <= 64 else 16
+    return min(max_batch, (batch + step - 1) // step * step)
+
+
 @dataclass
 class _DecodeGraph:
     graph: torch.cuda.CUDAGraph
@@ -38,7 +48,7 @@ class ModelRunner:
         self.model, self.pool = model, pool
         self.max_batch, self.max_seq_len = max_batch, max_seq_len
         self.max_blocks = (max_seq_len + pool.block_size - 1) // pool.block_size
-        self.use_graphs = use_graphs and not getattr(model, "has_moe", False)   # MoE routing is host driven
+        self.use_graphs = use_graphs        # mixture-of-experts routing is device side, so those models capture too
         dev = model.device
         model.ensure_rope(max_seq_len + 64)
         # static decode-step buffers; one packed int64 staging area so a step is a single H2D copy
@@ -57,6 +67,8 @@ class ModelRunner:
         self._host_tokens = torch.zeros(max_batch, dtype=torch.int64).pin_memory() if dev.type == "cuda" else \
             torch.zeros(max_batch, dtype=torch.int64)
         self._graphs: dict[tuple[int, int, bool], _DecodeGraph] = {}
+        self.pad_batches = self.use_graphs      # decode batches are padded to a bucket so graphs are reused
+        self.captures = 0
         self.h2d_bytes_last = 0
         self.d2h_bytes_last = 0
         self.launches_last = 0
@@ -101,7 +113,9 @@ class ModelRunner:
         return self.model.greedy_tokens(hidden)
 
     # ---- decode (graph-captured, one token per sequence) ---------------------------------------------
-    def _fill_decode_meta(self, seqs: list[PagedSequence], tokens: list[int]) -> int:
+    def _fill_decode_meta(self, seqs: list[PagedSequence], tokens: list[int], pad_to: int = 0) -> int:
+        """Writes the step metadata of the live rows; rows len(seqs)..pad_to-1 become copies of row 0 (same
+        token, position, slot and block table), so they recompute row 0 and store identical K / V bytes."""
         MB = self.max_batch
         h, table = self._host_np, self._host_table_np
         max_kv = 0
@@ -122,6 +136,12 @@ class ModelRunner:
             elif written < nb:
                 table[i, written:nb] = s.blocks[written:nb]
                 self._row_state[i] = (s.uid, s.epoch, nb)
+        if pad_to > len(seqs):
+            nb0 = len(seqs[0].blocks)
+            for i in range(len(seqs), pad_to):
+                h[i], h[MB + i], h[2 * MB + i], h[3 * MB + i] = h[0], h[MB], h[2 * MB], h[3 * MB]
+                table[i, :nb0] = table[0, :nb0]
+                self._row_state[i] = (-1, -1, 0)
         return max_kv
 
     def _unpack_meta(self, B: int, skip_ids: bool = False) -> None:
@@ -152,24 +172,27 @@ class ModelRunner:
         host tensor [B] (after a stream sync) or device fp32 logits [B, vocab]."""
         B = len(seqs)
         assert B <= self.max_batch
-        max_kv = self._fill_decode_meta(seqs, tokens)
+        Bp = _bucket(B, self.max_batch) if self.pad_batches else B
+        max_kv = self._fill_decode_meta(seqs, tokens, Bp)
         self._dev_meta.copy_(self._host_meta, non_blocking=True)
         self.h2d_bytes_last = self._host_meta.numel() * 4
-        splits = _splits_for(B, self.model.hkv, max_kv)
-        key = (B, splits, want_logits)
+        splits = _splits_for(Bp, self.model.hkv, max_kv)
+        key = (Bp, splits, want_logits)
         if not self.use_graphs or self.model.device.type != "cuda":
-            toks, logits = self._decode_body(B, splits, want_logits)
+            toks, logits = self._decode_body(Bp, splits, want_logits)
             self.launches_last = self.model.launches
         else:
             g = self._graphs.get(key)
             if g is None:
-                g = self._capture(B, splits, want_logits)
+                g = self._capture(Bp, splits, want_logits)
                 self._graphs[key] = g
+                self.captures += 1
             g.graph.replay()
             toks, logits = g.tokens_out, g.logits_out
             self.launches_last = g.launches
         if want_logits:
-            return logits
+            return logits[:B]
+        toks = toks[:B]
         self._host_tokens[:B].copy_(toks, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         self.d2h_bytes_last = B * 8

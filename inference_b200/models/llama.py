@@ -10,6 +10,7 @@ speculative verify all share one forward.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import torch
@@ -59,8 +60,8 @@ class MoeWeights:
     """Top-k routed experts with an optional (sigmoid-gated) shared expert (Qwen2-MoE: candle-llm models/llama.rs
     MoE FFN). Expert FFNs are sharded like the dense one: gate/up by rows, down by columns."""
     router: torch.Tensor                      # [E, H], replicated
-    gate_up: list[torch.Tensor]               # E x [2 * F_local, H]
-    down: list[torch.Tensor]                  # E x [H, F_local]
+    gate_up: torch.Tensor                     # [E, 2 * F_local, H] (stacked: the grouped GEMM indexes experts by row)
+    down: torch.Tensor                        # [E, H, F_local]
     shared_gate_up: torch.Tensor | None
     shared_down: torch.Tensor | None
     shared_gate: torch.Tensor | None          # [1, H]
@@ -155,8 +156,9 @@ class LlamaGpu:
                 sg = w.get(f"{p}.mlp.shared_expert_gate.weight")
                 moe = MoeWeights(
                     router=dev16(get(f"{p}.mlp.gate.weight")),
-                    gate_up=[gu(f"{p}.mlp.experts.{e}") for e in range(E)],
-                    down=[dev16(_shard_cols(get(f"{p}.mlp.experts.{e}.down_proj.weight"), r, P)) for e in range(E)],
+                    gate_up=torch.stack([gu(f"{p}.mlp.experts.{e}") for e in range(E)]).contiguous(),
+                    down=torch.stack([dev16(_shard_cols(get(f"{p}.mlp.experts.{e}.down_proj.weight"), r, P))
+                                      for e in range(E)]).contiguous(),
                     shared_gate_up=gu(f"{p}.mlp.shared_expert") if has_shared else None,
                     shared_down=dev16(_shard_cols(get(f"{p}.mlp.shared_expert.down_proj.weight"), r, P))
                     if has_shared else None,
@@ -331,17 +333,57 @@ class LlamaGpu:
         return final
 
     def _moe_ffn(self, h: torch.Tensor, m: MoeWeights) -> torch.Tensor:
-        """Sparse FFN on this rank's shard (partial sums; the caller all-reduces). The routing is data dependent
-        (experts are visited by a host loop over those that received tokens), so models with MoE layers decode
-        eagerly instead of replaying a CUDA graph."""
+        """Sparse FFN on this rank's shard (partial sums; the caller all-reduces). Routing stays on the device:
+        the (token, expert) pairs are sorted by expert into a buffer whose per-expert segments are padded to the
+        128-row GEMM tile, one grouped GEMM per projection picks each tile's expert from a device table, and the
+        weighted results are summed back per token. Every shape is a function of the token count only, so the step
+        can be captured in a CUDA graph. (The reference visits experts serially after a host top-k:
+        candle-llm/src/models/llama.rs:1415-1488.)"""
         moe = self.cfg.moe
         act = self.cfg.mlp_activation
+        T, H = h.shape
+        E, k = m.router.shape[0], moe.num_experts_per_tok
         logits = ops.gemm_bf16(h, m.router, out_dtype=torch.float32)
         probs = torch.softmax(logits, dim=-1)
-        topv, topi = probs.topk(moe.num_experts_per_tok, dim=-1)
+        topv, topi = probs.topk(k, dim=-1)
         if moe.norm_topk_prob:
             topv = topv / topv.sum(-1, keepdim=True)
         topv = topv * moe.routed_scaling_factor
+        if h.device.type != "cuda" or os.environ.get("SWB_MOE") == "loop":
+            out = self._moe_experts_loop(h, m, topv, topi)
+        else:
+            dev = h.device
+            flat_e = topi.reshape(-1)
+            order = torch.argsort(flat_e, stable=True)
+            sorted_e = flat_e.index_select(0, order)
+            counts = torch.zeros(E, dtype=torch.int64, device=dev).scatter_add_(0, flat_e, torch.ones_like(flat_e))
+            padded = (counts + 127) // 128 * 128
+            pad_end = torch.cumsum(padded, 0)
+            seg_start = torch.cumsum(counts, 0) - counts
+            dest = (pad_end - padded).index_select(0, sorted_e) + \
+                (torch.arange(T * k, device=dev) - seg_start.index_select(0, sorted_e))
+            R = (T * k + E * 127 + 127) // 128 * 128          # static bound on the padded row count
+            tile_start = torch.arange(R // 128, device=dev) * 128
+            tile_e = torch.searchsorted(pad_end, tile_start, right=True)
+            tile_e = torch.where(tile_e < E, tile_e, torch.full_like(tile_e, -1)).to(torch.int32)
+            src_tok = order // k
+            xp = torch.zeros((R, H), dtype=torch.bfloat16, device=dev)
+            xp.index_copy_(0, dest, h.index_select(0, src_tok))
+            gu = ops.gemm_bf16_grouped(xp, m.gate_up, tile_e)
+            y = ops.gemm_bf16_grouped(ops.gated_act_mul(gu, act), m.down, tile_e)
+            wgt = topv.reshape(-1).index_select(0, order)
+            out = torch.zeros((T, H), dtype=torch.float32, device=dev)
+            out.index_add_(0, src_tok, y.index_select(0, dest).float() * wgt[:, None])
+        if m.shared_gate_up is not None:
+            y = ops.gemm_bf16(ops.gated_act_mul(ops.gemm_bf16(h, m.shared_gate_up), act), m.shared_down).float()
+            if m.shared_gate is not None:
+                y = y * torch.sigmoid(ops.gemm_bf16(h, m.shared_gate, out_dtype=torch.float32)[:, :1])
+            out += y
+        return out.to(torch.bfloat16)
+
+    def _moe_experts_loop(self, h: torch.Tensor, m: MoeWeights, topv: torch.Tensor, topi: torch.Tensor) -> torch.Tensor:
+        """Host loop over the experts that received tokens (comparison path, SWB_MOE=loop)."""
+        act = self.cfg.mlp_activation
         out = torch.zeros(h.shape, dtype=torch.float32, device=h.device)
         for e in torch.unique(topi).tolist():
             sel = topi == e
@@ -350,12 +392,7 @@ class LlamaGpu:
             x = h.index_select(0, rows)
             y = ops.gemm_bf16(ops.gated_act_mul(ops.gemm_bf16(x, m.gate_up[e]), act), m.down[e])
             out.index_add_(0, rows, y.float() * wgt[:, None])
-        if m.shared_gate_up is not None:
-            y = ops.gemm_bf16(ops.gated_act_mul(ops.gemm_bf16(h, m.shared_gate_up), act), m.shared_down).float()
-            if m.shared_gate is not None:
-                y = y * torch.sigmoid(ops.gemm_bf16(h, m.shared_gate, out_dtype=torch.float32)[:, :1])
-            out += y
-        return out.to(torch.bfloat16)
+        return out
 
     @property
     def has_moe(self) -> bool:

@@ -50,6 +50,27 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, *, bias: torch.Tensor | None = N
     return out
 
 
+def gemm_bf16_grouped(a: torch.Tensor, w: torch.Tensor, tile_groups: torch.Tensor, *, act: str | None = None,
+                      out: torch.Tensor | None = None) -> torch.Tensor:
+    """Grouped GEMM (replaces the reference's per-expert serial matmuls, candle-llm/src/models/llama.rs:1415-1488).
+
+    a [R, K] with R a multiple of 128; w [G, N, K]; tile_groups int32 [R / 128] on the device: rows
+    128*i .. 128*i+127 of a use w[tile_groups[i]]; a negative entry skips the tile (output rows untouched)."""
+    require_cuda(a, w, tile_groups)
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and tile_groups.dtype == torch.int32
+    assert a.dim() == 2 and w.dim() == 3 and w.is_contiguous() and a.stride(1) == 1 and a.shape[1] == w.shape[2]
+    R, K = a.shape
+    G, N, _ = w.shape
+    assert R % 128 == 0 and tile_groups.numel() == R // 128 and tile_groups.is_contiguous()
+    if out is None:
+        out = torch.empty((R, N), dtype=torch.bfloat16, device=a.device)
+    assert out.shape == (R, N) and out.stride(1) == 1 and out.dtype == torch.bfloat16
+    rc = kernels().swb_gemm_bf16_grouped(a.data_ptr(), a.stride(0), w.data_ptr(), K, G, tile_groups.data_ptr(),
+                                         out.data_ptr(), out.stride(0), R, N, K, ACT[act], stream_ptr())
+    check(rc, "swb_gemm_bf16_grouped")
+    return out
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, **kw) -> torch.Tensor:
     """`x @ w^T (+ bias)` over the last dimension of x."""
     lead = x.shape[:-1]

@@ -91,3 +91,29 @@ def test_cluster_split_k_decode(T, cluster):
     y1 = _check(T, 1024, 2048, mode=2, ctas=cluster, bias=True, residual=True, act="silu")
     assert torch.equal(y0, y1)
     _check(T, 1000, 1096, mode=2, ctas=cluster, out_dtype=torch.float32)
+
+
+@pytest.mark.parametrize("N,K", [(512, 256), (2816, 2048), (200, 320)])
+def test_grouped_gemm_matches_per_group_matmul(N, K):
+    """Each 128-row tile multiplies the weight group its table entry names; skipped tiles stay untouched."""
+    from inference_b200 import ops
+
+    G = 5
+    g = torch.Generator(device="cuda").manual_seed(0)
+    w = (torch.randn(G, N, K, device="cuda", generator=g) * 0.05).bfloat16()
+    table = torch.tensor([3, 0, -1, 4, 4, 1, -1, 2], dtype=torch.int32, device="cuda")
+    R = table.numel() * 128
+    a = torch.randn(R, K, device="cuda", generator=g).bfloat16()
+    out = torch.full((R, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    ops.gemm_bf16_grouped(a, w, table, out=out)
+    ops.check_status()
+    for i, e in enumerate(table.tolist()):
+        rows = slice(i * 128, (i + 1) * 128)
+        if e < 0:
+            assert torch.all(out[rows] == 7.0)
+            continue
+        ref = a[rows].float() @ w[e].float().t()
+        torch.testing.assert_close(out[rows].float(), ref, rtol=2e-2, atol=2e-2)
+    act = ops.gemm_bf16_grouped(a, w, table, act="silu")
+    ref = torch.nn.functional.silu(a[:128].float() @ w[3].float().t())
+    torch.testing.assert_close(act[:128].float(), ref, rtol=2e-2, atol=2e-2)

@@ -123,3 +123,31 @@ def test_quantised_model_matches_oracle_on_dequantised_weights(fmt):
             ref = oracle.decode_logits(torch.tensor([[toks[i]]], device="cuda"), caches[i], caches[i].offset)[0]
             assert (lg[i] - ref).abs().max().item() < 0.1 * max(1.0, ref.abs().max().item()), (fmt, step, i)
         toks = [int(lg[i].argmax()) for i in range(2)]
+
+
+def test_padded_decode_buckets_reuse_graphs_and_match_exact_batches():
+    """Decode batches padded to a graph bucket produce the tokens of the unpadded eager step, and a job
+    whose batch shrinks one lane at a time captures one graph per bucket, not one per batch size."""
+    from inference_b200.engine.kv_pool import PagedKvPool, PagedSequence
+    from inference_b200.engine.runner import ModelRunner, _bucket
+
+    assert [_bucket(b, 128) for b in (1, 8, 9, 16, 17, 64, 65, 127)] == [1, 8, 16, 16, 24, 64, 80, 128]
+    cfg = _small_cfg()
+    _, model, _, _ = _build(cfg, seed=5)
+    outs = []
+    for padded in (True, False):
+        pool = PagedKvPool(cfg.num_layers, 512, model.hkv, cfg.head_dim, 16, device="cuda")
+        runner = ModelRunner(model, pool, max_batch=32, max_seq_len=256, use_graphs=padded)
+        g = torch.Generator().manual_seed(1)
+        prompts = [torch.randint(0, cfg.vocab_size, (5 + 3 * i,), generator=g).tolist() for i in range(13)]
+        seqs = [PagedSequence(pool) for _ in prompts]
+        toks = runner.prefill(seqs, prompts).tolist()
+        trace = []
+        for step in range(6):
+            toks = runner.decode(seqs, toks).tolist()
+            trace.append(list(toks))
+            seqs, toks = seqs[:-1], toks[:-1]       # one lane finishes per step: 13, 12, ..., 8 live rows
+        outs.append(trace)
+        if padded:
+            assert runner.captures == 2             # buckets 16 and 8
+    assert outs[0] == outs[1]

@@ -36,3 +36,28 @@ def test_large_token_count_uses_dense_path():
     out = quant.linear_quant(a, qw)
     ref = a.float().cpu() @ quant.dequantize_reference(qw).t()
     assert (out.float().cpu() - ref).abs().max().item() < 2e-2 * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("T,N,K", [(1, 256, 512), (16, 384, 1024), (64, 200, 256), (33, 3072, 3072)])
+def test_nvfp4_gemm_and_dequant_match_cpu_container(T, N, K):
+    """The device decode of E2M1 codes and swizzled E4M3 scales reproduces the container's dequantised values
+    exactly (they are bf16-representable up to the scale product), and the fused GEMM matches fp32 matmul on them."""
+    from inference_b200 import ops
+    from inference_b200.ops import nvfp4 as nv
+
+    g = torch.Generator().manual_seed(T + N)
+    w = torch.randn(N, K, generator=g) * 0.05
+    w[1, 3] = 1.5
+    bias = (torch.randn(N, generator=g) * 0.1).bfloat16().cuda()
+    lin = nv.Nvfp4Linear(nv.Nvfp4Tensor.pack(w).to("cuda"), bias)
+    ref_w = lin.t.dequantize()                                     # fp32 on the device, torch ops
+    dense = lin.dense_bf16()
+    ops.check_status()
+    torch.testing.assert_close(dense.float(), ref_w.bfloat16().float(), rtol=1e-2, atol=1e-6)
+    x = torch.randn(T, K, generator=g).bfloat16().cuda()
+    y = lin(x)
+    ops.check_status()
+    ref = x.float() @ dense.float().t() + bias.float()             # the kernel multiplies exactly these bf16 weights
+    torch.testing.assert_close(y.float(), ref, rtol=2e-2, atol=2e-2)
+    big = torch.randn(130, K, generator=g).bfloat16().cuda()       # more than 64 rows: expand + dense GEMM
+    torch.testing.assert_close(lin(big).float(), big.float() @ dense.float().t() + bias.float(), rtol=2e-2, atol=2e-2)
