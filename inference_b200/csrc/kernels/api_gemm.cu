@@ -125,6 +125,8 @@ int swb_gemm_bf16_grouped(const void* A, int lda, const void* W, int ldw, int gr
   return swb::gemm_bf16_launch(a, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int swb_gemm_gated_supported(int T, int N, int K) { return swb::gemm_bf16_gated_supported(T, N, K); }
+
 size_t swb_gemm_workspace_min(void) { return swb::SWB_GEMM_COUNTER_BYTES + (size_t)(8u << 20); }
 
 int swb_sm_count(void) { return swb::device_sm_count(); }

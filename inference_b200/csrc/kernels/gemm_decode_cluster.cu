@@ -256,7 +256,7 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
       }
       const int nvalid = min(8, p.M - feat);
       const size_t off = (size_t)tok * p.ldd + feat;
-      const bool vec = p.vec_ok && nvalid == 8 && ((p.ldd & 7) == 0) && ((feat & 7) == 0) && (!p.residual || (p.ld_res & 7) == 0);
+      const bool vec = p.vec_ok && nvalid == 8 && ((p.ldd & 7) == 0) && ((feat & 7) == 0) && (!p.residual || (p.ld_res & 7) == 0);   // gated pairs: ldd % 8 == 0 keeps the 8-byte stores aligned
       if (vec) {
         if (p.bias) {
           const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + feat));
@@ -267,6 +267,16 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
             acc[2 * j] += t.x;
             acc[2 * j + 1] += t.y;
           }
+        }
+        if (p.act >= SWB_ACT_SWIGLU_PAIRS) {
+          // rows come in (gate, up) pairs: four gated outputs, one 8-byte store
+          const int a1 = p.act == SWB_ACT_SWIGLU_PAIRS ? SWB_ACT_SILU : SWB_ACT_GELU_TANH;
+          uint2 o;
+          __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+          oh[0] = __floats2bfloat162_rn(act_apply(acc[0], a1) * acc[1], act_apply(acc[2], a1) * acc[3]);
+          oh[1] = __floats2bfloat162_rn(act_apply(acc[4], a1) * acc[5], act_apply(acc[6], a1) * acc[7]);
+          *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(p.out) + (size_t)tok * p.ldd + (feat >> 1)) = o;
+          continue;
         }
         if (p.act != SWB_ACT_NONE) {
 #pragma unroll
@@ -292,6 +302,13 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
 #pragma unroll
           for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
           *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + off) = o;
+        }
+      } else if (p.act >= SWB_ACT_SWIGLU_PAIRS) {
+        const int a1 = p.act == SWB_ACT_SWIGLU_PAIRS ? SWB_ACT_SILU : SWB_ACT_GELU_TANH;
+        for (int j = 0; j + 1 < nvalid; j += 2) {
+          const float gte = acc[j] + (p.bias ? __bfloat162float(p.bias[feat + j]) : 0.f);
+          const float up = acc[j + 1] + (p.bias ? __bfloat162float(p.bias[feat + j + 1]) : 0.f);
+          reinterpret_cast<bf16*>(p.out)[(size_t)tok * p.ldd + ((feat + j) >> 1)] = __float2bfloat16(act_apply(gte, a1) * up);
         }
       } else {
         for (int j = 0; j < nvalid; ++j) {

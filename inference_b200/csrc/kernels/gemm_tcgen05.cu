@@ -696,6 +696,13 @@ int launch_bn(int block_n, const CUtensorMap& ta, const CUtensorMap& tb, const G
 
 }  // namespace
 
+// 1 when a gate-up projection of this shape runs in the decode cluster kernel, whose epilogue can apply the gated
+// activation (the same routing rule as in gemm_bf16_launch).
+int gemm_bf16_gated_supported(int T, int N, int K) {
+  return gemm_decode_cluster_supported(T) && (N + BM - 1) / BM <= 2 * device_sm_count() && (K + BK - 1) / BK >= 8 &&
+         (N % 2) == 0;
+}
+
 int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
   if (a.T <= 0 || a.N <= 0 || a.K <= 0) return 0;
   if ((a.K % 8) != 0 || (a.lda % 8) != 0 || (a.ldw % 8) != 0) return -3;
@@ -716,6 +723,11 @@ int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
   if (swapped < 0) swapped = (a.T <= 256) ? 1 : 0;
   // decode-sized problems with at most two weight tiles per SM: the two-CTAs-per-SM cluster kernel (split-K over a
   // cluster with a DSMEM reduction when tiles are few, plain whole tiles otherwise)
+  // gated-pair epilogues exist in the decode cluster kernel only (bf16 output, no residual)
+  const bool pairs = a.act >= SWB_ACT_SWIGLU_PAIRS;
+  if (pairs && (a.scatter || a.group_of_mtile || a.residual || a.out_fp32 || (a.N & 1) || a.force_mode == 0 ||
+                a.force_mode == 1 || !gemm_bf16_gated_supported(a.T, a.N, a.K)))
+    return -3;
   if (!a.scatter && !a.group_of_mtile && (a.force_mode == 2 || (a.force_mode < 0 && gemm_decode_cluster_supported(a.T) && (a.N + BM - 1) / BM <= 2 * sms &&
                             (a.K + BK - 1) / BK >= 8))) {
     if (!gemm_decode_cluster_supported(a.T)) return -4;

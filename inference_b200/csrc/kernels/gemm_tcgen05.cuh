@@ -8,7 +8,10 @@
 
 namespace swb {
 
-enum GemmAct : int { SWB_ACT_NONE = 0, SWB_ACT_SILU = 1, SWB_ACT_GELU_TANH = 2 };
+// 3 / 4: gated pairs. Output features come in (gate, up) row pairs of the weight: out[t, f] = silu|gelu(acc[2f]) * acc[2f+1],
+// so the output is half as wide as the weight has rows (SwiGLU / GeGLU fused into the gate-up projection).
+enum GemmAct : int { SWB_ACT_NONE = 0, SWB_ACT_SILU = 1, SWB_ACT_GELU_TANH = 2, SWB_ACT_SWIGLU_PAIRS = 3,
+                     SWB_ACT_GEGLU_PAIRS = 4 };
 
 // The first SWB_GEMM_COUNTER_BYTES of a GEMM workspace hold per-tile arrival counters (zero between
 // launches: the caller zeroes them once, the kernel restores zero); fp32 split-K partials follow.
@@ -83,6 +86,7 @@ struct GemmArgs {
 };
 
 int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream);
+int gemm_bf16_gated_supported(int T, int N, int K);
 int gemm_decode_cluster_supported(int T);
 int gemm_decode_cluster_launch(const GemmArgs& a, int force_cluster, cudaStream_t stream);
 int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows);

@@ -358,7 +358,8 @@ __global__ void __launch_bounds__(256) rope_kv_write_d128_kernel(
   }
 }
 
-// out[t, f] = act(gu[t, f]) * gu[t, F + f]; act 1 = SiLU (SwiGLU), 2 = tanh-GELU (GeGLU).
+// out[t, f] = act(gu[t, f]) * gu[t, F + f]; act 1 = SiLU (SwiGLU), 2 = tanh-GELU (GeGLU). act 3 / 4: the same two
+// activations on a pair-interleaved projection output, out[t, f] = act(gu[t, 2f]) * gu[t, 2f + 1].
 __global__ void __launch_bounds__(256) gated_act_mul_kernel(const bf16* __restrict__ gu, int ld_gu, bf16* out,
                                                            int ldo, int T, int F, int act) {
   pdl_launch_dependents();
@@ -369,10 +370,24 @@ __global__ void __launch_bounds__(256) gated_act_mul_kernel(const bf16* __restri
   const int t = (int)(idx / nvec);
   const int v = (int)(idx % nvec);
   float g[8], u[8], o[8];
-  unpack8(*reinterpret_cast<const uint4*>(gu + (size_t)t * ld_gu + v * 8), g);
-  unpack8(*reinterpret_cast<const uint4*>(gu + (size_t)t * ld_gu + F + v * 8), u);
+  if (act >= 3) {
+    float lo[8], hi[8];
+    unpack8(*reinterpret_cast<const uint4*>(gu + (size_t)t * ld_gu + v * 16), lo);
+    unpack8(*reinterpret_cast<const uint4*>(gu + (size_t)t * ld_gu + v * 16 + 8), hi);
 #pragma unroll
-  for (int j = 0; j < 8; ++j) o[j] = (act == 2 ? gelu_tanh_f(g[j]) : silu_f(g[j])) * u[j];
+    for (int j = 0; j < 4; ++j) {
+      g[j] = lo[2 * j];
+      u[j] = lo[2 * j + 1];
+      g[4 + j] = hi[2 * j];
+      u[4 + j] = hi[2 * j + 1];
+    }
+  } else {
+    unpack8(*reinterpret_cast<const uint4*>(gu + (size_t)t * ld_gu + v * 8), g);
+    unpack8(*reinterpret_cast<const uint4*>(gu + (size_t)t * ld_gu + F + v * 8), u);
+  }
+  const bool gelu = act == 2 || act == 4;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j] = (gelu ? gelu_tanh_f(g[j]) : silu_f(g[j])) * u[j];
   *reinterpret_cast<uint4*>(out + (size_t)t * ldo + v * 8) = pack8(o);
 }
 

@@ -186,7 +186,7 @@ class LlamaGpu:
                 q_norm=dev16(qn) if qn is not None else None, k_norm=dev16(kn) if kn is not None else None,
                 o=dev16(_shard_cols(get(f"{p}.self_attn.o_proj.weight"), r, P)),
                 post_attn_ln=dev16(post_attn) if post_attn is not None else None, ln2=dev16(ln2),
-                gate_up=dev16(torch.cat([gate, up])), down=dev16(_shard_cols(get(f"{p}.mlp.down_proj.weight"), r, P)),
+                gate_up=dev16(torch.stack([gate, up], dim=1).reshape(2 * gate.shape[0], -1)), down=dev16(_shard_cols(get(f"{p}.mlp.down_proj.weight"), r, P)),
                 post_mlp_ln=dev16(post_mlp) if post_mlp is not None else None, moe=moe))
         assert D == 128
         return self
@@ -309,8 +309,7 @@ class LlamaGpu:
                 branch = self.comm.all_reduce(self._moe_ffn(h, L.moe))
                 n += 9 if inp.attn_splits == 1 or not inp.decode else 10
                 continue
-            gu = ops.linear_any(h, L.gate_up)
-            act = ops.gated_act_mul(gu, cfg.mlp_activation)
+            act = self._gated_mlp_in(h, L.gate_up)
             if fused is not None and L.post_mlp_ln is None:
                 # the down-projection's all-reduce fuses with the NEXT norm (next layer's ln1 or the final norm)
                 nxt = self.layers[li + 1].ln1 if li + 1 < len(self.layers) else self.norm
@@ -323,7 +322,7 @@ class LlamaGpu:
                 if L.post_mlp_ln is not None:
                     branch = ops.rmsnorm(branch, L.post_mlp_ln, eps, w_offset=woff)
                     n += 1
-            n += 9 if inp.attn_splits == 1 or not inp.decode else 10
+            n += (7 if inp.attn_splits == 1 or not inp.decode else 8) + self._mlp_in_launches
         self.launches = n
         final = pending_h if pending_h is not None else ops.rmsnorm(branch, self.norm, eps, residual=res,
                                                                     w_offset=woff)
@@ -331,6 +330,16 @@ class LlamaGpu:
         if inp.logits_rows is not None:
             return final.index_select(0, inp.logits_rows)
         return final
+
+    def _gated_mlp_in(self, h: torch.Tensor, gate_up) -> torch.Tensor:
+        """act(h W_gate^T) * (h W_up^T). A dense layer's gate_up rows are interleaved (gate_0, up_0, gate_1, ...) so a
+        decode-sized step applies the gated activation in the projection's epilogue."""
+        if isinstance(gate_up, torch.Tensor) and h.device.type == "cuda":
+            y = ops.linear_gated(h, gate_up, self.cfg.mlp_activation)
+            self._mlp_in_launches = 1 if y.shape[0] <= 64 and ops.gated_fused(h.shape[0], *gate_up.shape) else 2
+            return y
+        self._mlp_in_launches = 2
+        return ops.gated_act_mul(ops.linear_any(h, gate_up), self.cfg.mlp_activation, paired=True)
 
     def _moe_ffn(self, h: torch.Tensor, m: MoeWeights) -> torch.Tensor:
         """Sparse FFN on this rank's shard (partial sums; the caller all-reduces). Routing stays on the device:
@@ -457,8 +466,7 @@ class LlamaGpu:
                                            softcap=cfg.attn_logit_softcap or 0.0)
             ctx.gemm_scatter_rows(attn, L.o)
             h = ctx.reduce_norm_gather(T, res, L.ln2, eps, woff)
-            gu = ops.linear_any(h, L.gate_up)
-            act = ops.gated_act_mul(gu, cfg.mlp_activation)
+            act = self._gated_mlp_in(h, L.gate_up)
             ctx.gemm_scatter_rows(act, L.down)
             nxt = self.layers[li + 1].ln1 if li + 1 < len(self.layers) else self.norm
             h = ctx.reduce_norm_gather(T, res, nxt, eps, woff)

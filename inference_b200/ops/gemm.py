@@ -6,7 +6,7 @@ import torch
 from .._native import kernels
 from .runtime import check, ptr, require_cuda, stream_ptr
 
-ACT = {None: 0, "none": 0, "silu": 1, "gelu_tanh": 2}
+ACT = {None: 0, "none": 0, "silu": 1, "gelu_tanh": 2, "swiglu_pairs": 3, "geglu_pairs": 4}
 _WORKSPACES: dict[tuple[int, int], torch.Tensor] = {}
 WORKSPACE_BYTES = 64 * 1024 + (96 << 20)
 
@@ -33,9 +33,10 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, *, bias: torch.Tensor | None = N
     assert a.stride(1) == 1 and w.stride(1) == 1
     T, K = a.shape
     N = w.shape[0]
+    n_out = N // 2 if ACT[act] >= 3 else N      # gated pairs halve the width
     if out is None:
-        out = torch.empty((T, N), dtype=out_dtype, device=a.device)
-    assert out.shape == (T, N) and out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
+        out = torch.empty((T, n_out), dtype=out_dtype, device=a.device)
+    assert out.shape == (T, n_out) and out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
     if residual is not None:
         assert residual.dtype == torch.bfloat16 and residual.shape == (T, N) and residual.stride(1) == 1
     if bias is not None:
@@ -69,6 +70,30 @@ def gemm_bf16_grouped(a: torch.Tensor, w: torch.Tensor, tile_groups: torch.Tenso
                                          out.data_ptr(), out.stride(0), R, N, K, ACT[act], stream_ptr())
     check(rc, "swb_gemm_bf16_grouped")
     return out
+
+
+def gated_fused(T: int, N: int, K: int) -> bool:
+    """True when linear_gated applies the activation inside the projection kernel for this shape."""
+    return bool(kernels().swb_gemm_gated_supported(T, N, K))
+
+
+def linear_gated(x: torch.Tensor, w_pairs: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    """act(x W_gate^T) * (x W_up^T) for a gate-up weight whose rows are interleaved (gate_0, up_0, gate_1, ...).
+
+    Decode-sized token counts apply the gated activation in the GEMM's epilogue (the reference runs the projection,
+    a split and two elementwise kernels: candle-llm models/llama.rs:1386-1391); larger ones run the GEMM and the
+    paired activation kernel."""
+    from .llm import gated_act_mul
+
+    x2 = x.reshape(-1, x.shape[-1])
+    T, K = x2.shape
+    N = w_pairs.shape[0]
+    gelu = act in ("gelu", "gelu_tanh")
+    if kernels().swb_gemm_gated_supported(T, N, K):
+        y = gemm_bf16(x2, w_pairs, act="geglu_pairs" if gelu else "swiglu_pairs")
+    else:
+        y = gated_act_mul(gemm_bf16(x2, w_pairs), act, paired=True)
+    return y.reshape(*x.shape[:-1], N // 2)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, **kw) -> torch.Tensor:

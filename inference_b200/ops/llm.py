@@ -72,8 +72,10 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: torc
     check(rc, "swb_rope_kv_write")
 
 
-def gated_act_mul(gate_up: torch.Tensor, act: str = "silu", out: torch.Tensor | None = None) -> torch.Tensor:
-    """out[t, f] = act(gate_up[t, f]) * gate_up[t, F + f] (SwiGLU / GeGLU, candle-llm models/llama.rs:1386-1391)."""
+def gated_act_mul(gate_up: torch.Tensor, act: str = "silu", out: torch.Tensor | None = None,
+                  paired: bool = False) -> torch.Tensor:
+    """out[t, f] = act(gate_up[t, f]) * gate_up[t, F + f] (SwiGLU / GeGLU, candle-llm models/llama.rs:1386-1391).
+    paired: the projection's rows are interleaved (gate_0, up_0, gate_1, ...), out[t, f] = act(gu[t, 2f]) * gu[t, 2f+1]."""
     require_cuda(gate_up)
     g2 = gate_up.reshape(-1, gate_up.shape[-1])
     T, F2 = g2.shape
@@ -81,7 +83,7 @@ def gated_act_mul(gate_up: torch.Tensor, act: str = "silu", out: torch.Tensor | 
     if out is None:
         out = torch.empty((T, F), dtype=gate_up.dtype, device=gate_up.device)
     rc = kernels().swb_gated_act_mul(g2.data_ptr(), g2.stride(0), out.data_ptr(), out.stride(0), T, F,
-                                     2 if act in ("gelu", "gelu_tanh") else 1, stream_ptr())
+                                     (2 if act in ("gelu", "gelu_tanh") else 1) + (2 if paired else 0), stream_ptr())
     check(rc, "swb_gated_act_mul")
     return out.reshape(*gate_up.shape[:-1], F)
 

@@ -117,3 +117,23 @@ def test_grouped_gemm_matches_per_group_matmul(N, K):
     act = ops.gemm_bf16_grouped(a, w, table, act="silu")
     ref = torch.nn.functional.silu(a[:128].float() @ w[3].float().t())
     torch.testing.assert_close(act[:128].float(), ref, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("T,F,K,act", [(1, 256, 1024, "silu"), (64, 14336, 4096, "silu"), (17, 1000, 768, "gelu_tanh"),
+                                       (200, 512, 1024, "silu")])
+def test_gated_projection_pairs(T, F, K, act):
+    """Gate-up projection with interleaved (gate, up) rows: fused epilogue (decode sizes) and GEMM + paired
+    activation kernel (larger) both equal act(x Wg^T) * (x Wu^T)."""
+    from inference_b200 import ops
+
+    g = torch.Generator(device="cuda").manual_seed(T + F)
+    wg = (torch.randn(F, K, device="cuda", generator=g) * 0.03).bfloat16()
+    wu = (torch.randn(F, K, device="cuda", generator=g) * 0.03).bfloat16()
+    x = torch.randn(T, K, device="cuda", generator=g).bfloat16()
+    pairs = torch.stack([wg, wu], dim=1).reshape(2 * F, K).contiguous()
+    y = ops.linear_gated(x, pairs, act)
+    ops.check_status()
+    gate, up = x.float() @ wg.float().t(), x.float() @ wu.float().t()
+    fn = torch.nn.functional.silu if act == "silu" else (lambda t: torch.nn.functional.gelu(t, approximate="tanh"))
+    torch.testing.assert_close(y.float(), fn(gate) * up, rtol=3e-2, atol=3e-2)
+    assert ops.gated_fused(T, 2 * F, K) == (T <= 64)
