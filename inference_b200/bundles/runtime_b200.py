@@ -6,7 +6,7 @@ from __future__ import annotations
 from ..contracts.core_llm.prepare import SnapshotPreparerRegistry, SnapshotPreparerRegistryBuilder
 from ..contracts.core_llm.registry import TextLlmRegistry, TextLlmRegistryBuilder
 from ..contracts.gen_core.registry import ProviderRegistry
-from .catalog import RuntimeCatalog
+from .catalog import AudioSection, RuntimeCatalog
 
 PLATFORM = "cuda"
 BACKEND = "b200"
@@ -30,6 +30,14 @@ def snapshot_preparer_registry() -> SnapshotPreparerRegistry:
     return SnapshotPreparerRegistryBuilder().register(registration(BACKEND)).build()
 
 
+def audio_section() -> AudioSection:
+    """The audio lane: its own provider registry (transcribers, embedders, generators) on the same backend; its
+    snapshots are prepared by the lane's preparer list."""
+    from ..audio.catalog import provider_registry as audio_registry
+
+    return AudioSection(BACKEND, audio_registry(BACKEND), snapshot_preparer_registry())
+
+
 def catalog() -> RuntimeCatalog:
-    return RuntimeCatalog.try_new(PLATFORM, BACKEND, provider_registry(), text_registry(),
-                                  snapshot_preparer_registry())
+    return RuntimeCatalog.try_new_with_audio(PLATFORM, BACKEND, provider_registry(), text_registry(),
+                                             snapshot_preparer_registry(), audio_section())

@@ -25,7 +25,7 @@ def test_catalogs_validate_and_snapshot():
         snap = json.loads(cat.snapshot().to_json())
         assert snap["backend"] == backend and snap["text_llm_ids"] == [llm]
         assert snap["snapshot_preparer_backends"] == [backend] and len(snap["generator_ids"]) == 2
-        assert snap["audio_backend"] is None
+        assert snap["audio_backend"] == backend and snap["audio_transcriber_ids"] == ["whisper"]
 
 
 def test_catalog_rejects_mixed_backends_and_missing_preparer():
