@@ -75,9 +75,11 @@ class ModelRunner:
 
     # ---- prefill (eager, ragged) ------------------------------------------------------------------
     def prefill(self, seqs: list[PagedSequence], new_tokens: list[list[int]], *, want_logits: bool = False,
-                all_positions: bool = False):
+                all_positions: bool = False, embed_overrides: list[tuple[list[int], torch.Tensor] | None] | None = None):
         """Appends new_tokens[i] to seqs[i] (any mix of lengths, including chunked / prefix-seeded sequences)
-        and returns greedy next tokens [num_seqs] (or fp32 logits when want_logits)."""
+        and returns greedy next tokens [num_seqs] (or fp32 logits when want_logits). embed_overrides[i] =
+        (positions within new_tokens[i], vectors [len(positions), hidden]) replaces those tokens' embeddings (the
+        image placeholders of a vision-language prompt)."""
         dev = self.model.device
         ids, pos, slots, cu, kvl, rows = [], [], [], [0], [], []
         fresh = all(s.length == 0 for s in seqs)     # no earlier context: attention can read K / V from the QKV buffer
@@ -106,6 +108,15 @@ class ModelRunner:
             num_seqs=len(seqs), decode=decode, fresh_prefill=fresh and not decode,
             attn_splits=_splits_for(len(seqs), self.model.hkv, max(kvl)) if decode else 1,
             logits_rows=None if all_positions else torch.tensor(rows, dtype=torch.int64, device=dev))
+        if embed_overrides is not None:
+            er, ev = [], []
+            for i, ov in enumerate(embed_overrides):
+                if ov is not None:
+                    er += [cu[i] + p for p in ov[0]]
+                    ev.append(ov[1].to(dev))
+            if er:
+                inp.embed_rows = torch.tensor(er, dtype=torch.int64, device=dev)
+                inp.embed_values = torch.cat(ev, dim=0)
         hidden = self.model.forward_hidden(inp, self.pool.data)
         self.launches_last = self.model.launches
         if want_logits or all_positions:

@@ -13,4 +13,9 @@ def provider_registry(backend: str = "b200") -> ProviderRegistry:
     from .train import trainer_registration
 
     b.register("trainer", trainer_registration(backend))
+    from . import vision_providers
+
+    for kind, regs in vision_providers.registrations(backend).items():
+        for r in regs:
+            b.register(kind, r)
     return b.build()

@@ -37,6 +37,8 @@ class StepInputs:
     attn_splits: int = 1
     logits_rows: torch.Tensor | None = None  # int64 rows of the hidden state to project; None => all rows
     fresh_prefill: bool = False        # every sequence starts at position 0 (context == this step's tokens)
+    embed_rows: torch.Tensor | None = None    # int64 [R]: rows of the flat batch whose embedding is replaced ...
+    embed_values: torch.Tensor | None = None  # ... by these [R, H] vectors (projected image features of a VLM prompt)
 
 
 @dataclass
@@ -261,9 +263,11 @@ class LlamaGpu:
         D = cfg.head_dim
         eps, woff = cfg.rms_norm_eps, cfg.norm_weight_offset
         T = inp.input_ids.numel()
-        if self._use_tp_prefill(T):
+        if self._use_tp_prefill(T) and inp.embed_rows is None:
             return self._forward_hidden_tp_prefill(inp, kv_pool)
         res = ops.embedding(inp.input_ids, self.embed, scale=cfg.embed_scale)
+        if inp.embed_rows is not None:
+            res.index_copy_(0, inp.embed_rows, inp.embed_values.to(res.dtype))
         branch = None
         block_size = kv_pool.shape[4]
         q_cols = self.hq * D

@@ -151,3 +151,38 @@ def test_padded_decode_buckets_reuse_graphs_and_match_exact_batches():
         if padded:
             assert runner.captures == 2             # buckets 16 and 8
     assert outs[0] == outs[1]
+
+
+def test_prefill_embedding_override_matches_oracle_with_spliced_embeds():
+    """Rows whose embeddings are replaced (image features of a vision-language prompt) flow through the GPU
+    prefill exactly like the oracle's forward on spliced embeddings; decoding continues from the paged cache."""
+    from inference_b200.engine.kv_pool import PagedSequence
+    from inference_b200.media.vision_providers import EngineLm, OracleLm
+
+    cfg = _small_cfg()
+    oracle, model, pool, runner = _build(cfg, seed=9)
+    g = torch.Generator().manual_seed(4)
+    ids = torch.randint(0, cfg.vocab_size, (12,), generator=g).tolist()
+    pos = [2, 3, 4, 5]
+    feats = (torch.randn(4, cfg.hidden_size, generator=g) * 0.05).bfloat16().float()
+    seq = PagedSequence(pool)
+    logits = runner.prefill([seq], [ids], want_logits=True, embed_overrides=[(pos, feats.cuda())])[0]
+    emb = oracle.embed(torch.tensor([ids], device="cuda")).clone()
+    emb[0, pos] = feats.cuda()
+    cache = oracle.make_cache()
+    ref = oracle.project_logits(oracle.hidden_states(None, cache, 0, embeds=emb)[:, -1:, :])[0, 0]
+    assert (logits - ref).abs().max().item() < 0.05 * max(1.0, ref.abs().max().item())
+    plain = runner.prefill([PagedSequence(pool)], [ids], want_logits=True)[0]
+    assert (plain - logits).abs().max().item() > 1e-3           # the override changed the result
+    seq.release()
+
+    class _Eng:
+        def __init__(s):
+            s.runner = runner
+
+        def new_sequence(s):
+            return PagedSequence(pool)
+    got = EngineLm(_Eng()).generate_with_embeds(ids, pos, feats.cuda(), 8)
+    want = OracleLm(oracle).generate_with_embeds(ids, pos, feats, 8)
+    agree = sum(a == b for a, b in zip(got, want))
+    assert len(got) == 8 and agree >= 6, (got, want)

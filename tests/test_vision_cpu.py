@@ -1,0 +1,157 @@
+"""CLIP and SigLIP vision towers against Hugging Face on tiny random configurations."""
+import torch
+
+
+def test_clip_vision_and_joint_embeddings_match_hugging_face():
+    from transformers import CLIPConfig, CLIPModel
+
+    from inference_b200.models.text_encoders import ClipTextConfig, ClipTextEncoder
+    from inference_b200.models.vision import VisionConfig, VisionTower
+
+    torch.manual_seed(0)
+    hc = CLIPConfig(text_config=dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                                     vocab_size=100, max_position_embeddings=16, eos_token_id=99, bos_token_id=98,
+                                     pad_token_id=0),
+                    vision_config=dict(hidden_size=48, intermediate_size=96, num_hidden_layers=3, num_attention_heads=4,
+                                       image_size=28, patch_size=7), projection_dim=24)
+    hf = CLIPModel(hc).eval()
+    cfg = VisionConfig.from_json(hc.to_dict())
+    assert cfg.kind == "clip" and cfg.num_patches == 16 and cfg.projection_dim == 24
+    tower = VisionTower(cfg, dict(hf.state_dict()))
+    px = torch.randn(2, 3, 28, 28)
+    with torch.no_grad():
+        out = hf.vision_model(pixel_values=px, output_hidden_states=True)
+        emb = hf.get_image_features(pixel_values=px)
+        emb = emb if isinstance(emb, torch.Tensor) else emb.pooler_output
+    torch.testing.assert_close(tower.pooled(px), out.pooler_output, atol=2e-5, rtol=2e-5)
+    torch.testing.assert_close(tower.hidden_states(px, -2), out.hidden_states[-2], atol=2e-5, rtol=2e-5)
+    torch.testing.assert_close(tower.image_embeds(px), emb, atol=2e-5, rtol=2e-5)
+    assert tower.image_embeds(px).shape == (2, 24)
+
+
+def test_siglip_vision_matches_hugging_face():
+    from transformers import SiglipVisionConfig, SiglipVisionModel
+
+    from inference_b200.models.vision import VisionConfig, VisionTower
+
+    torch.manual_seed(1)
+    hc = SiglipVisionConfig(hidden_size=48, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                            image_size=32, patch_size=8)
+    hf = SiglipVisionModel(hc).eval()
+    cfg = VisionConfig.from_json(hc.to_dict())
+    assert cfg.kind == "siglip" and cfg.hidden_act == "gelu_pytorch_tanh"
+    tower = VisionTower(cfg, dict(hf.state_dict()))
+    px = torch.randn(2, 3, 32, 32)
+    with torch.no_grad():
+        out = hf(pixel_values=px, output_hidden_states=True)
+    torch.testing.assert_close(tower.hidden_states(px, -1), out.hidden_states[-1], atol=2e-5, rtol=2e-5)
+    torch.testing.assert_close(tower.pooled(px), out.pooler_output, atol=2e-5, rtol=2e-5)
+
+
+def test_preprocess_shapes_and_range():
+    from inference_b200.models.vision import SIGLIP_MEAN, SIGLIP_STD, preprocess
+
+    img = torch.randint(0, 256, (60, 90, 3), dtype=torch.uint8)
+    x = preprocess(img, 28)
+    assert x.shape == (1, 3, 28, 28) and float(x.abs().max()) < 3
+    y = preprocess(img, 32, SIGLIP_MEAN, SIGLIP_STD, crop=False)
+    assert y.shape == (1, 3, 32, 32) and -1.0 <= float(y.min()) and float(y.max()) <= 1.0
+    flat = torch.full((40, 40, 3), 255, dtype=torch.uint8)
+    assert torch.allclose(preprocess(flat, 20, SIGLIP_MEAN, SIGLIP_STD), torch.ones(1, 3, 20, 20))
+
+
+def _tiny_llava():
+    from transformers import CLIPVisionConfig, LlamaConfig, LlavaConfig, LlavaForConditionalGeneration
+
+    torch.manual_seed(2)
+    vc = CLIPVisionConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4, image_size=28,
+                          patch_size=14)
+    tc = LlamaConfig(vocab_size=120, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                     num_key_value_heads=2, max_position_embeddings=256, rms_norm_eps=1e-5, eos_token_id=119,
+                     tie_word_embeddings=False)
+    hc = LlavaConfig(vision_config=vc, text_config=tc, image_token_index=100, vision_feature_layer=-2,
+                     vision_feature_select_strategy="default")
+    return hc, LlavaForConditionalGeneration(hc).eval()
+
+
+class _WordTok:
+    def encode(self, text):
+        return [100 if w == "<image>" else int(w) for w in text.split()]
+
+    def decode(self, ids):
+        return " ".join(str(i) for i in ids)
+
+
+def test_llava_captioner_matches_hugging_face_greedy_decode():
+    from inference_b200.contracts.gen_core.media import Image
+    from inference_b200.media.vision_providers import LlavaCaptioner, OracleLm, image_tensor
+    from inference_b200.models.config import ModelConfig
+    from inference_b200.models.oracle import OracleLlama
+    from inference_b200.models.vision import CLIP_MEAN, CLIP_STD, VisionConfig, VisionTower, preprocess
+
+    hc, hf = _tiny_llava()
+    sd = {(k[6:] if k.startswith("model.") else k): v for k, v in hf.state_dict().items()}
+    vis = {k[len("vision_tower."):]: v for k, v in sd.items() if k.startswith("vision_tower.")}
+    proj = {k[len("multi_modal_projector."):]: v for k, v in sd.items() if k.startswith("multi_modal_projector.")}
+    lmw = {"model." + k[len("language_model."):]: v for k, v in sd.items() if k.startswith("language_model.")}
+    lmw["lm_head.weight"] = sd["lm_head.weight"]
+    tower = VisionTower(VisionConfig.from_json(hc.to_dict()), vis)
+    oracle = OracleLlama(ModelConfig.from_json(hc.text_config.to_dict()), lmw, dtype=torch.float32, device="cpu")
+    cap = LlavaCaptioner(tower, proj, OracleLm(oracle), _WordTok(), 100, "cpu", -2)
+    g = torch.Generator().manual_seed(0)
+    img = Image(40, 30, bytes(torch.randint(0, 256, (30 * 40 * 3,), generator=g, dtype=torch.uint8).tolist()))
+    prompt = "5 <image> 7 8"
+    feats = cap.image_features(img)
+    assert feats.shape == (4, 64)                       # 2 x 2 patches, class token dropped
+    ids = cap.build_prompt(prompt, 4)
+    assert ids == [5, 100, 100, 100, 100, 7, 8]
+    px = preprocess(image_tensor(img), 28, CLIP_MEAN, CLIP_STD)
+    with torch.no_grad():
+        ref_feats = hf.get_image_features(pixel_values=px, vision_feature_layer=-2,
+                                          vision_feature_select_strategy="default")
+        ref_feats = ref_feats if isinstance(ref_feats, torch.Tensor) else (
+            ref_feats[0] if isinstance(ref_feats, (list, tuple)) else ref_feats.pooler_output)
+        ref_feats = ref_feats[0] if isinstance(ref_feats, (list, tuple)) else ref_feats
+        torch.testing.assert_close(feats, ref_feats.reshape(-1, 64), atol=2e-5, rtol=2e-5)
+        out = hf.generate(input_ids=torch.tensor([ids]), pixel_values=px, max_new_tokens=6, do_sample=False,
+                          pad_token_id=0)
+    want = out[0, len(ids):].tolist()
+    if 119 in want:
+        want = want[: want.index(119)]
+    got = cap.caption_tokens(img, prompt, 6)
+    assert got == want[: len(got)] and len(got) >= min(len(want), 6) - 0
+    assert cap.caption(img, prompt, 3) == " ".join(str(t) for t in got[:3])
+    assert cap.build_prompt("7 8", 2) == [100, 100, 7, 8]          # a prompt without the placeholder gets one in front
+
+
+def test_clip_embedders_are_normalised_and_aligned():
+    from transformers import CLIPConfig, CLIPModel
+
+    from inference_b200.contracts.gen_core.media import Image
+    from inference_b200.media.vision_providers import ClipImageEmbedder, ClipTextEmbedder
+    from inference_b200.models.text_encoders import ClipTextConfig, ClipTextEncoder
+    from inference_b200.models.vision import VisionConfig, VisionTower
+
+    torch.manual_seed(3)
+    hc = CLIPConfig(text_config=dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                                     vocab_size=100, max_position_embeddings=8, eos_token_id=99, bos_token_id=98),
+                    vision_config=dict(hidden_size=48, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                                       image_size=28, patch_size=14), projection_dim=16)
+    hf = CLIPModel(hc).eval()
+    sd = dict(hf.state_dict())
+    ie = ClipImageEmbedder(VisionTower(VisionConfig.from_json(hc.to_dict()), sd), "cpu")
+    img = Image(28, 28, bytes([7] * (28 * 28 * 3)))
+    v = torch.tensor(ie.embed([img, img]))
+    assert v.shape == (2, 16) and torch.allclose(v.norm(dim=-1), torch.ones(2), atol=1e-5) and torch.allclose(v[0], v[1])
+
+    class Tok:
+        def encode(self, t):
+            return [98] + [int(x) for x in t.split()] + [99] * (7 - len(t.split()))
+    te = ClipTextEmbedder(ClipTextEncoder(ClipTextConfig.from_json(hc.text_config.to_dict()), sd),
+                          sd["text_projection.weight"], Tok(), "cpu")
+    t = torch.tensor(te.embed(["1 2 3", "4 5"]))
+    with torch.no_grad():
+        ref = hf.get_text_features(input_ids=torch.tensor([Tok().encode("1 2 3"), Tok().encode("4 5")]))
+        ref = ref if isinstance(ref, torch.Tensor) else ref.pooler_output
+    torch.testing.assert_close(t, torch.nn.functional.normalize(ref, dim=-1), atol=1e-5, rtol=1e-4)
+    assert ie.descriptor().id == "clip_vit_l14" and te.descriptor().id == "clip_vit_l14_text"
