@@ -44,7 +44,10 @@ class LlmEngine:
             nblocks = PagedKvPool.blocks_for_budget(c.kv_bytes, m.num_layers, model.hkv, m.head_dim, c.block_size)
         else:
             nblocks = c.max_batch * ((c.max_seq_len + c.block_size - 1) // c.block_size) + 8
-        self.pool = PagedKvPool(m.num_layers, nblocks, model.hkv, m.head_dim, c.block_size, device=model.device)
+        if hasattr(model, "make_pool"):      # pipeline-sharded model: one KV tensor per stage device, shared block ids
+            self.pool = model.make_pool(nblocks, c.block_size)
+        else:
+            self.pool = PagedKvPool(m.num_layers, nblocks, model.hkv, m.head_dim, c.block_size, device=model.device)
         self.runner = ModelRunner(model, self.pool, max_batch=c.max_batch, max_seq_len=c.max_seq_len,
                                   use_graphs=c.use_graphs)
 

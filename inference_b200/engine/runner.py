@@ -48,7 +48,7 @@ class ModelRunner:
         self.model, self.pool = model, pool
         self.max_batch, self.max_seq_len = max_batch, max_seq_len
         self.max_blocks = (max_seq_len + pool.block_size - 1) // pool.block_size
-        self.use_graphs = use_graphs        # mixture-of-experts routing is device side, so those models capture too
+        self.use_graphs = use_graphs and not getattr(model, "eager_only", False)   # mixture-of-experts routing is device side, so those models capture too
         dev = model.device
         model.ensure_rope(max_seq_len + 64)
         # static decode-step buffers; one packed int64 staging area so a step is a single H2D copy

@@ -120,8 +120,11 @@ class LlamaGpu:
         self.sin = ang.sin().float().to(self.device).contiguous()
         self.max_positions = max_positions
 
-    def load_state_dict(self, weights: dict[str, torch.Tensor]) -> "LlamaGpu":
-        """Takes full (unsharded) HF-named tensors and keeps this rank's tensor-parallel slice in bf16."""
+    def load_state_dict(self, weights: dict[str, torch.Tensor], *, layers: range | None = None,
+                        with_embed: bool = True, with_head: bool = True) -> "LlamaGpu":
+        """Takes full (unsharded) HF-named tensors and keeps this rank's tensor-parallel slice in bf16. `layers`
+        restricts the load to a contiguous block of decoder layers (one pipeline stage); a stage that is not the first
+        / last skips the embedding table / the final norm and output head."""
         cfg, r, P, dev = self.cfg, self.comm.rank, self.comm.world, self.device
         w = canonical_weights(weights, cfg)
         D = cfg.head_dim
@@ -134,12 +137,14 @@ class LlamaGpu:
         def dev16(t: torch.Tensor) -> torch.Tensor:
             return t.to(device=dev, dtype=torch.bfloat16).contiguous()
 
-        self.embed = dev16(get("model.embed_tokens.weight"))
-        self.norm = dev16(get("model.norm.weight"))
-        head = w.get("lm_head.weight", w["model.embed_tokens.weight"])
-        self.lm_head = dev16(_shard_rows(head, r, P))
+        if with_embed:
+            self.embed = dev16(get("model.embed_tokens.weight"))
+        if with_head:
+            self.norm = dev16(get("model.norm.weight"))
+            head = w.get("lm_head.weight", w["model.embed_tokens.weight"])
+            self.lm_head = dev16(_shard_rows(head, r, P))
         self.layers = []
-        for i in range(cfg.num_layers):
+        for i in (layers if layers is not None else range(cfg.num_layers)):
             p = f"model.layers.{i}"
             q = _shard_rows(get(f"{p}.self_attn.q_proj.weight"), r, P)
             k = _shard_rows(get(f"{p}.self_attn.k_proj.weight"), r, P)
@@ -256,7 +261,7 @@ class LlamaGpu:
         return n * 2 + q
 
     # ---- forward --------------------------------------------------------------------------------
-    def forward_hidden(self, inp: StepInputs, kv_pool: torch.Tensor) -> torch.Tensor:
+    def forward_hidden(self, inp: StepInputs, kv_pool: torch.Tensor, *, stage_in=None, last_stage: bool = True):
         """Runs the decoder stack; kv_pool is [layers, 2, blocks, Hkv_local, block_size, 128]. Returns the
         final (un-normed) branch output and residual folded together: rows of normed hidden states [T, H]."""
         cfg = self.cfg
@@ -265,10 +270,13 @@ class LlamaGpu:
         T = inp.input_ids.numel()
         if self._use_tp_prefill(T) and inp.embed_rows is None:
             return self._forward_hidden_tp_prefill(inp, kv_pool)
-        res = ops.embedding(inp.input_ids, self.embed, scale=cfg.embed_scale)
-        if inp.embed_rows is not None:
-            res.index_copy_(0, inp.embed_rows, inp.embed_values.to(res.dtype))
-        branch = None
+        if stage_in is None:
+            res = ops.embedding(inp.input_ids, self.embed, scale=cfg.embed_scale)
+            if inp.embed_rows is not None:
+                res.index_copy_(0, inp.embed_rows, inp.embed_values.to(res.dtype))
+            branch = None
+        else:       # a later pipeline stage: the residual stream and the pending branch output of the previous stage
+            res, branch = stage_in
         block_size = kv_pool.shape[4]
         q_cols = self.hq * D
         n = 1
@@ -328,6 +336,9 @@ class LlamaGpu:
                     n += 1
             n += (7 if inp.attn_splits == 1 or not inp.decode else 8) + self._mlp_in_launches
         self.launches = n
+        if not last_stage:
+            assert pending_h is None
+            return res, branch
         final = pending_h if pending_h is not None else ops.rmsnorm(branch, self.norm, eps, residual=res,
                                                                     w_offset=woff)
         self.launches += 1

@@ -186,3 +186,66 @@ def test_prefill_embedding_override_matches_oracle_with_spliced_embeds():
     want = OracleLm(oracle).generate_with_embeds(ids, pos, feats, 8)
     agree = sum(a == b for a, b in zip(got, want))
     assert len(got) == 8 and agree >= 6, (got, want)
+
+
+def test_pipeline_sharded_stages_match_the_single_model():
+    """Two pipeline stages (both placed on this GPU) hand the residual stream across the boundary and reproduce
+    the unsharded model's logits for prefill and paged decode."""
+    from inference_b200.engine.kv_pool import PagedSequence
+    from inference_b200.engine.llm_engine import EngineConfig, LlmEngine
+    from inference_b200.models.llama import LlamaGpu
+    from inference_b200.models.oracle import random_llama_weights
+    from inference_b200.models.pipeline import PipelineLlama
+
+    cfg = _small_cfg()
+    w = {k: v.bfloat16().float() for k, v in random_llama_weights(cfg, seed=4, std=0.05).items()}
+    single = LlmEngine(LlamaGpu(cfg, device=torch.device("cuda")).load_state_dict(w),
+                       EngineConfig(max_batch=4, max_seq_len=256, use_graphs=False))
+    pipe_model = PipelineLlama(cfg, ["cuda:0", "cuda:0"]).load_state_dict(w)
+    assert [len(b) for b in pipe_model.blocks] == [2, 1] and len(pipe_model.layer_devices()) == 3
+    assert pipe_model.stages[0].lm_head is None and pipe_model.stages[1].embed is None
+    pipe = LlmEngine(pipe_model, EngineConfig(max_batch=4, max_seq_len=256))
+    assert not pipe.runner.use_graphs and len(pipe.pool.data) == 2
+    prompts = [list(range(3, 40)), list(range(100, 109))]
+    outs = []
+    for eng in (single, pipe):
+        seqs = [eng.new_sequence() for _ in prompts]
+        lg = eng.runner.prefill(seqs, prompts, want_logits=True)
+        toks = [int(lg[i].argmax()) for i in range(2)]
+        steps = [lg]
+        for _ in range(3):
+            lg = eng.runner.decode(seqs, toks, want_logits=True)
+            steps.append(lg.clone())
+            toks = [int(lg[i].argmax()) for i in range(2)]
+        outs.append(steps)
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_pipeline_sharded_across_two_gpus_matches_single_gpu():
+    from inference_b200.engine.llm_engine import EngineConfig, LlmEngine
+    from inference_b200.models.llama import LlamaGpu
+    from inference_b200.models.oracle import random_llama_weights
+    from inference_b200.models.pipeline import PipelineLlama
+
+    cfg = _small_cfg()
+    w = {k: v.bfloat16().float() for k, v in random_llama_weights(cfg, seed=6, std=0.05).items()}
+    single = LlmEngine(LlamaGpu(cfg, device=torch.device("cuda:0")).load_state_dict(w),
+                       EngineConfig(max_batch=2, max_seq_len=128, use_graphs=False))
+    pipe = LlmEngine(PipelineLlama(cfg, ["cuda:0", "cuda:1"]).load_state_dict(w), EngineConfig(max_batch=2, max_seq_len=128))
+    assert pipe.model.stages[1].layers[0].qkv.device.index == 1 and all(b > 0 for b in pipe.model.weight_bytes())
+    prompt = [list(range(7, 50))]
+    outs = []
+    for eng in (single, pipe):
+        seqs = [eng.new_sequence()]
+        lg = eng.runner.prefill(seqs, prompt, want_logits=True)
+        tok = [int(lg[0].argmax())]
+        trace = [lg.cpu()]
+        for _ in range(3):
+            lg = eng.runner.decode(seqs, tok, want_logits=True)
+            trace.append(lg.cpu().clone())
+            tok = [int(lg[0].argmax())]
+        outs.append(trace)
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)

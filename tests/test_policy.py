@@ -108,3 +108,18 @@ def test_splitmix_and_sampler():
     assert [c[0] for c in cands] == [3]  # e^0 / sum = 0.64 >= 0.6
     cands = shaped_candidates([0.0, 1.0, 2.0, 3.0], [], SamplingParams(temperature=1.0, top_k=2))
     assert sorted(c[0] for c in cands) == [2, 3]
+
+
+def test_pipeline_shard_plan_splits_layers_contiguously():
+    from inference_b200.models.pipeline import layer_blocks, shard_for_layer, shard_plan
+
+    assert [shard_for_layer(i, 2, 4) for i in range(4)] == [0, 0, 1, 1]
+    assert [shard_for_layer(i, 3, 8) for i in range(8)] == [0, 0, 0, 1, 1, 1, 2, 2]
+    assert [shard_for_layer(i, 4, 2) for i in range(2)] == [0, 2]          # more shards than layers
+    assert shard_for_layer(0, 1, 0) == 0
+    assert layer_blocks(8, 3) == [range(0, 3), range(3, 6), range(6, 8)]
+    assert layer_blocks(2, 4) == [range(0, 1), range(0, 0), range(1, 2), range(0, 0)]
+    place = shard_plan(["d0", "d1"], 4)
+    assert place("model.embed_tokens.weight") == "d0" and place("model.layers.1.mlp.up_proj.weight") == "d0"
+    assert place("model.layers.2.self_attn.q_proj.weight") == "d1" and place("model.norm.weight") == "d1"
+    assert place("lm_head.weight") == "d1" and place("something.else") == "d0"
