@@ -262,6 +262,43 @@ __global__ void __launch_bounds__(THREADS) reduce_norm_gather_kernel(const RsAgP
   }
 }
 
+struct PairParams {
+  const float* vals[MAX_RANKS];          // per rank: [rows] best value of its vocabulary shard
+  const long long* ids[MAX_RANKS];       // per rank: [rows] index inside the shard
+  long long* out;                        // [rows] global token ids
+  int rows, vocab_local;
+};
+
+// One CTA: flag barrier (flag row 0, like peer_barrier_kernel), then thread = row pulls `world` candidates.
+__global__ void __launch_bounds__(128) argmax_peer_merge_kernel(const ArParams p, const PairParams q) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ int s_ok;
+  const uint32_t epoch = p.epochs[0] + 1u;
+  const bool ok = peer_barrier(p, epoch, &s_ok);
+  if (threadIdx.x == 0) p.epochs[0] = epoch;
+  if (!ok) return;
+  for (int row = threadIdx.x; row < q.rows; row += blockDim.x) {
+    float best = 0.f;
+    long long best_id = 0;
+#pragma unroll
+    for (int r = 0; r < MAX_RANKS; ++r) {
+      if (r < p.world) {
+        uint32_t vb;
+        unsigned long long ib;
+        asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(vb) : "l"(q.vals[r] + row) : "memory");
+        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(ib) : "l"(q.ids[r] + row) : "memory");
+        const float v = __uint_as_float(vb);
+        if (r == 0 || v > best) {
+          best = v;
+          best_id = (long long)ib + (long long)r * q.vocab_local;
+        }
+      }
+    }
+    q.out[row] = best_id;
+  }
+}
+
 // Barrier across ranks between two kernels of a stream (everything this rank's earlier kernels wrote to peers is
 // visible to a peer once that peer's barrier returns). One CTA; flag row `blockIdx.x` = 0 of its own flag pad.
 __global__ void __launch_bounds__(32) peer_barrier_kernel(const ArParams p) {
@@ -376,6 +413,31 @@ int swb_reduce_norm_gather(const void* slots, int n_src, void* residual, int ldr
   if (nvec <= 1024) return launch_kernel(reduce_norm_gather_kernel<512, 2>, dim3(grid), dim3(512), 0, s, q);
   if (nvec <= 2048) return launch_kernel(reduce_norm_gather_kernel<512, 4>, dim3(grid), dim3(512), 0, s, q);
   return -3;
+}
+
+// Distributed argmax of a vocabulary-parallel output head: every rank has written its shard's best (value, local
+// index) per row into its own symmetric buffers; after the flag barrier each rank pulls all shards' candidates over
+// NVLink and keeps the largest value (ties: lowest rank = lowest global index, like a single-device argmax).
+int swb_argmax_peer_merge(const void* const* peer_vals, const void* const* peer_ids, void* const* peer_flags,
+                          void* epochs, int rank, int world, int rows, int vocab_local, long long* out_ids,
+                          void* stream) {
+  using namespace swb;
+  if (world < 1 || world > MAX_RANKS || rows < 0) return -3;
+  if (rows == 0) return 0;
+  ArParams p{};
+  PairParams q{};
+  for (int r = 0; r < world; ++r) {
+    p.peer_flags[r] = reinterpret_cast<uint32_t*>(peer_flags[r]);
+    q.vals[r] = reinterpret_cast<const float*>(peer_vals[r]);
+    q.ids[r] = reinterpret_cast<const long long*>(peer_ids[r]);
+  }
+  p.epochs = reinterpret_cast<uint32_t*>(epochs);
+  p.rank = rank;
+  p.world = world;
+  q.rows = rows;
+  q.vocab_local = vocab_local;
+  q.out = out_ids;
+  return launch_kernel(argmax_peer_merge_kernel, dim3(1), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream), p, q);
 }
 
 // peer_flags: `world` pointers to flag pads of at least MAX_RANKS words; epochs: one local word.

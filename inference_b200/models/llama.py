@@ -508,6 +508,10 @@ class LlamaGpu:
         self.launches += 1
         if not self.comm.is_parallel:
             return ops.argmax(local)
+        f = self.comm.fused
+        if f is not None and local.shape[0] <= f.max_tokens and os.environ.get("SWB_TP_ARGMAX") != "nccl":
+            self.launches += 1
+            return f.argmax_vocab_parallel(local, self.vocab_local)
         vals = local.max(dim=-1)
         idx = vals.indices + self.comm.rank * self.vocab_local
         packed = torch.stack((vals.values.double(), idx.double()), dim=-1)  # [R, 2]

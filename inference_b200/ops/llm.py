@@ -132,9 +132,10 @@ def _argmax_scratch(device: torch.device) -> torch.Tensor:
     return t
 
 
-def argmax(logits: torch.Tensor, allow_mask: torch.Tensor | None = None, out: torch.Tensor | None = None
-           ) -> torch.Tensor:
-    """Row-wise argmax (ties -> lowest index) of fp32/bf16 logits; allow_mask: optional uint8 [V]."""
+def argmax(logits: torch.Tensor, allow_mask: torch.Tensor | None = None, out: torch.Tensor | None = None,
+           out_vals: torch.Tensor | None = None) -> torch.Tensor:
+    """Row-wise argmax (ties -> lowest index) of fp32/bf16 logits; allow_mask: optional uint8 [V]; out_vals:
+    optional fp32 [rows] receiving the maxima."""
     require_cuda(logits)
     l2 = logits.reshape(-1, logits.shape[-1])
     assert l2.stride(1) == 1 and l2.dtype in (torch.float32, torch.bfloat16)
@@ -142,7 +143,7 @@ def argmax(logits: torch.Tensor, allow_mask: torch.Tensor | None = None, out: to
         out = torch.empty(l2.shape[0], dtype=torch.int64, device=logits.device)
     scratch = _argmax_scratch(logits.device)
     rc = kernels().swb_argmax(l2.data_ptr(), 1 if l2.dtype == torch.float32 else 0, l2.stride(0), l2.shape[0],
-                              l2.shape[1], ptr(allow_mask), out.data_ptr(), None, scratch.data_ptr(), scratch.numel(),
+                              l2.shape[1], ptr(allow_mask), out.data_ptr(), ptr(out_vals), scratch.data_ptr(), scratch.numel(),
                               stream_ptr())
     check(rc, "swb_argmax")
     return out

@@ -45,6 +45,13 @@ class FusedCollectives:
         self._flag_ptrs = (ctypes.c_void_p * comm.world)(*[int(p) for p in fh.buffer_ptrs])
         self._epochs = torch.zeros(L.swb_comm_max_ctas(), dtype=torch.int32, device=dev)
         self._handles = [fh]
+        # candidates of the distributed argmax: this rank's best (value, index in its vocabulary shard) per row
+        self._am_vals = symm_mem.empty((max_tokens,), dtype=torch.float32, device=dev)
+        self._am_ids = symm_mem.empty((max_tokens,), dtype=torch.int64, device=dev)
+        vh, ih = symm_mem.rendezvous(self._am_vals, comm.group), symm_mem.rendezvous(self._am_ids, comm.group)
+        self._am_val_ptrs = (ctypes.c_void_p * comm.world)(*[int(p) for p in vh.buffer_ptrs])
+        self._am_id_ptrs = (ctypes.c_void_p * comm.world)(*[int(p) for p in ih.buffer_ptrs])
+        self._handles += [vh, ih]
         # Buffers 0/1 serve captured CUDA graphs (every capture starts at 0 and must contain an even number of
         # calls), buffers 2/3 serve eager launches, so consecutive collectives on the stream never reuse a buffer
         # that a peer may still be reading.
@@ -97,6 +104,22 @@ class FusedCollectives:
         ops.linear_any(a, w, out=buf)
         out = torch.empty((T, self.hidden), dtype=torch.bfloat16, device=a.device)
         self._launch(i, T, residual, norm_w, eps, w_offset, out)
+        return out
+
+    def argmax_vocab_parallel(self, local_logits: torch.Tensor, vocab_local: int) -> torch.Tensor:
+        """Global greedy token ids [rows] from this rank's logits shard [rows <= max_tokens, vocab / world]: the local
+        argmax kernel writes its (value, index) candidates into symmetric memory and one merge kernel (flag barrier +
+        peer loads) picks the winner on every rank. Between two calls the step's all-reduce barriers separate a peer's
+        reads from this rank's next writes, so one candidate buffer suffices."""
+        rows = local_logits.shape[0]
+        assert rows <= self.max_tokens
+        ops.argmax(local_logits, out=self._am_ids[:rows], out_vals=self._am_vals[:rows])
+        out = torch.empty(rows, dtype=torch.int64, device=local_logits.device)
+        rc = kernels().swb_argmax_peer_merge(self._am_val_ptrs, self._am_id_ptrs, self._flag_ptrs,
+                                             self._epochs.data_ptr(), self.comm.rank, self.comm.world, rows,
+                                             vocab_local, out.data_ptr(), stream_ptr())
+        check(rc, "swb_argmax_peer_merge")
+        self.comm.bytes_moved += rows * 12 * (self.comm.world - 1)
         return out
 
     def check(self) -> None:

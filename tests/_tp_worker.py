@@ -83,6 +83,13 @@ def main():
     got = runner.decode(seqs, toks).tolist()
     allg = comm.all_gather(torch.tensor([got], device=dev), dim=0)
     assert all(torch.equal(allg[0], allg[k]) for k in range(P)), "ranks disagree on sampled tokens"
+    # vocabulary-parallel greedy head (fused: candidates exchanged through peer memory) equals argmax of all logits
+    gh = torch.Generator(device=dev).manual_seed(123)
+    for rows in (1, 7, 64):
+        hid = torch.randn(rows, cfg.hidden_size, device=dev, generator=gh).bfloat16()
+        want = model.logits(hid).argmax(-1)
+        got_ids = model.greedy_tokens(hid)
+        assert torch.equal(want, got_ids), f"distributed argmax rows={rows}"
     for s_ in seqs:
         s_.release()
     # 3. prompts longer than the decode-sized exchange buffers: fused reduce-scatter / all-gather prefill path
