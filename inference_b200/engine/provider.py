@@ -275,6 +275,18 @@ def _pick_template(tokenizer_config: dict | None, cfg: ModelConfig) -> tuple[Cha
 
 
 def _build_backend(cfg: ModelConfig, weights: dict, backend_name: str, comm=None) -> DecodeBackend:
+    if cfg.architecture is Architecture.QWEN35:
+        # hybrid Gated-DeltaNet decoder: its own model class (recurrent state instead of a paged KV cache); on the
+        # b200 backend it runs in bf16 on the device with its projections on the tcgen05 GEMM
+        from ..models.qwen35 import Qwen35Config, Qwen35Model
+
+        on_gpu = backend_name == BACKEND_GPU
+        if on_gpu and not torch.cuda.is_available():
+            raise LoadError("the b200 backend needs a CUDA device (use the cpu runtime bundle on hosts without one)")
+        qcfg = Qwen35Config.from_json(cfg.raw)
+        model = Qwen35Model(qcfg, weights, dtype=torch.bfloat16 if on_gpu else torch.float32,
+                            device="cuda" if on_gpu else "cpu")
+        return OracleBackend(model, max_context=qcfg.max_position_embeddings or 8192)
     if backend_name == BACKEND_GPU:
         if not torch.cuda.is_available():
             raise LoadError("the b200 backend needs a CUDA device (use the cpu runtime bundle on hosts without one)")
@@ -308,12 +320,11 @@ def _descriptor(pid: str, backend: str) -> TextLlmDescriptor:
 
 def _can_load_gpu(spec: LoadSpec) -> bool:
     cfg = probe_config(spec)
-    return cfg is not None and _supported_on_gpu(cfg)
+    return cfg is not None and (_supported_on_gpu(cfg) or cfg.architecture is Architecture.QWEN35)
 
 
 def _can_load_cpu(spec: LoadSpec) -> bool:
-    cfg = probe_config(spec)
-    return cfg is not None and cfg.architecture is not Architecture.QWEN35
+    return probe_config(spec) is not None
 
 
 B200_LLAMA = TextLlmRegistration(lambda: _descriptor("b200-llama", BACKEND_GPU),
