@@ -19,9 +19,9 @@ def provider_registry() -> ProviderRegistry:
 
 
 def text_registry() -> TextLlmRegistry:
-    from ..engine.provider import B200_LLAMA
+    from ..engine.provider import B200_LLAMA, B200_LLAVA
 
-    return TextLlmRegistryBuilder().register(B200_LLAMA).build()
+    return TextLlmRegistryBuilder().register(B200_LLAMA).register(B200_LLAVA).build()
 
 
 def snapshot_preparer_registry() -> SnapshotPreparerRegistry:

@@ -19,9 +19,9 @@ def provider_registry() -> ProviderRegistry:
 
 
 def text_registry() -> TextLlmRegistry:
-    from ..engine.provider import CPU_LLAMA
+    from ..engine.provider import CPU_LLAMA, CPU_LLAVA
 
-    return TextLlmRegistryBuilder().register(CPU_LLAMA).build()
+    return TextLlmRegistryBuilder().register(CPU_LLAMA).register(CPU_LLAVA).build()
 
 
 def snapshot_preparer_registry() -> SnapshotPreparerRegistry:

