@@ -19,7 +19,13 @@ SWB_REGISTER_STATUS_UNIT(attn_decode_tma);
 
 namespace {
 
-constexpr int STAGES = 3;
+#ifndef SWB_DEC_STAGES
+#define SWB_DEC_STAGES 3
+#endif
+#ifndef SWB_DEC_MIN_CTAS
+#define SWB_DEC_MIN_CTAS 1
+#endif
+constexpr int STAGES = SWB_DEC_STAGES;
 constexpr int STAGE_BYTES = 2 * TILE_BYTES;  // K tile + V tile = 32 KB
 constexpr int Q_BYTES = 16 * 256;            // 4 KB
 constexpr int SMEM_BYTES = 1024 + Q_BYTES + STAGES * STAGE_BYTES + 256;
@@ -33,7 +39,7 @@ __device__ __forceinline__ uint32_t tma_tile_off(int tok, int c) {
 // Q rows are written by ordinary stores with the simple XOR swizzle of the other kernels.
 __device__ __forceinline__ uint32_t q_off(int r, int c) { return (uint32_t)(r * 256 + ((c ^ (r & 7)) << 4)); }
 
-__global__ void __launch_bounds__(160) attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap_k,
+__global__ void __launch_bounds__(160, SWB_DEC_MIN_CTAS) attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap_k,
                                                               const __grid_constant__ CUtensorMap tmap_v,
                                                               const AttnParams p) {
   pdl_launch_dependents();
