@@ -68,6 +68,8 @@ def _declare_kernels(lib: ctypes.CDLL) -> None:
     sig("swb_gemm_workspace_min", [], c_size_t)
     sig("swb_gemm_bf16", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                           c_int, c_int, c_int, c_void_p, c_size_t, c_int, c_int, c_int, c_void_p])
+    sig("swb_rmsnorm_prefetch", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
+                                 c_float, c_void_p, c_ll, c_void_p])
     sig("swb_rmsnorm", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float,
                         c_void_p])
     sig("swb_layernorm_mod", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,

@@ -43,9 +43,21 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 template <int THREADS, int VPT>
 __global__ void __launch_bounds__(THREADS) rmsnorm_kernel(const bf16* __restrict__ x, int ldx, bf16* residual,
                                                          int ldr, const bf16* __restrict__ w, bf16* out, int ldo,
-                                                         int H, float eps, float w_offset) {
+                                                         int H, float eps, float w_offset, const uint8_t* pf_ptr,
+                                                         long long pf_bytes) {
   pdl_launch_dependents();
   pdl_wait();
+  // The weights of the GEMM that consumes this norm do not depend on anything in flight: ask L2 for them now, so the
+  // memory system works through the norm and the GEMM's prologue instead of idling (decode steps are bandwidth bound).
+  if (pf_ptr) {
+    constexpr long long CHUNK = 4096;
+    const long long n_chunks = (pf_bytes + CHUNK - 1) / CHUNK;
+    for (long long c = (long long)blockIdx.x * THREADS + threadIdx.x; c < n_chunks; c += (long long)gridDim.x * THREADS) {
+      const long long off = c * CHUNK;
+      const unsigned bytes = (unsigned)min(CHUNK, pf_bytes - off) & ~15u;
+      if (bytes) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pf_ptr + off), "r"(bytes) : "memory");
+    }
+  }
   __shared__ float red[32];
   const int row = blockIdx.x;
   const int nvec = H / 8;
@@ -462,18 +474,31 @@ inline int last_err() { return launch_rc; }
 
 extern "C" {
 
+int swb_rmsnorm_prefetch(const void* x, int ldx, void* residual, int ldr, const void* w, void* out, int ldo, int T,
+                         int H, float eps, float w_offset, const void* prefetch_ptr, long long prefetch_bytes,
+                         void* stream);
+
 int swb_rmsnorm(const void* x, int ldx, void* residual, int ldr, const void* w, void* out, int ldo, int T, int H,
                 float eps, float w_offset, void* stream) {
+  return swb_rmsnorm_prefetch(x, ldx, residual, ldr, w, out, ldo, T, H, eps, w_offset, nullptr, 0, stream);
+}
+
+// As swb_rmsnorm; additionally asks L2 to fetch prefetch_bytes (16-byte aligned start) of the next kernel's weights.
+int swb_rmsnorm_prefetch(const void* x, int ldx, void* residual, int ldr, const void* w, void* out, int ldo, int T,
+                         int H, float eps, float w_offset, const void* prefetch_ptr, long long prefetch_bytes,
+                         void* stream) {
   using namespace swb;
   if (T <= 0) return 0;
   if (H % 8 != 0 || ldx % 8 != 0 || ldo % 8 != 0 || (residual && ldr % 8 != 0)) return -3;
+  if (prefetch_ptr && ((reinterpret_cast<uintptr_t>(prefetch_ptr) & 15) || prefetch_bytes < 0)) return -3;
+  const uint8_t* pf = prefetch_bytes > 0 ? reinterpret_cast<const uint8_t*>(prefetch_ptr) : nullptr;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   return launch_norm(H, [&](auto TH, auto VP) {
     constexpr int THREADS = decltype(TH)::value, VPT = decltype(VP)::value;
     launch_rc = launch_kernel(rmsnorm_kernel<THREADS, VPT>, dim3(T), dim3(THREADS), 0, s, reinterpret_cast<const bf16*>(x), ldx,
                                                         reinterpret_cast<bf16*>(residual), ldr,
                                                         reinterpret_cast<const bf16*>(w), reinterpret_cast<bf16*>(out),
-                                                        ldo, H, eps, w_offset);
+                                                        ldo, H, eps, w_offset, pf, prefetch_bytes);
     return last_err();
   });
 }

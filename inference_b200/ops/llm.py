@@ -8,8 +8,11 @@ from .runtime import check, ptr, require_cuda, stream_ptr
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, *, residual: torch.Tensor | None = None,
-            out: torch.Tensor | None = None, w_offset: float = 0.0) -> torch.Tensor:
+            out: torch.Tensor | None = None, w_offset: float = 0.0, prefetch: torch.Tensor | None = None,
+            prefetch_bytes: int = 0) -> torch.Tensor:
     """out = rmsnorm(x [+ residual]) * (w + w_offset); `residual` (if given) becomes x + residual in place.
+    `prefetch`: weights of the kernel that consumes this norm; the first `prefetch_bytes` of them (all when 0) are
+    requested into L2 while the norm runs.
 
     Semantics of the reference rms_norm (candle-llm/src/primitives/nn.rs:21-32): fp32 statistics over the
     last dimension. w_offset = 1 gives the Gemma "+1" convention."""
@@ -21,8 +24,15 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, *, residual: torch.Ten
         out = torch.empty_like(x2)
     o2 = out.reshape(-1, H)
     r2 = residual.reshape(-1, H) if residual is not None else None
-    rc = kernels().swb_rmsnorm(x2.data_ptr(), x2.stride(0), ptr(r2), r2.stride(0) if r2 is not None else 0,
-                               w.data_ptr(), o2.data_ptr(), o2.stride(0), T, H, eps, w_offset, stream_ptr())
+    if prefetch is not None:
+        nb = prefetch.numel() * prefetch.element_size()
+        nb = min(nb, prefetch_bytes) if prefetch_bytes > 0 else nb
+        rc = kernels().swb_rmsnorm_prefetch(x2.data_ptr(), x2.stride(0), ptr(r2), r2.stride(0) if r2 is not None else 0,
+                                            w.data_ptr(), o2.data_ptr(), o2.stride(0), T, H, eps, w_offset,
+                                            prefetch.data_ptr(), nb, stream_ptr())
+    else:
+        rc = kernels().swb_rmsnorm(x2.data_ptr(), x2.stride(0), ptr(r2), r2.stride(0) if r2 is not None else 0,
+                                   w.data_ptr(), o2.data_ptr(), o2.stride(0), T, H, eps, w_offset, stream_ptr())
     check(rc, "swb_rmsnorm")
     return out.reshape(x.shape)
 
