@@ -125,6 +125,35 @@ int swb_gemm_bf16_grouped(const void* A, int lda, const void* W, int ldw, int gr
   return swb::gemm_bf16_launch(a, reinterpret_cast<cudaStream_t>(stream));
 }
 
+// Decode GEMM inside a folded-RMSNorm chain (T <= 64, cluster kernel): ssq_in (nullable) = partial sums of squares
+// written by the producer of A, the accumulators are scaled by rsqrt(sum / norm_dim + eps) per token; ssq_out
+// (nullable) receives this launch's partials of the rows it stores (after the residual add). Buffers: 64 + 512 * 64
+// floats. Returns -3 when the shape is not served by the cluster kernel.
+int swb_gemm_bf16_normed(const void* A, int lda, const void* W, int ldw, void* D, int ldd, int T, int N, int K,
+                         const void* bias, const void* residual, int ld_res, int act, const void* ssq_in,
+                         void* ssq_out, int norm_dim, float norm_eps, void* stream) {
+  swb::GemmArgs a{};
+  a.A = A;
+  a.lda = lda;
+  a.W = W;
+  a.ldw = ldw;
+  a.D = D;
+  a.ldd = ldd;
+  a.T = T;
+  a.N = N;
+  a.K = K;
+  a.bias = bias;
+  a.residual = residual;
+  a.ld_res = ld_res;
+  a.act = act;
+  a.force_mode = -1;
+  a.ssq_in = reinterpret_cast<const float*>(ssq_in);
+  a.ssq_out = reinterpret_cast<float*>(ssq_out);
+  a.norm_dim = norm_dim;
+  a.norm_eps = norm_eps;
+  return swb::gemm_bf16_launch(a, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int swb_gemm_gated_supported(int T, int N, int K) { return swb::gemm_bf16_gated_supported(T, N, K); }
 
 size_t swb_gemm_workspace_min(void) { return swb::SWB_GEMM_COUNTER_BYTES + (size_t)(8u << 20); }

@@ -85,6 +85,7 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   uint64_t* bar_tfull = bar_empty + STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tfull + 1);
   volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  __shared__ float s_rstd[64];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -190,6 +191,18 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
 
   if (warp >= 2) {
     pdl_wait();
+    if (p.ssq_in) {
+      // per-token 1 / rms of the residual stream from the producer's per-CTA partial sums (fixed order: deterministic);
+      // two threads per token, overlapped with the weight streaming of the other warps
+      const int e = (warp - 2) * 32 + lane;
+      const int tok = e >> 1, half = e & 1;
+      const int count = __float_as_int(__ldcg(p.ssq_in));
+      float sacc = 0.f;
+      if (tok < BLOCK_N)
+        for (int i = half; i < count; i += 2) sacc += __ldcg(p.ssq_in + 64 + (size_t)i * 64 + tok);
+      sacc += __shfl_xor_sync(0xffffffffu, sacc, 1);
+      if (half == 0 && tok < BLOCK_N) s_rstd[tok] = rsqrtf(sacc / (float)p.norm_dim + p.norm_eps);
+    }
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     bool have = nkb > 0;
@@ -243,7 +256,9 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
       const int tok = idx / R8;
       const int row = (int)crank * R + f8 * 8;
       const int feat = tile_m * BM + row;
-      if (row >= BM || feat >= p.M || tok >= p.N) continue;
+      // (the body is a one-trip loop so that every lane reaches the convergent shuffle below it)
+      float ss = 0.f;
+      if (!(row >= BM || feat >= p.M || tok >= p.N)) do {
       float acc[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
@@ -253,6 +268,11 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
         const float4 a0 = rp[0], a1 = rp[1];
         acc[0] += a0.x; acc[1] += a0.y; acc[2] += a0.z; acc[3] += a0.w;
         acc[4] += a1.x; acc[5] += a1.y; acc[6] += a1.z; acc[7] += a1.w;
+      }
+      if (p.ssq_in) {
+        const float rs = s_rstd[tok];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] *= rs;
       }
       const int nvalid = min(8, p.M - feat);
       const size_t off = (size_t)tok * p.ldd + feat;
@@ -276,7 +296,7 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
           oh[0] = __floats2bfloat162_rn(act_apply(acc[0], a1) * acc[1], act_apply(acc[2], a1) * acc[3]);
           oh[1] = __floats2bfloat162_rn(act_apply(acc[4], a1) * acc[5], act_apply(acc[6], a1) * acc[7]);
           *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(p.out) + (size_t)tok * p.ldd + (feat >> 1)) = o;
-          continue;
+          break;
         }
         if (p.act != SWB_ACT_NONE) {
 #pragma unroll
@@ -302,6 +322,13 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
 #pragma unroll
           for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
           *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + off) = o;
+          if (p.ssq_out) {   // sum of squares of exactly what was stored (bf16-rounded)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 t = __bfloat1622float2(oh[j]);
+              ss += t.x * t.x + t.y * t.y;
+            }
+          }
         }
       } else if (p.act >= SWB_ACT_SWIGLU_PAIRS) {
         const int a1 = p.act == SWB_ACT_SWIGLU_PAIRS ? SWB_ACT_SILU : SWB_ACT_GELU_TANH;
@@ -320,9 +347,15 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
             reinterpret_cast<bf16*>(p.out)[off + j] = __float2bfloat16(x);
         }
       }
+      } while (0);
+      if (p.ssq_out) {       // every lane of the warp arrives here: reduce over the R8 threads that share a token
+        for (int o2 = 1; o2 < R8; o2 <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o2);
+        if (f8 == 0 && tok < BLOCK_N) p.ssq_out[64 + (size_t)blockIdx.x * 64 + tok] = ss;
+      }
     }
   }
 
+  if (p.ssq_out && blockIdx.x == 0 && threadIdx.x == 64) p.ssq_out[0] = __int_as_float((int)gridDim.x);
   if (tr && threadIdx.x == 64) tr[6] = global_timer_ns();    // outputs stored
   tc_fence_before_sync();
   __syncthreads();
@@ -407,6 +440,10 @@ int gemm_decode_cluster_launch(const GemmArgs& a, int force_cluster, cudaStream_
   p.residual = reinterpret_cast<const __nv_bfloat16*>(a.residual);
   p.ld_res = a.ld_res;
   p.act = a.act;
+  p.ssq_out = a.ssq_out;
+  p.ssq_in = a.ssq_in;
+  p.norm_dim = a.norm_dim;
+  p.norm_eps = a.norm_eps;
   p.trace = gemm_trace_buffer();
   p.vec_ok = ((reinterpret_cast<uintptr_t>(a.D) & 15) == 0) && (!a.bias || (reinterpret_cast<uintptr_t>(a.bias) & 15) == 0) &&
              (!a.residual || (reinterpret_cast<uintptr_t>(a.residual) & 15) == 0) && (!a.out_fp32 || (a.ldd % 4) == 0);
@@ -421,6 +458,13 @@ int gemm_decode_cluster_launch(const GemmArgs& a, int force_cluster, cudaStream_
   if (force_cluster > 0) cluster = std::min(8, force_cluster);
   if (cluster == 5) cluster = 4;
   if (cluster == 7) cluster = 6;
+  if (a.ssq_out || a.ssq_in) {
+    // the per-token reduction in the producer's epilogue pairs lanes by xor: rows per member / 8 must be a power of two
+    if (cluster == 3) cluster = 2;
+    if (cluster == 6) cluster = 4;
+    if (a.ssq_out && (a.N % BM != 0 || a.out_fp32 || p.tiles_m * cluster > 512)) return -3;
+    if (!p.vec_ok || (a.ldd & 7) != 0) return -3;
+  }
   CUtensorMap tw, tx;
   int r = make_tmap_bf16_2d(&tw, a.W, a.N, a.K, a.ldw, BM);
   if (r) return r;

@@ -723,6 +723,10 @@ int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
   if (swapped < 0) swapped = (a.T <= 256) ? 1 : 0;
   // decode-sized problems with at most two weight tiles per SM: the two-CTAs-per-SM cluster kernel (split-K over a
   // cluster with a DSMEM reduction when tiles are few, plain whole tiles otherwise)
+  // the folded-norm chain lives in the decode cluster kernel only
+  if ((a.ssq_out || a.ssq_in) && (a.scatter || a.group_of_mtile || a.force_mode == 0 || a.force_mode == 1 ||
+                                  !gemm_bf16_gated_supported(a.T, a.N & ~1, a.K)))
+    return -3;
   // gated-pair epilogues exist in the decode cluster kernel only (bf16 output, no residual)
   const bool pairs = a.act >= SWB_ACT_SWIGLU_PAIRS;
   if (pairs && (a.scatter || a.group_of_mtile || a.residual || a.out_fp32 || (a.N & 1) || a.force_mode == 0 ||

@@ -59,6 +59,15 @@ struct GemmParams {
   // [g * group_rows, g * group_rows + N) of the stacked weight); a negative entry skips the tile
   const int* group_of_mtile;
   int group_rows;
+  // RMSNorm folded into a chain of decode GEMMs (cluster kernel only). A producer (o / down projection with the
+  // residual add in its epilogue) writes, per CTA and token, the sum of squares of the rows it stored:
+  // ssq_out[0] = CTA count (as int bits), ssq_out[64 + cta * 64 + token]. The consumer (qkv / gate-up projection on the
+  // un-normalised residual stream, norm weight pre-multiplied into its weights) sums those partials in CTA order and
+  // scales its accumulators by rsqrt(sum / norm_dim + eps) per token.
+  float* ssq_out;
+  const float* ssq_in;
+  int norm_dim;
+  float norm_eps;
 };
 
 // User-level problem: D[T, N] = act(A[T, K] * W[N, K]^T + bias[N]) + residual[T, N].
@@ -83,6 +92,10 @@ struct GemmArgs {
   const GemmScatter* scatter = nullptr;
   const int* group_of_mtile = nullptr;   // device [ceil(T / 128)]: weight group per 128-row tile, < 0 = skip
   int groups = 0;                        // W is [groups * N, K] when group_of_mtile is set
+  float* ssq_out = nullptr;              // see GemmParams (decode cluster kernel only)
+  const float* ssq_in = nullptr;
+  int norm_dim = 0;
+  float norm_eps = 0.f;
 };
 
 int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream);

@@ -196,7 +196,39 @@ class LlamaGpu:
                 gate_up=dev16(torch.stack([gate, up], dim=1).reshape(2 * gate.shape[0], -1)), down=dev16(_shard_cols(get(f"{p}.mlp.down_proj.weight"), r, P)),
                 post_mlp_ln=dev16(post_mlp) if post_mlp is not None else None, moe=moe))
         assert D == 128
+        self.fold_norms()
         return self
+
+    def fold_norms(self) -> bool:
+        """Multiply each layer's input / post-attention norm weight into the projection that consumes it (qkv,
+        gate_up) and leave a unit norm weight behind. The model computes the same function; decode-sized steps can
+        then skip the norm kernels: the o / down projections add the residual and emit per-token sums of squares in
+        their epilogues and the qkv / gate_up projections scale their accumulators by 1 / rms
+        (`ops.gemm_bf16_normed`). Only for unsharded dense layers without sandwich norms."""
+        if self.norm_folded or self.comm.is_parallel or os.environ.get("SWB_FOLD_NORMS", "1") == "0":
+            return False
+        woff = self.cfg.norm_weight_offset
+        for L in self.layers:
+            if (L.moe is not None or L.post_attn_ln is not None or L.post_mlp_ln is not None or
+                    not all(isinstance(t, torch.Tensor) for t in (L.qkv, L.o, L.gate_up, L.down))):
+                return False
+        for L in self.layers:
+            for ln_name, w_name in (("ln1", "qkv"), ("ln2", "gate_up")):
+                g = getattr(L, ln_name).float() + woff
+                setattr(L, w_name, (getattr(L, w_name).float() * g[None, :]).to(torch.bfloat16).contiguous())
+                setattr(L, ln_name, torch.full_like(getattr(L, ln_name), 1.0 - woff))
+        H, F2 = self.cfg.hidden_size, 2 * self.ffn
+        shapes = (((self.hq + 2 * self.hkv) * self.cfg.head_dim, H), (H, self.hq * self.cfg.head_dim), (F2, H),
+                  (H, self.ffn))
+        self._chain_ok = (self.device.type == "cuda" and H % 128 == 0 and H // 128 * 8 <= 512 and
+                          all(ops.gated_fused(64, n & ~1, k) for n, k in shapes))
+        if self._chain_ok:
+            self._ssq = [torch.zeros(ops.SSQ_FLOATS, dtype=torch.float32, device=self.device) for _ in range(2)]
+        self.norm_folded = True
+        return True
+
+    norm_folded: bool = False
+    _chain_ok: bool = False
 
     def init_random(self, seed: int = 0, std: float = 0.02) -> "LlamaGpu":
         """Random N(0, std) weights generated directly on the device in this rank's shard shapes."""
@@ -230,6 +262,7 @@ class LlamaGpu:
                 k_norm=torch.ones(D, dtype=torch.bfloat16, device=dev) if cfg.architecture.has_qk_norm else None,
                 o=rnd(H, self.hq * D), post_attn_ln=ones(H) if sandwich else None, ln2=ones(H),
                 gate_up=rnd(2 * self.ffn, H), down=rnd(H, self.ffn), post_mlp_ln=ones(H) if sandwich else None))
+        self.fold_norms()
         return self
 
     def quantize_(self, fmt: str = "Q4_K") -> "LlamaGpu":
@@ -289,15 +322,25 @@ class LlamaGpu:
         # optional: each norm asks L2 for (the first megabytes of) its consumer's weights (see l2_prefetch_bytes)
         pf_bytes = self.l2_prefetch_bytes if inp.decode else -1
         pf = (lambda t: t if (pf_bytes >= 0 and isinstance(t, torch.Tensor)) else None)
+        # decode-sized steps of an unsharded dense model: the norms are folded into a chain of GEMM epilogues
+        chain = (self._chain_ok and inp.decode and T <= 64 and self.quant_format is None and
+                 os.environ.get("SWB_NORM_CHAIN", "1") != "0")
+        ssq_prev = None                 # partial sums of squares of `res` (valid while branch is None)
+        H = cfg.hidden_size
         for li, L in enumerate(self.layers):
-            if pending_h is not None:
+            if chain and ssq_prev is not None and branch is None:
+                h = None                # the qkv projection normalises the residual stream itself
+            elif pending_h is not None:
                 h = pending_h           # already all-reduced, added to the residual and normed with this ln1
             elif branch is None:
                 h = ops.rmsnorm(res, L.ln1, eps, w_offset=woff, prefetch=pf(L.qkv), prefetch_bytes=pf_bytes)
             else:
                 h = ops.rmsnorm(branch, L.ln1, eps, residual=res, w_offset=woff, prefetch=pf(L.qkv),
                                 prefetch_bytes=pf_bytes)
-            qkv = ops.linear_any(h, L.qkv, bias=L.qkv_bias)
+            if h is None:
+                qkv = ops.gemm_bf16_normed(res, L.qkv, bias=L.qkv_bias, ssq_in=ssq_prev, norm_dim=H, eps=eps)
+            else:
+                qkv = ops.linear_any(h, L.qkv, bias=L.qkv_bias)
             ops.rope_kv_write(qkv, inp.positions, inp.slot_mapping, self.cos, self.sin, kv_pool[li, 0], kv_pool[li, 1],
                               self.hq, self.hkv, D, rot_dim=self.rot_dim, interleaved=self.rope_interleaved,
                               q_norm=L.q_norm, k_norm=L.k_norm, norm_eps=eps, norm_w_offset=woff,
@@ -314,6 +357,19 @@ class LlamaGpu:
                                            cu_q=inp.cu_q, max_q_len=inp.max_q_len, scale=cfg.attn_scale, causal=True,
                                            decode=inp.decode, num_splits=inp.attn_splits,
                                            softcap=cfg.attn_logit_softcap or 0.0)
+            if chain:
+                if branch is not None:          # first layer of the chain: fold the pending branch into the stream
+                    res.add_(branch)
+                    branch = None
+                    n += 1
+                gelu = cfg.mlp_activation in ("gelu", "gelu_tanh")
+                ops.gemm_bf16_normed(attn.reshape(T, -1), L.o, out=res, residual=res, ssq_out=self._ssq[0])
+                act = ops.gemm_bf16_normed(res, L.gate_up, act="geglu_pairs" if gelu else "swiglu_pairs",
+                                           ssq_in=self._ssq[0], norm_dim=H, eps=eps)
+                ops.gemm_bf16_normed(act, L.down, out=res, residual=res, ssq_out=self._ssq[1])
+                ssq_prev, pending_h = self._ssq[1], None
+                n += (6 if inp.attn_splits == 1 else 7) + (1 if h is not None else 0)
+                continue
             fused = self.comm.fused if (self.comm.fused is not None and T <= self.comm.fused.max_tokens and
                                         L.post_attn_ln is None) else None
             if fused is not None:
@@ -349,8 +405,12 @@ class LlamaGpu:
         if not last_stage:
             assert pending_h is None
             return res, branch
-        final = pending_h if pending_h is not None else ops.rmsnorm(branch, self.norm, eps, residual=res,
-                                                                    w_offset=woff)
+        if pending_h is not None:
+            final = pending_h
+        elif branch is None:
+            final = ops.rmsnorm(res, self.norm, eps, w_offset=woff)
+        else:
+            final = ops.rmsnorm(branch, self.norm, eps, residual=res, w_offset=woff)
         self.launches += 1
         if inp.logits_rows is not None:
             return final.index_select(0, inp.logits_rows)

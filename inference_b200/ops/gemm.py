@@ -72,6 +72,35 @@ def gemm_bf16_grouped(a: torch.Tensor, w: torch.Tensor, tile_groups: torch.Tenso
     return out
 
 
+SSQ_FLOATS = 64 + 512 * 64
+
+
+def gemm_bf16_normed(a: torch.Tensor, w: torch.Tensor, *, out: torch.Tensor | None = None,
+                     bias: torch.Tensor | None = None, residual: torch.Tensor | None = None, act: str | None = None,
+                     ssq_in: torch.Tensor | None = None, ssq_out: torch.Tensor | None = None, norm_dim: int = 0,
+                     eps: float = 0.0) -> torch.Tensor:
+    """One link of a folded-RMSNorm chain of decode GEMMs (T <= 64; see swb_gemm_bf16_normed).
+
+    Consumer link (`ssq_in`): `a` is the un-normalised residual stream and `w` already carries the norm weight;
+    the result is rmsnorm(a) @ w^T. Producer link (`ssq_out`): stores a @ w^T + residual (in place when out is
+    residual) and the partial sums of squares of what it stored. fp32 buffers of SSQ_FLOATS elements."""
+    require_cuda(a, w)
+    T, K = a.shape
+    N = w.shape[0]
+    n_out = N // 2 if ACT[act] >= 3 else N
+    if out is None:
+        out = torch.empty((T, n_out), dtype=torch.bfloat16, device=a.device)
+    assert out.shape == (T, n_out) and out.dtype == torch.bfloat16 and a.stride(1) == 1 and w.stride(1) == 1
+    for b in (ssq_in, ssq_out):
+        assert b is None or (b.dtype == torch.float32 and b.numel() >= SSQ_FLOATS and b.is_contiguous())
+    rc = kernels().swb_gemm_bf16_normed(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
+                                        out.stride(0), T, N, K, ptr(bias), ptr(residual),
+                                        residual.stride(0) if residual is not None else 0, ACT[act], ptr(ssq_in),
+                                        ptr(ssq_out), norm_dim, eps, stream_ptr())
+    check(rc, "swb_gemm_bf16_normed")
+    return out
+
+
 def gated_fused(T: int, N: int, K: int) -> bool:
     """True when linear_gated applies the activation inside the projection kernel for this shape."""
     return bool(kernels().swb_gemm_gated_supported(T, N, K))
