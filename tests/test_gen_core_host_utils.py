@@ -83,3 +83,81 @@ def test_bs1770_loudness():
     norm = audio_dsp.normalize_loudness(mono, -16.0)
     assert audio_dsp.integrated_loudness(norm) == pytest.approx(-16.0, abs=0.1)
     assert audio_dsp.mixdown_mono(stereo).channels == 1 and math.isfinite(audio_dsp.integrated_loudness(norm))
+
+
+def test_sdxl_ldm_key_remap():
+    import torch
+
+    from inference_b200.contracts.gen_core.sdxl_ldm import SdxlComponent as C, apply_remap, remap_sdxl_ldm_key as r
+
+    a = r("model.diffusion_model.input_blocks.7.0.out_layers.3.weight")
+    assert (a.op, a.component, a.key) == ("rename", C.UNET, "down_blocks.2.resnets.0.conv2.weight")
+    a = r("first_stage_model.decoder.up.1.block.2.nin_shortcut.weight")
+    assert (a.op, a.component, a.key) == ("rename", C.VAE, "decoder.up_blocks.2.resnets.2.conv_shortcut.weight")
+    a = r("conditioner.embedders.1.model.transformer.resblocks.9.attn.in_proj_weight")
+    assert a.op == "split_qkv" and a.keys == tuple(f"text_model.encoder.layers.9.self_attn.{n}_proj.weight" for n in "qkv")
+    assert r("model.diffusion_model.time_embed.0.weight").key == "time_embedding.linear_1.weight"
+    assert r("model.diffusion_model.input_blocks.0.0.bias").key == "conv_in.bias"
+    assert r("model.diffusion_model.input_blocks.3.0.op.weight").key == "down_blocks.0.downsamplers.0.conv.weight"
+    assert r("model.diffusion_model.input_blocks.4.1.proj_in.weight").key == "down_blocks.1.attentions.0.proj_in.weight"
+    assert r("model.diffusion_model.middle_block.1.norm.weight").key == "mid_block.attentions.0.norm.weight"
+    assert r("model.diffusion_model.middle_block.2.in_layers.0.weight").key == "mid_block.resnets.1.norm1.weight"
+    assert r("model.diffusion_model.output_blocks.2.2.conv.weight").key == "up_blocks.0.upsamplers.0.conv.weight"
+    assert r("model.diffusion_model.output_blocks.5.1.conv.weight").key == "up_blocks.1.upsamplers.0.conv.weight"
+    assert r("conditioner.embedders.0.transformer.text_model.final_layer_norm.bias").component is C.CLIP_L
+    assert r("conditioner.embedders.1.model.text_projection").op == "transpose"
+    assert r("conditioner.embedders.1.model.positional_embedding").key == "text_model.embeddings.position_embedding.weight"
+    assert r("conditioner.embedders.1.model.transformer.resblocks.0.mlp.c_fc.bias").key == \
+        "text_model.encoder.layers.0.mlp.fc1.bias"
+    a = r("first_stage_model.decoder.mid.attn_1.q.weight")
+    assert (a.op, a.key) == ("squeeze", "decoder.mid_block.attentions.0.to_q.weight")
+    assert r("first_stage_model.encoder.down.2.downsample.conv.bias").key == "encoder.down_blocks.2.downsamplers.0.conv.bias"
+    assert r("first_stage_model.decoder.up.3.upsample.conv.weight").key == "decoder.up_blocks.0.upsamplers.0.conv.weight"
+    assert r("unrelated.key") is None and r("model.diffusion_model.unknown") is None
+    parts = apply_remap({
+        "conditioner.embedders.1.model.transformer.resblocks.0.attn.in_proj_bias": torch.arange(6.0),
+        "conditioner.embedders.1.model.text_projection": torch.arange(6.0).view(2, 3),
+        "first_stage_model.decoder.mid.attn_1.k.weight": torch.zeros(4, 4, 1, 1),
+        "model.diffusion_model.out.2.bias": torch.ones(4)})
+    g = parts[C.CLIP_BIG_G]
+    assert g["text_model.encoder.layers.0.self_attn.k_proj.bias"].tolist() == [2.0, 3.0]
+    assert g["text_projection.weight"].shape == (3, 2)
+    assert parts[C.VAE]["decoder.mid_block.attentions.0.to_k.weight"].shape == (4, 4)
+    assert parts[C.UNET]["conv_out.bias"].shape == (4,)
+
+
+def test_media_test_tools(tmp_path, monkeypatch):
+    import pytest
+    import torch
+
+    from inference_b200.contracts.gen_core.media import Image
+    from inference_b200.testkit import media_tools as mt
+
+    img = Image(3, 2, bytes(range(18)))
+    mt.write_ppm(tmp_path / "a.ppm", img)
+    back = mt.read_ppm(tmp_path / "a.ppm")
+    assert (back.width, back.height, back.pixels) == (3, 2, img.pixels)
+    (tmp_path / "c.ppm").write_bytes(b"P6\n# comment\n1 1\n255\n" + bytes([9, 8, 7]))
+    assert mt.read_ppm(tmp_path / "c.ppm").pixels == bytes([9, 8, 7])
+    (tmp_path / "bad.ppm").write_bytes(b"P5\n1 1\n255\n\x00")
+    with pytest.raises(ValueError):
+        mt.read_ppm(tmp_path / "bad.ppm")
+    assert mt.mean_abs_diff(img, Image(3, 2, bytes([v + 2 for v in range(18)]))) == 2.0
+    assert abs(mt.cosine([1, 0], [1, 0]) - 1) < 1e-12 and abs(mt.cosine([1, 0], [0, 1])) < 1e-12
+    assert mt.cosine([0, 0], [1, 1]) == 0.0
+    assert abs(mt.tensor_cosine(torch.tensor([1.0, 2.0]), torch.tensor([2.0, 4.0])) - 1) < 1e-12
+    monkeypatch.setenv("SWB_TEST_DIR", str(tmp_path))
+    assert mt.env_path("SWB_TEST_DIR") == tmp_path and mt.env_path_opt("SWB_UNSET_DIR") is None
+    with pytest.raises(RuntimeError, match="SWB_UNSET_DIR"):
+        mt.env_path("SWB_UNSET_DIR")
+    readings = iter([100, 100, 900, 400, 2500, 300, 300, 300, 300, 300, 300, 300])
+    probe = lambda: next(readings, 300)
+    vp = mt.VramProbe(probe, interval_s=0.001).assert_idle(1.0)
+    ph = vp.phase()
+    __import__("time").sleep(0.05)
+    vp.end_load(ph)
+    rep = vp.report().assert_trustworthy(1.0)
+    assert rep.baseline_mib == 100 and rep.load_peak_mib == 2500 and abs(rep.load_delta_gb - 2400 / 1024) < 1e-9
+    with pytest.raises(AssertionError):
+        mt.VramProbe(lambda: 5000).assert_idle(1.0)
+    assert mt.cuda_mempool_used_high_bytes() is None or mt.cuda_mempool_used_high_bytes() >= 0
