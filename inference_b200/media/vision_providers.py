@@ -232,4 +232,41 @@ def registrations(backend: str) -> dict[str, list[Registration]]:
         "image_embedder": [Registration(d(ClipImageEmbedder.ID, "clip"), lambda s: _load_clip_image(s, backend))],
         "text_embedder": [Registration(d(ClipTextEmbedder.ID, "clip"), lambda s: _load_clip_text(s, backend))],
         "captioner": [Registration(d(LlavaCaptioner.ID, "llava"), lambda s: _load_captioner(s, backend))],
+        "transform": [Registration(d(DepthTransform.ID, "depth_anything"), lambda s: _load_depth(s, backend))],
     }
+
+
+class DepthTransform:
+    """`Transform` provider: image -> depth map rendered as an 8-bit grey image of the input size (min-max
+    normalised; larger = closer for relative-depth checkpoints)."""
+
+    ID = "depth_anything_v2"
+
+    def __init__(self, model, backend: str):
+        self.model, self.backend = model, backend
+
+    def descriptor(self) -> SimpleDescriptor:
+        return SimpleDescriptor(self.ID, "depth_anything", self.backend, {"type": self.model.cfg.depth_estimation_type})
+
+    def depth(self, image: Image, target: int | None = None) -> torch.Tensor:
+        """fp32 [H, W] at the input resolution."""
+        from ..models.depth import preprocess as depth_pre
+
+        cfg = self.model.cfg
+        px = depth_pre(image_tensor(image), target or cfg.image_size, cfg.patch_size)
+        d = self.model.predict(px).float().unsqueeze(1)
+        return F.interpolate(d, size=(image.height, image.width), mode="bilinear", align_corners=False)[0, 0].cpu()
+
+    def apply(self, image: Image, params: dict | None = None) -> Image:
+        d = self.depth(image, (params or {}).get("target"))
+        lo, hi = float(d.min()), float(d.max())
+        g = ((d - lo) / (hi - lo) if hi > lo else torch.zeros_like(d)).mul(255).round().clamp(0, 255).to(torch.uint8)
+        return Image(image.width, image.height, bytes(g.unsqueeze(-1).expand(-1, -1, 3).contiguous().flatten().tolist()))
+
+
+def _load_depth(spec: LoadSpec, backend: str) -> DepthTransform:
+    from ..models.depth import DepthAnything, DepthConfig
+
+    _, cfg, w = _load_dir(spec, DepthTransform.ID)
+    dev, dtype = _device_dtype(backend)
+    return DepthTransform(DepthAnything(DepthConfig.from_json(cfg), w, dev, dtype), backend)

@@ -213,3 +213,40 @@ def test_llava_text_provider_answers_about_an_image(tmp_path):
     plain = llm.generate(TextLlmRequest(messages=[Message.user("hello world")], max_new_tokens=3, seed=0,
                                         sampling=Sampling(temperature=0.0)), on_event=lambda e: None)
     assert plain.usage.generated_tokens >= 1
+
+
+def test_depth_anything_matches_hugging_face_and_transform_provider():
+    from transformers import DepthAnythingConfig, DepthAnythingForDepthEstimation, Dinov2Config
+
+    from inference_b200.contracts.gen_core.media import Image
+    from inference_b200.media.vision_providers import DepthTransform
+    from inference_b200.models.depth import DepthAnything, DepthConfig, preprocess
+
+    torch.manual_seed(4)
+    bc = Dinov2Config(hidden_size=32, num_hidden_layers=4, num_attention_heads=4, mlp_ratio=2, patch_size=14,
+                      image_size=42, out_indices=[1, 2, 3, 4], apply_layernorm=True, reshape_hidden_states=False)
+    hc = DepthAnythingConfig(backbone_config=bc, patch_size=14, reassemble_hidden_size=32,
+                             neck_hidden_sizes=[8, 16, 24, 32], fusion_hidden_size=16, head_hidden_size=8,
+                             reassemble_factors=[4, 2, 1, 0.5])
+    hf = DepthAnythingForDepthEstimation(hc).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith("lambda1"):
+                p.copy_(0.5 + torch.rand_like(p))
+    cfg = DepthConfig.from_json(hc.to_dict())
+    assert cfg.out_indices == [1, 2, 3, 4] and cfg.neck_hidden_sizes == [8, 16, 24, 32] and cfg.hidden_size == 32
+    model = DepthAnything(cfg, dict(hf.state_dict()))
+    for size in ((42, 42), (56, 70)):               # the second needs the position embedding interpolated
+        px = torch.randn(2, 3, *size)
+        with torch.no_grad():
+            ref = hf(pixel_values=px).predicted_depth
+        got = model.predict(px)
+        assert got.shape == ref.shape == (2, *size)
+        torch.testing.assert_close(got, ref, atol=2e-4, rtol=2e-4)
+    img = Image(50, 40, bytes(torch.randint(0, 256, (40 * 50 * 3,), generator=torch.Generator().manual_seed(1),
+                                            dtype=torch.uint8).tolist()))
+    assert preprocess(torch.zeros(40, 50, 3, dtype=torch.uint8), 42, 14).shape == (1, 3, 42, 56)
+    tr = DepthTransform(model, "cpu")
+    out = tr.apply(img, {"target": 42})
+    assert (out.width, out.height) == (50, 40) and max(out.pixels) == 255 and min(out.pixels) == 0
+    assert out.pixels[0] == out.pixels[1] == out.pixels[2] and tr.descriptor().id == "depth_anything_v2"
