@@ -23,8 +23,26 @@ def _whisper_registration(backend: str) -> Registration:
     return Registration(lambda: SimpleDescriptor("whisper", "whisper", backend, {"sample_rate": 16_000}), load)
 
 
+CHATTERBOX_LICENSE = WeightLicense("MIT", "MIT License", "https://huggingface.co/ResembleAI/chatterbox", "Resemble AI", True)
+
+
+def _chatterbox_ve_registration(backend: str) -> Registration:
+    def load(spec: LoadSpec):
+        from ..contracts.errors import LoadError
+        from ..io.safetensors_io import load_file
+        from .voice_encoder import ChatterboxVoiceEmbedder, SpeakerEncoder
+
+        if spec.weights is None or not spec.weights.is_file:
+            raise LoadError("chatterbox_ve: the load spec needs the ve.safetensors file")
+        return ChatterboxVoiceEmbedder(SpeakerEncoder(load_file(spec.weights.path), "cuda" if backend == "b200" else "cpu"),
+                                       backend)
+
+    return Registration(lambda: SimpleDescriptor("chatterbox_ve", "chatterbox", backend, {"dim": 256}), load)
+
+
 def register_providers(b: ProviderRegistryBuilder, backend: str) -> ProviderRegistryBuilder:
     b.register("transcriber", _whisper_registration(backend))
+    b.register("voice_embedder", _chatterbox_ve_registration(backend))
     return b
 
 
@@ -33,7 +51,7 @@ def provider_registry(backend: str = "b200") -> ProviderRegistry:
 
 
 def weight_licenses() -> list[WeightLicenseEntry]:
-    return [WeightLicenseEntry("whisper", WHISPER_LICENSE)]
+    return [WeightLicenseEntry("whisper", WHISPER_LICENSE), WeightLicenseEntry("chatterbox_ve", CHATTERBOX_LICENSE)]
 
 
 def weight_licenses_manifest() -> str:

@@ -177,7 +177,7 @@ def test_audio_catalog_registers_whisper_and_licenses(tmp_path):
     reg = catalog.provider_registry("cpu")
     assert reg.ids("transcriber") == ["whisper"] and reg.descriptor_conformance_errors() == []
     manifest = json.loads(catalog.weight_licenses_manifest())
-    assert manifest["model_weight_licenses"][0]["provider_id"] == "whisper"
+    assert [r["provider_id"] for r in manifest["model_weight_licenses"]] == ["chatterbox_ve", "whisper"]
     assert catalog.can_prepare(["a/config.json", "a/tokenizer.json", "a/model.safetensors"])
     assert not catalog.can_prepare(["a/config.json", "a/model.safetensors"])
     hc, hf = _tiny_whisper()
@@ -196,3 +196,49 @@ def test_audio_catalog_registers_whisper_and_licenses(tmp_path):
     assert out.tokens <= 4
     with pytest.raises(Exception):
         reg.load_kind("transcriber", "whisper", LoadSpec(weights=WeightsSource.file(tmp_path / "model.safetensors")))
+
+
+def test_chatterbox_voice_encoder(tmp_path):
+    from inference_b200.audio import catalog, voice_encoder as ve
+    from inference_b200.contracts.gen_core.runtime import LoadSpec, WeightsSource
+    from inference_b200.io.safetensors_io import save_file
+
+    torch.manual_seed(0)
+    lstm = torch.nn.LSTM(40, 256, num_layers=3, batch_first=True)
+    proj = torch.nn.Linear(256, 256)
+    w = {f"lstm.{k}": v.detach() for k, v in lstm.state_dict().items()}
+    w.update({"proj.weight": proj.weight.detach(), "proj.bias": proj.bias.detach()})
+    enc = ve.SpeakerEncoder(w)
+    mel = torch.rand(57, 40)
+    with torch.no_grad():
+        ref = torch.relu(proj(lstm(mel[None])[1][0][-1, 0]))
+    torch.testing.assert_close(enc.forward_block(mel), ref, atol=1e-5, rtol=1e-5)
+    short = enc.embed_mel_frames(mel)
+    assert abs(float(short.norm()) - 1) < 1e-5
+    long_mel = torch.rand(400, 40)
+    starts = [0, 80, 160, 240]
+    want = ve.l2_normalize(sum(enc.forward_block(long_mel[s:s + 160]) for s in starts) / 4)
+    torch.testing.assert_close(enc.embed_mel_frames(long_mel), want)
+    odd = enc.embed_mel_frames(torch.rand(401, 40))            # a ragged tail adds one partial ending at the last frame
+    assert odd.shape == (256,)
+    # front end
+    quiet = torch.full((1600,), 0.001)
+    assert abs(10 * math.log10(float((ve.normalize_volume(quiet) ** 2).mean())) + 30) < 1e-3
+    loud = torch.full((1600,), 0.5)
+    assert torch.equal(ve.normalize_volume(loud), loud)
+    m = ve.wav_to_mel_frames(torch.sin(torch.arange(16000) * 0.05) * 0.1, 16000)
+    assert m.shape == (101, 40) and float(m.min()) >= 0
+    assert ve.wav_to_mel_frames(torch.zeros(10), 16000).shape[0] == 0
+    assert abs(ve.cosine_similarity([1, 0], [-1, 0]) + 1) < 1e-6 and ve.cosine_similarity([0, 0], [1, 1]) == 0.0
+    # provider through the audio catalog (a single passed-in file)
+    save_file({k: v.contiguous() for k, v in w.items()}, tmp_path / "ve.safetensors")
+    reg = catalog.provider_registry("cpu")
+    assert reg.ids("voice_embedder") == ["chatterbox_ve"]
+    emb = reg.load_kind("voice_embedder", "chatterbox_ve", LoadSpec(weights=WeightsSource.file(tmp_path / "ve.safetensors")))
+    track = AudioTrack(24_000, 2, [0.05 * math.sin(i / 11) for i in range(24_000)])
+    a, b = emb.embed(track), emb.embed(track)
+    assert len(a) == 256 and a == b and abs(sum(x * x for x in a) - 1) < 1e-4
+    with pytest.raises(Exception):
+        reg.load_kind("voice_embedder", "chatterbox_ve", LoadSpec.from_dir(tmp_path))
+    with pytest.raises(dsp.AudioError):
+        emb.embed(AudioTrack(16_000, 1, []))
