@@ -1,0 +1,115 @@
+// NVFP4 quantiser on the device: fp32 / bf16 rows -> E2M1 codes, swizzled unsigned-E4M3 block scales and one fp32
+// tensor scale, bit-identical to the host packer (`ops/nvfp4.py`, which restates candle-gen/src/quant/nvfp4.rs:150-260;
+// the reference's device version is candle-gen/src/quant/nvfp4_quant.cu:80-156).
+//   pass 1: one thread per 16-column block: block amax, and the tensor amax by atomicMax on the float's bit pattern
+//           (non-negative floats order like unsigned integers);
+//   pass 2: global = amax / (6 * 448); block scale = RNE-to-E4M3(block amax / (6 * global)); codes = nearest E2M1 of
+//           x / (e4m3 * global) with ties to the even code; two codes per byte (even column in the low nibble);
+//           scale bytes into the 128-row x 4-block atoms that block-scaled tensor-core instructions read.
+#include "common.cuh"
+
+#include <cuda_fp8.h>
+
+namespace swb {
+namespace {
+
+template <bool FP32>
+__device__ __forceinline__ float load_elem(const void* x, size_t i) {
+  if constexpr (FP32) return reinterpret_cast<const float*>(x)[i];
+  return __bfloat162float(reinterpret_cast<const bf16*>(x)[i]);
+}
+
+template <bool FP32>
+__global__ void __launch_bounds__(256) nvfp4_block_amax_kernel(const void* x, long long ld, int rows, int nb,
+                                                              float* block_amax, unsigned int* tensor_amax_bits) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  float a = 0.f;
+  if (i < (long long)rows * nb) {
+    const int r = (int)(i / nb), b = (int)(i % nb);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) a = fmaxf(a, fabsf(load_elem<FP32>(x, (size_t)r * ld + b * 16 + j)));
+    block_amax[i] = a;
+  }
+  // one atomic per warp
+  for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+  if ((threadIdx.x & 31) == 0 && a > 0.f) atomicMax(tensor_amax_bits, __float_as_uint(a));
+}
+
+__device__ __forceinline__ float e4m3_to_f32(unsigned char b) {
+  const __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3);
+  return __half2float(*reinterpret_cast<const __half*>(&h));
+}
+
+__device__ __forceinline__ unsigned e2m1_code(float q) {
+  if (q != q) return 0u;
+  const float m = fminf(fabsf(q), 6.f);
+  const unsigned idx = (m > 0.25f) + (m >= 0.75f) + (m > 1.25f) + (m >= 1.75f) + (m > 2.5f) + (m >= 3.5f) + (m > 5.0f);
+  return ((__float_as_uint(q) >> 31) << 3) | idx;
+}
+
+template <bool FP32>
+__global__ void __launch_bounds__(256) nvfp4_pack_kernel(const void* x, long long ld, int rows, int nb,
+                                                        const float* block_amax, const unsigned int* tensor_amax_bits,
+                                                        unsigned char* packed, unsigned char* scales, int sf_rows,
+                                                        float* global_scale_out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const float amax = __uint_as_float(*tensor_amax_bits);
+  const float gs = amax > 0.f ? __fdiv_rn(amax, 2688.f) : 1.f;      // 6 * 448
+  if (i == 0) *global_scale_out = gs;
+  if (i >= (long long)rows * nb) return;
+  const int r = (int)(i / nb), b = (int)(i % nb);
+  const float sf_real = __fdiv_rn(block_amax[i], __fmul_rn(6.f, gs));
+  const unsigned char sfb = sf_real > 0.f ? (unsigned char)__nv_cvt_float_to_fp8(sf_real, __NV_SATFINITE, __NV_E4M3) : 0;
+  const int m_atoms = sf_rows >> 7;
+  scales[((size_t)(r >> 7) + (size_t)m_atoms * (b >> 2)) * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4 + (b & 3)] = sfb;
+  const float es = __fmul_rn(e4m3_to_f32(sfb), gs);
+  unsigned long long bits = 0ull;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const float v = load_elem<FP32>(x, (size_t)r * ld + b * 16 + j);
+    const unsigned code = es > 0.f ? e2m1_code(__fdiv_rn(v, es)) : 0u;
+    bits |= (unsigned long long)code << (4 * j);
+  }
+  *reinterpret_cast<unsigned long long*>(packed + ((size_t)r * nb + b) * 8) = bits;
+}
+
+}  // namespace
+}  // namespace swb
+
+extern "C" {
+
+// x: [rows, cols] fp32 (is_fp32) or bf16, row stride ld elements, cols % 16 == 0. packed: [rows, cols / 2] bytes
+// (8-byte aligned); scales: sf_rows * sf_cols bytes, zero-filled by the caller, sf_rows = ceil(rows / 128) * 128,
+// sf_cols = ceil(cols / 64) * 4; block_amax: rows * cols / 16 floats of scratch; tensor_amax_bits: one zeroed word;
+// global_scale_out: one float on the device.
+int swb_nvfp4_quantize(const void* x, int is_fp32, long long ld, int rows, int cols, void* packed, void* scales,
+                       int sf_rows, void* block_amax, void* tensor_amax_bits, void* global_scale_out, void* stream) {
+  using namespace swb;
+  if (rows <= 0 || cols <= 0) return 0;
+  if (cols % 16 != 0 || sf_rows % 128 != 0 || sf_rows < rows || (reinterpret_cast<uintptr_t>(packed) & 7)) return -3;
+  const int nb = cols / 16;
+  const long long n = (long long)rows * nb;
+  const dim3 grid((unsigned)((n + 255) / 256)), block(256);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  float* ba = reinterpret_cast<float*>(block_amax);
+  unsigned int* ta = reinterpret_cast<unsigned int*>(tensor_amax_bits);
+  int rc;
+  if (is_fp32) {
+    rc = launch_kernel(nvfp4_block_amax_kernel<true>, grid, block, 0, s, x, ld, rows, nb, ba, ta);
+    if (rc) return rc;
+    return launch_kernel(nvfp4_pack_kernel<true>, grid, block, 0, s, x, ld, rows, nb, (const float*)ba,
+                         (const unsigned int*)ta, reinterpret_cast<unsigned char*>(packed),
+                         reinterpret_cast<unsigned char*>(scales), sf_rows, reinterpret_cast<float*>(global_scale_out));
+  }
+  rc = launch_kernel(nvfp4_block_amax_kernel<false>, grid, block, 0, s, x, ld, rows, nb, ba, ta);
+  if (rc) return rc;
+  return launch_kernel(nvfp4_pack_kernel<false>, grid, block, 0, s, x, ld, rows, nb, (const float*)ba,
+                       (const unsigned int*)ta, reinterpret_cast<unsigned char*>(packed),
+                       reinterpret_cast<unsigned char*>(scales), sf_rows, reinterpret_cast<float*>(global_scale_out));
+}
+
+}  // extern "C"

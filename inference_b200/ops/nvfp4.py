@@ -144,11 +144,38 @@ class Nvfp4Tensor:
         return self.packed.numel() + self.scales.numel() + 4
 
 
+def quantize_on_device(x: torch.Tensor) -> Nvfp4Tensor:
+    """The packer as two device kernels (block amax + tensor amax, then scales / codes / swizzle); bit-identical
+    to `Nvfp4Tensor.pack`. x: CUDA fp32 or bf16 [rows, cols] with cols a multiple of 16."""
+    from .._native import kernels
+    from .runtime import check, stream_ptr
+
+    assert x.is_cuda and x.dim() == 2 and x.dtype in (torch.float32, torch.bfloat16) and x.stride(1) == 1
+    rows, cols = x.shape
+    if cols % BLOCK != 0:
+        return Nvfp4Tensor.pack(x).to(x.device)
+    nb = cols // BLOCK
+    sf_rows, sf_cols = _round_up(rows, SF_ATOM_ROWS), _round_up(nb, SF_ATOM_COLS)
+    dev = x.device
+    packed = torch.empty((rows, cols // 2), dtype=torch.uint8, device=dev)
+    scales = torch.zeros(sf_rows * sf_cols, dtype=torch.uint8, device=dev)
+    block_amax = torch.empty(rows * nb, dtype=torch.float32, device=dev)
+    tmax = torch.zeros(1, dtype=torch.int32, device=dev)
+    gs = torch.empty(1, dtype=torch.float32, device=dev)
+    check(kernels().swb_nvfp4_quantize(x.data_ptr(), 1 if x.dtype == torch.float32 else 0, x.stride(0), rows, cols,
+                                       packed.data_ptr(), scales.data_ptr(), sf_rows, block_amax.data_ptr(),
+                                       tmax.data_ptr(), gs.data_ptr(), stream_ptr()), "swb_nvfp4_quantize")
+    return Nvfp4Tensor(rows, cols, cols, packed, scales, sf_rows, sf_cols, float(gs.item()))
+
+
 def quantize_activations(x: torch.Tensor) -> torch.Tensor:
     """Rounds activations [rows, cols] to the NVFP4 grid (per-tensor scale, per-16 block scales) and returns them in
     x's dtype: what a W4A4 GEMM sees on its activation side (the reference's fused activation quantiser,
     candle-gen/src/quant/nvfp4_quant.cu:80-156, followed by the decode the tensor core performs)."""
-    return Nvfp4Tensor.pack(x.reshape(-1, x.shape[-1])).dequantize().view(x.shape).to(x.dtype)
+    x2 = x.reshape(-1, x.shape[-1])
+    t = quantize_on_device(x2.contiguous()) if x2.is_cuda and x2.dtype in (torch.float32, torch.bfloat16) else \
+        Nvfp4Tensor.pack(x2)
+    return t.dequantize().view(x.shape).to(x.dtype)
 
 
 # ---- activation-outlier metric (candle-gen/src/quant/nvfp4_outlier.rs) -------------------------------------------------

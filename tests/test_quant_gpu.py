@@ -61,3 +61,24 @@ def test_nvfp4_gemm_and_dequant_match_cpu_container(T, N, K):
     torch.testing.assert_close(y.float(), ref, rtol=2e-2, atol=2e-2)
     big = torch.randn(130, K, generator=g).bfloat16().cuda()       # more than 64 rows: expand + dense GEMM
     torch.testing.assert_close(lin(big).float(), big.float() @ dense.float().t() + bias.float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("rows,cols,dtype", [(130, 80, torch.float32), (64, 4096, torch.bfloat16), (1, 16, torch.float32),
+                                            (257, 3072, torch.float32)])
+def test_nvfp4_device_quantiser_is_bit_identical_to_the_host_packer(rows, cols, dtype):
+    from inference_b200 import ops
+    from inference_b200.ops import nvfp4 as nv
+
+    g = torch.Generator().manual_seed(rows + cols)
+    x = (torch.randn(rows, cols, generator=g) * 0.3).to(dtype)
+    x[0, 0] = 7.0                                           # an outlier fixes the tensor scale
+    x[rows // 2, : min(32, cols)] = 0.0                     # all-zero blocks: scale byte 0, codes 0
+    if cols >= 32:
+        x[rows - 1, 16:32] = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -0.25] * 2).to(dtype) * 0.01
+    host = nv.Nvfp4Tensor.pack(x)
+    dev = nv.quantize_on_device(x.cuda())
+    ops.check_status()
+    assert dev.global_scale == host.global_scale
+    assert torch.equal(dev.scales.cpu(), host.scales)
+    assert torch.equal(dev.packed.cpu(), host.packed)
+    torch.testing.assert_close(nv.quantize_activations(x.cuda()).cpu().float(), host.dequantize().to(dtype).float())
