@@ -161,3 +161,38 @@ def test_media_test_tools(tmp_path, monkeypatch):
     with pytest.raises(AssertionError):
         mt.VramProbe(lambda: 5000).assert_idle(1.0)
     assert mt.cuda_mempool_used_high_bytes() is None or mt.cuda_mempool_used_high_bytes() >= 0
+
+
+def test_memory_adaptation_ladder():
+    from inference_b200.contracts.gen_core.mempolicy import LaneLevers, Lever, StagePeaks, plan_memory_adaptation
+    from inference_b200.contracts.gen_core.runtime import OffloadPolicy
+
+    def peaks_at(scale, tileable=True):
+        area = scale * scale
+        return StagePeaks(9.0 + 11.0 * area, 1.0 + 30.0 * area, (1.0 + 4.0 * area) if tileable else None)
+    levers = LaneLevers(8.0, True, 4.6, (0.75, 0.5))
+    plan = plan_memory_adaptation(100.0, levers, peaks_at)
+    assert plan.engaged == [] and plan.residency is OffloadPolicy.RESIDENT and plan.feasible and plan.resolution_scale == 1.0
+    plan = plan_memory_adaptation(12.0, levers, peaks_at)
+    assert plan.engaged == sorted(plan.engaged)
+    plan = plan_memory_adaptation(32.0, levers, peaks_at)
+    assert plan.engaged == [Lever.SEQUENTIAL_RESIDENCY] and plan.residency is OffloadPolicy.SEQUENTIAL
+    assert not plan.tile_decode and not plan.quantize_branch and plan.feasible and plan.projected_peak_gib <= 32.0
+    plan = plan_memory_adaptation(22.0, levers, peaks_at)
+    assert plan.engaged == [Lever.SEQUENTIAL_RESIDENCY, Lever.VAE_DECODE_TILING] and not plan.quantize_branch
+    plan = plan_memory_adaptation(16.0, levers, peaks_at)
+    assert plan.quantize_branch and plan.resolution_scale == 1.0 and Lever.RESOLUTION_REDUCTION not in plan.engaged
+    plan = plan_memory_adaptation(13.0, levers, peaks_at)
+    assert Lever.RESOLUTION_REDUCTION in plan.engaged and plan.resolution_scale == 0.75 and plan.feasible
+    assert plan.residency is OffloadPolicy.SEQUENTIAL and plan.quantize_branch
+    assert plan_memory_adaptation(8.0, levers, peaks_at).resolution_scale == 0.5
+    plan = plan_memory_adaptation(1.5, levers, peaks_at)
+    assert not plan.feasible and plan.projected_peak_gib > 1.5
+    bare = LaneLevers(0.0, False, 0.0, ())
+    fixed = lambda s: StagePeaks(20.0, 10.0, None)
+    ok, no = plan_memory_adaptation(25.0, bare, fixed), plan_memory_adaptation(15.0, bare, fixed)
+    assert ok.engaged == [] and ok.feasible and not no.feasible and no.engaged == []
+    unwired = LaneLevers(8.0, False, 4.6, (0.75, 0.5))
+    plan = plan_memory_adaptation(35.0, unwired, peaks_at)
+    assert Lever.SEQUENTIAL_RESIDENCY not in plan.engaged and plan.residency is OffloadPolicy.RESIDENT
+    assert plan.tile_decode and plan.feasible
