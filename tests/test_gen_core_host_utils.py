@@ -196,3 +196,26 @@ def test_memory_adaptation_ladder():
     plan = plan_memory_adaptation(35.0, unwired, peaks_at)
     assert Lever.SEQUENTIAL_RESIDENCY not in plan.engaged and plan.residency is OffloadPolicy.RESIDENT
     assert plan.tile_decode and plan.feasible
+
+
+def test_media_text_tokenizer_templates_truncation_and_padding():
+    from inference_b200.contracts.gen_core.tokenizer import PromptTemplate as P, TextTokenizer, TokenizerConfig
+    from inference_b200.testkit.synthetic import wordlevel_tokenizer_json
+
+    assert P.NONE.render("x") == "x"
+    assert P.QWEN_INSTRUCT.render("a cat") == "<|im_start|>user\na cat<|im_end|>\n<|im_start|>assistant\n"
+    assert P.QWEN_INSTRUCT_NO_THINK.render("p").endswith("<think>\n\n</think>\n\n")
+    assert P.QWEN_IMAGE.render("p").startswith("<|im_start|>system\nDescribe the image by detailing the color")
+    assert P.FLUX2_DEV_MISTRAL.render("p").startswith("[SYSTEM_PROMPT]You are an AI") and \
+        P.FLUX2_DEV_MISTRAL.render("p").endswith("[/SYSTEM_PROMPT][INST]p[/INST]")
+    js = wordlevel_tokenizer_json(64)
+    t = TextTokenizer.from_json_str(js, TokenizerConfig(max_length=4, pad_token_id=0))
+    out = t.tokenize("the cat sat on mat")
+    assert len(out.ids) == 4 and out.mask == [1, 1, 1, 1]                  # right truncation
+    assert t.tokenize("").ids == [] and t.decode(out.ids[:2]) == "the cat"
+    p = TextTokenizer.from_json_str(js, TokenizerConfig(max_length=6, pad_token_id=7, pad_to_max_length=True))
+    out = p.tokenize("hello world")
+    assert out.ids[2:] == [7] * 4 and out.mask == [1, 1, 0, 0, 0, 0]
+    assert p.tokenize("").mask == [0] * 6                                   # an empty prompt still pads
+    assert p.encode_ids("hello world", False) == out.ids[:2] == p.encode_chat_ids("hello world", False)
+    assert p.config().max_length == 6 and len(p.constraint_decode_table().pieces) == 64
