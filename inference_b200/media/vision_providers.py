@@ -52,6 +52,8 @@ class ClipImageEmbedder(ImageEmbedder):
         return SimpleDescriptor(self.ID, "clip", self.backend, {"dim": self.tower.cfg.projection_dim})
 
     def embed(self, images: list[Image]) -> list[list[float]]:
+        if not images:
+            return []
         px = torch.cat([preprocess(image_tensor(i), self.tower.cfg.image_size, CLIP_MEAN, CLIP_STD) for i in images])
         e = self.tower.image_embeds(px).float()
         return F.normalize(e, dim=-1).cpu().tolist()
@@ -67,6 +69,8 @@ class ClipTextEmbedder(TextEmbedder):
         return SimpleDescriptor(self.ID, "clip", self.backend, {})
 
     def embed(self, texts: list[str]) -> list[list[float]]:
+        if not texts:
+            return []
         ids = torch.tensor([self.tok.encode(t) for t in texts], dtype=torch.int64)
         _, pooled = self.enc.encode(ids)
         e = linear(pooled, self.proj) if self.proj is not None else pooled

@@ -242,3 +242,24 @@ def test_chatterbox_voice_encoder(tmp_path):
         reg.load_kind("voice_embedder", "chatterbox_ve", LoadSpec.from_dir(tmp_path))
     with pytest.raises(dsp.AudioError):
         emb.embed(AudioTrack(16_000, 1, []))
+
+
+def test_audio_providers_pass_their_conformance_suites():
+    from inference_b200.audio import voice_encoder as ve, whisper as W
+    from inference_b200.testkit.aux_suites import (ConformanceFailure, TranscriberProfile, transcriber_conformance,
+                                                   voice_embedder_conformance)
+
+    hc, hf = _tiny_whisper()
+    model = W.WhisperModel(W.WhisperConfig.from_json(hc.to_dict()), dict(hf.state_dict()), "cpu")
+    transcriber_conformance(W.WhisperTranscriber(model, _Tok(), "cpu"), TranscriberProfile())
+    torch.manual_seed(1)
+    lstm, proj = torch.nn.LSTM(40, 256, num_layers=3), torch.nn.Linear(256, 256)
+    w = {f"lstm.{k}": v.detach() for k, v in lstm.state_dict().items()}
+    w.update({"proj.weight": proj.weight.detach(), "proj.bias": proj.bias.detach()})
+    voice_embedder_conformance(ve.ChatterboxVoiceEmbedder(ve.SpeakerEncoder(w), "cpu"))
+
+    class Broken(ve.ChatterboxVoiceEmbedder):          # a provider that returns garbage for empty input
+        def embed(self, audio):
+            return [0.0] * 256 if not audio.samples else super().embed(audio)
+    with pytest.raises(ConformanceFailure, match="degenerate"):
+        voice_embedder_conformance(Broken(ve.SpeakerEncoder(w), "cpu"))

@@ -110,3 +110,10 @@ def test_adapter_is_applied_by_the_generator(tmp_path):
         bad = LoadSpec(weights=WeightsSource.dir(snap), adapters=[AdapterSpec(path=tmp_path / "nope.safetensors", scale=1.0,
                                                                               kind=AdapterKind.LORA)])
         reg.load("cpu_flux1_schnell", bad).generate(req(), lambda e: None)
+
+
+def test_trainer_conformance_suite(dataset, tmp_path):
+    from inference_b200.testkit.aux_suites import TrainerProfile, trainer_conformance
+
+    tr = FluxLoraTrainer(CFG, random_flux_weights(CFG, seed=3, std=0.05))
+    trainer_conformance(tr, TrainerProfile(dataset, tmp_path / "out", steps=3, rank=2))

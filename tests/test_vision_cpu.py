@@ -250,3 +250,33 @@ def test_depth_anything_matches_hugging_face_and_transform_provider():
     out = tr.apply(img, {"target": 42})
     assert (out.width, out.height) == (50, 40) and max(out.pixels) == 255 and min(out.pixels) == 0
     assert out.pixels[0] == out.pixels[1] == out.pixels[2] and tr.descriptor().id == "depth_anything_v2"
+
+
+def test_vision_providers_pass_their_conformance_suites():
+    from transformers import CLIPConfig, CLIPModel
+
+    from inference_b200.contracts.gen_core.media import Image
+    from inference_b200.media.vision_providers import ClipImageEmbedder, LlavaCaptioner, OracleLm
+    from inference_b200.models.config import ModelConfig
+    from inference_b200.models.oracle import OracleLlama
+    from inference_b200.models.vision import VisionConfig, VisionTower
+    from inference_b200.testkit.aux_suites import captioner_conformance, vector_embedder_conformance
+
+    torch.manual_seed(6)
+    hc = CLIPConfig(text_config=dict(hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=4,
+                                     vocab_size=100, max_position_embeddings=8),
+                    vision_config=dict(hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=4,
+                                       image_size=28, patch_size=14), projection_dim=8)
+    ie = ClipImageEmbedder(VisionTower(VisionConfig.from_json(hc.to_dict()), dict(CLIPModel(hc).eval().state_dict())), "cpu")
+    imgs = [Image(30, 20, bytes([i * 7 % 256 for i in range(30 * 20 * 3)])), Image(28, 28, bytes([9]) * (28 * 28 * 3))]
+    vector_embedder_conformance(ie, imgs)
+    lc, hf = _tiny_llava()
+    sd = {(k[6:] if k.startswith("model.") else k): v for k, v in hf.state_dict().items()}
+    lmw = {"model." + k[len("language_model."):]: v for k, v in sd.items() if k.startswith("language_model.")}
+    lmw["lm_head.weight"] = sd["lm_head.weight"]
+    cap = LlavaCaptioner(VisionTower(VisionConfig.from_json(lc.to_dict()),
+                                     {k[len("vision_tower."):]: v for k, v in sd.items() if k.startswith("vision_tower.")}),
+                         {k[len("multi_modal_projector."):]: v for k, v in sd.items() if k.startswith("multi_modal_projector.")},
+                         OracleLm(OracleLlama(ModelConfig.from_json(lc.text_config.to_dict()), lmw, dtype=torch.float32,
+                                              device="cpu")), _WordTok(), 100, "cpu", -2)
+    captioner_conformance(cap, prompt="5 <image> 7", budget=3, count_tokens=lambda s: len(s.split()))
