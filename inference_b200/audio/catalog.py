@@ -40,9 +40,44 @@ def _chatterbox_ve_registration(backend: str) -> Registration:
     return Registration(lambda: SimpleDescriptor("chatterbox_ve", "chatterbox", backend, {"dim": 256}), load)
 
 
+CLAP_LICENSE = WeightLicense("Apache-2.0", "Apache License 2.0", "https://huggingface.co/laion/clap-htsat-unfused",
+                             "LAION", True)
+
+
+def _clap_registration(backend: str) -> Registration:
+    def load(spec: LoadSpec):
+        import json
+        from pathlib import Path
+
+        import torch
+
+        from ..contracts.core_llm.tokenizer import Tokenizer
+        from ..contracts.errors import LoadError
+        from ..io.safetensors_io import load_dir
+        from .clap import ClapAudioConfig, ClapAudioEmbedder, ClapAudioTower, ClapTextConfig, ClapTextTower
+
+        if spec.weights is None or spec.weights.is_file:
+            raise LoadError("clap_htsat_unfused: the load spec needs a snapshot directory")
+        d = Path(spec.weights.path)
+        cfg = json.loads((d / "config.json").read_text())
+        w = load_dir(d)
+        dev, dtype = ("cuda", torch.bfloat16) if backend == "b200" else ("cpu", torch.float32)
+        acfg = ClapAudioConfig.from_json(cfg)
+        if isinstance(acfg.patch_stride, (list, tuple)):
+            acfg.patch_stride = int(acfg.patch_stride[0])
+        text = tok = None
+        if (d / "tokenizer.json").is_file() and any(k.startswith("text_model.") for k in w):
+            text, tok = ClapTextTower(ClapTextConfig.from_json(cfg), w, dev, dtype), Tokenizer.from_file(d / "tokenizer.json")
+        return ClapAudioEmbedder(ClapAudioTower(acfg, w, dev, dtype), text, tok, backend)
+
+    return Registration(lambda: SimpleDescriptor("clap_htsat_unfused", "clap", backend, {"dim": 512, "sample_rate": 48_000}),
+                        load)
+
+
 def register_providers(b: ProviderRegistryBuilder, backend: str) -> ProviderRegistryBuilder:
     b.register("transcriber", _whisper_registration(backend))
     b.register("voice_embedder", _chatterbox_ve_registration(backend))
+    b.register("audio_embedder", _clap_registration(backend))
     return b
 
 
@@ -51,7 +86,8 @@ def provider_registry(backend: str = "b200") -> ProviderRegistry:
 
 
 def weight_licenses() -> list[WeightLicenseEntry]:
-    return [WeightLicenseEntry("whisper", WHISPER_LICENSE), WeightLicenseEntry("chatterbox_ve", CHATTERBOX_LICENSE)]
+    return [WeightLicenseEntry("whisper", WHISPER_LICENSE), WeightLicenseEntry("chatterbox_ve", CHATTERBOX_LICENSE),
+            WeightLicenseEntry("clap_htsat_unfused", CLAP_LICENSE)]
 
 
 def weight_licenses_manifest() -> str:

@@ -177,7 +177,7 @@ def test_audio_catalog_registers_whisper_and_licenses(tmp_path):
     reg = catalog.provider_registry("cpu")
     assert reg.ids("transcriber") == ["whisper"] and reg.descriptor_conformance_errors() == []
     manifest = json.loads(catalog.weight_licenses_manifest())
-    assert [r["provider_id"] for r in manifest["model_weight_licenses"]] == ["chatterbox_ve", "whisper"]
+    assert [r["provider_id"] for r in manifest["model_weight_licenses"]] == ["chatterbox_ve", "clap_htsat_unfused", "whisper"]
     assert catalog.can_prepare(["a/config.json", "a/tokenizer.json", "a/model.safetensors"])
     assert not catalog.can_prepare(["a/config.json", "a/model.safetensors"])
     hc, hf = _tiny_whisper()
@@ -263,3 +263,94 @@ def test_audio_providers_pass_their_conformance_suites():
             return [0.0] * 256 if not audio.samples else super().embed(audio)
     with pytest.raises(ConformanceFailure, match="degenerate"):
         voice_embedder_conformance(Broken(ve.SpeakerEncoder(w), "cpu"))
+
+
+def _tiny_clap():
+    from transformers import ClapAudioConfig as HA, ClapConfig, ClapModel, ClapTextConfig as HT
+
+    torch.manual_seed(0)
+    ac = HA(spec_size=64, num_mel_bins=16, patch_size=4, patch_stride=[4, 4], patch_embeds_hidden_size=16, depths=[2, 2],
+            num_attention_heads=[2, 4], window_size=4, hidden_size=32, projection_dim=12, enable_fusion=False)
+    tc = HT(vocab_size=120, hidden_size=32, num_hidden_layers=2, num_attention_heads=4, intermediate_size=64,
+            max_position_embeddings=40, projection_dim=12, pad_token_id=1)
+    hc = ClapConfig(text_config=tc.to_dict(), audio_config=ac.to_dict(), projection_dim=12)
+    hf = ClapModel(hc).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "relative_position_bias_table" in n:
+                p.copy_(torch.randn_like(p) * 0.5)
+        hf.audio_model.audio_encoder.batch_norm.running_mean.copy_(torch.randn(16) * 0.1)
+        hf.audio_model.audio_encoder.batch_norm.running_var.copy_(0.5 + torch.rand(16))
+    return hc, hf
+
+
+def test_clap_towers_match_hugging_face():
+    from inference_b200.audio import clap as C
+
+    hc, hf = _tiny_clap()
+    d = hc.to_dict()
+    acfg = C.ClapAudioConfig.from_json(d)
+    acfg.patch_stride = 4
+    assert acfg.depths == [2, 2] and acfg.projection_dim == 12 and acfg.window_size == 4
+    sd = dict(hf.state_dict())
+    tower = C.ClapAudioTower(acfg, sd)
+    feats = torch.randn(2, 1, 256, 16)                  # 256 frames x 16 mels -> 64 x 64 image (shifted windows in use)
+    with torch.no_grad():
+        ref = hf.get_audio_features(input_features=feats)
+        ref = ref if isinstance(ref, torch.Tensor) else ref.pooler_output
+        pooled = hf.audio_model(input_features=feats).pooler_output
+    torch.testing.assert_close(tower.pooled(feats), pooled, atol=2e-4, rtol=2e-4)
+    torch.testing.assert_close(tower.embed(feats), torch.nn.functional.normalize(ref, dim=-1), atol=2e-4, rtol=2e-4)
+    short = torch.randn(1, 1, 100, 16)                  # fewer frames: stretched bicubically to the model's width
+    with torch.no_grad():
+        ref = hf.audio_model(input_features=short).pooler_output
+    torch.testing.assert_close(tower.pooled(short), ref, atol=2e-4, rtol=2e-4)
+    text = C.ClapTextTower(C.ClapTextConfig.from_json(d), sd)
+    ids = torch.tensor([[0, 5, 6, 7, 2, 1, 1], [0, 9, 2, 1, 1, 1, 1]])
+    with torch.no_grad():
+        ref = hf.get_text_features(input_ids=ids, attention_mask=(ids != 1).long())
+        ref = ref if isinstance(ref, torch.Tensor) else ref.pooler_output
+    torch.testing.assert_close(text.embed(ids), torch.nn.functional.normalize(ref, dim=-1), atol=2e-4, rtol=2e-4)
+
+
+def test_clap_front_end_and_provider():
+    from transformers import ClapFeatureExtractor
+
+    from inference_b200.audio import clap as C
+    from inference_b200.testkit.aux_suites import vector_embedder_conformance
+
+    g = torch.Generator().manual_seed(3)
+    wav = torch.randn(48_000 * 2, generator=g) * 0.05
+    fe = ClapFeatureExtractor(truncation="rand_trunc", padding="repeatpad", frequency_min=50, frequency_max=14_000)
+    ref = torch.from_numpy(fe(wav.numpy(), sampling_rate=48_000, return_tensors="np")["input_features"])[0, 0]
+    got = C.log_mel_db(C.fit_length(wav))
+    assert got.shape == ref.shape == (1001, 64)
+    assert float((got - ref).abs().max()) < 2e-2        # dB scale; fp32 vs float64 STFT
+    assert C.fit_length(torch.arange(5.0), 12).tolist() == [0, 1, 2, 3, 4, 0, 1, 2, 3, 4, 0, 0]
+    assert C.fit_length(torch.arange(20.0), 12).numel() == 12
+    assert C.resample_linear(torch.zeros(2400), 24_000).numel() == 4800
+
+    hc, hf = _tiny_clap()
+
+    class Tiny(C.ClapAudioTower):                       # the tiny tower takes 16 mel bins: fold the 64-band front end
+        def embed(self, feats):
+            return super().embed(feats[:, :, :256, :].reshape(feats.shape[0], 1, 256, 16, 4).mean(-1))
+    acfg = C.ClapAudioConfig.from_json(hc.to_dict())
+    acfg.patch_stride = 4
+    sd = dict(hf.state_dict())
+
+    class Tok:
+        def encode(self, t, add_special_tokens=True):
+            return [0] + [int(x) for x in t.split()] + [2]
+    from inference_b200.audio import catalog
+
+    assert catalog.provider_registry("cpu").ids("audio_embedder") == ["clap_htsat_unfused"]
+    emb = C.ClapAudioEmbedder(Tiny(acfg, sd), C.ClapTextTower(C.ClapTextConfig.from_json(hc.to_dict()), sd), Tok(), "cpu")
+    clips = [AudioTrack(24_000, 2, [0.05 * math.sin(i / 13) for i in range(12_000)]),
+             AudioTrack(48_000, 1, [0.02 * math.sin(i / 5) for i in range(30_000)])]
+    vector_embedder_conformance(emb, clips)
+    tv = emb.embed_text(["5 6 7", "9"])
+    assert len(tv) == 2 and len(tv[0]) == 12 and abs(sum(x * x for x in tv[0]) - 1) < 1e-4
+    assert emb.descriptor().id == "clap_htsat_unfused" and emb.descriptor().extra["joint_text"]
+    with pytest.raises(C.AudioError):
+        emb.embed([AudioTrack(48_000, 1, [])])
