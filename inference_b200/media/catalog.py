@@ -6,10 +6,11 @@ from ..contracts.gen_core.registry import ProviderRegistry, ProviderRegistryBuil
 
 
 def provider_registry(backend: str = "b200") -> ProviderRegistry:
-    from . import flux
+    from . import chroma, flux
 
     b = ProviderRegistryBuilder()
     b.register_generators(flux.registrations(backend))
+    b.register_generators(chroma.registrations(backend))
     from .train import trainer_registration
 
     b.register("trainer", trainer_registration(backend))

@@ -164,6 +164,18 @@ class OracleFluxDiT:
     def forward(self, img, img_ids, txt, txt_ids, timesteps, y, guidance=None):
         return self.forward_grad(img, img_ids, txt, txt_ids, timesteps, y, guidance)
 
+    def _modulations(self, timesteps, y, guidance, dtype) -> dict[str, torch.Tensor]:
+        """{modulation name: [B, rows]}: every adaLN modulation is a linear map of silu(conditioning vector)."""
+        cfg = self.cfg
+        vec = self._mlp_embed(timestep_embedding(timesteps).to(dtype), "time_in")
+        if cfg.guidance_embed:
+            vec = vec + self._mlp_embed(timestep_embedding(guidance).to(dtype), "guidance_in")
+        vec = vec + self._mlp_embed(y, "vector_in")
+        sv = F.silu(vec)
+        names = [f"double_blocks.{i}.{s}_mod.lin" for i in range(cfg.depth) for s in ("img", "txt")]
+        names += [f"single_blocks.{i}.modulation.lin" for i in range(cfg.depth_single)]
+        return {n: self._lin(sv, n) for n in names + ["final_layer.adaLN_modulation.1"]}
+
     def forward_grad(self, img, img_ids, txt, txt_ids, timesteps, y, guidance=None):
         """The same computation with autograd enabled (adapter training differentiates through it)."""
         cfg = self.cfg
@@ -171,17 +183,13 @@ class OracleFluxDiT:
         cos, sin = rope_table(torch.cat([txt_ids, img_ids], 0), cfg.axes_dim, cfg.theta)
         img = self._lin(img, "img_in")
         txt = self._lin(txt, "txt_in")
-        vec = self._mlp_embed(timestep_embedding(timesteps).to(img.dtype), "time_in")
-        if cfg.guidance_embed:
-            vec = vec + self._mlp_embed(timestep_embedding(guidance).to(img.dtype), "guidance_in")
-        vec = vec + self._mlp_embed(y, "vector_in")
-        sv = F.silu(vec)
+        M = self._modulations(timesteps, y, guidance, img.dtype)
         ln = lambda x: F.layer_norm(x, (Hs,), eps=1e-6)  # noqa: E731
         T = txt.shape[1]
         for i in range(cfg.depth):
             mods = {}
             for s in ("img", "txt"):
-                mods[s] = self._lin(sv, f"double_blocks.{i}.{s}_mod.lin")[:, None, :].chunk(6, dim=-1)
+                mods[s] = M[f"double_blocks.{i}.{s}_mod.lin"][:, None, :].chunk(6, dim=-1)
             qkvs = {}
             for s, x in (("img", img), ("txt", txt)):
                 sh1, sc1 = mods[s][0], mods[s][1]
@@ -204,7 +212,7 @@ class OracleFluxDiT:
         x = torch.cat([txt, img], 1)
         for i in range(cfg.depth_single):
             p = f"single_blocks.{i}"
-            sh, sc, g = self._lin(sv, p + ".modulation.lin")[:, None, :].chunk(3, dim=-1)
+            sh, sc, g = M[p + ".modulation.lin"][:, None, :].chunk(3, dim=-1)
             xm = (1 + sc) * ln(x) + sh
             l1 = self._lin(xm, p + ".linear1")
             qkv, mlp = l1[..., : 3 * Hs], l1[..., 3 * Hs:]
@@ -212,7 +220,7 @@ class OracleFluxDiT:
             attn = self._attn(q, k, v, cos, sin)
             x = x + g * self._lin(torch.cat([attn, F.gelu(mlp, approximate="tanh")], -1), p + ".linear2")
         img = x[:, T:]
-        sh, sc = self._lin(sv, "final_layer.adaLN_modulation.1")[:, None, :].chunk(2, dim=-1)
+        sh, sc = M["final_layer.adaLN_modulation.1"][:, None, :].chunk(2, dim=-1)
         return self._lin((1 + sc) * ln(img) + sh, "final_layer.linear")
 
 
@@ -409,7 +417,7 @@ class FluxDiTGpu:
         if g is None:
             if rope is None:
                 rope = rope_table(torch.cat([txt_ids, img_ids], 0).to(img.device), self.cfg.axes_dim, self.cfg.theta)
-            static = {"img": img.clone(), "txt": txt.clone(), "t": timesteps.clone(), "y": y.clone(),
+            static = {"img": img.clone(), "txt": txt.clone(), "t": timesteps.clone(), "y": y.clone() if y is not None else None,
                       "g": guidance.clone() if guidance is not None else None, "rope": rope,
                       "img_ids": img_ids, "txt_ids": txt_ids}
             run = lambda: self.forward(static["img"], static["img_ids"], static["txt"], static["txt_ids"],  # noqa: E731
@@ -431,7 +439,8 @@ class FluxDiTGpu:
         static["img"].copy_(img)
         static["txt"].copy_(txt)
         static["t"].copy_(timesteps)
-        static["y"].copy_(y)
+        if y is not None:
+            static["y"].copy_(y)
         if guidance is not None:
             static["g"].copy_(guidance)
         graph.replay()

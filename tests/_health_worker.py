@@ -59,6 +59,10 @@ def main():
             guarded_step(comm, hb, lambda: dist.all_reduce(torch.ones(2)))
         assert comm.health == "healthy" and max(hb.ages().values()) < 0.6
         print(f"RANK{rank}_HEALTHY", flush=True)
+        store.add("healthy_done", 1)              # rank 0 hosts the store: it leaves last
+        t0 = time.time()
+        while rank == 0 and store.add("healthy_done", 0) < world and time.time() - t0 < 10.0:
+            time.sleep(0.02)
     os._exit(0)
 
 

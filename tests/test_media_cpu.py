@@ -21,13 +21,13 @@ def registry():
 
 
 def test_registry_lists_both_variants(registry):
-    assert registry.ids() == ["cpu_flux1_schnell", "cpu_flux1_dev"]
+    assert registry.ids()[:2] == ["cpu_flux1_schnell", "cpu_flux1_dev"]
     assert registry.descriptor_conformance_errors() == []
     dev = registry.find("generator", "cpu_flux1_dev").descriptor()
     sch = registry.find("generator", "cpu_flux1_schnell").descriptor()
     assert dev.capabilities.supports_guidance and not sch.capabilities.supports_guidance
     assert (dev.capabilities.min_size, dev.capabilities.max_size, dev.capabilities.max_count) == (256, 2048, 8)
-    assert provider_registry("b200").ids() == ["flux1_schnell", "flux1_dev"]
+    assert provider_registry("b200").ids() == ["flux1_schnell", "flux1_dev", "chroma1_hd", "chroma1_base", "chroma1_flash"]
 
 
 def test_generator_conformance(registry, snapshot):
