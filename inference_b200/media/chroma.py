@@ -13,7 +13,6 @@ from __future__ import annotations
 
 import enum
 import json
-import math
 from dataclasses import dataclass
 from pathlib import Path
 from typing import Any, Callable
@@ -59,47 +58,11 @@ class ChromaVariant(enum.Enum):
 
 
 # ---- sigma schedules ---------------------------------------------------------------------------------------------------------
-def _beta_cdf(x: float, a: float = 0.6) -> float:
-    """Regularised incomplete beta function I_x(a, a) by Lentz's continued fraction."""
-    if x <= 0.0:
-        return 0.0
-    if x >= 1.0:
-        return 1.0
-    if x > 0.5:                                   # the fraction converges fast below the mean; use the symmetry
-        return 1.0 - _beta_cdf(1.0 - x, a)
-    b = a
-    front = math.exp(math.lgamma(a + b) - math.lgamma(a) - math.lgamma(b) + a * math.log(x) + b * math.log1p(-x)) / a
-    tiny = 1e-300
-    c, d = 1.0, 1.0 - (a + b) * x / (a + 1.0)
-    d = 1.0 / (d if abs(d) > tiny else tiny)
-    h = d
-    for m in range(1, 400):
-        for num in (m * (b - m) * x / ((a + 2 * m - 1) * (a + 2 * m)),
-                    -(a + m) * (a + b + m) * x / ((a + 2 * m) * (a + 2 * m + 1))):
-            d = 1.0 + num * d
-            d = 1.0 / (d if abs(d) > tiny else tiny)
-            c = 1.0 + num / c
-            c = c if abs(c) > tiny else tiny
-            h *= d * c
-        if abs(d * c - 1.0) < 1e-14:
-            break
-    return front * h
-
-
 def beta_ppf(p: float, a: float = 0.6) -> float:
-    """Quantile of Beta(a, a) by bisection on the CDF."""
-    if p <= 0.0:
-        return 0.0
-    if p >= 1.0:
-        return 1.0
-    lo, hi = 0.0, 1.0
-    for _ in range(80):
-        mid = 0.5 * (lo + hi)
-        if _beta_cdf(mid, a) < p:
-            lo = mid
-        else:
-            hi = mid
-    return 0.5 * (lo + hi)
+    """Quantile of Beta(a, a)."""
+    from ..contracts.gen_core.sampling.schedulers import beta_ppf as ppf
+
+    return ppf(p, a, a)
 
 
 def chroma_sigmas(variant: ChromaVariant, steps: int) -> list[float]:

@@ -320,14 +320,15 @@ class OracleLlama:
 
     def hidden_states(self, ids: torch.Tensor | None, cache: ContiguousKvCache | None, offset: int = 0, *,
                       embeds: torch.Tensor | None = None, positions: torch.Tensor | None = None,
-                      additive_mask: torch.Tensor | None = None) -> torch.Tensor:
+                      additive_mask: torch.Tensor | None = None, num_layers: int | None = None) -> torch.Tensor:
+        """The residual stream after `num_layers` decoder layers (all of them by default), before the final norm."""
         x = self.embed(ids.to(self.device)) if embeds is None else embeds.to(self.device, self.dtype)
         B, S, _ = x.shape
         if positions is None:
             positions = torch.arange(offset, offset + S, device=self.device)[None, :].expand(B, S)
         cos, sin = rope_cos_sin(self.inv_freq, positions.to(self.device))
         causal = additive_mask is None
-        for layer in range(self.cfg.num_layers):
+        for layer in range(self.cfg.num_layers if num_layers is None else num_layers):
             x = self._layer(x, layer, cos, sin, cache, causal, additive_mask)
         return x
 

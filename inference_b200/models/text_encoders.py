@@ -166,3 +166,76 @@ class ClipTextEncoder:
         else:
             eos = (ids == cfg.eos_token_id).int().argmax(-1)
         return x, x[torch.arange(B, device=self.device), eos]
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# decoder-only language model used as a prompt encoder
+# ---------------------------------------------------------------------------------------------------------------
+class CausalLmTextEncoder:
+    """Hidden states of a Llama-family decoder after all but `skip_last` of its layers, before the final norm
+    (Z-Image and its relatives condition on the second-to-last layer of Qwen3: candle-gen-z-image/src/pipeline.rs:115-127).
+
+    On a CUDA device with head_dim 128 the stack runs on the sm_100a kernels (one fused q/k/v GEMM, q/k RMSNorm + RoPE
+    in place, causal tcgen05 attention, gated-pair MLP GEMM); elsewhere it is the fp32 oracle decoder."""
+
+    def __init__(self, cfg, weights: dict[str, torch.Tensor], device="cpu", skip_last: int = 1):
+        from .oracle import OracleLlama, canonical_weights
+        from .config import build_rope
+
+        self.cfg, self.device = cfg, torch.device(device)
+        self.layers = cfg.num_layers - skip_last
+        self.native = (self.device.type == "cuda" and cfg.head_dim == 128 and not cfg.is_moe and cfg.mla is None and
+                       cfg.architecture.value in ("llama", "qwen3"))
+        if not self.native:
+            self.oracle = OracleLlama(cfg, weights, torch.float32, self.device)
+            return
+        w = canonical_weights(weights, cfg)
+        dev = self.device
+        bf = lambda t: t.to(device=dev, dtype=torch.bfloat16).contiguous()      # noqa: E731
+        self.embed = bf(w["model.embed_tokens.weight"])
+        self.blocks = []
+        for i in range(self.layers):
+            p = f"model.layers.{i}."
+            qkv = torch.cat([w[p + f"self_attn.{n}_proj.weight"] for n in ("q", "k", "v")], 0)
+            bias = None
+            if p + "self_attn.q_proj.bias" in w:
+                bias = bf(torch.cat([w[p + f"self_attn.{n}_proj.bias"] for n in ("q", "k", "v")], 0))
+            gate, up = w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"]
+            self.blocks.append({
+                "ln1": bf(w[p + "input_layernorm.weight"]), "ln2": bf(w[p + "post_attention_layernorm.weight"]),
+                "qkv": bf(qkv), "qkv_bias": bias, "o": bf(w[p + "self_attn.o_proj.weight"]),
+                "q_norm": bf(w[p + "self_attn.q_norm.weight"]) if p + "self_attn.q_norm.weight" in w else None,
+                "k_norm": bf(w[p + "self_attn.k_norm.weight"]) if p + "self_attn.k_norm.weight" in w else None,
+                "gate_up": bf(torch.stack([gate, up], 1).reshape(-1, gate.shape[1])), "down": bf(w[p + "mlp.down_proj.weight"])})
+        rope = build_rope(cfg)
+        self.inv_freq = torch.tensor(rope.inv_freq, dtype=torch.float32, device=dev)
+        self.rot_dim, self.rope_interleaved = rope.dim, rope.interleaved
+
+    @torch.no_grad()
+    def encode(self, ids: list[int]) -> torch.Tensor:
+        """token ids -> [1, len(ids), hidden]."""
+        t = torch.tensor([ids], dtype=torch.int64, device=self.device)
+        if not self.native:
+            return self.oracle.hidden_states(t, None, num_layers=self.layers)
+        from .. import ops
+
+        cfg = self.cfg
+        S, D, Hq, Hkv = len(ids), cfg.head_dim, cfg.num_heads, cfg.num_kv_heads
+        eps, woff = cfg.rms_norm_eps, cfg.norm_weight_offset
+        pos = torch.arange(S, dtype=torch.int32, device=self.device)
+        ang = pos.float()[:, None] * self.inv_freq[None]
+        cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+        x = ops.embedding(t, self.embed, scale=cfg.embed_scale)
+        for b in self.blocks:
+            qkv = ops.gemm_bf16(ops.rmsnorm(x, b["ln1"], eps, w_offset=woff), b["qkv"], bias=b["qkv_bias"])
+            ops.rope_kv_write(qkv, pos, None, cos, sin, None, None, Hq, Hkv, D, rot_dim=self.rot_dim,
+                              interleaved=self.rope_interleaved, q_norm=b["q_norm"], k_norm=b["k_norm"], norm_eps=eps,
+                              norm_w_offset=woff)
+            q3 = qkv.view(1, S, Hq + 2 * Hkv, D)
+            attn = ops.dense_attention(q3[:, :, :Hq], q3[:, :, Hq:Hq + Hkv], q3[:, :, Hq + Hkv:], scale=cfg.attn_scale,
+                                       causal=True)
+            x = ops.gemm_bf16(attn.view(S, Hq * D), b["o"], residual=x)
+            h = ops.linear_gated(ops.rmsnorm(x, b["ln2"], eps, w_offset=woff), b["gate_up"],
+                                 cfg.mlp_activation)
+            x = ops.gemm_bf16(h, b["down"], residual=x)
+        return x[None]

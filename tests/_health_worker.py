@@ -20,6 +20,11 @@ def main():
     store = dist.TCPStore("127.0.0.1", int(os.environ["MASTER_PORT"]) + 1, world, rank == 0, wait_for_workers=True)
     plan = FaultPlan.from_env()
     hb = Heartbeat(store, rank, world, deadline_s=0.6, plan=plan)
+    if mode in ("die", "healthy"):
+        # processes start (and import) at different speeds: line the ranks up, then publish a fresh beat, so that the
+        # first check measures time since this point and not since the fastest rank came up
+        host_barrier(store, "start", rank, world, 60.0, plan, index=99)
+        hb.beat()
     if mode == "die":
         # every rank steps; rank 1 leaves between steps (no collective in flight); the others notice before launching
         detected = None
@@ -59,10 +64,12 @@ def main():
             guarded_step(comm, hb, lambda: dist.all_reduce(torch.ones(2)))
         assert comm.health == "healthy" and max(hb.ages().values()) < 0.6
         print(f"RANK{rank}_HEALTHY", flush=True)
-        store.add("healthy_done", 1)              # rank 0 hosts the store: it leaves last
-        t0 = time.time()
-        while rank == 0 and store.add("healthy_done", 0) < world and time.time() - t0 < 10.0:
-            time.sleep(0.02)
+    # rank 0 hosts the store: it leaves after every surviving rank has finished with it
+    store.add("finished", 1)
+    survivors = world - len(plan.die_at_step)
+    t0 = time.time()
+    while rank == 0 and store.add("finished", 0) < survivors and time.time() - t0 < 10.0:
+        time.sleep(0.02)
     os._exit(0)
 
 

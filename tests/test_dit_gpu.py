@@ -137,7 +137,7 @@ def test_chroma_dit_matches_oracle():
         assert torch.equal(eager, model.forward_graphed(img, img_ids, txt, txt_ids, t, None, None))
 
 
-@pytest.mark.parametrize("family", ["flux", "chroma"])
+@pytest.mark.parametrize("family", ["flux", "chroma", "z_image"])
 def test_generator_providers_on_device_track_the_oracle_backend(tmp_path, family):
     """The sm_100a provider and the fp32 oracle provider render the same snapshot, seed and request."""
     import numpy as np
@@ -148,9 +148,14 @@ def test_generator_providers_on_device_track_the_oracle_backend(tmp_path, family
     if family == "flux":
         from inference_b200.media.flux import write_synthetic_snapshot
         mid, extra = "flux1_dev", {}
-    else:
+    elif family == "chroma":
         from inference_b200.media.chroma import write_synthetic_snapshot
         mid, extra = "chroma1_hd", {"true_cfg": 2.0, "negative_prompt": "blurry"}
+    else:
+        from inference_b200.media.z_image import write_synthetic_snapshot as zi
+
+        write_synthetic_snapshot = lambda root: zi(root, text="qwen3", te_head_dim=128)      # noqa: E731
+        mid, extra = "z_image", {"guidance": 2.0, "negative_prompt": "blurry"}
     snap = write_synthetic_snapshot(tmp_path / family)
     req = dict(prompt="a lighthouse at dusk", width=256, height=256, steps=2, seed=11, **extra)
     imgs = {}
@@ -161,3 +166,45 @@ def test_generator_providers_on_device_track_the_oracle_backend(tmp_path, family
         imgs[backend] = np.frombuffer(im.pixels, dtype=np.uint8).astype(np.float32)
     diff = float(np.abs(imgs["b200"] - imgs["cpu"]).mean())
     assert diff < 8.0, diff
+
+
+def test_z_image_dit_matches_oracle():
+    from inference_b200.models.dit_zimage import OracleZImageDiT, ZImageConfig, ZImageDiTGpu, random_zimage_weights
+
+    cfg = ZImageConfig(dim=384, n_layers=2, n_refiner_layers=1, n_heads=3, cap_feat_dim=64)
+    w = {k: v.bfloat16().float() for k, v in random_zimage_weights(cfg, seed=0, std=0.05).items()}
+    oracle = OracleZImageDiT(cfg, w, device="cuda")
+    model = ZImageDiTGpu(cfg, torch.device("cuda")).load_state_dict(w)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    z = torch.randn(1, 16, 12, 10, device="cuda", generator=g).bfloat16()
+    cap = torch.randn(1, 37, 64, device="cuda", generator=g).bfloat16()
+    t = torch.full((1,), 0.3, device="cuda")
+    ref = oracle.forward(z.float(), t, cap.float())
+    tokens = model.refine_caption(cap)
+    ref_tokens = oracle.refine_caption(cap.float())[0]
+    assert (tokens.float() - ref_tokens).abs().max().item() < 0.06 * max(1.0, ref_tokens.abs().max().item())
+    out = model.forward(z, t, tokens)
+    err = (out.float() - ref).abs().max().item()
+    assert out.shape == ref.shape and err < 0.06 * max(1.0, ref.abs().max().item()), err
+    eager = out.clone()
+    for _ in range(2):                                         # capture, then replay
+        assert torch.equal(eager, model.forward_graphed(z, t, tokens))
+
+
+def test_causal_lm_prompt_encoder_matches_oracle():
+    from inference_b200.models.config import ModelConfig
+    from inference_b200.models.oracle import OracleLlama, random_llama_weights
+    from inference_b200.models.text_encoders import CausalLmTextEncoder
+
+    cfg = ModelConfig.from_json({"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_size": 256,
+                                 "intermediate_size": 512, "num_hidden_layers": 3, "num_attention_heads": 4,
+                                 "num_key_value_heads": 2, "head_dim": 128, "vocab_size": 300, "rms_norm_eps": 1e-6,
+                                 "rope_theta": 1000000.0, "tie_word_embeddings": True})
+    w = {k: v.bfloat16().float() for k, v in random_llama_weights(cfg, 1, std=0.05).items()}
+    enc = CausalLmTextEncoder(cfg, w, "cuda")
+    assert enc.native
+    ids = [5, 17, 200, 3, 99, 42, 7, 250, 11]
+    out = enc.encode(ids)
+    ref = OracleLlama(cfg, w, device="cuda").hidden_states(torch.tensor([ids], device="cuda"), None, num_layers=2)
+    assert out.shape == ref.shape
+    assert (out.float() - ref).abs().max().item() < 0.05 * max(1.0, ref.abs().max().item())
