@@ -96,14 +96,16 @@ def convert_chroma_weights(sd: dict[str, torch.Tensor], cfg: ChromaConfig) -> di
     return out
 
 
-def random_chroma_weights(cfg: ChromaConfig, seed: int = 0, std: float = 0.05) -> dict[str, torch.Tensor]:
+def random_chroma_weights(cfg: ChromaConfig, seed: int = 0, std: float = 0.05, dtype=torch.float32, device="cpu"
+                          ) -> dict[str, torch.Tensor]:
     """A random checkpoint in the diffusers layout (tests, synthetic snapshots)."""
-    g = torch.Generator().manual_seed(seed)
+    g = torch.Generator(device=device).manual_seed(seed)
+    rn = lambda *shape: torch.randn(*shape, generator=g, device=device)      # noqa: E731
     H, M = cfg.inner_dim, 4 * cfg.inner_dim
     w: dict[str, torch.Tensor] = {}
 
     def lin(name, o, i):
-        w[name + ".weight"], w[name + ".bias"] = torch.randn(o, i, generator=g) * std, torch.randn(o, generator=g) * std
+        w[name + ".weight"], w[name + ".bias"] = (rn(o, i) * std).to(dtype), (rn(o) * std).to(dtype)
 
     lin("x_embedder", H, cfg.in_channels)
     lin("context_embedder", H, cfg.joint_attention_dim)
@@ -113,7 +115,7 @@ def random_chroma_weights(cfg: ChromaConfig, seed: int = 0, std: float = 0.05) -
         for n in ("to_q", "to_k", "to_v", "to_out.0", "add_q_proj", "add_k_proj", "add_v_proj", "to_add_out"):
             lin(f"{p}.attn.{n}", H, H)
         for n in ("norm_q", "norm_k", "norm_added_q", "norm_added_k"):
-            w[f"{p}.attn.{n}.weight"] = 1.0 + torch.randn(cfg.attention_head_dim, generator=g) * 0.1
+            w[f"{p}.attn.{n}.weight"] = (1.0 + rn(cfg.attention_head_dim) * 0.1).to(dtype)
         for ff in ("ff", "ff_context"):
             lin(f"{p}.{ff}.net.0.proj", M, H)
             lin(f"{p}.{ff}.net.2", H, M)
@@ -122,7 +124,7 @@ def random_chroma_weights(cfg: ChromaConfig, seed: int = 0, std: float = 0.05) -
         for n in ("to_q", "to_k", "to_v"):
             lin(f"{p}.attn.{n}", H, H)
         for n in ("norm_q", "norm_k"):
-            w[f"{p}.attn.{n}.weight"] = 1.0 + torch.randn(cfg.attention_head_dim, generator=g) * 0.1
+            w[f"{p}.attn.{n}.weight"] = (1.0 + rn(cfg.attention_head_dim) * 0.1).to(dtype)
         lin(f"{p}.proj_mlp", M, H)
         lin(f"{p}.proj_out", H, H + M)
     a, hid = "distilled_guidance_layer", cfg.approximator_hidden_dim
@@ -130,7 +132,7 @@ def random_chroma_weights(cfg: ChromaConfig, seed: int = 0, std: float = 0.05) -
     for i in range(cfg.approximator_layers):
         lin(f"{a}.layers.{i}.linear_1", hid, hid)
         lin(f"{a}.layers.{i}.linear_2", hid, hid)
-        w[f"{a}.norms.{i}.weight"] = 1.0 + torch.randn(hid, generator=g) * 0.1
+        w[f"{a}.norms.{i}.weight"] = (1.0 + rn(hid) * 0.1).to(dtype)
     lin(f"{a}.out_proj", H, hid)
     return w
 
@@ -208,7 +210,7 @@ class ChromaDiTGpu(FluxDiTGpu):
         return super().load_state_dict(convert_chroma_weights(weights, self.ccfg))
 
     def init_random(self, seed: int = 0, std: float = 0.02) -> "ChromaDiTGpu":
-        return self.load_state_dict(random_chroma_weights(self.ccfg, seed, std))
+        return self.load_state_dict(random_chroma_weights(self.ccfg, seed, std, torch.bfloat16, self.device))
 
     def _build_modulation_table(self) -> None:       # no per-block modulation linears in this family
         return None

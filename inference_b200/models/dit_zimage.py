@@ -72,18 +72,19 @@ def block_names(cfg: ZImageConfig) -> list[tuple[str, bool]]:
     return out + [(f"layers.{i}", True) for i in range(cfg.n_layers)]
 
 
-def random_zimage_weights(cfg: ZImageConfig, seed: int = 0, std: float = 0.05) -> dict[str, torch.Tensor]:
-    g = torch.Generator().manual_seed(seed)
+def random_zimage_weights(cfg: ZImageConfig, seed: int = 0, std: float = 0.05, dtype=torch.float32, device="cpu"
+                          ) -> dict[str, torch.Tensor]:
+    g = torch.Generator(device=device).manual_seed(seed)
     w: dict[str, torch.Tensor] = {}
     D, Fd, A = cfg.dim, cfg.ffn_dim, cfg.adaln_dim
 
     def lin(name, o, i, bias=True):
-        w[name + ".weight"] = torch.randn(o, i, generator=g) * std
+        w[name + ".weight"] = (torch.randn(o, i, generator=g, device=device) * std).to(dtype)
         if bias:
-            w[name + ".bias"] = torch.randn(o, generator=g) * std
+            w[name + ".bias"] = (torch.randn(o, generator=g, device=device) * std).to(dtype)
 
     def norm(name, n):
-        w[name + ".weight"] = 1.0 + torch.randn(n, generator=g) * 0.1
+        w[name + ".weight"] = (1.0 + torch.randn(n, generator=g, device=device) * 0.1).to(dtype)
 
     lin("t_embedder.mlp.0", 1024, 256)
     lin("t_embedder.mlp.2", A, 1024)
@@ -92,7 +93,7 @@ def random_zimage_weights(cfg: ZImageConfig, seed: int = 0, std: float = 0.05) -
     lin("all_x_embedder.2-1", D, cfg.patch_dim)
     lin("all_final_layer.2-1.linear", cfg.patch_dim, D)
     lin("all_final_layer.2-1.adaLN_modulation.1", D, A)
-    w["x_pad_token"], w["cap_pad_token"] = torch.zeros(1, D), torch.zeros(1, D)
+    w["x_pad_token"], w["cap_pad_token"] = torch.zeros(1, D, dtype=dtype), torch.zeros(1, D, dtype=dtype)
     for p, modulated in block_names(cfg):
         for n in ("to_q", "to_k", "to_v", "to_out.0"):
             lin(f"{p}.attention.{n}", D, D, bias=False)
@@ -267,7 +268,7 @@ class ZImageDiTGpu:
         return self
 
     def init_random(self, seed: int = 0, std: float = 0.02) -> "ZImageDiTGpu":
-        return self.load_state_dict(random_zimage_weights(self.cfg, seed, std))
+        return self.load_state_dict(random_zimage_weights(self.cfg, seed, std, torch.bfloat16, self.device))
 
     def weight_bytes(self) -> int:
         return sum(t.numel() * 2 for t in self.w.values()) + self._mod_w.numel() * 2
@@ -340,7 +341,7 @@ class ZImageDiTGpu:
         self.launches += 2
         n1 = (self._norm1 * (1 + blocks[:, 0])).bfloat16()
         n3 = (self._norm3 * (1 + blocks[:, 2])).bfloat16()
-        gates = blocks[:, (1, 3)].tanh().bfloat16()
+        gates = blocks[:, 1::2].tanh().bfloat16()          # rows 1 and 3: the two gates
         return n1, gates[:, 0].contiguous(), n3, gates[:, 1].contiguous(), fin
 
     @torch.no_grad()
