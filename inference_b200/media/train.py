@@ -39,9 +39,9 @@ def lr_at(schedule: str, step: int, total: int, warmup: int, base: float) -> flo
     raise InferenceError(f"unknown lr_schedule {schedule!r} (constant | linear | cosine)")
 
 
-def lora_targets(weights: dict[str, torch.Tensor]) -> list[str]:
+def lora_targets(weights: dict[str, torch.Tensor], suffixes: tuple[str, ...] = TARGET_SUFFIXES) -> list[str]:
     names = sorted({k[: -len(".weight")] for k in weights if k.endswith(".weight") and weights[k].dim() == 2})
-    return [n for n in names if n.endswith(TARGET_SUFFIXES)]
+    return [n for n in names if n.endswith(suffixes)]
 
 
 def merge_lora(weights: dict[str, torch.Tensor], adapter: dict[str, torch.Tensor], scale: float = 1.0,
@@ -64,6 +64,8 @@ def merge_lora(weights: dict[str, torch.Tensor], adapter: dict[str, torch.Tensor
 
 
 class FluxLoraTrainer(Trainer):
+    family, target_suffixes, item_keys = "flux", TARGET_SUFFIXES, ("latent", "txt", "pooled")
+
     def __init__(self, cfg: FluxConfig, weights: dict[str, torch.Tensor], backend: str = "cpu", device="cpu"):
         self.cfg, self.backend, self.device = cfg, backend, torch.device(device)
         self.model = OracleFluxDiT(cfg, weights, dtype=torch.float32, device=self.device)
@@ -93,14 +95,14 @@ class FluxLoraTrainer(Trainer):
         items = []
         for f in files:
             t = load_file(f)
-            if not {"latent", "txt", "pooled"} <= set(t):
-                raise InferenceError(f"{f}: needs tensors latent, txt, pooled")
+            if not set(self.item_keys) <= set(t):
+                raise InferenceError(f"{f}: needs tensors {', '.join(self.item_keys)}")
             items.append({k: v.float().to(self.device) for k, v in t.items()})
         return items
 
     def _init_adapters(self, rank: int, gen: torch.Generator) -> dict[str, list[torch.Tensor]]:
         ad = {}
-        for name in lora_targets(self.model.w):
+        for name in lora_targets(self.model.w, self.target_suffixes):
             w = self.model.w[name + ".weight"]
             a = (torch.randn(rank, w.shape[1], generator=gen) / math.sqrt(w.shape[1])).to(self.device).requires_grad_()
             b = torch.zeros(w.shape[0], rank, device=self.device, requires_grad=True)
@@ -170,7 +172,7 @@ class FluxLoraTrainer(Trainer):
             t[f"transformer.{n}.lora_A.weight"] = a.detach().cpu().contiguous()
             t[f"transformer.{n}.lora_B.weight"] = b.detach().cpu().contiguous()
         save_file(t, path, metadata={"format": "peft-lora", "rank": str(c.rank), "alpha": str(c.alpha),
-                                     "step": str(step), "base": "flux"})
+                                     "step": str(step), "base": self.family})
         state = {"rng": gen.get_state()}
         for i, p in enumerate(opt.param_groups[0]["params"]):
             st = opt.state.get(p, {})
@@ -202,6 +204,57 @@ class FluxLoraTrainer(Trainer):
                 opt.state[p] = {"exp_avg": st[f"exp_avg.{i}"].to(p.device), "exp_avg_sq": st[f"exp_avg_sq.{i}"].to(p.device),
                                 "step": st[f"step.{i}"].reshape(()).to(torch.float32)}
         return step
+
+
+Z_IMAGE_TARGETS = ("attention.to_q", "attention.to_k", "attention.to_v", "attention.to_out.0")
+
+
+class ZImageLoraTrainer(FluxLoraTrainer):
+    """The same loop on the Z-Image DiT (candle-gen-z-image/src/training.rs): adapters on the four attention projections
+    of every block; the model is conditioned on 1 - t and its output is negated to give the velocity. Items hold
+    `latent` [16, h, w] and `txt` [L, cap_feat_dim] (the caption encoder's features)."""
+    family, target_suffixes, item_keys = "z-image", Z_IMAGE_TARGETS, ("latent", "txt")
+
+    def __init__(self, cfg, weights: dict[str, torch.Tensor], backend: str = "cpu", device="cpu"):
+        from ..models.dit_zimage import OracleZImageDiT
+
+        self.cfg, self.backend, self.device = cfg, backend, torch.device(device)
+        self.model = OracleZImageDiT(cfg, weights, dtype=torch.float32, device=self.device)
+        for t in self.model.w.values():
+            t.requires_grad_(False)
+
+    def descriptor(self) -> SimpleDescriptor:
+        return SimpleDescriptor("z_image_lora_trainer" if self.backend != "cpu" else "cpu_z_image_lora_trainer",
+                                "z-image", self.backend, {"adapters": ["lora"], "targets": list(Z_IMAGE_TARGETS)})
+
+    def loss_on(self, item, t: float, noise: torch.Tensor) -> torch.Tensor:
+        x0, eps = item["latent"][None], noise[None]
+        xt = (1.0 - t) * x0 + t * eps
+        out = self.model.forward_grad(xt, torch.full((1,), 1.0 - t, device=self.device), item["txt"][None])
+        return torch.mean((-out - (eps - x0)) ** 2)
+
+
+def z_image_trainer_registration(backend: str):
+    """`z_image_lora_trainer` (kind "trainer"): loads the DiT of a Z-Image snapshot directory."""
+    from ..contracts.gen_core.registry import Registration
+    from ..contracts.gen_core.runtime import LoadSpec
+
+    tid = "z_image_lora_trainer" if backend != "cpu" else "cpu_z_image_lora_trainer"
+
+    def load(spec: LoadSpec) -> ZImageLoraTrainer:
+        from ..io.safetensors_io import load_dir
+        from .z_image import ZImagePipeline, ZImageVariant
+
+        if spec.weights is None or spec.weights.is_file:
+            raise InferenceError(f"{tid}: needs a snapshot directory")
+        root = Path(spec.weights.path)
+        device = torch.device("cuda", torch.cuda.current_device()) if backend != "cpu" else torch.device("cpu")
+        if not (root / "transformer").is_dir():
+            raise LoadError(f"{tid}: missing {root / 'transformer'}")
+        pipe = ZImagePipeline(ZImageVariant.BASE, root, "cpu", device)
+        return ZImageLoraTrainer(pipe.dit_cfg, load_dir(root / "transformer"), backend, device)
+
+    return Registration(descriptor=lambda: SimpleDescriptor(tid, "z-image", backend, {"adapters": ["lora"]}), load=load)
 
 
 def trainer_registration(backend: str):

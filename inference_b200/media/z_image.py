@@ -24,7 +24,7 @@ from ..contracts.gen_core.generator import (Capabilities, GenerationOutput, Gene
                                             ModelDescriptor)
 from ..contracts.gen_core.media import Image
 from ..contracts.gen_core.registry import Registration
-from ..contracts.gen_core.runtime import LoadSpec, OffloadPolicy, ProgressDecoding, ProgressStep
+from ..contracts.gen_core.runtime import AdapterKind, LoadSpec, OffloadPolicy, ProgressDecoding, ProgressStep
 from ..contracts.gen_core.sampling import (SCHEDULERS, SOLVERS, FlowModelSampling, TorchLatentOps, denoise, get_solver,
                                            schedule_sigmas)
 from ..contracts.gen_core.tokenizer import PromptTemplate, TextTokenizer, TokenizerConfig
@@ -152,6 +152,13 @@ class ZImagePipeline:
             if not (self.root / d).is_dir():
                 raise LoadError(f"{self.variant.value}: snapshot {self.root} lacks {d}/")
         dit_w = load_dir(self.root / "transformer")
+        for ad in getattr(self, "adapters", []):          # low-rank adapters are merged into the weights at load
+            from ..io.safetensors_io import load_file
+            from .train import merge_lora
+
+            if not Path(ad.path).is_file():
+                raise LoadError(f"{self.variant.value}: adapter file {ad.path} not found")
+            dit_w = merge_lora(dit_w, load_file(ad.path), ad.scale if ad.scale is not None else 1.0)
         vae_w = convert_diffusers_vae_decoder(load_dir(self.root / "vae"), len(self.vae_cfg.ch_mult))
         if self.backend == "b200":
             from ..models.dit_zimage import ZImageDiTGpu
@@ -242,7 +249,7 @@ def z_image_descriptor(variant: ZImageVariant, backend: str, prefix: str = "") -
         id=prefix + variant.value, family="z-image", backend=backend, modality=Modality.IMAGE,
         capabilities=Capabilities(
             supports_negative_prompt=cfg, supports_guidance=cfg, supports_true_cfg=cfg, conditioning=[],
-            supports_lora=False, supports_lokr=False, samplers=list(SOLVERS), schedulers=list(SCHEDULERS),
+            supports_lora=True, supports_lokr=False, samplers=list(SOLVERS), schedulers=list(SCHEDULERS),
             supported_guidance_methods=[], min_size=256, max_size=2048, max_count=8,
             supports_sequential_offload=True),
         required_components=[])
@@ -283,16 +290,20 @@ def _load(variant: ZImageVariant, backend: str, prefix: str) -> Callable[[LoadSp
         if spec.quantize is not None:
             raise Unsupported(f"{mid}: quantised loading ({spec.quantize.name}) is not supported")
         reject_unknown_components(spec.components, [], mid)
-        if spec.control or spec.extra_controls or spec.ip_adapter or spec.adapters:
-            raise Unsupported(f"{mid}: adapters, control branches and IP adapters are not supported by this provider")
+        if spec.control or spec.extra_controls or spec.ip_adapter:
+            raise Unsupported(f"{mid}: control branches and IP adapters are not supported by this provider")
+        for ad in spec.adapters:
+            if ad.kind is not AdapterKind.LORA:
+                raise Unsupported(f"{mid}: adapter kind {ad.kind.value} is not supported (lora)")
         if backend == "b200":
             if not torch.cuda.is_available():
                 raise LoadError(f"{mid}: no CUDA device")
             device = torch.device("cuda", torch.cuda.current_device())
         else:
             device = torch.device("cpu")
-        return ZImageGenerator(ZImagePipeline(variant, Path(spec.weights.path), backend, device),
-                               z_image_descriptor(variant, backend, prefix), spec.offload_policy)
+        pipe = ZImagePipeline(variant, Path(spec.weights.path), backend, device)
+        pipe.adapters = list(spec.adapters)
+        return ZImageGenerator(pipe, z_image_descriptor(variant, backend, prefix), spec.offload_policy)
     return load
 
 

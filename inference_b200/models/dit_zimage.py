@@ -156,9 +156,14 @@ class OracleZImageDiT:
         self.cfg = cfg
         self.w = {k: v.to(device=device, dtype=dtype) for k, v in weights.items()}
         self.dtype, self.device = dtype, torch.device(device)
+        self.lora = None                    # training: {module name: (A [r, in], B [out, r], scale)}
 
     def _lin(self, x, name):
-        return F.linear(x, self.w[name + ".weight"], self.w.get(name + ".bias"))
+        y = F.linear(x, self.w[name + ".weight"], self.w.get(name + ".bias"))
+        if self.lora is not None and name in self.lora:
+            a, b, scale = self.lora[name]
+            y = y + F.linear(F.linear(x, a), b) * scale
+        return y
 
     def _rms(self, x, name, eps=None):
         xf = x.float()

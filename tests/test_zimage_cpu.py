@@ -151,3 +151,49 @@ def test_z_image_providers_conform(tmp_path):
     c = base.generate(GenerationRequest(**req, guidance=4.0, negative_prompt="")).images[0].pixels
     d = base.generate(GenerationRequest(**req, sampler="heun", scheduler="simple")).images[0].pixels
     assert b == c and a != b and d != b and len(a) == 256 * 256 * 3
+
+
+# ---- trainer and adapters ----------------------------------------------------------------------------------------------------
+def test_z_image_trainer_and_adapter_round_trip(tmp_path):
+    from inference_b200.contracts.gen_core import (AdapterKind, AdapterSpec, GenerationRequest, LoadSpec, TrainingConfig,
+                                                   WeightsSource)
+    from inference_b200.io.safetensors_io import load_file, save_file
+    from inference_b200.media import provider_registry
+    from inference_b200.media.train import Z_IMAGE_TARGETS, merge_lora
+    from inference_b200.media.z_image import write_synthetic_snapshot
+    from inference_b200.testkit.aux_suites import TrainerProfile, trainer_conformance
+
+    snap = write_synthetic_snapshot(tmp_path / "zi")
+    ds = tmp_path / "ds"
+    ds.mkdir()
+    g = torch.Generator().manual_seed(0)
+    for i in range(2):
+        save_file({"latent": torch.randn(16, 8, 8, generator=g), "txt": torch.randn(9, 64, generator=g)},
+                  ds / f"item{i}.safetensors")
+    reg = provider_registry("cpu")
+    tr = reg.load_kind("trainer", "cpu_z_image_lora_trainer", LoadSpec.from_dir(snap))
+    assert tr.descriptor().id == "cpu_z_image_lora_trainer"
+    items = tr._items(ds)
+    noise = torch.randn(16, 8, 8, generator=torch.Generator().manual_seed(9))
+    before = float(tr.loss_on(items[0], 0.5, noise))
+    cfg = TrainingConfig(dataset_dir=ds, output_dir=tmp_path / "run", steps=10, learning_rate=5e-3, rank=4, alpha=4.0, seed=3)
+    final = tr.train(cfg, lambda p: None)
+    ad = load_file(final)
+    assert all(k.split(".lora_")[0].endswith(Z_IMAGE_TARGETS) for k in ad) and len(ad) == 2 * 4 * 4     # 4 blocks x 4 targets
+    base_w = {k: v.float() for k, v in load_file(snap / "transformer" / "diffusion_pytorch_model.safetensors").items()}
+    tr.model.w.update({k: v for k, v in merge_lora(base_w, ad).items() if k in tr.model.w})
+    assert float(tr.loss_on(items[0], 0.5, noise)) < before
+    # the generator merges the same file at load
+    req = lambda: GenerationRequest(prompt="a fox", width=256, height=256, steps=1, seed=2)      # noqa: E731
+    big = {k: v * (30.0 if "lora_B" in k else 1.0) for k, v in ad.items()}
+    save_file(big, tmp_path / "big.safetensors")
+
+    def run(scale):
+        spec = LoadSpec(weights=WeightsSource.dir(snap),
+                        adapters=[] if scale is None else [AdapterSpec(path=tmp_path / "big.safetensors", scale=scale,
+                                                                       kind=AdapterKind.LORA)])
+        return reg.load("cpu_z_image_turbo", spec).generate(req(), lambda e: None).images[0].pixels
+    plain = run(None)
+    assert run(0.0) == plain and run(1.0) != plain
+    trainer_conformance(reg.load_kind("trainer", "cpu_z_image_lora_trainer", LoadSpec.from_dir(snap)),
+                        TrainerProfile(ds, tmp_path / "out", steps=3, rank=2))
