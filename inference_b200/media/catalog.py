@@ -6,12 +6,13 @@ from ..contracts.gen_core.registry import ProviderRegistry, ProviderRegistryBuil
 
 
 def provider_registry(backend: str = "b200") -> ProviderRegistry:
-    from . import chroma, flux, z_image
+    from . import chroma, flux, sd3, z_image
 
     b = ProviderRegistryBuilder()
     b.register_generators(flux.registrations(backend))
     b.register_generators(chroma.registrations(backend))
     b.register_generators(z_image.registrations(backend))
+    b.register_generators(sd3.registrations(backend))
     from .train import trainer_registration
 
     b.register("trainer", trainer_registration(backend))

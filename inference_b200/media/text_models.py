@@ -68,7 +68,8 @@ class ClipBpeTokenizer:
             word = out
         return word
 
-    def encode(self, text: str) -> list[int]:
+    def encode(self, text: str, pad_id: int | None = None) -> list[int]:
+        """<|startoftext|> ... <|endoftext|>, padded to max_len with `pad_id` (the end token by default)."""
         text = " ".join(text.split()).strip().lower()
         ids = [self.bos]
         unk = self.vocab.get("<|endoftext|>")
@@ -76,7 +77,7 @@ class ClipBpeTokenizer:
             mapped = "".join(self.b2u[b] for b in tok.encode("utf-8"))
             ids += [self.vocab.get(p, unk) for p in self._bpe(mapped)]
         ids = ids[: self.max_len - 1] + [self.eos]
-        return ids + [self.eos] * (self.max_len - len(ids))
+        return ids + [self.eos if pad_id is None else pad_id] * (self.max_len - len(ids))
 
 
 class T5SentencePieceTokenizer:

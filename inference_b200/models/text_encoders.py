@@ -126,7 +126,7 @@ class ClipTextEncoder:
     def __init__(self, cfg: ClipTextConfig, weights: dict[str, torch.Tensor], device="cpu", dtype=torch.float32):
         self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
         self.w = {k: v.to(device=self.device, dtype=dtype).contiguous() for k, v in weights.items()
-                  if k.startswith("text_model.")}
+                  if k.startswith(("text_model.", "text_projection."))}
 
     def _ln(self, x, name):
         return F.layer_norm(x.float(), (x.shape[-1],), self.w[name + ".weight"].float(), self.w[name + ".bias"].float(),
@@ -141,6 +141,14 @@ class ClipTextEncoder:
     @torch.no_grad()
     def encode(self, ids: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
         """ids [B, L <= 77] -> (last hidden state [B, L, hidden], pooled [B, hidden] = state at the first EOS token)."""
+        out = self.encode_all(ids)
+        return out["last"], out["pooled"]
+
+    @torch.no_grad()
+    def encode_all(self, ids: torch.Tensor) -> dict[str, torch.Tensor]:
+        """last / pooled as in encode(), `penultimate` = the input of the final layer (Hugging Face
+        `hidden_states[-2]`, no final LayerNorm) and, when the checkpoint has a `text_projection`, `projected` = the
+        pooled vector through it (`text_embeds`)."""
         cfg = self.cfg
         B, L = ids.shape
         H = cfg.num_attention_heads
@@ -149,8 +157,11 @@ class ClipTextEncoder:
         p = "text_model."
         x = self.w[p + "embeddings.token_embedding.weight"][ids] + self.w[p + "embeddings.position_embedding.weight"][:L]
         causal = torch.full((L, L), float("-inf"), device=self.device).triu(1)
+        penultimate = x
         for i in range(cfg.num_hidden_layers):
             lp = f"{p}encoder.layers.{i}."
+            if i == cfg.num_hidden_layers - 1:
+                penultimate = x
             h = self._ln(x, lp + "layer_norm1")
             q, k, v = (linear(h, self.w[f"{lp}self_attn.{n}_proj.weight"], self.w[f"{lp}self_attn.{n}_proj.bias"])
                        .view(B, L, H, D).transpose(1, 2).float() for n in "qkv")
@@ -165,7 +176,11 @@ class ClipTextEncoder:
             eos = ids.argmax(-1)
         else:
             eos = (ids == cfg.eos_token_id).int().argmax(-1)
-        return x, x[torch.arange(B, device=self.device), eos]
+        pooled = x[torch.arange(B, device=self.device), eos]
+        out = {"last": x, "pooled": pooled, "penultimate": penultimate}
+        if "text_projection.weight" in self.w:
+            out["projected"] = linear(pooled, self.w["text_projection.weight"])
+        return out
 
 
 # ---------------------------------------------------------------------------------------------------------------

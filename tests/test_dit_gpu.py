@@ -137,7 +137,7 @@ def test_chroma_dit_matches_oracle():
         assert torch.equal(eager, model.forward_graphed(img, img_ids, txt, txt_ids, t, None, None))
 
 
-@pytest.mark.parametrize("family", ["flux", "chroma", "z_image"])
+@pytest.mark.parametrize("family", ["flux", "chroma", "z_image", "sd3"])
 def test_generator_providers_on_device_track_the_oracle_backend(tmp_path, family):
     """The sm_100a provider and the fp32 oracle provider render the same snapshot, seed and request."""
     import numpy as np
@@ -151,6 +151,11 @@ def test_generator_providers_on_device_track_the_oracle_backend(tmp_path, family
     elif family == "chroma":
         from inference_b200.media.chroma import write_synthetic_snapshot
         mid, extra = "chroma1_hd", {"true_cfg": 2.0, "negative_prompt": "blurry"}
+    elif family == "sd3":
+        from inference_b200.media.sd3 import write_synthetic_snapshot as s3
+
+        write_synthetic_snapshot = lambda root: s3(root, dual=True)      # noqa: E731
+        mid, extra = "sd3_5_medium", {"guidance": 2.0, "negative_prompt": "blurry"}
     else:
         from inference_b200.media.z_image import write_synthetic_snapshot as zi
 
