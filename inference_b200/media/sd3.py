@@ -36,11 +36,18 @@ from .chroma import convert_diffusers_vae_decoder, native_vae_to_diffusers
 from .flux import SIZE_MULTIPLE
 from .residency import Residency
 from .seed import default_seed, for_each_image_seed, seeded_noise_nchw
-from .z_image import flow_match_sigmas
 
 SCHEDULE_SHIFT = 3.0
 T5_TOKENS = 256
 VAE_SCALE, VAE_SHIFT = 1.5305, 0.0609
+
+
+def sd3_sigmas(steps: int, shift: float = SCHEDULE_SHIFT) -> list[float]:
+    """`steps` values evenly spaced from 1 to 1 / 1000, each through the static shift `s x / (1 + (s - 1) x)`, then 0
+    (candle-gen-sd3/src/pipeline.rs:118-138; four steps at shift 3 give 1, 0.8573, 0.6007, 0.002994, 0)."""
+    n = max(1, steps)
+    ramp = [1.0 - (0.0 if n == 1 else i / (n - 1)) * (1.0 - 1.0 / 1000.0) for i in range(n)]
+    return [shift * s / (1.0 + (shift - 1.0) * s) for s in ramp] + [0.0]
 
 
 class Sd3Variant(enum.Enum):
@@ -199,7 +206,7 @@ class Sd3Pipeline:
         lh, lw = req.height // 8, req.width // 8
         dev, dt = self.device, self.dtype
         if req.scheduler is None:
-            sigmas = flow_match_sigmas(steps, SCHEDULE_SHIFT, apply_shift=True)
+            sigmas = sd3_sigmas(steps)
         else:
             sigmas = schedule_sigmas(req.scheduler, FlowModelSampling(mu=req.scheduler_shift or 0.0), steps)
         solver, ops, ms = get_solver(req.sampler or "euler"), TorchLatentOps(), FlowModelSampling()

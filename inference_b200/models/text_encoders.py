@@ -193,12 +193,13 @@ class CausalLmTextEncoder:
     On a CUDA device with head_dim 128 the stack runs on the sm_100a kernels (one fused q/k/v GEMM, q/k RMSNorm + RoPE
     in place, causal tcgen05 attention, gated-pair MLP GEMM); elsewhere it is the fp32 oracle decoder."""
 
-    def __init__(self, cfg, weights: dict[str, torch.Tensor], device="cpu", skip_last: int = 1):
+    def __init__(self, cfg, weights: dict[str, torch.Tensor], device="cpu", skip_last: int = 1, final_norm: bool = False):
         from .oracle import OracleLlama, canonical_weights
         from .config import build_rope
 
         self.cfg, self.device = cfg, torch.device(device)
         self.layers = cfg.num_layers - skip_last
+        self.final_norm = final_norm            # Qwen-Image conditions on the last layer after the model's final norm
         self.native = (self.device.type == "cuda" and cfg.head_dim == 128 and not cfg.is_moe and cfg.mla is None and
                        cfg.architecture.value in ("llama", "qwen3"))
         if not self.native:
@@ -208,6 +209,7 @@ class CausalLmTextEncoder:
         dev = self.device
         bf = lambda t: t.to(device=dev, dtype=torch.bfloat16).contiguous()      # noqa: E731
         self.embed = bf(w["model.embed_tokens.weight"])
+        self.norm_w = bf(w["model.norm.weight"]) if final_norm else None
         self.blocks = []
         for i in range(self.layers):
             p = f"model.layers.{i}."
@@ -231,7 +233,8 @@ class CausalLmTextEncoder:
         """token ids -> [1, len(ids), hidden]."""
         t = torch.tensor([ids], dtype=torch.int64, device=self.device)
         if not self.native:
-            return self.oracle.hidden_states(t, None, num_layers=self.layers)
+            h = self.oracle.hidden_states(t, None, num_layers=self.layers)
+            return self.oracle._norm(h, "model.norm.weight") if self.final_norm else h
         from .. import ops
 
         cfg = self.cfg
@@ -253,4 +256,6 @@ class CausalLmTextEncoder:
             h = ops.linear_gated(ops.rmsnorm(x, b["ln2"], eps, w_offset=woff), b["gate_up"],
                                  cfg.mlp_activation)
             x = ops.gemm_bf16(h, b["down"], residual=x)
+        if self.final_norm:
+            x = ops.rmsnorm(x, self.norm_w, eps, w_offset=woff)
         return x[None]

@@ -1,0 +1,131 @@
+"""Qwen-Image autoencoder, decoder side, for single images (parity: candle-gen-qwen-image/src/vae.rs; checkpoint keys
+are the diffusers `AutoencoderKLQwenImage` names).
+
+The checkpoint is a video autoencoder with causal 3-D convolutions. A single image is one frame whose causal padding
+is all zeros, so only the last temporal slice of every 3-D kernel ever meets data: each causal convolution becomes a
+2-D convolution with `weight[:, :, -1]`. The norms are per-pixel L2 normalisations over channels
+(x / ||x|| * sqrt(C) * gamma); the middle block has one single-head attention over pixels; three of the four up blocks
+end in nearest 2x upsampling + a 3x3 convolution that halves the channels. Latents are stored normalised per channel
+and are de-normalised (x * std + mean) before `post_quant_conv`."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+LATENTS_MEAN = (-0.7571, -0.7089, -0.9113, 0.1075, -0.1745, 0.9653, -0.1517, 1.5508, 0.4134, -0.0715, 0.5517, -0.3632,
+                -0.1922, -0.9497, 0.2503, -0.2921)
+LATENTS_STD = (2.8184, 1.4541, 2.3275, 2.6558, 1.2196, 1.7708, 2.6052, 2.0743, 3.2687, 2.1526, 2.8652, 1.5579, 1.6382,
+               1.1253, 2.8251, 1.916)
+NORM_EPS = 1e-12
+
+
+@dataclass
+class QwenVaeConfig:
+    base_dim: int = 96
+    z_dim: int = 16
+    dim_mult: tuple[int, ...] = (1, 2, 4, 4)
+    num_res_blocks: int = 2
+
+    def up_plan(self) -> list[tuple[int, int, int | None]]:
+        """(input channels, width, channels after the upsampler or None) for every up block, top first."""
+        dims = [self.base_dim * m for m in (self.dim_mult[-1],) + tuple(reversed(self.dim_mult))]
+        plan = []
+        for i, (cin, width) in enumerate(zip(dims[:-1], dims[1:])):
+            if i > 0:
+                cin //= 2                       # the previous block's upsampler halved the channels
+            plan.append((cin, width, width // 2 if i < len(self.dim_mult) - 1 else None))
+        return plan
+
+
+def random_qwen_vae_weights(cfg: QwenVaeConfig, seed: int = 0, std: float = 0.05) -> dict[str, torch.Tensor]:
+    g = torch.Generator().manual_seed(seed)
+    w: dict[str, torch.Tensor] = {}
+
+    def conv3(name, o, i, k):
+        w[name + ".weight"], w[name + ".bias"] = torch.randn(o, i, k, k, k, generator=g) * std, torch.randn(o, generator=g) * std
+
+    def conv2(name, o, i, k):
+        w[name + ".weight"], w[name + ".bias"] = torch.randn(o, i, k, k, generator=g) * std, torch.randn(o, generator=g) * std
+
+    def gamma(name, c, dims=3):
+        w[name + ".gamma"] = 1.0 + torch.randn(c, *([1] * dims), generator=g) * 0.1
+
+    def res(p, cin, cout):
+        gamma(p + ".norm1", cin)
+        conv3(p + ".conv1", cout, cin, 3)
+        gamma(p + ".norm2", cout)
+        conv3(p + ".conv2", cout, cout, 3)
+        if cin != cout:
+            conv3(p + ".conv_shortcut", cout, cin, 1)
+
+    top = cfg.base_dim * cfg.dim_mult[-1]
+    conv3("post_quant_conv", cfg.z_dim, cfg.z_dim, 1)
+    conv3("decoder.conv_in", top, cfg.z_dim, 3)
+    res("decoder.mid_block.resnets.0", top, top)
+    res("decoder.mid_block.resnets.1", top, top)
+    a = "decoder.mid_block.attentions.0"
+    gamma(a + ".norm", top, dims=2)
+    conv2(a + ".to_qkv", 3 * top, top, 1)
+    conv2(a + ".proj", top, top, 1)
+    for i, (cin, width, up) in enumerate(cfg.up_plan()):
+        for j in range(cfg.num_res_blocks + 1):
+            res(f"decoder.up_blocks.{i}.resnets.{j}", cin if j == 0 else width, width)
+        if up is not None:
+            conv2(f"decoder.up_blocks.{i}.upsamplers.0.resample.1", up, width, 3)
+    gamma("decoder.norm_out", cfg.base_dim)
+    conv3("decoder.conv_out", 3, cfg.base_dim, 3)
+    return w
+
+
+class QwenVaeDecoder:
+    def __init__(self, cfg: QwenVaeConfig, weights: dict[str, torch.Tensor], dtype=torch.float32, device="cpu"):
+        self.cfg, self.dtype, self.device = cfg, dtype, torch.device(device)
+        self.w: dict[str, torch.Tensor] = {}
+        for k, v in weights.items():
+            if not k.startswith(("decoder.", "post_quant_conv.")):
+                continue
+            if k.endswith(".weight") and v.dim() == 5:
+                v = v[:, :, -1]                              # the only temporal tap a single frame reaches
+            if k.endswith(".gamma"):
+                v = v.reshape(1, -1, 1, 1)
+            self.w[k] = v.to(device=self.device, dtype=dtype).contiguous()
+        self.mean = torch.tensor(LATENTS_MEAN[: cfg.z_dim], device=self.device, dtype=dtype).view(1, -1, 1, 1)
+        self.std = torch.tensor(LATENTS_STD[: cfg.z_dim], device=self.device, dtype=dtype).view(1, -1, 1, 1)
+
+    def _conv(self, x, name, pad):
+        return F.conv2d(x, self.w[name + ".weight"], self.w[name + ".bias"], padding=pad)
+
+    def _norm(self, x, name):
+        xf = x.float()
+        c = x.shape[1]
+        y = xf / torch.sqrt(xf.pow(2).sum(1, keepdim=True) + NORM_EPS) * (c ** 0.5) * self.w[name + ".gamma"].float()
+        return y.to(x.dtype)
+
+    def _res(self, x, p):
+        h = self._conv(F.silu(self._norm(x, p + ".norm1")), p + ".conv1", 1)
+        h = self._conv(F.silu(self._norm(h, p + ".norm2")), p + ".conv2", 1)
+        return h + (self._conv(x, p + ".conv_shortcut", 0) if p + ".conv_shortcut.weight" in self.w else x)
+
+    def _attention(self, x, p):
+        B, C, H, W = x.shape
+        q, k, v = self._conv(self._norm(x, p + ".norm"), p + ".to_qkv", 0).reshape(B, 3, C, H * W).transpose(2, 3).unbind(1)
+        o = F.scaled_dot_product_attention(q[:, None], k[:, None], v[:, None])[:, 0]          # one head of width C
+        return x + self._conv(o.transpose(1, 2).reshape(B, C, H, W), p + ".proj", 0)
+
+    @torch.no_grad()
+    def decode(self, latents: torch.Tensor) -> torch.Tensor:
+        """Normalised latents [B, 16, h, w] -> image [B, 3, 8h, 8w] in about [-1, 1]."""
+        z = latents.to(self.device, self.dtype) * self.std + self.mean
+        h = self._conv(self._conv(z, "post_quant_conv", 0), "decoder.conv_in", 1)
+        h = self._res(h, "decoder.mid_block.resnets.0")
+        h = self._attention(h, "decoder.mid_block.attentions.0")
+        h = self._res(h, "decoder.mid_block.resnets.1")
+        for i, (_, _, up) in enumerate(self.cfg.up_plan()):
+            for j in range(self.cfg.num_res_blocks + 1):
+                h = self._res(h, f"decoder.up_blocks.{i}.resnets.{j}")
+            if up is not None:
+                h = self._conv(F.interpolate(h, scale_factor=2, mode="nearest"),
+                               f"decoder.up_blocks.{i}.upsamplers.0.resample.1", 1)
+        return self._conv(F.silu(self._norm(h, "decoder.norm_out")), "decoder.conv_out", 1)

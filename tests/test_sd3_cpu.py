@@ -151,3 +151,13 @@ def test_triple_text_conditioning_shapes():
     c = enc.encode("x")
     assert c.context.shape == (1, 77 + 16, 40) and c.pooled.shape == (1, 16)
     assert c.context[0, 0, :20].eq(1).all() and c.context[0, 0, 20:].eq(0).all() and c.context[0, 77:].eq(3).all()
+
+
+def test_sigma_table_golden():
+    from inference_b200.media.sd3 import sd3_sigmas
+
+    got = sd3_sigmas(4)
+    for a, b in zip(got, [1.0, 0.8573265, 0.6007194, 0.002994012, 0.0]):
+        assert abs(a - b) < 1e-6
+    s = sd3_sigmas(28)
+    assert len(s) == 29 and all(x > y for x, y in zip(s, s[1:]))
