@@ -6,13 +6,14 @@ from ..contracts.gen_core.registry import ProviderRegistry, ProviderRegistryBuil
 
 
 def provider_registry(backend: str = "b200") -> ProviderRegistry:
-    from . import chroma, flux, sd3, z_image
+    from . import chroma, flux, qwen_image, sd3, z_image
 
     b = ProviderRegistryBuilder()
     b.register_generators(flux.registrations(backend))
     b.register_generators(chroma.registrations(backend))
     b.register_generators(z_image.registrations(backend))
     b.register_generators(sd3.registrations(backend))
+    b.register_generators(qwen_image.registrations(backend))
     from .train import trainer_registration
 
     b.register("trainer", trainer_registration(backend))

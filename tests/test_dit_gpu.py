@@ -137,7 +137,7 @@ def test_chroma_dit_matches_oracle():
         assert torch.equal(eager, model.forward_graphed(img, img_ids, txt, txt_ids, t, None, None))
 
 
-@pytest.mark.parametrize("family", ["flux", "chroma", "z_image", "sd3"])
+@pytest.mark.parametrize("family", ["flux", "chroma", "z_image", "sd3", "qwen_image"])
 def test_generator_providers_on_device_track_the_oracle_backend(tmp_path, family):
     """The sm_100a provider and the fp32 oracle provider render the same snapshot, seed and request."""
     import numpy as np
@@ -151,6 +151,11 @@ def test_generator_providers_on_device_track_the_oracle_backend(tmp_path, family
     elif family == "chroma":
         from inference_b200.media.chroma import write_synthetic_snapshot
         mid, extra = "chroma1_hd", {"true_cfg": 2.0, "negative_prompt": "blurry"}
+    elif family == "qwen_image":
+        from inference_b200.media.qwen_image import write_synthetic_snapshot as qi
+
+        write_synthetic_snapshot = lambda root: qi(root, text="qwen_vl", te_head_dim=128)      # noqa: E731
+        mid, extra = "qwen_image", {"true_cfg": 2.0, "negative_prompt": "blurry"}
     elif family == "sd3":
         from inference_b200.media.sd3 import write_synthetic_snapshot as s3
 
@@ -213,3 +218,27 @@ def test_causal_lm_prompt_encoder_matches_oracle():
     ref = OracleLlama(cfg, w, device="cuda").hidden_states(torch.tensor([ids], device="cuda"), None, num_layers=2)
     assert out.shape == ref.shape
     assert (out.float() - ref).abs().max().item() < 0.05 * max(1.0, ref.abs().max().item())
+
+
+def test_qwen_image_dit_matches_oracle():
+    from inference_b200.models.dit_qwen_image import (OracleQwenImageDiT, QwenImageConfig, QwenImageDiTGpu, position_ids,
+                                                      random_qwen_image_weights)
+
+    cfg = QwenImageConfig(num_layers=2, num_attention_heads=2, joint_attention_dim=128)
+    w = {k: v.bfloat16().float() for k, v in random_qwen_image_weights(cfg, seed=0, std=0.05).items()}
+    oracle = OracleQwenImageDiT(cfg, w, device="cuda")
+    model = QwenImageDiTGpu(cfg, device=torch.device("cuda")).load_state_dict(w)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    hh, ww, St = 6, 5, 19
+    img = torch.randn(1, hh * ww, 64, device="cuda", generator=g).bfloat16()
+    txt = torch.randn(1, St, 128, device="cuda", generator=g).bfloat16()
+    t = torch.full((1,), 0.7, device="cuda")
+    txt_ids, img_ids = position_ids(hh, ww, St, "cuda")
+    ref = oracle.forward(img.float(), img_ids, oracle.prepare_text(txt.float()), txt_ids, t, None, None)
+    ptxt = model.prepare_text(txt)
+    out = model.forward(img, img_ids, ptxt, txt_ids, t, None, None)
+    err = (out.float() - ref).abs().max().item()
+    assert err < 0.06 * max(1.0, ref.abs().max().item()), err
+    eager = out.clone()
+    for _ in range(2):
+        assert torch.equal(eager, model.forward_graphed(img, img_ids, ptxt, txt_ids, t, None, None))

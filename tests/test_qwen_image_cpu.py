@@ -123,3 +123,37 @@ def test_single_frame_autoencoder_equals_causal_3d_convolutions():
                          padding=1)[:, :, None]
     ref = cconv(F.silu(norm(h, "decoder.norm_out")), "decoder.conv_out", 1)[:, :, 0]
     torch.testing.assert_close(out, ref, atol=1e-4, rtol=1e-4)
+
+
+def test_schedule_and_guidance_helpers():
+    from inference_b200.media.qwen_image import guided_velocity, qwen_mu, qwen_sigmas
+
+    assert abs(qwen_mu(256, 256) - 0.5) < 1e-9 and abs(qwen_mu(1024, 1024) - (0.5 + 0.4 * (4096 - 256) / (8192 - 256))) < 1e-9
+    s = qwen_sigmas(20, 1024, 1024)
+    assert len(s) == 21 and s[0] == 1.0 and s[-1] == 0.0 and abs(s[19] - 0.02) < 1e-9
+    assert all(a > b for a, b in zip(s, s[1:]))
+    g = torch.Generator().manual_seed(0)
+    pos, neg = torch.randn(1, 5, 8, generator=g), torch.randn(1, 5, 8, generator=g)
+    v = guided_velocity(pos, neg, 4.0)
+    torch.testing.assert_close(v.norm(dim=-1), pos.norm(dim=-1))
+    comb = neg + 4.0 * (pos - neg)
+    torch.testing.assert_close(v / v.norm(dim=-1, keepdim=True), comb / comb.norm(dim=-1, keepdim=True))
+
+
+def test_qwen_image_provider_conforms(tmp_path):
+    from inference_b200.contracts.gen_core import GenerationRequest, LoadSpec
+    from inference_b200.media import provider_registry
+    from inference_b200.media.qwen_image import write_synthetic_snapshot
+    from inference_b200.testkit import generator as kit
+
+    snap = write_synthetic_snapshot(tmp_path / "qi", text="qwen_vl")
+    reg = provider_registry("cpu")
+    assert "cpu_qwen_image" in reg.ids() and reg.descriptor_conformance_errors() == []
+    gen = reg.load("cpu_qwen_image", LoadSpec.from_dir(snap))
+    kit.conformance(gen, kit.Profile(steps=2, cancel_steps=5))
+    kit.registry_conformance(reg, "cpu_qwen_image", LoadSpec.from_dir(snap))
+    req = dict(prompt="a red fox", width=256, height=256, steps=2, seed=5)
+    a = gen.generate(GenerationRequest(**req, true_cfg=1.0)).images[0].pixels
+    b = gen.generate(GenerationRequest(**req)).images[0].pixels                     # default true CFG 4, negative " "
+    c = gen.generate(GenerationRequest(**req, guidance=4.0, negative_prompt=" ")).images[0].pixels
+    assert b == c and a != b and len(a) == 256 * 256 * 3
