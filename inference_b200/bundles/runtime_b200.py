@@ -19,9 +19,9 @@ def provider_registry() -> ProviderRegistry:
 
 
 def text_registry() -> TextLlmRegistry:
-    from ..engine.provider import B200_LLAMA, B200_LLAVA
+    from ..engine.provider import B200_LLAMA, B200_LLAVA, B200_QWEN3_VL
 
-    return TextLlmRegistryBuilder().register(B200_LLAMA).register(B200_LLAVA).build()
+    return TextLlmRegistryBuilder().register(B200_LLAMA).register(B200_LLAVA).register(B200_QWEN3_VL).build()
 
 
 def snapshot_preparer_registry() -> SnapshotPreparerRegistry:

@@ -19,9 +19,9 @@ def provider_registry() -> ProviderRegistry:
 
 
 def text_registry() -> TextLlmRegistry:
-    from ..engine.provider import CPU_LLAMA, CPU_LLAVA
+    from ..engine.provider import CPU_LLAMA, CPU_LLAVA, CPU_QWEN3_VL
 
-    return TextLlmRegistryBuilder().register(CPU_LLAMA).register(CPU_LLAVA).build()
+    return TextLlmRegistryBuilder().register(CPU_LLAMA).register(CPU_LLAVA).register(CPU_QWEN3_VL).build()
 
 
 def snapshot_preparer_registry() -> SnapshotPreparerRegistry:

@@ -38,6 +38,13 @@ def set_embed_override(seq: Any, positions: list[int], values: torch.Tensor) -> 
     seq.pending_embeds = (list(positions), values)
 
 
+def set_mrope_override(seq: Any, positions: torch.Tensor, next_position: int, rows: torch.Tensor,
+                       taps: list[torch.Tensor]) -> None:
+    """Qwen3-VL prompts (oracle backend): the next forward on `seq` uses the three-axis positions [3, S] of its new
+    tokens and adds the DeepStack taps at `rows`; later tokens continue at `next_position`."""
+    seq.pending_mrope = (positions, int(next_position), rows, taps)
+
+
 def _take_overrides(seqs) -> list | None:
     ov = [getattr(s, "pending_embeds", None) for s in seqs]
     if not any(o is not None for o in ov):
@@ -123,10 +130,16 @@ class OracleBackend:
                 emb = self.model.embed(ids.to(self.model.device)).clone()
                 emb[0, o[0]] = o[1].to(emb.device, emb.dtype)
                 kw["embeds"] = emb
+            mr = getattr(s, "pending_mrope", None)
+            offset = s.cache.offset + getattr(s, "rope_delta", 0)
+            if mr is not None:
+                s.pending_mrope = None
+                kw["mrope_positions"], kw["deepstack"] = mr[0], (mr[2], mr[3])
+                s.rope_delta = mr[1] - (s.cache.offset + len(toks))
             if all_positions:
-                out.append(self.model.decode_logits_all(ids, s.cache, s.cache.offset, **kw)[0].float())
+                out.append(self.model.decode_logits_all(ids, s.cache, offset, **kw)[0].float())
             else:
-                out.append(self.model.decode_logits(ids, s.cache, s.cache.offset, **kw)[0].float())
+                out.append(self.model.decode_logits(ids, s.cache, offset, **kw)[0].float())
         return out
 
     def forward_greedy(self, seqs, new_tokens):
@@ -138,7 +151,10 @@ class OracleBackend:
     def fork(self, seq, n_tokens):
         c = seq.cache.clone()
         c.truncate(n_tokens)
-        return _OracleSeq(c)
+        f = _OracleSeq(c)
+        if getattr(seq, "rope_delta", 0):
+            f.rope_delta = seq.rope_delta
+        return f
 
     def release(self, seq):
         seq.cache.reset()

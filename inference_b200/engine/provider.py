@@ -429,6 +429,117 @@ class LlavaProvider(LlamaProvider):
         return ids, seq
 
 
+# ---- Qwen3-VL: vision tower with DeepStack in front of the M-RoPE decoder -----------------------------------------
+class Qwen3VlProvider(LlamaProvider):
+    """Image-and-text chat over a Hugging Face Qwen3-VL snapshot (candle-llm/src/models/qwen35_vision.rs,
+    deepstack.rs). Every image becomes `<|vision_start|><|image_pad|><|vision_end|>` in its message; after
+    tokenisation the pad token expands to one token per merged patch group, the prefill replaces those embeddings by
+    the tower's tokens, uses three-axis positions and adds the DeepStack taps after the first decoder layers. The
+    decoder runs on the oracle backend (fp32 on the CPU bundle, bf16 on the device for the b200 bundle): the paged
+    sm_100a decoder has no three-axis rotary table."""
+
+    IMAGE_BLOCK = "<|vision_start|><|image_pad|><|vision_end|>"
+
+    def __init__(self, base: LlamaProvider, tower, image_token_id: int):
+        caps = base._descriptor.capabilities
+        caps.supports_vision = True
+        super().__init__(base._descriptor, base.backend, base.tokenizer, base.template, base.stop_tokens, base.cfg)
+        self.tower, self.image_token_id = tower, image_token_id
+
+    @staticmethod
+    def load(spec: LoadSpec, provider_id: str, backend_name: str, comm=None) -> "Qwen3VlProvider":
+        from ..models.qwen3_vl import Qwen3VlVisionConfig, Qwen3VlVisionTower
+
+        p = Path(spec.source)
+        top = _read_json(p / "config.json")
+        if "vision_config" not in top or "text_config" not in top:
+            raise LoadError(f"{p}: not a Qwen3-VL snapshot (config.json lacks vision_config / text_config)")
+        w = load_dir(p)
+        text = {k.replace("model.language_model.", "model."): v for k, v in w.items()
+                if not k.startswith(("model.visual.", "visual."))}
+        cfg = ModelConfig.from_json(top)
+        tokenizer = Tokenizer.from_file(p / "tokenizer.json")
+        tcfg = _read_json(p / "tokenizer_config.json")
+        template, thinking, tools = _pick_template(tcfg.get("chat_template") and tcfg, cfg)
+        stop = sorted(_eos_ids(top) | _eos_ids(top["text_config"]) |
+                      {i for n in _STOP_NAMES if (i := tokenizer.token_to_id(n)) is not None})
+        on_gpu = backend_name == BACKEND_GPU
+        if on_gpu and not torch.cuda.is_available():
+            raise LoadError("the b200 backend needs a CUDA device (use the cpu runtime bundle on hosts without one)")
+        dev, dtype = ("cuda", torch.bfloat16) if on_gpu else ("cpu", torch.float32)
+        backend = OracleBackend(OracleLlama(cfg, text, dtype=dtype, device=dev),
+                                max_context=cfg.max_position_embeddings or 8192)
+        caps = TextLlmCapabilities(max_context_tokens=backend.max_context, max_new_tokens=0, supports_system_prompt=True,
+                                   supports_vision=True, supports_video=False, supports_thinking=thinking,
+                                   supports_tools=tools, supported_constraints=[Constraint.JSON])
+        base = LlamaProvider(TextLlmDescriptor(provider_id, "qwen3-vl", backend_name, caps), backend, tokenizer, template,
+                             stop, cfg)
+        prefix = "model.visual." if any(k.startswith("model.visual.") for k in w) else "visual."
+        tower = Qwen3VlVisionTower(Qwen3VlVisionConfig.from_json(top), w, dev, dtype, prefix=prefix)
+        image_token = top.get("image_token_id")
+        if image_token is None:
+            image_token = tokenizer.token_to_id("<|image_pad|>")
+        if image_token is None:
+            raise LoadError(f"{p}: no image_token_id in config.json and no <|image_pad|> token in the tokenizer")
+        return Qwen3VlProvider(base, tower, int(image_token))
+
+    def _render_messages(self, req: TextLlmRequest):
+        from ..contracts.core_llm.message import ImageRef, Message, Text
+
+        out = []
+        for m in req.messages:
+            n = sum(isinstance(c, ImageRef) for c in m.content)
+            if n == 0:
+                out.append(m)
+                continue
+            out.append(Message(m.role, [Text(self.IMAGE_BLOCK * n + m.text_content())], m.thinking, list(m.tool_calls)))
+        return out
+
+    def _splice_media(self, req: TextLlmRequest, prompt_ids: list[int]):
+        import numpy as np
+
+        from ..contracts.core_llm import InvalidRequest
+        from ..contracts.core_llm.message import ImageRef
+        from ..models.qwen3_vl import image_to_patches, mrope_positions
+        from .backend import set_embed_override, set_mrope_override
+
+        images = [c for m in req.messages for c in m.content if isinstance(c, ImageRef)]
+        if not images:
+            return prompt_ids, None
+        tid = self.image_token_id
+        if prompt_ids.count(tid) != len(images):
+            raise InvalidRequest(f"[{self._descriptor.id}] the rendered prompt holds {prompt_ids.count(tid)} image "
+                                 f"placeholders for {len(images)} images")
+        vc = self.tower.cfg
+        patches, grids = [], []
+        for im in images:
+            rgb = torch.from_numpy(np.frombuffer(bytes(im.pixels), dtype=np.uint8).reshape(im.height, im.width, 3).copy())
+            pt, g = image_to_patches(rgb, vc)
+            patches.append(pt)
+            grids.append(g)
+        tokens, taps = self.tower.forward(torch.cat(patches, 0), grids)
+        per_image = [g[0] * (g[1] // vc.spatial_merge_size) * (g[2] // vc.spatial_merge_size) for g in grids]
+        ids, rows, k = [], [], 0
+        for t in prompt_ids:
+            if t == tid:
+                rows += list(range(len(ids), len(ids) + per_image[k]))
+                ids += [tid] * per_image[k]
+                k += 1
+            else:
+                ids.append(t)
+        pos, nxt = mrope_positions(ids, grids, tid, vc.spatial_merge_size)
+        seq = self.backend.new_sequence()
+        set_embed_override(seq, rows, tokens)
+        set_mrope_override(seq, pos, nxt, torch.tensor(rows), taps)
+        return ids, seq
+
+
+def _can_load_qwen3_vl(spec: LoadSpec) -> bool:
+    p = Path(spec.source)
+    top = _read_json(p / "config.json") if p.is_dir() else {}
+    return "vision_config" in top and "text_config" in top and "qwen3_vl" in str(top.get("model_type", "")).lower()
+
+
 def _can_load_llava(spec: LoadSpec) -> bool:
     p = Path(spec.source)
     top = _read_json(p / "config.json") if p.is_dir() else {}
@@ -450,18 +561,30 @@ def _descriptor_vision(pid: str, backend: str) -> TextLlmDescriptor:
 
 
 def _can_load_gpu(spec: LoadSpec) -> bool:
+    if _can_load_qwen3_vl(spec):            # a snapshot with a vision tower belongs to the vision-language provider
+        return False
     cfg = probe_config(spec)
     return cfg is not None and (_supported_on_gpu(cfg) or cfg.architecture is Architecture.QWEN35)
 
 
 def _can_load_cpu(spec: LoadSpec) -> bool:
-    return probe_config(spec) is not None
+    return not _can_load_qwen3_vl(spec) and probe_config(spec) is not None
 
 
 B200_LLAVA = TextLlmRegistration(lambda: _descriptor_vision("b200-llava", BACKEND_GPU),
                                  lambda spec: LlavaProvider.load(spec, "b200-llava", BACKEND_GPU), _can_load_llava)
 CPU_LLAVA = TextLlmRegistration(lambda: _descriptor_vision("cpu-llava", BACKEND_CPU),
                                 lambda spec: LlavaProvider.load(spec, "cpu-llava", BACKEND_CPU), _can_load_llava)
+def _descriptor_qwen3_vl(pid: str, backend: str) -> TextLlmDescriptor:
+    d = _descriptor_vision(pid, backend)
+    d.family = "qwen3-vl"
+    return d
+
+
+B200_QWEN3_VL = TextLlmRegistration(lambda: _descriptor_qwen3_vl("b200-qwen3-vl", BACKEND_GPU),
+                                    lambda spec: Qwen3VlProvider.load(spec, "b200-qwen3-vl", BACKEND_GPU), _can_load_qwen3_vl)
+CPU_QWEN3_VL = TextLlmRegistration(lambda: _descriptor_qwen3_vl("cpu-qwen3-vl", BACKEND_CPU),
+                                   lambda spec: Qwen3VlProvider.load(spec, "cpu-qwen3-vl", BACKEND_CPU), _can_load_qwen3_vl)
 B200_LLAMA = TextLlmRegistration(lambda: _descriptor("b200-llama", BACKEND_GPU),
                                  lambda spec: LlamaProvider.load(spec, "b200-llama", BACKEND_GPU), _can_load_gpu)
 CPU_LLAMA = TextLlmRegistration(lambda: _descriptor("cpu-llama", BACKEND_CPU),

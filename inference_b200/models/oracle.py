@@ -320,16 +320,28 @@ class OracleLlama:
 
     def hidden_states(self, ids: torch.Tensor | None, cache: ContiguousKvCache | None, offset: int = 0, *,
                       embeds: torch.Tensor | None = None, positions: torch.Tensor | None = None,
-                      additive_mask: torch.Tensor | None = None, num_layers: int | None = None) -> torch.Tensor:
-        """The residual stream after `num_layers` decoder layers (all of them by default), before the final norm."""
+                      additive_mask: torch.Tensor | None = None, num_layers: int | None = None,
+                      mrope_positions: torch.Tensor | None = None,
+                      deepstack: tuple[torch.Tensor, list[torch.Tensor]] | None = None) -> torch.Tensor:
+        """The residual stream after `num_layers` decoder layers (all of them by default), before the final norm.
+        mrope_positions [3, S] (batch 1) replaces `positions` with the three-axis interleaved rotary table of
+        Qwen3-VL; deepstack = (rows, taps) adds taps[i] to those rows of the stream after decoder layer i."""
         x = self.embed(ids.to(self.device)) if embeds is None else embeds.to(self.device, self.dtype)
         B, S, _ = x.shape
         if positions is None:
             positions = torch.arange(offset, offset + S, device=self.device)[None, :].expand(B, S)
         cos, sin = rope_cos_sin(self.inv_freq, positions.to(self.device))
+        if mrope_positions is not None:
+            from .qwen3_vl import interleaved_mrope_table
+
+            cos, sin = (t[None] for t in interleaved_mrope_table(mrope_positions, self.inv_freq,
+                                                                 self.cfg.mrope_section_resolved()))
         causal = additive_mask is None
         for layer in range(self.cfg.num_layers if num_layers is None else num_layers):
             x = self._layer(x, layer, cos, sin, cache, causal, additive_mask)
+            if deepstack is not None and layer < len(deepstack[1]):
+                x = x.clone()
+                x[0, deepstack[0].to(self.device)] += deepstack[1][layer].to(self.device, x.dtype)
         return x
 
     def project_logits(self, h: torch.Tensor) -> torch.Tensor:

@@ -45,7 +45,7 @@ def test_text_and_media_through_the_c_abi(lib, tmp_path):
     out = ctypes.c_char_p()
     assert lib.swb_rt_catalog_json(rt, ctypes.byref(out)) == 0
     cat = json.loads(out.value)
-    assert cat["backend"] == "cpu" and cat["text_llm_ids"] == ["cpu-llama", "cpu-llava"]
+    assert cat["backend"] == "cpu" and cat["text_llm_ids"] == ["cpu-llama", "cpu-llava", "cpu-qwen3-vl"]
     # ---- text ------------------------------------------------------------------------------------------
     h = ctypes.c_uint64()
     assert lib.swb_text_load(rt, None, json.dumps({"source": str(tmp_path / "missing")}).encode(), ctypes.byref(h)) < 0
@@ -119,4 +119,4 @@ def test_standalone_c_host_embeds_an_interpreter(tmp_path):
     env = dict(os.environ, PYTHONPATH=os.pathsep.join(site.getsitepackages()))
     r = subprocess.run([str(exe), str(repo)], capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0, r.stdout + r.stderr
-    assert '"text_llm_ids": ["cpu-llama", "cpu-llava"]' in r.stdout
+    assert '"text_llm_ids": ["cpu-llama", "cpu-llava", "cpu-qwen3-vl"]' in r.stdout

@@ -71,3 +71,99 @@ def test_position_ids_and_interleaved_table_match_hugging_face():
     cos, sin = V.interleaved_mrope_table(pos, rot.inv_freq, (6, 5, 5))
     torch.testing.assert_close(cos, cos_ref[0, :, :16], atol=1e-6, rtol=1e-6)
     torch.testing.assert_close(sin, sin_ref[0, :, :16], atol=1e-6, rtol=1e-6)
+
+
+def test_multimodal_forward_matches_hugging_face():
+    from inference_b200.models.config import ModelConfig
+    from inference_b200.models.oracle import OracleLlama
+
+    cfg, model = _hf(seed=3)
+    sd = dict(model.state_dict())
+    mc = ModelConfig.from_json(cfg.to_dict() | {"architectures": ["Qwen3VLForConditionalGeneration"]})
+    assert mc.mrope_section == (6, 5, 5)
+    text = {k.replace("model.language_model.", "model."): v for k, v in sd.items() if not k.startswith("model.visual.")}
+    oracle = OracleLlama(mc, text)
+    vc = V.Qwen3VlVisionConfig.from_json(cfg.to_dict())
+    tower = V.Qwen3VlVisionTower(vc, sd)
+    ids = [5, 6, 152] + [150] * 6 + [153, 7, 8]
+    grids = [(1, 4, 6)]
+    patches = torch.randn(24, vc.patch_dim, generator=torch.Generator().manual_seed(4))
+    tokens, taps = tower.forward(patches, grids)
+    rows = torch.tensor([i for i, t in enumerate(ids) if t == 150])
+    emb = oracle.embed(torch.tensor([ids]))
+    emb[0, rows] = tokens
+    pos, nxt = V.mrope_positions(ids, grids, 150)
+    h = oracle.hidden_states(None, None, embeds=emb, mrope_positions=pos, deepstack=(rows, taps))
+    logits = oracle.project_logits(h)
+    mm = torch.zeros(1, len(ids), dtype=torch.int32)
+    mm[0, rows] = 1
+    with torch.no_grad():
+        ref = model(input_ids=torch.tensor([ids]), pixel_values=patches, image_grid_thw=torch.tensor(grids),
+                    mm_token_type_ids=mm).logits
+    torch.testing.assert_close(logits, ref, atol=3e-5, rtol=1e-4)
+
+
+def test_text_provider_answers_about_an_image(tmp_path):
+    """A Qwen3-VL snapshot loads model-first through the text registry; greedy decoding with an image in the prompt
+    matches Hugging Face generate() on the same token ids and patches (so the positions of the decode steps continue
+    after the image block as the library's do)."""
+    import json
+
+    from inference_b200.bundles import runtime_cpu
+    from inference_b200.contracts.core_llm import LoadSpec, Message, Role, TextLlmRequest
+    from inference_b200.contracts.core_llm.message import ImageRef, Text
+    from inference_b200.contracts.core_llm.request import Sampling
+    from inference_b200.contracts.core_llm.template import RenderOptions
+    from inference_b200.io.safetensors_io import save_file
+    from inference_b200.testkit.synthetic import wordlevel_tokenizer_json
+
+    cfg, hf = _hf(seed=5)
+    top = cfg.to_dict()
+    top["model_type"] = "qwen3_vl"
+    top["architectures"] = ["Qwen3VLForConditionalGeneration"]
+    (tmp_path / "config.json").write_text(json.dumps(top))
+    save_file({k: v.contiguous() for k, v in hf.state_dict().items()}, tmp_path / "model.safetensors")
+    tok = json.loads(wordlevel_tokenizer_json(200))
+    special = {150: "<|image_pad|>", 152: "<|vision_start|>", 153: "<|vision_end|>"}
+    tok["model"]["vocab"] = {special.get(i, w): i for w, i in tok["model"]["vocab"].items()}
+    tok["added_tokens"] = tok.get("added_tokens", []) + [
+        {"id": i, "content": c, "single_word": False, "lstrip": False, "rstrip": False, "normalized": False, "special": True}
+        for i, c in special.items()]
+    (tmp_path / "tokenizer.json").write_text(json.dumps(tok))
+    (tmp_path / "tokenizer_config.json").write_text(json.dumps({"eos_token": "<|im_end|>"}))
+    llm = runtime_cpu.catalog().text().load_for_model(LoadSpec.dense(str(tmp_path)))
+    d = llm.descriptor()
+    assert d.id == "cpu-qwen3-vl" and d.capabilities.supports_vision
+    g = torch.Generator().manual_seed(5)
+    raw = bytes(torch.randint(0, 256, (16 * 24 * 3,), generator=g, dtype=torch.uint8).tolist())
+    msg = Message(Role.USER, [ImageRef(24, 16, raw), Text("the cat sat")])
+    req = TextLlmRequest(messages=[msg], max_new_tokens=5, seed=0, sampling=Sampling(temperature=0.0))
+    # this tiny tower has 4-pixel patches: keep the test image at its own size
+    import inference_b200.models.qwen3_vl as Q3
+
+    orig = Q3.image_to_patches
+    Q3.image_to_patches = lambda rgb, vc, **kw: orig(rgb, vc, min_pixels=16, max_pixels=10 ** 6)
+    try:
+        ids, seq = llm._splice_media(req, llm.tokenizer.encode(
+            llm.template.render_with(llm._render_messages(req), RenderOptions(True, None, [])), add_special_tokens=False))
+        assert ids.count(150) == (16 // 8) * (24 // 8) and seq is not None
+        llm.backend.release(seq)
+        out = llm.generate(req, on_event=lambda e: None)
+    finally:
+        Q3.image_to_patches = orig
+    patches, grid = orig(torch.frombuffer(bytearray(raw), dtype=torch.uint8).view(16, 24, 3),
+                         Q3.Qwen3VlVisionConfig.from_json(top), min_pixels=16, max_pixels=10 ** 6)
+    mm = torch.tensor([[1 if t == 150 else 0 for t in ids]], dtype=torch.int32)
+    with torch.no_grad():
+        ref = hf.generate(input_ids=torch.tensor([ids]), pixel_values=patches, image_grid_thw=torch.tensor([grid]),
+                          mm_token_type_ids=mm, attention_mask=torch.ones(1, len(ids), dtype=torch.long), max_new_tokens=5,
+                          do_sample=False, pad_token_id=0)[0, len(ids):].tolist()
+    stops = set(llm.stop_tokens)
+    want = []
+    for t in ref:
+        if t in stops:
+            break
+        want.append(t)
+    words = {i: w for w, i in tok["model"]["vocab"].items()}
+    got = out.text.split()
+    assert len(got) >= 1 and got == [words[t] for t in want][: len(got)]

@@ -180,7 +180,7 @@ def test_llava_text_provider_answers_about_an_image(tmp_path):
     (tmp_path / "tokenizer.json").write_text(json.dumps(tok))
     (tmp_path / "tokenizer_config.json").write_text(json.dumps({"bos_token": "<|begin_of_text|>", "eos_token": "<|eot_id|>"}))
     cat = runtime_cpu.catalog()
-    assert cat.text().ids() == ["cpu-llama", "cpu-llava"] if hasattr(cat.text(), "ids") else True
+    assert [r.descriptor().id for r in cat.text().registrations()] == ["cpu-llama", "cpu-llava", "cpu-qwen3-vl"]
     llm = cat.text().load_for_model(LoadSpec.dense(str(tmp_path)))
     d = llm.descriptor()
     assert d.id == "cpu-llava" and d.capabilities.supports_vision
