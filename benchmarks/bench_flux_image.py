@@ -31,7 +31,7 @@ def main():
         json.dump({"text": "hash", "random_init": 0}, f)
     gen = runtime_b200.catalog().media().load(args.model, LoadSpec.from_dir(d))
     extra = {"guidance": 3.5} if args.model == "flux1_dev" else {}
-    if args.model in ("chroma1_hd", "chroma1_base", "z_image", "qwen_image", "sd3_5_large", "sd3_5_medium"):
+    if args.model in ("chroma1_hd", "chroma1_base", "z_image", "qwen_image", "sd3_5_large", "sd3_5_medium", "sdxl"):
         extra["negative_prompt"] = "blurry, low quality"
     events = []
     req = lambda seed: GenerationRequest(prompt="a photo of a fox", width=args.size, height=args.size,  # noqa: E731

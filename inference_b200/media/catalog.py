@@ -6,7 +6,7 @@ from ..contracts.gen_core.registry import ProviderRegistry, ProviderRegistryBuil
 
 
 def provider_registry(backend: str = "b200") -> ProviderRegistry:
-    from . import chroma, flux, qwen_image, sd3, z_image
+    from . import chroma, flux, qwen_image, sd3, sdxl, z_image
 
     b = ProviderRegistryBuilder()
     b.register_generators(flux.registrations(backend))
@@ -14,6 +14,7 @@ def provider_registry(backend: str = "b200") -> ProviderRegistry:
     b.register_generators(z_image.registrations(backend))
     b.register_generators(sd3.registrations(backend))
     b.register_generators(qwen_image.registrations(backend))
+    b.register_generators(sdxl.registrations(backend))
     from .train import trainer_registration
 
     b.register("trainer", trainer_registration(backend))

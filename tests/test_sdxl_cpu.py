@@ -1,0 +1,90 @@
+"""SDXL: the UNet's block plan against the published model's geometry, building blocks against torch.nn modules, and
+provider conformance on a synthetic snapshot."""
+import pytest
+import torch
+import torch.nn as nn
+
+from inference_b200.models import unet_sdxl as U
+
+
+def test_plan_matches_the_published_geometry(monkeypatch):
+    cfg = U.SdxlUnetConfig()
+    down, up = U.unet_plan(cfg)
+    assert [(lvl, res, d, s) for lvl, res, d, s in down] == [
+        (0, [(320, 320), (320, 320)], 0, True), (1, [(320, 640), (640, 640)], 2, True),
+        (2, [(640, 1280), (1280, 1280)], 10, False)]
+    assert [res for _, res, _, _ in up] == [[(2560, 1280), (2560, 1280), (1920, 1280)], [(1920, 640), (1280, 640), (960, 640)],
+                                            [(960, 320), (640, 320), (640, 320)]]
+    count = {"n": 0}
+
+    def fake(*shape, generator=None, device=None):
+        count["n"] += int(torch.tensor(shape).prod())
+        return torch.zeros(1)
+    monkeypatch.setattr(torch, "randn", fake)
+    w = U.random_sdxl_unet_weights(cfg)
+    assert len(w) == 1680 and count["n"] == 2_567_463_684          # tensors and parameters of the SDXL base UNet
+    j = {"block_out_channels": [320, 640, 1280], "transformer_layers_per_block": [1, 2, 10], "attention_head_dim": [5, 10, 20],
+         "down_block_types": ["DownBlock2D", "CrossAttnDownBlock2D", "CrossAttnDownBlock2D"]}
+    assert U.SdxlUnetConfig.from_json(j) == cfg
+
+
+def test_blocks_match_torch_modules():
+    cfg = U.SdxlUnetConfig(block_out_channels=(16, 32), transformer_layers_per_block=(0, 1), attention_head_dim=8,
+                           cross_attention_dim=12, addition_time_embed_dim=4, projection_class_embeddings_input_dim=24 + 10,
+                           norm_groups=4)
+    w = U.random_sdxl_unet_weights(cfg, seed=2, std=0.2)
+    net = U.SdxlUnet(cfg, w)
+    g = torch.Generator().manual_seed(0)
+    # residual block
+    x, emb = torch.randn(2, 16, 6, 5, generator=g), torch.randn(2, 64, generator=g)
+    p = "down_blocks.1.resnets.0"
+    n1, n2 = nn.GroupNorm(4, 16, eps=1e-5), nn.GroupNorm(4, 32, eps=1e-5)
+    c1, c2, sc, tp = nn.Conv2d(16, 32, 3, padding=1), nn.Conv2d(32, 32, 3, padding=1), nn.Conv2d(16, 32, 1), nn.Linear(64, 32)
+    for m, k in ((n1, "norm1"), (n2, "norm2"), (c1, "conv1"), (c2, "conv2"), (sc, "conv_shortcut"), (tp, "time_emb_proj")):
+        m.load_state_dict({"weight": w[f"{p}.{k}.weight"], "bias": w[f"{p}.{k}.bias"]})
+    act = nn.SiLU()
+    with torch.no_grad():
+        h = c1(act(n1(x))) + tp(act(emb))[:, :, None, None]
+        ref = sc(x) + c2(act(n2(h)))
+    torch.testing.assert_close(net._resnet(x, p, torch.nn.functional.silu(emb)), ref, atol=1e-5, rtol=1e-5)
+    # cross-attention against nn.MultiheadAttention (separate projection weights, no input bias)
+    b = "down_blocks.1.attentions.0.transformer_blocks.0.attn2"
+    mha = nn.MultiheadAttention(32, 4, bias=True, kdim=12, vdim=12, batch_first=True)
+    mha.load_state_dict({"q_proj_weight": w[b + ".to_q.weight"], "k_proj_weight": w[b + ".to_k.weight"],
+                         "v_proj_weight": w[b + ".to_v.weight"], "in_proj_bias": torch.zeros(96),
+                         "out_proj.weight": w[b + ".to_out.0.weight"], "out_proj.bias": w[b + ".to_out.0.bias"]})
+    q, ctx = torch.randn(2, 9, 32, generator=g), torch.randn(2, 7, 12, generator=g)
+    with torch.no_grad():
+        ref = mha(q, ctx, ctx, need_weights=False)[0]
+    torch.testing.assert_close(net._attention(q, ctx, b), ref, atol=1e-5, rtol=1e-5)
+    # the whole network: shape, and dependence on timestep, context and the size numbers
+    args = dict(x=torch.randn(1, 4, 8, 12, generator=g), timestep=torch.tensor([400.0]), context=torch.randn(1, 7, 12, generator=g),
+                pooled=torch.randn(1, 10, generator=g), time_ids=torch.tensor([[64.0, 96, 0, 0, 64, 96]]))
+    base = net.forward(**args)
+    assert base.shape == (1, 4, 8, 12)
+    for k, v in (("timestep", torch.tensor([10.0])), ("context", args["context"] * 0.5),
+                 ("time_ids", torch.tensor([[512.0, 512, 0, 0, 64, 96]]))):
+        assert (net.forward(**{**args, k: v}) - base).abs().max() > 1e-5
+
+
+def test_sdxl_provider_conforms(tmp_path):
+    from inference_b200.contracts.errors import InferenceError
+    from inference_b200.contracts.gen_core import GenerationRequest, LoadSpec
+    from inference_b200.media import provider_registry
+    from inference_b200.media.sdxl import write_synthetic_snapshot
+    from inference_b200.testkit import generator as kit
+
+    snap = write_synthetic_snapshot(tmp_path / "sdxl")
+    reg = provider_registry("cpu")
+    assert "cpu_sdxl" in reg.ids() and reg.descriptor_conformance_errors() == []
+    gen = reg.load("cpu_sdxl", LoadSpec.from_dir(snap))
+    kit.conformance(gen, kit.Profile(steps=2, cancel_steps=5))
+    kit.registry_conformance(reg, "cpu_sdxl", LoadSpec.from_dir(snap))
+    req = dict(prompt="a red fox", width=256, height=256, steps=2, seed=5)
+    a = gen.generate(GenerationRequest(**req, guidance=1.0)).images[0].pixels
+    b = gen.generate(GenerationRequest(**req)).images[0].pixels
+    c = gen.generate(GenerationRequest(**req, guidance=7.0, negative_prompt="", sampler="ddim", scheduler="normal")).images[0].pixels
+    d = gen.generate(GenerationRequest(**req, sampler="euler_ancestral", scheduler="karras")).images[0].pixels
+    assert b == c and a != b and d != b and len(a) == 256 * 256 * 3
+    with pytest.raises(InferenceError):
+        gen.generate(GenerationRequest(**{**req, "width": 264}))
