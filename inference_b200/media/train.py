@@ -257,6 +257,88 @@ def z_image_trainer_registration(backend: str):
     return Registration(descriptor=lambda: SimpleDescriptor(tid, "z-image", backend, {"adapters": ["lora"]}), load=load)
 
 
+SDXL_TARGETS = ("attn1.to_q", "attn1.to_k", "attn1.to_v", "attn1.to_out.0", "attn2.to_q", "attn2.to_k", "attn2.to_v",
+                "attn2.to_out.0")
+
+
+class SdxlLoraTrainer(FluxLoraTrainer):
+    """The same loop on the SDXL UNet with the noise-prediction objective (candle-gen-sdxl/src/training.rs): adapters on
+    the attention projections of every transformer block; the loop's t in (0, 1) picks the DDPM timestep round(999 t),
+    x_t = sqrt(a) x0 + sqrt(1 - a) eps with a the cumulative alpha of the scaled-linear table, loss || eps_theta - eps ||^2.
+    Items hold `latent` [4, h, w] (scaled VAE latents), `txt` [77, 2048] and `pooled` [1280]; adapter files use the
+    `unet.` prefix."""
+    family, target_suffixes, item_keys = "sdxl", SDXL_TARGETS, ("latent", "txt", "pooled")
+
+    def __init__(self, cfg, weights: dict[str, torch.Tensor], backend: str = "cpu", device="cpu"):
+        from ..contracts.gen_core.sampling.policy import AlphaSchedule
+        from ..models.unet_sdxl import SdxlUnet
+
+        self.cfg, self.backend, self.device = cfg, backend, torch.device(device)
+        self.model = SdxlUnet(cfg, weights, dtype=torch.float32, device=self.device)
+        for t in self.model.w.values():
+            t.requires_grad_(False)
+        self.alphas = AlphaSchedule.scaled_linear().alphas_cumprod
+
+    def descriptor(self) -> SimpleDescriptor:
+        return SimpleDescriptor("sdxl_lora_trainer" if self.backend != "cpu" else "cpu_sdxl_lora_trainer", "sdxl",
+                                self.backend, {"adapters": ["lora"], "targets": list(SDXL_TARGETS)})
+
+    def loss_on(self, item, t: float, noise: torch.Tensor) -> torch.Tensor:
+        step = min(len(self.alphas) - 1, max(0, round(t * (len(self.alphas) - 1))))
+        a = self.alphas[step]
+        x0, eps = item["latent"][None], noise[None]
+        xt = math.sqrt(a) * x0 + math.sqrt(1.0 - a) * eps
+        h, w = x0.shape[2] * 8, x0.shape[3] * 8
+        ids = torch.tensor([[h, w, 0, 0, h, w]], dtype=torch.float32, device=self.device)
+        out = self.model.forward_grad(xt, torch.full((1,), float(step), device=self.device), item["txt"][None],
+                                      item["pooled"][None], ids)
+        return torch.mean((out - eps) ** 2)
+
+    def _save(self, path: Path, adapters, c: TrainingConfig, step: int, opt, gen) -> Path:
+        out = super()._save(path, adapters, c, step, opt, gen)
+        t = load_file(out)                                    # the UNet's adapter files carry the `unet.` prefix
+        save_file({k.replace("transformer.", "unet.", 1): v for k, v in t.items()}, out,
+                  metadata={"format": "peft-lora", "rank": str(c.rank), "alpha": str(c.alpha), "step": str(step),
+                            "base": self.family})
+        return out
+
+    def _load_checkpoint(self, path: Path, adapters, opt, gen) -> int:
+        t = load_file(path)
+        tmp = path.with_name(path.stem + ".resume.safetensors")
+        save_file({k.replace("unet.", "transformer.", 1): v for k, v in t.items()}, tmp)
+        state = path.with_suffix(".state.safetensors")
+        tmp_state = tmp.with_suffix(".state.safetensors")
+        tmp_state.write_bytes(state.read_bytes())
+        try:
+            return super()._load_checkpoint(tmp, adapters, opt, gen)
+        finally:
+            tmp.unlink(missing_ok=True)
+            tmp_state.unlink(missing_ok=True)
+
+
+def sdxl_trainer_registration(backend: str):
+    """`sdxl_lora_trainer` (kind "trainer"): loads the UNet of an SDXL snapshot directory."""
+    from ..contracts.gen_core.registry import Registration
+    from ..contracts.gen_core.runtime import LoadSpec
+
+    tid = "sdxl_lora_trainer" if backend != "cpu" else "cpu_sdxl_lora_trainer"
+
+    def load(spec: LoadSpec) -> SdxlLoraTrainer:
+        from ..io.safetensors_io import load_dir
+        from .sdxl import SdxlPipeline
+
+        if spec.weights is None or spec.weights.is_file:
+            raise InferenceError(f"{tid}: needs a snapshot directory")
+        root = Path(spec.weights.path)
+        device = torch.device("cuda", torch.cuda.current_device()) if backend != "cpu" else torch.device("cpu")
+        if not (root / "unet").is_dir():
+            raise LoadError(f"{tid}: missing {root / 'unet'}")
+        pipe = SdxlPipeline(root, "cpu", device)
+        return SdxlLoraTrainer(pipe.unet_cfg, load_dir(root / "unet"), backend, device)
+
+    return Registration(descriptor=lambda: SimpleDescriptor(tid, "sdxl", backend, {"adapters": ["lora"]}), load=load)
+
+
 def trainer_registration(backend: str):
     """`flux1_lora_trainer` (kind "trainer"): loads the DiT of a FLUX snapshot directory and trains adapters on it."""
     from ..contracts.gen_core.registry import Registration

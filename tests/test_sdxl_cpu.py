@@ -88,3 +88,55 @@ def test_sdxl_provider_conforms(tmp_path):
     assert b == c and a != b and d != b and len(a) == 256 * 256 * 3
     with pytest.raises(InferenceError):
         gen.generate(GenerationRequest(**{**req, "width": 264}))
+
+
+def test_sdxl_trainer_and_adapter_round_trip(tmp_path):
+    from inference_b200.contracts.gen_core import (AdapterKind, AdapterSpec, GenerationRequest, LoadSpec, TrainingConfig,
+                                                   WeightsSource)
+    from inference_b200.io.safetensors_io import load_file, save_file
+    from inference_b200.media import provider_registry
+    from inference_b200.media.sdxl import write_synthetic_snapshot
+    from inference_b200.media.train import SDXL_TARGETS
+    from inference_b200.testkit.aux_suites import TrainerProfile, trainer_conformance
+
+    snap = write_synthetic_snapshot(tmp_path / "sdxl")
+    ds = tmp_path / "ds"
+    ds.mkdir()
+    g = torch.Generator().manual_seed(0)
+    for i in range(2):
+        save_file({"latent": torch.randn(4, 8, 8, generator=g), "txt": torch.randn(9, 64, generator=g),
+                   "pooled": torch.randn(32, generator=g)}, ds / f"item{i}.safetensors")
+    reg = provider_registry("cpu")
+    tr = reg.load_kind("trainer", "cpu_sdxl_lora_trainer", LoadSpec.from_dir(snap))
+    items = tr._items(ds)
+    noise = torch.randn(4, 8, 8, generator=torch.Generator().manual_seed(9))
+    before = float(tr.loss_on(items[0], 0.5, noise))
+    cfg = TrainingConfig(dataset_dir=ds, output_dir=tmp_path / "run", steps=10, learning_rate=5e-3, rank=4, alpha=4.0, seed=3,
+                         save_every=5)
+    final = tr.train(cfg, lambda p: None)
+    ad = load_file(final)
+    assert all(k.startswith("unet.") and k.split(".lora_")[0].endswith(SDXL_TARGETS) for k in ad)
+    # resume from the step-5 checkpoint reproduces the straight run
+    tr2 = reg.load_kind("trainer", "cpu_sdxl_lora_trainer", LoadSpec.from_dir(snap))
+    final2 = tr2.train(TrainingConfig(dataset_dir=ds, output_dir=tmp_path / "run2", steps=10, learning_rate=5e-3, rank=4,
+                                      alpha=4.0, seed=3, resume=tmp_path / "run" / "adapter-step000005.safetensors"),
+                       lambda p: None)
+    ad2 = load_file(final2)
+    assert all(torch.equal(ad[k], ad2[k]) for k in ad)
+    tr.model.lora = {k[len("unet."):-len(".lora_A.weight")]: (ad[k], ad[k.replace("lora_A", "lora_B")], 1.0)
+                     for k in ad if k.endswith("lora_A.weight")}
+    assert float(tr.loss_on(items[0], 0.5, noise)) < before
+    tr.model.lora = None
+    big = {k: v * (30.0 if "lora_B" in k else 1.0) for k, v in ad.items()}
+    save_file(big, tmp_path / "big.safetensors")
+    req = lambda: GenerationRequest(prompt="a fox", width=256, height=256, steps=1, seed=2)      # noqa: E731
+
+    def run(scale):
+        spec = LoadSpec(weights=WeightsSource.dir(snap),
+                        adapters=[] if scale is None else [AdapterSpec(path=tmp_path / "big.safetensors", scale=scale,
+                                                                       kind=AdapterKind.LORA)])
+        return reg.load("cpu_sdxl", spec).generate(req(), lambda e: None).images[0].pixels
+    plain = run(None)
+    assert run(0.0) == plain and run(1.0) != plain
+    trainer_conformance(reg.load_kind("trainer", "cpu_sdxl_lora_trainer", LoadSpec.from_dir(snap)),
+                        TrainerProfile(ds, tmp_path / "out", steps=3, rank=2))
