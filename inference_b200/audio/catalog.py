@@ -74,10 +74,27 @@ def _clap_registration(backend: str) -> Registration:
                         load)
 
 
+OPENVOICE_LICENSE = WeightLicense("MIT", "MIT License", "https://huggingface.co/myshell-ai/OpenVoiceV2", "MyShell", True)
+
+
+def _openvoice_registration(backend: str) -> Registration:
+    def load(spec: LoadSpec):
+        from ..contracts.errors import LoadError
+        from .openvoice import OpenVoiceConverter, OpenVoiceTransform, load_checkpoint
+
+        if spec.weights is None:
+            raise LoadError("openvoice_v2: the load spec needs the converter checkpoint (a file or its directory)")
+        return OpenVoiceTransform(OpenVoiceConverter(load_checkpoint(spec.weights.path), "cuda" if backend == "b200" else "cpu"),
+                                  backend)
+
+    return Registration(lambda: SimpleDescriptor("openvoice_v2", "openvoice", backend, {"sample_rate": 22_050}), load)
+
+
 def register_providers(b: ProviderRegistryBuilder, backend: str) -> ProviderRegistryBuilder:
     b.register("transcriber", _whisper_registration(backend))
     b.register("voice_embedder", _chatterbox_ve_registration(backend))
     b.register("audio_embedder", _clap_registration(backend))
+    b.register("audio_transform", _openvoice_registration(backend))
     return b
 
 
@@ -87,7 +104,7 @@ def provider_registry(backend: str = "b200") -> ProviderRegistry:
 
 def weight_licenses() -> list[WeightLicenseEntry]:
     return [WeightLicenseEntry("whisper", WHISPER_LICENSE), WeightLicenseEntry("chatterbox_ve", CHATTERBOX_LICENSE),
-            WeightLicenseEntry("clap_htsat_unfused", CLAP_LICENSE)]
+            WeightLicenseEntry("clap_htsat_unfused", CLAP_LICENSE), WeightLicenseEntry("openvoice_v2", OPENVOICE_LICENSE)]
 
 
 def weight_licenses_manifest() -> str:
