@@ -113,6 +113,34 @@ def convert_diffusers_vae_decoder(sd: dict[str, torch.Tensor], levels: int = 4) 
     return out
 
 
+def convert_diffusers_vae_encoder(sd: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+    """AutoencoderKL encoder keys in diffusers naming -> the latent-diffusion naming of `OracleVaeEncoder`."""
+    out = {}
+    attn = {"group_norm": "norm", "to_q": "q", "to_k": "k", "to_v": "v", "to_out.0": "proj_out"}
+    for k, v in sd.items():
+        if not k.startswith("encoder."):
+            continue
+        r = k[len("encoder."):]
+        if r.startswith("conv_norm_out."):
+            nk = "norm_out." + r[len("conv_norm_out."):]
+        elif r.startswith("mid_block.resnets."):
+            i, rest = r[len("mid_block.resnets."):].split(".", 1)
+            nk = f"mid.block_{int(i) + 1}.{rest}"
+        elif r.startswith("mid_block.attentions.0."):
+            name, leaf = r[len("mid_block.attentions.0."):].rsplit(".", 1)
+            nk = f"mid.attn_1.{attn[name]}.{leaf}"
+            if leaf == "weight" and name != "group_norm" and v.dim() == 2:
+                v = v[:, :, None, None]
+        elif r.startswith("down_blocks."):
+            lvl, rest = r[len("down_blocks."):].split(".", 1)
+            nk = f"down.{lvl}.block.{rest[len('resnets.'):]}" if rest.startswith("resnets.") else \
+                f"down.{lvl}.downsample.conv.{rest[len('downsamplers.0.conv.'):]}"
+        else:
+            nk = r
+        out["encoder." + nk.replace("conv_shortcut", "nin_shortcut")] = v
+    return out
+
+
 class T5OnlyEncoder:
     """T5 without padding: one row per prompt token plus the end-of-sequence token."""
 

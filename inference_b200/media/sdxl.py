@@ -86,6 +86,17 @@ class HashDualEncoders:
 class _Heavy:
     unet: Any
     vae: Any
+    post_quant: tuple[torch.Tensor, torch.Tensor] | None = None      # the autoencoder's 1x1 convolution in front of the decoder
+
+
+def apply_post_quant(z: torch.Tensor, post_quant, cfg: VaeConfig) -> torch.Tensor:
+    """The decoders compute conv_in(z / scale + shift); a checkpoint with `post_quant_conv` wants
+    conv_in(pq(z / scale + shift)). Returns z' with z' / scale + shift == pq(z / scale + shift)."""
+    if post_quant is None:
+        return z
+    w, b = post_quant
+    u = torch.nn.functional.conv2d(z.float() / cfg.scale_factor + cfg.shift_factor, w.float().to(z.device), b.float().to(z.device))
+    return (u - cfg.shift_factor) * cfg.scale_factor
 
 
 class SdxlPipeline:
@@ -126,6 +137,7 @@ class SdxlPipeline:
         from ..models.vae import random_vae_weights
 
         gpu = self.backend == "b200"
+        pq = None
         if self.random_init is not None and gpu:
             seed = int(self.random_init)
             unet_w = random_sdxl_unet_weights(self.unet_cfg, seed, 0.02, torch.bfloat16, self.device)
@@ -141,13 +153,16 @@ class SdxlPipeline:
                 if not Path(ad.path).is_file():
                     raise LoadError(f"{MODEL_ID}: adapter file {ad.path} not found")
                 unet_w = merge_lora(unet_w, load_file(ad.path), ad.scale if ad.scale is not None else 1.0, prefix="unet.")
-            vae_w = convert_diffusers_vae_decoder(load_dir(self.root / "vae"), len(self.vae_cfg.ch_mult))
+            raw_vae = load_dir(self.root / "vae")
+            vae_w = convert_diffusers_vae_decoder(raw_vae, len(self.vae_cfg.ch_mult))
+            if "post_quant_conv.weight" in raw_vae:
+                pq = (raw_vae["post_quant_conv.weight"], raw_vae["post_quant_conv.bias"])
         unet = SdxlUnet(self.unet_cfg, unet_w, self.dtype, self.device)
         if gpu:
             from ..models.vae import VaeDecoderGpu
 
-            return _Heavy(unet, VaeDecoderGpu(self.vae_cfg, self.device).load_state_dict(vae_w))
-        return _Heavy(unet, OracleVaeDecoder(self.vae_cfg, vae_w, device=self.device))
+            return _Heavy(unet, VaeDecoderGpu(self.vae_cfg, self.device).load_state_dict(vae_w), pq)
+        return _Heavy(unet, OracleVaeDecoder(self.vae_cfg, vae_w, device=self.device), pq)
 
     @staticmethod
     def guidance(req: GenerationRequest) -> float:
@@ -196,7 +211,7 @@ class SdxlPipeline:
             if req.cancel.is_cancelled():
                 raise Canceled(f"{MODEL_ID}: cancelled before decode")
             on_progress(ProgressDecoding())
-            z = x.float()
+            z = apply_post_quant(x.float(), heavy.post_quant, self.vae_cfg)
             if self.backend == "b200":
                 host = heavy.vae.decode_rgb8(z)[0].cpu()
             else:
@@ -292,9 +307,11 @@ def write_synthetic_snapshot(root, seed: int = 0) -> Path:
     (root / "vae").mkdir(exist_ok=True)
     save_file({k: v.bfloat16() for k, v in random_sdxl_unet_weights(unet, seed).items()},
               root / "unet" / "diffusion_pytorch_model.safetensors")
-    save_file({k: v.bfloat16() for k, v in native_vae_to_diffusers(random_vae_weights(vae, seed + 1),
-                                                                   len(vae.ch_mult)).items()},
-              root / "vae" / "diffusion_pytorch_model.safetensors")
+    vae_sd = {k: v.bfloat16() for k, v in native_vae_to_diffusers(random_vae_weights(vae, seed + 1), len(vae.ch_mult)).items()}
+    g = torch.Generator().manual_seed(seed + 2)
+    vae_sd["post_quant_conv.weight"] = (torch.eye(4).view(4, 4, 1, 1) + 0.2 * torch.randn(4, 4, 1, 1, generator=g)).bfloat16()
+    vae_sd["post_quant_conv.bias"] = (0.1 * torch.randn(4, generator=g)).bfloat16()
+    save_file(vae_sd, root / "vae" / "diffusion_pytorch_model.safetensors")
     (root / "swb_config.json").write_text(json.dumps({
         "unet": {"block_out_channels": list(unet.block_out_channels),
                  "transformer_layers_per_block": list(unet.transformer_layers_per_block),

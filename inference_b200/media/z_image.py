@@ -20,8 +20,8 @@ from typing import Any, Callable
 import torch
 
 from ..contracts.errors import Canceled, InferenceError, LoadError, Unsupported
-from ..contracts.gen_core.generator import (Capabilities, GenerationOutput, GenerationRequest, Generator, Modality,
-                                            ModelDescriptor)
+from ..contracts.gen_core.generator import (Capabilities, ConditioningKind, GenerationOutput, GenerationRequest, Generator,
+                                            Modality, ModelDescriptor)
 from ..contracts.gen_core.media import Image
 from ..contracts.gen_core.registry import Registration
 from ..contracts.gen_core.runtime import AdapterKind, LoadSpec, OffloadPolicy, ProgressDecoding, ProgressStep
@@ -31,7 +31,7 @@ from ..contracts.gen_core.tokenizer import PromptTemplate, TextTokenizer, Tokeni
 from ..contracts.gen_core.traits import reject_unknown_components
 from ..models.dit_zimage import OracleZImageDiT, ZImageConfig
 from ..models.vae import OracleVaeDecoder, VaeConfig
-from .chroma import convert_diffusers_vae_decoder, native_vae_to_diffusers
+from .chroma import convert_diffusers_vae_decoder, convert_diffusers_vae_encoder, native_vae_to_diffusers
 from .flux import SIZE_MULTIPLE
 from .residency import Residency
 from .seed import default_seed, for_each_image_seed, seeded_noise_nchw
@@ -67,6 +67,24 @@ def flow_match_sigmas(steps: int, shift: float, apply_shift: bool) -> list[float
     if apply_shift:
         ramp = [shift * s / (1.0 + (shift - 1.0) * s) for s in ramp]
     return ramp + [0.0]
+
+
+def init_time_step(steps: int, strength: float | None) -> int:
+    """Where a reference-guided run enters the schedule: max(1, floor(steps * strength)) for a strength in (0, 1], 0
+    (plain text-to-image) otherwise. A higher strength starts later and keeps more of the reference."""
+    if strength is None or not strength > 0.0:
+        return 0
+    return max(1, min(steps - 1, int(steps * min(strength, 1.0)))) if steps > 1 else 0
+
+
+def reference_of(req: GenerationRequest):
+    """(image, strength) of the request's single REFERENCE conditioning, or None."""
+    refs = [c for c in req.conditioning if c.kind is ConditioningKind.REFERENCE]
+    if not refs:
+        return None
+    if len(refs) > 1 or refs[0].image is None:
+        raise InferenceError("z-image: exactly one reference image is supported")
+    return refs[0].image, refs[0].strength
 
 
 def z_image_sigmas(variant: ZImageVariant, steps: int) -> list[float]:
@@ -169,6 +187,23 @@ class ZImagePipeline:
         return _Heavy(OracleZImageDiT(self.dit_cfg, dit_w, device=self.device),
                       OracleVaeDecoder(self.vae_cfg, vae_w, device=self.device))
 
+    def encode_reference(self, image: Image, width: int, height: int) -> torch.Tensor:
+        """Reference image -> clean latents [1, 16, h/8, w/8] (the autoencoder's mean; fp32 encoder, loaded on demand)."""
+        import numpy as np
+
+        from ..contracts.gen_core.imageops import resize
+        from ..io.safetensors_io import load_dir
+        from ..models.vae import OracleVaeEncoder
+
+        enc_w = convert_diffusers_vae_encoder(load_dir(self.root / "vae"))
+        if "encoder.conv_in.weight" not in enc_w:
+            raise LoadError(f"{self.variant.value}: the snapshot's vae/ has no encoder, which a reference image needs")
+        if (image.width, image.height) != (width, height):
+            image = resize(image, width, height, "lanczos")
+        px = torch.from_numpy(np.frombuffer(bytes(image.pixels), dtype=np.uint8).reshape(height, width, 3).copy())
+        x = (px.permute(2, 0, 1)[None].float() / 127.5 - 1.0)
+        return OracleVaeEncoder(self.vae_cfg, enc_w, device=self.device).encode(x).float()
+
     def guidance(self, req: GenerationRequest) -> float | None:
         if self.variant is ZImageVariant.TURBO:
             return None
@@ -193,6 +228,12 @@ class ZImagePipeline:
             sigmas = native
         else:
             sigmas = schedule_sigmas(req.scheduler, FlowModelSampling(mu=req.scheduler_shift or 0.0), steps)
+        ref = reference_of(req)
+        clean, start = None, 0
+        if ref is not None and init_time_step(steps, ref[1]) > 0:
+            start = min(init_time_step(steps, ref[1]), len(sigmas) - 2)
+            clean = self.encode_reference(ref[0], req.width, req.height).to(dev)
+            sigmas = sigmas[start:]                    # the run enters the schedule at sigma_start
         solver, ops, ms = get_solver(req.sampler or "euler"), TorchLatentOps(), FlowModelSampling()
         gpu = self.backend == "b200"
         p = self.dit_cfg.patch_size
@@ -208,8 +249,13 @@ class ZImagePipeline:
                 caps.append((emb.to(dev, dt), None))
 
         def one_image(seed: int) -> Image:
-            x = seeded_noise_nchw(seed, self.vae_cfg.z_channels, lh, lw).to(dev, dt).contiguous()
-            state = {"step": 0}
+            x = seeded_noise_nchw(seed, self.vae_cfg.z_channels, lh, lw).to(dev)
+            if clean is not None:                       # x_t = (1 - sigma) clean + sigma noise at the entry point
+                x = (1.0 - sigmas[0]) * clean + sigmas[0] * x.float()
+            x = x.to(dt).contiguous()
+            state = {"step": start}
+            for s_done in range(1, start + 1):
+                on_progress(ProgressStep(s_done, steps))
 
             def run_model(x_in, sigma):
                 if req.cancel.is_cancelled():
@@ -248,7 +294,8 @@ def z_image_descriptor(variant: ZImageVariant, backend: str, prefix: str = "") -
     return ModelDescriptor(
         id=prefix + variant.value, family="z-image", backend=backend, modality=Modality.IMAGE,
         capabilities=Capabilities(
-            supports_negative_prompt=cfg, supports_guidance=cfg, supports_true_cfg=cfg, conditioning=[],
+            supports_negative_prompt=cfg, supports_guidance=cfg, supports_true_cfg=cfg,
+            conditioning=[ConditioningKind.REFERENCE],
             supports_lora=True, supports_lokr=False, samplers=list(SOLVERS), schedulers=list(SCHEDULERS),
             supported_guidance_methods=[], min_size=256, max_size=2048, max_count=8,
             supports_sequential_offload=True),
@@ -329,9 +376,11 @@ def write_synthetic_snapshot(root, seed: int = 0, text: str = "hash", te_head_di
     (root / "vae").mkdir(exist_ok=True)
     save_file({k: v.bfloat16() for k, v in random_zimage_weights(dit, seed).items()},
               root / "transformer" / "diffusion_pytorch_model.safetensors")
-    save_file({k: v.bfloat16() for k, v in native_vae_to_diffusers(random_vae_weights(vae, seed + 1),
-                                                                   len(vae.ch_mult)).items()},
-              root / "vae" / "diffusion_pytorch_model.safetensors")
+    from ..models.vae import random_vae_encoder_weights
+
+    vae_sd = native_vae_to_diffusers(random_vae_weights(vae, seed + 1), len(vae.ch_mult))
+    vae_sd.update(native_vae_encoder_to_diffusers(random_vae_encoder_weights(vae, seed + 3)))
+    save_file({k: v.bfloat16() for k, v in vae_sd.items()}, root / "vae" / "diffusion_pytorch_model.safetensors")
     (root / "swb_config.json").write_text(json.dumps({
         "dit": {"dim": dit.dim, "n_layers": dit.n_layers, "n_refiner_layers": dit.n_refiner_layers,
                 "n_heads": dit.n_heads, "cap_feat_dim": dit.cap_feat_dim},
@@ -339,6 +388,32 @@ def write_synthetic_snapshot(root, seed: int = 0, text: str = "hash", te_head_di
     if text == "qwen3":
         _write_synthetic_qwen3(root, cap_dim, te_head_dim, seed + 2)
     return root
+
+
+def native_vae_encoder_to_diffusers(sd: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+    """Inverse of convert_diffusers_vae_encoder (synthetic snapshots)."""
+    out = {}
+    attn = {"norm": "group_norm", "q": "to_q", "k": "to_k", "v": "to_v", "proj_out": "to_out.0"}
+    for k, v in sd.items():
+        r = k[len("encoder."):]
+        if r.startswith("norm_out."):
+            nk = "conv_norm_out." + r[len("norm_out."):]
+        elif r.startswith("mid.block_"):
+            i, rest = r[len("mid.block_"):].split(".", 1)
+            nk = f"mid_block.resnets.{int(i) - 1}.{rest}"
+        elif r.startswith("mid.attn_1."):
+            name, leaf = r[len("mid.attn_1."):].rsplit(".", 1)
+            nk = f"mid_block.attentions.0.{attn[name]}.{leaf}"
+            if leaf == "weight" and name != "norm":
+                v = v.reshape(v.shape[0], v.shape[1])
+        elif r.startswith("down."):
+            lvl, rest = r[len("down."):].split(".", 1)
+            nk = f"down_blocks.{lvl}.resnets.{rest[len('block.'):]}" if rest.startswith("block.") else \
+                f"down_blocks.{lvl}.downsamplers.0.conv.{rest[len('downsample.conv.'):]}"
+        else:
+            nk = r
+        out["encoder." + nk.replace("nin_shortcut", "conv_shortcut")] = v
+    return out
 
 
 def _write_synthetic_qwen3(root: Path, hidden: int, head_dim: int, seed: int) -> None:

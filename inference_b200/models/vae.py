@@ -116,6 +116,68 @@ class OracleVaeDecoder:
         return self._conv(self._gn(h, "decoder.norm_out", True), "decoder.conv_out", 1)
 
 
+def random_vae_encoder_weights(cfg: VaeConfig, seed: int = 0, std: float = 0.05) -> dict[str, torch.Tensor]:
+    """Random encoder tensors under the `encoder.*` names of the latent-diffusion layout."""
+    g = torch.Generator().manual_seed(seed)
+    w: dict[str, torch.Tensor] = {}
+
+    def conv(name, cout, cin, k):
+        w[name + ".weight"] = torch.randn(cout, cin, k, k, generator=g) * std / (k * (cin ** 0.5) / 4)
+        w[name + ".bias"] = torch.randn(cout, generator=g) * 0.01
+
+    def norm(name, c):
+        w[name + ".weight"], w[name + ".bias"] = 1 + 0.1 * torch.randn(c, generator=g), 0.05 * torch.randn(c, generator=g)
+
+    def res(name, cin, cout):
+        norm(name + ".norm1", cin)
+        conv(name + ".conv1", cout, cin, 3)
+        norm(name + ".norm2", cout)
+        conv(name + ".conv2", cout, cout, 3)
+        if cin != cout:
+            conv(name + ".nin_shortcut", cout, cin, 1)
+
+    conv("encoder.conv_in", cfg.ch, 3, 3)
+    block_in = cfg.ch
+    for lvl, m in enumerate(cfg.ch_mult):
+        for i in range(cfg.num_res_blocks):
+            res(f"encoder.down.{lvl}.block.{i}", block_in, cfg.ch * m)
+            block_in = cfg.ch * m
+        if lvl != len(cfg.ch_mult) - 1:
+            conv(f"encoder.down.{lvl}.downsample.conv", block_in, block_in, 3)
+    res("encoder.mid.block_1", block_in, block_in)
+    norm("encoder.mid.attn_1.norm", block_in)
+    for n in ("q", "k", "v", "proj_out"):
+        conv(f"encoder.mid.attn_1.{n}", block_in, block_in, 1)
+    res("encoder.mid.block_2", block_in, block_in)
+    norm("encoder.norm_out", block_in)
+    conv("encoder.conv_out", 2 * cfg.z_channels, block_in, 3)
+    return w
+
+
+class OracleVaeEncoder(OracleVaeDecoder):
+    """Image -> latent mean (the deterministic encode used for reference-guided generation and for caching training
+    latents): strided convolutions with (0, 1, 0, 1) padding between levels, the same residual / attention blocks as the
+    decoder, the first half of `conv_out`'s channels is the mean; the stored latent is (mean - shift) * scale."""
+
+    @torch.no_grad()
+    def encode(self, image: torch.Tensor) -> torch.Tensor:
+        """image [B, 3, H, W] in [-1, 1] -> scaled latents [B, z, H/8.., W/8..]."""
+        cfg = self.cfg
+        dev = next(iter(self.w.values()))
+        h = self._conv(image.to(dev.device, dev.dtype), "encoder.conv_in", 1)
+        for lvl in range(len(cfg.ch_mult)):
+            for i in range(cfg.num_res_blocks):
+                h = self._res(h, f"encoder.down.{lvl}.block.{i}")
+            if lvl != len(cfg.ch_mult) - 1:
+                n = f"encoder.down.{lvl}.downsample.conv"
+                h = F.conv2d(F.pad(h, (0, 1, 0, 1)), self.w[n + ".weight"], self.w[n + ".bias"], stride=2)
+        h = self._res(h, "encoder.mid.block_1")
+        h = self._attn(h, "encoder.mid.attn_1")
+        h = self._res(h, "encoder.mid.block_2")
+        moments = self._conv(self._gn(h, "encoder.norm_out", True), "encoder.conv_out", 1)
+        return (moments[:, : cfg.z_channels] - cfg.shift_factor) * cfg.scale_factor
+
+
 class VaeDecoderGpu:
     def __init__(self, cfg: VaeConfig, device: torch.device | None = None):
         self.cfg = cfg

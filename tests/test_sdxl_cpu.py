@@ -140,3 +140,16 @@ def test_sdxl_trainer_and_adapter_round_trip(tmp_path):
     assert run(0.0) == plain and run(1.0) != plain
     trainer_conformance(reg.load_kind("trainer", "cpu_sdxl_lora_trainer", LoadSpec.from_dir(snap)),
                         TrainerProfile(ds, tmp_path / "out", steps=3, rank=2))
+
+
+def test_post_quant_convolution_is_applied_in_front_of_the_decoder():
+    from inference_b200.media.sdxl import VAE_SCALE, apply_post_quant
+    from inference_b200.models.vae import VaeConfig
+
+    cfg = VaeConfig(z_channels=4, scale_factor=VAE_SCALE, shift_factor=0.25)
+    g = torch.Generator().manual_seed(0)
+    w, b, z = torch.randn(4, 4, 1, 1, generator=g), torch.randn(4, generator=g), torch.randn(1, 4, 5, 6, generator=g)
+    out = apply_post_quant(z, (w, b), cfg)
+    want = torch.nn.functional.conv2d(z / VAE_SCALE + 0.25, w, b)
+    torch.testing.assert_close(out / VAE_SCALE + 0.25, want, atol=1e-5, rtol=1e-5)
+    assert apply_post_quant(z, None, cfg) is z

@@ -197,3 +197,35 @@ def test_z_image_trainer_and_adapter_round_trip(tmp_path):
     assert run(0.0) == plain and run(1.0) != plain
     trainer_conformance(reg.load_kind("trainer", "cpu_z_image_lora_trainer", LoadSpec.from_dir(snap)),
                         TrainerProfile(ds, tmp_path / "out", steps=3, rank=2))
+
+
+def test_reference_guided_generation(tmp_path):
+    from inference_b200.contracts.gen_core import GenerationRequest, LoadSpec
+    from inference_b200.contracts.gen_core.generator import Conditioning, ConditioningKind
+    from inference_b200.contracts.gen_core.media import Image
+    from inference_b200.media import provider_registry
+    from inference_b200.media.chroma import convert_diffusers_vae_encoder
+    from inference_b200.media.z_image import init_time_step, native_vae_encoder_to_diffusers, write_synthetic_snapshot
+    from inference_b200.models.vae import VaeConfig, random_vae_encoder_weights
+
+    assert [init_time_step(28, s) for s in (None, 0.0, -1.0, 0.5, 0.01, 1.0)] == [0, 0, 0, 14, 1, 27]
+    cfg = VaeConfig(ch=32, ch_mult=(1, 2, 2, 2), num_res_blocks=1)
+    native = random_vae_encoder_weights(cfg, 1)
+    back = convert_diffusers_vae_encoder(native_vae_encoder_to_diffusers(native))
+    assert back.keys() == native.keys() and all(torch.equal(back[k], native[k]) for k in native)
+    snap = write_synthetic_snapshot(tmp_path / "zi")
+    gen = provider_registry("cpu").load("cpu_z_image_turbo", LoadSpec.from_dir(snap))
+    g = torch.Generator().manual_seed(3)
+    ref = Image(width=200, height=120, pixels=bytes(torch.randint(0, 256, (120 * 200 * 3,), generator=g, dtype=torch.uint8).tolist()))
+    base = dict(prompt="a red fox", width=256, height=256, steps=4, seed=5)
+    events = []
+    plain = gen.generate(GenerationRequest(**base)).images[0].pixels
+    guided = gen.generate(GenerationRequest(**base, conditioning=[Conditioning(ConditioningKind.REFERENCE, image=ref, strength=0.5)]),
+                          events.append).images[0].pixels
+    again = gen.generate(GenerationRequest(**base, conditioning=[Conditioning(ConditioningKind.REFERENCE, image=ref, strength=0.5)])
+                         ).images[0].pixels
+    zero = gen.generate(GenerationRequest(**base, conditioning=[Conditioning(ConditioningKind.REFERENCE, image=ref, strength=0.0)])
+                        ).images[0].pixels
+    assert guided == again and guided != plain and zero == plain
+    steps = [e.current for e in events if hasattr(e, "current")]
+    assert steps == [1, 2, 3, 4]                     # the skipped head of the schedule is still reported
