@@ -81,12 +81,18 @@ class T5Encoder:
         pos = torch.arange(L, device=self.device)
         buckets = _t5_bucket(pos[None, :] - pos[:, None], cfg.relative_attention_num_buckets,
                              cfg.relative_attention_max_distance)
-        table = self.w["encoder.block.0.layer.0.SelfAttention.relative_attention_bias.weight"]      # [buckets, H]
-        bias = table[buckets].permute(2, 0, 1)[None].float()                                          # [1, H, L, L]
+        neg = None
         if mask is not None:
-            bias = bias + (1.0 - mask.to(self.device).float())[:, None, None, :] * torch.finfo(torch.float32).min
+            neg = (1.0 - mask.to(self.device).float())[:, None, None, :] * torch.finfo(torch.float32).min
+        bias = None
         for i in range(cfg.num_layers):
             p = f"encoder.block.{i}.layer"
+            # T5 shares the first layer's relative-position table; UMT5 stores one per layer
+            table = self.w.get(f"{p}.0.SelfAttention.relative_attention_bias.weight")                 # [buckets, H]
+            if table is not None:
+                bias = table[buckets].permute(2, 0, 1)[None].float()                                  # [1, H, L, L]
+                if neg is not None:
+                    bias = bias + neg
             h = self._norm(x, f"{p}.0.layer_norm.weight")
             q, k, v = (linear(h, self.w[f"{p}.0.SelfAttention.{n}.weight"]).view(B, L, H, D).transpose(1, 2)
                        for n in "qkv")
