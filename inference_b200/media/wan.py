@@ -1,0 +1,270 @@
+"""Wan 2.2 text-to-video provider `wan2_2_t2v_14b` (and `cpu_wan2_2_t2v_14b` on the fp32 backend)
+(parity: candle-gen-wan/src/wan14b.rs, pipeline.rs, scheduler.rs, text_encode.rs, config.rs).
+
+generate(): UMT5 encodes the prompt (512 positions; rows past the prompt's length are zeroed) -> flow-matching steps
+over `sigma = shift * s / (1 + (shift - 1) * s)`, s from 1 to 1 / 1000, shift 12 -> at every step the high-noise expert
+(timestep >= 875) or the low-noise expert predicts the velocity with classifier-free guidance (4.0 / 3.0) ->
+the 16-channel video autoencoder turns (frames - 1) / 4 + 1 latent frames into `frames` RGB frames (default 81 frames,
+16 fps, 40 steps). The flow integrator is the shared framework's (default `euler`); the reference's own second-order
+multistep integrator is not restated.
+
+Snapshot layout (diffusers): `transformer/` (high-noise expert), `transformer_2/` (low-noise expert; optional for
+single-network checkpoints), `text_encoder/` + `tokenizer/`, `vae/`; `swb_config.json` overrides dimensions for synthetic
+snapshots."""
+from __future__ import annotations
+
+import json
+from dataclasses import dataclass
+from pathlib import Path
+from typing import Any, Callable
+
+import torch
+
+from ..contracts.errors import Canceled, InferenceError, LoadError, Unsupported
+from ..contracts.gen_core.generator import (Capabilities, GenerationOutput, GenerationRequest, Generator, Modality,
+                                            ModelDescriptor)
+from ..contracts.gen_core.media import Image
+from ..contracts.gen_core.registry import Registration
+from ..contracts.gen_core.runtime import LoadSpec, OffloadPolicy, ProgressDecoding, ProgressStep
+from ..contracts.gen_core.sampling import SOLVERS, FlowModelSampling, TorchLatentOps, denoise, get_solver
+from ..contracts.gen_core.traits import reject_unknown_components
+from ..models.dit_wan import WanConfig, WanDiT
+from ..models.vae_qwen import QwenVaeConfig, WanVaeDecoder
+from .residency import Residency
+from .seed import default_seed, for_each_image_seed, seeded_noise_nchw
+
+MODEL_ID = "wan2_2_t2v_14b"
+DEFAULT_STEPS, DEFAULT_FRAMES, DEFAULT_FPS = 40, 81, 16
+BOUNDARY, FLOW_SHIFT, GUIDANCE_HIGH, GUIDANCE_LOW = 0.875, 12.0, 4.0, 3.0
+TRAIN_TIMESTEPS, TEXT_TOKENS, SIZE_MULTIPLE = 1000, 512, 16
+NEGATIVE_FALLBACK = ("色调艳丽，过曝，静态，细节模糊不清，字幕，风格，作品，画作，画面，静止，整体发灰，最差质量，低质量，JPEG压缩残留，丑陋的，残缺的，"
+                     "多余的手指，画得不好的手部，画得不好的脸部，畸形的，毁容的，形态畸形的肢体，手指融合，静止不动的画面，杂乱的背景，三条腿，背景人很多，倒着走")
+
+
+def wan_sigmas(steps: int, shift: float = FLOW_SHIFT) -> list[float]:
+    n = max(1, steps)
+    ramp = [1.0 + (1.0 / TRAIN_TIMESTEPS - 1.0) * i / n for i in range(n)]            # linspace(1, 1/N, n + 1)[:-1]
+    out = [shift * s / (1.0 + (shift - 1.0) * s) for s in ramp]
+    out[0] -= 1e-6
+    return out + [0.0]
+
+
+class Umt5PromptEncoder:
+    def __init__(self, t5, tokenizer, tokens: int = TEXT_TOKENS):
+        self.t5, self.tok, self.tokens = t5, tokenizer, tokens
+
+    def encode(self, prompt: str) -> torch.Tensor:
+        """[1, tokens, d_model]: the encoder's states for the prompt's tokens, zeros after them."""
+        ids = (self.tok.sp.encode(prompt) + [self.tok.eos])[: self.tokens]
+        n = len(ids)
+        padded = torch.tensor([ids + [self.tok.pad] * (self.tokens - n)], dtype=torch.int64)
+        mask = torch.tensor([[1] * n + [0] * (self.tokens - n)])
+        out = self.t5.encode(padded, mask).clone()
+        out[:, n:] = 0
+        return out
+
+
+class HashPromptEncoder:
+    def __init__(self, dim: int, device, dtype):
+        from .text_encoders import HashTextEncoders
+
+        self.h = HashTextEncoders(dim, 8, device, dtype)
+
+    def encode(self, prompt: str) -> torch.Tensor:
+        return self.h.encode(prompt, 16).txt
+
+
+@dataclass
+class _Heavy:
+    high: Any
+    low: Any
+    vae: Any
+
+
+class WanPipeline:
+    def __init__(self, root: Path, backend: str, device: torch.device):
+        self.root, self.backend, self.device = Path(root), backend, device
+        self.dit_cfg, self.vae_cfg, self.text_kind, self.random_init = WanConfig(), QwenVaeConfig(), "umt5", None
+        cfg_path = self.root / "swb_config.json"
+        if cfg_path.exists():
+            raw = json.loads(cfg_path.read_text())
+            if "dit" in raw:
+                self.dit_cfg = WanConfig.from_json(raw["dit"])
+            if "vae" in raw:
+                v = dict(raw["vae"])
+                if "dim_mult" in v:
+                    v["dim_mult"] = tuple(v["dim_mult"])
+                self.vae_cfg = QwenVaeConfig(**v)
+            self.text_kind = raw.get("text", self.text_kind)
+            self.random_init = raw.get("random_init")
+        elif (self.root / "transformer" / "config.json").exists():
+            self.dit_cfg = WanConfig.from_json(json.loads((self.root / "transformer" / "config.json").read_text()))
+        self.dtype = torch.bfloat16 if backend == "b200" else torch.float32
+
+    def load_text(self):
+        if self.text_kind == "hash":
+            return HashPromptEncoder(self.dit_cfg.text_dim, self.device, self.dtype)
+        from ..models.text_encoders import T5Config, T5Encoder
+        from .text_models import T5SentencePieceTokenizer, _load_component
+
+        te, sp = self.root / "text_encoder", self.root / "tokenizer" / "spiece.model"
+        if not te.is_dir() or not sp.exists():
+            raise LoadError(f"{MODEL_ID}: snapshot {self.root} lacks text_encoder/ or tokenizer/spiece.model")
+        cfg, w = _load_component(te)
+        return Umt5PromptEncoder(T5Encoder(T5Config.from_json(cfg), w, self.device, self.dtype), T5SentencePieceTokenizer(sp))
+
+    def load_heavy(self) -> _Heavy:
+        from ..io.safetensors_io import load_dir
+        from ..models.dit_wan import random_wan_weights
+        from ..models.vae_qwen import random_wan_vae_weights
+
+        if self.random_init is not None and self.backend == "b200":
+            seed = int(self.random_init)
+            mk = lambda s: WanDiT(self.dit_cfg, random_wan_weights(self.dit_cfg, s, 0.02, torch.bfloat16, self.device),      # noqa: E731
+                                  self.dtype, self.device)
+            return _Heavy(mk(seed), mk(seed + 1), WanVaeDecoder(self.vae_cfg, random_wan_vae_weights(self.vae_cfg, seed + 2),
+                                                                torch.float32, self.device))
+        for d in ("transformer", "vae"):
+            if not (self.root / d).is_dir():
+                raise LoadError(f"{MODEL_ID}: snapshot {self.root} lacks {d}/")
+        high = WanDiT(self.dit_cfg, load_dir(self.root / "transformer"), self.dtype, self.device)
+        low = high
+        if (self.root / "transformer_2").is_dir():
+            low = WanDiT(self.dit_cfg, load_dir(self.root / "transformer_2"), self.dtype, self.device)
+        return _Heavy(high, low, WanVaeDecoder(self.vae_cfg, load_dir(self.root / "vae"), torch.float32, self.device))
+
+    def encode(self, text, req: GenerationRequest):
+        g = req.guidance
+        pos = text.encode(req.prompt)
+        neg = text.encode(req.negative_prompt or NEGATIVE_FALLBACK) if g is None or g > 1.0 else None
+        return pos, neg
+
+    def render(self, heavy: _Heavy, cond, req: GenerationRequest, on_progress) -> list[list[Image]]:
+        steps = req.steps or DEFAULT_STEPS
+        frames = req.frames or DEFAULT_FRAMES
+        base_seed = req.seed if req.seed is not None else default_seed()
+        lt, lh, lw = (frames - 1) // 4 + 1, req.height // 8, req.width // 8
+        dev, dt = self.device, self.dtype
+        sigmas = wan_sigmas(steps, float(req.scheduler_shift) if req.scheduler_shift else FLOW_SHIFT)
+        solver, ops, ms = get_solver(req.sampler or "euler"), TorchLatentOps(), FlowModelSampling()
+        conds = [c for c in cond if c is not None]
+        # the text projection does not depend on the step: once per expert and prompt
+        ctx = {id(m): [m.embed_text(c) for c in conds] for m in {id(heavy.high): heavy.high, id(heavy.low): heavy.low}.values()}
+        C = self.dit_cfg.in_channels
+
+        def one_video(seed: int) -> list[Image]:
+            x = seeded_noise_nchw(seed, C * lt, lh, lw).reshape(1, C, lt, lh, lw).to(dev, dt).contiguous()
+            state = {"step": 0}
+
+            def run_model(x_in, sigma):
+                if req.cancel.is_cancelled():
+                    raise Canceled(f"{MODEL_ID}: cancelled at step {state['step']}")
+                t = float(sigma) * TRAIN_TIMESTEPS
+                high = t >= BOUNDARY * TRAIN_TIMESTEPS
+                model = heavy.high if high else heavy.low
+                g = req.guidance if req.guidance is not None else (GUIDANCE_HIGH if high else GUIDANCE_LOW)
+                tt = torch.full((1,), t, device=dev)
+                outs = [model.forward(x_in, tt, c, embedded=True).float() for c in ctx[id(model)]]
+                vel = outs[0] if len(outs) == 1 else outs[1] + (outs[0] - outs[1]) * g
+                state["step"] += 1
+                if state["step"] <= steps:
+                    on_progress(ProgressStep(state["step"], steps))
+                return vel.to(dt).contiguous()
+
+            x = solver.sample(ops, ms, lambda xx, s: denoise(ops, ms, xx, s, run_model), x, sigmas, seed)
+            while state["step"] < steps:
+                state["step"] += 1
+                on_progress(ProgressStep(state["step"], steps))
+            if req.cancel.is_cancelled():
+                raise Canceled(f"{MODEL_ID}: cancelled before decode")
+            on_progress(ProgressDecoding())
+            video = heavy.vae.decode(x.float())[0].float()                              # [3, F, H, W]
+            u8 = torch.round((video.clamp(-1, 1) + 1) * 127.5).to(torch.uint8).permute(1, 2, 3, 0).contiguous().cpu()
+            return [Image(width=req.width, height=req.height, pixels=f.numpy().tobytes()) for f in u8[:frames]]
+
+        return for_each_image_seed(base_seed, req.count, one_video)
+
+
+def wan_descriptor(backend: str, prefix: str = "") -> ModelDescriptor:
+    return ModelDescriptor(
+        id=prefix + MODEL_ID, family="wan", backend=backend, modality=Modality.VIDEO,
+        capabilities=Capabilities(
+            supports_negative_prompt=True, supports_guidance=True, supports_true_cfg=False, conditioning=[],
+            supports_lora=False, supports_lokr=False, samplers=list(SOLVERS), schedulers=[],
+            supported_guidance_methods=[], min_size=256, max_size=1280, max_count=1, supports_sequential_offload=True),
+        required_components=[])
+
+
+class WanGenerator(Generator):
+    def __init__(self, pipe: WanPipeline, descriptor: ModelDescriptor, policy: OffloadPolicy):
+        self.pipe, self._descriptor = pipe, descriptor
+        sync = torch.cuda.synchronize if pipe.backend == "b200" else (lambda: None)
+        self.residency = Residency.from_policy(policy, pipe.load_text, pipe.load_heavy, sync)
+
+    def descriptor(self) -> ModelDescriptor:
+        return self._descriptor
+
+    def validate(self, req: GenerationRequest) -> None:
+        mid = self._descriptor.id
+        self._descriptor.capabilities.validate_request(mid, req)
+        if not req.prompt:
+            raise InferenceError(f"{mid}: prompt must not be empty")
+        if req.width % SIZE_MULTIPLE or req.height % SIZE_MULTIPLE:
+            raise InferenceError(f"{mid}: width/height must be multiples of {SIZE_MULTIPLE} (got {req.width}x{req.height})")
+        if req.frames is not None and (req.frames < 1 or (req.frames - 1) % 4):
+            raise InferenceError(f"{mid}: frames must be 4k + 1 (got {req.frames})")
+
+    def generate(self, req: GenerationRequest, on_progress: Callable = lambda p: None) -> GenerationOutput:
+        self.validate(req)
+        videos = self.residency.run(req.cancel, on_progress, lambda text: self.pipe.encode(text, req),
+                                    lambda heavy, cond: self.pipe.render(heavy, cond, req, on_progress))
+        return GenerationOutput(video_frames=videos[0], fps=req.fps or DEFAULT_FPS)
+
+
+def _load(backend: str, prefix: str) -> Callable[[LoadSpec], WanGenerator]:
+    def load(spec: LoadSpec) -> WanGenerator:
+        mid = prefix + MODEL_ID
+        if spec.weights is None or spec.weights.is_file:
+            raise Unsupported(f"{mid}: needs a snapshot directory")
+        if spec.quantize is not None:
+            raise Unsupported(f"{mid}: quantised loading ({spec.quantize.name}) is not supported")
+        reject_unknown_components(spec.components, [], mid)
+        if spec.control or spec.extra_controls or spec.ip_adapter or spec.adapters:
+            raise Unsupported(f"{mid}: adapters, control branches and IP adapters are not supported by this provider")
+        if backend == "b200":
+            if not torch.cuda.is_available():
+                raise LoadError(f"{mid}: no CUDA device")
+            device = torch.device("cuda", torch.cuda.current_device())
+        else:
+            device = torch.device("cpu")
+        return WanGenerator(WanPipeline(Path(spec.weights.path), backend, device), wan_descriptor(backend, prefix),
+                            spec.offload_policy)
+    return load
+
+
+def registrations(backend: str = "b200") -> list[Registration]:
+    prefix = "" if backend == "b200" else "cpu_"
+    return [Registration(descriptor=lambda: wan_descriptor(backend, prefix), load=_load(backend, prefix))]
+
+
+def write_synthetic_snapshot(root, seed: int = 0) -> Path:
+    """A tiny random two-expert snapshot in the diffusers directory layout with the weight-free prompt encoder."""
+    from ..io.safetensors_io import save_file
+    from ..models.dit_wan import random_wan_weights
+    from ..models.vae_qwen import random_wan_vae_weights
+
+    root = Path(root)
+    dit = WanConfig(num_attention_heads=2, attention_head_dim=128, num_layers=2, ffn_dim=256, text_dim=64)
+    vae = QwenVaeConfig(base_dim=8, dim_mult=(1, 2, 2, 2), num_res_blocks=1)
+    for name, s in (("transformer", seed), ("transformer_2", seed + 1)):
+        (root / name).mkdir(parents=True, exist_ok=True)
+        save_file({k: v.bfloat16() for k, v in random_wan_weights(dit, s).items()},
+                  root / name / "diffusion_pytorch_model.safetensors")
+    (root / "vae").mkdir(exist_ok=True)
+    save_file({k: v.bfloat16() for k, v in random_wan_vae_weights(vae, seed + 2).items()},
+              root / "vae" / "diffusion_pytorch_model.safetensors")
+    (root / "swb_config.json").write_text(json.dumps({
+        "dit": {"num_attention_heads": 2, "attention_head_dim": 128, "num_layers": 2, "ffn_dim": 256, "text_dim": 64},
+        "vae": {"base_dim": vae.base_dim, "dim_mult": list(vae.dim_mult), "num_res_blocks": vae.num_res_blocks},
+        "text": "hash"}))
+    return root

@@ -129,3 +129,88 @@ class QwenVaeDecoder:
                 h = self._conv(F.interpolate(h, scale_factor=2, mode="nearest"),
                                f"decoder.up_blocks.{i}.upsamplers.0.resample.1", 1)
         return self._conv(F.silu(self._norm(h, "decoder.norm_out")), "decoder.conv_out", 1)
+
+
+# =================================================================================================================
+# the same autoencoder over time (Wan 2.1 video latents)
+# =================================================================================================================
+def random_wan_vae_weights(cfg: QwenVaeConfig, seed: int = 0, std: float = 0.05) -> dict[str, torch.Tensor]:
+    """The image checkpoint's tensors plus the temporal-upsampling convolutions of the first two up blocks."""
+    w = random_qwen_vae_weights(cfg, seed, std)
+    g = torch.Generator().manual_seed(seed + 101)
+    for i, (_, width, up) in enumerate(cfg.up_plan()):
+        if up is not None and i < 2:
+            w[f"decoder.up_blocks.{i}.upsamplers.0.time_conv.weight"] = torch.randn(2 * width, width, 3, 1, 1, generator=g) * std
+            w[f"decoder.up_blocks.{i}.upsamplers.0.time_conv.bias"] = torch.randn(2 * width, generator=g) * std
+    return w
+
+
+class WanVaeDecoder:
+    """Video decode of the causal 3-D autoencoder (parity: candle-gen-wan/src/vae16.rs): T latent frames become
+    1 + 4 (T - 1) frames. Every convolution is causal in time (two frames of zero history in front). The first two up
+    blocks double the frame count of everything after the first frame: frame 0 passes through, and a temporal
+    convolution over frames 1.. (with zero history, so it never sees frame 0) produces two frames for each of them. The
+    middle attention is per frame."""
+
+    def __init__(self, cfg: QwenVaeConfig, weights: dict[str, torch.Tensor], dtype=torch.float32, device="cpu"):
+        self.cfg, self.dtype, self.device = cfg, dtype, torch.device(device)
+        self.w = {}
+        for k, v in weights.items():
+            if k.startswith(("decoder.", "post_quant_conv.")):
+                if k.endswith(".gamma"):
+                    v = v.reshape(1, -1, 1, 1, 1)
+                elif k.endswith(".weight") and v.dim() == 4:
+                    v = v[:, :, None]                              # 2-D convolutions run per frame
+                self.w[k] = v.to(device=self.device, dtype=dtype).contiguous()
+        self.mean = torch.tensor(LATENTS_MEAN[: cfg.z_dim], device=self.device, dtype=dtype).view(1, -1, 1, 1, 1)
+        self.std = torch.tensor(LATENTS_STD[: cfg.z_dim], device=self.device, dtype=dtype).view(1, -1, 1, 1, 1)
+
+    def _conv(self, x, name, pad):
+        w = self.w[name + ".weight"]
+        kt = w.shape[2]
+        return F.conv3d(F.pad(x, (pad, pad, pad, pad, kt - 1, 0)), w, self.w[name + ".bias"])
+
+    def _norm(self, x, name):
+        xf = x.float()
+        y = xf / torch.sqrt(xf.pow(2).sum(1, keepdim=True) + NORM_EPS) * (x.shape[1] ** 0.5) * self.w[name + ".gamma"].float()
+        return y.to(x.dtype)
+
+    def _res(self, x, p):
+        h = self._conv(F.silu(self._norm(x, p + ".norm1")), p + ".conv1", 1)
+        h = self._conv(F.silu(self._norm(h, p + ".norm2")), p + ".conv2", 1)
+        return h + (self._conv(x, p + ".conv_shortcut", 0) if p + ".conv_shortcut.weight" in self.w else x)
+
+    def _attention(self, x, p):
+        B, C, T, H, W = x.shape
+        qkv = self._conv(self._norm(x, p + ".norm"), p + ".to_qkv", 0)                      # [B, 3C, T, H, W]
+        q, k, v = qkv.permute(0, 2, 1, 3, 4).reshape(B * T, 3, C, H * W).transpose(2, 3).unbind(1)
+        o = F.scaled_dot_product_attention(q[:, None], k[:, None], v[:, None])[:, 0]
+        o = o.transpose(1, 2).reshape(B, T, C, H, W).permute(0, 2, 1, 3, 4)
+        return x + self._conv(o, p + ".proj", 0)
+
+    def _upsample(self, x, p, temporal: bool):
+        B, C, T, H, W = x.shape
+        if temporal and T > 1:
+            y = self._conv(x[:, :, 1:], p + ".time_conv", 0)                                  # [B, 2C, T - 1, H, W]
+            y = torch.stack((y[:, :C], y[:, C:]), 3).reshape(B, C, 2 * (T - 1), H, W)
+            x = torch.cat([x[:, :, :1], y], 2)
+        T2 = x.shape[2]
+        frames = x.permute(0, 2, 1, 3, 4).reshape(B * T2, C, H, W)
+        frames = F.interpolate(frames, scale_factor=2, mode="nearest")
+        x = frames.reshape(B, T2, C, 2 * H, 2 * W).permute(0, 2, 1, 3, 4)
+        return self._conv(x, p + ".resample.1", 1)
+
+    @torch.no_grad()
+    def decode(self, latents: torch.Tensor) -> torch.Tensor:
+        """Normalised latents [B, 16, T, h, w] -> video [B, 3, 1 + 4 (T - 1), 8h, 8w] in about [-1, 1]."""
+        z = latents.to(self.device, self.dtype) * self.std + self.mean
+        h = self._conv(self._conv(z, "post_quant_conv", 0), "decoder.conv_in", 1)
+        h = self._res(h, "decoder.mid_block.resnets.0")
+        h = self._attention(h, "decoder.mid_block.attentions.0")
+        h = self._res(h, "decoder.mid_block.resnets.1")
+        for i, (_, _, up) in enumerate(self.cfg.up_plan()):
+            for j in range(self.cfg.num_res_blocks + 1):
+                h = self._res(h, f"decoder.up_blocks.{i}.resnets.{j}")
+            if up is not None:
+                h = self._upsample(h, f"decoder.up_blocks.{i}.upsamplers.0", temporal=i < 2)
+        return self._conv(F.silu(self._norm(h, "decoder.norm_out")), "decoder.conv_out", 1)

@@ -68,3 +68,59 @@ def test_dit_matches_direct_restatement():
     assert out.shape == z.shape and ref.abs().max() > 0.05
     assert (out[0] - ref).abs().max().item() < 2e-4 * max(1.0, ref.abs().max().item())
     assert W.WanConfig().rope_axes == (44, 42, 42) and W.WanConfig().dim == 5120
+
+
+def test_video_autoencoder_invariants():
+    from inference_b200.models.vae_qwen import QwenVaeConfig, QwenVaeDecoder, WanVaeDecoder, random_wan_vae_weights
+
+    cfg = QwenVaeConfig(base_dim=8, dim_mult=(1, 2, 2, 2), num_res_blocks=1)
+    w = random_wan_vae_weights(cfg, seed=3, std=0.2)
+    dec = WanVaeDecoder(cfg, w)
+    g = torch.Generator().manual_seed(1)
+    z = torch.randn(1, 16, 3, 3, 4, generator=g)
+    out = dec.decode(z)
+    assert out.shape == (1, 3, 9, 24, 32)                                   # 1 + 4 * (3 - 1) frames
+    # one latent frame is the image autoencoder
+    torch.testing.assert_close(dec.decode(z[:, :, :1])[:, :, 0], QwenVaeDecoder(cfg, w).decode(z[:, :, 0]), atol=1e-5, rtol=1e-5)
+    # causal in time: the frames that latent frames 0..k produce do not move when later latent frames change
+    z2 = z.clone()
+    z2[:, :, 2] = torch.randn(1, 16, 3, 4, generator=g)
+    out2 = dec.decode(z2)
+    torch.testing.assert_close(out2[:, :, :5], out[:, :, :5], atol=1e-5, rtol=1e-5)
+    assert (out2[:, :, 5:] - out[:, :, 5:]).abs().max() > 1e-3
+    torch.testing.assert_close(dec.decode(z[:, :, :2]), out[:, :, :5], atol=1e-5, rtol=1e-5)
+
+
+def test_schedule_and_provider(tmp_path):
+    from inference_b200.contracts.errors import InferenceError
+    from inference_b200.contracts.gen_core import GenerationRequest, LoadSpec
+    from inference_b200.media import provider_registry
+    from inference_b200.media.wan import wan_sigmas, write_synthetic_snapshot
+
+    s = wan_sigmas(40)
+    assert len(s) == 41 and abs(s[0] - (1.0 - 1e-6)) < 1e-12 and s[-1] == 0.0 and all(a > b for a, b in zip(s, s[1:]))
+    raw = 1.0 + (0.001 - 1.0) * 39 / 40
+    assert abs(s[39] - 12 * raw / (1 + 11 * raw)) < 1e-12
+    assert sum(1 for v in s[:-1] if v * 1000 >= 875) > 20                 # shift 12 keeps most steps on the high-noise expert
+    snap = write_synthetic_snapshot(tmp_path / "wan")
+    reg = provider_registry("cpu")
+    assert "cpu_wan2_2_t2v_14b" in reg.ids() and reg.descriptor_conformance_errors() == []
+    gen = reg.load("cpu_wan2_2_t2v_14b", LoadSpec.from_dir(snap))
+    assert gen.descriptor().modality.name == "VIDEO"
+    events = []
+    req = dict(prompt="a fox runs", width=256, height=256, steps=3, seed=5, frames=5)
+    out = gen.generate(GenerationRequest(**req), events.append)
+    assert out.kind == "video" and len(out.video_frames) == 5 and out.fps == 16
+    assert all(len(f.pixels) == 256 * 256 * 3 for f in out.video_frames)
+    assert [e.current for e in events if hasattr(e, "current")] == [1, 2, 3]
+    again = gen.generate(GenerationRequest(**req))
+    assert [f.pixels for f in again.video_frames] == [f.pixels for f in out.video_frames]
+    other = gen.generate(GenerationRequest(**{**req, "guidance": 1.0}))
+    assert [f.pixels for f in other.video_frames] != [f.pixels for f in out.video_frames]
+    with pytest.raises(InferenceError):
+        gen.generate(GenerationRequest(**{**req, "frames": 6}))
+    cancelled = GenerationRequest(**req)
+    cancelled.cancel.cancel()
+    from inference_b200.contracts.errors import Canceled
+    with pytest.raises(Canceled):
+        gen.generate(cancelled)
