@@ -245,3 +245,34 @@ def test_qwen_image_dit_matches_oracle():
     eager = out.clone()
     for _ in range(2):
         assert torch.equal(eager, model.forward_graphed(img, img_ids, ptxt, txt_ids, t, None, None))
+
+
+def test_wan_dit_on_device_matches_fp32_and_provider_renders_frames(tmp_path):
+    from inference_b200.contracts.gen_core import GenerationRequest, LoadSpec
+    from inference_b200.media import provider_registry
+    from inference_b200.media.wan import write_synthetic_snapshot
+    from inference_b200.models.dit_wan import WanConfig, WanDiT, random_wan_weights
+
+    cfg = WanConfig(num_attention_heads=2, attention_head_dim=128, num_layers=2, ffn_dim=256, text_dim=64)
+    w = {k: v.bfloat16().float() for k, v in random_wan_weights(cfg, seed=0, std=0.05).items()}
+    ref_model = WanDiT(cfg, w, torch.float32, "cuda")
+    model = WanDiT(cfg, w, torch.bfloat16, "cuda")
+    g = torch.Generator(device="cuda").manual_seed(3)
+    z = torch.randn(1, 16, 3, 8, 12, device="cuda", generator=g).bfloat16()
+    ctx = torch.randn(1, 21, 64, device="cuda", generator=g).bfloat16()
+    t = torch.full((1,), 600.0, device="cuda")
+    ref = ref_model.forward(z.float(), t, ctx.float())
+    out = model.forward(z, t, ctx)
+    err = (out.float() - ref).abs().max().item()
+    assert out.shape == ref.shape and err < 0.06 * max(1.0, ref.abs().max().item()), err
+    snap = write_synthetic_snapshot(tmp_path / "wan")
+    req = dict(prompt="a fox runs", width=256, height=256, steps=2, seed=5, frames=5)
+    import numpy as np
+
+    vids = {}
+    for backend, prefix in (("b200", ""), ("cpu", "cpu_")):
+        gen = provider_registry(backend).load(prefix + "wan2_2_t2v_14b", LoadSpec.from_dir(snap))
+        o = gen.generate(GenerationRequest(**req))
+        assert len(o.video_frames) == 5
+        vids[backend] = np.frombuffer(b"".join(f.pixels for f in o.video_frames), dtype=np.uint8).astype(np.float32)
+    assert float(np.abs(vids["b200"] - vids["cpu"]).mean()) < 8.0
