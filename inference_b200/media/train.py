@@ -257,6 +257,59 @@ def z_image_trainer_registration(backend: str):
     return Registration(descriptor=lambda: SimpleDescriptor(tid, "z-image", backend, {"adapters": ["lora"]}), load=load)
 
 
+WAN_TARGETS = ("attn1.to_q", "attn1.to_k", "attn1.to_v", "attn1.to_out.0", "attn2.to_q", "attn2.to_k", "attn2.to_v",
+               "attn2.to_out.0")
+
+
+class WanLoraTrainer(FluxLoraTrainer):
+    """The same loop on one Wan expert (candle-gen-wan/src/training.rs): adapters on the self- and cross-attention
+    projections; x_t = (1 - t) x0 + t eps, the model sees the timestep 1000 t and predicts the velocity eps - x0. Items
+    hold `latent` [16, T, h, w] (normalised video latents; T = 1 for stills) and `txt` [L, text_dim]."""
+    family, target_suffixes, item_keys = "wan", WAN_TARGETS, ("latent", "txt")
+
+    def __init__(self, cfg, weights: dict[str, torch.Tensor], backend: str = "cpu", device="cpu"):
+        from ..models.dit_wan import WanDiT
+
+        self.cfg, self.backend, self.device = cfg, backend, torch.device(device)
+        self.model = WanDiT(cfg, weights, dtype=torch.float32, device=self.device)
+        for t in self.model.w.values():
+            t.requires_grad_(False)
+
+    def descriptor(self) -> SimpleDescriptor:
+        return SimpleDescriptor("wan_lora_trainer" if self.backend != "cpu" else "cpu_wan_lora_trainer", "wan", self.backend,
+                                {"adapters": ["lora"], "targets": list(WAN_TARGETS)})
+
+    def loss_on(self, item, t: float, noise: torch.Tensor) -> torch.Tensor:
+        x0, eps = item["latent"][None], noise[None]
+        xt = (1.0 - t) * x0 + t * eps
+        out = self.model.forward_grad(xt, torch.full((1,), 1000.0 * t, device=self.device), item["txt"][None])
+        return torch.mean((out - (eps - x0)) ** 2)
+
+
+def wan_trainer_registration(backend: str):
+    """`wan_lora_trainer` (kind "trainer"): loads one expert of a Wan snapshot directory (`transformer/` unless the load
+    spec's components name another sub-directory)."""
+    from ..contracts.gen_core.registry import Registration
+    from ..contracts.gen_core.runtime import LoadSpec
+
+    tid = "wan_lora_trainer" if backend != "cpu" else "cpu_wan_lora_trainer"
+
+    def load(spec: LoadSpec) -> WanLoraTrainer:
+        from ..io.safetensors_io import load_dir
+        from .wan import WanPipeline
+
+        if spec.weights is None or spec.weights.is_file:
+            raise InferenceError(f"{tid}: needs a snapshot directory")
+        root = Path(spec.weights.path)
+        device = torch.device("cuda", torch.cuda.current_device()) if backend != "cpu" else torch.device("cpu")
+        if not (root / "transformer").is_dir():
+            raise LoadError(f"{tid}: missing {root / 'transformer'}")
+        pipe = WanPipeline(root, "cpu", device)
+        return WanLoraTrainer(pipe.dit_cfg, load_dir(root / "transformer"), backend, device)
+
+    return Registration(descriptor=lambda: SimpleDescriptor(tid, "wan", backend, {"adapters": ["lora"]}), load=load)
+
+
 SDXL_TARGETS = ("attn1.to_q", "attn1.to_k", "attn1.to_v", "attn1.to_out.0", "attn2.to_q", "attn2.to_k", "attn2.to_v",
                 "attn2.to_out.0")
 

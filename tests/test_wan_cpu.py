@@ -124,3 +124,34 @@ def test_schedule_and_provider(tmp_path):
     from inference_b200.contracts.errors import Canceled
     with pytest.raises(Canceled):
         gen.generate(cancelled)
+
+
+def test_wan_trainer(tmp_path):
+    from inference_b200.contracts.gen_core import LoadSpec, TrainingConfig
+    from inference_b200.io.safetensors_io import load_file, save_file
+    from inference_b200.media import provider_registry
+    from inference_b200.media.train import WAN_TARGETS
+    from inference_b200.media.wan import write_synthetic_snapshot
+    from inference_b200.testkit.aux_suites import TrainerProfile, trainer_conformance
+
+    snap = write_synthetic_snapshot(tmp_path / "wan")
+    ds = tmp_path / "ds"
+    ds.mkdir()
+    g = torch.Generator().manual_seed(0)
+    for i in range(2):
+        save_file({"latent": torch.randn(16, 2, 4, 4, generator=g), "txt": torch.randn(7, 64, generator=g)}, ds / f"item{i}.safetensors")
+    reg = provider_registry("cpu")
+    tr = reg.load_kind("trainer", "cpu_wan_lora_trainer", LoadSpec.from_dir(snap))
+    items = tr._items(ds)
+    noise = torch.randn(16, 2, 4, 4, generator=torch.Generator().manual_seed(9))
+    before = float(tr.loss_on(items[0], 0.5, noise))
+    final = tr.train(TrainingConfig(dataset_dir=ds, output_dir=tmp_path / "run", steps=8, learning_rate=5e-3, rank=4, alpha=4.0,
+                                    seed=3), lambda p: None)
+    ad = load_file(final)
+    assert all(k.split(".lora_")[0].endswith(WAN_TARGETS) for k in ad) and len(ad) == 2 * 2 * 8
+    tr.model.lora = {k[len("transformer."):-len(".lora_A.weight")]: (ad[k], ad[k.replace("lora_A", "lora_B")], 1.0)
+                     for k in ad if k.endswith("lora_A.weight")}
+    assert float(tr.loss_on(items[0], 0.5, noise)) < before
+    tr.model.lora = None
+    trainer_conformance(reg.load_kind("trainer", "cpu_wan_lora_trainer", LoadSpec.from_dir(snap)),
+                        TrainerProfile(ds, tmp_path / "out", steps=3, rank=2))
