@@ -22,6 +22,7 @@ class Architecture(enum.Enum):
     QWEN2_MOE = "qwen2_moe"  # Qwen2 attention + sparse MoE FFN with a shared expert
     GEMMA2 = "gemma2"        # (1 + w) RMSNorm, embed * sqrt(hidden), GeGLU, soft-caps, 4-norm sandwich
     GLM4 = "glm4"            # 4-norm sandwich, q/k/v bias, packed gate_up, partial interleaved RoPE
+    GLM = "glm"              # GLM-4-9b (`GlmForCausalLM`): the same without the sandwich norms
     DEEPSEEK_V2 = "deepseek_v2"  # multi-head latent attention + fine-grained MoE + YaRN
     QWEN35 = "qwen3_5"       # hybrid Gated-DeltaNet / gated full attention
     QWEN3_VL = "qwen3_vl"    # VLM-wrapped Qwen3 decoder with interleaved M-RoPE
@@ -44,6 +45,8 @@ class Architecture(enum.Enum):
             return Architecture.GEMMA2
         if "glm4" in hay:
             return Architecture.GLM4
+        if "glmforcausallm" in hay or model_type == "glm":
+            return Architecture.GLM
         if "deepseek" in hay:
             return Architecture.DEEPSEEK_V2
         if "phi3" in hay:
@@ -62,7 +65,7 @@ class Architecture(enum.Enum):
 
     @property
     def rope_interleaved(self) -> bool:
-        return self is Architecture.GLM4
+        return self in (Architecture.GLM4, Architecture.GLM)
 
     @property
     def sandwich_norms(self) -> bool:

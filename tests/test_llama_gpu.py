@@ -32,14 +32,14 @@ def _build(cfg, bias=False, seed=0):
 
 
 @pytest.mark.parametrize("arch,bias", [(None, False), ("qwen2", True), ("qwen3", False), ("gemma2", False),
-                                       ("glm4", True), ("qwen2_moe", True)])
+                                       ("glm4", True), ("glm", True), ("qwen2_moe", True)])
 def test_prefill_and_decode_logits_match_oracle(arch, bias):
     from inference_b200.engine.kv_pool import PagedSequence
 
     kw = {}
     if arch == "gemma2":
         kw = dict(attn_logit_softcapping=50.0, final_logit_softcapping=30.0, query_pre_attn_scalar=128)
-    if arch == "glm4":
+    if arch in ("glm4", "glm"):
         kw = dict(partial_rotary_factor=0.5)
     if arch == "qwen2_moe":
         kw = dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=256,

@@ -21,6 +21,7 @@ CASES = {
     "gemma2": ("Gemma2Config", "Gemma2ForCausalLM", dict(head_dim=16, query_pre_attn_scalar=16, attn_logit_softcapping=50.0,
                                                          final_logit_softcapping=30.0, sliding_window=4096,
                                                          hidden_activation="gelu_pytorch_tanh", tie_word_embeddings=True)),
+    "glm": ("GlmConfig", "GlmForCausalLM", dict(head_dim=16, partial_rotary_factor=0.5, attention_bias=True, pad_token_id=0)),
     "glm4": ("Glm4Config", "Glm4ForCausalLM", dict(head_dim=16, partial_rotary_factor=0.5, attention_bias=True, pad_token_id=0)),
     "qwen2_moe": ("Qwen2MoeConfig", "Qwen2MoeForCausalLM", dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48,
                                                                 shared_expert_intermediate_size=80, norm_topk_prob=False,
