@@ -159,9 +159,17 @@ class SdxlPipeline:
                 pq = (raw_vae["post_quant_conv.weight"], raw_vae["post_quant_conv.bias"])
         unet = SdxlUnet(self.unet_cfg, unet_w, self.dtype, self.device)
         if gpu:
+            import dataclasses
+
             from ..models.vae import VaeDecoderGpu
 
-            return _Heavy(unet, VaeDecoderGpu(self.vae_cfg, self.device).load_state_dict(vae_w), pq)
+            # the device decoder's convolutions are GEMMs whose reduction size must be a multiple of 8: the 4 latent
+            # channels are padded to 8 with zero weights (render pads the latents with zero channels; the shift is 0)
+            pad = (-self.vae_cfg.z_channels) % 8
+            vae_w = dict(vae_w)
+            vae_w["decoder.conv_in.weight"] = torch.nn.functional.pad(vae_w["decoder.conv_in.weight"], (0, 0, 0, 0, 0, pad))
+            gpu_cfg = dataclasses.replace(self.vae_cfg, z_channels=self.vae_cfg.z_channels + pad)
+            return _Heavy(unet, VaeDecoderGpu(gpu_cfg, self.device).load_state_dict(vae_w), pq)
         return _Heavy(unet, OracleVaeDecoder(self.vae_cfg, vae_w, device=self.device), pq)
 
     @staticmethod
@@ -213,6 +221,7 @@ class SdxlPipeline:
             on_progress(ProgressDecoding())
             z = apply_post_quant(x.float(), heavy.post_quant, self.vae_cfg)
             if self.backend == "b200":
+                z = torch.nn.functional.pad(z, (0, 0, 0, 0, 0, heavy.vae.cfg.z_channels - z.shape[1]))
                 host = heavy.vae.decode_rgb8(z)[0].cpu()
             else:
                 img = heavy.vae.decode(z)[0].permute(1, 2, 0)
