@@ -11,6 +11,7 @@ Snapshot layout (diffusers): `unet/`, `text_encoder/` + `tokenizer/`, `text_enco
 `swb_config.json` overrides dimensions for synthetic snapshots."""
 from __future__ import annotations
 
+import dataclasses
 import json
 from dataclasses import dataclass
 from pathlib import Path
@@ -100,9 +101,20 @@ def apply_post_quant(z: torch.Tensor, post_quant, cfg: VaeConfig) -> torch.Tenso
 
 
 class SdxlPipeline:
+    model_id, default_steps, default_guidance = MODEL_ID, DEFAULT_STEPS, DEFAULT_GUIDANCE
+    default_sampler, default_scheduler = DEFAULT_SAMPLER, DEFAULT_SCHEDULER
+
+    @staticmethod
+    def default_unet_config() -> SdxlUnetConfig:
+        return SdxlUnetConfig()
+
+    @staticmethod
+    def model_sampling() -> DiscreteModelSampling:
+        return DiscreteModelSampling()
+
     def __init__(self, root: Path, backend: str, device: torch.device):
         self.root, self.backend, self.device = Path(root), backend, device
-        self.unet_cfg = SdxlUnetConfig()
+        self.unet_cfg = self.default_unet_config()
         self.vae_cfg = VaeConfig(z_channels=4, scale_factor=VAE_SCALE, shift_factor=0.0)
         self.text_kind, self.random_init, self.adapters = "dual_clip", None, []
         cfg_path = self.root / "swb_config.json"
@@ -113,7 +125,7 @@ class SdxlPipeline:
                 for k in ("block_out_channels", "transformer_layers_per_block"):
                     if k in u:
                         u[k] = tuple(u[k])
-                self.unet_cfg = SdxlUnetConfig(**u)
+                self.unet_cfg = dataclasses.replace(self.default_unet_config(), **u)
             if "vae" in raw:
                 v = dict(raw["vae"])
                 if "ch_mult" in v:
@@ -159,8 +171,6 @@ class SdxlPipeline:
                 pq = (raw_vae["post_quant_conv.weight"], raw_vae["post_quant_conv.bias"])
         unet = SdxlUnet(self.unet_cfg, unet_w, self.dtype, self.device)
         if gpu:
-            import dataclasses
-
             from ..models.vae import VaeDecoderGpu
 
             # the device decoder's convolutions are GEMMs whose reduction size must be a multiple of 8: the 4 latent
@@ -172,9 +182,8 @@ class SdxlPipeline:
             return _Heavy(unet, VaeDecoderGpu(gpu_cfg, self.device).load_state_dict(vae_w), pq)
         return _Heavy(unet, OracleVaeDecoder(self.vae_cfg, vae_w, device=self.device), pq)
 
-    @staticmethod
-    def guidance(req: GenerationRequest) -> float:
-        return float(req.guidance) if req.guidance is not None else DEFAULT_GUIDANCE
+    def guidance(self, req: GenerationRequest) -> float:
+        return float(req.guidance) if req.guidance is not None else self.default_guidance
 
     def encode(self, text, req: GenerationRequest):
         pos = text.encode(req.prompt)
@@ -182,14 +191,14 @@ class SdxlPipeline:
         return pos, neg
 
     def render(self, heavy: _Heavy, cond, req: GenerationRequest, on_progress) -> list[Image]:
-        steps = req.steps or DEFAULT_STEPS
+        steps = req.steps or self.default_steps
         guidance = self.guidance(req)
         base_seed = req.seed if req.seed is not None else default_seed()
         lh, lw = req.height // 8, req.width // 8
         dev, dt = self.device, self.dtype
-        ms = DiscreteModelSampling()
-        sigmas = schedule_sigmas(req.scheduler or DEFAULT_SCHEDULER, ms, steps)
-        solver, ops = get_solver(req.sampler or DEFAULT_SAMPLER), TorchLatentOps()
+        ms = self.model_sampling()
+        sigmas = schedule_sigmas(req.scheduler or self.default_scheduler, ms, steps)
+        solver, ops = get_solver(req.sampler or self.default_sampler), TorchLatentOps()
         conds = [c for c in cond if c is not None]                 # [prompt] or [prompt, negative]
         context = torch.cat([c.context for c in conds], 0).to(dev, dt)
         pooled = torch.cat([c.pooled for c in conds], 0).to(dev, dt)
@@ -203,7 +212,7 @@ class SdxlPipeline:
 
             def run_model(x_in, timestep):
                 if req.cancel.is_cancelled():
-                    raise Canceled(f"{MODEL_ID}: cancelled at step {state['step']}")
+                    raise Canceled(f"{self.model_id}: cancelled at step {state['step']}")
                 tt = torch.full((nb,), float(timestep), device=dev)
                 o = heavy.unet.forward(x_in.expand(nb, -1, -1, -1), tt, context, pooled, time_ids).float()
                 eps = o[0:1] if nb == 1 else o[1:2] + (o[0:1] - o[1:2]) * guidance
@@ -217,7 +226,7 @@ class SdxlPipeline:
                 state["step"] += 1
                 on_progress(ProgressStep(state["step"], steps))
             if req.cancel.is_cancelled():
-                raise Canceled(f"{MODEL_ID}: cancelled before decode")
+                raise Canceled(f"{self.model_id}: cancelled before decode")
             on_progress(ProgressDecoding())
             z = apply_post_quant(x.float(), heavy.post_quant, self.vae_cfg)
             if self.backend == "b200":

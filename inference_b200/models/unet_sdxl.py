@@ -31,6 +31,7 @@ class SdxlUnetConfig:
     addition_time_embed_dim: int = 256
     projection_class_embeddings_input_dim: int = 2816
     norm_groups: int = 32
+    encoder_hid_dim: int = 0          # Kolors: the text states are 4096 wide and projected to cross_attention_dim first
 
     @property
     def time_dim(self) -> int:
@@ -51,7 +52,7 @@ class SdxlUnetConfig:
                               cross_attention_dim=j.get("cross_attention_dim", 2048),
                               addition_time_embed_dim=j.get("addition_time_embed_dim", 256),
                               projection_class_embeddings_input_dim=j.get("projection_class_embeddings_input_dim", 2816),
-                              norm_groups=j.get("norm_num_groups", 32))
+                              norm_groups=j.get("norm_num_groups", 32), encoder_hid_dim=int(j.get("encoder_hid_dim") or 0))
 
 
 def unet_plan(cfg: SdxlUnetConfig):
@@ -130,6 +131,8 @@ def random_sdxl_unet_weights(cfg: SdxlUnetConfig, seed: int = 0, std: float = 0.
     lin("time_embedding.linear_2", T, T)
     lin("add_embedding.linear_1", T, cfg.projection_class_embeddings_input_dim)
     lin("add_embedding.linear_2", T, T)
+    if cfg.encoder_hid_dim:
+        lin("encoder_hid_proj", cfg.cross_attention_dim, cfg.encoder_hid_dim)
     for lvl, res, depth, sampler in down:
         for j, (cin, cout) in enumerate(res):
             resnet(f"down_blocks.{lvl}.resnets.{j}", cin, cout)
@@ -213,6 +216,8 @@ class SdxlUnet:
         cfg = self.cfg
         dev, dt = self.device, self.dtype
         x, context = x.to(dev, dt), context.to(dev, dt)
+        if cfg.encoder_hid_dim:
+            context = self._lin(context, "encoder_hid_proj")
         B = x.shape[0]
         t_emb = timestep_embedding(timestep.to(dev).float(), cfg.block_out_channels[0], time_factor=1.0).to(dt)
         emb = self._lin(F.silu(self._lin(t_emb, "time_embedding.linear_1").float()).to(dt), "time_embedding.linear_2")

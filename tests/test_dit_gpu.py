@@ -137,7 +137,7 @@ def test_chroma_dit_matches_oracle():
         assert torch.equal(eager, model.forward_graphed(img, img_ids, txt, txt_ids, t, None, None))
 
 
-@pytest.mark.parametrize("family", ["flux", "chroma", "z_image", "sd3", "qwen_image", "sdxl"])
+@pytest.mark.parametrize("family", ["flux", "chroma", "z_image", "sd3", "qwen_image", "sdxl", "kolors"])
 def test_generator_providers_on_device_track_the_oracle_backend(tmp_path, family):
     """The sm_100a provider and the fp32 oracle provider render the same snapshot, seed and request."""
     import numpy as np
@@ -154,6 +154,11 @@ def test_generator_providers_on_device_track_the_oracle_backend(tmp_path, family
     elif family == "sdxl":
         from inference_b200.media.sdxl import write_synthetic_snapshot
         mid, extra = "sdxl", {"guidance": 2.0, "negative_prompt": "blurry"}
+    elif family == "kolors":
+        from inference_b200.media.kolors import write_synthetic_snapshot as ko
+
+        write_synthetic_snapshot = lambda root: ko(root, text="chatglm")      # noqa: E731
+        mid, extra = "kolors", {"guidance": 2.0, "negative_prompt": "blurry"}
     elif family == "qwen_image":
         from inference_b200.media.qwen_image import write_synthetic_snapshot as qi
 

@@ -29,7 +29,7 @@ def test_registry_lists_both_variants(registry):
     assert (dev.capabilities.min_size, dev.capabilities.max_size, dev.capabilities.max_count) == (256, 2048, 8)
     assert provider_registry("b200").ids() == ["flux1_schnell", "flux1_dev", "chroma1_hd", "chroma1_base", "chroma1_flash",
                                              "z_image", "z_image_turbo", "sd3_5_large", "sd3_5_large_turbo",
-                                             "sd3_5_medium", "qwen_image", "sdxl", "wan2_2_t2v_14b"]
+                                             "sd3_5_medium", "qwen_image", "sdxl", "kolors", "wan2_2_t2v_14b"]
 
 
 def test_generator_conformance(registry, snapshot):

@@ -24,7 +24,7 @@ def test_catalogs_validate_and_snapshot():
         cat = bundle.catalog()
         snap = json.loads(cat.snapshot().to_json())
         assert snap["backend"] == backend and snap["text_llm_ids"] == [llm, llm.replace("llama", "llava"), llm.replace("llama", "qwen3-vl")]
-        assert snap["snapshot_preparer_backends"] == [backend] and len(snap["generator_ids"]) == 13
+        assert snap["snapshot_preparer_backends"] == [backend] and len(snap["generator_ids"]) == 14
         assert snap["audio_backend"] == backend and snap["audio_transcriber_ids"] == ["whisper"]
 
 
