@@ -9,8 +9,8 @@ image-only attention with its own modulation; the last block's context stream is
 stops). The conditioning vector is timestep embedding + pooled-text embedding.
 
 One implementation serves both backends: fp32 on the CPU oracle backend, bf16 on a CUDA device where every projection
-goes through the tcgen05 GEMM (`text_encoders.linear`); the head dimension is 64, so attention uses the framework's
-scaled-dot-product call there rather than the head-dim-128 tcgen05 attention kernels."""
+goes through the tcgen05 GEMM (`text_encoders.linear`) and attention through the tcgen05 attention kernel with the
+64-wide heads zero-padded to its 128 (`ops.dense_attention_padded`)."""
 from __future__ import annotations
 
 from dataclasses import dataclass, field
@@ -147,7 +147,12 @@ class Sd3DiT:
         return x.transpose(1, 2)
 
     def _sdpa(self, q, k, v):
-        B, _, S, _ = q.shape
+        """q, k, v [B, heads, S, hd] -> [B, S, heads * hd]; on the device the zero-padded tcgen05 kernel."""
+        B, _, S, D = q.shape
+        if q.is_cuda and q.dtype == torch.bfloat16 and D <= 128 and D % 8 == 0:
+            from .. import ops
+
+            return ops.dense_attention_padded(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), scale=D ** -0.5)
         return F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B, S, -1)
 
     def _ff(self, x, p):

@@ -6,8 +6,8 @@ cross-attention on the [77, 2048] text context, GEGLU feed-forward; head width 6
 the timestep embedding and an embedding of (pooled text vector, six size / crop numbers).
 
 One implementation serves both backends: fp32 on the CPU oracle backend; bf16 on a CUDA device, where linear
-projections go through the tcgen05 GEMM (`text_encoders.linear`) and convolutions, group norms and the head-width-64
-attention go through the framework's library calls."""
+projections go through the tcgen05 GEMM (`text_encoders.linear`), attention through the tcgen05 attention kernel with
+the 64-wide heads zero-padded to its 128, and convolutions and group norms through the framework's library calls."""
 from __future__ import annotations
 
 from dataclasses import dataclass
@@ -190,10 +190,16 @@ class SdxlUnet:
     def _attention(self, x, ctx, p):
         B, S, C = x.shape
         nh = C // self.cfg.attention_head_dim
-        q = self._lin(x, p + ".to_q").view(B, S, nh, -1).transpose(1, 2)
-        k = self._lin(ctx, p + ".to_k").view(B, ctx.shape[1], nh, -1).transpose(1, 2)
-        v = self._lin(ctx, p + ".to_v").view(B, ctx.shape[1], nh, -1).transpose(1, 2)
-        o = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B, S, C)
+        q = self._lin(x, p + ".to_q").view(B, S, nh, -1)
+        k = self._lin(ctx, p + ".to_k").view(B, ctx.shape[1], nh, -1)
+        v = self._lin(ctx, p + ".to_v").view(B, ctx.shape[1], nh, -1)
+        hd = q.shape[-1]
+        if q.is_cuda and q.dtype == torch.bfloat16 and hd <= 128 and hd % 8 == 0:
+            from .. import ops
+
+            o = ops.dense_attention_padded(q, k, v, scale=hd ** -0.5)          # tcgen05 kernel, heads zero-padded to 128
+        else:
+            o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)).transpose(1, 2).reshape(B, S, C)
         return self._lin(o, p + ".to_out.0")
 
     def _transformer(self, x, ctx, p, depth):

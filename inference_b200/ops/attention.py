@@ -66,6 +66,20 @@ def dense_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale:
     return out
 
 
+def dense_attention_padded(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float) -> torch.Tensor:
+    """dense_attention for head widths below 128 (64 in SD3 / SDXL blocks, 72 in the Qwen3-VL tower): q, k and v are
+    zero-padded to 128 per head, which changes neither q . k nor the first D output columns, so the tcgen05 kernel
+    serves them at twice the arithmetic. q [B, Sq, H, D], k / v [B, Skv, Hkv, D] bf16 -> [B, Sq, H * D]."""
+    B, Sq, H, D = q.shape
+    if D == 128:
+        return dense_attention(q.contiguous(), k.contiguous(), v.contiguous(), scale=scale)
+    assert D < 128
+    pad = (0, 128 - D)
+    qp, kp, vp = (torch.nn.functional.pad(t, pad).contiguous() for t in (q, k, v))
+    out = dense_attention(qp, kp, vp, scale=scale)
+    return out.view(B, Sq, H, 128)[..., :D].reshape(B, Sq, H * D)
+
+
 def set_dense_impl(legacy: bool) -> None:
     """Comparison runs only: True forces the mma.sync kernel for dense attention, False restores the tcgen05 kernel."""
     kernels().swb_attn_dense_set_impl(1 if legacy else 0)

@@ -281,3 +281,18 @@ def test_wan_dit_on_device_matches_fp32_and_provider_renders_frames(tmp_path):
         assert len(o.video_frames) == 5
         vids[backend] = np.frombuffer(b"".join(f.pixels for f in o.video_frames), dtype=np.uint8).astype(np.float32)
     assert float(np.abs(vids["b200"] - vids["cpu"]).mean()) < 8.0
+
+
+@pytest.mark.parametrize("D,Sq,Skv,B", [(64, 300, 300, 2), (64, 1024, 77, 2), (72, 96, 96, 1), (128, 130, 50, 1)])
+def test_padded_dense_attention_serves_narrow_heads(D, Sq, Skv, B):
+    from inference_b200 import ops
+
+    g = torch.Generator(device="cuda").manual_seed(D + Sq)
+    q = torch.randn(B, Sq, 5, D, device="cuda", generator=g).bfloat16()
+    k = torch.randn(B, Skv, 5, D, device="cuda", generator=g).bfloat16()
+    v = torch.randn(B, Skv, 5, D, device="cuda", generator=g).bfloat16()
+    out = ops.dense_attention_padded(q, k, v, scale=D ** -0.5)
+    ref = torch.nn.functional.scaled_dot_product_attention(q.float().transpose(1, 2), k.float().transpose(1, 2),
+                                                           v.float().transpose(1, 2)).transpose(1, 2).reshape(B, Sq, 5 * D)
+    assert out.shape == ref.shape
+    assert (out.float() - ref).abs().max().item() < 0.03
