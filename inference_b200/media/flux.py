@@ -19,7 +19,7 @@ from typing import Any, Callable
 import torch
 
 from ..contracts.errors import Canceled, InferenceError, LoadError, Unsupported
-from ..contracts.gen_core.generator import (Capabilities, GenerationOutput, GenerationRequest, Generator, Modality,
+from ..contracts.gen_core.generator import (Capabilities, ConditioningKind, GenerationOutput, GenerationRequest, Generator, Modality,
                                             ModelDescriptor)
 from ..contracts.gen_core.media import Image
 from ..contracts.gen_core.registry import PerComponentBytes, Registration
@@ -71,7 +71,7 @@ def flux_descriptor(variant: Variant, backend: str, prefix: str = "") -> ModelDe
         id=prefix + variant.model_id, family="flux", backend=backend, modality=Modality.IMAGE,
         capabilities=Capabilities(
             supports_negative_prompt=False, supports_guidance=variant.supports_guidance, supports_true_cfg=False,
-            conditioning=[], supports_lora=True, supports_lokr=False, samplers=list(SOLVERS),
+            conditioning=[ConditioningKind.REFERENCE], supports_lora=True, supports_lokr=False, samplers=list(SOLVERS),
             schedulers=list(SCHEDULERS), supported_guidance_methods=[], min_size=256, max_size=2048, max_count=8,
             supports_sequential_offload=True),
         required_components=[])
@@ -192,6 +192,18 @@ class FluxPipeline:
             sigmas = flux_schedule(v, steps, req.width, req.height)
         else:
             sigmas = schedule_sigmas(req.scheduler, FlowModelSampling(mu=req.scheduler_shift or 0.0), steps)
+        from .reference import encode_reference_image, init_time_step, reference_of
+
+        ref = reference_of(req, v.model_id)
+        clean, start = None, 0
+        if ref is not None and init_time_step(steps, ref[1]) > 0:
+            from ..io.safetensors_io import load_file
+
+            start = min(init_time_step(steps, ref[1]), len(sigmas) - 2)
+            latents = encode_reference_image(self.vae_cfg, load_file(self.root / "ae.safetensors"), ref[0], req.width,
+                                             req.height, dev, v.model_id)
+            clean = patchify(latents).to(dev)
+            sigmas = sigmas[start:]                    # the run enters the schedule at sigma_start
         solver = get_solver(req.sampler or "euler")
         ops = TorchLatentOps()
         gvec = torch.full((1,), float(guidance), device=dev) if guidance is not None else None
@@ -199,8 +211,13 @@ class FluxPipeline:
 
         def one_image(seed: int) -> Image:
             noise = seeded_noise_nchw(seed, c_lat, lh, lw)                    # CPU draw -> device
-            x = patchify(noise).to(dev, dt).contiguous()
-            state = {"step": 0}
+            x = patchify(noise).to(dev)
+            if clean is not None:                       # x_t = (1 - sigma) clean + sigma noise at the entry point
+                x = (1.0 - sigmas[0]) * clean + sigmas[0] * x.float()
+            x = x.to(dt).contiguous()
+            state = {"step": start}
+            for s_done in range(1, start + 1):
+                on_progress(ProgressStep(s_done, steps))
 
             def run_model(x_in, t):
                 if req.cancel.is_cancelled():
@@ -324,7 +341,10 @@ def write_synthetic_snapshot(root, variant: Variant = Variant.DEV, seed: int = 0
                      depth_single=2, guidance_embed=variant.supports_guidance)
     vae = VaeConfig(ch=32, ch_mult=(1, 2, 2, 2), num_res_blocks=1)
     save_file({k: v.bfloat16() for k, v in random_flux_weights(dit, seed).items()}, root / variant.transformer_file)
-    save_file({k: v.bfloat16() for k, v in random_vae_weights(vae, seed + 1).items()}, root / "ae.safetensors")
+    from ..models.vae import random_vae_encoder_weights
+
+    save_file({k: v.bfloat16() for k, v in {**random_vae_weights(vae, seed + 1), **random_vae_encoder_weights(vae, seed + 3)}.items()},
+              root / "ae.safetensors")
     (root / "swb_config.json").write_text(json.dumps({
         "dit": {**{k: getattr(dit, k) for k in ("in_channels", "vec_in_dim", "context_in_dim", "hidden_size",
                                                 "num_heads", "depth", "depth_single", "guidance_embed")},

@@ -34,6 +34,7 @@ from ..models.vae import OracleVaeDecoder, VaeConfig
 from .chroma import convert_diffusers_vae_decoder, convert_diffusers_vae_encoder, native_vae_to_diffusers
 from .flux import SIZE_MULTIPLE
 from .residency import Residency
+from .reference import encode_reference_image, init_time_step, reference_of  # noqa: F401
 from .seed import default_seed, for_each_image_seed, seeded_noise_nchw
 
 MAX_PROMPT_TOKENS = 512
@@ -67,24 +68,6 @@ def flow_match_sigmas(steps: int, shift: float, apply_shift: bool) -> list[float
     if apply_shift:
         ramp = [shift * s / (1.0 + (shift - 1.0) * s) for s in ramp]
     return ramp + [0.0]
-
-
-def init_time_step(steps: int, strength: float | None) -> int:
-    """Where a reference-guided run enters the schedule: max(1, floor(steps * strength)) for a strength in (0, 1], 0
-    (plain text-to-image) otherwise. A higher strength starts later and keeps more of the reference."""
-    if strength is None or not strength > 0.0:
-        return 0
-    return max(1, min(steps - 1, int(steps * min(strength, 1.0)))) if steps > 1 else 0
-
-
-def reference_of(req: GenerationRequest):
-    """(image, strength) of the request's single REFERENCE conditioning, or None."""
-    refs = [c for c in req.conditioning if c.kind is ConditioningKind.REFERENCE]
-    if not refs:
-        return None
-    if len(refs) > 1 or refs[0].image is None:
-        raise InferenceError("z-image: exactly one reference image is supported")
-    return refs[0].image, refs[0].strength
 
 
 def z_image_sigmas(variant: ZImageVariant, steps: int) -> list[float]:
@@ -188,21 +171,10 @@ class ZImagePipeline:
                       OracleVaeDecoder(self.vae_cfg, vae_w, device=self.device))
 
     def encode_reference(self, image: Image, width: int, height: int) -> torch.Tensor:
-        """Reference image -> clean latents [1, 16, h/8, w/8] (the autoencoder's mean; fp32 encoder, loaded on demand)."""
-        import numpy as np
-
-        from ..contracts.gen_core.imageops import resize
         from ..io.safetensors_io import load_dir
-        from ..models.vae import OracleVaeEncoder
 
-        enc_w = convert_diffusers_vae_encoder(load_dir(self.root / "vae"))
-        if "encoder.conv_in.weight" not in enc_w:
-            raise LoadError(f"{self.variant.value}: the snapshot's vae/ has no encoder, which a reference image needs")
-        if (image.width, image.height) != (width, height):
-            image = resize(image, width, height, "lanczos")
-        px = torch.from_numpy(np.frombuffer(bytes(image.pixels), dtype=np.uint8).reshape(height, width, 3).copy())
-        x = (px.permute(2, 0, 1)[None].float() / 127.5 - 1.0)
-        return OracleVaeEncoder(self.vae_cfg, enc_w, device=self.device).encode(x).float()
+        return encode_reference_image(self.vae_cfg, convert_diffusers_vae_encoder(load_dir(self.root / "vae")), image, width,
+                                      height, self.device, self.variant.value)
 
     def guidance(self, req: GenerationRequest) -> float | None:
         if self.variant is ZImageVariant.TURBO:
@@ -228,7 +200,7 @@ class ZImagePipeline:
             sigmas = native
         else:
             sigmas = schedule_sigmas(req.scheduler, FlowModelSampling(mu=req.scheduler_shift or 0.0), steps)
-        ref = reference_of(req)
+        ref = reference_of(req, v.value)
         clean, start = None, 0
         if ref is not None and init_time_step(steps, ref[1]) > 0:
             start = min(init_time_step(steps, ref[1]), len(sigmas) - 2)

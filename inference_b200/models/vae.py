@@ -188,6 +188,8 @@ class VaeDecoderGpu:
     def load_state_dict(self, weights) -> "VaeDecoderGpu":
         self.w = {}
         for k, v in weights.items():
+            if not k.startswith("decoder."):          # full autoencoder checkpoints also carry the encoder
+                continue
             t = v.to(device=self.device, dtype=torch.float32)
             if t.dim() == 4:   # OIHW -> [O, (kh, kw, I)] matching the patch-gather column order
                 o, i, kh, kw = t.shape

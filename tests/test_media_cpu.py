@@ -128,3 +128,20 @@ def test_flux_with_t5_and_clip_text_encoders(tmp_path):
     assert x.images[0].pixels == y.images[0].pixels and x.images[0].pixels != z.images[0].pixels
     fp = provider_registry("cpu").footprint("cpu_flux1_schnell", LoadSpec.from_dir(snap))
     assert fp.components["text_encoder"] > 0 and fp.components["text_encoder_2"] > 0
+
+
+def test_flux_reference_guided_generation(registry, snapshot):
+    from inference_b200.contracts.gen_core.generator import Conditioning, ConditioningKind
+    from inference_b200.contracts.gen_core.media import Image
+
+    gen = registry.load("cpu_flux1_dev", LoadSpec.from_dir(snapshot))
+    g = torch.Generator().manual_seed(3)
+    ref = Image(width=96, height=160, pixels=bytes(torch.randint(0, 256, (160 * 96 * 3,), generator=g, dtype=torch.uint8).tolist()))
+    base = dict(prompt="a red fox", width=256, height=256, steps=4, seed=5)
+    cond = lambda s: [Conditioning(ConditioningKind.REFERENCE, image=ref, strength=s)]      # noqa: E731
+    plain = gen.generate(GenerationRequest(**base)).images[0].pixels
+    events = []
+    guided = gen.generate(GenerationRequest(**base, conditioning=cond(0.5)), events.append).images[0].pixels
+    assert guided != plain and gen.generate(GenerationRequest(**base, conditioning=cond(0.5))).images[0].pixels == guided
+    assert gen.generate(GenerationRequest(**base, conditioning=cond(0.0))).images[0].pixels == plain
+    assert [e.current for e in events if hasattr(e, "current")] == [1, 2, 3, 4]
