@@ -22,8 +22,8 @@ from typing import Any, Callable
 import torch
 
 from ..contracts.errors import Canceled, InferenceError, LoadError, Unsupported
-from ..contracts.gen_core.generator import (Capabilities, GenerationOutput, GenerationRequest, Generator, Modality,
-                                            ModelDescriptor)
+from ..contracts.gen_core.generator import (Capabilities, ConditioningKind, GenerationOutput, GenerationRequest, Generator,
+                                            Modality, ModelDescriptor)
 from ..contracts.gen_core.media import Image
 from ..contracts.gen_core.registry import Registration
 from ..contracts.gen_core.runtime import AdapterKind, LoadSpec, OffloadPolicy, ProgressDecoding, ProgressStep
@@ -210,6 +210,18 @@ class Sd3Pipeline:
         else:
             sigmas = schedule_sigmas(req.scheduler, FlowModelSampling(mu=req.scheduler_shift or 0.0), steps)
         solver, ops, ms = get_solver(req.sampler or "euler"), TorchLatentOps(), FlowModelSampling()
+        from .chroma import convert_diffusers_vae_encoder
+        from .reference import encode_reference_image, init_time_step, reference_of
+
+        ref = reference_of(req, v.value)
+        clean, start = None, 0
+        if ref is not None and init_time_step(steps, ref[1]) > 0:
+            from ..io.safetensors_io import load_dir
+
+            start = min(init_time_step(steps, ref[1]), len(sigmas) - 2)
+            clean = encode_reference_image(self.vae_cfg, convert_diffusers_vae_encoder(load_dir(self.root / "vae")), ref[0],
+                                           req.width, req.height, dev, v.value).to(dev)
+            sigmas = sigmas[start:]                    # the run enters the schedule at sigma_start
         conds = [c for c in cond if c is not None]
         # both guidance branches share every shape: one batched forward per step
         context = torch.cat([c.context for c in conds], 0).to(dev, dt)
@@ -217,8 +229,13 @@ class Sd3Pipeline:
         nb = len(conds)
 
         def one_image(seed: int) -> Image:
-            x = seeded_noise_nchw(seed, self.vae_cfg.z_channels, lh, lw).to(dev, dt).contiguous()
-            state = {"step": 0}
+            x = seeded_noise_nchw(seed, self.vae_cfg.z_channels, lh, lw).to(dev)
+            if clean is not None:                       # x_t = (1 - sigma) clean + sigma noise at the entry point
+                x = (1.0 - sigmas[0]) * clean + sigmas[0] * x.float()
+            x = x.to(dt).contiguous()
+            state = {"step": start}
+            for s_done in range(1, start + 1):
+                on_progress(ProgressStep(s_done, steps))
 
             def run_model(x_in, sigma):
                 if req.cancel.is_cancelled():
@@ -254,7 +271,8 @@ def sd3_descriptor(variant: Sd3Variant, backend: str, prefix: str = "") -> Model
     return ModelDescriptor(
         id=prefix + variant.value, family="sd3", backend=backend, modality=Modality.IMAGE,
         capabilities=Capabilities(
-            supports_negative_prompt=cfg, supports_guidance=cfg, supports_true_cfg=False, conditioning=[],
+            supports_negative_prompt=cfg, supports_guidance=cfg, supports_true_cfg=False,
+            conditioning=[ConditioningKind.REFERENCE],
             supports_lora=True, supports_lokr=False, samplers=list(SOLVERS), schedulers=list(SCHEDULERS),
             supported_guidance_methods=[], min_size=256, max_size=2048, max_count=8,
             supports_sequential_offload=True),
@@ -337,9 +355,12 @@ def write_synthetic_snapshot(root, seed: int = 0, dual: bool = False) -> Path:
     (root / "vae").mkdir(exist_ok=True)
     save_file({k: v.bfloat16() for k, v in random_sd3_weights(dit, seed).items()},
               root / "transformer" / "diffusion_pytorch_model.safetensors")
-    save_file({k: v.bfloat16() for k, v in native_vae_to_diffusers(random_vae_weights(vae, seed + 1),
-                                                                   len(vae.ch_mult)).items()},
-              root / "vae" / "diffusion_pytorch_model.safetensors")
+    from ..models.vae import random_vae_encoder_weights
+    from .z_image import native_vae_encoder_to_diffusers
+
+    vae_sd = native_vae_to_diffusers(random_vae_weights(vae, seed + 1), len(vae.ch_mult))
+    vae_sd.update(native_vae_encoder_to_diffusers(random_vae_encoder_weights(vae, seed + 3)))
+    save_file({k: v.bfloat16() for k, v in vae_sd.items()}, root / "vae" / "diffusion_pytorch_model.safetensors")
     (root / "swb_config.json").write_text(json.dumps({
         "dit": {"pos_embed_max_size": dit.pos_embed_max_size, "num_attention_heads": dit.num_attention_heads,
                 "attention_head_dim": dit.attention_head_dim, "num_layers": dit.num_layers,

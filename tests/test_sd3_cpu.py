@@ -161,3 +161,23 @@ def test_sigma_table_golden():
         assert abs(a - b) < 1e-6
     s = sd3_sigmas(28)
     assert len(s) == 29 and all(x > y for x, y in zip(s, s[1:]))
+
+
+def test_sd3_reference_guided_generation(tmp_path):
+    from inference_b200.contracts.gen_core import GenerationRequest, LoadSpec
+    from inference_b200.contracts.gen_core.generator import Conditioning, ConditioningKind
+    from inference_b200.contracts.gen_core.media import Image
+    from inference_b200.media import provider_registry
+    from inference_b200.media.reference import init_time_step
+    from inference_b200.media.sd3 import write_synthetic_snapshot
+
+    assert init_time_step(28, 0.5) == 14 and init_time_step(28, 0.01) == 1 and init_time_step(28, None) == 0
+    gen = provider_registry("cpu").load("cpu_sd3_5_large_turbo", LoadSpec.from_dir(write_synthetic_snapshot(tmp_path / "s")))
+    g = torch.Generator().manual_seed(3)
+    ref = Image(width=128, height=128, pixels=bytes(torch.randint(0, 256, (128 * 128 * 3,), generator=g, dtype=torch.uint8).tolist()))
+    base = dict(prompt="a red fox", width=256, height=256, steps=4, seed=5)
+    cond = lambda s: [Conditioning(ConditioningKind.REFERENCE, image=ref, strength=s)]      # noqa: E731
+    plain = gen.generate(GenerationRequest(**base)).images[0].pixels
+    guided = gen.generate(GenerationRequest(**base, conditioning=cond(0.5))).images[0].pixels
+    assert guided != plain and gen.generate(GenerationRequest(**base, conditioning=cond(0.5))).images[0].pixels == guided
+    assert gen.generate(GenerationRequest(**base, conditioning=cond(0.0))).images[0].pixels == plain
