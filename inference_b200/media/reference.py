@@ -44,5 +44,5 @@ def encode_reference_image(vae_cfg, encoder_weights: dict[str, torch.Tensor], im
         image = resize(image, width, height, "lanczos")
     px = torch.from_numpy(np.frombuffer(bytes(image.pixels), dtype=np.uint8).reshape(height, width, 3).copy())
     x = px.permute(2, 0, 1)[None].float() / 127.5 - 1.0
-    enc = {k: v.float() for k, v in encoder_weights.items() if k.startswith("encoder.")}
+    enc = {k: v.float() for k, v in encoder_weights.items() if k.startswith(("encoder.", "quant_conv."))}
     return OracleVaeEncoder(vae_cfg, enc, device=device).encode(x).float()

@@ -20,8 +20,8 @@ from typing import Any, Callable
 import torch
 
 from ..contracts.errors import Canceled, InferenceError, LoadError, Unsupported
-from ..contracts.gen_core.generator import (Capabilities, GenerationOutput, GenerationRequest, Generator, Modality,
-                                            ModelDescriptor)
+from ..contracts.gen_core.generator import (Capabilities, ConditioningKind, GenerationOutput, GenerationRequest, Generator,
+                                            Modality, ModelDescriptor)
 from ..contracts.gen_core.media import Image
 from ..contracts.gen_core.registry import Registration
 from ..contracts.gen_core.runtime import AdapterKind, LoadSpec, OffloadPolicy, ProgressDecoding, ProgressStep
@@ -199,6 +199,20 @@ class SdxlPipeline:
         ms = self.model_sampling()
         sigmas = schedule_sigmas(req.scheduler or self.default_scheduler, ms, steps)
         solver, ops = get_solver(req.sampler or self.default_sampler), TorchLatentOps()
+        from .chroma import convert_diffusers_vae_encoder
+        from .reference import encode_reference_image, init_time_step, reference_of
+
+        ref = reference_of(req, self.model_id)
+        clean, start = None, 0
+        if ref is not None and init_time_step(steps, ref[1]) > 0:
+            from ..io.safetensors_io import load_dir
+
+            raw = load_dir(self.root / "vae")
+            enc_w = convert_diffusers_vae_encoder(raw)
+            enc_w.update({k: t for k, t in raw.items() if k.startswith("quant_conv.")})
+            start = min(init_time_step(steps, ref[1]), len(sigmas) - 2)
+            clean = encode_reference_image(self.vae_cfg, enc_w, ref[0], req.width, req.height, dev, self.model_id).to(dev)
+            sigmas = sigmas[start:]                    # the run enters the schedule at sigma_start
         conds = [c for c in cond if c is not None]                 # [prompt] or [prompt, negative]
         context = torch.cat([c.context for c in conds], 0).to(dev, dt)
         pooled = torch.cat([c.pooled for c in conds], 0).to(dev, dt)
@@ -206,9 +220,14 @@ class SdxlPipeline:
         time_ids = torch.tensor([[req.height, req.width, 0, 0, req.height, req.width]] * nb, dtype=torch.float32, device=dev)
 
         def one_image(seed: int) -> Image:
-            k_noise, _ = ms.noise_scaling_coeffs(sigmas[0])
-            x = (seeded_noise_nchw(seed, self.vae_cfg.z_channels, lh, lw) * k_noise).to(dev, dt).contiguous()
-            state = {"step": 0}
+            k_noise, k_latent = ms.noise_scaling_coeffs(sigmas[0])
+            x = seeded_noise_nchw(seed, self.vae_cfg.z_channels, lh, lw).to(dev) * k_noise
+            if clean is not None:                       # variance-exploding form: clean + sigma * noise
+                x = x.float() + k_latent * clean
+            x = x.to(dt).contiguous()
+            state = {"step": start}
+            for s_done in range(1, start + 1):
+                on_progress(ProgressStep(s_done, steps))
 
             def run_model(x_in, timestep):
                 if req.cancel.is_cancelled():
@@ -244,7 +263,8 @@ def sdxl_descriptor(backend: str, prefix: str = "") -> ModelDescriptor:
     return ModelDescriptor(
         id=prefix + MODEL_ID, family="sdxl", backend=backend, modality=Modality.IMAGE,
         capabilities=Capabilities(
-            supports_negative_prompt=True, supports_guidance=True, supports_true_cfg=False, conditioning=[],
+            supports_negative_prompt=True, supports_guidance=True, supports_true_cfg=False,
+            conditioning=[ConditioningKind.REFERENCE],
             supports_lora=True, supports_lokr=False, samplers=list(SOLVERS), schedulers=list(SCHEDULERS),
             supported_guidance_methods=[], min_size=256, max_size=2048, max_count=8,
             supports_sequential_offload=True),
@@ -329,6 +349,12 @@ def write_synthetic_snapshot(root, seed: int = 0) -> Path:
     g = torch.Generator().manual_seed(seed + 2)
     vae_sd["post_quant_conv.weight"] = (torch.eye(4).view(4, 4, 1, 1) + 0.2 * torch.randn(4, 4, 1, 1, generator=g)).bfloat16()
     vae_sd["post_quant_conv.bias"] = (0.1 * torch.randn(4, generator=g)).bfloat16()
+    from ..models.vae import random_vae_encoder_weights
+    from .z_image import native_vae_encoder_to_diffusers
+
+    vae_sd.update({k: t.bfloat16() for k, t in native_vae_encoder_to_diffusers(random_vae_encoder_weights(vae, seed + 3)).items()})
+    vae_sd["quant_conv.weight"] = (torch.eye(8).view(8, 8, 1, 1) + 0.2 * torch.randn(8, 8, 1, 1, generator=g)).bfloat16()
+    vae_sd["quant_conv.bias"] = (0.1 * torch.randn(8, generator=g)).bfloat16()
     save_file(vae_sd, root / "vae" / "diffusion_pytorch_model.safetensors")
     (root / "swb_config.json").write_text(json.dumps({
         "unet": {"block_out_channels": list(unet.block_out_channels),

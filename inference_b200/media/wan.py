@@ -5,8 +5,8 @@ generate(): UMT5 encodes the prompt (512 positions; rows past the prompt's lengt
 over `sigma = shift * s / (1 + (shift - 1) * s)`, s from 1 to 1 / 1000, shift 12 -> at every step the high-noise expert
 (timestep >= 875) or the low-noise expert predicts the velocity with classifier-free guidance (4.0 / 3.0) ->
 the 16-channel video autoencoder turns (frames - 1) / 4 + 1 latent frames into `frames` RGB frames (default 81 frames,
-16 fps, 40 steps). The flow integrator is the shared framework's (default `euler`); the reference's own second-order
-multistep integrator is not restated.
+16 fps, 40 steps). The default integrator is the model's own second-order multistep predictor-corrector (`FlowUniPc`,
+also selected by `uni_pc`); any other sampler name routes to the shared solver framework (`euler`, ...).
 
 Snapshot layout (diffusers): `transformer/` (high-noise expert), `transformer_2/` (low-noise expert; optional for
 single-network checkpoints), `text_encoder/` + `tokenizer/`, `vae/`; `swb_config.json` overrides dimensions for synthetic
@@ -47,6 +47,70 @@ def wan_sigmas(steps: int, shift: float = FLOW_SHIFT) -> list[float]:
     out = [shift * s / (1.0 + (shift - 1.0) * s) for s in ramp]
     out[0] -= 1e-6
     return out + [0.0]
+
+
+class FlowUniPc:
+    """Second-order multistep predictor-corrector for flow matching (the checkpoint's default integrator: UniPC with
+    the B(h) = e^h - 1 variant, data prediction, lower order on the first and the last step;
+    candle-gen-wan/src/scheduler.rs:101-213). It works in half-log-SNR lambda = log((1 - sigma) / sigma): with
+    h = lambda_t - lambda_s, a step from sigma_s to sigma_t is
+    x_t = (sigma_t / sigma_s) x_s - (1 - sigma_t)(e^{-h} - 1)(x0_s + correction), where the correction extrapolates the
+    data prediction from the previous step (predictor) and, once the model has been evaluated at x_t, also interpolates
+    towards the new prediction (corrector, applied at the start of the next step)."""
+
+    def __init__(self, sigmas: list[float], order: int = 2):
+        self.sigmas, self.order = sigmas, order
+        self.steps = len(sigmas) - 1
+        self.history: list[torch.Tensor] = []         # data predictions of the last evaluated points, newest last
+        self.last_sample: torch.Tensor | None = None
+        self.last_order, self.warm = 1, 0
+
+    @staticmethod
+    def _lam(sigma: float) -> float:
+        import math
+
+        return math.inf if sigma <= 0.0 else math.log((1.0 - sigma) / sigma)
+
+    def _base(self, x, m0, s_from: float, s_to: float):
+        import math
+
+        h = self._lam(s_to) - self._lam(s_from)
+        em1 = math.expm1(-h)                              # e^{-h} - 1 (-1 at the terminal sigma 0)
+        return x * (s_to / s_from) - m0 * ((1.0 - s_to) * em1), h, em1
+
+    def _predict(self, x, i: int, order: int):
+        m0 = self.history[-1]
+        xt, h, em1 = self._base(x, m0, self.sigmas[i], self.sigmas[i + 1])
+        if order >= 2 and len(self.history) >= 2:
+            rk = (self._lam(self.sigmas[i - 1]) - self._lam(self.sigmas[i])) / h
+            xt = xt - (self.history[-2] - m0) * ((1.0 - self.sigmas[i + 1]) * em1 * 0.5 / rk)
+        return xt
+
+    def _correct(self, x0_new, i: int, order: int):
+        """Re-does the step i-1 -> i from the stored sample, now knowing the data prediction at its end point."""
+        m0 = self.history[-1]                              # prediction at sigma_{i-1}
+        s_from, s_to = self.sigmas[i - 1], self.sigmas[i]
+        xt, h, em1 = self._base(self.last_sample, m0, s_from, s_to)
+        a_t, d_new = 1.0 - s_to, x0_new - m0
+        if order == 1 or len(self.history) < 2:
+            return xt - d_new * (a_t * em1 * 0.5)
+        hh = -h
+        rk = (self._lam(self.sigmas[i - 2]) - self._lam(s_from)) / h
+        phi1 = em1 / hh - 1.0
+        b0, b1 = phi1 / em1, (phi1 / hh - 0.5) * 2.0 / em1
+        r0, r1 = (b0 - b1) / (1.0 - rk), (b1 - rk * b0) / (1.0 - rk)
+        return xt - ((self.history[-2] - m0) * (r0 / rk) + d_new * r1) * (a_t * em1)
+
+    def step(self, velocity: torch.Tensor, x: torch.Tensor, i: int) -> torch.Tensor:
+        """x at sigma_i and the model's velocity there -> x at sigma_{i+1}."""
+        x0 = x - velocity * self.sigmas[i]
+        if i > 0 and self.last_sample is not None:
+            x = self._correct(x0, i, self.last_order)
+        self.history = (self.history + [x0])[-2:]
+        order = min(self.order, self.steps - i, self.warm + 1)
+        self.last_sample, self.last_order = x, order
+        self.warm = min(self.warm + 1, self.order)
+        return self._predict(x, i, order)
 
 
 class Umt5PromptEncoder:
@@ -146,6 +210,7 @@ class WanPipeline:
         lt, lh, lw = (frames - 1) // 4 + 1, req.height // 8, req.width // 8
         dev, dt = self.device, self.dtype
         sigmas = wan_sigmas(steps, float(req.scheduler_shift) if req.scheduler_shift else FLOW_SHIFT)
+        native_unipc = req.sampler in (None, "uni_pc", "unipc")        # the model's own multistep integrator
         solver, ops, ms = get_solver(req.sampler or "euler"), TorchLatentOps(), FlowModelSampling()
         conds = [c for c in cond if c is not None]
         # the text projection does not depend on the step: once per expert and prompt
@@ -171,7 +236,13 @@ class WanPipeline:
                     on_progress(ProgressStep(state["step"], steps))
                 return vel.to(dt).contiguous()
 
-            x = solver.sample(ops, ms, lambda xx, s: denoise(ops, ms, xx, s, run_model), x, sigmas, seed)
+            if native_unipc:
+                stepper, xf = FlowUniPc(sigmas), x.float()
+                for i in range(steps):
+                    xf = stepper.step(run_model(xf.to(dt).contiguous(), sigmas[i]).float(), xf, i)
+                x = xf
+            else:
+                x = solver.sample(ops, ms, lambda xx, s: denoise(ops, ms, xx, s, run_model), x, sigmas, seed)
             while state["step"] < steps:
                 state["step"] += 1
                 on_progress(ProgressStep(state["step"], steps))

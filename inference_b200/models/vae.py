@@ -175,6 +175,8 @@ class OracleVaeEncoder(OracleVaeDecoder):
         h = self._attn(h, "encoder.mid.attn_1")
         h = self._res(h, "encoder.mid.block_2")
         moments = self._conv(self._gn(h, "encoder.norm_out", True), "encoder.conv_out", 1)
+        if "quant_conv.weight" in self.w:               # SDXL-style autoencoders: a 1x1 convolution over the moments
+            moments = self._conv(moments, "quant_conv", 0)
         return (moments[:, : cfg.z_channels] - cfg.shift_factor) * cfg.scale_factor
 
 

@@ -153,3 +153,21 @@ def test_post_quant_convolution_is_applied_in_front_of_the_decoder():
     want = torch.nn.functional.conv2d(z / VAE_SCALE + 0.25, w, b)
     torch.testing.assert_close(out / VAE_SCALE + 0.25, want, atol=1e-5, rtol=1e-5)
     assert apply_post_quant(z, None, cfg) is z
+
+
+def test_sdxl_reference_guided_generation(tmp_path):
+    from inference_b200.contracts.gen_core import GenerationRequest, LoadSpec
+    from inference_b200.contracts.gen_core.generator import Conditioning, ConditioningKind
+    from inference_b200.contracts.gen_core.media import Image
+    from inference_b200.media import provider_registry
+    from inference_b200.media.sdxl import write_synthetic_snapshot
+
+    gen = provider_registry("cpu").load("cpu_sdxl", LoadSpec.from_dir(write_synthetic_snapshot(tmp_path / "s")))
+    g = torch.Generator().manual_seed(3)
+    ref = Image(width=128, height=128, pixels=bytes(torch.randint(0, 256, (128 * 128 * 3,), generator=g, dtype=torch.uint8).tolist()))
+    base = dict(prompt="a red fox", width=256, height=256, steps=4, seed=5)
+    cond = lambda s: [Conditioning(ConditioningKind.REFERENCE, image=ref, strength=s)]      # noqa: E731
+    plain = gen.generate(GenerationRequest(**base)).images[0].pixels
+    guided = gen.generate(GenerationRequest(**base, conditioning=cond(0.5))).images[0].pixels
+    assert guided != plain and gen.generate(GenerationRequest(**base, conditioning=cond(0.5))).images[0].pixels == guided
+    assert gen.generate(GenerationRequest(**base, conditioning=cond(0.0))).images[0].pixels == plain

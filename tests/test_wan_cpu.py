@@ -155,3 +155,33 @@ def test_wan_trainer(tmp_path):
     tr.model.lora = None
     trainer_conformance(reg.load_kind("trainer", "cpu_wan_lora_trainer", LoadSpec.from_dir(snap)),
                         TrainerProfile(ds, tmp_path / "out", steps=3, rank=2))
+
+
+def test_flow_unipc_integrator():
+    from inference_b200.media.wan import FlowUniPc, wan_sigmas
+
+    g = torch.Generator().manual_seed(0)
+    target, noise = torch.randn(6, generator=g), torch.randn(6, generator=g)
+    # a model that always predicts the same clean sample: every consistent integrator must land on it exactly
+    sig = wan_sigmas(6, 3.0)
+    x, st = noise * sig[0] + target * (1 - sig[0]), FlowUniPc(sig)
+    first = None
+    for i in range(6):
+        v = (x - target) / sig[i]
+        nxt = st.step(v, x, i)
+        if i == 0:
+            first = nxt
+            torch.testing.assert_close(first, x + v * (sig[1] - sig[0]))          # the warm-up step is the Euler step
+        x = nxt
+    torch.testing.assert_close(x, target, atol=1e-5, rtol=1e-5)
+    # a curved problem, x0(x, sigma) = tanh(x): the multistep integrator is closer to a fine Euler run than coarse Euler
+    def run(n, unipc):
+        s = wan_sigmas(n, 3.0)
+        z = noise.double() * s[0]
+        stp = FlowUniPc(s)
+        for i in range(n):
+            v = (z - torch.tanh(z)) / s[i]
+            z = stp.step(v, z, i) if unipc else z + v * (s[i + 1] - s[i])
+        return z
+    fine = run(400, False)
+    assert (run(10, True) - fine).abs().max() < (run(10, False) - fine).abs().max()
