@@ -22,6 +22,12 @@ from .dit_flux import timestep_embedding
 from .text_encoders import linear
 
 
+def _narrow_on_kernel() -> bool:
+    from ..ops.attention import narrow_heads_on_kernel
+
+    return narrow_heads_on_kernel()
+
+
 @dataclass
 class Sd3Config:
     in_channels: int = 16
@@ -149,7 +155,7 @@ class Sd3DiT:
     def _sdpa(self, q, k, v):
         """q, k, v [B, heads, S, hd] -> [B, S, heads * hd]; on the device the zero-padded tcgen05 kernel."""
         B, _, S, D = q.shape
-        if q.is_cuda and q.dtype == torch.bfloat16 and D <= 128 and D % 8 == 0:
+        if q.is_cuda and q.dtype == torch.bfloat16 and D <= 128 and D % 8 == 0 and _narrow_on_kernel():
             from .. import ops
 
             return ops.dense_attention_padded(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), scale=D ** -0.5)

@@ -19,6 +19,12 @@ from .dit_flux import timestep_embedding
 from .text_encoders import linear
 
 
+def _narrow_on_kernel() -> bool:
+    from ..ops.attention import narrow_heads_on_kernel
+
+    return narrow_heads_on_kernel()
+
+
 @dataclass
 class SdxlUnetConfig:
     in_channels: int = 4
@@ -194,7 +200,7 @@ class SdxlUnet:
         k = self._lin(ctx, p + ".to_k").view(B, ctx.shape[1], nh, -1)
         v = self._lin(ctx, p + ".to_v").view(B, ctx.shape[1], nh, -1)
         hd = q.shape[-1]
-        if q.is_cuda and q.dtype == torch.bfloat16 and hd <= 128 and hd % 8 == 0:
+        if q.is_cuda and q.dtype == torch.bfloat16 and hd <= 128 and hd % 8 == 0 and _narrow_on_kernel():
             from .. import ops
 
             o = ops.dense_attention_padded(q, k, v, scale=hd ** -0.5)          # tcgen05 kernel, heads zero-padded to 128

@@ -1,5 +1,6 @@
 """Python wrappers over the sm_100a kernel library (tensors in, tensors out, current CUDA stream)."""
-from .attention import dense_attention, dense_attention_padded, paged_attention, varlen_causal_attention  # noqa: F401
+from .attention import (dense_attention, dense_attention_padded, narrow_heads_on_kernel, paged_attention,  # noqa: F401
+                        varlen_causal_attention)
 from .gemm import SSQ_FLOATS, gemm_bf16, gemm_bf16_grouped, gemm_bf16_normed, gated_fused, gemm_workspace, linear, linear_gated  # noqa: F401
 from .llm import (argmax, embedding, gated_act_mul, gated_residual, layernorm_mod, rmsnorm, rope_kv_write,  # noqa: F401
                   spec_verify_greedy)

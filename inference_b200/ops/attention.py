@@ -66,6 +66,15 @@ def dense_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale:
     return out
 
 
+def narrow_heads_on_kernel() -> bool:
+    """Heads narrower than 128 run zero-padded on the tcgen05 kernel unless SWB_NARROW_ATTN=library selects the
+    framework's scaled-dot-product call (measured on SD3.5-Large at 1024 x 1024: 4.66 s / image padded, 3.99 s through
+    the library call, whose kernels are specialised for 64-wide heads)."""
+    import os
+
+    return os.environ.get("SWB_NARROW_ATTN", "kernel") != "library"
+
+
 def dense_attention_padded(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float) -> torch.Tensor:
     """dense_attention for head widths below 128 (64 in SD3 / SDXL blocks, 72 in the Qwen3-VL tower): q, k and v are
     zero-padded to 128 per head, which changes neither q . k nor the first D output columns, so the tcgen05 kernel
