@@ -440,11 +440,12 @@ class Qwen3VlProvider(LlamaProvider):
 
     IMAGE_BLOCK = "<|vision_start|><|image_pad|><|vision_end|>"
 
-    def __init__(self, base: LlamaProvider, tower, image_token_id: int):
+    def __init__(self, base: LlamaProvider, tower, image_token_id: int, video_token_id: int | None = None):
         caps = base._descriptor.capabilities
         caps.supports_vision = True
+        caps.supports_video = video_token_id is not None
         super().__init__(base._descriptor, base.backend, base.tokenizer, base.template, base.stop_tokens, base.cfg)
-        self.tower, self.image_token_id = tower, image_token_id
+        self.tower, self.image_token_id, self.video_token_id = tower, image_token_id, video_token_id
 
     @staticmethod
     def load(spec: LoadSpec, provider_id: str, backend_name: str, comm=None) -> "Qwen3VlProvider":
@@ -481,53 +482,78 @@ class Qwen3VlProvider(LlamaProvider):
             image_token = tokenizer.token_to_id("<|image_pad|>")
         if image_token is None:
             raise LoadError(f"{p}: no image_token_id in config.json and no <|image_pad|> token in the tokenizer")
-        return Qwen3VlProvider(base, tower, int(image_token))
+        video_token = top.get("video_token_id")
+        if video_token is None:
+            video_token = tokenizer.token_to_id("<|video_pad|>")
+        return Qwen3VlProvider(base, tower, int(image_token), int(video_token) if video_token is not None else None)
 
     def _render_messages(self, req: TextLlmRequest):
-        from ..contracts.core_llm.message import ImageRef, Message, Text
+        """Images become one vision block each; a video becomes one block per temporal patch (two frames), each
+        announced by the patch's time in seconds."""
+        from ..contracts.core_llm.message import ImageRef, Message, Text, VideoRef
+        from ..models.qwen3_vl import video_placeholder_text
 
+        T = self.tower.cfg.temporal_patch_size
         out = []
         for m in req.messages:
-            n = sum(isinstance(c, ImageRef) for c in m.content)
-            if n == 0:
+            blocks = ""
+            for c in m.content:
+                if isinstance(c, ImageRef):
+                    blocks += self.IMAGE_BLOCK
+                elif isinstance(c, VideoRef):
+                    ts = list(c.timestamps)
+                    while len(ts) % T:
+                        ts.append(ts[-1])
+                    blocks += video_placeholder_text([sum(ts[i:i + T]) / T for i in range(0, len(ts), T)])
+            if not blocks:
                 out.append(m)
                 continue
-            out.append(Message(m.role, [Text(self.IMAGE_BLOCK * n + m.text_content())], m.thinking, list(m.tool_calls)))
+            out.append(Message(m.role, [Text(blocks + m.text_content())], m.thinking, list(m.tool_calls)))
         return out
 
     def _splice_media(self, req: TextLlmRequest, prompt_ids: list[int]):
         import numpy as np
 
         from ..contracts.core_llm import InvalidRequest
-        from ..contracts.core_llm.message import ImageRef
-        from ..models.qwen3_vl import image_to_patches, mrope_positions
+        from ..contracts.core_llm.message import ImageRef, VideoRef
+        from ..models.qwen3_vl import image_to_patches, mrope_positions, video_to_patches
         from .backend import set_embed_override, set_mrope_override
 
-        images = [c for m in req.messages for c in m.content if isinstance(c, ImageRef)]
-        if not images:
+        media = [c for m in req.messages for c in m.content if isinstance(c, (ImageRef, VideoRef))]
+        if not media:
             return prompt_ids, None
-        tid = self.image_token_id
-        if prompt_ids.count(tid) != len(images):
-            raise InvalidRequest(f"[{self._descriptor.id}] the rendered prompt holds {prompt_ids.count(tid)} image "
-                                 f"placeholders for {len(images)} images")
         vc = self.tower.cfg
-        patches, grids = [], []
-        for im in images:
-            rgb = torch.from_numpy(np.frombuffer(bytes(im.pixels), dtype=np.uint8).reshape(im.height, im.width, 3).copy())
-            pt, g = image_to_patches(rgb, vc)
+        rgb = lambda im: torch.from_numpy(np.frombuffer(bytes(im.pixels), dtype=np.uint8)                  # noqa: E731
+                                          .reshape(im.height, im.width, 3).copy())
+        patches, tower_grids, runs = [], [], []          # runs: one (placeholder id, (1, h, w)) per vision run of the prompt
+        for c in media:
+            if isinstance(c, ImageRef):
+                pt, g = image_to_patches(rgb(c), vc)
+                runs.append((self.image_token_id, g))
+            else:
+                if self.video_token_id is None:
+                    raise InvalidRequest(f"[{self._descriptor.id}] this snapshot has no video placeholder token")
+                pt, g, _ = video_to_patches([rgb(f) for f in c.frames], list(c.timestamps), vc)
+                runs += [(self.video_token_id, (1, g[1], g[2]))] * g[0]
             patches.append(pt)
-            grids.append(g)
-        tokens, taps = self.tower.forward(torch.cat(patches, 0), grids)
-        per_image = [g[0] * (g[1] // vc.spatial_merge_size) * (g[2] // vc.spatial_merge_size) for g in grids]
+            tower_grids.append(g)
+        vision_ids = {self.image_token_id} | ({self.video_token_id} if self.video_token_id is not None else set())
+        found = [t for t in prompt_ids if t in vision_ids]
+        if found != [tid for tid, _ in runs]:
+            raise InvalidRequest(f"[{self._descriptor.id}] the rendered prompt holds {len(found)} vision placeholders for "
+                                 f"{len(runs)} vision runs")
+        tokens, taps = self.tower.forward(torch.cat(patches, 0), tower_grids)
+        m2 = vc.spatial_merge_size ** 2
         ids, rows, k = [], [], 0
         for t in prompt_ids:
-            if t == tid:
-                rows += list(range(len(ids), len(ids) + per_image[k]))
-                ids += [tid] * per_image[k]
+            if t in vision_ids:
+                n = runs[k][1][1] * runs[k][1][2] // m2
+                rows += list(range(len(ids), len(ids) + n))
+                ids += [t] * n
                 k += 1
             else:
                 ids.append(t)
-        pos, nxt = mrope_positions(ids, grids, tid, vc.spatial_merge_size)
+        pos, nxt = mrope_positions(ids, [g for _, g in runs], vision_ids, vc.spatial_merge_size)
         seq = self.backend.new_sequence()
         set_embed_override(seq, rows, tokens)
         set_mrope_override(seq, pos, nxt, torch.tensor(rows), taps)

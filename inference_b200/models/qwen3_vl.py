@@ -183,15 +183,47 @@ def image_to_patches(rgb: torch.Tensor, cfg: Qwen3VlVisionConfig, **limits) -> t
     return x.reshape(h * w, cfg.patch_dim).contiguous(), (1, h, w)
 
 
+def video_to_patches(frames: list[torch.Tensor], timestamps: list[float], cfg: Qwen3VlVisionConfig, **limits
+                     ) -> tuple[torch.Tensor, tuple[int, int, int], list[float]]:
+    """uint8 [H, W, 3] frames -> (patches [t*h*w, patch_dim] in merge order, (t, h, w), one timestamp per temporal patch).
+    Frames are grouped in pairs (the last frame repeats when the count is odd); a pair's timestamp is the mean of its
+    frames' times."""
+    P, m, T = cfg.patch_size, cfg.spatial_merge_size, cfg.temporal_patch_size
+    frames, timestamps = list(frames), list(timestamps)
+    while len(frames) % T:
+        frames.append(frames[-1])
+        timestamps.append(timestamps[-1])
+    H, W = smart_resize(frames[0].shape[0], frames[0].shape[1], P * m, **limits)
+    h, w = H // P, W // P
+    px = []
+    for f in frames:
+        x = f.permute(2, 0, 1)[None].float()
+        if (H, W) != tuple(f.shape[:2]):
+            x = F.interpolate(x, size=(H, W), mode="bicubic", align_corners=False, antialias=True).clamp(0, 255)
+        px.append((x[0] / 255.0 - 0.5) / 0.5)
+    v = torch.stack(px, 0).view(len(frames) // T, T, 3, h // m, m, P, w // m, m, P)
+    v = v.permute(0, 3, 6, 4, 7, 2, 1, 5, 8)                                  # [t, h/m, w/m, m, m, 3, T, P, P]
+    t = len(frames) // T
+    stamps = [sum(timestamps[i * T:(i + 1) * T]) / T for i in range(t)]
+    return v.reshape(t * h * w, cfg.patch_dim).contiguous(), (t, h, w), stamps
+
+
+def video_placeholder_text(stamps: list[float]) -> str:
+    """One vision run per temporal patch, each announced by its time: `<0.2 seconds><|vision_start|><|video_pad|><|vision_end|>`."""
+    return "".join(f"<{s:.1f} seconds><|vision_start|><|video_pad|><|vision_end|>" for s in stamps)
+
+
 # ---- decoder side ------------------------------------------------------------------------------------------------------------
-def mrope_positions(ids: list[int], grids: list[tuple[int, int, int]], image_token_id: int, merge: int = 2
+def mrope_positions(ids: list[int], grids: list[tuple[int, int, int]], image_token_id, merge: int = 2
                     ) -> tuple[torch.Tensor, int]:
-    """(positions [3, S], next position) for a prompt whose runs of `image_token_id` are, in order, the images of
-    `grids` (t, h, w before merging; t = 1)."""
+    """(positions [3, S], next position) for a prompt whose runs of vision placeholder tokens are, in order, the grids
+    of `grids` (t, h, w before merging). `image_token_id` is one id or a collection (image and video placeholders); a
+    video contributes one (1, h, w) grid per temporal patch, since every patch is its own run behind its timestamp."""
+    vision = {image_token_id} if isinstance(image_token_id, int) else set(image_token_id)
     pos = torch.zeros(3, len(ids), dtype=torch.int64)
     nxt, i, g = 0, 0, 0
     while i < len(ids):
-        if ids[i] != image_token_id:
+        if ids[i] not in vision:
             pos[:, i] = nxt
             nxt += 1
             i += 1
@@ -200,7 +232,7 @@ def mrope_positions(ids: list[int], grids: list[tuple[int, int, int]], image_tok
         g += 1
         rows, cols = h // merge, w // merge
         n = t * rows * cols
-        if ids[i:i + n] != [image_token_id] * n:
+        if len(set(ids[i:i + n])) != 1 or len(ids[i:i + n]) != n:
             raise ValueError(f"image {g - 1} needs a run of {n} placeholder tokens at position {i}")
         pos[0, i:i + n] = nxt
         pos[1, i:i + n] = nxt + torch.arange(rows).repeat_interleave(cols).repeat(t)

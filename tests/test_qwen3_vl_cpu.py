@@ -31,12 +31,12 @@ def test_vision_tower_matches_hugging_face():
     assert (vc.depth, vc.hidden_size, vc.patch_dim, vc.grid_side) == (4, 48, 96, 6)
     tower = V.Qwen3VlVisionTower(vc, dict(model.state_dict()))
     g = torch.Generator().manual_seed(1)
-    grids = [(1, 4, 6), (1, 2, 2)]
-    patches = torch.randn(4 * 6 + 2 * 2, vc.patch_dim, generator=g)
+    grids = [(1, 4, 6), (1, 2, 2), (2, 2, 4)]                       # two stills and a two-patch video
+    patches = torch.randn(4 * 6 + 2 * 2 + 2 * 2 * 4, vc.patch_dim, generator=g)
     with torch.no_grad():
         ref = model.model.visual(patches, grid_thw=torch.tensor(grids))
     out, taps = tower.forward(patches, grids)
-    assert out.shape == (7, 64) and len(taps) == 3
+    assert out.shape == (7 + 4, 64) and len(taps) == 3
     torch.testing.assert_close(out, ref.pooler_output, atol=2e-5, rtol=1e-4)
     for a, b in zip(taps, ref.deepstack_features):
         torch.testing.assert_close(a, b, atol=2e-5, rtol=1e-4)
@@ -162,6 +162,91 @@ def test_text_provider_answers_about_an_image(tmp_path):
     want = []
     for t in ref:
         if t in stops:
+            break
+        want.append(t)
+    words = {i: w for w, i in tok["model"]["vocab"].items()}
+    got = out.text.split()
+    assert len(got) >= 1 and got == [words[t] for t in want][: len(got)]
+
+
+def test_video_patches_placeholders_and_positions():
+    vc = V.Qwen3VlVisionConfig(patch_size=4, hidden_size=48, num_heads=4)
+    g = torch.Generator().manual_seed(0)
+    frames = [torch.randint(0, 256, (16, 16, 3), generator=g, dtype=torch.uint8) for _ in range(3)]
+    patches, grid, stamps = V.video_to_patches(frames, [0.0, 0.5, 1.0], vc, min_pixels=16, max_pixels=10 ** 6)
+    assert grid == (2, 4, 4) and patches.shape == (2 * 16, 3 * 2 * 4 * 4) and stamps == [0.25, 1.0]
+    norm = lambda f: (f.float() / 255 - 0.5) / 0.5                                    # noqa: E731
+    p0 = patches[0].view(3, 2, 4, 4)
+    torch.testing.assert_close(p0[:, 0], norm(frames[0])[:4, :4].permute(2, 0, 1))
+    torch.testing.assert_close(p0[:, 1], norm(frames[1])[:4, :4].permute(2, 0, 1))
+    last = patches[16].view(3, 2, 4, 4)                                              # second temporal patch: frame 2 twice
+    torch.testing.assert_close(last[:, 0], last[:, 1])
+    # the timestamp text of the published alignment case: frames at 0, 0.5, 1.0, 1.5 s
+    assert V.video_placeholder_text([0.25, 1.25]) == ("<0.2 seconds><|vision_start|><|video_pad|><|vision_end|>"
+                                                      "<1.2 seconds><|vision_start|><|video_pad|><|vision_end|>")
+    # positions: every temporal patch is its own run with its own (1, h, w) grid
+    ids = [27, 15, 152] + [151] * 4 + [153, 27, 16, 152] + [151] * 4 + [153, 9]
+    pos, nxt = V.mrope_positions(ids, [(1, 4, 4), (1, 4, 4)], {150, 151})
+    assert pos[0, 3:7].tolist() == [3] * 4 and pos[1, 3:7].tolist() == [3, 3, 4, 4] and pos[2, 3:7].tolist() == [3, 4, 3, 4]
+    assert pos[:, 7].tolist() == [5, 5, 5] and nxt == int(pos.max()) + 1
+    cfg, model = _hf()
+    mm = torch.tensor([[2 if t == 151 else 0 for t in ids]], dtype=torch.int32)
+    ref, _ = model.model.get_rope_index(torch.tensor([ids]), mm_token_type_ids=mm, video_grid_thw=torch.tensor([[2, 4, 4]]))
+    assert torch.equal(pos, ref[:, 0])
+
+
+def test_text_provider_answers_about_a_video(tmp_path):
+    import json
+
+    from inference_b200.bundles import runtime_cpu
+    from inference_b200.contracts.core_llm import LoadSpec, Message, Role, TextLlmRequest
+    from inference_b200.contracts.core_llm.message import ImageRef, Text, VideoRef
+    from inference_b200.contracts.core_llm.request import Sampling
+    from inference_b200.contracts.core_llm.template import RenderOptions
+    from inference_b200.io.safetensors_io import save_file
+    from inference_b200.testkit.synthetic import wordlevel_tokenizer_json
+    import inference_b200.models.qwen3_vl as Q3
+
+    cfg, hf = _hf(seed=6)
+    top = cfg.to_dict()
+    top["model_type"], top["architectures"] = "qwen3_vl", ["Qwen3VLForConditionalGeneration"]
+    (tmp_path / "config.json").write_text(json.dumps(top))
+    save_file({k: v.contiguous() for k, v in hf.state_dict().items()}, tmp_path / "model.safetensors")
+    tok = json.loads(wordlevel_tokenizer_json(200))
+    special = {150: "<|image_pad|>", 151: "<|video_pad|>", 152: "<|vision_start|>", 153: "<|vision_end|>"}
+    tok["model"]["vocab"] = {special.get(i, w): i for w, i in tok["model"]["vocab"].items()}
+    tok["added_tokens"] = tok.get("added_tokens", []) + [
+        {"id": i, "content": c, "single_word": False, "lstrip": False, "rstrip": False, "normalized": False, "special": True}
+        for i, c in special.items()]
+    (tmp_path / "tokenizer.json").write_text(json.dumps(tok))
+    (tmp_path / "tokenizer_config.json").write_text(json.dumps({"eos_token": "<|im_end|>"}))
+    llm = runtime_cpu.catalog().text().load_for_model(LoadSpec.dense(str(tmp_path)))
+    assert llm.descriptor().capabilities.supports_video
+    g = torch.Generator().manual_seed(5)
+    frames = [torch.randint(0, 256, (16, 16, 3), generator=g, dtype=torch.uint8) for _ in range(4)]
+    video = VideoRef(tuple(ImageRef(16, 16, bytes(f.flatten().tolist())) for f in frames), (0.0, 0.5, 1.0, 1.5))
+    req = TextLlmRequest(messages=[Message(Role.USER, [video, Text("the cat sat")])], max_new_tokens=4, seed=0,
+                         sampling=Sampling(temperature=0.0))
+    lim = dict(min_pixels=16, max_pixels=10 ** 6)
+    orig_v = Q3.video_to_patches
+    Q3.video_to_patches = lambda fr, ts, vc, **kw: orig_v(fr, ts, vc, **lim)
+    try:
+        ids, seq = llm._splice_media(req, llm.tokenizer.encode(
+            llm.template.render_with(llm._render_messages(req), RenderOptions(True, None, [])), add_special_tokens=False))
+        assert ids.count(151) == 2 * 4 and ids.count(152) == 2                 # two temporal patches, four merged tokens each
+        llm.backend.release(seq)
+        out = llm.generate(req, on_event=lambda e: None)
+    finally:
+        Q3.video_to_patches = orig_v
+    patches, grid, _ = orig_v(frames, [0.0, 0.5, 1.0, 1.5], Q3.Qwen3VlVisionConfig.from_json(top), **lim)
+    mm = torch.tensor([[2 if t == 151 else 0 for t in ids]], dtype=torch.int32)
+    with torch.no_grad():
+        ref = hf.generate(input_ids=torch.tensor([ids]), pixel_values_videos=patches, video_grid_thw=torch.tensor([grid]),
+                          mm_token_type_ids=mm, attention_mask=torch.ones(1, len(ids), dtype=torch.long), max_new_tokens=4,
+                          do_sample=False, pad_token_id=0)[0, len(ids):].tolist()
+    want = []
+    for t in ref:
+        if t in set(llm.stop_tokens):
             break
         want.append(t)
     words = {i: w for w, i in tok["model"]["vocab"].items()}
