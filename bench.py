@@ -26,7 +26,7 @@ import time
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
-REFERENCE_UNAVAILABLE = ("reference is a Rust/Candle Cargo workspace: pip install of /root/reference fails (no "
+REFERENCE_UNAVAILABLE = ("reference is a Rust/Candle Cargo workspace: pip install of the reference tree fails (no "
                          "setup.py/pyproject.toml), no cargo/rustc in the image, git crate deps need network")
 
 

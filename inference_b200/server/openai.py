@@ -1,4 +1,4 @@
-"""OpenAI chat-completions wire format <-> the TextLlm contract (role of mlx-llm-server's openai.rs, SURVEY of its
+"""OpenAI chat-completions wire format <-> the TextLlm contract (role of mlx-llm-server's openai.rs; its
 behaviour: POST /v1/chat/completions with `messages`, `max_tokens`, `temperature`, `top_p`, `seed`, `stop`, `stream`,
 `response_format: {"type": "json_object"}`, `tools`; responses `chat.completion` / `chat.completion.chunk`)."""
 from __future__ import annotations
