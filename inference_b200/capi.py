@@ -148,8 +148,8 @@ def _op(rt: _Runtime | None, op: str, p: dict):
 
         g = rt.get(p["handle"])
         fields = {k: v for k, v in p["request"].items()
-                  if k in ("prompt", "width", "height", "count", "steps", "seed", "guidance", "sampler", "scheduler",
-                           "scheduler_shift", "negative_prompt")}
+                  if k in ("prompt", "width", "height", "count", "steps", "seed", "guidance", "true_cfg", "sampler", "scheduler",
+                           "scheduler_shift", "negative_prompt", "frames", "fps")}
         req = GenerationRequest(**fields)
         emit = _emitter(p.get("callback", 0), p.get("user", 0), req.cancel)
 
@@ -161,9 +161,10 @@ def _op(rt: _Runtime | None, op: str, p: dict):
             elif isinstance(ev, ProgressLoading):
                 emit({"type": "loading", "phase": ev.phase.value})
         out = g.generate(req, on_progress)
-        rt.images[p["handle"]] = out.images
-        return json.dumps({"images": [{"width": i.width, "height": i.height, "bytes": len(i.pixels)}
-                                      for i in out.images]})
+        pictures = out.images or out.video_frames            # a video's frames are fetched like images, by index
+        rt.images[p["handle"]] = pictures
+        return json.dumps({"kind": out.kind, "fps": out.fps,
+                           "images": [{"width": i.width, "height": i.height, "bytes": len(i.pixels)} for i in pictures]})
     if op == "gen_image_copy":
         imgs = rt.images.get(p["handle"], [])
         if not 0 <= p["index"] < len(imgs):

@@ -96,6 +96,17 @@ def test_text_and_media_through_the_c_abi(lib, tmp_path):
     assert lib.swb_gen_image_copy(rt, g, 0, buf, meta["bytes"]) == meta["bytes"]
     assert lib.swb_gen_image_copy(rt, g, 0, buf, 10) == -1 and lib.swb_gen_image_copy(rt, g, 3, buf, meta["bytes"]) == -1
     assert lib.swb_gen_generate(rt, g, json.dumps(dict(greq, width=250)).encode(), CB(0), None, ctypes.byref(out)) < 0
+    # a video generator: the frames come back through the same image-copy call
+    from inference_b200.media.wan import write_synthetic_snapshot as write_wan
+
+    wan = write_wan(tmp_path / "wan")
+    v = ctypes.c_uint64()
+    assert lib.swb_gen_load(rt, b"cpu_wan2_2_t2v_14b", json.dumps({"weights": str(wan)}).encode(), ctypes.byref(v)) == 0
+    vreq = {"prompt": "a fox runs", "width": 256, "height": 256, "steps": 2, "seed": 1, "frames": 5, "fps": 12}
+    assert lib.swb_gen_generate(rt, v, json.dumps(vreq).encode(), CB(0), None, ctypes.byref(out)) == 0
+    vmeta = json.loads(out.value)
+    assert vmeta["kind"] == "video" and vmeta["fps"] == 12 and len(vmeta["images"]) == 5
+    assert lib.swb_gen_image_copy(rt, v, 4, buf, meta["bytes"]) == meta["bytes"]
     lib.swb_rt_close(rt)
 
 
