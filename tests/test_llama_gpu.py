@@ -317,3 +317,51 @@ def test_folded_norm_decode_chain_matches_oracle_with_non_unit_norm_weights(arch
             if step == 0 or same[i]:
                 d = (folded[step][i] - plain[step][i]).abs().max().item()
                 assert d < 0.05 * max(1.0, plain[step][i].abs().max().item()), (step, i, d)
+
+
+def test_qwen3_vl_provider_on_the_device(tmp_path):
+    """The vision-language provider of the sm_100a bundle: tower and decoder in bf16 on the device; an image prompt
+    decodes, and the tower's tokens track the fp32 tower."""
+    import json
+    import sys
+    from pathlib import Path
+
+    sys.path.insert(0, str(Path(__file__).parent))
+    from test_qwen3_vl_cpu import _hf
+
+    import inference_b200.models.qwen3_vl as Q3
+    from inference_b200.bundles import runtime_b200
+    from inference_b200.contracts.core_llm import LoadSpec, Message, Role, TextLlmRequest
+    from inference_b200.contracts.core_llm.message import ImageRef, Text
+    from inference_b200.contracts.core_llm.request import Sampling
+    from inference_b200.io.safetensors_io import save_file
+    from inference_b200.testkit.synthetic import wordlevel_tokenizer_json
+
+    cfg, hf = _hf(seed=5)
+    top = cfg.to_dict()
+    top["model_type"], top["architectures"] = "qwen3_vl", ["Qwen3VLForConditionalGeneration"]
+    (tmp_path / "config.json").write_text(json.dumps(top))
+    sd = {k: v.contiguous() for k, v in hf.state_dict().items()}
+    save_file(sd, tmp_path / "model.safetensors")
+    tok = json.loads(wordlevel_tokenizer_json(200))
+    special = {150: "<|image_pad|>", 151: "<|video_pad|>", 152: "<|vision_start|>", 153: "<|vision_end|>"}
+    tok["model"]["vocab"] = {special.get(i, w): i for w, i in tok["model"]["vocab"].items()}
+    tok["added_tokens"] = tok.get("added_tokens", []) + [
+        {"id": i, "content": c, "single_word": False, "lstrip": False, "rstrip": False, "normalized": False, "special": True}
+        for i, c in special.items()]
+    (tmp_path / "tokenizer.json").write_text(json.dumps(tok))
+    (tmp_path / "tokenizer_config.json").write_text(json.dumps({"eos_token": "<|im_end|>"}))
+    llm = runtime_b200.catalog().text().load_for_model(LoadSpec.dense(str(tmp_path)))
+    assert llm.descriptor().id == "b200-qwen3-vl"
+    vc = Q3.Qwen3VlVisionConfig.from_json(top)
+    patches = torch.randn(24, vc.patch_dim, generator=torch.Generator().manual_seed(4))
+    ref, _ = Q3.Qwen3VlVisionTower(vc, sd).forward(patches, [(1, 4, 6)])
+    out, taps = llm.tower.forward(patches, [(1, 4, 6)])
+    assert out.is_cuda and len(taps) == 3
+    assert (out.float().cpu() - ref).abs().max().item() < 0.08 * max(1.0, ref.abs().max().item())
+    g = torch.Generator().manual_seed(5)
+    raw = bytes(torch.randint(0, 256, (64 * 96 * 3,), generator=g, dtype=torch.uint8).tolist())
+    req = TextLlmRequest(messages=[Message(Role.USER, [ImageRef(96, 64, raw), Text("the cat sat")])], max_new_tokens=4,
+                         seed=0, sampling=Sampling(temperature=0.0))
+    res = llm.generate(req, on_event=lambda e: None)
+    assert res.usage.generated_tokens >= 1
