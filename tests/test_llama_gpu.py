@@ -360,8 +360,13 @@ def test_qwen3_vl_provider_on_the_device(tmp_path):
     assert out.is_cuda and len(taps) == 3
     assert (out.float().cpu() - ref).abs().max().item() < 0.08 * max(1.0, ref.abs().max().item())
     g = torch.Generator().manual_seed(5)
-    raw = bytes(torch.randint(0, 256, (64 * 96 * 3,), generator=g, dtype=torch.uint8).tolist())
-    req = TextLlmRequest(messages=[Message(Role.USER, [ImageRef(96, 64, raw), Text("the cat sat")])], max_new_tokens=4,
+    raw = bytes(torch.randint(0, 256, (16 * 24 * 3,), generator=g, dtype=torch.uint8).tolist())
+    req = TextLlmRequest(messages=[Message(Role.USER, [ImageRef(24, 16, raw), Text("the cat sat")])], max_new_tokens=4,
                          seed=0, sampling=Sampling(temperature=0.0))
-    res = llm.generate(req, on_event=lambda e: None)
+    orig = Q3.image_to_patches                    # this tiny tower has 4-pixel patches: keep the image at its own size
+    Q3.image_to_patches = lambda rgb, vc_, **kw: orig(rgb, vc_, min_pixels=16, max_pixels=10 ** 6)
+    try:
+        res = llm.generate(req, on_event=lambda e: None)
+    finally:
+        Q3.image_to_patches = orig
     assert res.usage.generated_tokens >= 1
