@@ -22,6 +22,7 @@ def main():
     ap.add_argument("--model", default="flux1_dev")
     ap.add_argument("--steps", type=int, default=0, help="0 = the model's default")
     ap.add_argument("--images", type=int, default=2)
+    ap.add_argument("--frames", type=int, default=0, help="video models: frames per clip (0 = the model's default)")
     args = ap.parse_args()
     from inference_b200.bundles import runtime_b200
     from inference_b200.contracts.gen_core import GenerationRequest, LoadSpec
@@ -31,8 +32,11 @@ def main():
         json.dump({"text": "hash", "random_init": 0}, f)
     gen = runtime_b200.catalog().media().load(args.model, LoadSpec.from_dir(d))
     extra = {"guidance": 3.5} if args.model == "flux1_dev" else {}
-    if args.model in ("chroma1_hd", "chroma1_base", "z_image", "qwen_image", "sd3_5_large", "sd3_5_medium", "sdxl"):
+    if args.model in ("chroma1_hd", "chroma1_base", "z_image", "qwen_image", "sd3_5_large", "sd3_5_medium", "sdxl", "kolors",
+                      "wan2_2_t2v_14b"):
         extra["negative_prompt"] = "blurry, low quality"
+    if args.frames:
+        extra["frames"] = args.frames
     events = []
     req = lambda seed: GenerationRequest(prompt="a photo of a fox", width=args.size, height=args.size,  # noqa: E731
                                          steps=args.steps or None, seed=seed, **extra)
@@ -45,10 +49,11 @@ def main():
         t0 = time.perf_counter()
         out = gen.generate(req(1 + i), lambda e: None)
         times.append(time.perf_counter() - t0)          # the image bytes are on the host when generate returns
-        assert len(out.images[0].pixels) == args.size * args.size * 3
+        pictures = out.images or out.video_frames
+        assert len(pictures[0].pixels) == args.size * args.size * 3
     print(json.dumps({"metric": f"{args.model}_seconds_per_image", "size": args.size,
                       "steps": args.steps or "model default",
-                      "s_per_image": round(min(times), 3), "s_per_image_all": [round(t, 3) for t in times],
+                      "s_per_image": round(min(times), 3), "frames": len(pictures) if out.video_frames else None, "s_per_image_all": [round(t, 3) for t in times],
                       "first_image_s_including_load_and_capture": round(first_s, 2), "n_gpus": 1,
                       "data": "random-init weights, hash prompt encoder"}))
 
