@@ -380,15 +380,16 @@ class ZImageDiTGpu:
 
     def forward_graphed(self, z, t, cap_tokens, ropes=None):
         """Same result as forward(); the first call for a shape captures a CUDA graph, later calls replay it."""
-        key = (tuple(z.shape), cap_tokens.data_ptr(), tuple(cap_tokens.shape))
+        key = (tuple(z.shape), tuple(cap_tokens.shape))
         st = self.__dict__.setdefault("_graphs", {})
         g = st.get(key)
         if g is None:
             if ropes is None:
                 ropes = self.rope_tables(z.shape[2] // self.cfg.patch_size, z.shape[3] // self.cfg.patch_size,
                                          cap_tokens.shape[0])
-            static = {"z": z.to(self.device, torch.bfloat16).clone(), "t": t.to(self.device).float().clone()}
-            run = lambda: self.forward(static["z"], static["t"], cap_tokens, ropes)      # noqa: E731
+            static = {"z": z.to(self.device, torch.bfloat16).clone(), "t": t.to(self.device).float().clone(),
+                      "cap": cap_tokens.clone()}         # the caption is an input like the others: one graph per shape
+            run = lambda: self.forward(static["z"], static["t"], static["cap"], ropes)      # noqa: E731
             side = torch.cuda.Stream(device=self.device)
             side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(side):
@@ -398,11 +399,12 @@ class ZImageDiTGpu:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 static["out"] = run()
-            static["launches"], static["cap"] = self.launches, cap_tokens       # keeps the captured caption alive
+            static["launches"] = self.launches
             g = st[key] = (graph, static)
         graph, static = g
         static["z"].copy_(z)
         static["t"].copy_(t)
+        static["cap"].copy_(cap_tokens)
         graph.replay()
         self.launches = static["launches"]
         return static["out"]
