@@ -110,6 +110,13 @@ def _declare_kernels(lib: ctypes.CDLL) -> None:
     sig("swb_gemm_bf16_normed", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                  c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p])
     sig("swb_gemm_gated_supported", [c_int, c_int, c_int])
+    sig("swb_gemm_bf16_peer_reduce", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                                      c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int,
+                                      c_int, c_int, c_void_p])
+    sig("swb_gemm_peer_max_ctas", [])
+    sig("swb_decode_meta_unpack", [c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_void_p, c_void_p])
+    sig("swb_decode_step_tail", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
     sig("swb_gemm_bf16_grouped", [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                   c_int, c_void_p])
     sig("swb_reduce_norm_gather", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_float, c_void_p, c_int, c_int,

@@ -154,6 +154,49 @@ int swb_gemm_bf16_normed(const void* A, int lda, const void* W, int ldw, void* D
   return swb::gemm_bf16_launch(a, reinterpret_cast<cudaStream_t>(stream));
 }
 
+// Row-parallel decode GEMM (T <= 64) whose epilogue sums the partial products over the tensor-parallel ranks through
+// peer memory (see GemmPeerReduce): D = sum_ranks(A_r W_r^T) + residual on every rank, ssq_out (nullable) as in
+// swb_gemm_bf16_normed. slots / flags / out_peers: `world` device pointers each (out_peers only for mode 2, where
+// out_peers[rank] must equal D); epochs: local [swb_gemm_peer_max_ctas()] words, zero at start.
+int swb_gemm_bf16_peer_reduce(const void* A, int lda, const void* W, int ldw, void* D, int ldd, int T, int N, int K,
+                              const void* residual, int ld_res, void* ssq_out, void* const* slots, void* const* flags,
+                              void* const* out_peers, void* epochs, long long slot_stride, int slot_ld, int mode,
+                              int world, int rank, int force_cluster, void* stream) {
+  if (world < 2 || world > 8 || !slots || !flags || !epochs || (mode == 2 && !out_peers)) return -3;
+  swb::GemmPeerReduce q{};
+  for (int r = 0; r < world; ++r) {
+    q.slots[r] = reinterpret_cast<__nv_bfloat16*>(slots[r]);
+    q.flags[r] = reinterpret_cast<uint32_t*>(flags[r]);
+    q.out_peers[r] = out_peers ? reinterpret_cast<__nv_bfloat16*>(out_peers[r]) : nullptr;
+  }
+  if (mode == 2 && q.out_peers[rank] != D) return -3;
+  q.epochs = reinterpret_cast<uint32_t*>(epochs);
+  q.slot_stride = slot_stride;
+  q.ld = slot_ld;
+  q.mode = mode;
+  q.world = world;
+  q.rank = rank;
+  swb::GemmArgs a{};
+  a.A = A;
+  a.lda = lda;
+  a.W = W;
+  a.ldw = ldw;
+  a.D = D;
+  a.ldd = ldd;
+  a.T = T;
+  a.N = N;
+  a.K = K;
+  a.residual = residual;
+  a.ld_res = ld_res;
+  a.force_mode = 2;
+  a.force_ctas = force_cluster;
+  a.ssq_out = reinterpret_cast<float*>(ssq_out);
+  a.peer = &q;
+  return swb::gemm_bf16_launch(a, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int swb_gemm_peer_max_ctas(void) { return swb::SWB_PEER_MAX_CTAS; }
+
 int swb_gemm_gated_supported(int T, int N, int K) { return swb::gemm_bf16_gated_supported(T, N, K); }
 
 size_t swb_gemm_workspace_min(void) { return swb::SWB_GEMM_COUNTER_BYTES + (size_t)(8u << 20); }

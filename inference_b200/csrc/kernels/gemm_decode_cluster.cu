@@ -60,6 +60,40 @@ __device__ __forceinline__ void st_cluster_f32x2(uint32_t addr, float a, float b
   asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(a), "f"(b) : "memory");
 }
 
+// barrier of the four epilogue warps (threads 64..191) only
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_relaxed_sys_16(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+// Bounded spin until *flag reaches `epoch` (wrap-safe). On expiry records {where, rank, peer} and returns false.
+__device__ __forceinline__ bool peer_flag_wait(const uint32_t* flag, uint32_t epoch, int where, int rank, int peer) {
+  uint64_t t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    if ((int32_t)(ld_acquire_sys_u32(flag) - epoch) >= 0) return true;
+    if ((it & 0x3F) == 0x3F) {
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > g_wait_limit_ns) {
+        report_error(SWB_ERR_PEER_TIMEOUT, where, rank, peer);
+        return false;
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ float act_apply(float x, int act) {
   if (act == SWB_ACT_SILU) return silu_f(x);
   if (act == SWB_ACT_GELU_TANH) return gelu_tanh_f(x);
@@ -86,6 +120,7 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tfull + 1);
   volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
   __shared__ float s_rstd[64];
+  __shared__ int s_peer_fail;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -251,7 +286,68 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   if (warp >= 2) {
     const int et = (warp - 2) * 32 + lane;  // 0..127
     constexpr int R8 = R / 8;
-    for (int idx = et; idx < R8 * BLOCK_N; idx += 128) {
+    const GemmPeerReduce& q = p.peer;
+    const int pmode = q.mode;
+    // two-shot: the rank that finishes this weight tile's slice for everybody
+    const int owner_rank = pmode == 2 ? tile_m % q.world : q.rank;
+    const bool i_finish = pmode != 2 || owner_rank == q.rank;
+    bool peer_ok = true;
+    uint32_t epoch = 0;
+    if (pmode) {
+      epoch = q.epochs[blockIdx.x] + 1u;
+      // ---- pass 1: deliver this CTA's partial slice (cluster-reduced, rounded to bf16) to the summing rank(s) ----
+      for (int idx = et; idx < R8 * BLOCK_N; idx += 128) {
+        const int f8 = idx % R8;
+        const int tok = idx / R8;
+        const int row = (int)crank * R + f8 * 8;
+        const int feat = tile_m * BM + row;
+        if (row >= BM || feat >= p.M || tok >= p.N) continue;
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+        for (int src = 0; src < CLUSTER; ++src) {
+          const float4* rp = reinterpret_cast<const float4*>(recv + ((size_t)src * BLOCK_N + tok) * R + f8 * 8);
+          const float4 a0 = rp[0], a1 = rp[1];
+          acc[0] += a0.x; acc[1] += a0.y; acc[2] += a0.z; acc[3] += a0.w;
+          acc[4] += a1.x; acc[5] += a1.y; acc[6] += a1.z; acc[7] += a1.w;
+        }
+        uint4 o;
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        const size_t soff = (size_t)q.rank * q.slot_stride + (size_t)tok * q.ld + feat;
+        if (pmode == 2) {
+          *reinterpret_cast<uint4*>(q.slots[owner_rank] + soff) = o;
+        } else {
+#pragma unroll
+          for (int r = 0; r < 8; ++r)
+            if (r < q.world) *reinterpret_cast<uint4*>(q.slots[(q.rank + r) % q.world] + soff) = o;
+        }
+      }
+      if (et == 0) s_peer_fail = 0;
+      epi_bar_sync();
+      // ---- phase-one flags: "my partial of this slice has landed" ----
+      if (et < q.world) {
+        const int peer = et;
+        if (pmode == 1 || peer == owner_rank)
+          st_release_sys_u32(q.flags[peer] + (size_t)blockIdx.x * 16 + q.rank, epoch);
+        if (i_finish && !peer_flag_wait(q.flags[q.rank] + (size_t)blockIdx.x * 16 + peer, epoch, 1100, q.rank, peer))
+          s_peer_fail = 1;
+      }
+      epi_bar_sync();
+      peer_ok = s_peer_fail == 0;
+      if (tr && et == 0) tr[5] = global_timer_ns();          // peers' partials have arrived
+      if (et == 0) q.epochs[blockIdx.x] = epoch;
+      if (pmode == 2 && !i_finish) {
+        // the owner's final pass stores the finished slice into this rank's output and then raises the second flag
+        if (et == 0 && !peer_flag_wait(q.flags[q.rank] + (size_t)blockIdx.x * 16 + 8, epoch, 1200, q.rank, owner_rank))
+          s_peer_fail = 1;
+        epi_bar_sync();
+        peer_ok = s_peer_fail == 0;
+      }
+    }
+    for (int idx = et; peer_ok && idx < R8 * BLOCK_N; idx += 128) {
       const int f8 = idx % R8;         // consecutive threads -> consecutive 16-byte feature groups of one token
       const int tok = idx / R8;
       const int row = (int)crank * R + f8 * 8;
@@ -262,6 +358,34 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
       float acc[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      const size_t off = (size_t)tok * p.ldd + feat;
+      if (pmode) {
+        if (!i_finish) {
+          // the owner stored the finished row slice into this rank's output: only the sum of squares is left
+          const uint4 r = ld_relaxed_sys_16(reinterpret_cast<const bf16*>(p.out) + off);
+          const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 t = __bfloat1622float2(rh[j]);
+            ss += t.x * t.x + t.y * t.y;
+          }
+          break;
+        }
+        // sum the ranks' partials in rank order: every rank computes bit-identical rows
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          if (r < q.world) {
+            const uint4 u = ld_relaxed_sys_16(q.slots[q.rank] + (size_t)r * q.slot_stride + (size_t)tok * q.ld + feat);
+            const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 t = __bfloat1622float2(uh[j]);
+              acc[2 * j] += t.x;
+              acc[2 * j + 1] += t.y;
+            }
+          }
+        }
+      } else {
 #pragma unroll
       for (int src = 0; src < CLUSTER; ++src) {
         const float4* rp = reinterpret_cast<const float4*>(recv + ((size_t)src * BLOCK_N + tok) * R + f8 * 8);
@@ -269,13 +393,13 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
         acc[0] += a0.x; acc[1] += a0.y; acc[2] += a0.z; acc[3] += a0.w;
         acc[4] += a1.x; acc[5] += a1.y; acc[6] += a1.z; acc[7] += a1.w;
       }
+      }
       if (p.ssq_in) {
         const float rs = s_rstd[tok];
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] *= rs;
       }
       const int nvalid = min(8, p.M - feat);
-      const size_t off = (size_t)tok * p.ldd + feat;
       const bool vec = p.vec_ok && nvalid == 8 && ((p.ldd & 7) == 0) && ((feat & 7) == 0) && (!p.residual || (p.ld_res & 7) == 0);   // gated pairs: ldd % 8 == 0 keeps the 8-byte stores aligned
       if (vec) {
         if (p.bias) {
@@ -321,7 +445,13 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
           __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
           for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-          *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + off) = o;
+          if (pmode == 2) {
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+              if (r < q.world) *reinterpret_cast<uint4*>(q.out_peers[(q.rank + r) % q.world] + off) = o;
+          } else {
+            *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + off) = o;
+          }
           if (p.ssq_out) {   // sum of squares of exactly what was stored (bf16-rounded)
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -352,6 +482,11 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
         for (int o2 = 1; o2 < R8; o2 <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o2);
         if (f8 == 0 && tok < BLOCK_N) p.ssq_out[64 + (size_t)blockIdx.x * 64 + tok] = ss;
       }
+    }
+    if (pmode == 2 && i_finish && peer_ok) {
+      // phase two: the finished slice is in every rank's output buffer
+      epi_bar_sync();
+      if (et < q.world && et != q.rank) st_release_sys_u32(q.flags[et] + (size_t)blockIdx.x * 16 + 8, epoch);
     }
   }
 
@@ -445,6 +580,7 @@ int gemm_decode_cluster_launch(const GemmArgs& a, int force_cluster, cudaStream_
   p.norm_dim = a.norm_dim;
   p.norm_eps = a.norm_eps;
   p.trace = gemm_trace_buffer();
+  if (a.peer && a.peer->mode) p.peer = *a.peer;
   p.vec_ok = ((reinterpret_cast<uintptr_t>(a.D) & 15) == 0) && (!a.bias || (reinterpret_cast<uintptr_t>(a.bias) & 15) == 0) &&
              (!a.residual || (reinterpret_cast<uintptr_t>(a.residual) & 15) == 0) && (!a.out_fp32 || (a.ldd % 4) == 0);
   // Two CTAs can be resident per SM. Measured on B200 over Llama-3-8B projections: the fastest member count is
@@ -458,6 +594,19 @@ int gemm_decode_cluster_launch(const GemmArgs& a, int force_cluster, cudaStream_
   if (force_cluster > 0) cluster = std::min(8, force_cluster);
   if (cluster == 5) cluster = 4;
   if (cluster == 7) cluster = 6;
+  if (p.peer.mode) {
+    // the cross-rank sum moves whole 16-byte groups of a full 128-row tile grid, bf16 in and out, nothing else fused;
+    // at most 4 members per cluster keep a token's run of peer stores at 64 bytes or more
+    const GemmPeerReduce& q = p.peer;
+    if (q.world < 2 || q.world > 8 || q.rank < 0 || q.rank >= q.world || (q.mode != 1 && q.mode != 2)) return -3;
+    if (a.bias || a.act != SWB_ACT_NONE || a.out_fp32 || a.ssq_in || !p.vec_ok || (a.ldd & 7) || (a.N % BM) ||
+        (q.ld & 7) || (a.residual && (a.ld_res & 7)))
+      return -3;
+    if (q.mode == 2 && p.tiles_m < q.world) p.peer.mode = 1;   // every rank must own a tile for the flags to order buffer reuse
+    if (force_cluster <= 0) cluster = std::min(cluster, 4);
+    if (cluster == 3) cluster = 2;
+    if (p.tiles_m * cluster > SWB_PEER_MAX_CTAS) return -3;
+  }
   if (a.ssq_out || a.ssq_in) {
     // the per-token reduction in the producer's epilogue pairs lanes by xor: rows per member / 8 must be a power of two
     if (cluster == 3) cluster = 2;

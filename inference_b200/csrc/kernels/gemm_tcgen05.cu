@@ -721,6 +721,10 @@ int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
     swapped = 0;
   }
   if (swapped < 0) swapped = (a.T <= 256) ? 1 : 0;
+  if (a.peer && a.peer->mode) {   // cross-rank sum in the epilogue: decode cluster kernel only, any K
+    if (a.scatter || a.group_of_mtile || !gemm_decode_cluster_supported(a.T)) return -3;
+    return gemm_decode_cluster_launch(a, a.force_mode == 2 ? a.force_ctas : 0, stream);
+  }
   // decode-sized problems with at most two weight tiles per SM: the two-CTAs-per-SM cluster kernel (split-K over a
   // cluster with a DSMEM reduction when tiles are few, plain whole tiles otherwise)
   // the folded-norm chain lives in the decode cluster kernel only

@@ -33,6 +33,32 @@ struct GemmScatter {
   int rows_per_rank, src_rank;
 };
 
+// Sum of a row-parallel decode GEMM over the tensor-parallel ranks, performed inside the cluster kernel's epilogue
+// over peer memory (plain 16-byte peer stores and system-scope flags; no collective library call, no multicast).
+// CTA b of every rank owns the same slice of the output, so the exchange is per CTA: a slice is summed as soon as the
+// same CTA of every peer has delivered it, while other CTAs are still streaming weights.
+// mode 1 (one shot): each CTA stores its bf16 partial slice into slot `rank` of EVERY rank's slot buffer
+//   [world][max_tokens][ld], release-stores epoch flags, waits for the flags of all peers, then sums the `world`
+//   slots in rank order (bit-identical on every rank), adds the local residual and stores the row.
+// mode 2 (two shot): the slice of weight tile t belongs to rank t % world. Every rank stores its partial only into
+//   the owner's slot buffer; the owner sums, adds its residual and stores the finished bf16 slice into every rank's
+//   output buffer (`out_peers`, symmetric), then raises a second flag the other ranks wait for. 2 (world - 1) / world
+//   of the one-shot traffic at the price of a second hop.
+// flags: per rank a pad of [SWB_PEER_MAX_CTAS][16] words (0..7: phase-one flag per source rank, 8: phase two);
+// epochs: local [SWB_PEER_MAX_CTAS] counters advanced by the kernel (graph-replay safe). Two slot buffers must
+// alternate between consecutive reductions of a stream (a buffer is rewritten only after the next reduction's flags
+// proved that every peer finished reading it).
+constexpr int SWB_PEER_MAX_CTAS = 512;
+struct GemmPeerReduce {
+  __nv_bfloat16* slots[8];
+  uint32_t* flags[8];
+  __nv_bfloat16* out_peers[8];
+  uint32_t* epochs;
+  long long slot_stride;   // elements between two source ranks' slots
+  int ld;                  // row stride of a slot
+  int mode, world, rank;
+};
+
 // Kernel-level problem: D[M, N] = A[M, K] * B[N, K]^T, possibly stored transposed.
 struct GemmParams {
   int M, N, K;
@@ -68,6 +94,7 @@ struct GemmParams {
   const float* ssq_in;
   int norm_dim;
   float norm_eps;
+  GemmPeerReduce peer;   // decode cluster kernel only
 };
 
 // User-level problem: D[T, N] = act(A[T, K] * W[N, K]^T + bias[N]) + residual[T, N].
@@ -96,6 +123,7 @@ struct GemmArgs {
   const float* ssq_in = nullptr;
   int norm_dim = 0;
   float norm_eps = 0.f;
+  const GemmPeerReduce* peer = nullptr;  // see GemmPeerReduce (decode cluster kernel only)
 };
 
 int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream);

@@ -49,22 +49,26 @@ def _pick(backend: DecodeBackend, logits: torch.Tensor, history: list[int], cfg:
 
 
 def decode_loop(backend: DecodeBackend, seq: Any, first_logits: torch.Tensor | None, first_token: int | None,
-                cfg: GenerationConfig, sink: TokenSink | None = None, mask: AllowMask | None = None
-                ) -> tuple[list[int], FinishReason]:
+                cfg: GenerationConfig, sink: TokenSink | None = None, mask: AllowMask | None = None,
+                prompt: list[int] | None = None) -> tuple[list[int], FinishReason]:
     """Shared token loop: sample, check stop / sink / budget, step. `first_logits` (or a pre-sampled greedy
-    `first_token`) come from the prefill."""
+    `first_token`) come from the prefill. The repetition-penalty window is the prompt followed by the generated
+    tokens (candle-llm/src/decode/stream.rs:210-285 seeds the history with the prompt ids); the allow mask sees the
+    generated tokens only."""
     rng = hs.SplitMix64(cfg.seed)
     out: list[int] = []
+    history: list[int] = list(prompt) if prompt is not None else []
     logits, tok = first_logits, first_token
     greedy_fast = cfg.sampling.is_plain_greedy() and mask is None
     for _ in range(cfg.max_new_tokens):
         if cfg.cancel is not None and cfg.cancel.is_cancelled():
             return out, FinishReason.CANCELLED
         if tok is None:
-            tok = _pick(backend, logits, out, cfg, rng, mask(out) if mask else None)
+            tok = _pick(backend, logits, history, cfg, rng, mask(out) if mask else None)
         if tok in cfg.stop_tokens:
             return out, FinishReason.STOP
         out.append(tok)
+        history.append(tok)
         if sink is not None and sink(tok) is False:
             return out, FinishReason.STOP
         if len(out) >= cfg.max_new_tokens:
@@ -91,10 +95,10 @@ def generate(backend: DecodeBackend, prompt: list[int], cfg: GenerationConfig, s
             return GenerationResult([], FinishReason.CANCELLED, len(prompt))
         if cfg.sampling.is_plain_greedy() and mask is None:
             first = backend.forward_greedy([seq], [suffix])[0]
-            toks, why = decode_loop(backend, seq, None, first, cfg, sink, mask)
+            toks, why = decode_loop(backend, seq, None, first, cfg, sink, mask, prompt=prompt)
         else:
             logits = backend.forward([seq], [suffix])[0]
-            toks, why = decode_loop(backend, seq, logits, None, cfg, sink, mask)
+            toks, why = decode_loop(backend, seq, logits, None, cfg, sink, mask, prompt=prompt)
         return GenerationResult(toks, why, len(prompt))
     finally:
         if own:
@@ -119,7 +123,9 @@ def generate_batch(backend: DecodeBackend, prompts: list[list[int]], cfg: Genera
                 toks = backend.forward_greedy([seqs[i] for i in live], new)
             else:
                 logits = backend.forward([seqs[i] for i in live], new)
-                toks = [_pick(backend, logits[k], sched.generated(i), cfg, rngs[i], None) for k, i in enumerate(live)]
+                # penalty window = prompt + generated (candle-llm/src/decode/batch.rs:133)
+                toks = [_pick(backend, logits[k], list(prompts[i]) + sched.generated(i), cfg, rngs[i], None)
+                        for k, i in enumerate(live)]
             nxt, new = [], []
             for k, i in enumerate(live):
                 if sched.record(i, toks[k]) is None:
@@ -268,11 +274,11 @@ def generate_cached(backend: DecodeBackend, cache: PrefixCache, prompt: list[int
         if cfg.sampling.is_plain_greedy():
             first = backend.forward_greedy([seq], [prompt[backend.length(seq):]])[0]
             cache.store(prompt, seq)
-            toks, why = decode_loop(backend, seq, None, first, cfg, sink)
+            toks, why = decode_loop(backend, seq, None, first, cfg, sink, prompt=prompt)
         else:
             logits = backend.forward([seq], [prompt[backend.length(seq):]])[0]
             cache.store(prompt, seq)
-            toks, why = decode_loop(backend, seq, logits, None, cfg, sink)
+            toks, why = decode_loop(backend, seq, logits, None, cfg, sink, prompt=prompt)
         return GenerationResult(toks, why, len(prompt))
     finally:
         backend.release(seq)
@@ -298,11 +304,22 @@ class SpeculativeStats:
 
 def _verify(target: DecodeBackend, seq: Any, last: int, drafts: list[int], draft_dists, cfg: GenerationConfig,
             rng: hs.SplitMix64, history: list[int]) -> tuple[list[int], int]:
-    """One target forward over [last, d_1..d_k]; returns (tokens to emit, number of drafts accepted)."""
+    """One target forward over [last, d_1..d_k]; returns (tokens to emit, number of drafts accepted). `history` is
+    the penalty window up to and including `last` (prompt + emitted tokens), the same list the draft shapes q with."""
     base = target.length(seq)
     logits = target.forward([seq], [[last] + drafts], all_positions=True)[0]   # [k + 1, vocab]
     if cfg.sampling.temperature <= 0.0:
-        argmax = [int(x) for x in torch.argmax(logits, dim=-1).tolist()]
+        if cfg.sampling.is_plain_greedy():
+            argmax = [int(x) for x in torch.argmax(logits, dim=-1).tolist()]
+        else:
+            # penalty-aware argmax per verify position, the window growing by the drafts
+            # (candle-llm/src/decode/speculative.rs:399-421)
+            argmax, hist = [], list(history)
+            rows = logits.detach().float().cpu().numpy()
+            for i in range(len(drafts) + 1):
+                argmax.append(hs.sample(rows[i], hist, cfg.sampling, rng, None))
+                if i < len(drafts):
+                    hist.append(drafts[i])
         n = accept_greedy_run(argmax, drafts)
         emit = drafts[:n] + [argmax[n]]
     else:
@@ -336,7 +353,7 @@ def _spec_loop(target: DecodeBackend, prompt: list[int], cfg: GenerationConfig, 
             return GenerationResult([], FinishReason.LENGTH, len(prompt)), stats
         logits = target.forward([seq], [prompt])[0]
         stats.forwards += 1
-        last = _pick(target, logits, out, cfg, rng, None)
+        last = _pick(target, logits, list(prompt), cfg, rng, None)
         done = False
         while not done:
             if cfg.cancel is not None and cfg.cancel.is_cancelled():
@@ -353,7 +370,7 @@ def _spec_loop(target: DecodeBackend, prompt: list[int], cfg: GenerationConfig, 
                 break
             budget = cfg.max_new_tokens - len(out)
             drafts, dists = propose(prompt + out, min(budget - 1, 1 << 30))
-            emit, n = _verify(target, seq, last, drafts, dists, cfg, rng, out)
+            emit, n = _verify(target, seq, last, drafts, dists, cfg, rng, prompt + out)
             stats.forwards += 1
             stats.proposed += len(drafts)
             stats.accepted += n

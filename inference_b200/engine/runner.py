@@ -43,6 +43,8 @@ class _DecodeGraph:
 
 
 class ModelRunner:
+    MULTI_STEPS = 256
+
     def __init__(self, model: LlamaGpu, pool: PagedKvPool, max_batch: int = 64, max_seq_len: int = 8192,
                  use_graphs: bool = True):
         self.model, self.pool = model, pool
@@ -66,6 +68,11 @@ class ModelRunner:
         self._table = torch.zeros((max_batch, self.max_blocks), dtype=torch.int32, device=dev)
         self._host_tokens = torch.zeros(max_batch, dtype=torch.int64).pin_memory() if dev.type == "cuda" else \
             torch.zeros(max_batch, dtype=torch.int64)
+        # multi-step greedy runs: the metadata of up to MULTI_STEPS steps, the tokens they produce and a device-side
+        # step counter; the captured graph indexes both by the counter, so a step is one graph replay and nothing else
+        self._multi_meta = torch.zeros((self.MULTI_STEPS, self._n_meta), dtype=torch.int32, device=dev)
+        self._multi_out = torch.zeros(self.MULTI_STEPS * max_batch, dtype=torch.int64, device=dev)
+        self._step = torch.zeros(1, dtype=torch.int32, device=dev)
         self._graphs: dict[tuple[int, int, bool], _DecodeGraph] = {}
         self.pad_batches = self.use_graphs      # decode batches are padded to a bucket so graphs are reused
         self.captures = 0
@@ -155,18 +162,31 @@ class ModelRunner:
                 self._row_state[i] = (-1, -1, 0)
         return max_kv
 
-    def _unpack_meta(self, B: int, skip_ids: bool = False) -> None:
+    def _unpack_meta(self, B: int, skip_ids: bool = False, multi: bool = False) -> None:
+        """One kernel: packed int32 step metadata -> the typed static input tensors. `multi` reads row
+        `self._step` of the multi-step table instead of the single-step staging buffer."""
         MB, mb = self.max_batch, self.max_blocks
-        m = self._dev_meta
-        if not skip_ids:
-            self._ids[:B].copy_(m[:B])
-        self._pos[:B].copy_(m[MB:MB + B])
-        self._slots[:B].copy_(m[2 * MB:2 * MB + B])
-        self._kvl[:B].copy_(m[3 * MB:3 * MB + B])
-        self._table[:B].copy_(m[4 * MB:4 * MB + B * mb].view(B, mb))
+        if self.model.device.type != "cuda":
+            m = self._dev_meta
+            if not skip_ids:
+                self._ids[:B].copy_(m[:B])
+            self._pos[:B].copy_(m[MB:MB + B])
+            self._slots[:B].copy_(m[2 * MB:2 * MB + B])
+            self._kvl[:B].copy_(m[3 * MB:3 * MB + B])
+            self._table[:B].copy_(m[4 * MB:4 * MB + B * mb].view(B, mb))
+            return
+        from .._native import kernels
+        from ..ops.runtime import check, stream_ptr
+
+        src = self._multi_meta if multi else self._dev_meta
+        rc = kernels().swb_decode_meta_unpack(src.data_ptr(), self._n_meta, self._step.data_ptr() if multi else None,
+                                              MB, B, mb, None if skip_ids else self._ids.data_ptr(),
+                                              self._pos.data_ptr(), self._slots.data_ptr(), self._kvl.data_ptr(),
+                                              self._table.data_ptr(), stream_ptr())
+        check(rc, "swb_decode_meta_unpack")
 
     def _decode_body(self, B: int, splits: int, want_logits: bool, feedback: bool = False):
-        self._unpack_meta(B, skip_ids=feedback)
+        self._unpack_meta(B, skip_ids=feedback, multi=feedback and self.model.device.type == "cuda")
         inp = StepInputs(input_ids=self._ids[:B], positions=self._pos[:B], slot_mapping=self._slots[:B],
                          block_table=self._table[:B], kv_lens=self._kvl[:B], cu_q=None, max_q_len=1, num_seqs=B,
                          decode=True, attn_splits=splits, logits_rows=None)
@@ -175,7 +195,16 @@ class ModelRunner:
             return None, self.model.logits(hidden)
         toks = self.model.greedy_tokens(hidden)
         if feedback:
-            self._ids[:B].copy_(toks)  # the next replay consumes these without a host round trip
+            if self.model.device.type == "cuda":
+                # the next replay consumes these without a host round trip; the step counter advances
+                from .._native import kernels
+                from ..ops.runtime import check, stream_ptr
+
+                rc = kernels().swb_decode_step_tail(toks.data_ptr(), self._ids.data_ptr(), self._multi_out.data_ptr(),
+                                                    self._step.data_ptr(), B, stream_ptr())
+                check(rc, "swb_decode_step_tail")
+            else:
+                self._ids[:B].copy_(toks)
         return toks, None
 
     def decode(self, seqs: list[PagedSequence], tokens: list[int], *, want_logits: bool = False):
@@ -211,10 +240,18 @@ class ModelRunner:
 
     def decode_multi(self, seqs: list[PagedSequence], tokens: list[int], n_steps: int) -> torch.Tensor:
         """n_steps greedy decode steps with the sampled token fed back on the device: the host uploads the
-        metadata of all steps once, then only enqueues one small device copy and one graph launch per step.
+        metadata of all steps once, then only replays one captured graph per step (the graph reads its step's
+        metadata and files its tokens through a device-side step counter).
         Returns the generated tokens [n_steps, B] on the device (no synchronisation is performed)."""
         B = len(seqs)
         dev = self.model.device
+        if n_steps > self.MULTI_STEPS:
+            parts, toks = [], tokens
+            for k0 in range(0, n_steps, self.MULTI_STEPS):
+                part = self.decode_multi(seqs, toks, min(self.MULTI_STEPS, n_steps - k0))
+                parts.append(part)
+                toks = part[-1].tolist()
+            return torch.cat(parts, dim=0)
         n_meta = self._n_meta
         host_all = torch.empty((n_steps, n_meta), dtype=torch.int32)
         if dev.type == "cuda":
@@ -223,29 +260,38 @@ class ModelRunner:
         for k in range(n_steps):
             max_kv = self._fill_decode_meta(seqs, tokens if k == 0 else [0] * B)
             host_all[k].copy_(self._host_meta)
-        dev_all = host_all.to(dev, non_blocking=True)
         self.h2d_bytes_last = host_all.numel() * 4
         splits = _splits_for(B, self.model.hkv, max_kv)
-        out = torch.empty((n_steps, B), dtype=torch.int64, device=dev)
-        self._ids[:B].copy_(torch.tensor(tokens, dtype=torch.int64).to(dev, non_blocking=True))
-        key = (B, splits, "feedback")
-        g = self._graphs.get(key)
-        if g is None and self.use_graphs and dev.type == "cuda":
-            self._dev_meta.copy_(dev_all[0])
-            saved = self._ids[:B].clone()
-            g = self._capture(B, splits, False, feedback=True)
-            self._ids[:B].copy_(saved)
-            self._graphs[key] = g
-        for k in range(n_steps):
-            self._dev_meta.copy_(dev_all[k], non_blocking=True)
-            if g is not None:
-                g.graph.replay()
-                out[k].copy_(g.tokens_out)
-            else:
+        first = torch.tensor(tokens, dtype=torch.int64)
+        if dev.type != "cuda" or not self.use_graphs:
+            out = torch.empty((n_steps, B), dtype=torch.int64, device=dev)
+            self._ids[:B].copy_(first.to(dev))
+            for k in range(n_steps):
+                if dev.type == "cuda":
+                    self._multi_meta[0].copy_(host_all[k], non_blocking=True)
+                    self._step.zero_()
+                else:
+                    self._dev_meta.copy_(host_all[k])
                 toks, _ = self._decode_body(B, splits, False, feedback=True)
                 out[k].copy_(toks)
-        self.launches_last = (g.launches if g is not None else self.model.launches) * n_steps
-        return out
+            self.launches_last = self.model.launches * n_steps
+            return out
+        key = (B, splits, "feedback")
+        g = self._graphs.get(key)
+        if g is None:
+            self._multi_meta[0].copy_(host_all[0], non_blocking=True)
+            self._step.zero_()
+            self._ids[:B].copy_(first.to(dev, non_blocking=True))
+            g = self._capture(B, splits, False, feedback=True)
+            self._graphs[key] = g
+            self.captures += 1
+        self._multi_meta[:n_steps].copy_(host_all, non_blocking=True)
+        self._step.zero_()
+        self._ids[:B].copy_(first.pin_memory().to(dev, non_blocking=True))
+        for _ in range(n_steps):
+            g.graph.replay()
+        self.launches_last = g.launches * n_steps
+        return self._multi_out[:n_steps * B].view(n_steps, B).clone()
 
     def _capture(self, B: int, splits: int, want_logits: bool, feedback: bool = False) -> _DecodeGraph:
         # warm-up on a side stream (sets kernel attributes, fills the tensor-map cache), then capture
@@ -253,6 +299,8 @@ class ModelRunner:
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
             for _ in range(2):
+                if feedback:
+                    self._step.zero_()      # every warm-up run reads the same (first) row of the step table
                 self._decode_body(B, splits, want_logits, feedback)
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()

@@ -114,6 +114,9 @@ class FluxPipeline:
         self.text_kind = "t5_clip"
         self.random_init = None
         self.adapters: list = []
+        # when set to a dict, render() records device-timed phases of the last image into it:
+        # "step_ms" (one entry per model evaluation) and "vae_ms" (CUDA events; read after the image is on the host)
+        self.timings: dict | None = None
         cfg_path = self.root / "swb_config.json"
         if cfg_path.exists():
             raw = json.loads(cfg_path.read_text())
@@ -146,8 +149,13 @@ class FluxPipeline:
             from ..models.dit_flux import FluxDiTGpu
             from ..models.vae import VaeDecoderGpu
 
+            from ..parallel import default_communicator
+
             seed = int(self.random_init)
-            return _Heavy(FluxDiTGpu(self.dit_cfg, device=self.device).init_random(seed),
+            comm = default_communicator()      # a multi-GPU job renders sequence parallel: every rank calls generate
+            if comm is not None and (not comm.is_parallel or comm.device != self.device):
+                comm = None
+            return _Heavy(FluxDiTGpu(self.dit_cfg, comm=comm, device=self.device).init_random(seed),
                           VaeDecoderGpu(self.vae_cfg, self.device).init_random(seed + 1), self.device, self.dtype)
         tf = self.root / self.variant.transformer_file
         ae = self.root / "ae.safetensors"
@@ -209,7 +217,11 @@ class FluxPipeline:
         gvec = torch.full((1,), float(guidance), device=dev) if guidance is not None else None
         c_lat = self.vae_cfg.z_channels
 
+        events = [] if (self.timings is not None and self.backend == "b200") else None
+
         def one_image(seed: int) -> Image:
+            if events is not None:
+                events.clear()
             noise = seeded_noise_nchw(seed, c_lat, lh, lw)                    # CPU draw -> device
             x = patchify(noise).to(dev)
             if clean is not None:                       # x_t = (1 - sigma) clean + sigma noise at the entry point
@@ -224,7 +236,12 @@ class FluxPipeline:
                     raise Canceled(f"{v.model_id}: cancelled at step {state['step']}")
                 tt = torch.full((1,), float(t), device=dev)
                 if self.backend == "b200":
+                    if events is not None:
+                        events.append((torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)))
+                        events[-1][0].record()
                     out = heavy.dit.forward_graphed(x_in, img_ids, txt, txt_ids, tt, pooled, gvec, rope=rope)
+                    if events is not None:
+                        events[-1][1].record()
                 else:
                     out = heavy.dit.forward(x_in, img_ids, txt, txt_ids, tt, pooled, gvec)
                 state["step"] += 1
@@ -241,8 +258,16 @@ class FluxPipeline:
             on_progress(ProgressDecoding())
             z = unpatchify(x.float(), lh, lw)
             if self.backend == "b200":
+                if events is not None:
+                    v0, v1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    v0.record()
                 u8 = heavy.vae.decode_rgb8(z)[0]                               # [H, W, 3] uint8 on device
+                if events is not None:
+                    v1.record()
                 host = u8.cpu()
+                if events is not None:
+                    self.timings["step_ms"] = [a.elapsed_time(b) for a, b in events]
+                    self.timings["vae_ms"] = v0.elapsed_time(v1)
             else:
                 img = heavy.vae.decode(z)[0].permute(1, 2, 0)
                 host = torch.round((img.clamp(-1, 1) + 1) * 127.5).to(torch.uint8).cpu()

@@ -204,8 +204,13 @@ class LlamaGpu:
         gate_up) and leave a unit norm weight behind. The model computes the same function; decode-sized steps can
         then skip the norm kernels: the o / down projections add the residual and emit per-token sums of squares in
         their epilogues and the qkv / gate_up projections scale their accumulators by 1 / rms
-        (`ops.gemm_bf16_normed`). Only for unsharded dense layers without sandwich norms."""
-        if self.norm_folded or self.comm.is_parallel or os.environ.get("SWB_FOLD_NORMS", "1") == "0":
+        (`ops.gemm_bf16_normed`). Under tensor parallelism the o / down epilogues also sum the ranks' partial products
+        over peer memory (`FusedCollectives.gemm_peer_reduce`), so a sharded decode step launches the same six kernels
+        per layer as an unsharded one. Only for dense layers without sandwich norms; a sharded model needs the
+        peer-memory collectives (the library all-reduce path keeps its norm kernels)."""
+        if self.norm_folded or os.environ.get("SWB_FOLD_NORMS", "1") == "0":
+            return False
+        if self.comm.is_parallel and (self.comm.fused is None or os.environ.get("SWB_TP_CHAIN", "1") == "0"):
             return False
         woff = self.cfg.norm_weight_offset
         for L in self.layers:
@@ -217,15 +222,66 @@ class LlamaGpu:
                 g = getattr(L, ln_name).float() + woff
                 setattr(L, w_name, (getattr(L, w_name).float() * g[None, :]).to(torch.bfloat16).contiguous())
                 setattr(L, ln_name, torch.full_like(getattr(L, ln_name), 1.0 - woff))
+        self.norm_folded = True
+        self._setup_chain()
+        return True
+
+    def _setup_chain(self) -> None:
+        """Decides whether decode-sized steps can run the folded-norm GEMM chain on this rank's shard shapes."""
         H, F2 = self.cfg.hidden_size, 2 * self.ffn
         shapes = (((self.hq + 2 * self.hkv) * self.cfg.head_dim, H), (H, self.hq * self.cfg.head_dim), (F2, H),
                   (H, self.ffn))
+        par = self.comm.is_parallel      # the sharded o / down projections take any K that is a multiple of 64
         self._chain_ok = (self.device.type == "cuda" and H % 128 == 0 and H // 128 * 8 <= 512 and
-                          all(ops.gated_fused(64, n & ~1, k) for n, k in shapes))
+                          all(ops.gated_fused(64, n & ~1, k) or (par and i in (1, 3) and k % 64 == 0)
+                              for i, (n, k) in enumerate(shapes)))
         if self._chain_ok:
             self._ssq = [torch.zeros(ops.SSQ_FLOATS, dtype=torch.float32, device=self.device) for _ in range(2)]
-        self.norm_folded = True
-        return True
+
+    def gather_unsharded(self, dst: int = 0) -> "LlamaGpu | None":
+        """Collective over the model's ranks: rebuilds the complete (tensor-parallel degree 1) model on rank `dst`
+        from every rank's shards and returns it there (None elsewhere). The copy shares no memory with the shards;
+        it serves equivalence checks (TP = k tokens against TP = 1 tokens on the same weights) and re-sharding.
+        Dense bf16 layers only."""
+        import torch.distributed as dist
+
+        if not self.comm.is_parallel:
+            return self
+        P, r = self.comm.world, self.comm.rank
+        if self.quant_format is not None or self.has_moe:
+            raise Unsupported("gather_unsharded: dense bf16 layers only")
+
+        def gather(t: torch.Tensor) -> list[torch.Tensor] | None:
+            t = t.contiguous()
+            parts = [torch.empty_like(t) for _ in range(P)] if r == dst else None
+            dist.gather(t, parts, dst=dst, group=self.comm.group)
+            return parts
+
+        full = LlamaGpu(self.cfg, comm=single(self.device), device=self.device) if r == dst else None
+        D = self.cfg.head_dim
+        nq, nkv = self.hq * D, self.hkv * D
+        head = gather(self.lm_head)
+        if full is not None:
+            full.embed, full.norm, full.lm_head = self.embed, self.norm, torch.cat(head, 0)
+            full.cos, full.sin, full.max_positions = self.cos, self.sin, self.max_positions
+        for L in self.layers:
+            qkv, o, gu, down = gather(L.qkv), gather(L.o), gather(L.gate_up), gather(L.down)
+            bias = gather(L.qkv_bias) if L.qkv_bias is not None else None
+            if full is None:
+                continue
+
+            def regroup(parts):
+                return torch.cat([p[:nq] for p in parts] + [p[nq:nq + nkv] for p in parts] +
+                                 [p[nq + nkv:] for p in parts], 0)
+            full.layers.append(LayerWeights(
+                ln1=L.ln1, qkv=regroup(qkv), qkv_bias=regroup(bias) if bias is not None else None, q_norm=L.q_norm,
+                k_norm=L.k_norm, o=torch.cat(o, 1).contiguous(), post_attn_ln=L.post_attn_ln, ln2=L.ln2,
+                gate_up=torch.cat(gu, 0), down=torch.cat(down, 1).contiguous(), post_mlp_ln=L.post_mlp_ln))
+        if full is not None:
+            full.norm_folded = self.norm_folded
+            if self.norm_folded:
+                full._setup_chain()
+        return full
 
     norm_folded: bool = False
     _chain_ok: bool = False
@@ -308,8 +364,17 @@ class LlamaGpu:
         T = inp.input_ids.numel()
         if self._use_tp_prefill(T) and inp.embed_rows is None:
             return self._forward_hidden_tp_prefill(inp, kv_pool)
+        # decode-sized steps of a dense model: the norms are folded into a chain of GEMM epilogues
+        chain = (self._chain_ok and inp.decode and T <= 64 and self.quant_format is None and
+                 os.environ.get("SWB_NORM_CHAIN", "1") != "0")
+        fc = self.comm.fused if self.comm.is_parallel else None
+        if chain and self.comm.is_parallel:
+            chain = fc is not None and T <= fc.chain_tokens and stage_in is None
         if stage_in is None:
-            res = ops.embedding(inp.input_ids, self.embed, scale=cfg.embed_scale)
+            # (sharded chain: the residual stream lives in symmetric memory, the two-shot reduction stores into it
+            # from the peers)
+            res = ops.embedding(inp.input_ids, self.embed, scale=cfg.embed_scale,
+                                out=fc.residual_stream(T) if (chain and fc is not None) else None)
             if inp.embed_rows is not None:
                 res.index_copy_(0, inp.embed_rows, inp.embed_values.to(res.dtype))
             branch = None
@@ -322,9 +387,6 @@ class LlamaGpu:
         # optional: each norm asks L2 for (the first megabytes of) its consumer's weights (see l2_prefetch_bytes)
         pf_bytes = self.l2_prefetch_bytes if inp.decode else -1
         pf = (lambda t: t if (pf_bytes >= 0 and isinstance(t, torch.Tensor)) else None)
-        # decode-sized steps of an unsharded dense model: the norms are folded into a chain of GEMM epilogues
-        chain = (self._chain_ok and inp.decode and T <= 64 and self.quant_format is None and
-                 os.environ.get("SWB_NORM_CHAIN", "1") != "0")
         ssq_prev = None                 # partial sums of squares of `res` (valid while branch is None)
         H = cfg.hidden_size
         for li, L in enumerate(self.layers):
@@ -363,10 +425,16 @@ class LlamaGpu:
                     branch = None
                     n += 1
                 gelu = cfg.mlp_activation in ("gelu", "gelu_tanh")
-                ops.gemm_bf16_normed(attn.reshape(T, -1), L.o, out=res, residual=res, ssq_out=self._ssq[0])
+                if fc is not None:
+                    fc.gemm_peer_reduce(attn.reshape(T, -1), L.o, res, 0, ssq_out=self._ssq[0])
+                else:
+                    ops.gemm_bf16_normed(attn.reshape(T, -1), L.o, out=res, residual=res, ssq_out=self._ssq[0])
                 act = ops.gemm_bf16_normed(res, L.gate_up, act="geglu_pairs" if gelu else "swiglu_pairs",
                                            ssq_in=self._ssq[0], norm_dim=H, eps=eps)
-                ops.gemm_bf16_normed(act, L.down, out=res, residual=res, ssq_out=self._ssq[1])
+                if fc is not None:
+                    fc.gemm_peer_reduce(act, L.down, res, 1, ssq_out=self._ssq[1])
+                else:
+                    ops.gemm_bf16_normed(act, L.down, out=res, residual=res, ssq_out=self._ssq[1])
                 ssq_prev, pending_h = self._ssq[1], None
                 n += (6 if inp.attn_splits == 1 else 7) + (1 if h is not None else 0)
                 continue

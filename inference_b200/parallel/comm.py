@@ -95,6 +95,21 @@ class Communicator:
         return float(t.item())
 
 
+_DEFAULT: Communicator | None = None
+
+
+def default_communicator() -> Communicator | None:
+    """The communicator of this process's job (set by `init_distributed`), or None in a single-process run.
+    Providers that can spread one request over the job's GPUs (sequence-parallel DiT rendering) pick it up at load
+    time; every rank then issues the same `generate` call."""
+    return _DEFAULT
+
+
+def set_default_communicator(comm: Communicator | None) -> None:
+    global _DEFAULT
+    _DEFAULT = comm
+
+
 def single(device: torch.device | str | None = None) -> Communicator:
     if device is None:
         device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
@@ -120,4 +135,6 @@ def init_distributed(backend: str | None = None, timeout_s: float = 600.0) -> Co
         kw = {"device_id": device} if device.type == "cuda" else {}
         dist.init_process_group(backend=backend, rank=rank, world_size=world, timeout=timedelta(seconds=timeout_s),
                                 **kw)
-    return Communicator(rank, world, dist.group.WORLD, device, backend)
+    comm = Communicator(rank, world, dist.group.WORLD, device, backend)
+    set_default_communicator(comm)
+    return comm

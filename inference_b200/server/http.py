@@ -112,6 +112,8 @@ def make_handler(service: LlmService):
                 return self._error(400, str(e), "unsupported")
             except (InvalidRequest, InferenceError) as e:
                 return self._error(400, str(e))
+            except Exception as e:  # noqa: BLE001  (a malformed field that slipped past validation: still a 400)
+                return self._error(400, f"malformed request: {type(e).__name__}: {e}")
             service.metrics.inc("requests_total")
             service.metrics.add_gauge("requests_in_flight", 1)
             t0 = time.perf_counter()
@@ -133,6 +135,9 @@ def make_handler(service: LlmService):
                 return self._error(499, "request cancelled", "cancelled")
             except InferenceError as e:
                 return self._error(500, str(e), "server_error")
+            except Exception as e:  # noqa: BLE001  (a device / runtime failure must still produce a response)
+                service.metrics.inc("request_errors_total")
+                return self._error(500, f"{type(e).__name__}: {e}", "server_error")
             if first[0] is not None:
                 service.metrics.observe("ttft_seconds", first[0])
             service.metrics.inc("generated_tokens_total", out.usage.generated_tokens)
@@ -172,6 +177,9 @@ def make_handler(service: LlmService):
                 pass
             except InferenceError as e:
                 send(openai.error_body(str(e), "server_error"))
+            except Exception as e:  # noqa: BLE001
+                service.metrics.inc("request_errors_total")
+                send(openai.error_body(f"{type(e).__name__}: {e}", "server_error"))
             send(b"[DONE]")
 
     return Handler

@@ -31,6 +31,20 @@ def _content_text(content: Any) -> str:
     raise InvalidRequest("message content must be a string or a list of content parts")
 
 
+def _number(j: dict, key: str, default, kind=float, lo=None):
+    """A numeric request field: absent -> default; null, a string, a list, a bool or a non-finite value -> 400."""
+    if key not in j:
+        return default
+    v = j[key]
+    if isinstance(v, bool) or not isinstance(v, (int, float)) or v != v or v in (float("inf"), float("-inf")):
+        raise InvalidRequest(f"`{key}` must be a number")
+    if kind is int and int(v) != v:
+        raise InvalidRequest(f"`{key}` must be an integer")
+    if lo is not None and v < lo:
+        raise InvalidRequest(f"`{key}` must be >= {lo}")
+    return kind(v)
+
+
 def parse_chat_request(body: bytes) -> tuple[TextLlmRequest, bool, str | None]:
     """-> (request, stream, requested model id). Raises InvalidRequest on malformed input."""
     try:
@@ -45,10 +59,16 @@ def parse_chat_request(body: bytes) -> tuple[TextLlmRequest, bool, str | None]:
         if role is None:
             raise InvalidRequest(f"unknown message role {m.get('role') if isinstance(m, dict) else m!r}")
         msgs.append(Message.text(role, _content_text(m.get("content"))))
-    temp = float(j.get("temperature", 1.0))
-    sampling = Sampling.greedy() if temp <= 0 else Sampling(temperature=temp, top_p=float(j.get("top_p", 1.0)),
-                                                            top_k=int(j.get("top_k", 0)),
-                                                            repetition_penalty=float(j.get("repetition_penalty", 1.0)))
+    temp = _number(j, "temperature", 1.0)
+    top_p = _number(j, "top_p", 1.0, lo=0.0)
+    top_k = _number(j, "top_k", 0, int, lo=0)
+    rep = _number(j, "repetition_penalty", 1.0, lo=0.0)
+    sampling = Sampling.greedy() if temp <= 0 else Sampling(temperature=temp, top_p=top_p, top_k=top_k,
+                                                            repetition_penalty=rep)
+    if j.get("seed") is not None and (isinstance(j["seed"], bool) or not isinstance(j["seed"], int)):
+        raise InvalidRequest("`seed` must be an integer")
+    if not isinstance(j.get("stop") or [], (str, list)):
+        raise InvalidRequest("`stop` must be a string or a list of strings")
     stop = j.get("stop") or []
     if isinstance(stop, str):
         stop = [stop]

@@ -50,6 +50,39 @@ def main():
             assert (t2.float() - allp.sum(0)).abs().max().item() < 2e-2
     fc.check()
 
+    # 1b. row-parallel decode GEMM with the cross-rank sum in its epilogue (one-shot and two-shot), against torch;
+    #     every rank must hold bit-identical rows, and the sums of squares must describe exactly what was stored
+    for mode_id in (1, 2):
+        fc.reduce_mode = mode_id
+        for T, Kl in ((1, 512), (7, 256), (64, 1792 // 7 * 2)):
+            for it in range(3):
+                gk = torch.Generator(device=dev).manual_seed(1000 * mode_id + 10 * T + it + 100 * r)
+                a = (torch.randn(T, Kl, device=dev, generator=gk) * 0.5).bfloat16()
+                wgt = (torch.randn(H, Kl, device=dev, generator=gk) * 0.05).bfloat16()
+                res0 = (torch.randn(T, H, device=dev, generator=torch.Generator(device=dev).manual_seed(it)) * 0.5) \
+                    .bfloat16()
+                part = (a.float() @ wgt.float().t()).bfloat16()
+                allp = comm.all_gather(part[None], dim=0).float()
+                want = (allp.sum(0) + res0.float()).bfloat16()
+                res = fc.residual_stream(T)
+                res.copy_(res0)
+                torch.cuda.synchronize()
+                comm.barrier()
+                ssq = torch.zeros(ops.SSQ_FLOATS, dtype=torch.float32, device=dev)
+                fc.gemm_peer_reduce(a, wgt, res, it & 1, ssq_out=ssq)
+                torch.cuda.synchronize()
+                fc.check()
+                err = (res.float() - want.float()).abs().max().item()
+                assert err < 0.06, f"rank {r}: peer-reduce GEMM mode {mode_id} T={T} err {err}"
+                allr = comm.all_gather(res.clone()[None], dim=0)
+                assert all(torch.equal(allr[0], allr[k]) for k in range(P)), f"mode {mode_id}: ranks differ"
+                nct = int(ssq[:1].view(torch.int32).item())
+                got_ss = ssq[64:64 + nct * 64].view(nct, 64).sum(0)[:T]
+                ref_ss = res.float().pow(2).sum(-1)
+                assert torch.allclose(got_ss, ref_ss, rtol=1e-3, atol=1e-3), f"mode {mode_id} T={T}: ssq"
+                comm.barrier()
+    fc.reduce_mode = 0
+
     # 2. TP=k model == TP=1 oracle within bf16 tolerance, through prefill and graph decode
     cfg = ModelConfig.from_json({"hidden_size": 1024, "intermediate_size": 2048, "num_hidden_layers": 2,
                                  "num_attention_heads": 8, "num_key_value_heads": 8, "head_dim": 128,
@@ -62,6 +95,7 @@ def main():
         attach_fused(comm)
     model = LlamaGpu(cfg, comm=comm, device=dev).load_state_dict(w)
     assert (comm.fused is not None) == (mode == "fused")
+    assert model.norm_folded == (mode == "fused") and model._chain_ok == (mode == "fused")
     pool = PagedKvPool(cfg.num_layers, 64, model.hkv, cfg.head_dim, 16, device=dev)
     runner = ModelRunner(model, pool, max_batch=4, max_seq_len=256)
     prompts = [list(range(3, 40)), list(range(100, 109))]

@@ -117,3 +117,43 @@ def test_speculative_stochastic_runs_and_is_seeded():
     a, sa = generate_draft_speculative(target, draft, [5, 6, 7], cfg)
     b, sb = generate_draft_speculative(target, draft, [5, 6, 7], cfg)
     assert a.tokens == b.tokens and len(a.tokens) == 12 and sa.proposed == sb.proposed
+
+
+def test_repetition_penalty_window_includes_the_prompt():
+    """The penalty window is prompt + generated tokens (candle-llm decode/stream.rs:210-285): build a prompt that
+    contains the token plain greedy would pick first, so a strong penalty must change that pick, and check the
+    solo, batched and speculative loops against a direct restatement."""
+    import numpy as np
+
+    from inference_b200.policy import sampler as hs
+
+    be = _model(seed=3)
+    base = [1, 5, 9, 2]
+    first_plain = generate(be, base, GenerationConfig(max_new_tokens=1)).tokens[0]
+    prompt = base[:-1] + [first_plain] + base[-1:]           # the would-be winner now sits in the prompt
+    params = SamplingParams(temperature=0.0, repetition_penalty=50.0)
+    cfg = GenerationConfig(max_new_tokens=6, sampling=params)
+
+    # restatement: greedy over penalised logits, window = prompt + generated
+    seq = be.new_sequence()
+    logits = be.forward([seq], [prompt])[0]
+    hist, want = list(prompt), []
+    rng = hs.SplitMix64(0)
+    for _ in range(6):
+        t = hs.sample(logits.float().numpy(), hist, params, rng, None)
+        want.append(t)
+        hist.append(t)
+        logits = be.forward([seq], [[t]])[0]
+    be.release(seq)
+    plain_first = int(np.argmax(be.forward([be.new_sequence()], [prompt])[0].float().numpy()))
+
+    got = generate(be, prompt, cfg)
+    assert got.tokens == want
+    if plain_first in prompt:
+        assert got.tokens[0] != plain_first                   # a prompt token lost its lead to the penalty
+    assert generate_batch(be, [prompt, PROMPTS[1]], cfg)[0].tokens == want
+    spec, _ = generate_prompt_lookup(be, prompt, cfg, SpeculativeConfig(max_ngram=2, num_draft=3))
+    assert spec.tokens == want
+    draft = _model(seed=3)
+    dspec, _ = generate_draft_speculative(be, draft, prompt, cfg, SpeculativeConfig(num_draft=3))
+    assert dspec.tokens == want
