@@ -108,11 +108,11 @@ def _declare_kernels(lib: ctypes.CDLL) -> None:
                            c_void_p, ctypes.c_size_t, c_int, c_void_p])
     sig("swb_argmax_peer_merge", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
     sig("swb_gemm_bf16_normed", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                 c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p])
+                                 c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p])
     sig("swb_gemm_gated_supported", [c_int, c_int, c_int])
     sig("swb_gemm_bf16_peer_reduce", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
-                                      c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int,
-                                      c_int, c_int, c_void_p])
+                                      c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                      c_int, c_int, c_int, c_void_p])
     sig("swb_gemm_peer_max_ctas", [])
     sig("swb_decode_meta_unpack", [c_void_p, c_ll, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_void_p])

@@ -125,13 +125,14 @@ int swb_gemm_bf16_grouped(const void* A, int lda, const void* W, int ldw, int gr
   return swb::gemm_bf16_launch(a, reinterpret_cast<cudaStream_t>(stream));
 }
 
-// Decode GEMM inside a folded-RMSNorm chain (T <= 64, cluster kernel): ssq_in (nullable) = partial sums of squares
-// written by the producer of A, the accumulators are scaled by rsqrt(sum / norm_dim + eps) per token; ssq_out
-// (nullable) receives this launch's partials of the rows it stores (after the residual add). Buffers: 64 + 512 * 64
-// floats. Returns -3 when the shape is not served by the cluster kernel.
+// Decode GEMM inside a folded-RMSNorm chain (T <= 64, cluster kernel): ssq_in (nullable) = per-token sums of squares
+// accumulated by the producer of A, the accumulators are scaled by rsqrt(sum / norm_dim + eps) per token; ssq_out
+// (nullable) accumulates this launch's sums of the rows it stores (after the residual add) and must be zero at
+// launch; ssq_zero (nullable) is zeroed by this launch (the chain's other accumulator). Buffers: 64 x u64, 2^-24
+// fixed point. Returns -3 when the shape is not served by the cluster kernel.
 int swb_gemm_bf16_normed(const void* A, int lda, const void* W, int ldw, void* D, int ldd, int T, int N, int K,
                          const void* bias, const void* residual, int ld_res, int act, const void* ssq_in,
-                         void* ssq_out, int norm_dim, float norm_eps, void* stream) {
+                         void* ssq_out, void* ssq_zero, int norm_dim, float norm_eps, void* stream) {
   swb::GemmArgs a{};
   a.A = A;
   a.lda = lda;
@@ -147,31 +148,31 @@ int swb_gemm_bf16_normed(const void* A, int lda, const void* W, int ldw, void* D
   a.ld_res = ld_res;
   a.act = act;
   a.force_mode = -1;
-  a.ssq_in = reinterpret_cast<const float*>(ssq_in);
-  a.ssq_out = reinterpret_cast<float*>(ssq_out);
+  a.ssq_in = ssq_in;
+  a.ssq_out = ssq_out;
+  a.ssq_zero = ssq_zero;
   a.norm_dim = norm_dim;
   a.norm_eps = norm_eps;
   return swb::gemm_bf16_launch(a, reinterpret_cast<cudaStream_t>(stream));
 }
 
 // Row-parallel decode GEMM (T <= 64) whose epilogue sums the partial products over the tensor-parallel ranks through
-// peer memory (see GemmPeerReduce): D = sum_ranks(A_r W_r^T) + residual on every rank, ssq_out (nullable) as in
-// swb_gemm_bf16_normed. slots / flags / out_peers: `world` device pointers each (out_peers only for mode 2, where
-// out_peers[rank] must equal D); epochs: local [swb_gemm_peer_max_ctas()] words, zero at start.
+// peer memory (see GemmPeerReduce): D = sum_ranks(A_r W_r^T) + residual on every rank; ssq_out / ssq_zero as in
+// swb_gemm_bf16_normed. slots / results: `world` device pointers each to line buffers of [world][cap][slot_ld / 8][2]
+// and [cap][slot_ld / 8][2] 16-byte lines (zero at start); epochs: local [swb_gemm_peer_max_ctas()] words, zero at
+// start.
 int swb_gemm_bf16_peer_reduce(const void* A, int lda, const void* W, int ldw, void* D, int ldd, int T, int N, int K,
-                              const void* residual, int ld_res, void* ssq_out, void* const* slots, void* const* flags,
-                              void* const* out_peers, void* epochs, long long slot_stride, int slot_ld, int mode,
-                              int world, int rank, int force_cluster, void* stream) {
-  if (world < 2 || world > 8 || !slots || !flags || !epochs || (mode == 2 && !out_peers)) return -3;
+                              const void* residual, int ld_res, void* ssq_out, void* ssq_zero, void* const* slots,
+                              void* const* results, void* epochs, int cap, int slot_ld, int mode, int world, int rank,
+                              int force_cluster, void* stream) {
+  if (world < 2 || world > 8 || !slots || !epochs || (mode == 2 && !results)) return -3;
   swb::GemmPeerReduce q{};
   for (int r = 0; r < world; ++r) {
-    q.slots[r] = reinterpret_cast<__nv_bfloat16*>(slots[r]);
-    q.flags[r] = reinterpret_cast<uint32_t*>(flags[r]);
-    q.out_peers[r] = out_peers ? reinterpret_cast<__nv_bfloat16*>(out_peers[r]) : nullptr;
+    q.slots[r] = reinterpret_cast<uint4*>(slots[r]);
+    q.result[r] = results ? reinterpret_cast<uint4*>(results[r]) : nullptr;
   }
-  if (mode == 2 && q.out_peers[rank] != D) return -3;
   q.epochs = reinterpret_cast<uint32_t*>(epochs);
-  q.slot_stride = slot_stride;
+  q.cap = cap;
   q.ld = slot_ld;
   q.mode = mode;
   q.world = world;
@@ -190,7 +191,8 @@ int swb_gemm_bf16_peer_reduce(const void* A, int lda, const void* W, int ldw, vo
   a.ld_res = ld_res;
   a.force_mode = 2;
   a.force_ctas = force_cluster;
-  a.ssq_out = reinterpret_cast<float*>(ssq_out);
+  a.ssq_out = ssq_out;
+  a.ssq_zero = ssq_zero;
   a.peer = &q;
   return swb::gemm_bf16_launch(a, reinterpret_cast<cudaStream_t>(stream));
 }

@@ -62,15 +62,15 @@ __device__ __forceinline__ void st_cluster_f32x2(uint32_t addr, float a, float b
 
 // barrier of the four epilogue warps (threads 64..191) only
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+
+// Flag-in-data lines for the cross-rank sum: 16 bytes = {data, epoch, data, epoch}. Each 8-byte half is written
+// atomically, so a reader that sees both epochs has both data words; no fence or separate flag is needed and a row
+// crosses NVLink in one hop. (The same idea as the low-latency protocol of collective libraries.)
+__device__ __forceinline__ void st_line(uint4* p, const uint4& v) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint4 ld_relaxed_sys_16(const void* p) {
+__device__ __forceinline__ uint4 ld_line(const uint4* p) {
   uint4 v;
   asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
@@ -78,11 +78,16 @@ __device__ __forceinline__ uint4 ld_relaxed_sys_16(const void* p) {
                : "memory");
   return v;
 }
-// Bounded spin until *flag reaches `epoch` (wrap-safe). On expiry records {where, rank, peer} and returns false.
-__device__ __forceinline__ bool peer_flag_wait(const uint32_t* flag, uint32_t epoch, int where, int rank, int peer) {
+// Bounded spin until both lines at `src` carry `epoch`; returns their four data words in `out`. On expiry records
+// {where, rank, peer} in the status word and returns false.
+__device__ __forceinline__ bool ld_lines(const uint4* src, uint32_t epoch, uint4& out, int where, int rank, int peer) {
   uint64_t t0 = 0;
   for (uint32_t it = 0;; ++it) {
-    if ((int32_t)(ld_acquire_sys_u32(flag) - epoch) >= 0) return true;
+    const uint4 a = ld_line(src), b = ld_line(src + 1);
+    if (a.y == epoch && a.w == epoch && b.y == epoch && b.w == epoch) {
+      out = make_uint4(a.x, a.z, b.x, b.z);
+      return true;
+    }
     if ((it & 0x3F) == 0x3F) {
       const uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
@@ -92,6 +97,11 @@ __device__ __forceinline__ bool peer_flag_wait(const uint32_t* flag, uint32_t ep
       }
     }
   }
+}
+// sum of squares -> 2^-24 fixed point (integer accumulation is order independent, so every rank and every replay
+// gets the same bits)
+__device__ __forceinline__ unsigned long long ssq_fixed(float ss) {
+  return __float2ull_rn(fminf(ss, 5.0e11f) * 16777216.f);
 }
 
 __device__ __forceinline__ float act_apply(float x, int act) {
@@ -120,7 +130,6 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tfull + 1);
   volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
   __shared__ float s_rstd[64];
-  __shared__ int s_peer_fail;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -227,16 +236,13 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   if (warp >= 2) {
     pdl_wait();
     if (p.ssq_in) {
-      // per-token 1 / rms of the residual stream from the producer's per-CTA partial sums (fixed order: deterministic);
-      // two threads per token, overlapped with the weight streaming of the other warps
-      const int e = (warp - 2) * 32 + lane;
-      const int tok = e >> 1, half = e & 1;
-      const int count = __float_as_int(__ldcg(p.ssq_in));
-      float sacc = 0.f;
-      if (tok < BLOCK_N)
-        for (int i = half; i < count; i += 2) sacc += __ldcg(p.ssq_in + 64 + (size_t)i * 64 + tok);
-      sacc += __shfl_xor_sync(0xffffffffu, sacc, 1);
-      if (half == 0 && tok < BLOCK_N) s_rstd[tok] = rsqrtf(sacc / (float)p.norm_dim + p.norm_eps);
+      // per-token 1 / rms of the residual stream: the producer accumulated every token's sum of squares in 2^-24 fixed
+      // point (integer adds: the order of the CTAs cannot change the result), one load per token
+      const int tok = (warp - 2) * 32 + lane;
+      if (tok < BLOCK_N && tok < 64) {
+        const unsigned long long acc = __ldcg(p.ssq_in + tok);
+        s_rstd[tok] = rsqrtf((float)acc * (1.f / 16777216.f) / (float)p.norm_dim + p.norm_eps);
+      }
     }
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
@@ -283,71 +289,151 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   }
 
   if (tr && threadIdx.x == 64) tr[5] = global_timer_ns();    // cluster barrier passed
-  if (warp >= 2) {
+  if (warp >= 2 && p.ssq_zero && blockIdx.x == 0) {
+    // the chain's other accumulator: its consumer finished before this kernel's dependency resolved, its producer
+    // starts after this kernel ends
+    const int e = (warp - 2) * 32 + lane;
+    if (e < 64) p.ssq_zero[e] = 0ull;
+  }
+  if (warp >= 2 && p.peer.mode) {
+    // ---- cross-rank sum over peer memory, flag-in-data lines: no barrier, no fence, one NVLink hop per shot ----
     const int et = (warp - 2) * 32 + lane;  // 0..127
     constexpr int R8 = R / 8;
+    constexpr int ITEMS = (R8 * BLOCK_N + 127) / 128;
     const GemmPeerReduce& q = p.peer;
     const int pmode = q.mode;
-    // two-shot: the rank that finishes this weight tile's slice for everybody
-    const int owner_rank = pmode == 2 ? tile_m % q.world : q.rank;
+    const int owner_rank = pmode == 2 ? tile_m % q.world : q.rank;   // two-shot: who finishes this weight tile's rows
     const bool i_finish = pmode != 2 || owner_rank == q.rank;
-    bool peer_ok = true;
-    uint32_t epoch = 0;
-    if (pmode) {
-      epoch = q.epochs[blockIdx.x] + 1u;
-      // ---- pass 1: deliver this CTA's partial slice (cluster-reduced, rounded to bf16) to the summing rank(s) ----
-      for (int idx = et; idx < R8 * BLOCK_N; idx += 128) {
-        const int f8 = idx % R8;
-        const int tok = idx / R8;
-        const int row = (int)crank * R + f8 * 8;
-        const int feat = tile_m * BM + row;
-        if (row >= BM || feat >= p.M || tok >= p.N) continue;
-        float acc[8];
+    const uint32_t counter = q.epochs[blockIdx.x] + 1u;
+    // unique per (launch, CTA): a line left behind by another CTA of an earlier launch shape never matches
+    const uint32_t epoch = (counter << 9) | ((uint32_t)blockIdx.x & 511u);
+    const int ld8 = q.ld >> 3;
+    uint4 own[ITEMS];
+    // pass 1: deliver this CTA's partial rows (cluster-reduced, rounded to bf16) to the rank(s) that sum them
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int it = 0; it < ITEMS; ++it) {
+      const int idx = et + it * 128;
+      const int f8 = idx % R8, tok = idx / R8;
+      const int row = (int)crank * R + f8 * 8;
+      const int feat = tile_m * BM + row;
+      own[it] = make_uint4(0u, 0u, 0u, 0u);
+      if (idx >= R8 * BLOCK_N || row >= BM || feat >= p.M || tok >= p.N) continue;
+      float acc[8];
 #pragma unroll
-        for (int src = 0; src < CLUSTER; ++src) {
-          const float4* rp = reinterpret_cast<const float4*>(recv + ((size_t)src * BLOCK_N + tok) * R + f8 * 8);
-          const float4 a0 = rp[0], a1 = rp[1];
-          acc[0] += a0.x; acc[1] += a0.y; acc[2] += a0.z; acc[3] += a0.w;
-          acc[4] += a1.x; acc[5] += a1.y; acc[6] += a1.z; acc[7] += a1.w;
-        }
-        uint4 o;
-        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-        const size_t soff = (size_t)q.rank * q.slot_stride + (size_t)tok * q.ld + feat;
-        if (pmode == 2) {
-          *reinterpret_cast<uint4*>(q.slots[owner_rank] + soff) = o;
-        } else {
-#pragma unroll
-          for (int r = 0; r < 8; ++r)
-            if (r < q.world) *reinterpret_cast<uint4*>(q.slots[(q.rank + r) % q.world] + soff) = o;
-        }
+      for (int src = 0; src < CLUSTER; ++src) {
+        const float4* rp = reinterpret_cast<const float4*>(recv + ((size_t)src * BLOCK_N + tok) * R + f8 * 8);
+        const float4 a0 = rp[0], a1 = rp[1];
+        acc[0] += a0.x; acc[1] += a0.y; acc[2] += a0.z; acc[3] += a0.w;
+        acc[4] += a1.x; acc[5] += a1.y; acc[6] += a1.z; acc[7] += a1.w;
       }
-      if (et == 0) s_peer_fail = 0;
-      epi_bar_sync();
-      // ---- phase-one flags: "my partial of this slice has landed" ----
-      if (et < q.world) {
-        const int peer = et;
-        if (pmode == 1 || peer == owner_rank)
-          st_release_sys_u32(q.flags[peer] + (size_t)blockIdx.x * 16 + q.rank, epoch);
-        if (i_finish && !peer_flag_wait(q.flags[q.rank] + (size_t)blockIdx.x * 16 + peer, epoch, 1100, q.rank, peer))
-          s_peer_fail = 1;
-      }
-      epi_bar_sync();
-      peer_ok = s_peer_fail == 0;
-      if (tr && et == 0) tr[5] = global_timer_ns();          // peers' partials have arrived
-      if (et == 0) q.epochs[blockIdx.x] = epoch;
-      if (pmode == 2 && !i_finish) {
-        // the owner's final pass stores the finished slice into this rank's output and then raises the second flag
-        if (et == 0 && !peer_flag_wait(q.flags[q.rank] + (size_t)blockIdx.x * 16 + 8, epoch, 1200, q.rank, owner_rank))
-          s_peer_fail = 1;
-        epi_bar_sync();
-        peer_ok = s_peer_fail == 0;
+      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&own[it]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      const size_t line = (((size_t)q.rank * q.cap + tok) * ld8 + (feat >> 3)) * 2;
+      const uint4 l0 = make_uint4(own[it].x, epoch, own[it].y, epoch);
+      const uint4 l1 = make_uint4(own[it].z, epoch, own[it].w, epoch);
+      if (pmode == 2) {
+        if (!i_finish) {
+          st_line(q.slots[owner_rank] + line, l0);
+          st_line(q.slots[owner_rank] + line + 1, l1);
+        }
+      } else {
+#pragma unroll
+        for (int r = 1; r < 8; ++r) {
+          if (r < q.world) {
+            uint4* dst = q.slots[(q.rank + r) % q.world] + line;
+            st_line(dst, l0);
+            st_line(dst + 1, l1);
+          }
+        }
       }
     }
-    for (int idx = et; peer_ok && idx < R8 * BLOCK_N; idx += 128) {
+    // pass 2: sum in rank order (bit-identical on every rank), add the residual, store; or take the owner's rows
+    bool failed = false;
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+      const int idx = et + it * 128;
+      const int f8 = idx % R8, tok = idx / R8;
+      const int row = (int)crank * R + f8 * 8;
+      const int feat = tile_m * BM + row;
+      float ss = 0.f;
+      const bool valid = !(idx >= R8 * BLOCK_N || row >= BM || feat >= p.M || tok >= p.N);
+      if (valid && !failed) {
+        const size_t off = (size_t)tok * p.ldd + feat;
+        uint4 o;
+        if (i_finish) {
+          float acc[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            if (r < q.world && !failed) {
+              uint4 u = own[it];
+              if (r != q.rank) {
+                const uint4* src = q.slots[q.rank] + (((size_t)r * q.cap + tok) * ld8 + (feat >> 3)) * 2;
+                failed = !ld_lines(src, epoch, u, 1100, q.rank, r);
+              }
+              const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 t = __bfloat1622float2(uh[j]);
+                acc[2 * j] += t.x;
+                acc[2 * j + 1] += t.y;
+              }
+            }
+          }
+          if (p.residual) {
+            const uint4 r = *reinterpret_cast<const uint4*>(p.residual + (size_t)tok * p.ld_res + feat);
+            const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 t = __bfloat1622float2(rh[j]);
+              acc[2 * j] += t.x;
+              acc[2 * j + 1] += t.y;
+            }
+          }
+          __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+          if (pmode == 2 && !failed) {
+            const size_t line = ((size_t)tok * ld8 + (feat >> 3)) * 2;
+            const uint4 l0 = make_uint4(o.x, epoch, o.y, epoch);
+            const uint4 l1 = make_uint4(o.z, epoch, o.w, epoch);
+#pragma unroll
+            for (int r = 1; r < 8; ++r) {
+              if (r < q.world) {
+                uint4* dst = q.result[(q.rank + r) % q.world] + line;
+                st_line(dst, l0);
+                st_line(dst + 1, l1);
+              }
+            }
+          }
+        } else {
+          failed = !ld_lines(q.result[q.rank] + ((size_t)tok * ld8 + (feat >> 3)) * 2, epoch, o, 1200, q.rank, owner_rank);
+        }
+        if (!failed) {
+          *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + off) = o;
+          const __nv_bfloat162* oh = reinterpret_cast<const __nv_bfloat162*>(&o);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 t = __bfloat1622float2(oh[j]);
+            ss += t.x * t.x + t.y * t.y;
+          }
+        }
+      }
+      if (p.ssq_out && idx < R8 * BLOCK_N) {   // warp-uniform (R8 * BLOCK_N is a multiple of 32)
+        for (int o2 = 1; o2 < R8; o2 <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o2);
+        if (f8 == 0 && valid) atomicAdd(p.ssq_out + tok, ssq_fixed(ss));
+      }
+    }
+    epi_bar_sync();     // every thread has read its epoch
+    if (et == 0) q.epochs[blockIdx.x] = counter;
+  } else if (warp >= 2) {
+    const int et = (warp - 2) * 32 + lane;  // 0..127
+    constexpr int R8 = R / 8;
+    for (int idx = et; idx < R8 * BLOCK_N; idx += 128) {
       const int f8 = idx % R8;         // consecutive threads -> consecutive 16-byte feature groups of one token
       const int tok = idx / R8;
       const int row = (int)crank * R + f8 * 8;
@@ -358,34 +444,6 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
       float acc[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-      const size_t off = (size_t)tok * p.ldd + feat;
-      if (pmode) {
-        if (!i_finish) {
-          // the owner stored the finished row slice into this rank's output: only the sum of squares is left
-          const uint4 r = ld_relaxed_sys_16(reinterpret_cast<const bf16*>(p.out) + off);
-          const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&r);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 t = __bfloat1622float2(rh[j]);
-            ss += t.x * t.x + t.y * t.y;
-          }
-          break;
-        }
-        // sum the ranks' partials in rank order: every rank computes bit-identical rows
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-          if (r < q.world) {
-            const uint4 u = ld_relaxed_sys_16(q.slots[q.rank] + (size_t)r * q.slot_stride + (size_t)tok * q.ld + feat);
-            const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 t = __bfloat1622float2(uh[j]);
-              acc[2 * j] += t.x;
-              acc[2 * j + 1] += t.y;
-            }
-          }
-        }
-      } else {
 #pragma unroll
       for (int src = 0; src < CLUSTER; ++src) {
         const float4* rp = reinterpret_cast<const float4*>(recv + ((size_t)src * BLOCK_N + tok) * R + f8 * 8);
@@ -393,13 +451,13 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
         acc[0] += a0.x; acc[1] += a0.y; acc[2] += a0.z; acc[3] += a0.w;
         acc[4] += a1.x; acc[5] += a1.y; acc[6] += a1.z; acc[7] += a1.w;
       }
-      }
       if (p.ssq_in) {
         const float rs = s_rstd[tok];
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] *= rs;
       }
       const int nvalid = min(8, p.M - feat);
+      const size_t off = (size_t)tok * p.ldd + feat;
       const bool vec = p.vec_ok && nvalid == 8 && ((p.ldd & 7) == 0) && ((feat & 7) == 0) && (!p.residual || (p.ld_res & 7) == 0);   // gated pairs: ldd % 8 == 0 keeps the 8-byte stores aligned
       if (vec) {
         if (p.bias) {
@@ -445,13 +503,7 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
           __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
           for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-          if (pmode == 2) {
-#pragma unroll
-            for (int r = 0; r < 8; ++r)
-              if (r < q.world) *reinterpret_cast<uint4*>(q.out_peers[(q.rank + r) % q.world] + off) = o;
-          } else {
-            *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + off) = o;
-          }
+          *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + off) = o;
           if (p.ssq_out) {   // sum of squares of exactly what was stored (bf16-rounded)
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -480,17 +532,11 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
       } while (0);
       if (p.ssq_out) {       // every lane of the warp arrives here: reduce over the R8 threads that share a token
         for (int o2 = 1; o2 < R8; o2 <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o2);
-        if (f8 == 0 && tok < BLOCK_N) p.ssq_out[64 + (size_t)blockIdx.x * 64 + tok] = ss;
+        if (f8 == 0 && tok < p.N && row < BM) atomicAdd(p.ssq_out + tok, ssq_fixed(ss));
       }
-    }
-    if (pmode == 2 && i_finish && peer_ok) {
-      // phase two: the finished slice is in every rank's output buffer
-      epi_bar_sync();
-      if (et < q.world && et != q.rank) st_release_sys_u32(q.flags[et] + (size_t)blockIdx.x * 16 + 8, epoch);
     }
   }
 
-  if (p.ssq_out && blockIdx.x == 0 && threadIdx.x == 64) p.ssq_out[0] = __int_as_float((int)gridDim.x);
   if (tr && threadIdx.x == 64) tr[6] = global_timer_ns();    // outputs stored
   tc_fence_before_sync();
   __syncthreads();
@@ -575,8 +621,9 @@ int gemm_decode_cluster_launch(const GemmArgs& a, int force_cluster, cudaStream_
   p.residual = reinterpret_cast<const __nv_bfloat16*>(a.residual);
   p.ld_res = a.ld_res;
   p.act = a.act;
-  p.ssq_out = a.ssq_out;
-  p.ssq_in = a.ssq_in;
+  p.ssq_out = reinterpret_cast<unsigned long long*>(a.ssq_out);
+  p.ssq_in = reinterpret_cast<const unsigned long long*>(a.ssq_in);
+  p.ssq_zero = reinterpret_cast<unsigned long long*>(a.ssq_zero);
   p.norm_dim = a.norm_dim;
   p.norm_eps = a.norm_eps;
   p.trace = gemm_trace_buffer();
@@ -602,16 +649,17 @@ int gemm_decode_cluster_launch(const GemmArgs& a, int force_cluster, cudaStream_
     if (a.bias || a.act != SWB_ACT_NONE || a.out_fp32 || a.ssq_in || !p.vec_ok || (a.ldd & 7) || (a.N % BM) ||
         (q.ld & 7) || (a.residual && (a.ld_res & 7)))
       return -3;
-    if (q.mode == 2 && p.tiles_m < q.world) p.peer.mode = 1;   // every rank must own a tile for the flags to order buffer reuse
-    if (force_cluster <= 0) cluster = std::min(cluster, 4);
+    if (q.mode == 2 && p.tiles_m < q.world) p.peer.mode = 1;   // every rank must own a tile for the lines to order buffer reuse
+    if (a.T > q.cap) return -3;
     if (cluster == 3) cluster = 2;
+    if (cluster == 6) cluster = 4;
     if (p.tiles_m * cluster > SWB_PEER_MAX_CTAS) return -3;
   }
   if (a.ssq_out || a.ssq_in) {
     // the per-token reduction in the producer's epilogue pairs lanes by xor: rows per member / 8 must be a power of two
     if (cluster == 3) cluster = 2;
     if (cluster == 6) cluster = 4;
-    if (a.ssq_out && (a.N % BM != 0 || a.out_fp32 || p.tiles_m * cluster > 512)) return -3;
+    if (a.ssq_out && (a.N % BM != 0 || a.out_fp32)) return -3;
     if (!p.vec_ok || (a.ldd & 7) != 0) return -3;
   }
   CUtensorMap tw, tx;

@@ -34,28 +34,28 @@ struct GemmScatter {
 };
 
 // Sum of a row-parallel decode GEMM over the tensor-parallel ranks, performed inside the cluster kernel's epilogue
-// over peer memory (plain 16-byte peer stores and system-scope flags; no collective library call, no multicast).
-// CTA b of every rank owns the same slice of the output, so the exchange is per CTA: a slice is summed as soon as the
-// same CTA of every peer has delivered it, while other CTAs are still streaming weights.
-// mode 1 (one shot): each CTA stores its bf16 partial slice into slot `rank` of EVERY rank's slot buffer
-//   [world][max_tokens][ld], release-stores epoch flags, waits for the flags of all peers, then sums the `world`
-//   slots in rank order (bit-identical on every rank), adds the local residual and stores the row.
-// mode 2 (two shot): the slice of weight tile t belongs to rank t % world. Every rank stores its partial only into
-//   the owner's slot buffer; the owner sums, adds its residual and stores the finished bf16 slice into every rank's
-//   output buffer (`out_peers`, symmetric), then raises a second flag the other ranks wait for. 2 (world - 1) / world
-//   of the one-shot traffic at the price of a second hop.
-// flags: per rank a pad of [SWB_PEER_MAX_CTAS][16] words (0..7: phase-one flag per source rank, 8: phase two);
-// epochs: local [SWB_PEER_MAX_CTAS] counters advanced by the kernel (graph-replay safe). Two slot buffers must
-// alternate between consecutive reductions of a stream (a buffer is rewritten only after the next reduction's flags
-// proved that every peer finished reading it).
+// over peer memory (plain 16-byte peer stores; no collective library call, no multicast, no fence, no barrier).
+// Rows travel as flag-in-data lines: 16 bytes = {2 bf16, epoch, 2 bf16, epoch}; a reader spins (bounded) on the
+// lines it needs until both epochs match, so a row costs one NVLink hop and the wire carries 2x the row bytes.
+// CTA b of every rank owns the same slice of the output, so the exchange is per CTA and per 16-byte group.
+// mode 1 (one shot): each CTA stores its bf16 partial slice into slot `rank` of every PEER's slot buffer
+//   [world][cap tokens][ld / 8][2 lines], keeps its own slice in registers, then sums the `world` contributions in
+//   rank order (bit-identical on every rank), adds the local residual and stores the rows.
+// mode 2 (two shot): the slice of weight tile t belongs to rank t % world. Every rank sends its partial only to the
+//   owner; the owner sums, adds its residual, stores its own rows and sends the finished bf16 slice to every peer's
+//   result buffer [cap][ld / 8][2 lines], from which the peers copy it into their output. About 2 / world of the
+//   one-shot traffic at the price of a second hop.
+// epochs: local [SWB_PEER_MAX_CTAS] launch counters advanced by the kernel (graph-replay safe); a line's epoch is
+// (counter << 9 | CTA index). Two slot / result buffer pairs must alternate between consecutive reductions of a
+// stream: a rank enters reduction k + 2 only after reduction k + 1 delivered every peer's lines to it, which those
+// peers sent after they had finished reading reduction k.
 constexpr int SWB_PEER_MAX_CTAS = 512;
 struct GemmPeerReduce {
-  __nv_bfloat16* slots[8];
-  uint32_t* flags[8];
-  __nv_bfloat16* out_peers[8];
+  uint4* slots[8];
+  uint4* result[8];
   uint32_t* epochs;
-  long long slot_stride;   // elements between two source ranks' slots
-  int ld;                  // row stride of a slot
+  int cap;                 // token rows of a slot
+  int ld;                  // row width in elements (multiple of 8)
   int mode, world, rank;
 };
 
@@ -86,12 +86,14 @@ struct GemmParams {
   const int* group_of_mtile;
   int group_rows;
   // RMSNorm folded into a chain of decode GEMMs (cluster kernel only). A producer (o / down projection with the
-  // residual add in its epilogue) writes, per CTA and token, the sum of squares of the rows it stored:
-  // ssq_out[0] = CTA count (as int bits), ssq_out[64 + cta * 64 + token]. The consumer (qkv / gate-up projection on the
-  // un-normalised residual stream, norm weight pre-multiplied into its weights) sums those partials in CTA order and
-  // scales its accumulators by rsqrt(sum / norm_dim + eps) per token.
-  float* ssq_out;
-  const float* ssq_in;
+  // residual add in its epilogue) adds, per token, the sum of squares of the rows it stored to ssq_out[token] in
+  // 2^-24 fixed point (64 x u64; integer adds commute, so the result does not depend on CTA order). The consumer
+  // (qkv / gate-up projection on the un-normalised residual stream, norm weight pre-multiplied into its weights)
+  // scales its accumulators by rsqrt(sum / norm_dim + eps) per token. An accumulator must be zero when its producer
+  // starts: each producer zeroes the chain's OTHER accumulator (ssq_zero), whose consumer has finished by then.
+  unsigned long long* ssq_out;
+  const unsigned long long* ssq_in;
+  unsigned long long* ssq_zero;
   int norm_dim;
   float norm_eps;
   GemmPeerReduce peer;   // decode cluster kernel only
@@ -119,8 +121,9 @@ struct GemmArgs {
   const GemmScatter* scatter = nullptr;
   const int* group_of_mtile = nullptr;   // device [ceil(T / 128)]: weight group per 128-row tile, < 0 = skip
   int groups = 0;                        // W is [groups * N, K] when group_of_mtile is set
-  float* ssq_out = nullptr;              // see GemmParams (decode cluster kernel only)
-  const float* ssq_in = nullptr;
+  void* ssq_out = nullptr;               // see GemmParams (decode cluster kernel only): 64 x u64
+  const void* ssq_in = nullptr;
+  void* ssq_zero = nullptr;
   int norm_dim = 0;
   float norm_eps = 0.f;
   const GemmPeerReduce* peer = nullptr;  // see GemmPeerReduce (decode cluster kernel only)

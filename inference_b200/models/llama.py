@@ -236,7 +236,7 @@ class LlamaGpu:
                           all(ops.gated_fused(64, n & ~1, k) or (par and i in (1, 3) and k % 64 == 0)
                               for i, (n, k) in enumerate(shapes)))
         if self._chain_ok:
-            self._ssq = [torch.zeros(ops.SSQ_FLOATS, dtype=torch.float32, device=self.device) for _ in range(2)]
+            self._ssq = [ops.ssq_buffer(self.device) for _ in range(2)]
 
     def gather_unsharded(self, dst: int = 0) -> "LlamaGpu | None":
         """Collective over the model's ranks: rebuilds the complete (tensor-parallel degree 1) model on rank `dst`
@@ -371,10 +371,7 @@ class LlamaGpu:
         if chain and self.comm.is_parallel:
             chain = fc is not None and T <= fc.chain_tokens and stage_in is None
         if stage_in is None:
-            # (sharded chain: the residual stream lives in symmetric memory, the two-shot reduction stores into it
-            # from the peers)
-            res = ops.embedding(inp.input_ids, self.embed, scale=cfg.embed_scale,
-                                out=fc.residual_stream(T) if (chain and fc is not None) else None)
+            res = ops.embedding(inp.input_ids, self.embed, scale=cfg.embed_scale)
             if inp.embed_rows is not None:
                 res.index_copy_(0, inp.embed_rows, inp.embed_values.to(res.dtype))
             branch = None
@@ -426,15 +423,17 @@ class LlamaGpu:
                     n += 1
                 gelu = cfg.mlp_activation in ("gelu", "gelu_tanh")
                 if fc is not None:
-                    fc.gemm_peer_reduce(attn.reshape(T, -1), L.o, res, 0, ssq_out=self._ssq[0])
+                    fc.gemm_peer_reduce(attn.reshape(T, -1), L.o, res, 0, ssq_out=self._ssq[0], ssq_zero=self._ssq[1])
                 else:
-                    ops.gemm_bf16_normed(attn.reshape(T, -1), L.o, out=res, residual=res, ssq_out=self._ssq[0])
+                    ops.gemm_bf16_normed(attn.reshape(T, -1), L.o, out=res, residual=res, ssq_out=self._ssq[0],
+                                         ssq_zero=self._ssq[1])
                 act = ops.gemm_bf16_normed(res, L.gate_up, act="geglu_pairs" if gelu else "swiglu_pairs",
                                            ssq_in=self._ssq[0], norm_dim=H, eps=eps)
                 if fc is not None:
-                    fc.gemm_peer_reduce(act, L.down, res, 1, ssq_out=self._ssq[1])
+                    fc.gemm_peer_reduce(act, L.down, res, 1, ssq_out=self._ssq[1], ssq_zero=self._ssq[0])
                 else:
-                    ops.gemm_bf16_normed(act, L.down, out=res, residual=res, ssq_out=self._ssq[1])
+                    ops.gemm_bf16_normed(act, L.down, out=res, residual=res, ssq_out=self._ssq[1],
+                                         ssq_zero=self._ssq[0])
                 ssq_prev, pending_h = self._ssq[1], None
                 n += (6 if inp.attn_splits == 1 else 7) + (1 if h is not None else 0)
                 continue

@@ -72,18 +72,30 @@ def gemm_bf16_grouped(a: torch.Tensor, w: torch.Tensor, tile_groups: torch.Tenso
     return out
 
 
-SSQ_FLOATS = 64 + 512 * 64
+SSQ_WORDS = 64      # one u64 accumulator per token (2^-24 fixed point)
+
+
+def ssq_buffer(device: torch.device) -> torch.Tensor:
+    """A zeroed per-token sum-of-squares accumulator for a folded-RMSNorm chain (see gemm_bf16_normed)."""
+    return torch.zeros(SSQ_WORDS, dtype=torch.int64, device=device)
+
+
+def ssq_values(buf: torch.Tensor) -> torch.Tensor:
+    """The accumulated sums of squares as fp32 [64]."""
+    return buf.double().mul(2.0 ** -24).float()
 
 
 def gemm_bf16_normed(a: torch.Tensor, w: torch.Tensor, *, out: torch.Tensor | None = None,
                      bias: torch.Tensor | None = None, residual: torch.Tensor | None = None, act: str | None = None,
-                     ssq_in: torch.Tensor | None = None, ssq_out: torch.Tensor | None = None, norm_dim: int = 0,
-                     eps: float = 0.0) -> torch.Tensor:
+                     ssq_in: torch.Tensor | None = None, ssq_out: torch.Tensor | None = None,
+                     ssq_zero: torch.Tensor | None = None, norm_dim: int = 0, eps: float = 0.0) -> torch.Tensor:
     """One link of a folded-RMSNorm chain of decode GEMMs (T <= 64; see swb_gemm_bf16_normed).
 
     Consumer link (`ssq_in`): `a` is the un-normalised residual stream and `w` already carries the norm weight;
     the result is rmsnorm(a) @ w^T. Producer link (`ssq_out`): stores a @ w^T + residual (in place when out is
-    residual) and the partial sums of squares of what it stored. fp32 buffers of SSQ_FLOATS elements."""
+    residual) and adds the per-token sums of squares of what it stored to `ssq_out`, which must be zero at launch;
+    `ssq_zero` is cleared by the launch (a chain alternates two accumulators: each producer clears the other one).
+    Accumulators come from `ssq_buffer`."""
     require_cuda(a, w)
     T, K = a.shape
     N = w.shape[0]
@@ -91,12 +103,12 @@ def gemm_bf16_normed(a: torch.Tensor, w: torch.Tensor, *, out: torch.Tensor | No
     if out is None:
         out = torch.empty((T, n_out), dtype=torch.bfloat16, device=a.device)
     assert out.shape == (T, n_out) and out.dtype == torch.bfloat16 and a.stride(1) == 1 and w.stride(1) == 1
-    for b in (ssq_in, ssq_out):
-        assert b is None or (b.dtype == torch.float32 and b.numel() >= SSQ_FLOATS and b.is_contiguous())
+    for b in (ssq_in, ssq_out, ssq_zero):
+        assert b is None or (b.dtype == torch.int64 and b.numel() >= SSQ_WORDS and b.is_contiguous())
     rc = kernels().swb_gemm_bf16_normed(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
                                         out.stride(0), T, N, K, ptr(bias), ptr(residual),
                                         residual.stride(0) if residual is not None else 0, ACT[act], ptr(ssq_in),
-                                        ptr(ssq_out), norm_dim, eps, stream_ptr())
+                                        ptr(ssq_out), ptr(ssq_zero), norm_dim, eps, stream_ptr())
     check(rc, "swb_gemm_bf16_normed")
     return out
 

@@ -52,29 +52,25 @@ class FusedCollectives:
         self._am_val_ptrs = (ctypes.c_void_p * comm.world)(*[int(p) for p in vh.buffer_ptrs])
         self._am_id_ptrs = (ctypes.c_void_p * comm.world)(*[int(p) for p in ih.buffer_ptrs])
         self._handles += [vh, ih]
-        # In-GEMM reduction of the row-parallel decode projections (GemmPeerReduce in gemm_tcgen05.cuh): two slot
-        # buffers [world, chain_tokens, hidden] (attention-out uses 0, MLP-down uses 1, so consecutive reductions
-        # alternate), flag pad [ctas, 16], local epoch counters, and the symmetric residual stream [chain_tokens,
-        # hidden] into which the two-shot mode stores finished rows on every rank.
+        # In-GEMM reduction of the row-parallel decode projections (GemmPeerReduce in gemm_tcgen05.cuh): two pairs of
+        # line buffers (attention-out uses pair 0, MLP-down pair 1, so consecutive reductions alternate): slots
+        # [world, chain_tokens, hidden / 8, 2 lines of 16 bytes] for the partial rows and results [chain_tokens,
+        # hidden / 8, 2] for the rows a two-shot owner finishes; local launch counters per CTA.
         self.chain_tokens = min(64, max_tokens)
         ctas = L.swb_gemm_peer_max_ctas()
-        self._pr_slots, self._pr_slot_ptrs = [], []
+        self._pr_slots, self._pr_slot_ptrs, self._pr_results, self._pr_result_ptrs = [], [], [], []
         for _ in range(2):
-            t = symm_mem.empty((comm.world, self.chain_tokens, hidden), dtype=torch.bfloat16, device=dev)
-            t.zero_()
-            h = symm_mem.rendezvous(t, comm.group)
-            self._pr_slots.append(t)
-            self._pr_slot_ptrs.append((ctypes.c_void_p * comm.world)(*[int(p) for p in h.buffer_ptrs]))
-            self._handles.append(h)
-        self._pr_flags = symm_mem.empty((ctas * 16,), dtype=torch.int32, device=dev)
-        self._pr_flags.zero_()
-        pfh = symm_mem.rendezvous(self._pr_flags, comm.group)
-        self._pr_flag_ptrs = (ctypes.c_void_p * comm.world)(*[int(p) for p in pfh.buffer_ptrs])
+            for shape, keep, ptrs in (((comm.world, self.chain_tokens, hidden // 8, 2, 4), self._pr_slots,
+                                       self._pr_slot_ptrs),
+                                      ((self.chain_tokens, hidden // 8, 2, 4), self._pr_results,
+                                       self._pr_result_ptrs)):
+                t = symm_mem.empty(shape, dtype=torch.int32, device=dev)
+                t.zero_()
+                h = symm_mem.rendezvous(t, comm.group)
+                keep.append(t)
+                ptrs.append((ctypes.c_void_p * comm.world)(*[int(p) for p in h.buffer_ptrs]))
+                self._handles.append(h)
         self._pr_epochs = torch.zeros(ctas, dtype=torch.int32, device=dev)
-        self._pr_res = symm_mem.empty((self.chain_tokens, hidden), dtype=torch.bfloat16, device=dev)
-        prh = symm_mem.rendezvous(self._pr_res, comm.group)
-        self._pr_res_ptrs = (ctypes.c_void_p * comm.world)(*[int(p) for p in prh.buffer_ptrs])
-        self._handles += [pfh, prh]
         mode = os.environ.get("SWB_TP_REDUCE", "auto")
         self.reduce_mode = {"1": 1, "oneshot": 1, "2": 2, "twoshot": 2}.get(mode, 0)
         # Buffers 0/1 serve captured CUDA graphs (every capture starts at 0 and must contain an even number of
@@ -131,34 +127,31 @@ class FusedCollectives:
         self._launch(i, T, residual, norm_w, eps, w_offset, out)
         return out
 
-    def residual_stream(self, tokens: int) -> torch.Tensor:
-        """Rows [0, tokens) of the symmetric residual-stream buffer (every rank holds the same values)."""
-        assert tokens <= self.chain_tokens
-        return self._pr_res[:tokens]
-
     def peer_reduce_mode(self, tokens: int) -> int:
-        """1 = one shot (every rank receives every partial), 2 = two shot (owners sum and broadcast). One shot moves
-        (world - 1) x the row bytes per rank and has one hop; two shot moves about 2 x and has two hops."""
+        """1 = one shot (every rank receives every partial), 2 = two shot (owners sum and send the finished rows).
+        One shot moves (world - 1) x the row bytes per rank and has one hop; two shot moves about 2 x and has two."""
         if self.reduce_mode:
             return self.reduce_mode
-        return 2 if self.comm.world > 2 and tokens * self.hidden * 2 * (self.comm.world - 1) > (1 << 20) else 1
+        return 2 if self.comm.world > 2 and tokens * self.hidden * 4 * (self.comm.world - 1) > (1 << 20) else 1
 
     def gemm_peer_reduce(self, a: torch.Tensor, w: torch.Tensor, res: torch.Tensor, which: int,
-                         ssq_out: torch.Tensor | None = None, cluster: int = 0) -> torch.Tensor:
+                         ssq_out: torch.Tensor | None = None, ssq_zero: torch.Tensor | None = None,
+                         cluster: int = 0) -> torch.Tensor:
         """res += sum over ranks of (a @ w^T), summed inside the GEMM's epilogue over peer memory (one kernel; no
-        collective call). `res` must be `residual_stream(T)`; `which` (0: attention-out, 1: MLP-down) picks the slot
-        buffer. ssq_out receives the per-CTA sums of squares of the new residual rows (folded-norm chain)."""
+        collective call). `which` (0: attention-out, 1: MLP-down) picks the line-buffer pair; consecutive calls on
+        a stream must alternate it. ssq_out accumulates the per-token sums of squares of the new residual rows,
+        ssq_zero is cleared (folded-norm chain, see ops.gemm_bf16_normed)."""
         T = a.shape[0]
-        assert T <= self.chain_tokens and res.data_ptr() == self._pr_res.data_ptr() and res.shape == (T, self.hidden)
+        assert T <= self.chain_tokens and res.shape == (T, self.hidden) and res.stride(1) == 1
         a2 = a.reshape(T, -1)
         mode = self.peer_reduce_mode(T)
         rc = kernels().swb_gemm_bf16_peer_reduce(
             a2.data_ptr(), a2.stride(0), w.data_ptr(), w.stride(0), res.data_ptr(), res.stride(0), T, w.shape[0],
-            a2.shape[1], res.data_ptr(), res.stride(0), ptr(ssq_out), self._pr_slot_ptrs[which], self._pr_flag_ptrs,
-            self._pr_res_ptrs, self._pr_epochs.data_ptr(), self.chain_tokens * self.hidden, self.hidden, mode,
+            a2.shape[1], res.data_ptr(), res.stride(0), ptr(ssq_out), ptr(ssq_zero), self._pr_slot_ptrs[which],
+            self._pr_result_ptrs[which], self._pr_epochs.data_ptr(), self.chain_tokens, self.hidden, mode,
             self.comm.world, self.comm.rank, cluster, stream_ptr())
         check(rc, "swb_gemm_bf16_peer_reduce")
-        self.comm.bytes_moved += T * self.hidden * 2 * ((self.comm.world - 1) if mode == 1 else 2)
+        self.comm.bytes_moved += T * self.hidden * 4 * ((self.comm.world - 1) if mode == 1 else 2)
         return res
 
     def argmax_vocab_parallel(self, local_logits: torch.Tensor, vocab_local: int) -> torch.Tensor:

@@ -64,22 +64,21 @@ def main():
                 part = (a.float() @ wgt.float().t()).bfloat16()
                 allp = comm.all_gather(part[None], dim=0).float()
                 want = (allp.sum(0) + res0.float()).bfloat16()
-                res = fc.residual_stream(T)
-                res.copy_(res0)
-                torch.cuda.synchronize()
-                comm.barrier()
-                ssq = torch.zeros(ops.SSQ_FLOATS, dtype=torch.float32, device=dev)
-                fc.gemm_peer_reduce(a, wgt, res, it & 1, ssq_out=ssq)
+                res = res0.clone()
+                ssq, other = ops.ssq_buffer(dev), ops.ssq_buffer(dev).fill_(5)
+                fc.gemm_peer_reduce(a, wgt, res, it & 1, ssq_out=ssq, ssq_zero=other)
                 torch.cuda.synchronize()
                 fc.check()
                 err = (res.float() - want.float()).abs().max().item()
                 assert err < 0.06, f"rank {r}: peer-reduce GEMM mode {mode_id} T={T} err {err}"
                 allr = comm.all_gather(res.clone()[None], dim=0)
                 assert all(torch.equal(allr[0], allr[k]) for k in range(P)), f"mode {mode_id}: ranks differ"
-                nct = int(ssq[:1].view(torch.int32).item())
-                got_ss = ssq[64:64 + nct * 64].view(nct, 64).sum(0)[:T]
+                got_ss = ops.ssq_values(ssq)[:T]
                 ref_ss = res.float().pow(2).sum(-1)
-                assert torch.allclose(got_ss, ref_ss, rtol=1e-3, atol=1e-3), f"mode {mode_id} T={T}: ssq"
+                assert torch.allclose(got_ss, ref_ss, rtol=1e-4, atol=1e-4), f"mode {mode_id} T={T}: ssq"
+                assert int(other.abs().sum()) == 0, "the other accumulator was not cleared"
+                allq = comm.all_gather(ssq[None], dim=0)
+                assert all(torch.equal(allq[0], allq[k]) for k in range(P)), "sums of squares differ between ranks"
                 comm.barrier()
     fc.reduce_mode = 0
 
