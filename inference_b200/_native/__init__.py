@@ -64,6 +64,8 @@ def _declare_kernels(lib: ctypes.CDLL) -> None:
     sig("swb_status_read", [ctypes.POINTER(c_int)])
     sig("swb_status_clear", [])
     sig("swb_set_wait_limit_ns", [ctypes.c_ulonglong])
+    sig("swb_set_timeline", [c_void_p])
+    sig("swb_gemm_set_trace", [c_void_p], None)
     sig("swb_sm_count", [])
     sig("swb_gemm_workspace_min", [], c_size_t)
     sig("swb_gemm_bf16", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,

@@ -10,9 +10,11 @@ unsigned long long* gemm_trace_buffer() { return g_trace; }
 
 extern "C" {
 
-// Profiling aid: when set to a device buffer of at least grid * 8 uint64, decode GEMM CTAs record globaltimer
-// stamps of their phases (start, setup done, dependency satisfied, accumulator complete, partials delivered,
-// cluster barrier passed, outputs stored, end). Pass null to switch it off.
+// Profiling aid: when set to a device buffer of at least grid * 16 uint64, decode GEMM CTAs record per CTA eight
+// globaltimer stamps of their phases (start, setup done, dependency satisfied, accumulator complete, partials
+// delivered, cluster barrier passed, outputs stored, end) followed by eight SM-clock stamps of the epilogue
+// ([8] barrier passed, [9] first group summed, [10] first group stored, [11] all stored, [12] accumulator complete,
+// [13] partials delivered, [14] first group's sum of squares sent). Pass null to switch it off.
 void swb_gemm_set_trace(void* device_buffer) { swb::g_trace = reinterpret_cast<unsigned long long*>(device_buffer); }
 
 int swb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* D, int ldd, int T, int N, int K,

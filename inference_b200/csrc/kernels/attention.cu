@@ -15,6 +15,8 @@
 #include "gemm_tcgen05.cuh"
 
 namespace swb {
+
+SWB_REGISTER_STATUS_UNIT(attention);
 int g_dense_impl = 0;
 using namespace attn;
 namespace {
@@ -53,7 +55,7 @@ __device__ __forceinline__ void load_kv_tile(const AttnParams& p, int seq, int k
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnParams p) {
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait(TL_ATTN_PREFILL);
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t sQ = smem_u32(smem);
   const uint32_t sKV = sQ + TILE_BYTES;  // stage s: K at sKV + s*2*TILE, V at + TILE
@@ -226,7 +228,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnParams p) {
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait(TL_ATTN_DECODE);
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t sQ = smem_u32(smem);           // 16 rows x 256 B = 4 KB
   const uint32_t sKV = sQ + 16 * 256;            // 2 stages x (K, V)
@@ -419,7 +421,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnParams p) {
 
 __global__ void __launch_bounds__(128) attn_merge_kernel(const AttnParams p) {
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait(TL_ATTN_MERGE);
   const int kvh = blockIdx.x;
   const int seq = blockIdx.y;
   const int q_start = p.cu_q ? p.cu_q[seq] : seq * p.uniform_q_len;
@@ -473,8 +475,11 @@ int attn_decode_tma_launch(const AttnParams& p, int num_blocks, cudaStream_t str
 extern "C" {
 
 // Bytes of fp32 scratch the decode path needs for `num_splits` KV splits.
+// Split-KV scratch: [ticket counters: num_seqs * Hkv ints, rounded up to 256 bytes][partial O][partial max / sum].
+// The counters must be zero before the first launch (the kernel leaves them zero).
+static size_t attn_counter_bytes(int num_seqs, int Hkv) { return (((size_t)num_seqs * Hkv * sizeof(int)) + 255) / 256 * 256; }
 size_t swb_attn_decode_workspace_bytes(int num_seqs, int Hkv, int num_splits) {
-  return (size_t)num_seqs * Hkv * num_splits * 16 * (swb::HD + 2) * sizeof(float);
+  return attn_counter_bytes(num_seqs, Hkv) + (size_t)num_seqs * Hkv * num_splits * 16 * (swb::HD + 2) * sizeof(float);
 }
 
 // Paged-KV attention. q: [T, Hq, 128] with element strides; out: [T, Hq*128] rows of stride out_stride_tok.
@@ -521,13 +526,15 @@ int swb_attn_paged(const void* q, long long q_stride_tok, int q_stride_head, voi
   if (num_splits < 1) num_splits = 1;
   if (num_splits > 1) {
     if (!workspace || workspace_bytes < swb_attn_decode_workspace_bytes(num_seqs, Hkv, num_splits)) return -5;
-    p.part_o = reinterpret_cast<float*>(workspace);
+    if (num_splits > 32) num_splits = 32;
+    p.part_o = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + attn_counter_bytes(num_seqs, Hkv));
     p.part_ml = p.part_o + (size_t)num_seqs * Hkv * num_splits * 16 * HD;
   }
   p.num_splits = num_splits;
   if (block_size == 16 && num_blocks > 0 && kv_lens != nullptr) {
-    // TMA-fed warp-specialised kernel (the cp.async kernel below serves other block sizes)
-    rc = attn_decode_tma_launch(p, num_blocks, s);
+    // TMA-fed warp-specialised kernel (the cp.async kernel below serves other block sizes); it merges its own splits
+    if (num_splits > 1) p.split_counters = reinterpret_cast<int*>(workspace);
+    return attn_decode_tma_launch(p, num_blocks, s);
   } else {
     dim3 grid(num_splits, Hkv, num_seqs);
     launch_rc = launch_kernel(attn_decode_kernel, dim3(grid), dim3(128), DECODE_SMEM, s, p);

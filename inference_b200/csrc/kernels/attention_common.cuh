@@ -33,6 +33,8 @@ struct AttnParams {
   int num_splits;
   float* part_o;
   float* part_ml;
+  int cluster_merge;     // the splits of a (sequence, kv head) are one thread-block cluster (num_splits <= 8)
+  int* split_counters;   // [num_seqs * Hkv] zero between launches: in-kernel merge by the last split to arrive (TMA kernel)
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {

@@ -6,7 +6,8 @@
 // 16-token slice of every tile: S = Q K^T and O += P V on mma.sync with ldmatrix from the swizzled ring,
 // online softmax in registers, then a cross-warp merge in shared memory. The <=16 MMA rows are the GQA
 // group's query heads times the (1..4) query tokens of the step. With num_splits > 1 the CTA writes an
-// un-normalised partial (O, max, sum) that attn_merge_kernel combines.
+// un-normalised partial (O, max, sum); the last split CTA of a (sequence, kv head) to finish merges them (ticket
+// counter in the workspace, reset by the merger), so split-KV decode is still one launch.
 // The decode step is bandwidth bound (KV bytes >> FLOPs), so the design goal is bytes in flight:
 // 2 CTAs/SM x 3 stages x 32 KB with no per-thread address arithmetic on the load path.
 #include "attention_common.cuh"
@@ -68,7 +69,7 @@ __global__ void __launch_bounds__(160, SWB_DEC_MIN_CTAS) attn_decode_tma_kernel(
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
   }
-  pdl_wait();  // everything below reads what the preceding kernels wrote (q, the newest K/V, kv_lens)
+  pdl_wait(TL_ATTN_DECODE);  // everything below reads what the preceding kernels wrote (q, the newest K/V, kv_lens)
 
   const int q_start = p.cu_q ? p.cu_q[seq] : seq * p.uniform_q_len;
   const int q_len = p.cu_q ? p.cu_q[seq + 1] - q_start : p.uniform_q_len;
@@ -283,6 +284,89 @@ __global__ void __launch_bounds__(160, SWB_DEC_MIN_CTAS) attn_decode_tma_kernel(
       }
     }
   }
+  if (p.num_splits > 1 && p.split_counters) {
+    // Merge of the splits inside this launch. Cluster launch (the splits of a (sequence, kv head) form one
+    // thread-block cluster): a cluster barrier orders the partials, the first CTA merges. Otherwise the last split
+    // to arrive (ticket counter in the workspace, reset by the merger) merges.
+    int* ctr = p.split_counters + (size_t)seq * p.Hkv + kvh;
+    if (p.cluster_merge) {
+      asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+      if (split != 0) return;
+    } else {
+      __shared__ int s_last;
+      __threadfence();                       // this CTA's partials are visible device-wide before its ticket
+      __syncthreads();
+      if (threadIdx.x == 0) s_last = (atomicAdd(ctr, 1) == p.num_splits - 1) ? 1 : 0;
+      __syncthreads();
+      if (!s_last) return;
+      __threadfence();
+    }
+    const int S = p.num_splits;            // <= 32
+    float* sSc = sMerge;                   // [16][32] weights of the splits, then normalised
+    float* sL = sMerge + 16 * 32;          // [16][32]
+    const size_t base0 = ((size_t)seq * p.Hkv + kvh) * S * 16;
+    __syncthreads();                       // (cluster path: the cross-warp merge area is free)
+    for (int i = threadIdx.x; i < nrows * S; i += blockDim.x) {
+      const int row = i / S, sp = i % S;
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + (base0 + (size_t)sp * 16 + row) * 2));
+      sSc[row * 32 + sp] = ml.x;
+      sL[row * 32 + sp] = ml.y;
+    }
+    // the partial outputs do not depend on the weights: request them now (up to 4 rows x 8 splits stay in registers)
+    float po[4][8];
+    const bool small = nrows <= 4 && S <= 8 && threadIdx.x < 128;
+    if (small) {
+#pragma unroll
+      for (int row = 0; row < 4; ++row)
+#pragma unroll
+        for (int sp = 0; sp < 8; ++sp)
+          po[row][sp] = (row < nrows && sp < S)
+                            ? __ldcg(p.part_o + (base0 + (size_t)sp * 16 + row) * HD + threadIdx.x) : 0.f;
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < nrows) {
+      const int row = threadIdx.x;
+      float M = -INFINITY;
+      for (int sp = 0; sp < S; ++sp) M = fmaxf(M, sSc[row * 32 + sp]);
+      const float Ms = (M == -INFINITY) ? 0.f : M;
+      float L = 0.f;
+      for (int sp = 0; sp < S; ++sp) {
+        const float sc = exp2f(sSc[row * 32 + sp] - Ms);
+        sSc[row * 32 + sp] = sc;
+        L += sc * sL[row * 32 + sp];
+      }
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      for (int sp = 0; sp < S; ++sp) sSc[row * 32 + sp] *= inv;
+    }
+    __syncthreads();
+    if (threadIdx.x < 128) {
+      const int d = threadIdx.x;
+      if (small) {
+#pragma unroll
+        for (int row = 0; row < 4; ++row) {
+          if (row < nrows) {
+            float acc = 0.f;
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp)
+              if (sp < S) acc += sSc[row * 32 + sp] * po[row][sp];
+            const int qtok = row / p.G, hg = row % p.G;
+            p.out[(size_t)(q_start + qtok) * p.out_stride_tok + (size_t)(kvh * p.G + hg) * HD + d] = __float2bfloat16(acc);
+          }
+        }
+      } else {
+        for (int row = 0; row < nrows; ++row) {
+          float acc = 0.f;
+#pragma unroll 8
+          for (int sp = 0; sp < S; ++sp)
+            acc += sSc[row * 32 + sp] * __ldcg(p.part_o + (base0 + (size_t)sp * 16 + row) * HD + d);
+          const int qtok = row / p.G, hg = row % p.G;
+          p.out[(size_t)(q_start + qtok) * p.out_stride_tok + (size_t)(kvh * p.G + hg) * HD + d] = __float2bfloat16(acc);
+        }
+      }
+    }
+    if (!p.cluster_merge && threadIdx.x == 0) *ctr = 0;        // ready for the next launch
+  }
 }
 
 }  // namespace
@@ -305,6 +389,31 @@ int attn_decode_tma_launch(const AttnParams& p, int num_blocks, cudaStream_t str
   rc = make_tmap_bf16_2d(&tv, p.v, rows, HD, HD, 16);
   if (rc) return rc;
   dim3 grid(p.num_splits, p.Hkv, p.num_seqs);
+  if (p.num_splits > 1 && p.num_splits <= 8 && p.split_counters) {
+    // the splits of one (sequence, kv head) as a thread-block cluster: merged after a cluster barrier
+    AttnParams pc = p;
+    pc.cluster_merge = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(160);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = p.num_splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    int na = 1;
+    if (pdl_enabled()) {
+      attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[na].val.programmaticStreamSerializationAllowed = 1;
+      ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attn_decode_tma_kernel, tk, tv, pc);
+    return e == cudaSuccess ? 0 : -(int)e;
+  }
   return launch_kernel(attn_decode_tma_kernel, grid, dim3(160), SMEM_BYTES, stream, tk, tv, p);
 }
 

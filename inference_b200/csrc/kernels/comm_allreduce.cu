@@ -100,7 +100,7 @@ __device__ __forceinline__ bool peer_barrier(const ArParams& p, uint32_t epoch, 
 template <int THREADS, int VPT>
 __global__ void __launch_bounds__(THREADS) allreduce_rmsnorm_kernel(const ArParams p) {
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait(TL_PEER);
   __shared__ float red[32];
   __shared__ int s_ok;
   const uint32_t epoch = p.epochs[blockIdx.x] + 1u;
@@ -272,7 +272,7 @@ struct PairParams {
 // One CTA: flag barrier (flag row 0, like peer_barrier_kernel), then thread = row pulls `world` candidates.
 __global__ void __launch_bounds__(128) argmax_peer_merge_kernel(const ArParams p, const PairParams q) {
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait(TL_PEER);
   __shared__ int s_ok;
   const uint32_t epoch = p.epochs[0] + 1u;
   const bool ok = peer_barrier(p, epoch, &s_ok);

@@ -29,12 +29,17 @@ enum StatusCode : int {
 // registers its copy with the host-side registry so swb_status_read() can aggregate them.
 static __device__ int g_status[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 static __device__ unsigned long long g_wait_limit_ns = 2000000000ULL;
+// Optional launch timeline (profiling aid, null = off): [0] = records written, [1] = capacity, records of four
+// words from word 8 on: {kernel id, globaltimer before the dependency wait, after it, gridDim.x}. Written by thread 0
+// of block 0 inside pdl_wait(), so the "after" stamp of launch k + 1 is the moment launch k had completely finished.
+static __device__ unsigned long long* g_timeline = nullptr;
 
 struct StatusUnit {
   const char* name;
   int (*read)(int* out8);
   int (*clear)();
   int (*set_limit)(unsigned long long ns);
+  int (*set_timeline)(unsigned long long* buf);
 };
 void register_status_unit(const StatusUnit& u);
 
@@ -48,9 +53,12 @@ static int tu_status_clear() {
 static int tu_status_set_limit(unsigned long long ns) {
   return (int)cudaMemcpyToSymbol(g_wait_limit_ns, &ns, sizeof(ns));
 }
+static int tu_set_timeline(unsigned long long* buf) {
+  return (int)cudaMemcpyToSymbol(g_timeline, &buf, sizeof(buf));
+}
 struct StatusRegistrar {
   explicit StatusRegistrar(const char* name) {
-    register_status_unit(StatusUnit{name, tu_status_read, tu_status_clear, tu_status_set_limit});
+    register_status_unit(StatusUnit{name, tu_status_read, tu_status_clear, tu_status_set_limit, tu_set_timeline});
   }
 };
 #define SWB_REGISTER_STATUS_UNIT(name) static ::swb::StatusRegistrar swb_status_registrar_##name(#name)
@@ -64,12 +72,6 @@ __device__ __forceinline__ void report_error(int code, int a, int b, int c) {
   }
 }
 
-__device__ __forceinline__ uint64_t global_timer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
@@ -80,7 +82,36 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 // produces (or anything the predecessor still reads and this kernel overwrites). pdl_launch_dependents()
 // lets the successor begin launching. Both are no-ops for a normally launched kernel.
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// kernel ids of the launch timeline
+enum TimelineId : int {
+  TL_OTHER = 0, TL_EMBED = 1, TL_RMSNORM = 2, TL_GEMM_DECODE = 3, TL_ROPE_KV = 4, TL_ATTN_DECODE = 5, TL_ATTN_MERGE = 6,
+  TL_GEMM = 7, TL_ARGMAX = 8, TL_ARGMAX_MERGE = 9, TL_META = 10, TL_TAIL = 11, TL_PEER = 12, TL_GATED_ACT = 13,
+  TL_ATTN_PREFILL = 14, TL_GEMM_QUANT = 15,
+};
+
+__device__ __forceinline__ void pdl_wait(int timeline_id = TL_OTHER) {
+  unsigned long long* tl = g_timeline;
+  if (tl != nullptr && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+    const unsigned long long slot = atomicAdd(tl, 1ull);
+    const unsigned long long t0 = global_timer_ns();
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (slot < tl[1]) {
+      unsigned long long* rec = tl + 8 + slot * 4;
+      rec[0] = (unsigned long long)timeline_id;
+      rec[1] = t0;
+      rec[2] = global_timer_ns();
+      rec[3] = gridDim.x;
+    }
+    return;
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 bool pdl_enabled();  // host: process-wide switch (env SWB_PDL=0 disables), defined in status.cu
@@ -278,7 +309,7 @@ __device__ __forceinline__ float gelu_tanh_f(float x) {
   float u = k0 * (x + k1 * x * x * x);
   return 0.5f * x * (1.f + tanhf(u));
 }
-__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.f + __expf(-x)); }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

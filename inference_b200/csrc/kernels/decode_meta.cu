@@ -5,6 +5,8 @@
 #include "common.cuh"
 
 namespace swb {
+
+SWB_REGISTER_STATUS_UNIT(decode_meta);
 namespace {
 
 // meta rows: [ids MB][positions MB][slots MB][kv lens MB][block table MB * mb], int32.
@@ -13,7 +15,7 @@ __global__ void __launch_bounds__(256) decode_meta_unpack_kernel(const int* __re
                                                                  int mb, long long* ids, int* pos, long long* slots,
                                                                  int* kvl, int* table) {
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait(TL_META);
   const int step = step_ptr ? *step_ptr : 0;
   const int* m = meta_all + (size_t)step * n_meta;
   const int n_table = B * mb;
@@ -34,7 +36,7 @@ __global__ void __launch_bounds__(256) decode_meta_unpack_kernel(const int* __re
 __global__ void __launch_bounds__(128) decode_step_tail_kernel(const long long* __restrict__ tokens, long long* ids,
                                                                long long* out_all, int* step_ptr, int B) {
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait(TL_TAIL);
   const int step = *step_ptr;
   for (int r = threadIdx.x; r < B; r += blockDim.x) {
     const long long t = tokens[r];

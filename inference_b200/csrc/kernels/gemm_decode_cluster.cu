@@ -14,6 +14,7 @@
 #include "gemm_tcgen05.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 
 namespace swb {
 
@@ -23,17 +24,26 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int THREADS = 192;
+constexpr int EPI_WARPS = 8;                 // two warps per TMEM lane quarter: each takes half of the token columns
+constexpr int EPI_THREADS = EPI_WARPS * 32;
+constexpr int THREADS = 64 + EPI_THREADS;
 
-template <int BLOCK_N>
+// STAGES_ = 4: two CTAs per SM (large weights: bytes in flight across the whole GPU); STAGES_ = 8: one CTA per SM with
+// a ring deep enough to hold most or all of a small projection's k-range, requested before the dependency on the
+// previous kernel resolves (decode steps are a chain of small dependent kernels: whatever is already in shared memory
+// when the activations arrive is off the critical path). The receive buffer of the cluster reduction aliases the ring:
+// partial tiles are exchanged only after every member's last MMA has read its ring.
+template <int BLOCK_N, int STAGES_>
 struct DecCfg {
-  static constexpr int STAGES = BLOCK_N >= 64 ? 3 : 4;
+  static constexpr int STAGES = STAGES_;
   static constexpr uint32_t A_BYTES = BM * BK * 2;
   static constexpr uint32_t B_BYTES = BLOCK_N * BK * 2;
   static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr uint32_t RECV_BYTES = (BM + 16) * BLOCK_N * 4;  // CLUSTER slots of [BLOCK_N][rows per member] fp32
+  static constexpr uint32_t RING_BYTES = STAGES * STAGE_BYTES;
+  static constexpr uint32_t DATA_BYTES = RING_BYTES > RECV_BYTES ? RING_BYTES : RECV_BYTES;
   static constexpr uint32_t TMEM_COLS = BLOCK_N < 32 ? 32 : BLOCK_N;
-  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + RECV_BYTES + 1024 + 256;
+  static constexpr size_t SMEM_BYTES = (size_t)DATA_BYTES + 1024 + 256;
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -60,8 +70,8 @@ __device__ __forceinline__ void st_cluster_f32x2(uint32_t addr, float a, float b
   asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(a), "f"(b) : "memory");
 }
 
-// barrier of the four epilogue warps (threads 64..191) only
-__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// barrier of the epilogue warps (threads 64 ..) only
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory"); }
 
 // Flag-in-data lines for the cross-rank sum: 16 bytes = {data, epoch, data, epoch}. Each 8-byte half is written
 // atomically, so a reader that sees both epochs has both data words; no fence or separate flag is needed and a row
@@ -110,11 +120,11 @@ __device__ __forceinline__ float act_apply(float x, int act) {
   return x;
 }
 
-template <int BLOCK_N, int CLUSTER>
-__global__ void __launch_bounds__(THREADS, 2)
+template <int BLOCK_N, int CLUSTER, int STAGES_>
+__global__ void __launch_bounds__(THREADS, STAGES_ > 4 ? 1 : 2)
 gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                            const GemmParams p) {
-  using Cfg = DecCfg<BLOCK_N>;
+  using Cfg = DecCfg<BLOCK_N, STAGES_>;
   constexpr int STAGES = Cfg::STAGES;
   // output-feature rows owned by each cluster member, rounded up to 8 so the final store is 16-byte vectors
   constexpr int R = (((BM + CLUSTER - 1) / CLUSTER) + 7) / 8 * 8;
@@ -123,8 +133,8 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
-  float* recv = reinterpret_cast<float*>(smem + STAGES * Cfg::STAGE_BYTES);
-  uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES + Cfg::RECV_BYTES);
+  float* recv = reinterpret_cast<float*>(smem);      // aliases the ring (free once every member's MMAs are done)
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + Cfg::DATA_BYTES);
   uint64_t* bar_empty = bar_full + STAGES;
   uint64_t* bar_tfull = bar_empty + STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tfull + 1);
@@ -133,7 +143,7 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  unsigned long long* tr = p.trace ? p.trace + (size_t)blockIdx.x * 8 : nullptr;
+  unsigned long long* tr = p.trace ? p.trace + (size_t)blockIdx.x * 16 : nullptr;   // [0..7] globaltimer, [8..15] SM clock
   if (tr && threadIdx.x == 0) tr[0] = global_timer_ns();
   const uint32_t crank = CLUSTER > 1 ? cluster_ctarank() : 0u;
   const int tile_m = (int)blockIdx.x / CLUSTER;
@@ -163,7 +173,6 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   const uint32_t tmem_base = *tmem_slot;
   pdl_launch_dependents();
   if (tr && threadIdx.x == 0) tr[1] = global_timer_ns();   // setup done
-  if (CLUSTER > 1) cluster_arrive();  // phase 1: "my shared memory is live" (waited on before remote stores)
 
   if (warp == 0) {
     if (lane == 0) {
@@ -174,7 +183,7 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
         mbar_arrive_expect_tx(&bar_full[i], Cfg::STAGE_BYTES);
         tma_load_2d_hint(smem + i * Cfg::STAGE_BYTES, &tmap_w, &bar_full[i], (kb0 + i) * BK, tile_m * BM, pol_w);
       }
-      pdl_wait();
+      pdl_wait(TL_GEMM_DECODE);
       if (tr) tr[2] = global_timer_ns();                   // dependency satisfied
       int stage = 0;
       uint32_t phase = 0;
@@ -229,9 +238,15 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
     }
   }
 
-  // ---- all threads: make sure every member's shared memory is live before any remote store ----
-  __syncwarp();
-  if (CLUSTER > 1) cluster_wait();
+  // ---- phase 1 of the cluster exchange: a member arrives once its accumulator is complete (its ring is then free to
+  // receive partial tiles); nobody stores remotely before every member has arrived ----
+  if (warp < 2) {
+    __syncwarp();
+    if (CLUSTER > 1) {
+      cluster_arrive();
+      cluster_wait();
+    }
+  }
 
   if (warp >= 2) {
     pdl_wait();
@@ -248,8 +263,12 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
     const int row = quarter * 32 + lane;
     bool have = nkb > 0;
     if (have) have = mbar_wait(bar_tfull, 0, s_abort, 900);
-    have = __all_sync(0xffffffffu, have);
-    if (tr && threadIdx.x == 64) tr[3] = global_timer_ns();  // accumulator complete  // warp-uniform: tcgen05.ld is warp-collective
+    have = __all_sync(0xffffffffu, have);   // warp-uniform: tcgen05.ld is warp-collective
+    if (tr && threadIdx.x == 64) { tr[3] = global_timer_ns(); tr[12] = clock64(); }  // accumulator complete
+    if (CLUSTER > 1) {
+      cluster_arrive();
+      cluster_wait();
+    }
     tc_fence_after_sync();
     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const uint32_t recv_local = smem_u32(recv);
@@ -259,8 +278,12 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
     // store 128 contiguous bytes per token, and the owner later reads 8 consecutive rows as two float4
     const uint32_t col_base = recv_local + (uint32_t)((crank * BLOCK_N * R + lr) * 4);
     const uint32_t remote = CLUSTER > 1 ? map_to_cta(col_base, owner) : col_base;
+    constexpr int NCH = BLOCK_N / 16;
+    const int half = (warp - 2) >> 2;                       // which half of the token chunks this warp moves
+    const int ch0 = half == 0 ? 0 : (NCH + 1) / 2;
+    const int ch1 = half == 0 ? (NCH + 1) / 2 : NCH;
 #pragma unroll 1
-    for (int ch = 0; ch < BLOCK_N / 16; ++ch) {
+    for (int ch = ch0; ch < ch1; ++ch) {
       float v[16];
       if (have) {
         tmem_ld_32x32b_x16(taddr + ch * 16, v);
@@ -276,19 +299,38 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
       }
     }
     tc_fence_before_sync();
-    if (tr && threadIdx.x == 64) tr[4] = global_timer_ns();  // partials delivered
+    if (tr && threadIdx.x == 64) { tr[4] = global_timer_ns(); tr[13] = clock64(); }  // partials delivered
   }
 
   // ---- phase 2: every partial slice has been delivered ----
+  // Each epilogue thread finishes ITEMS 16-byte groups (8 features of one token). Their residual values do not
+  // depend on the cluster, so they are requested between the barrier's arrive and wait.
+  constexpr int R8 = R / 8;
+  constexpr int ITEMS = (R8 * BLOCK_N + EPI_THREADS - 1) / EPI_THREADS;
+  constexpr bool PREFETCH_RES = ITEMS <= 4;     // (more items would not stay in registers)
+  uint4 resv[PREFETCH_RES ? ITEMS : 1];
   __syncwarp();
+  if (CLUSTER > 1) cluster_arrive();
+  if (PREFETCH_RES && warp >= 2 && p.residual && p.vec_ok && (p.ld_res & 7) == 0) {
+    const int et = (warp - 2) * 32 + lane;
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+      const int idx = et + it * EPI_THREADS;
+      const int f8 = idx % R8, tok = idx / R8;
+      const int row = (int)crank * R + f8 * 8;
+      const int feat = tile_m * BM + row;
+      resv[PREFETCH_RES ? it : 0] = make_uint4(0u, 0u, 0u, 0u);
+      if (idx < R8 * BLOCK_N && row < BM && feat + 8 <= p.M && tok < p.N)
+        resv[PREFETCH_RES ? it : 0] = *reinterpret_cast<const uint4*>(p.residual + (size_t)tok * p.ld_res + feat);
+    }
+  }
   if (CLUSTER > 1) {
-    cluster_arrive();
     cluster_wait();
   } else {
     __syncthreads();
   }
 
-  if (tr && threadIdx.x == 64) tr[5] = global_timer_ns();    // cluster barrier passed
+  if (tr && threadIdx.x == 64) { tr[5] = global_timer_ns(); tr[8] = clock64(); }    // cluster barrier passed
   if (warp >= 2 && p.ssq_zero && blockIdx.x == 0) {
     // the chain's other accumulator: its consumer finished before this kernel's dependency resolved, its producer
     // starts after this kernel ends
@@ -297,9 +339,7 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   }
   if (warp >= 2 && p.peer.mode) {
     // ---- cross-rank sum over peer memory, flag-in-data lines: no barrier, no fence, one NVLink hop per shot ----
-    const int et = (warp - 2) * 32 + lane;  // 0..127
-    constexpr int R8 = R / 8;
-    constexpr int ITEMS = (R8 * BLOCK_N + 127) / 128;
+    const int et = (warp - 2) * 32 + lane;  // 0 .. EPI_THREADS - 1
     const GemmPeerReduce& q = p.peer;
     const int pmode = q.mode;
     const int owner_rank = pmode == 2 ? tile_m % q.world : q.rank;   // two-shot: who finishes this weight tile's rows
@@ -312,7 +352,7 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
     // pass 1: deliver this CTA's partial rows (cluster-reduced, rounded to bf16) to the rank(s) that sum them
 #pragma unroll
     for (int it = 0; it < ITEMS; ++it) {
-      const int idx = et + it * 128;
+      const int idx = et + it * EPI_THREADS;
       const int f8 = idx % R8, tok = idx / R8;
       const int row = (int)crank * R + f8 * 8;
       const int feat = tile_m * BM + row;
@@ -354,7 +394,7 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
     bool failed = false;
 #pragma unroll
     for (int it = 0; it < ITEMS; ++it) {
-      const int idx = et + it * 128;
+      const int idx = et + it * EPI_THREADS;
       const int f8 = idx % R8, tok = idx / R8;
       const int row = (int)crank * R + f8 * 8;
       const int feat = tile_m * BM + row;
@@ -385,8 +425,9 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
             }
           }
           if (p.residual) {
-            const uint4 r = *reinterpret_cast<const uint4*>(p.residual + (size_t)tok * p.ld_res + feat);
-            const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&r);
+            const uint4 rr = PREFETCH_RES ? resv[PREFETCH_RES ? it : 0]
+                                          : *reinterpret_cast<const uint4*>(p.residual + (size_t)tok * p.ld_res + feat);
+            const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&rr);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const float2 t = __bfloat1622float2(rh[j]);
@@ -431,113 +472,119 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
     epi_bar_sync();     // every thread has read its epoch
     if (et == 0) q.epochs[blockIdx.x] = counter;
   } else if (warp >= 2) {
-    const int et = (warp - 2) * 32 + lane;  // 0..127
-    constexpr int R8 = R / 8;
-    for (int idx = et; idx < R8 * BLOCK_N; idx += 128) {
+    const int et = (warp - 2) * 32 + lane;  // 0 .. EPI_THREADS - 1
+    const bool res_vec = PREFETCH_RES && p.residual && p.vec_ok && (p.ld_res & 7) == 0;
+#pragma unroll(ITEMS < 4 ? ITEMS : 4)
+    for (int it = 0; it < ITEMS; ++it) {
+      const int idx = et + it * EPI_THREADS;
       const int f8 = idx % R8;         // consecutive threads -> consecutive 16-byte feature groups of one token
       const int tok = idx / R8;
       const int row = (int)crank * R + f8 * 8;
       const int feat = tile_m * BM + row;
-      // (the body is a one-trip loop so that every lane reaches the convergent shuffle below it)
       float ss = 0.f;
-      if (!(row >= BM || feat >= p.M || tok >= p.N)) do {
-      float acc[8];
+      const bool valid = idx < R8 * BLOCK_N && row < BM && feat < p.M && tok < p.N;
+      if (valid) {
+        float acc[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
 #pragma unroll
-      for (int src = 0; src < CLUSTER; ++src) {
-        const float4* rp = reinterpret_cast<const float4*>(recv + ((size_t)src * BLOCK_N + tok) * R + f8 * 8);
-        const float4 a0 = rp[0], a1 = rp[1];
-        acc[0] += a0.x; acc[1] += a0.y; acc[2] += a0.z; acc[3] += a0.w;
-        acc[4] += a1.x; acc[5] += a1.y; acc[6] += a1.z; acc[7] += a1.w;
-      }
-      if (p.ssq_in) {
-        const float rs = s_rstd[tok];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] *= rs;
-      }
-      const int nvalid = min(8, p.M - feat);
-      const size_t off = (size_t)tok * p.ldd + feat;
-      const bool vec = p.vec_ok && nvalid == 8 && ((p.ldd & 7) == 0) && ((feat & 7) == 0) && (!p.residual || (p.ld_res & 7) == 0);   // gated pairs: ldd % 8 == 0 keeps the 8-byte stores aligned
-      if (vec) {
-        if (p.bias) {
-          const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + feat));
-          const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&b);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 t = __bfloat1622float2(bh[j]);
-            acc[2 * j] += t.x;
-            acc[2 * j + 1] += t.y;
-          }
+        for (int src = 0; src < CLUSTER; ++src) {
+          const float4* rp = reinterpret_cast<const float4*>(recv + ((size_t)src * BLOCK_N + tok) * R + f8 * 8);
+          const float4 a0 = rp[0], a1 = rp[1];
+          acc[0] += a0.x; acc[1] += a0.y; acc[2] += a0.z; acc[3] += a0.w;
+          acc[4] += a1.x; acc[5] += a1.y; acc[6] += a1.z; acc[7] += a1.w;
         }
-        if (p.act >= SWB_ACT_SWIGLU_PAIRS) {
-          // rows come in (gate, up) pairs: four gated outputs, one 8-byte store
-          const int a1 = p.act == SWB_ACT_SWIGLU_PAIRS ? SWB_ACT_SILU : SWB_ACT_GELU_TANH;
-          uint2 o;
-          __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
-          oh[0] = __floats2bfloat162_rn(act_apply(acc[0], a1) * acc[1], act_apply(acc[2], a1) * acc[3]);
-          oh[1] = __floats2bfloat162_rn(act_apply(acc[4], a1) * acc[5], act_apply(acc[6], a1) * acc[7]);
-          *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(p.out) + (size_t)tok * p.ldd + (feat >> 1)) = o;
-          break;
-        }
-        if (p.act != SWB_ACT_NONE) {
+        if (p.ssq_in) {
+          const float rs = s_rstd[tok];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) acc[j] = act_apply(acc[j], p.act);
+          for (int j = 0; j < 8; ++j) acc[j] *= rs;
         }
-        if (p.residual) {
-          const uint4 r = *reinterpret_cast<const uint4*>(p.residual + (size_t)tok * p.ld_res + feat);
-          const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&r);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 t = __bfloat1622float2(rh[j]);
-            acc[2 * j] += t.x;
-            acc[2 * j + 1] += t.y;
-          }
-        }
-        if (p.out_fp32) {
-          float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + off);
-          op[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-          op[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
-        } else {
-          uint4 o;
-          __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-          *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + off) = o;
-          if (p.ssq_out) {   // sum of squares of exactly what was stored (bf16-rounded)
+        if (tr && threadIdx.x == 64 && it == 0) tr[9] = clock64();    // first item summed
+        const int nvalid = min(8, p.M - feat);
+        const size_t off = (size_t)tok * p.ldd + feat;
+        const bool vec = p.vec_ok && nvalid == 8 && ((p.ldd & 7) == 0) && ((feat & 7) == 0) && (!p.residual || (p.ld_res & 7) == 0);   // gated pairs: ldd % 8 == 0 keeps the 8-byte stores aligned
+        if (vec) {
+          if (p.bias) {
+            const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + feat));
+            const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&b);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              const float2 t = __bfloat1622float2(oh[j]);
-              ss += t.x * t.x + t.y * t.y;
+              const float2 t = __bfloat1622float2(bh[j]);
+              acc[2 * j] += t.x;
+              acc[2 * j + 1] += t.y;
             }
           }
-        }
-      } else if (p.act >= SWB_ACT_SWIGLU_PAIRS) {
-        const int a1 = p.act == SWB_ACT_SWIGLU_PAIRS ? SWB_ACT_SILU : SWB_ACT_GELU_TANH;
-        for (int j = 0; j + 1 < nvalid; j += 2) {
-          const float gte = acc[j] + (p.bias ? __bfloat162float(p.bias[feat + j]) : 0.f);
-          const float up = acc[j + 1] + (p.bias ? __bfloat162float(p.bias[feat + j + 1]) : 0.f);
-          reinterpret_cast<bf16*>(p.out)[(size_t)tok * p.ldd + ((feat + j) >> 1)] = __float2bfloat16(act_apply(gte, a1) * up);
-        }
-      } else {
-        for (int j = 0; j < nvalid; ++j) {
-          float x = act_apply(acc[j] + (p.bias ? __bfloat162float(p.bias[feat + j]) : 0.f), p.act);
-          if (p.residual) x += __bfloat162float(p.residual[(size_t)tok * p.ld_res + feat + j]);
-          if (p.out_fp32)
-            reinterpret_cast<float*>(p.out)[off + j] = x;
-          else
-            reinterpret_cast<bf16*>(p.out)[off + j] = __float2bfloat16(x);
+          if (p.act >= SWB_ACT_SWIGLU_PAIRS) {
+            // rows come in (gate, up) pairs: four gated outputs, one 8-byte store
+            const int a1 = p.act == SWB_ACT_SWIGLU_PAIRS ? SWB_ACT_SILU : SWB_ACT_GELU_TANH;
+            uint2 o;
+            __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+            oh[0] = __floats2bfloat162_rn(act_apply(acc[0], a1) * acc[1], act_apply(acc[2], a1) * acc[3]);
+            oh[1] = __floats2bfloat162_rn(act_apply(acc[4], a1) * acc[5], act_apply(acc[6], a1) * acc[7]);
+            *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(p.out) + (size_t)tok * p.ldd + (feat >> 1)) = o;
+          } else {
+            if (p.act != SWB_ACT_NONE) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc[j] = act_apply(acc[j], p.act);
+            }
+            if (p.residual) {
+              const uint4 r = res_vec ? resv[PREFETCH_RES ? it : 0]
+                                      : *reinterpret_cast<const uint4*>(p.residual + (size_t)tok * p.ld_res + feat);
+              const __nv_bfloat162* rh = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 t = __bfloat1622float2(rh[j]);
+                acc[2 * j] += t.x;
+                acc[2 * j + 1] += t.y;
+              }
+            }
+            if (p.out_fp32) {
+              float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + off);
+              op[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+              op[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+            } else {
+              uint4 o;
+              __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+              *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + off) = o;
+              if (p.ssq_out) {   // sum of squares of exactly what was stored (bf16-rounded)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 t = __bfloat1622float2(oh[j]);
+                  ss += t.x * t.x + t.y * t.y;
+                }
+              }
+            }
+          }
+        } else if (p.act >= SWB_ACT_SWIGLU_PAIRS) {
+          const int a1 = p.act == SWB_ACT_SWIGLU_PAIRS ? SWB_ACT_SILU : SWB_ACT_GELU_TANH;
+          for (int j = 0; j + 1 < nvalid; j += 2) {
+            const float gte = acc[j] + (p.bias ? __bfloat162float(p.bias[feat + j]) : 0.f);
+            const float up = acc[j + 1] + (p.bias ? __bfloat162float(p.bias[feat + j + 1]) : 0.f);
+            reinterpret_cast<bf16*>(p.out)[(size_t)tok * p.ldd + ((feat + j) >> 1)] = __float2bfloat16(act_apply(gte, a1) * up);
+          }
+        } else {
+          for (int j = 0; j < nvalid; ++j) {
+            float x = act_apply(acc[j] + (p.bias ? __bfloat162float(p.bias[feat + j]) : 0.f), p.act);
+            if (p.residual) x += __bfloat162float(p.residual[(size_t)tok * p.ld_res + feat + j]);
+            if (p.out_fp32)
+              reinterpret_cast<float*>(p.out)[off + j] = x;
+            else
+              reinterpret_cast<bf16*>(p.out)[off + j] = __float2bfloat16(x);
+          }
         }
       }
-      } while (0);
-      if (p.ssq_out) {       // every lane of the warp arrives here: reduce over the R8 threads that share a token
+      if (tr && threadIdx.x == 64 && it == 0) tr[10] = clock64();     // first item stored
+      if (p.ssq_out && idx < R8 * BLOCK_N) {   // warp-uniform (R8 * BLOCK_N is a multiple of 32)
         for (int o2 = 1; o2 < R8; o2 <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o2);
-        if (f8 == 0 && tok < p.N && row < BM) atomicAdd(p.ssq_out + tok, ssq_fixed(ss));
+        if (f8 == 0 && valid) atomicAdd(p.ssq_out + tok, ssq_fixed(ss));
       }
+      if (tr && threadIdx.x == 64 && it == 0) tr[14] = clock64();     // first item's sum of squares sent
     }
   }
 
-  if (tr && threadIdx.x == 64) tr[6] = global_timer_ns();    // outputs stored
+  if (tr && threadIdx.x == 64) { tr[6] = global_timer_ns(); tr[11] = clock64(); }    // outputs stored
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) {
@@ -547,10 +594,10 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   if (tr && threadIdx.x == 0) tr[7] = global_timer_ns();
 }
 
-template <int BLOCK_N, int CLUSTER>
+template <int BLOCK_N, int CLUSTER, int STAGES_>
 int launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
-  using Cfg = DecCfg<BLOCK_N>;
-  auto kern = gemm_decode_cluster_kernel<BLOCK_N, CLUSTER>;
+  using Cfg = DecCfg<BLOCK_N, STAGES_>;
+  auto kern = gemm_decode_cluster_kernel<BLOCK_N, CLUSTER, STAGES_>;
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -584,17 +631,22 @@ int launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p
   return e == cudaSuccess ? 0 : -(int)e;
 }
 
-template <int BLOCK_N>
+template <int BLOCK_N, int STAGES_>
 int launch_cluster(int cluster, const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t s) {
   switch (cluster) {
-    case 1: return launch_one<BLOCK_N, 1>(tw, tx, p, s);
-    case 2: return launch_one<BLOCK_N, 2>(tw, tx, p, s);
-    case 3: return launch_one<BLOCK_N, 3>(tw, tx, p, s);
-    case 4: return launch_one<BLOCK_N, 4>(tw, tx, p, s);
-    case 6: return launch_one<BLOCK_N, 6>(tw, tx, p, s);
-    case 8: return launch_one<BLOCK_N, 8>(tw, tx, p, s);
+    case 1: return launch_one<BLOCK_N, 1, STAGES_>(tw, tx, p, s);
+    case 2: return launch_one<BLOCK_N, 2, STAGES_>(tw, tx, p, s);
+    case 3: return launch_one<BLOCK_N, 3, STAGES_>(tw, tx, p, s);
+    case 4: return launch_one<BLOCK_N, 4, STAGES_>(tw, tx, p, s);
+    case 6: return launch_one<BLOCK_N, 6, STAGES_>(tw, tx, p, s);
+    case 8: return launch_one<BLOCK_N, 8, STAGES_>(tw, tx, p, s);
   }
   return -2;
+}
+template <int BLOCK_N>
+int launch_stages(bool deep, int cluster, const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p,
+                  cudaStream_t s) {
+  return deep ? launch_cluster<BLOCK_N, 8>(cluster, tw, tx, p, s) : launch_cluster<BLOCK_N, 4>(cluster, tw, tx, p, s);
 }
 
 }  // namespace
@@ -633,12 +685,33 @@ int gemm_decode_cluster_launch(const GemmArgs& a, int force_cluster, cudaStream_
   // Two CTAs can be resident per SM. Measured on B200 over Llama-3-8B projections: the fastest member count is
   // the largest one that keeps the grid under ~1.75 CTAs per SM with at least 6 k-blocks per member.
   int cluster = 1;
+  // Small projections (default: up to 24 MB of weights): as many members per cluster as keep the grid within one CTA
+  // per SM; up to 16 MB with the 8-stage ring. Larger ones: two CTAs per SM, grid under ~1.75 CTAs per SM, 4 stages.
+  // Measured on Llama-3-8B decode steps (batch 64): the 8-stage ring fills the SM, so the next kernel's CTAs cannot
+  // become resident and request their own weights before this kernel ends; that costs more than the deeper ring
+  // gains once a projection streams tens of megabytes (unsharded step 5.06 ms with 4 stages, 5.40 ms with 8 stages
+  // on the 50 MB qkv projection), and gains about 5 % on the shard shapes of 8-way tensor parallelism.
+  static const long deep_mb = [] {
+    const char* e = getenv("SWB_DEC_DEEP_MB");
+    return e ? atol(e) : 24L;
+  }();
+  static const long stages8_mb = [] {
+    const char* e = getenv("SWB_DEC_STAGES8_MB");
+    return e ? atol(e) : 16L;
+  }();
+  const long wbytes = (long)a.N * a.K * 2;
+  const bool one_per_sm = wbytes <= deep_mb * (1L << 20) && p.tiles_m <= sms;
+  bool deep = one_per_sm && wbytes <= stages8_mb * (1L << 20);
   for (int c : {2, 3, 4, 6, 8}) {
-    if ((long)p.tiles_m * c * 4 > 7L * sms) break;
+    if (one_per_sm ? (long)p.tiles_m * c > sms : (long)p.tiles_m * c * 4 > 7L * sms) break;
+    if (p.kblocks_total / c < 4 && c > 2) break;
     if (p.kblocks_total / c < 2) break;
     cluster = c;
   }
-  if (force_cluster > 0) cluster = std::min(8, force_cluster);
+  if (force_cluster > 0) {
+    cluster = std::min(8, force_cluster);
+    deep = deep && (long)p.tiles_m * cluster <= sms;
+  }
   if (cluster == 5) cluster = 4;
   if (cluster == 7) cluster = 6;
   if (p.peer.mode) {
@@ -655,22 +728,22 @@ int gemm_decode_cluster_launch(const GemmArgs& a, int force_cluster, cudaStream_
     if (cluster == 6) cluster = 4;
     if (p.tiles_m * cluster > SWB_PEER_MAX_CTAS) return -3;
   }
-  if (a.ssq_out || a.ssq_in) {
+  if (a.ssq_out) {
     // the per-token reduction in the producer's epilogue pairs lanes by xor: rows per member / 8 must be a power of two
     if (cluster == 3) cluster = 2;
     if (cluster == 6) cluster = 4;
-    if (a.ssq_out && (a.N % BM != 0 || a.out_fp32)) return -3;
-    if (!p.vec_ok || (a.ldd & 7) != 0) return -3;
+    if (a.N % BM != 0 || a.out_fp32) return -3;
   }
+  if ((a.ssq_out || a.ssq_in) && (!p.vec_ok || (a.ldd & 7) != 0)) return -3;
   CUtensorMap tw, tx;
   int r = make_tmap_bf16_2d(&tw, a.W, a.N, a.K, a.ldw, BM);
   if (r) return r;
   r = make_tmap_bf16_2d(&tx, a.A, a.T, a.K, a.lda, block_n);
   if (r) return r;
   switch (block_n) {
-    case 16: return launch_cluster<16>(cluster, tw, tx, p, stream);
-    case 32: return launch_cluster<32>(cluster, tw, tx, p, stream);
-    default: return launch_cluster<64>(cluster, tw, tx, p, stream);
+    case 16: return launch_stages<16>(deep, cluster, tw, tx, p, stream);
+    case 32: return launch_stages<32>(deep, cluster, tw, tx, p, stream);
+    default: return launch_stages<64>(deep, cluster, tw, tx, p, stream);
   }
 }
 

@@ -353,7 +353,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           }
         }
       }
-      pdl_wait();
+      pdl_wait(TL_GEMM);
       int issued = 0;
       SegIter iter(p);
       while (ok && iter.next(c)) {
@@ -406,7 +406,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       bool ok = true;
       SegIter iter(p);
       Seg c;
-      pdl_wait();
+      pdl_wait(TL_GEMM);
       while (ok && iter.next(c)) {
         const int kb0 = c.kb0, kb1 = c.kb1;
         ok = mbar_wait(&bar_tempty[acc], acc_phase ^ 1, s_abort, 200 + acc);

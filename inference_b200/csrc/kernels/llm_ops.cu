@@ -7,6 +7,8 @@
 #include "common.cuh"
 
 namespace swb {
+
+SWB_REGISTER_STATUS_UNIT(llm_ops);
 namespace {
 
 __device__ __forceinline__ void unpack8(const uint4& u, float* f) {
@@ -46,7 +48,7 @@ __global__ void __launch_bounds__(THREADS) rmsnorm_kernel(const bf16* __restrict
                                                          int H, float eps, float w_offset, const uint8_t* pf_ptr,
                                                          long long pf_bytes) {
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait(TL_RMSNORM);
   // The weights of the GEMM that consumes this norm do not depend on anything in flight: ask L2 for them now, so the
   // memory system works through the norm and the GEMM's prologue instead of idling (decode steps are bandwidth bound).
   if (pf_ptr) {
@@ -185,7 +187,7 @@ __global__ void __launch_bounds__(256) rope_kv_write_kernel(
     const bf16* __restrict__ q_norm_w, const bf16* __restrict__ k_norm_w, float norm_eps, float norm_w_offset,
     bf16* kcache, bf16* vcache, int block_size, int T, int Hq, int Hkv, int D) {
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait(TL_ROPE_KV);
   __shared__ float rope_smem[8 * 256];
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -298,7 +300,7 @@ __global__ void __launch_bounds__(256) rope_kv_write_d128_kernel(
     const bf16* __restrict__ k_norm_w, float norm_eps, float norm_w_offset, bf16* kcache, bf16* vcache, int block_size,
     int T, int Hq, int Hkv, int heads_active) {
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait(TL_ROPE_KV);
   constexpr int D = 128;
   const int lane = threadIdx.x & 31;
   const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -375,7 +377,7 @@ __global__ void __launch_bounds__(256) rope_kv_write_d128_kernel(
 __global__ void __launch_bounds__(256) gated_act_mul_kernel(const bf16* __restrict__ gu, int ld_gu, bf16* out,
                                                            int ldo, int T, int F, int act) {
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait(TL_GATED_ACT);
   const int nvec = F / 8;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)T * nvec) return;
@@ -407,7 +409,7 @@ __global__ void __launch_bounds__(256) embedding_kernel(const long long* __restr
                                                        bf16* out, int T, int H, int vocab_start, int vocab_end,
                                                        float scale) {
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait(TL_EMBED);
   const int nvec = H / 8;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)T * nvec) return;

@@ -7,6 +7,8 @@
 #include <algorithm>
 
 namespace swb {
+
+SWB_REGISTER_STATUS_UNIT(sampling);
 namespace {
 
 struct ArgMax {
@@ -35,7 +37,7 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ logi
                                                       const uint8_t* __restrict__ allow, long long* out_ids,
                                                       float* out_vals, float* part_val, long long* part_idx) {
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait(TL_ARGMAX);
   __shared__ ArgMax red[32];
   const int row = blockIdx.x;
   const int chunks = gridDim.y;
@@ -81,7 +83,7 @@ __global__ void __launch_bounds__(32) argmax_merge_kernel(const float* __restric
                                                          const long long* __restrict__ part_idx, int chunks, int V,
                                                          long long* out_ids, float* out_vals) {
   pdl_launch_dependents();
-  pdl_wait();
+  pdl_wait(TL_ARGMAX_MERGE);
   const int row = blockIdx.x;
   ArgMax best{-INFINITY, (long long)V};
   for (int c = threadIdx.x; c < chunks; c += 32)

@@ -66,6 +66,15 @@ int swb_set_wait_limit_ns(unsigned long long ns) {
   return rc;
 }
 
+// Launch timeline (profiling aid): `buf` = device buffer of 8 + 4 * capacity u64 words with buf[1] = capacity and
+// buf[0] = 0, or null to switch it off. See g_timeline in common.cuh for the record layout.
+int swb_set_timeline(void* buf) {
+  std::lock_guard<std::mutex> g(swb::units_mu());
+  int rc = 0;
+  for (auto& u : swb::units()) rc |= u.set_timeline(reinterpret_cast<unsigned long long*>(buf));
+  return rc;
+}
+
 // Programmatic dependent launch on (1) / off (0) for every kernel of this library.
 void swb_set_pdl(int on) { swb::g_pdl = on ? 1 : 0; }
 

@@ -12,6 +12,7 @@ from dataclasses import dataclass
 import torch
 
 from ..models.llama import LlamaGpu, StepInputs
+from ..utils import tracing
 from .kv_pool import PagedKvPool, PagedSequence
 
 
@@ -74,6 +75,7 @@ class ModelRunner:
         self._multi_out = torch.zeros(self.MULTI_STEPS * max_batch, dtype=torch.int64, device=dev)
         self._step = torch.zeros(1, dtype=torch.int32, device=dev)
         self._graphs: dict[tuple[int, int, bool], _DecodeGraph] = {}
+        self._meta_copy_done = None
         self.pad_batches = self.use_graphs      # decode batches are padded to a bucket so graphs are reused
         self.captures = 0
         self.h2d_bytes_last = 0
@@ -124,11 +126,12 @@ class ModelRunner:
             if er:
                 inp.embed_rows = torch.tensor(er, dtype=torch.int64, device=dev)
                 inp.embed_values = torch.cat(ev, dim=0)
-        hidden = self.model.forward_hidden(inp, self.pool.data)
-        self.launches_last = self.model.launches
-        if want_logits or all_positions:
-            return self.model.logits(hidden)
-        return self.model.greedy_tokens(hidden)
+        with tracing.span("runner.prefill", tokens=len(ids), seqs=len(seqs)):
+            hidden = self.model.forward_hidden(inp, self.pool.data)
+            self.launches_last = self.model.launches
+            if want_logits or all_positions:
+                return self.model.logits(hidden)
+            return self.model.greedy_tokens(hidden)
 
     # ---- decode (graph-captured, one token per sequence) ---------------------------------------------
     def _fill_decode_meta(self, seqs: list[PagedSequence], tokens: list[int], pad_to: int = 0) -> int:
@@ -136,6 +139,11 @@ class ModelRunner:
         token, position, slot and block table), so they recompute row 0 and store identical K / V bytes."""
         MB = self.max_batch
         h, table = self._host_np, self._host_table_np
+        if self._meta_copy_done is not None:
+            # a caller that kept the previous step's logits on the device never synchronised: the staging buffer is
+            # rewritten only after the copy that reads it has finished
+            self._meta_copy_done.synchronize()
+            self._meta_copy_done = None
         max_kv = 0
         for i, s in enumerate(seqs):
             p = s.length
@@ -212,9 +220,17 @@ class ModelRunner:
         host tensor [B] (after a stream sync) or device fp32 logits [B, vocab]."""
         B = len(seqs)
         assert B <= self.max_batch
+        with tracing.span("runner.decode", batch=B):
+            return self._decode(seqs, tokens, want_logits)
+
+    def _decode(self, seqs: list[PagedSequence], tokens: list[int], want_logits: bool):
+        B = len(seqs)
         Bp = _bucket(B, self.max_batch) if self.pad_batches else B
         max_kv = self._fill_decode_meta(seqs, tokens, Bp)
         self._dev_meta.copy_(self._host_meta, non_blocking=True)
+        if want_logits and self.model.device.type == "cuda":
+            self._meta_copy_done = torch.cuda.Event()
+            self._meta_copy_done.record()
         self.h2d_bytes_last = self._host_meta.numel() * 4
         splits = _splits_for(Bp, self.model.hkv, max_kv)
         key = (Bp, splits, want_logits)

@@ -435,7 +435,7 @@ class LlamaGpu:
                     ops.gemm_bf16_normed(act, L.down, out=res, residual=res, ssq_out=self._ssq[1],
                                          ssq_zero=self._ssq[0])
                 ssq_prev, pending_h = self._ssq[1], None
-                n += (6 if inp.attn_splits == 1 else 7) + (1 if h is not None else 0)
+                n += 6 + (1 if h is not None else 0)
                 continue
             fused = self.comm.fused if (self.comm.fused is not None and T <= self.comm.fused.max_tokens and
                                         L.post_attn_ln is None) else None
@@ -452,7 +452,7 @@ class LlamaGpu:
             if L.moe is not None:
                 pending_h = None
                 branch = self.comm.all_reduce(self._moe_ffn(h, L.moe))
-                n += 9 if inp.attn_splits == 1 or not inp.decode else 10
+                n += 9
                 continue
             act = self._gated_mlp_in(h, L.gate_up)
             if fused is not None and L.post_mlp_ln is None:
@@ -467,7 +467,7 @@ class LlamaGpu:
                 if L.post_mlp_ln is not None:
                     branch = ops.rmsnorm(branch, L.post_mlp_ln, eps, w_offset=woff)
                     n += 1
-            n += (7 if inp.attn_splits == 1 or not inp.decode else 8) + self._mlp_in_launches
+            n += 7 + self._mlp_in_launches
         self.launches = n
         if not last_stage:
             assert pending_h is None

@@ -13,7 +13,8 @@ def decode_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     idx = device.index if device.index is not None else torch.cuda.current_device()
     ws = _DECODE_WS.get(idx)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(max(nbytes, 16 << 20), dtype=torch.uint8, device=device)
+        # zeroed: the head of the buffer holds the split-KV ticket counters, which the kernels leave at zero
+        ws = torch.zeros(max(nbytes, 16 << 20), dtype=torch.uint8, device=device)
         _DECODE_WS[idx] = ws
     return ws
 
