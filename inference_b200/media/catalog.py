@@ -6,7 +6,7 @@ from ..contracts.gen_core.registry import ProviderRegistry, ProviderRegistryBuil
 
 
 def provider_registry(backend: str = "b200") -> ProviderRegistry:
-    from . import chroma, flux, kolors, qwen_image, sd3, sdxl, wan, z_image
+    from . import chroma, flux, kolors, krea, qwen_image, sd3, sdxl, wan, z_image
 
     b = ProviderRegistryBuilder()
     b.register_generators(flux.registrations(backend))
@@ -17,6 +17,7 @@ def provider_registry(backend: str = "b200") -> ProviderRegistry:
     b.register_generators(sdxl.registrations(backend))
     b.register_generators(kolors.registrations(backend))
     b.register_generators(wan.registrations(backend))
+    b.register_generators(krea.registrations(backend))
     from .train import trainer_registration
 
     b.register("trainer", trainer_registration(backend))

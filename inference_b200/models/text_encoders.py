@@ -235,7 +235,21 @@ class CausalLmTextEncoder:
         self.rot_dim, self.rope_interleaved = rope.dim, rope.interleaved
 
     @torch.no_grad()
-    def encode(self, ids: list[int]) -> torch.Tensor:
+    def encode_layers(self, ids: list[int], select: list[int]) -> torch.Tensor:
+        """token ids -> [1, len(ids), len(select), hidden]: the residual stream after `select[j]` decoder layers
+        (0 = the embeddings), stacked along a new axis (Krea conditions on twelve layers of its encoder:
+        candle-gen-krea/src/text_encoder.rs:41-56,491-520). Needs skip_last small enough to reach max(select)."""
+        if max(select) > self.layers:
+            raise ValueError(f"layer {max(select)} requested but the encoder keeps {self.layers} layers")
+        if not self.native:
+            t = torch.tensor([ids], dtype=torch.int64, device=self.device)
+            return torch.stack([self.oracle.hidden_states(t, None, num_layers=i) for i in select], dim=2)
+        taps: dict[int, torch.Tensor] = {}
+        self.encode(ids, _taps=(set(select), taps))
+        return torch.stack([taps[i] for i in select], dim=1)[None]
+
+    @torch.no_grad()
+    def encode(self, ids: list[int], _taps=None) -> torch.Tensor:
         """token ids -> [1, len(ids), hidden]."""
         t = torch.tensor([ids], dtype=torch.int64, device=self.device)
         if not self.native:
@@ -250,7 +264,11 @@ class CausalLmTextEncoder:
         ang = pos.float()[:, None] * self.inv_freq[None]
         cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
         x = ops.embedding(t, self.embed, scale=cfg.embed_scale)
-        for b in self.blocks:
+        if _taps is not None and 0 in _taps[0]:
+            _taps[1][0] = x.clone()
+        for li, b in enumerate(self.blocks):
+            if _taps is not None and li > 0 and li in _taps[0]:
+                _taps[1][li] = x.clone()
             qkv = ops.gemm_bf16(ops.rmsnorm(x, b["ln1"], eps, w_offset=woff), b["qkv"], bias=b["qkv_bias"])
             ops.rope_kv_write(qkv, pos, None, cos, sin, None, None, Hq, Hkv, D, rot_dim=self.rot_dim,
                               interleaved=self.rope_interleaved, q_norm=b["q_norm"], k_norm=b["k_norm"], norm_eps=eps,
@@ -262,6 +280,8 @@ class CausalLmTextEncoder:
             h = ops.linear_gated(ops.rmsnorm(x, b["ln2"], eps, w_offset=woff), b["gate_up"],
                                  cfg.mlp_activation)
             x = ops.gemm_bf16(h, b["down"], residual=x)
+        if _taps is not None and len(self.blocks) in _taps[0]:
+            _taps[1][len(self.blocks)] = x.clone()
         if self.final_norm:
             x = ops.rmsnorm(x, self.norm_w, eps, w_offset=woff)
         return x[None]

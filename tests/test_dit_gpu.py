@@ -137,7 +137,13 @@ def test_chroma_dit_matches_oracle():
         assert torch.equal(eager, model.forward_graphed(img, img_ids, txt, txt_ids, t, None, None))
 
 
-@pytest.mark.parametrize("family", ["flux", "chroma", "z_image", "sd3", "qwen_image", "sdxl", "kolors"])
+# families built on media/family.py: module name -> (model id, request extras)
+FAMILY_TABLE = {
+    "krea": ("krea_2_raw", {"guidance": 2.0, "negative_prompt": "blurry"}),
+}
+
+
+@pytest.mark.parametrize("family", ["flux", "chroma", "z_image", "sd3", "qwen_image", "sdxl", "kolors", *FAMILY_TABLE])
 def test_generator_providers_on_device_track_the_oracle_backend(tmp_path, family):
     """The sm_100a provider and the fp32 oracle provider render the same snapshot, seed and request."""
     import numpy as np
@@ -145,7 +151,12 @@ def test_generator_providers_on_device_track_the_oracle_backend(tmp_path, family
     from inference_b200.contracts.gen_core import GenerationRequest, LoadSpec
     from inference_b200.media import provider_registry
 
-    if family == "flux":
+    if family in FAMILY_TABLE:
+        import importlib
+
+        write_synthetic_snapshot = importlib.import_module(f"inference_b200.media.{family}").write_synthetic_snapshot
+        mid, extra = FAMILY_TABLE[family]
+    elif family == "flux":
         from inference_b200.media.flux import write_synthetic_snapshot
         mid, extra = "flux1_dev", {}
     elif family == "chroma":

@@ -45,6 +45,12 @@ def test_tp4_fused():
     _run(4, "fused", 29543)
 
 
+def test_tp8_fused():
+    if torch.cuda.device_count() < 8:
+        pytest.skip("needs 8 GPUs")
+    _run(8, "fused", 29544)
+
+
 def test_bounded_flag_wait_times_out_without_faulting():
     """A wait on a flag nothing sets gives up after the (shortened) budget, reports it, and the context survives."""
     import ctypes
