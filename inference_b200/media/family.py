@@ -48,11 +48,12 @@ class Variant:
     size_multiple: int = 16
     supports_lora: bool = False
     supports_lokr: bool = False
+    embedded_guidance: bool = False             # the guidance scale is an input of the network (one forward per step)
     extra: dict = field(default_factory=dict)   # family-specific constants (checkpoint file names, shifts, ...)
 
     @property
     def uses_cfg(self) -> bool:
-        return self.default_guidance is not None
+        return self.default_guidance is not None and not self.embedded_guidance
 
 
 def rgb8_image(img: torch.Tensor, width: int, height: int) -> Image:
@@ -108,7 +109,7 @@ class FamilyPipeline:
         raise NotImplementedError
 
     def cfg_active(self, guidance: float | None) -> bool:
-        return guidance is not None and guidance > 1.0
+        return self.variant.uses_cfg and guidance is not None and guidance > 1.0
 
     def combine(self, cond_v: torch.Tensor, uncond_v: torch.Tensor, guidance: float) -> torch.Tensor:
         return uncond_v + (cond_v - uncond_v) * guidance
@@ -121,7 +122,7 @@ class FamilyPipeline:
 
     # ---- shared program ------------------------------------------------------------------------------------------
     def guidance(self, req: GenerationRequest) -> float | None:
-        if not self.variant.uses_cfg:
+        if self.variant.default_guidance is None:
             return None
         g = req.true_cfg if req.true_cfg is not None else req.guidance
         return float(g) if g is not None else self.variant.default_guidance
@@ -226,7 +227,8 @@ def family_descriptor(v: Variant, backend: str, prefix: str = "") -> ModelDescri
     return ModelDescriptor(
         id=prefix + v.id, family=v.family, backend=backend, modality=v.modality,
         capabilities=Capabilities(
-            supports_negative_prompt=v.uses_cfg, supports_guidance=v.uses_cfg, supports_true_cfg=v.uses_cfg,
+            supports_negative_prompt=v.uses_cfg, supports_guidance=v.default_guidance is not None,
+            supports_true_cfg=v.uses_cfg,
             conditioning=list(v.conditioning), supports_lora=v.supports_lora, supports_lokr=v.supports_lokr,
             samplers=list(SOLVERS), schedulers=list(SCHEDULERS), supported_guidance_methods=[], min_size=v.min_size,
             max_size=v.max_size, max_count=8, supports_sequential_offload=True),

@@ -189,7 +189,7 @@ class KreaPipeline(FamilyPipeline):
         return dynamic_mu((req.height // p) * (req.width // p))
 
     def cfg_active(self, guidance):                      # the reference runs the unconditional branch iff guidance > 0
-        return guidance is not None and guidance > 0.0
+        return self.variant.uses_cfg and guidance is not None and guidance > 0.0
 
     def combine(self, cond_v, uncond_v, guidance):
         return krea_cfg_combine(cond_v, uncond_v, guidance)

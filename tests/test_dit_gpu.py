@@ -140,6 +140,7 @@ def test_chroma_dit_matches_oracle():
 # families built on media/family.py: module name -> (model id, request extras)
 FAMILY_TABLE = {
     "krea": ("krea_2_raw", {"guidance": 2.0, "negative_prompt": "blurry"}),
+    "flux2": ("flux2_klein_9b", {"guidance": 2.0, "negative_prompt": "blurry"}),
 }
 
 
