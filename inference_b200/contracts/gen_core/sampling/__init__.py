@@ -8,3 +8,4 @@ from .policy import (AlphaSchedule, FlowMatchPolicy, StepCoeffs, build_flow_sigm
                      vp_sigma_from_edm)
 from .schedulers import SCHEDULERS, beta_ppf, exponential_sigmas, karras_sigmas, schedule_sigmas  # noqa: F401
 from .solvers import SOLVERS, Euler, get_solver  # noqa: F401
+from .scm import ScmScheduler, run_scm_sampler  # noqa: F401

@@ -49,6 +49,7 @@ class Variant:
     supports_lora: bool = False
     supports_lokr: bool = False
     embedded_guidance: bool = False             # the guidance scale is an input of the network (one forward per step)
+    fixed_sampler: bool = False                 # the model has its own sampler: no sampler / scheduler menu
     extra: dict = field(default_factory=dict)   # family-specific constants (checkpoint file names, shifts, ...)
 
     @property
@@ -230,7 +231,8 @@ def family_descriptor(v: Variant, backend: str, prefix: str = "") -> ModelDescri
             supports_negative_prompt=v.uses_cfg, supports_guidance=v.default_guidance is not None,
             supports_true_cfg=v.uses_cfg,
             conditioning=list(v.conditioning), supports_lora=v.supports_lora, supports_lokr=v.supports_lokr,
-            samplers=list(SOLVERS), schedulers=list(SCHEDULERS), supported_guidance_methods=[], min_size=v.min_size,
+            samplers=[] if v.fixed_sampler else list(SOLVERS), schedulers=[] if v.fixed_sampler else list(SCHEDULERS),
+            supported_guidance_methods=[], min_size=v.min_size,
             max_size=v.max_size, max_count=8, supports_sequential_offload=True),
         required_components=[])
 

@@ -141,6 +141,7 @@ def test_chroma_dit_matches_oracle():
 FAMILY_TABLE = {
     "krea": ("krea_2_raw", {"guidance": 2.0, "negative_prompt": "blurry"}),
     "flux2": ("flux2_klein_9b", {"guidance": 2.0, "negative_prompt": "blurry"}),
+    "sana": ("sana_1600m", {"guidance": 2.0, "negative_prompt": "blurry"}),
 }
 
 
