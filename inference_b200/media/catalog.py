@@ -37,4 +37,7 @@ def provider_registry(backend: str = "b200") -> ProviderRegistry:
     for kind, regs in vision_providers.registrations(backend).items():
         for r in regs:
             b.register(kind, r)
+    from . import joycaption
+
+    b.register("captioner", joycaption.registration(backend))
     return b.build()
