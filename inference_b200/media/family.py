@@ -115,6 +115,10 @@ class FamilyPipeline:
     def combine(self, cond_v: torch.Tensor, uncond_v: torch.Tensor, guidance: float) -> torch.Tensor:
         return uncond_v + (cond_v - uncond_v) * guidance
 
+    def step_guidance(self, step: int, steps: int, guidance: float) -> float:
+        """Guidance scale of evaluation `step` (0-based) out of `steps`; constant unless a family schedules it."""
+        return guidance
+
     def latent_shape(self, req: GenerationRequest) -> tuple[int, int, int]:
         return self.latent_channels, req.height // self.latent_downscale, req.width // self.latent_downscale
 
@@ -162,7 +166,8 @@ class FamilyPipeline:
                     events[-1][0].record()
                 vel = self.velocity(heavy, x_in, float(sigma), pos).float()
                 if neg is not None:
-                    vel = self.combine(vel, self.velocity(heavy, x_in, float(sigma), neg).float(), guidance)
+                    vel = self.combine(vel, self.velocity(heavy, x_in, float(sigma), neg).float(),
+                                       self.step_guidance(state["step"], steps, guidance))
                 if events is not None:
                     events[-1][1].record()
                 state["step"] += 1
@@ -228,7 +233,7 @@ def family_descriptor(v: Variant, backend: str, prefix: str = "") -> ModelDescri
     return ModelDescriptor(
         id=prefix + v.id, family=v.family, backend=backend, modality=v.modality,
         capabilities=Capabilities(
-            supports_negative_prompt=v.uses_cfg, supports_guidance=v.default_guidance is not None,
+            supports_negative_prompt=v.uses_cfg and not v.extra.get("no_negative"), supports_guidance=v.default_guidance is not None,
             supports_true_cfg=v.uses_cfg,
             conditioning=list(v.conditioning), supports_lora=v.supports_lora, supports_lokr=v.supports_lokr,
             samplers=[] if v.fixed_sampler else list(SOLVERS), schedulers=[] if v.fixed_sampler else list(SCHEDULERS),
@@ -298,3 +303,30 @@ def merged_adapters(weights: dict[str, torch.Tensor], adapters: list, mid: str) 
             raise LoadError(f"{mid}: adapter file {ad.path} not found")
         weights = merge_lora(weights, load_file(ad.path), ad.scale if ad.scale is not None else 1.0)
     return weights
+
+
+def load_vl_text_tower(mid: str, root: Path, device, deepest_layer: int):
+    """(CausalLmTextEncoder, tokenizer) for families conditioned on intermediate layers of a Qwen3-VL language tower
+    stored under `text_encoder/` (+ `tokenizer/tokenizer.json`): the vision tower is dropped and decoder layers above
+    `deepest_layer` are never run."""
+    import tokenizers
+
+    from ..io.safetensors_io import load_dir
+    from ..models.qwen3_vl import language_model_config
+    from ..models.text_encoders import CausalLmTextEncoder
+
+    te, tk = Path(root) / "text_encoder", Path(root) / "tokenizer" / "tokenizer.json"
+    if not te.is_dir() or not tk.exists():
+        raise LoadError(f"{mid}: snapshot {root} lacks text_encoder/ or tokenizer/tokenizer.json")
+    cfg = language_model_config(json.loads((te / "config.json").read_text()))
+    w = {}
+    for k, v in load_dir(te).items():
+        for pre in ("model.language_model.", "language_model.model.", "language_model."):
+            if k.startswith(pre):
+                w["model." + k[len(pre):]] = v
+                break
+        else:
+            if k.startswith("model.") and not k.startswith("model.visual"):
+                w[k] = v
+    enc = CausalLmTextEncoder(cfg, w, device, skip_last=max(0, cfg.num_layers - deepest_layer))
+    return enc, tokenizers.Tokenizer.from_file(str(tk))

@@ -140,37 +140,52 @@ class Flux2Pipeline(FamilyPipeline):
         pad = int(top.get("pad_token_id") or 0)
         return Flux2PromptEncoder(lm, tok, tuple(self.raw.get("te_layers", self.variant.extra["te_layers"])), pad, self.max_len)
 
-    def load_heavy(self) -> _Heavy:
+    def load_vae(self):
+        """(decoder, post-quant 1x1 conv or None, bn mean, bn std [1, 128, 1, 1]) of the FLUX.2 autoencoder."""
         from ..io.safetensors_io import load_dir
         from .chroma import convert_diffusers_vae_decoder
 
         if self.random_init is not None:
-            seed = int(self.random_init)
-            dit_w = random_flux2_weights(self.dit_cfg, seed, 0.02, self.dtype, self.device)
-            vae_w = random_vae_weights(self.vae_cfg, seed + 1)
-            extra = {}
+            vae_w, extra = random_vae_weights(self.vae_cfg, int(self.random_init) + 1), {}
         else:
-            for d in ("transformer", "vae"):
-                if not (self.root / d).is_dir():
-                    raise LoadError(f"{self.variant.id}: snapshot {self.root} lacks {d}/")
-            dit_w = load_dir(self.root / "transformer")
+            if not (self.root / "vae").is_dir():
+                raise LoadError(f"{self.variant.id}: snapshot {self.root} lacks vae/")
             raw_vae = load_dir(self.root / "vae")
             vae_w = convert_diffusers_vae_decoder(raw_vae, len(self.vae_cfg.ch_mult))
             extra = {k: v for k, v in raw_vae.items() if k.startswith(("post_quant_conv.", "bn."))}
-        dit = Flux2DiT(self.dit_cfg, dit_w, self.dtype, self.device)
         if self.backend == "b200":
             from ..models.vae import VaeDecoderGpu
 
             vae = VaeDecoderGpu(self.vae_cfg, self.device).load_state_dict(vae_w)
         else:
             vae = OracleVaeDecoder(self.vae_cfg, vae_w, device=self.device)
-        C = self.latent_channels
+        C = 128
         mean = extra.get("bn.running_mean", torch.zeros(C)).float().view(1, C, 1, 1).to(self.device)
         std = torch.sqrt(extra.get("bn.running_var", torch.ones(C) - 1e-4).float() + 1e-4).view(1, C, 1, 1).to(self.device)
         pq = None
         if "post_quant_conv.weight" in extra:
             pq = (extra["post_quant_conv.weight"].float().to(self.device), extra["post_quant_conv.bias"].float().to(self.device))
-        return _Heavy(dit, vae, pq, mean, std)
+        return vae, pq, mean, std
+
+    def decode_latent(self, heavy, lat: torch.Tensor, req: GenerationRequest) -> list[Image]:
+        """[1, 32, H/8, W/8] de-normalised latent -> RGB8."""
+        if heavy.post_quant is not None:
+            lat = F.conv2d(lat, heavy.post_quant[0], heavy.post_quant[1])
+        if self.backend == "b200":
+            u8 = heavy.vae.decode_rgb8(lat)[0].cpu()
+            return [Image(width=req.width, height=req.height, pixels=u8.contiguous().numpy().tobytes())]
+        return [rgb8_image(heavy.vae.decode(lat)[0], req.width, req.height)]
+
+    def load_heavy(self) -> _Heavy:
+        from ..io.safetensors_io import load_dir
+
+        if self.random_init is not None:
+            dit_w = random_flux2_weights(self.dit_cfg, int(self.random_init), 0.02, self.dtype, self.device)
+        else:
+            if not (self.root / "transformer").is_dir():
+                raise LoadError(f"{self.variant.id}: snapshot {self.root} lacks transformer/")
+            dit_w = load_dir(self.root / "transformer")
+        return _Heavy(Flux2DiT(self.dit_cfg, dit_w, self.dtype, self.device), *self.load_vae())
 
     def native_sigmas(self, steps: int, req: GenerationRequest) -> list[float]:
         return build_sigmas(steps, compute_mu((req.height // 16) * (req.width // 16), steps))
@@ -194,13 +209,7 @@ class Flux2Pipeline(FamilyPipeline):
         return out.transpose(1, 2).reshape(B, C, h, w)
 
     def decode(self, heavy: _Heavy, z: torch.Tensor, req: GenerationRequest) -> list[Image]:
-        lat = vae_unpatchify(z.to(self.device).float() * heavy.bn_std + heavy.bn_mean)       # [1, 32, H/8, W/8]
-        if heavy.post_quant is not None:
-            lat = F.conv2d(lat, heavy.post_quant[0], heavy.post_quant[1])
-        if self.backend == "b200":
-            u8 = heavy.vae.decode_rgb8(lat)[0].cpu()
-            return [Image(width=req.width, height=req.height, pixels=u8.contiguous().numpy().tobytes())]
-        return [rgb8_image(heavy.vae.decode(lat)[0], req.width, req.height)]
+        return self.decode_latent(heavy, vae_unpatchify(z.to(self.device).float() * heavy.bn_std + heavy.bn_mean), req)
 
 
 def registrations(backend: str = "b200") -> list[Registration]:

@@ -28,7 +28,8 @@ from ..contracts.gen_core.media import Image
 from ..contracts.gen_core.registry import Registration
 from ..models.dit_krea import KreaConfig, KreaDiT, random_krea_weights
 from ..models.vae_qwen import QwenVaeConfig, QwenVaeDecoder
-from .family import (FamilyPipeline, HashPromptEncoder, Variant, family_registrations, merged_adapters, rgb8_image)
+from .family import (FamilyPipeline, HashPromptEncoder, Variant, family_registrations, load_vl_text_tower, merged_adapters,
+                     rgb8_image)
 
 TURBO_MU, TURBO_STEPS = 1.15, 8
 RAW_STEPS, RAW_GUIDANCE = 52, 3.5
@@ -127,29 +128,8 @@ class KreaPipeline(FamilyPipeline):
     def load_text(self):
         if self.text_kind == "hash":
             return HashPromptEncoder(self.dit_cfg.text_hidden_dim, self.device, self.dtype, layers=self.dit_cfg.num_text_layers)
-        import tokenizers
-
-        from ..io.safetensors_io import load_dir
-        from ..models.qwen3_vl import language_model_config
-        from ..models.text_encoders import CausalLmTextEncoder
-
-        te, tk = self.root / "text_encoder", self.root / "tokenizer" / "tokenizer.json"
-        if not te.is_dir() or not tk.exists():
-            raise LoadError(f"{self.variant.id}: snapshot {self.root} lacks text_encoder/ or tokenizer/tokenizer.json")
-        top = json.loads((te / "config.json").read_text())
-        cfg = language_model_config(top)
-        w = {}
-        for k, v in load_dir(te).items():               # keep the language model, drop the vision tower
-            for pre in ("model.language_model.", "language_model.model.", "language_model."):
-                if k.startswith(pre):
-                    w["model." + k[len(pre):]] = v
-                    break
-            else:
-                if k.startswith("model.") and not k.startswith("model.visual"):
-                    w[k] = v
-        skip = max(0, cfg.num_layers - max(self.select))
-        enc = CausalLmTextEncoder(cfg, w, self.device, skip_last=skip)
-        return KreaPromptEncoder(enc, tokenizers.Tokenizer.from_file(str(tk)), self.select, self.prefix_tokens)
+        enc, tok = load_vl_text_tower(self.variant.id, self.root, self.device, max(self.select))
+        return KreaPromptEncoder(enc, tok, self.select, self.prefix_tokens)
 
     def load_heavy(self) -> _Heavy:
         from ..io.safetensors_io import load_dir

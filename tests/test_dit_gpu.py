@@ -142,6 +142,7 @@ FAMILY_TABLE = {
     "krea": ("krea_2_raw", {"guidance": 2.0, "negative_prompt": "blurry"}),
     "flux2": ("flux2_klein_9b", {"guidance": 2.0, "negative_prompt": "blurry"}),
     "sana": ("sana_1600m", {"guidance": 2.0, "negative_prompt": "blurry"}),
+    "ideogram": ("ideogram_4", {"guidance": 2.0}),
 }
 
 
