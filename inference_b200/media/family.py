@@ -50,6 +50,7 @@ class Variant:
     supports_lokr: bool = False
     embedded_guidance: bool = False             # the guidance scale is an input of the network (one forward per step)
     fixed_sampler: bool = False                 # the model has its own sampler: no sampler / scheduler menu
+    max_count: int = 8
     extra: dict = field(default_factory=dict)   # family-specific constants (checkpoint file names, shifts, ...)
 
     @property
@@ -62,6 +63,12 @@ def rgb8_image(img: torch.Tensor, width: int, height: int) -> Image:
     `round_rgb8` (candle-gen/src/lib.rs:188-280)."""
     host = torch.round((img.float().clamp(-1, 1) + 1) * 127.5).to(torch.uint8).permute(1, 2, 0).contiguous().cpu()
     return Image(width=width, height=height, pixels=host.numpy().tobytes())
+
+
+def video_frames_rgb8(video: torch.Tensor, width: int, height: int) -> list[Image]:
+    """[3, F, H, W] in [-1, 1] -> one host RGB8 image per frame (round-half-even)."""
+    u8 = torch.round((video.float().clamp(-1, 1) + 1) * 127.5).to(torch.uint8).permute(1, 2, 3, 0).contiguous().cpu()
+    return [Image(width=width, height=height, pixels=f.numpy().tobytes()) for f in u8]
 
 
 class FamilyPipeline:
@@ -114,6 +121,9 @@ class FamilyPipeline:
 
     def combine(self, cond_v: torch.Tensor, uncond_v: torch.Tensor, guidance: float) -> torch.Tensor:
         return uncond_v + (cond_v - uncond_v) * guidance
+
+    def output_fps(self, req: GenerationRequest) -> int | None:
+        return req.fps
 
     def step_guidance(self, step: int, steps: int, guidance: float) -> float:
         """Guidance scale of evaluation `step` (0-based) out of `steps`; constant unless a family schedules it."""
@@ -225,7 +235,7 @@ class FamilyGenerator(Generator):
         images = self.residency.run(req.cancel, on_progress, lambda text: self.pipe.encode(text, req),
                                     lambda heavy, cond: self.pipe.render(heavy, cond, req, on_progress))
         if self.pipe.variant.modality is Modality.VIDEO:
-            return GenerationOutput(video_frames=images)
+            return GenerationOutput(video_frames=images, fps=self.pipe.output_fps(req))
         return GenerationOutput(images=images)
 
 
@@ -238,7 +248,7 @@ def family_descriptor(v: Variant, backend: str, prefix: str = "") -> ModelDescri
             conditioning=list(v.conditioning), supports_lora=v.supports_lora, supports_lokr=v.supports_lokr,
             samplers=[] if v.fixed_sampler else list(SOLVERS), schedulers=[] if v.fixed_sampler else list(SCHEDULERS),
             supported_guidance_methods=[], min_size=v.min_size,
-            max_size=v.max_size, max_count=8, supports_sequential_offload=True),
+            max_size=v.max_size, max_count=v.max_count, supports_sequential_offload=True),
         required_components=[])
 
 

@@ -143,6 +143,7 @@ FAMILY_TABLE = {
     "flux2": ("flux2_klein_9b", {"guidance": 2.0, "negative_prompt": "blurry"}),
     "sana": ("sana_1600m", {"guidance": 2.0, "negative_prompt": "blurry"}),
     "ideogram": ("ideogram_4", {"guidance": 2.0}),
+    "mochi": ("mochi_1", {"guidance": 2.0, "negative_prompt": "blurry", "frames": 7}),
 }
 
 
@@ -193,7 +194,8 @@ def test_generator_providers_on_device_track_the_oracle_backend(tmp_path, family
     imgs = {}
     for backend, prefix in (("b200", ""), ("cpu", "cpu_")):
         g = provider_registry(backend).load(prefix + mid, LoadSpec.from_dir(snap))
-        im = g.generate(GenerationRequest(**req)).images[0]
+        out = g.generate(GenerationRequest(**req))
+        im = (out.images or out.video_frames)[-1]
         assert (im.width, im.height) == (256, 256)
         imgs[backend] = np.frombuffer(im.pixels, dtype=np.uint8).astype(np.float32)
     diff = float(np.abs(imgs["b200"] - imgs["cpu"]).mean())
