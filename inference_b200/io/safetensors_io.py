@@ -116,7 +116,7 @@ def save_file(tensors: dict[str, torch.Tensor], path: str | Path, metadata: dict
         t = tensors[name].detach().cpu().contiguous()
         if t.dtype not in _NAMES:
             raise LoadError(f"cannot save dtype {t.dtype}")
-        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [offset, offset + len(raw)]}
         offset += len(raw)
         blobs.append(raw)

@@ -340,3 +340,59 @@ def load_vl_text_tower(mid: str, root: Path, device, deepest_layer: int):
                 w[k] = v
     enc = CausalLmTextEncoder(cfg, w, device, skip_last=max(0, cfg.num_layers - deepest_layer))
     return enc, tokenizers.Tokenizer.from_file(str(tk))
+
+
+ADAPTER_ROOTS = ("", "model.diffusion_model.", "diffusion_model.", "transformer.", "net.", "model.", "lora_unet_", "lycoris_")
+
+
+def fold_adapters(weights: dict[str, torch.Tensor], adapters: list, mid: str) -> dict[str, torch.Tensor]:
+    """LoRA and LoKr adapter files folded into a state dict at load, stacked in order. A module is addressed by its
+    dotted path under any of the usual roots, or by the kohya spelling (dots replaced by underscores); a target that
+    matches no 2-D weight of the model is an error, never a silent partial application."""
+    from ..io.safetensors_io import load_file
+    from .adapters import parse_thirdparty
+
+    out = dict(weights)
+    modules = {k[: -len(".weight")] for k, v in out.items() if k.endswith(".weight") and v.dim() == 2}
+    flat = {m.replace(".", "_"): m for m in modules}
+
+    def route(name: str) -> str:
+        for root in ADAPTER_ROOTS:
+            if name.startswith(root):
+                n = name[len(root):]
+                hit = n if n in modules else flat.get(n.replace(".", "_"))
+                if hit is not None:
+                    return hit
+        raise LoadError(f"{mid}: adapter targets '{name}', which the model does not have")
+
+    for ad in adapters:
+        if not Path(ad.path).is_file():
+            raise LoadError(f"{mid}: adapter file {ad.path} not found")
+        t = load_file(ad.path)
+        user = ad.scale if ad.scale is not None else 1.0
+        if ad.kind is AdapterKind.LOKR:
+            lokr, loha = parse_thirdparty(t)
+            if not lokr and not loha:
+                raise LoadError(f"{mid}: {ad.path} holds no LoKr / LoHa factors")
+            for mod, f in {**lokr, **loha}.items():
+                key = route(mod) + ".weight"
+                w = out[key]
+                out[key] = (w.float() + f.delta(tuple(w.shape), user).to(w.device)).to(w.dtype)
+            continue
+        pairs: dict[str, dict] = {}
+        for k, v in t.items():
+            for leaf, slot in ((".lora_A.weight", "a"), (".lora_down.weight", "a"), (".lora_B.weight", "b"),
+                               (".lora_up.weight", "b"), (".alpha", "alpha")):
+                if k.endswith(leaf):
+                    pairs.setdefault(k[: -len(leaf)], {})[slot] = v
+        if not pairs:
+            raise LoadError(f"{mid}: {ad.path} holds no LoRA factors")
+        for mod, f in pairs.items():
+            if "a" not in f or "b" not in f:
+                raise LoadError(f"{mid}: adapter module '{mod}' lacks a down or an up factor")
+            key = route(mod) + ".weight"
+            a, b, w = f["a"].float(), f["b"].float(), out[key]
+            r = a.shape[0]
+            alpha = float(f["alpha"].flatten()[0]) if "alpha" in f else float(r)
+            out[key] = (w.float() + (b @ a).to(w.device) * (user * alpha / r)).to(w.dtype)
+    return out

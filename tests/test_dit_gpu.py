@@ -143,6 +143,7 @@ FAMILY_TABLE = {
     "flux2": ("flux2_klein_9b", {"guidance": 2.0, "negative_prompt": "blurry"}),
     "sana": ("sana_1600m", {"guidance": 2.0, "negative_prompt": "blurry"}),
     "ideogram": ("ideogram_4", {"guidance": 2.0}),
+    "anima": ("anima_base", {"guidance": 2.0, "negative_prompt": "blurry", "width": 512, "height": 512}),
     "mochi": ("mochi_1", {"guidance": 2.0, "negative_prompt": "blurry", "frames": 7}),
 }
 
@@ -190,13 +191,13 @@ def test_generator_providers_on_device_track_the_oracle_backend(tmp_path, family
         write_synthetic_snapshot = lambda root: zi(root, text="qwen3", te_head_dim=128)      # noqa: E731
         mid, extra = "z_image", {"guidance": 2.0, "negative_prompt": "blurry"}
     snap = write_synthetic_snapshot(tmp_path / family)
-    req = dict(prompt="a lighthouse at dusk", width=256, height=256, steps=2, seed=11, **extra)
+    req = {**dict(prompt="a lighthouse at dusk", width=256, height=256, steps=2, seed=11), **extra}
     imgs = {}
     for backend, prefix in (("b200", ""), ("cpu", "cpu_")):
         g = provider_registry(backend).load(prefix + mid, LoadSpec.from_dir(snap))
         out = g.generate(GenerationRequest(**req))
         im = (out.images or out.video_frames)[-1]
-        assert (im.width, im.height) == (256, 256)
+        assert (im.width, im.height) == (req["width"], req["height"])
         imgs[backend] = np.frombuffer(im.pixels, dtype=np.uint8).astype(np.float32)
     diff = float(np.abs(imgs["b200"] - imgs["cpu"]).mean())
     assert diff < 8.0, diff
