@@ -6,7 +6,7 @@ from ..contracts.gen_core.registry import ProviderRegistry, ProviderRegistryBuil
 
 
 def provider_registry(backend: str = "b200") -> ProviderRegistry:
-    from . import anima, chroma, flux, flux2, ideogram, kolors, mochi, krea, qwen_image, sana, sd3, sdxl, wan, z_image
+    from . import anima, chroma, flux, flux2, ideogram, kolors, mochi, krea, qwen_image, sana, sd3, sdxl, svd, wan, z_image
 
     b = ProviderRegistryBuilder()
     b.register_generators(flux.registrations(backend))
@@ -23,6 +23,7 @@ def provider_registry(backend: str = "b200") -> ProviderRegistry:
     b.register_generators(ideogram.registrations(backend))
     b.register_generators(mochi.registrations(backend))
     b.register_generators(anima.registrations(backend))
+    b.register_generators(svd.registrations(backend))
     from .train import trainer_registration
 
     b.register("trainer", trainer_registration(backend))

@@ -219,7 +219,7 @@ class FamilyGenerator(Generator):
     def validate(self, req: GenerationRequest) -> None:
         mid, v = self._descriptor.id, self.pipe.variant
         self._descriptor.capabilities.validate_request(mid, req)
-        if not req.prompt:
+        if not req.prompt and not v.extra.get("promptless"):
             raise InferenceError(f"{mid}: prompt must not be empty")
         if req.steps == 0:
             raise InferenceError(f"{mid}: steps must be >= 1 (an explicit 0 renders undenoised noise)")

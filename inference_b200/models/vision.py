@@ -157,3 +157,27 @@ def preprocess(rgb8: torch.Tensor, size: int, mean=CLIP_MEAN, std=CLIP_STD, crop
     x = x.round() / 255.0
     m, s = torch.tensor(mean).view(1, 3, 1, 1), torch.tensor(std).view(1, 3, 1, 1)
     return (x - m) / s
+
+
+def random_vision_weights(cfg: VisionConfig, seed: int = 0, std: float = 0.05) -> dict[str, torch.Tensor]:
+    """A random CLIP-style vision tower (class token, pre / post LayerNorm, optional visual projection)."""
+    g = torch.Generator().manual_seed(seed)
+    rn = lambda *s: torch.randn(*s, generator=g)      # noqa: E731
+    E, I, P = cfg.hidden_size, cfg.intermediate_size, cfg.patch_size
+    p = "vision_model."
+    w = {p + "embeddings.patch_embedding.weight": rn(E, cfg.num_channels, P, P) * std,
+         p + "embeddings.class_embedding": rn(E) * std,
+         p + "embeddings.position_embedding.weight": rn(cfg.num_patches + 1, E) * std}
+    for n in ("pre_layrnorm", "post_layernorm"):
+        w[p + n + ".weight"], w[p + n + ".bias"] = 1.0 + rn(E) * 0.05, rn(E) * 0.02
+    for i in range(cfg.num_hidden_layers):
+        lp = f"{p}encoder.layers.{i}."
+        for n in ("layer_norm1", "layer_norm2"):
+            w[lp + n + ".weight"], w[lp + n + ".bias"] = 1.0 + rn(E) * 0.05, rn(E) * 0.02
+        for m in ("q_proj", "k_proj", "v_proj", "out_proj"):
+            w[f"{lp}self_attn.{m}.weight"], w[f"{lp}self_attn.{m}.bias"] = rn(E, E) * std, rn(E) * 0.01
+        w[lp + "mlp.fc1.weight"], w[lp + "mlp.fc1.bias"] = rn(I, E) * std, rn(I) * 0.01
+        w[lp + "mlp.fc2.weight"], w[lp + "mlp.fc2.bias"] = rn(E, I) * std, rn(E) * 0.01
+    if cfg.projection_dim:
+        w["visual_projection.weight"] = rn(cfg.projection_dim, E) * std
+    return w

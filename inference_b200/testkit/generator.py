@@ -29,10 +29,12 @@ class Profile:
     steps: int = 2          # requested AND expected resolved step count
     seed: int = 42
     cancel_steps: int = 6
+    conditioning: tuple = ()      # conditioning every request of the profile carries (image -> video providers ...)
 
 
 def base_request(p: Profile) -> GenerationRequest:
-    return GenerationRequest(prompt=p.prompt, width=p.width, height=p.height, steps=p.steps, seed=p.seed)
+    return GenerationRequest(prompt=p.prompt, width=p.width, height=p.height, steps=p.steps, seed=p.seed,
+                             conditioning=list(p.conditioning))
 
 
 def output_bytes(out: GenerationOutput) -> bytes:

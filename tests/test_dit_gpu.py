@@ -137,8 +137,18 @@ def test_chroma_dit_matches_oracle():
         assert torch.equal(eager, model.forward_graphed(img, img_ids, txt, txt_ids, t, None, None))
 
 
+def _reference_conditioning():
+    from inference_b200.contracts.gen_core.generator import Conditioning, ConditioningKind
+    from inference_b200.contracts.gen_core.media import Image
+
+    g = torch.Generator().manual_seed(0)
+    px = torch.randint(0, 255, (30 * 40 * 3,), generator=g, dtype=torch.uint8).numpy().tobytes()
+    return [Conditioning(kind=ConditioningKind.REFERENCE, image=Image(40, 30, px))]
+
+
 # families built on media/family.py: module name -> (model id, request extras)
 FAMILY_TABLE = {
+    "svd": ("svd_xt", {"prompt": "", "frames": 3, "width": 64, "height": 64, "conditioning": _reference_conditioning()}),
     "krea": ("krea_2_raw", {"guidance": 2.0, "negative_prompt": "blurry"}),
     "flux2": ("flux2_klein_9b", {"guidance": 2.0, "negative_prompt": "blurry"}),
     "sana": ("sana_1600m", {"guidance": 2.0, "negative_prompt": "blurry"}),
