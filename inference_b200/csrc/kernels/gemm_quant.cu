@@ -22,6 +22,10 @@
 
 namespace swb {
 
+bool gemv_q4k_accepts(int T, int K, int lda, const void* A, const void* Wq);      // gemv_q4k.cu
+int gemv_q4k_launch(const void* A, int lda, const void* Wq, void* D, int ldd, int T, int N, int K, const void* bias,
+                    cudaStream_t stream);
+
 SWB_REGISTER_STATUS_UNIT(gemm_quant);
 
 namespace {
@@ -610,6 +614,12 @@ static int gemm_quant_impl(int fmt, const void* A, int lda, const void* Wq, cons
     return -3;
   if ((fmt == 2 || fmt == 3) && (!scales || !biases)) return -3;
   if (fmt == 4 && (!scales || (reinterpret_cast<uintptr_t>(scales) & 3))) return -3;
+  // up to 8 tokens of Q4_K go to the integer matrix-vector kernel (force_splits < 0 keeps the tensor-core path)
+  if (fmt == 0 && force_splits >= 0 && gemv_q4k_accepts(T, K, lda, A, Wq)) {
+    static const bool off = [] { const char* e = getenv("SWB_Q4K_GEMV"); return e && e[0] == '0'; }();
+    if (!off) return gemv_q4k_launch(A, lda, Wq, D, ldd, T, N, K, bias, reinterpret_cast<cudaStream_t>(stream));
+  }
+  if (force_splits < 0) force_splits = 0;
   QParams p{};
   p.sf = reinterpret_cast<const uint8_t*>(scales);
   p.sf_m_atoms = (N + 127) / 128;

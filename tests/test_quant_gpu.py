@@ -27,6 +27,36 @@ def test_gemm_quant_matches_reference(fmt, T, N, K, splits):
         assert err < 2e-2 * max(1.0, ref.abs().max().item()), (fmt, rep, err)
 
 
+@pytest.mark.parametrize("T,N,K", [(1, 200, 256), (3, 512, 4096), (5, 300, 14336), (8, 130, 7168), (2, 33, 1024)])
+def test_q4k_matvec_kernel_matches_reference_and_the_tensor_core_path(T, N, K):
+    """Up to 8 tokens of Q4_K run the integer matrix-vector kernel (int8 activations per 32-block); splits = -1 keeps
+    the dequantising tensor-core kernel. Both against CPU dequantisation + fp32 matmul."""
+    from inference_b200 import ops
+    from inference_b200.ops import quant
+
+    g = torch.Generator().manual_seed(T * 7 + K)
+    w = torch.randn(N, K, generator=g) * 0.05
+    qw = quant.quantize_weight(w, "Q4_K").to("cuda")
+    wref = quant.dequantize_reference(qw)
+    a = (torch.randn(T, K, generator=g) * 0.5).bfloat16().cuda()
+    bias = (torch.randn(N, generator=g) * 0.1).bfloat16().cuda()
+    ref = a.float().cpu() @ wref.t() + bias.float().cpu()
+    tol = 2e-2 * max(1.0, ref.abs().max().item())
+    mv = quant.linear_quant(a, qw, bias=bias)
+    tc = quant.linear_quant(a, qw, bias=bias, splits=-1)
+    ops.check_status()
+    assert (mv.float().cpu() - ref).abs().max().item() < tol
+    assert (tc.float().cpu() - ref).abs().max().item() < tol
+    assert not torch.equal(mv, tc) or T * N < 64          # two different kernels produced the two results
+    # activations with a zero block and a large outlier block keep their per-block scales
+    a2 = a.clone()
+    a2[:, :32] = 0
+    a2[:, 32:64] *= 40
+    ref2 = a2.float().cpu() @ wref.t()
+    out2 = quant.linear_quant(a2, qw)
+    assert (out2.float().cpu() - ref2).abs().max().item() < 2e-2 * max(1.0, ref2.abs().max().item())
+
+
 def test_large_token_count_uses_dense_path():
     from inference_b200.ops import quant
 
