@@ -1,0 +1,305 @@
+// NVFP4 x NVFP4 GEMM on the block-scaled tensor-core path (W4A4): D[T, N] = alpha * (Aq[T, K] . Wq[N, K]^T) + bias.
+//
+// Both operands are E2M1 codes, two per byte, K-major, with one unsigned E4M3 scale per 16 elements stored in
+// 128-row x 4-scale atoms (512 bytes: row r of the atom at (r % 32) * 16 + (r / 32) * 4, atoms ordered row-atom
+// fastest) and one fp32 scale per tensor; alpha is the product of the two tensor scales (the activation's lives on the
+// device: it was produced by the quantiser that ran just before). The reference reaches this regime through
+// cuBLASLt's FP4 matmul (candle-gen/src/quant/nvfp4_linear.rs, W4A4 lane); here it is one kernel:
+//
+//   warp 0   one thread: per stage two TMA tiles (128 rows x 256 K = 128 bytes per row, 128-byte swizzle) and eight
+//            512-byte bulk copies of scale atoms, all completing on the stage's mbarrier
+//   warp 1   one thread: per stage 8 tcgen05.cp (scale atoms -> tensor memory, the 32-lane x 128-bit shape replicated
+//            to the four lane quarters) and 4 tcgen05.mma.kind::mxf4nvf4.block_scale (M 128, N 128, K 64 each) into one
+//            of two 128-column fp32 accumulators; tcgen05.commit releases the stage / hands the accumulator over
+//   warps 2..5  epilogue: tcgen05.ld 16 columns at a time, * alpha + bias, bf16, 32-byte stores; overlaps the next
+//            tile's main loop through the second accumulator
+//
+// Persistent: one CTA per SM walks tiles (row-tile fastest, so concurrent CTAs share a weight tile in L2).
+// Every wait is bounded (mbar_wait): on timeout the CTA raises the status word, drains its copies and frees its TMEM.
+#include "common.cuh"
+#include "gemm_tcgen05.cuh"
+
+#include <algorithm>
+
+namespace swb {
+
+SWB_REGISTER_STATUS_UNIT(gemm_nvfp4);
+
+namespace {
+
+constexpr int FM = 128, FN = 128, FK = 256;          // tile; FK elements = 128 bytes of codes per row
+constexpr int F_STAGES = 5;
+constexpr int F_THREADS = 192;
+constexpr uint32_t F_TILE_BYTES = FM * (FK / 2);      // 16 KB per operand tile
+constexpr uint32_t F_SF_BYTES = 4 * 512;              // four scale atoms (K 256 = 4 x 64) per operand
+constexpr uint32_t F_STAGE_BYTES = 2 * F_TILE_BYTES + 2 * F_SF_BYTES;
+constexpr uint32_t F_SMEM = F_STAGES * F_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr uint32_t F_TMEM_COLS = 512;
+constexpr uint32_t F_SFA_COL = 256, F_SFB_COL = 272;  // after the two 128-column accumulators
+
+struct FParams {
+  const uint8_t* sfa;     // activation scale atoms
+  const uint8_t* sfb;     // weight scale atoms
+  int sfa_m_atoms, sfb_m_atoms;
+  const float* a_scale;   // device: activation tensor scale
+  float w_scale;
+  const bf16* bias;
+  bf16* out;
+  int ldd, T, N, kblocks, tiles_m, tiles_n;
+};
+
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+// 32 rows x 16 bytes, rows contiguous: 8-row core matrices 128 bytes apart, no swizzle
+__device__ __forceinline__ uint64_t sf_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;            // leading byte offset: one 16-byte column only
+  d |= (uint64_t)(128 >> 4) << 32;   // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+// E2M1 x E2M1 with UE4M3 scales per 16, fp32 accumulate, both K-major
+__host__ __device__ constexpr uint32_t idesc_nvf4(int m, int n) {
+  return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | (0u << 23) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_nvf4(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate,
+                                          uint32_t tsfa, uint32_t tsfb) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(F_THREADS, 1)
+gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const FParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(smem + F_STAGES * F_STAGE_BYTES);
+  uint64_t* bar_empty = bar_full + F_STAGES;
+  uint64_t* bar_tfull = bar_empty + F_STAGES;
+  uint64_t* bar_tempty = bar_tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 2);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < F_STAGES; ++s) {
+      mbar_init(&bar_full[s], 1);
+      mbar_init(&bar_empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&bar_tfull[a], 1);
+      mbar_init(&bar_tempty[a], 4);
+    }
+    *s_abort = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, F_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  const int tiles = p.tiles_m * p.tiles_n;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint64_t pol = l2_policy_evict_last();
+      int stage = 0;
+      uint32_t phase = 0, outstanding = 0, issue_phase_bits = 0;
+      bool ok = true;
+      pdl_wait(TL_GEMM_QUANT);
+      for (int t = blockIdx.x; ok && t < tiles; t += gridDim.x) {
+        const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+        for (int kb = 0; kb < p.kblocks; ++kb) {
+          ok = mbar_wait(&bar_empty[stage], phase ^ 1, s_abort, 100 + stage);
+          if (!ok) break;
+          uint8_t* sa = smem + stage * F_STAGE_BYTES;
+          uint8_t* sb = sa + F_TILE_BYTES;
+          uint8_t* ssa = sb + F_TILE_BYTES;
+          uint8_t* ssb = ssa + F_SF_BYTES;
+          mbar_arrive_expect_tx(&bar_full[stage], F_STAGE_BYTES);
+          // x counts 16-bit words: 64 per stage
+          tma_load_2d_hint(sa, &tmap_a, &bar_full[stage], kb * 64, tm * FM, pol);
+          tma_load_2d_hint(sb, &tmap_b, &bar_full[stage], kb * 64, tn * FN, pol);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const size_t ka = (size_t)(kb * 4 + q);
+            bulk_g2s(ssa + q * 512, p.sfa + ((size_t)tm + ka * p.sfa_m_atoms) * 512, 512, &bar_full[stage]);
+            bulk_g2s(ssb + q * 512, p.sfb + ((size_t)tn + ka * p.sfb_m_atoms) * 512, 512, &bar_full[stage]);
+          }
+          outstanding |= 1u << stage;
+          issue_phase_bits = (issue_phase_bits & ~(1u << stage)) | (phase << stage);
+          if (++stage == F_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (*s_abort) {
+        for (int s = 0; s < F_STAGES; ++s) {
+          if (outstanding & (1u << s)) {
+            const uint32_t par = (issue_phase_bits >> s) & 1u;
+            for (int it = 0; it < (1 << 20); ++it)
+              if (mbar_try_wait(&bar_full[s], par)) break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_nvf4(FM, FN);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      pdl_wait(TL_GEMM_QUANT);
+      for (int t = blockIdx.x; ok && t < tiles; t += gridDim.x) {
+        ok = mbar_wait(&bar_tempty[acc], acc_phase ^ 1, s_abort, 200 + acc);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * FN);
+        for (int kb = 0; kb < p.kblocks; ++kb) {
+          ok = mbar_wait(&bar_full[stage], phase, s_abort, 300 + stage);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * F_STAGE_BYTES);
+          const uint32_t ssa = sa + 2 * F_TILE_BYTES, ssb = ssa + F_SF_BYTES;
+          const uint64_t adesc = umma_desc_kmajor_sw128(sa), bdesc = umma_desc_kmajor_sw128(sa + F_TILE_BYTES);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            tmem_cp_sf(tmem_base + F_SFA_COL + 4 * q, sf_desc(ssa + q * 512));
+            tmem_cp_sf(tmem_base + F_SFB_COL + 4 * q, sf_desc(ssb + q * 512));
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            // 64 codes = 32 bytes along K inside the 128-byte swizzle atom: +2 in 16-byte units
+            umma_nvf4(tmem_d, adesc + (uint64_t)(2 * q), bdesc + (uint64_t)(2 * q), idesc, (kb > 0 || q > 0) ? 1u : 0u,
+                      tmem_base + F_SFA_COL + 4 * q, tmem_base + F_SFB_COL + 4 * q);
+          }
+          umma_commit(&bar_empty[stage]);
+          if (++stage == F_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&bar_tfull[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    pdl_wait();
+    const float alpha = __ldg(p.a_scale) * p.w_scale;
+    for (int t = blockIdx.x; ok && t < tiles; t += gridDim.x) {
+      const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+      ok = mbar_wait(&bar_tfull[acc], acc_phase, s_abort, 400 + acc);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * FN);
+      const int row = tm * FM + row_in_tile;
+#pragma unroll 1
+      for (int ch = 0; ch < FN / 16; ++ch) {
+        float v[16];
+        tmem_ld_32x32b_x16(taddr + ch * 16, v);
+        const int col0 = tn * FN + ch * 16;
+        if (row < p.T && col0 < p.N) {
+          uint32_t o[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            float x0 = v[2 * e] * alpha, x1 = v[2 * e + 1] * alpha;
+            if (p.bias) {
+              x0 += __bfloat162float(p.bias[col0 + 2 * e]);
+              x1 += __bfloat162float(p.bias[col0 + 2 * e + 1]);
+            }
+            __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+            o[e] = *reinterpret_cast<uint32_t*>(&h);
+          }
+          uint4* dst = reinterpret_cast<uint4*>(p.out + (size_t)row * p.ldd + col0);
+          dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+          dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_tempty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, F_TMEM_COLS);
+  }
+}
+
+}  // namespace
+}  // namespace swb
+
+extern "C" {
+
+// D[T, N] (bf16, ldd) = a_scale[0] * w_scale * (Aq . Wq^T) + bias. Aq: [T, K / 2] code bytes; Wq: [N, K / 2]; sfa / sfb:
+// scale atoms covering ceil(T / 128) / ceil(N / 128) row atoms x K / 64 column atoms; K % 256 == 0, N % 16 == 0,
+// 16-byte aligned operands, ldd % 8 == 0.
+int swb_gemm_nvfp4_w4a4(const void* Aq, const void* sfa, const void* a_scale, const void* Wq, const void* sfb, float w_scale,
+                        void* D, int ldd, int T, int N, int K, const void* bias, void* stream) {
+  using namespace swb;
+  if (T <= 0 || N <= 0) return 0;
+  auto mis = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) != 0; };
+  if (K <= 0 || K % FK != 0 || N % 16 != 0 || ldd % 8 != 0 || mis(Aq) || mis(Wq) || mis(sfa) || mis(sfb) || mis(D) || !a_scale)
+    return -3;
+  FParams p{};
+  p.sfa = reinterpret_cast<const uint8_t*>(sfa);
+  p.sfb = reinterpret_cast<const uint8_t*>(sfb);
+  p.sfa_m_atoms = (T + 127) / 128;
+  p.sfb_m_atoms = (N + 127) / 128;
+  p.a_scale = reinterpret_cast<const float*>(a_scale);
+  p.w_scale = w_scale;
+  p.bias = reinterpret_cast<const bf16*>(bias);
+  p.out = reinterpret_cast<bf16*>(D);
+  p.ldd = ldd;
+  p.T = T;
+  p.N = N;
+  p.kblocks = K / FK;
+  p.tiles_m = (T + FM - 1) / FM;
+  p.tiles_n = (N + FN - 1) / FN;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_u16_2d(&ta, Aq, K / 4, T, K / 2, 64, FM, 1);
+  if (rc) return rc;
+  rc = make_tmap_u16_2d(&tb, Wq, K / 4, N, K / 2, 64, FN, 1);
+  if (rc) return rc;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F_SMEM);
+    if (e != cudaSuccess) return -(int)e;
+    configured[dev] = true;
+  }
+  const int grid = std::min(device_sm_count(), p.tiles_m * p.tiles_n);
+  return launch_kernel(gemm_nvfp4_kernel, dim3(grid), dim3(F_THREADS), F_SMEM, reinterpret_cast<cudaStream_t>(stream), ta, tb, p);
+}
+
+}  // extern "C"

@@ -144,6 +144,51 @@ class Nvfp4Tensor:
         return self.packed.numel() + self.scales.numel() + 4
 
 
+def quantize_device_raw(x: torch.Tensor):
+    """The device packer without any host synchronisation: (codes uint8 [rows, cols / 2], scale atoms uint8, tensor
+    scale as a one-element device tensor). cols must be a multiple of 16."""
+    from .._native import kernels
+    from .runtime import check, stream_ptr
+
+    assert x.is_cuda and x.dim() == 2 and x.dtype in (torch.float32, torch.bfloat16) and x.stride(1) == 1
+    rows, cols = x.shape
+    assert cols % BLOCK == 0
+    nb = cols // BLOCK
+    sf_rows, sf_cols = _round_up(rows, SF_ATOM_ROWS), _round_up(nb, SF_ATOM_COLS)
+    dev = x.device
+    packed = torch.empty((rows, cols // 2), dtype=torch.uint8, device=dev)
+    scales = torch.zeros(sf_rows * sf_cols, dtype=torch.uint8, device=dev)
+    block_amax = torch.empty(rows * nb, dtype=torch.float32, device=dev)
+    tmax = torch.zeros(1, dtype=torch.int32, device=dev)
+    gs = torch.empty(1, dtype=torch.float32, device=dev)
+    check(kernels().swb_nvfp4_quantize(x.data_ptr(), 1 if x.dtype == torch.float32 else 0, x.stride(0), rows, cols,
+                                       packed.data_ptr(), scales.data_ptr(), sf_rows, block_amax.data_ptr(),
+                                       tmax.data_ptr(), gs.data_ptr(), stream_ptr()), "swb_nvfp4_quantize")
+    return packed, scales, gs
+
+
+def gemm_w4a4(x: torch.Tensor, w: "Nvfp4Tensor", bias: torch.Tensor | None = None) -> torch.Tensor:
+    """x [T, K] (bf16 / fp32, CUDA) times an NVFP4 weight [N, K] on the block-scaled FP4 tensor-core path: the
+    activations are packed to NVFP4 by the device quantiser, then one tcgen05 kind::mxf4nvf4 GEMM produces bf16 [T, N]."""
+    from .._native import kernels
+    from .runtime import check, ptr, stream_ptr
+
+    assert x.is_cuda and x.dim() == 2 and x.shape[1] == w.cols == w.cols_padded and w.cols % 256 == 0 and w.rows % 16 == 0
+    aq, sfa, gs = quantize_device_raw(x.contiguous())
+    T = x.shape[0]
+    out = torch.empty((T, w.rows), dtype=torch.bfloat16, device=x.device)
+    check(kernels().swb_gemm_nvfp4_w4a4(aq.data_ptr(), sfa.data_ptr(), gs.data_ptr(), w.packed.data_ptr(), w.scales.data_ptr(),
+                                        w.global_scale, out.data_ptr(), out.stride(0), T, w.rows, w.cols, ptr(bias),
+                                        stream_ptr()), "swb_gemm_nvfp4_w4a4")
+    return out
+
+
+def native_w4a4_enabled() -> bool:
+    import os
+
+    return os.environ.get("SWB_NVFP4_NATIVE", "1") != "0"
+
+
 def quantize_on_device(x: torch.Tensor) -> Nvfp4Tensor:
     """The packer as two device kernels (block amax + tensor amax, then scales / codes / swizzle); bit-identical
     to `Nvfp4Tensor.pack`. x: CUDA fp32 or bf16 [rows, cols] with cols a multiple of 16."""
@@ -280,7 +325,8 @@ class Nvfp4Partition:
 class Nvfp4Linear:
     """y = x W^T + b with W stored as NVFP4 (candle-gen/src/quant/nvfp4_linear.rs:463-800).
 
-    On a CUDA device: up to 64 token rows run the fused dequantise-and-multiply kernel; more rows expand the weight
+    On a CUDA device with `act_precision=W4A4` and more than 64 token rows, activations are packed to NVFP4 on the
+    device and the product runs on the block-scaled FP4 tensor-core kernel (`gemm_w4a4`). Otherwise: up to 64 token rows run the fused dequantise-and-multiply kernel; more rows expand the weight
     to bf16 once per call (or once for good with `keep_dense=True`) and run the dense tcgen05 GEMM. On the CPU the
     dequantised weight is multiplied in fp32 (the oracle). `act_precision=W4A4` rounds activations to the NVFP4
     grid before the multiply."""
@@ -329,9 +375,13 @@ class Nvfp4Linear:
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         lead = x.shape[:-1]
         x2 = x.reshape(-1, x.shape[-1])
+        t = self.t
+        if (self.act_precision is ActPrecision.W4A4 and t.packed.is_cuda and x2.shape[0] > 64 and t.rows % 16 == 0 and
+                x2.dtype in (torch.float32, torch.bfloat16) and native_w4a4_enabled()):
+            # both operands stay 4-bit all the way into the tensor core
+            return gemm_w4a4(x2, t, self.bias).to(x.dtype).reshape(*lead, t.rows)
         if self.act_precision is ActPrecision.W4A4:
             x2 = quantize_activations(x2)
-        t = self.t
         if not t.packed.is_cuda:
             y = x2.float() @ t.dequantize().t()
             if self.bias is not None:

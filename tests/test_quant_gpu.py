@@ -112,3 +112,26 @@ def test_nvfp4_device_quantiser_is_bit_identical_to_the_host_packer(rows, cols, 
     assert torch.equal(dev.scales.cpu(), host.scales)
     assert torch.equal(dev.packed.cpu(), host.packed)
     torch.testing.assert_close(nv.quantize_activations(x.cuda()).cpu().float(), host.dequantize().to(dtype).float())
+
+
+@pytest.mark.parametrize("T,N,K", [(128, 128, 256), (300, 400, 512), (1000, 272, 1024), (65, 4096, 3072)])
+def test_nvfp4_w4a4_tensor_core_gemm_matches_the_dequantised_product(T, N, K):
+    """Both operands 4-bit in the tensor core: the result equals the fp32 product of the two dequantised NVFP4
+    tensors (every partial product is exact in fp32; only the accumulation order differs)."""
+    from inference_b200 import ops
+    from inference_b200.ops import nvfp4 as nv
+
+    g = torch.Generator().manual_seed(T + N + K)
+    w = torch.randn(N, K, generator=g) * 0.05
+    x = (torch.randn(T, K, generator=g) * 0.7).bfloat16()
+    x[:, :16] *= 6.0                                              # one loud block per row: block scales matter
+    wq = nv.Nvfp4Tensor.pack(w).to("cuda")
+    bias = (torch.randn(N, generator=g) * 0.1).bfloat16().cuda()
+    out = nv.gemm_w4a4(x.cuda(), wq, bias)
+    ops.check_status()
+    xq = nv.Nvfp4Tensor.pack(x.float())
+    ref = xq.dequantize() @ wq.to("cpu").dequantize().t() + bias.float().cpu()
+    err = (out.float().cpu() - ref).abs().max().item()
+    assert err < 1e-2 * max(1.0, ref.abs().max().item()), err
+    lin = nv.Nvfp4Linear(wq, bias, act_precision=nv.ActPrecision.W4A4)
+    assert torch.equal(lin(x.cuda()), out)                       # the layer takes the same path above 64 rows
