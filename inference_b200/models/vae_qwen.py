@@ -214,3 +214,96 @@ class WanVaeDecoder:
             if up is not None:
                 h = self._upsample(h, f"decoder.up_blocks.{i}.upsamplers.0", temporal=i < 2)
         return self._conv(F.silu(self._norm(h, "decoder.norm_out")), "decoder.conv_out", 1)
+
+
+def random_wan_vae_encoder_weights(cfg: QwenVaeConfig, seed: int = 0, std: float = 0.05) -> dict[str, torch.Tensor]:
+    """Encoder + quant_conv tensors of the video autoencoder (diffusers spelling)."""
+    g = torch.Generator().manual_seed(seed + 211)
+    rn = lambda *s: torch.randn(*s, generator=g)      # noqa: E731
+    w: dict[str, torch.Tensor] = {}
+
+    def conv3(name, o, i, k):
+        w[name + ".weight"], w[name + ".bias"] = rn(o, i, k, k, k) * std, rn(o) * std
+
+    def res(p, cin, cout):
+        w[p + ".norm1.gamma"], w[p + ".norm2.gamma"] = 1.0 + rn(cin, 1, 1, 1) * 0.05, 1.0 + rn(cout, 1, 1, 1) * 0.05
+        conv3(p + ".conv1", cout, cin, 3)
+        conv3(p + ".conv2", cout, cout, 3)
+        if cin != cout:
+            conv3(p + ".conv_shortcut", cout, cin, 1)
+
+    b = cfg.base_dim
+    dims = [b * m for m in cfg.dim_mult]
+    conv3("encoder.conv_in", b, 3, 3)
+    idx, cin = 0, b
+    for s, d in enumerate(dims):
+        for j in range(cfg.num_res_blocks):
+            res(f"encoder.down_blocks.{idx}", cin if j == 0 else d, d)
+            idx += 1
+        cin = d
+        if s < len(dims) - 1:
+            p = f"encoder.down_blocks.{idx}"
+            w[p + ".resample.1.weight"], w[p + ".resample.1.bias"] = rn(d, d, 3, 3) * std, rn(d) * std
+            if s > 0:
+                w[p + ".time_conv.weight"], w[p + ".time_conv.bias"] = rn(d, d, 3, 1, 1) * std, rn(d) * std
+            idx += 1
+    top = dims[-1]
+    res("encoder.mid_block.resnets.0", top, top)
+    res("encoder.mid_block.resnets.1", top, top)
+    a = "encoder.mid_block.attentions.0"
+    w[a + ".norm.gamma"] = 1.0 + rn(top, 1, 1) * 0.05
+    w[a + ".to_qkv.weight"], w[a + ".to_qkv.bias"] = rn(3 * top, top, 1, 1) * std, rn(3 * top) * std
+    w[a + ".proj.weight"], w[a + ".proj.bias"] = rn(top, top, 1, 1) * std, rn(top) * std
+    w["encoder.norm_out.gamma"] = 1.0 + rn(top, 1, 1, 1) * 0.05
+    conv3("encoder.conv_out", 2 * cfg.z_dim, top, 3)
+    conv3("quant_conv", 2 * cfg.z_dim, 2 * cfg.z_dim, 1)
+    return w
+
+
+class WanVaeEncoder(WanVaeDecoder):
+    """Video encode of the causal 3-D autoencoder (parity: candle-gen-wan/src/vae16.rs:74-300,554-598): 1 + 4n frames
+    become 1 + n normalised latent frames (the posterior mean). Stages 1 and 2 halve the frame count of everything
+    after the first frame: frame 0 passes through untouched and a stride-2 three-tap temporal convolution runs over
+    the whole clip (the reference streams it in chunks of 1, 4, 4, ... frames with one cached frame, which is the same
+    convolution). Spatial downsampling is a stride-2 3x3 convolution padded by one row / column at the bottom / right."""
+
+    def __init__(self, cfg: QwenVaeConfig, weights: dict[str, torch.Tensor], dtype=torch.float32, device="cpu"):
+        self.cfg, self.dtype, self.device = cfg, dtype, torch.device(device)
+        self.w = {}
+        for k, v in weights.items():
+            if k.startswith(("encoder.", "quant_conv.")):
+                if k.endswith(".gamma"):
+                    v = v.reshape(1, -1, 1, 1, 1)
+                elif k.endswith(".weight") and v.dim() == 4:
+                    v = v[:, :, None]
+                self.w[k] = v.to(device=self.device, dtype=dtype).contiguous()
+        self.mean = torch.tensor(LATENTS_MEAN[: cfg.z_dim], device=self.device, dtype=torch.float32).view(1, -1, 1, 1, 1)
+        self.std = torch.tensor(LATENTS_STD[: cfg.z_dim], device=self.device, dtype=torch.float32).view(1, -1, 1, 1, 1)
+
+    @torch.no_grad()
+    def encode(self, video: torch.Tensor) -> torch.Tensor:
+        """[B, 3, 1 + 4n, H, W] in [-1, 1] -> normalised latents [B, 16, 1 + n, H / 8, W / 8] (fp32)."""
+        T = video.shape[2]
+        if (T - 1) % 4:
+            raise ValueError(f"the causal encoder consumes 1 + 4n frames (got {T})")
+        cfg = self.cfg
+        h = self._conv(video.to(self.device, self.dtype), "encoder.conv_in", 1)
+        idx, stages = 0, len(cfg.dim_mult)
+        for s in range(stages):
+            for _ in range(cfg.num_res_blocks):
+                h = self._res(h, f"encoder.down_blocks.{idx}")
+                idx += 1
+            if s < stages - 1:
+                p = f"encoder.down_blocks.{idx}"
+                h = F.conv3d(F.pad(h, (0, 1, 0, 1)), self.w[p + ".resample.1.weight"], self.w[p + ".resample.1.bias"],
+                             stride=(1, 2, 2))
+                if p + ".time_conv.weight" in self.w and h.shape[2] > 1:
+                    rest = F.conv3d(h, self.w[p + ".time_conv.weight"], self.w[p + ".time_conv.bias"], stride=(2, 1, 1))
+                    h = torch.cat([h[:, :, :1], rest], dim=2)
+                idx += 1
+        h = self._res(h, "encoder.mid_block.resnets.0")
+        h = self._attention(h, "encoder.mid_block.attentions.0")
+        h = self._res(h, "encoder.mid_block.resnets.1")
+        h = self._conv(F.silu(self._norm(h, "encoder.norm_out")), "encoder.conv_out", 1)
+        mu = self._conv(h, "quant_conv", 0)[:, : cfg.z_dim].float()
+        return (mu - self.mean) / self.std

@@ -185,3 +185,56 @@ def test_flow_unipc_integrator():
         return z
     fine = run(400, False)
     assert (run(10, True) - fine).abs().max() < (run(10, False) - fine).abs().max()
+
+
+def test_wan_vae_encoder_is_causal_and_streams():
+    """Encoding a prefix of the clip gives the prefix of the latents (what the reference's chunked streaming encode
+    relies on), the first latent frame depends on frame 0 only, and the frame count law 1 + 4n -> 1 + n holds."""
+    from inference_b200.models.vae_qwen import QwenVaeConfig, WanVaeEncoder, random_wan_vae_encoder_weights
+
+    cfg = QwenVaeConfig(base_dim=8, dim_mult=(1, 2, 2, 2), num_res_blocks=1)
+    enc = WanVaeEncoder(cfg, random_wan_vae_encoder_weights(cfg, seed=1, std=0.2))
+    v = torch.randn(1, 3, 9, 16, 24)
+    z = enc.encode(v)
+    assert z.shape == (1, 16, 3, 2, 3)
+    assert torch.allclose(enc.encode(v[:, :, :5]), z[:, :, :2], atol=1e-5)
+    assert torch.allclose(enc.encode(v[:, :, :1]), z[:, :, :1], atol=1e-5)
+    v2 = v.clone()
+    v2[:, :, 1:] += 1.0
+    z2 = enc.encode(v2)
+    assert torch.equal(z2[:, :, 0], z[:, :, 0]) and not torch.allclose(z2[:, :, 1], z[:, :, 1], atol=1e-4)
+    with pytest.raises(ValueError):
+        enc.encode(v[:, :, :6])
+
+
+def test_wan_i2v_provider(tmp_path):
+    from inference_b200.contracts.errors import InferenceError
+    from inference_b200.contracts.gen_core import GenerationRequest, LoadSpec
+    from inference_b200.contracts.gen_core.generator import Conditioning, ConditioningKind
+    from inference_b200.contracts.gen_core.media import Image
+    from inference_b200.media import provider_registry
+    from inference_b200.media.wan import I2V_14B, preprocess_i2v_image, write_synthetic_snapshot
+
+    assert (I2V_14B.boundary, I2V_14B.shift, I2V_14B.guidance_high, I2V_14B.guidance_low) == (0.9, 5.0, 3.5, 3.5)
+    # cover-fit: a 4x2 image onto 2x2 keeps the centre columns; values map to [-1, 1]
+    img = Image(4, 2, bytes([0, 0, 0, 255, 255, 255, 255, 255, 255, 0, 0, 0] * 2))
+    t = preprocess_i2v_image(img, 2, 2)
+    assert t.shape == (1, 3, 1, 2, 2) and torch.allclose(t, torch.ones_like(t))
+    snap = write_synthetic_snapshot(tmp_path / "wan_i2v", i2v=True)
+    reg = provider_registry("cpu")
+    assert {"cpu_wan2_2_t2v_14b", "cpu_wan2_2_i2v_14b"} <= set(reg.ids()) and reg.descriptor_conformance_errors() == []
+    gen = reg.load("cpu_wan2_2_i2v_14b", LoadSpec.from_dir(snap))
+    assert gen.descriptor().capabilities.accepts(ConditioningKind.REFERENCE)
+    g = torch.Generator().manual_seed(0)
+    ref = Image(48, 32, torch.randint(0, 255, (32 * 48 * 3,), generator=g, dtype=torch.uint8).numpy().tobytes())
+    req = dict(prompt="the fox turns its head", width=256, height=256, steps=2, seed=5, frames=5)
+    with pytest.raises(InferenceError):
+        gen.generate(GenerationRequest(**req))                               # no reference image
+    cond = [Conditioning(kind=ConditioningKind.REFERENCE, image=ref)]
+    out = gen.generate(GenerationRequest(**req, conditioning=cond))
+    assert len(out.video_frames) == 5 and out.fps == 16
+    ref2 = Image(48, 32, bytes(32 * 48 * 3))
+    other = gen.generate(GenerationRequest(**req, conditioning=[Conditioning(kind=ConditioningKind.REFERENCE, image=ref2)]))
+    assert [f.pixels for f in other.video_frames] != [f.pixels for f in out.video_frames]
+    with pytest.raises(InferenceError):
+        gen.validate(GenerationRequest(**{**req, "width": 1280, "height": 1280}, conditioning=cond))
