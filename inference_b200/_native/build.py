@@ -62,7 +62,8 @@ def _compile_all(srcs: list[Path], headers: list[Path], compiler: list[str], tag
 
 def build_kernels(force: bool = False, verbose_ptxas: bool = False) -> Path:
     srcs = sorted((CSRC / "kernels").glob("*.cu"))
-    headers = sorted((CSRC / "kernels").glob("*.cuh")) + sorted((CSRC / "include").glob("*.h"))
+    headers = (sorted((CSRC / "kernels").glob("*.cuh")) + sorted((CSRC / "kernels").glob("*.h")) +
+               sorted((CSRC / "include").glob("*.h")))
     flags = list(NVCC_FLAGS)
     if verbose_ptxas:
         flags += ["-Xptxas", "-v"]

@@ -52,11 +52,12 @@ __global__ void __launch_bounds__(1024) argmax_static_kernel(const T* __restrict
   float* part_val = reinterpret_cast<float*>(scratch + OFF_VALS);
   long long* part_idx = reinterpret_cast<long long*>(scratch + OFF_IDX);
   const int row = blockIdx.x, chunks = gridDim.y;
-  const int per = (V + chunks - 1) / chunks;
-  const int v0 = min(V, (int)blockIdx.y * per), v1 = min(V, v0 + per);
+  // 64-bit index arithmetic: V may be anywhere up to INT_MAX
+  const long long per = ((long long)V + chunks - 1) / chunks;
+  const long long v0 = min((long long)V, (long long)blockIdx.y * per), v1 = min((long long)V, v0 + per);
   const T* x = logits + (size_t)row * ld;
   Best best{-INFINITY, (long long)V};
-  for (int i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
+  for (long long i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
     if (allow && !allow[i]) continue;
     const float v = as_float<T>(x[i]);
     if (v != v) continue;

@@ -28,6 +28,14 @@
  * the previous call left in its chunk slots; that is harmless because a call writes every slot before it reads it.
  * The arrival counters must be zero when a call starts: they are zero when the library is loaded and every call
  * puts them back to zero before it ends, so the caller never clears anything.
+ *
+ * After a failure: a launch that does not run to completion (a sticky device fault in this or an earlier kernel, the
+ * context torn down under it) can leave arrival counters non-zero, and nothing in this interface clears them; the
+ * device is then only usable again from a new process (a fresh load of the library image zeroes the array).
+ * cudaDeviceReset() destroys the array whose address was remembered on the first call: after it, do not call this
+ * function on that device again in the same process.
+ *
+ * V may be any value from 1 to INT_MAX (index arithmetic is 64-bit).
  */
 #ifndef SWB_ARGMAX_STATIC_H_
 #define SWB_ARGMAX_STATIC_H_

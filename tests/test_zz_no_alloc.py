@@ -48,6 +48,20 @@ def test_matches_existing_entry_point_twice(rows, V, dtype):
         assert torch.allclose(vals, logits.float().gather(1, ref[:, None])[:, 0], rtol=0, atol=0)
 
 
+@pytest.mark.parametrize("rows,V,dtype", [(3, 128256, torch.float32), (40, 50000, torch.float32), (2, 777, torch.float32)])
+def test_matches_torch_argmax_on_tie_free_rows(rows, V, dtype):
+    """An independent oracle: distinct values per row (a shuffled ramp), so torch.argmax has one right answer."""
+    fn = _symbol()
+    g = torch.Generator(device="cuda").manual_seed(V + rows)
+    ramp = torch.arange(V, device="cuda", dtype=torch.float32) * 1e-3 - 20.0
+    logits = torch.stack([ramp[torch.randperm(V, generator=g, device="cuda")] for _ in range(rows)]).to(dtype)
+    rc, ids, vals = _call(fn, logits, want_vals=True)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.equal(ids, torch.argmax(logits, dim=-1))
+    assert torch.equal(vals, logits.max(dim=-1).values.float())
+
+
 def test_allow_mask_and_strided_rows():
     from inference_b200 import ops
 
