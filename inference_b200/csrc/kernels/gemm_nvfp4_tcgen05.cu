@@ -6,8 +6,9 @@
 // device: it was produced by the quantiser that ran just before). The reference reaches this regime through
 // cuBLASLt's FP4 matmul (candle-gen/src/quant/nvfp4_linear.rs, W4A4 lane); here it is one kernel:
 //
-//   warp 0   one thread: per stage two TMA tiles (128 rows x 256 K = 128 bytes per row, 128-byte swizzle) and eight
-//            512-byte bulk copies of scale atoms, all completing on the stage's mbarrier
+//   warp 0   one thread: per stage two TMA tiles (128 rows x 256 K = 128 bytes per row, 128-byte swizzle) and two 3-D TMA
+//            boxes of four scale atoms each (the atoms of one row-atom are strided in memory), all completing on the
+//            stage's mbarrier
 //   warp 1   one thread: per stage 8 tcgen05.cp (scale atoms -> tensor memory, the 32-lane x 128-bit shape replicated
 //            to the four lane quarters) and 4 tcgen05.mma.kind::mxf4nvf4.block_scale (M 128, N 128, K 64 each) into one
 //            of two 128-column fp32 accumulators; tcgen05.commit releases the stage / hands the accumulator over
@@ -38,9 +39,6 @@ constexpr uint32_t F_TMEM_COLS = 512;
 constexpr uint32_t F_SFA_COL = 256, F_SFB_COL = 272;  // after the two 128-column accumulators
 
 struct FParams {
-  const uint8_t* sfa;     // activation scale atoms
-  const uint8_t* sfb;     // weight scale atoms
-  int sfa_m_atoms, sfb_m_atoms;
   const float* a_scale;   // device: activation tensor scale
   float w_scale;
   const bf16* bias;
@@ -48,11 +46,6 @@ struct FParams {
   int ldd, T, N, kblocks, tiles_m, tiles_n;
 };
 
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
-}
 // 32 rows x 16 bytes, rows contiguous: 8-row core matrices 128 bytes apart, no swizzle
 __device__ __forceinline__ uint64_t sf_desc(uint32_t smem_addr) {
   uint64_t d = 0;
@@ -79,7 +72,8 @@ __device__ __forceinline__ void umma_nvf4(uint32_t tmem_d, uint64_t adesc, uint6
 }
 
 __global__ void __launch_bounds__(F_THREADS, 1)
-gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const FParams p) {
+gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                  const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb, const FParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -104,6 +98,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(&tmap_sfa);
+    tma_prefetch_desc(&tmap_sfb);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, F_TMEM_COLS);
@@ -136,12 +132,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           // x counts 16-bit words: 64 per stage
           tma_load_2d_hint(sa, &tmap_a, &bar_full[stage], kb * 64, tm * FM, pol);
           tma_load_2d_hint(sb, &tmap_b, &bar_full[stage], kb * 64, tn * FN, pol);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const size_t ka = (size_t)(kb * 4 + q);
-            bulk_g2s(ssa + q * 512, p.sfa + ((size_t)tm + ka * p.sfa_m_atoms) * 512, 512, &bar_full[stage]);
-            bulk_g2s(ssb + q * 512, p.sfb + ((size_t)tn + ka * p.sfb_m_atoms) * 512, 512, &bar_full[stage]);
-          }
+          // scale atoms: [k atom][row atom][128 words]; box = 128 words x 1 row atom x 4 k atoms
+          tma_load_3d(ssa, &tmap_sfa, &bar_full[stage], 0, tm, kb * 4);
+          tma_load_3d(ssb, &tmap_sfb, &bar_full[stage], 0, tn, kb * 4);
           outstanding |= 1u << stage;
           issue_phase_bits = (issue_phase_bits & ~(1u << stage)) | (phase << stage);
           if (++stage == F_STAGES) {
@@ -271,10 +264,6 @@ int swb_gemm_nvfp4_w4a4(const void* Aq, const void* sfa, const void* a_scale, co
   if (K <= 0 || K % FK != 0 || N % 16 != 0 || ldd % 8 != 0 || mis(Aq) || mis(Wq) || mis(sfa) || mis(sfb) || mis(D) || !a_scale)
     return -3;
   FParams p{};
-  p.sfa = reinterpret_cast<const uint8_t*>(sfa);
-  p.sfb = reinterpret_cast<const uint8_t*>(sfb);
-  p.sfa_m_atoms = (T + 127) / 128;
-  p.sfb_m_atoms = (N + 127) / 128;
   p.a_scale = reinterpret_cast<const float*>(a_scale);
   p.w_scale = w_scale;
   p.bias = reinterpret_cast<const bf16*>(bias);
@@ -290,6 +279,17 @@ int swb_gemm_nvfp4_w4a4(const void* Aq, const void* sfa, const void* a_scale, co
   if (rc) return rc;
   rc = make_tmap_u16_2d(&tb, Wq, K / 4, N, K / 2, 64, FN, 1);
   if (rc) return rc;
+  CUtensorMap tsa, tsb;
+  const unsigned box[3] = {128u, 1u, 4u};
+  {
+    const unsigned long long ma = (unsigned long long)(T + 127) / 128, mb = (unsigned long long)(N + 127) / 128;
+    const unsigned long long da[3] = {128ull, ma, (unsigned long long)K / 64}, db[3] = {128ull, mb, (unsigned long long)K / 64};
+    const unsigned long long sa[2] = {512ull, 512ull * ma}, sb[2] = {512ull, 512ull * mb};
+    rc = make_tmap_u32_3d(&tsa, sfa, da, sa, box);
+    if (rc) return rc;
+    rc = make_tmap_u32_3d(&tsb, sfb, db, sb, box);
+    if (rc) return rc;
+  }
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -299,7 +299,8 @@ int swb_gemm_nvfp4_w4a4(const void* Aq, const void* sfa, const void* a_scale, co
     configured[dev] = true;
   }
   const int grid = std::min(device_sm_count(), p.tiles_m * p.tiles_n);
-  return launch_kernel(gemm_nvfp4_kernel, dim3(grid), dim3(F_THREADS), F_SMEM, reinterpret_cast<cudaStream_t>(stream), ta, tb, p);
+  return launch_kernel(gemm_nvfp4_kernel, dim3(grid), dim3(F_THREADS), F_SMEM, reinterpret_cast<cudaStream_t>(stream), ta, tb, tsa,
+                       tsb, p);
 }
 
 }  // extern "C"

@@ -651,6 +651,20 @@ int make_tmap_u16_2d(CUtensorMap* out, const void* ptr, long long cols, long lon
   return 0;
 }
 
+// Uncached 3-D map over 32-bit words, no swizzle: dims / box innermost first, strides in bytes for dims 1 and 2.
+int make_tmap_u32_3d(CUtensorMap* out, const void* ptr, const unsigned long long dims[3], const unsigned long long strides[2],
+                     const unsigned box[3]) {
+  auto encode = get_encode_fn();
+  if (!encode) return -1;
+  cuuint64_t d[3] = {dims[0], dims[1], dims[2]};
+  cuuint64_t st[2] = {strides[0], strides[1]};
+  cuuint32_t b[3] = {box[0], box[1], box[2]};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(ptr), d, st, b, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -(int)r - 1000;
+}
+
 int device_sm_count() {
   static int sms[64] = {0};
   int dev = 0;

@@ -134,6 +134,8 @@ int gemm_bf16_gated_supported(int T, int N, int K);
 int gemm_decode_cluster_supported(int T);
 int gemm_decode_cluster_launch(const GemmArgs& a, int force_cluster, cudaStream_t stream);
 int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows);
+int make_tmap_u32_3d(CUtensorMap* out, const void* ptr, const unsigned long long dims[3], const unsigned long long strides[2],
+                     const unsigned box[3]);
 int make_tmap_u16_2d(CUtensorMap* out, const void* ptr, long long cols, long long rows, long long row_pitch_bytes,
                      int box_cols, int box_rows, int swizzle128);
 int device_sm_count();

@@ -19,6 +19,39 @@ __device__ __forceinline__ float load_elem(const void* x, size_t i) {
   return __bfloat162float(reinterpret_cast<const bf16*>(x)[i]);
 }
 
+// 16 consecutive elements of a block as floats; 16-byte vector loads when the block's address allows them
+template <bool FP32>
+__device__ __forceinline__ void load_block16(const void* x, size_t i0, float* v) {
+  if constexpr (FP32) {
+    const float* p = reinterpret_cast<const float*>(x) + i0;
+    if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float4 f = reinterpret_cast<const float4*>(p)[c];
+        v[4 * c] = f.x, v[4 * c + 1] = f.y, v[4 * c + 2] = f.z, v[4 * c + 3] = f.w;
+      }
+      return;
+    }
+  } else {
+    const bf16* p = reinterpret_cast<const bf16*>(x) + i0;
+    if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const uint4 u = reinterpret_cast<const uint4*>(p)[c];
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          v[8 * c + 2 * e] = __uint_as_float(w[e] << 16);
+          v[8 * c + 2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u);
+        }
+      }
+      return;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 16; ++j) v[j] = load_elem<FP32>(x, i0 + j);
+}
+
 template <bool FP32>
 __global__ void __launch_bounds__(256) nvfp4_block_amax_kernel(const void* x, long long ld, int rows, int nb,
                                                               float* block_amax, unsigned int* tensor_amax_bits) {
@@ -28,8 +61,10 @@ __global__ void __launch_bounds__(256) nvfp4_block_amax_kernel(const void* x, lo
   float a = 0.f;
   if (i < (long long)rows * nb) {
     const int r = (int)(i / nb), b = (int)(i % nb);
+    float v[16];
+    load_block16<FP32>(x, (size_t)r * ld + b * 16, v);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) a = fmaxf(a, fabsf(load_elem<FP32>(x, (size_t)r * ld + b * 16 + j)));
+    for (int j = 0; j < 16; ++j) a = fmaxf(a, fabsf(v[j]));
     block_amax[i] = a;
   }
   // one atomic per warp
@@ -68,9 +103,11 @@ __global__ void __launch_bounds__(256) nvfp4_pack_kernel(const void* x, long lon
   scales[((size_t)(r >> 7) + (size_t)m_atoms * (b >> 2)) * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4 + (b & 3)] = sfb;
   const float es = __fmul_rn(e4m3_to_f32(sfb), gs);
   unsigned long long bits = 0ull;
+  float vals[16];
+  load_block16<FP32>(x, (size_t)r * ld + b * 16, vals);
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
-    const float v = load_elem<FP32>(x, (size_t)r * ld + b * 16 + j);
+    const float v = vals[j];
     const unsigned code = es > 0.f ? e2m1_code(__fdiv_rn(v, es)) : 0u;
     bits |= (unsigned long long)code << (4 * j);
   }

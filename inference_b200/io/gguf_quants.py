@@ -12,11 +12,14 @@ import numpy as np
 from ..contracts.errors import Unsupported
 
 GGML_TYPES = {0: "F32", 1: "F16", 2: "Q4_0", 3: "Q4_1", 6: "Q5_0", 7: "Q5_1", 8: "Q8_0", 10: "Q2_K", 11: "Q3_K",
-              12: "Q4_K", 13: "Q5_K", 14: "Q6_K", 24: "I8", 25: "I16", 26: "I32", 27: "I64", 28: "F64", 30: "BF16"}
+              12: "Q4_K", 13: "Q5_K", 14: "Q6_K", 20: "IQ4_NL", 23: "IQ4_XS", 24: "I8", 25: "I16", 26: "I32", 27: "I64", 28: "F64", 30: "BF16"}
 TYPE_IDS = {v: k for k, v in GGML_TYPES.items()}
 BLOCK = {"F32": (4, 1), "F16": (2, 1), "BF16": (2, 1), "F64": (8, 1), "I8": (1, 1), "I16": (2, 1), "I32": (4, 1),
          "I64": (8, 1), "Q4_0": (18, 32), "Q4_1": (20, 32), "Q5_0": (22, 32), "Q5_1": (24, 32), "Q8_0": (34, 32),
-         "Q2_K": (84, 256), "Q3_K": (110, 256), "Q4_K": (144, 256), "Q5_K": (176, 256), "Q6_K": (210, 256)}
+         "Q2_K": (84, 256), "Q3_K": (110, 256), "Q4_K": (144, 256), "Q5_K": (176, 256), "Q6_K": (210, 256),
+         "IQ4_NL": (18, 32), "IQ4_XS": (136, 256)}
+# the 16 non-uniform levels of the 4-bit "non-linear" formats (ggml's kvalues_iq4nl)
+IQ4_LEVELS = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], dtype=np.float32)
 
 
 def type_name(type_id: int) -> str:
@@ -91,6 +94,20 @@ def dequantize(raw: bytes | np.ndarray, tname: str, n_elements: int) -> np.ndarr
         h1 = ((qh >> (j + 16)) & 1).astype(np.uint8) << 4
         q = np.concatenate([(qs & 0x0F) | h0, (qs >> 4) | h1], axis=1).astype(np.float32)
         return ((q - 16.0) * d if tname == "Q5_0" else q * d + m).reshape(-1)
+    if tname == "IQ4_NL":                      # fp16 d + 16 bytes: low nibbles are weights 0..15, high nibbles 16..31
+        d = _f16(blk[:, 0:2]).reshape(nb, 1)
+        qs = blk[:, 2:18]
+        return (np.concatenate([IQ4_LEVELS[qs & 0x0F], IQ4_LEVELS[qs >> 4]], axis=1) * d).reshape(-1)
+    if tname == "IQ4_XS":                      # fp16 d, u16 high scale bits, 4 bytes of low scale nibbles, 8 x 16 bytes
+        d = _f16(blk[:, 0:2]).reshape(nb, 1)
+        sh = blk[:, 2:4].copy().view(np.uint16).reshape(nb, 1).astype(np.int32)
+        sl = blk[:, 4:8].astype(np.int32)
+        ib = np.arange(8)
+        ls = ((sl[:, ib // 2] >> (4 * (ib % 2))) & 0xF) | (((sh >> (2 * ib)) & 3) << 4)          # [nb, 8], 6 bits
+        dl = d * (ls - 32).astype(np.float32)
+        qs = blk[:, 8:136].reshape(nb, 8, 16)
+        vals = np.concatenate([IQ4_LEVELS[qs & 0x0F], IQ4_LEVELS[qs >> 4]], axis=2)              # [nb, 8, 32]
+        return (vals * dl[:, :, None]).reshape(-1)
     if tname == "Q4_K":
         d = _f16(blk[:, 0:2]).reshape(nb, 1, 1)
         dmin = _f16(blk[:, 2:4]).reshape(nb, 1, 1)
@@ -192,4 +209,41 @@ def quantize_q4_k(x: np.ndarray) -> np.ndarray:
     out[:, 4:16] = packed
     q = q.reshape(nb, 4, 2, 32)
     out[:, 16:144] = (q[:, :, 0, :] | (q[:, :, 1, :] << 4)).reshape(nb, 128)
+    return out.reshape(-1)
+
+
+def quantize_iq4_nl(x: np.ndarray) -> np.ndarray:
+    """float32 [n] (n % 32 == 0) -> IQ4_NL bytes: per block d = max-magnitude value / -127 (the largest level in
+    magnitude), each weight to the nearest level."""
+    b = np.asarray(x, dtype=np.float32).reshape(-1, 32)
+    idx = np.abs(b).argmax(axis=1)
+    vmax = b[np.arange(len(b)), idx]
+    d = (vmax / -127.0).astype(np.float16)
+    inv = np.where(d.astype(np.float32) != 0, 1.0 / np.where(d == 0, 1, d).astype(np.float32), 0.0)
+    q = np.abs((b * inv[:, None])[:, :, None] - IQ4_LEVELS[None, None, :]).argmin(axis=2).astype(np.uint8)
+    out = np.zeros((len(b), 18), dtype=np.uint8)
+    out[:, 0:2] = d.view(np.uint8).reshape(-1, 2)
+    out[:, 2:18] = q[:, :16] | (q[:, 16:] << 4)
+    return out.reshape(-1)
+
+
+def quantize_iq4_xs(x: np.ndarray) -> np.ndarray:
+    """float32 [n] (n % 256 == 0) -> IQ4_XS bytes: one fp16 d per 256 weights, a 6-bit scale (offset 32) per 32."""
+    b = np.asarray(x, dtype=np.float32).reshape(-1, 8, 32)
+    nb = len(b)
+    sub_max = np.abs(b).max(axis=2)                                   # [nb, 8]
+    d = (sub_max.max(axis=1) / (127.0 * 31.0)).astype(np.float16)     # largest sub-block gets scale 31
+    df = d.astype(np.float32)
+    ls = np.where(df[:, None] > 0, np.rint(sub_max / (127.0 * np.where(df == 0, 1, df))[:, None]), 0).clip(0, 31).astype(np.int32) + 32
+    dl = df[:, None] * (ls - 32)
+    inv = np.where(dl != 0, 1.0 / np.where(dl == 0, 1, dl), 0.0)
+    q = np.abs((b * inv[:, :, None])[..., None] - IQ4_LEVELS).argmin(axis=3).astype(np.uint8)      # [nb, 8, 32]
+    out = np.zeros((nb, 136), dtype=np.uint8)
+    out[:, 0:2] = d.view(np.uint8).reshape(-1, 2)
+    sh = np.zeros(nb, dtype=np.uint16)
+    for i in range(8):
+        sh |= ((ls[:, i] >> 4) & 3).astype(np.uint16) << (2 * i)
+        out[:, 4 + i // 2] |= ((ls[:, i] & 0xF) << (4 * (i % 2))).astype(np.uint8)
+    out[:, 2:4] = sh.view(np.uint8).reshape(-1, 2)
+    out[:, 8:136] = (q[:, :, :16] | (q[:, :, 16:] << 4)).reshape(nb, 128)
     return out.reshape(-1)
