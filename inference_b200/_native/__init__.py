@@ -110,6 +110,8 @@ def _declare_kernels(lib: ctypes.CDLL) -> None:
                            c_void_p, ctypes.c_size_t, c_int, c_void_p])
     sig("swb_gemm_nvfp4_w4a4", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int,
                                 c_void_p, c_void_p])
+    sig("swb_sample_device", [c_void_p, c_int, c_ll, c_int, c_int, c_float, c_int, c_float, c_void_p, c_void_p, c_void_p,
+                              c_void_p, c_void_p])
     sig("swb_argmax_peer_merge", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
     sig("swb_gemm_bf16_normed", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                  c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p])

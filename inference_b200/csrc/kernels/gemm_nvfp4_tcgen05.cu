@@ -28,15 +28,27 @@ SWB_REGISTER_STATUS_UNIT(gemm_nvfp4);
 
 namespace {
 
-constexpr int FM = 128, FN = 128, FK = 256;          // tile; FK elements = 128 bytes of codes per row
-constexpr int F_STAGES = 5;
+constexpr int FM = 128, FK = 256;                    // tile rows; FK elements = 128 bytes of codes per row
 constexpr int F_THREADS = 192;
-constexpr uint32_t F_TILE_BYTES = FM * (FK / 2);      // 16 KB per operand tile
-constexpr uint32_t F_SF_BYTES = 4 * 512;              // four scale atoms (K 256 = 4 x 64) per operand
-constexpr uint32_t F_STAGE_BYTES = 2 * F_TILE_BYTES + 2 * F_SF_BYTES;
-constexpr uint32_t F_SMEM = F_STAGES * F_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr uint32_t F_TMEM_COLS = 512;
-constexpr uint32_t F_SFA_COL = 256, F_SFB_COL = 272;  // after the two 128-column accumulators
+
+// FN = 128: two accumulators (the epilogue of a tile overlaps the next tile's main loop), 5 stages.
+// FN = 256: one 256-column accumulator (two would leave no tensor memory for the scales), 4 stages; each MMA does twice
+//           the work per A fetch and per scale copy.
+template <int FN>
+struct FCfg {
+  static constexpr int ACCS = FN == 128 ? 2 : 1;
+  static constexpr int STAGES = FN == 128 ? 5 : 4;
+  static constexpr int B_ATOMS = FN / 128;                         // scale atoms of the B tile per 64 K
+  static constexpr uint32_t A_BYTES = FM * (FK / 2);               // 16 KB
+  static constexpr uint32_t B_BYTES = FN * (FK / 2);
+  static constexpr uint32_t SFA_BYTES = 4 * 512;                   // four scale atoms (K 256 = 4 x 64)
+  static constexpr uint32_t SFB_BYTES = 4 * 512 * B_ATOMS;
+  static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+  static constexpr uint32_t SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr uint32_t SFA_COL = ACCS * FN;                   // scale columns follow the accumulators
+  static constexpr uint32_t SFB_COL = SFA_COL + 16;
+};
 
 struct FParams {
   const float* a_scale;   // device: activation tensor scale
@@ -71,9 +83,13 @@ __device__ __forceinline__ void umma_nvf4(uint32_t tmem_d, uint64_t adesc, uint6
       : "memory");
 }
 
+template <int FN>
 __global__ void __launch_bounds__(F_THREADS, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb, const FParams p) {
+  using Cfg = FCfg<FN>;
+  constexpr int F_STAGES = Cfg::STAGES;
+  constexpr uint32_t F_STAGE_BYTES = Cfg::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -125,16 +141,20 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           ok = mbar_wait(&bar_empty[stage], phase ^ 1, s_abort, 100 + stage);
           if (!ok) break;
           uint8_t* sa = smem + stage * F_STAGE_BYTES;
-          uint8_t* sb = sa + F_TILE_BYTES;
-          uint8_t* ssa = sb + F_TILE_BYTES;
-          uint8_t* ssb = ssa + F_SF_BYTES;
+          uint8_t* sb = sa + Cfg::A_BYTES;
+          uint8_t* ssa = sb + Cfg::B_BYTES;
+          uint8_t* ssb = ssa + Cfg::SFA_BYTES;
           mbar_arrive_expect_tx(&bar_full[stage], F_STAGE_BYTES);
-          // x counts 16-bit words: 64 per stage
+          // x counts 16-bit words: 64 per stage; the B tile arrives as 128-row boxes
           tma_load_2d_hint(sa, &tmap_a, &bar_full[stage], kb * 64, tm * FM, pol);
-          tma_load_2d_hint(sb, &tmap_b, &bar_full[stage], kb * 64, tn * FN, pol);
+#pragma unroll
+          for (int h = 0; h < Cfg::B_ATOMS; ++h)
+            tma_load_2d_hint(sb + h * Cfg::A_BYTES, &tmap_b, &bar_full[stage], kb * 64, tn * FN + h * 128, pol);
           // scale atoms: [k atom][row atom][128 words]; box = 128 words x 1 row atom x 4 k atoms
           tma_load_3d(ssa, &tmap_sfa, &bar_full[stage], 0, tm, kb * 4);
-          tma_load_3d(ssb, &tmap_sfb, &bar_full[stage], 0, tn, kb * 4);
+#pragma unroll
+          for (int h = 0; h < Cfg::B_ATOMS; ++h)
+            tma_load_3d(ssb + h * 2048, &tmap_sfb, &bar_full[stage], 0, tn * Cfg::B_ATOMS + h, kb * 4);
           outstanding |= 1u << stage;
           issue_phase_bits = (issue_phase_bits & ~(1u << stage)) | (phase << stage);
           if (++stage == F_STAGES) {
@@ -170,18 +190,20 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * F_STAGE_BYTES);
-          const uint32_t ssa = sa + 2 * F_TILE_BYTES, ssb = ssa + F_SF_BYTES;
-          const uint64_t adesc = umma_desc_kmajor_sw128(sa), bdesc = umma_desc_kmajor_sw128(sa + F_TILE_BYTES);
+          const uint32_t ssa = sa + Cfg::A_BYTES + Cfg::B_BYTES, ssb = ssa + Cfg::SFA_BYTES;
+          const uint64_t adesc = umma_desc_kmajor_sw128(sa), bdesc = umma_desc_kmajor_sw128(sa + Cfg::A_BYTES);
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            tmem_cp_sf(tmem_base + F_SFA_COL + 4 * q, sf_desc(ssa + q * 512));
-            tmem_cp_sf(tmem_base + F_SFB_COL + 4 * q, sf_desc(ssb + q * 512));
+            tmem_cp_sf(tmem_base + Cfg::SFA_COL + 4 * q, sf_desc(ssa + q * 512));
+#pragma unroll
+            for (int h = 0; h < Cfg::B_ATOMS; ++h)
+              tmem_cp_sf(tmem_base + Cfg::SFB_COL + (q * Cfg::B_ATOMS + h) * 4, sf_desc(ssb + h * 2048 + q * 512));
           }
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             // 64 codes = 32 bytes along K inside the 128-byte swizzle atom: +2 in 16-byte units
             umma_nvf4(tmem_d, adesc + (uint64_t)(2 * q), bdesc + (uint64_t)(2 * q), idesc, (kb > 0 || q > 0) ? 1u : 0u,
-                      tmem_base + F_SFA_COL + 4 * q, tmem_base + F_SFB_COL + 4 * q);
+                      tmem_base + Cfg::SFA_COL + 4 * q, tmem_base + Cfg::SFB_COL + 4 * q * Cfg::B_ATOMS);
           }
           umma_commit(&bar_empty[stage]);
           if (++stage == F_STAGES) {
@@ -191,8 +213,10 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         }
         if (!ok) break;
         umma_commit(&bar_tfull[acc]);
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1;
+        if (++acc == Cfg::ACCS) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
       }
     }
   } else {
@@ -235,8 +259,10 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar_tempty[acc]);
-      acc ^= 1;
-      if (acc == 0) acc_phase ^= 1;
+      if (++acc == Cfg::ACCS) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
     }
   }
 
@@ -272,12 +298,14 @@ int swb_gemm_nvfp4_w4a4(const void* Aq, const void* sfa, const void* a_scale, co
   p.T = T;
   p.N = N;
   p.kblocks = K / FK;
+  static const int forced_fn = [] { const char* e = getenv("SWB_NVFP4_FN"); return e ? atoi(e) : 0; }();
+  const int FN = forced_fn == 128 || forced_fn == 256 ? forced_fn : 128;
   p.tiles_m = (T + FM - 1) / FM;
   p.tiles_n = (N + FN - 1) / FN;
   CUtensorMap ta, tb;
   int rc = make_tmap_u16_2d(&ta, Aq, K / 4, T, K / 2, 64, FM, 1);
   if (rc) return rc;
-  rc = make_tmap_u16_2d(&tb, Wq, K / 4, N, K / 2, 64, FN, 1);
+  rc = make_tmap_u16_2d(&tb, Wq, K / 4, N, K / 2, 64, 128, 1);
   if (rc) return rc;
   CUtensorMap tsa, tsb;
   const unsigned box[3] = {128u, 1u, 4u};
@@ -290,17 +318,26 @@ int swb_gemm_nvfp4_w4a4(const void* Aq, const void* sfa, const void* a_scale, co
     rc = make_tmap_u32_3d(&tsb, sfb, db, sb, box);
     if (rc) return rc;
   }
-  static bool configured[64] = {false};
+  const int grid = std::min(device_sm_count(), p.tiles_m * p.tiles_n);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int dev = 0;
   cudaGetDevice(&dev);
+  if (FN == 256) {
+    static bool configured[64] = {false};
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FCfg<256>::SMEM);
+      if (e != cudaSuccess) return -(int)e;
+      configured[dev] = true;
+    }
+    return launch_kernel(gemm_nvfp4_kernel<256>, dim3(grid), dim3(F_THREADS), FCfg<256>::SMEM, st, ta, tb, tsa, tsb, p);
+  }
+  static bool configured[64] = {false};
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)F_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FCfg<128>::SMEM);
     if (e != cudaSuccess) return -(int)e;
     configured[dev] = true;
   }
-  const int grid = std::min(device_sm_count(), p.tiles_m * p.tiles_n);
-  return launch_kernel(gemm_nvfp4_kernel, dim3(grid), dim3(F_THREADS), F_SMEM, reinterpret_cast<cudaStream_t>(stream), ta, tb, tsa,
-                       tsb, p);
+  return launch_kernel(gemm_nvfp4_kernel<128>, dim3(grid), dim3(F_THREADS), FCfg<128>::SMEM, st, ta, tb, tsa, tsb, p);
 }
 
 }  // extern "C"

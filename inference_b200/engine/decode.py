@@ -28,6 +28,7 @@ class GenerationConfig:
     seed: int = 0
     stop_tokens: tuple[int, ...] = ()
     cancel: CancelFlag | None = None
+    device_sampling: bool | None = None      # None: on the device when several rows step together, else on the host
 
 
 @dataclass
@@ -105,6 +106,25 @@ def generate(backend: DecodeBackend, prompt: list[int], cfg: GenerationConfig, s
             backend.release(seq)
 
 
+def _device_sampling(cfg: GenerationConfig, logits: torch.Tensor, rows: int) -> bool:
+    """Stochastic rows are drawn on the device when the logits live there, no repetition penalty reshapes them and
+    either the request asked for it or more than one row steps together (the host sampler reproduces the reference's
+    token stream for a seed; the device sampler draws from the same distribution with its own index order, so single
+    sequences stay on the host path unless `device_sampling` is set)."""
+    sp = cfg.sampling
+    if not isinstance(logits, torch.Tensor) or not logits.is_cuda or sp.temperature <= 0.0 or sp.repetition_penalty != 1.0:
+        return False
+    want = getattr(cfg, "device_sampling", None)
+    return bool(want) if want is not None else rows > 1
+
+
+def ops_sample_device(logits, temperature, top_k, top_p, uniforms):
+    from .. import ops
+
+    l2 = logits if logits.dtype in (torch.float32, torch.bfloat16) else logits.float()
+    return ops.sample_device(l2.contiguous(), temperature, top_k, top_p, uniforms)
+
+
 def generate_batch(backend: DecodeBackend, prompts: list[list[int]], cfg: GenerationConfig) -> list[GenerationResult]:
     """Synchronous batched greedy/stochastic decode: one ragged prefill, then lock-step steps over the live rows
     (rows retire independently; no padding, no masks)."""
@@ -123,9 +143,15 @@ def generate_batch(backend: DecodeBackend, prompts: list[list[int]], cfg: Genera
                 toks = backend.forward_greedy([seqs[i] for i in live], new)
             else:
                 logits = backend.forward([seqs[i] for i in live], new)
-                # penalty window = prompt + generated (candle-llm/src/decode/batch.rs:133)
-                toks = [_pick(backend, logits[k], list(prompts[i]) + sched.generated(i), cfg, rngs[i], None)
-                        for k, i in enumerate(live)]
+                if _device_sampling(cfg, logits, len(live)):
+                    # one kernel for all rows; each row consumes one number of its own stream per step
+                    u = torch.tensor([rngs[i].next_f32() for i in live], dtype=torch.float32).to(logits.device, non_blocking=True)
+                    sp = cfg.sampling
+                    toks = [int(t) for t in ops_sample_device(logits, sp.temperature, sp.top_k, sp.top_p, u).tolist()]
+                else:
+                    # penalty window = prompt + generated (candle-llm/src/decode/batch.rs:133)
+                    toks = [_pick(backend, logits[k], list(prompts[i]) + sched.generated(i), cfg, rngs[i], None)
+                            for k, i in enumerate(live)]
             nxt, new = [], []
             for k, i in enumerate(live):
                 if sched.record(i, toks[k]) is None:

@@ -39,6 +39,17 @@ def lr_at(schedule: str, step: int, total: int, warmup: int, base: float) -> flo
     raise InferenceError(f"unknown lr_schedule {schedule!r} (constant | linear | cosine)")
 
 
+ADAPTER_KEYS = {2: ("lora_A.weight", "lora_B.weight"), 3: ("lokr_w1", "lokr_w2_a", "lokr_w2_b")}
+
+
+def kron_split(n: int) -> tuple[int, int]:
+    """(small, large) with small * large == n and small the largest divisor not above sqrt(n)."""
+    m = int(math.isqrt(n))
+    while n % m:
+        m -= 1
+    return m, n // m
+
+
 def lora_targets(weights: dict[str, torch.Tensor], suffixes: tuple[str, ...] = TARGET_SUFFIXES) -> list[str]:
     names = sorted({k[: -len(".weight")] for k in weights if k.endswith(".weight") and weights[k].dim() == 2})
     return [n for n in names if n.endswith(suffixes)]
@@ -74,11 +85,11 @@ class FluxLoraTrainer(Trainer):
 
     def descriptor(self) -> SimpleDescriptor:
         return SimpleDescriptor("flux1_lora_trainer" if self.backend != "cpu" else "cpu_flux1_lora_trainer", "flux",
-                                self.backend, {"adapters": ["lora"], "targets": list(TARGET_SUFFIXES)})
+                                self.backend, {"adapters": ["lora", "lokr"], "targets": list(TARGET_SUFFIXES)})
 
     def validate(self, c: TrainingConfig) -> None:
-        if c.adapter != "lora":
-            raise InferenceError(f"adapter kind {c.adapter!r} is not supported (lora)")
+        if c.adapter not in ("lora", "lokr"):
+            raise InferenceError(f"adapter kind {c.adapter!r} is not supported (lora, lokr)")
         if c.dataset_dir is None or not Path(c.dataset_dir).is_dir():
             raise InferenceError("dataset_dir must be an existing directory of cached items")
         if c.output_dir is None:
@@ -100,13 +111,24 @@ class FluxLoraTrainer(Trainer):
             items.append({k: v.float().to(self.device) for k, v in t.items()})
         return items
 
-    def _init_adapters(self, rank: int, gen: torch.Generator) -> dict[str, list[torch.Tensor]]:
+    def _init_adapters(self, rank: int, gen: torch.Generator, kind: str = "lora") -> dict[str, list[torch.Tensor]]:
+        """LoRA: [A [r, in] ~ N(0, 1 / in), B [out, r] = 0]. LoKr (candle-gen/src/train/lokr.rs; LyCORIS layout): the
+        delta is kron(w1 [a, c], w2_a [b, r] w2_b [r, d]) with out = a b, in = c d split at the divisor nearest the
+        square root (small factor first); w1 and w2_a start random, w2_b at zero, so training starts from the base."""
         ad = {}
         for name in lora_targets(self.model.w, self.target_suffixes):
             w = self.model.w[name + ".weight"]
-            a = (torch.randn(rank, w.shape[1], generator=gen) / math.sqrt(w.shape[1])).to(self.device).requires_grad_()
-            b = torch.zeros(w.shape[0], rank, device=self.device, requires_grad=True)
-            ad[name] = [a, b]
+            if kind == "lora":
+                a = (torch.randn(rank, w.shape[1], generator=gen) / math.sqrt(w.shape[1])).to(self.device).requires_grad_()
+                b = torch.zeros(w.shape[0], rank, device=self.device, requires_grad=True)
+                ad[name] = [a, b]
+                continue
+            (oa, ob), (ic, idd) = kron_split(w.shape[0]), kron_split(w.shape[1])
+            r = max(1, min(rank, ob, idd))
+            w1 = (torch.randn(oa, ic, generator=gen) / math.sqrt(ic)).to(self.device).requires_grad_()
+            w2a = (torch.randn(ob, r, generator=gen) / math.sqrt(r)).to(self.device).requires_grad_()
+            w2b = torch.zeros(r, idd, device=self.device, requires_grad=True)
+            ad[name] = [w1, w2a, w2b]
         return ad
 
     def loss_on(self, item, t: float, noise: torch.Tensor) -> torch.Tensor:
@@ -128,14 +150,14 @@ class FluxLoraTrainer(Trainer):
         out_dir.mkdir(parents=True, exist_ok=True)
         items = self._items(Path(c.dataset_dir))
         gen = torch.Generator().manual_seed(c.seed)
-        adapters = self._init_adapters(c.rank, gen)
+        adapters = self._init_adapters(c.rank, gen, c.adapter)
         params = [p for ab in adapters.values() for p in ab]
         opt = torch.optim.AdamW(params, lr=c.learning_rate, weight_decay=0.0)
         start = 0
         if c.resume is not None:
             start = self._load_checkpoint(Path(c.resume), adapters, opt, gen)
         scale = c.alpha / c.rank
-        self.model.lora = {n: (a, b, scale) for n, (a, b) in adapters.items()}
+        self.model.lora = {n: (*ts, (c.alpha / ts[1].shape[1]) if len(ts) == 3 else scale) for n, ts in adapters.items()}
         last = None
         try:
             for step in range(start, c.steps):
@@ -168,10 +190,13 @@ class FluxLoraTrainer(Trainer):
     # ---- checkpoints ---------------------------------------------------------------------------------------
     def _save(self, path: Path, adapters, c: TrainingConfig, step: int, opt, gen) -> Path:
         t = {}
-        for n, (a, b) in adapters.items():
-            t[f"transformer.{n}.lora_A.weight"] = a.detach().cpu().contiguous()
-            t[f"transformer.{n}.lora_B.weight"] = b.detach().cpu().contiguous()
-        save_file(t, path, metadata={"format": "peft-lora", "rank": str(c.rank), "alpha": str(c.alpha),
+        for n, ts in adapters.items():
+            for key, v in zip(ADAPTER_KEYS[len(ts)], ts):
+                t[f"transformer.{n}.{key}"] = v.detach().cpu().contiguous()
+            if len(ts) == 3:
+                t[f"transformer.{n}.alpha"] = torch.tensor(float(c.alpha))
+        fmt = "peft-lora" if c.adapter == "lora" else "lycoris-lokr"
+        save_file(t, path, metadata={"format": fmt, "rank": str(c.rank), "alpha": str(c.alpha),
                                      "step": str(step), "base": self.family})
         state = {"rng": gen.get_state()}
         for i, p in enumerate(opt.param_groups[0]["params"]):
@@ -190,9 +215,9 @@ class FluxLoraTrainer(Trainer):
         if not path.is_file():
             raise LoadError(f"resume checkpoint {path} not found")
         t = load_file(path)
-        for n, (a, b) in adapters.items():
-            a.data.copy_(t[f"transformer.{n}.lora_A.weight"])
-            b.data.copy_(t[f"transformer.{n}.lora_B.weight"])
+        for n, ts in adapters.items():
+            for key, v in zip(ADAPTER_KEYS[len(ts)], ts):
+                v.data.copy_(t[f"transformer.{n}.{key}"])
         sp = path.with_suffix(".state.safetensors")
         f = SafetensorsFile(sp)
         step = int(f.metadata.get("step", "0")) if hasattr(f, "metadata") else 0

@@ -17,6 +17,8 @@ from dataclasses import dataclass
 import torch
 import torch.nn.functional as F
 
+from .nn_dual import adapter_residual
+
 from .. import ops
 from ..parallel.comm import Communicator, single
 
@@ -129,8 +131,7 @@ class OracleFluxDiT:
     def _lin(self, x, name):
         y = F.linear(x, self.w[name + ".weight"], self.w[name + ".bias"])
         if self.lora is not None and name in self.lora:
-            a, b, scale = self.lora[name]
-            y = y + F.linear(F.linear(x, a), b) * scale
+            y = y + adapter_residual(self.lora[name], x)
         return y
 
     def _mlp_embed(self, x, name):

@@ -18,6 +18,8 @@ from dataclasses import dataclass, field
 import torch
 import torch.nn.functional as F
 
+from .nn_dual import adapter_residual
+
 from .dit_flux import timestep_embedding
 from .text_encoders import linear
 
@@ -136,8 +138,7 @@ class Sd3DiT:
     def _lin(self, x, name):
         y = linear(x, self.w[name + ".weight"], self.w.get(name + ".bias"))
         if self.lora is not None and name in self.lora:
-            a, b, scale = self.lora[name]
-            y = y + F.linear(F.linear(x, a), b) * scale
+            y = y + adapter_residual(self.lora[name], x)
         return y
 
     def _ln(self, x):

@@ -17,6 +17,8 @@ from dataclasses import dataclass
 import torch
 import torch.nn.functional as F
 
+from .nn_dual import adapter_residual
+
 from .dit_flux import rope_table, timestep_embedding
 from .text_encoders import linear
 
@@ -112,8 +114,7 @@ class WanDiT:
     def _lin(self, x, name):
         y = linear(x, self.w[name + ".weight"], self.w.get(name + ".bias"))
         if self.lora is not None and name in self.lora:
-            a, b, scale = self.lora[name]
-            y = y + F.linear(F.linear(x, a), b) * scale
+            y = y + adapter_residual(self.lora[name], x)
         return y
 
     def _ln(self, x):

@@ -19,6 +19,8 @@ from dataclasses import dataclass
 import torch
 import torch.nn.functional as F
 
+from .nn_dual import adapter_residual
+
 from .dit_flux import rope_table
 
 ADALN_DIM = 256
@@ -161,8 +163,7 @@ class OracleZImageDiT:
     def _lin(self, x, name):
         y = F.linear(x, self.w[name + ".weight"], self.w.get(name + ".bias"))
         if self.lora is not None and name in self.lora:
-            a, b, scale = self.lora[name]
-            y = y + F.linear(F.linear(x, a), b) * scale
+            y = y + adapter_residual(self.lora[name], x)
         return y
 
     def _rms(self, x, name, eps=None):

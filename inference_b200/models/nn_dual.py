@@ -138,6 +138,21 @@ def unpatchify(x: torch.Tensor, ht: int, wt: int, p: int, c: int) -> torch.Tenso
     return x.reshape(B, ht, wt, c, p, p).permute(0, 3, 1, 4, 2, 5).reshape(B, c, ht * p, wt * p)
 
 
+def adapter_residual(entry, x: torch.Tensor) -> torch.Tensor:
+    """The additive branch of a trainable adapter on a linear layer. entry = (A [r, in], B [out, r], scale): LoRA,
+    scale * B A x. entry = (w1 [a, c], w2_a [b, r], w2_b [r, d], scale): LoKr, scale * kron(w1, w2_a w2_b) x with
+    out = a b and in = c d, applied factor by factor (never forming the dense delta)."""
+    if len(entry) == 3:
+        a, b, scale = entry
+        return F.linear(F.linear(x, a), b) * scale
+    w1, w2a, w2b, scale = entry
+    (a, c), bd, d = w1.shape, w2a.shape[0], w2b.shape[1]
+    lead, n = x.shape[:-1], x.numel() // x.shape[-1]
+    t = (x.reshape(n * c, d) @ (w2a @ w2b).t().to(x.dtype)).reshape(n, c, bd)
+    y = w1.to(x.dtype).reshape(1, a, c) @ t
+    return y.reshape(*lead, a * bd) * scale
+
+
 class WeightBag:
     """A flat name -> tensor map moved to one device / dtype, with the lookups a functional model needs."""
 

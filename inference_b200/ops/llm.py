@@ -159,6 +159,25 @@ def argmax(logits: torch.Tensor, allow_mask: torch.Tensor | None = None, out: to
     return out
 
 
+def sample_device(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, uniforms: torch.Tensor,
+                  allow_mask: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                  out_prob: torch.Tensor | None = None) -> torch.Tensor:
+    """Row-wise draw from softmax(logits / temperature) restricted to the top_k largest weights and the top_p nucleus
+    (either limit off with top_k <= 0 / top_p >= 1), on the device. `uniforms`: fp32 [rows] in [0, 1), one per row.
+    Returns int64 [rows]; `out_prob` (fp32 [rows]) receives the drawn token's probability within the kept set."""
+    require_cuda(logits, uniforms)
+    l2 = logits.reshape(-1, logits.shape[-1])
+    assert l2.stride(1) == 1 and l2.dtype in (torch.float32, torch.bfloat16) and temperature > 0
+    assert uniforms.dtype == torch.float32 and uniforms.numel() == l2.shape[0]
+    if out is None:
+        out = torch.empty(l2.shape[0], dtype=torch.int64, device=logits.device)
+    rc = kernels().swb_sample_device(l2.data_ptr(), 1 if l2.dtype == torch.float32 else 0, l2.stride(0), l2.shape[0], l2.shape[1],
+                                     float(temperature), int(top_k), float(top_p), uniforms.data_ptr(), ptr(allow_mask),
+                                     out.data_ptr(), ptr(out_prob), stream_ptr())
+    check(rc, "swb_sample_device")
+    return out
+
+
 def spec_verify_greedy(target_ids: torch.Tensor, draft: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     """target_ids [S, k+1], draft [S, k] (int64) -> (n_accepted int32 [S], next_token int64 [S])."""
     require_cuda(target_ids, draft)

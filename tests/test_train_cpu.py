@@ -64,9 +64,43 @@ def test_training_reduces_loss_resumes_and_merges(dataset, tmp_path):
     assert all(torch.equal(ad[k], ad2[k]) for k in ad)
 
 
+def test_lokr_training_reduces_loss_and_its_file_folds_like_any_lokr(dataset, tmp_path):
+    """adapter="lokr": Kronecker-factored deltas (w1 (x) w2_a w2_b) train through the same loop; the saved LyCORIS-style
+    file, folded into the base by the generic adapter loader, reproduces the adapted model."""
+    from inference_b200.contracts.gen_core import AdapterKind, AdapterSpec
+    from inference_b200.media.family import fold_adapters
+    from inference_b200.media.train import kron_split
+    from inference_b200.models.nn_dual import adapter_residual
+
+    assert kron_split(128) == (8, 16) and kron_split(384) == (16, 24) and kron_split(13) == (1, 13)
+    g = torch.Generator().manual_seed(4)
+    w1, w2a, w2b, x = torch.randn(3, 2, generator=g), torch.randn(4, 2, generator=g), torch.randn(2, 5, generator=g), torch.randn(7, 10, generator=g)
+    dense = torch.kron(w1, w2a @ w2b)
+    assert torch.allclose(adapter_residual((w1, w2a, w2b, 0.5), x), x @ dense.t() * 0.5, atol=1e-5)
+    w = random_flux_weights(CFG, seed=1, std=0.05)
+    tr = FluxLoraTrainer(CFG, w)
+    items = tr._items(dataset)
+    noise = torch.randn(16, 8, 8, generator=torch.Generator().manual_seed(9))
+    before = float(tr.loss_on(items[0], 0.5, noise))
+    cfg = TrainingConfig(dataset_dir=dataset, output_dir=tmp_path / "lokr", steps=14, learning_rate=5e-3, rank=4, alpha=4.0,
+                         seed=3, adapter="lokr", save_every=7)
+    prog = []
+    final = tr.train(cfg, prog.append)
+    ad = load_file(final)
+    assert any(k.endswith(".lokr_w1") for k in ad) and any(k.endswith(".lokr_w2_b") for k in ad) and not any("lora_A" in k for k in ad)
+    merged = fold_adapters(w, [AdapterSpec(path=str(final), scale=1.0, kind=AdapterKind.LOKR)], "test")
+    after = float(FluxLoraTrainer(CFG, merged).loss_on(items[0], 0.5, noise))
+    assert after < before, (before, after)
+    # resume is exact for this adapter kind too
+    cfg2 = TrainingConfig(dataset_dir=dataset, output_dir=tmp_path / "lokr2", steps=14, learning_rate=5e-3, rank=4, alpha=4.0,
+                          seed=3, adapter="lokr", resume=tmp_path / "lokr" / "adapter-step000007.safetensors")
+    ad2 = load_file(FluxLoraTrainer(CFG, w).train(cfg2))
+    assert all(torch.equal(ad[k], ad2[k]) for k in ad)
+
+
 def test_validation_and_cancellation(dataset, tmp_path):
     tr = FluxLoraTrainer(CFG, random_flux_weights(CFG, seed=2, std=0.05))
-    for bad in (dict(adapter="lokr"), dict(steps=0), dict(dataset_dir=tmp_path / "missing"), dict(lr_schedule="zigzag"),
+    for bad in (dict(adapter="loha"), dict(steps=0), dict(dataset_dir=tmp_path / "missing"), dict(lr_schedule="zigzag"),
                 dict(batch_size=2)):
         kw = dict(dataset_dir=dataset, output_dir=tmp_path / "o", steps=2)
         kw.update(bad)
