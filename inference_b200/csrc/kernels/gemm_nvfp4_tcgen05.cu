@@ -12,8 +12,8 @@
 //   warp 1   one thread: per stage 8 tcgen05.cp (scale atoms -> tensor memory, the 32-lane x 128-bit shape replicated
 //            to the four lane quarters) and 4 tcgen05.mma.kind::mxf4nvf4.block_scale (M 128, N 128, K 64 each) into one
 //            of two 128-column fp32 accumulators; tcgen05.commit releases the stage / hands the accumulator over
-//   warps 2..5  epilogue: tcgen05.ld 16 columns at a time, * alpha + bias, bf16, 32-byte stores; overlaps the next
-//            tile's main loop through the second accumulator
+//   warps 2..9  epilogue: two warps per lane quarter, each half of the tile's columns: tcgen05.ld 16 columns at a time,
+//            * alpha + bias, bf16, 32-byte stores
 //
 // Persistent: one CTA per SM walks tiles (row-tile fastest, so concurrent CTAs share a weight tile in L2).
 // Every wait is bounded (mbar_wait): on timeout the CTA raises the status word, drains its copies and frees its TMEM.
@@ -29,7 +29,7 @@ SWB_REGISTER_STATUS_UNIT(gemm_nvfp4);
 namespace {
 
 constexpr int FM = 128, FK = 256;                    // tile rows; FK elements = 128 bytes of codes per row
-constexpr int F_THREADS = 192;
+constexpr int F_THREADS = 320;                        // TMA warp, MMA warp, 8 epilogue warps
 constexpr uint32_t F_TMEM_COLS = 512;
 
 // FN = 128: two accumulators (the epilogue of a tile overlaps the next tile's main loop), 5 stages.
@@ -108,7 +108,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&bar_tfull[a], 1);
-      mbar_init(&bar_tempty[a], 4);
+      mbar_init(&bar_tempty[a], 8);
     }
     *s_abort = 0;
     mbar_fence_init();
@@ -220,7 +220,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       }
     }
   } else {
-    const int quarter = warp & 3;
+    const int quarter = warp & 3;                   // the TMEM lane quarter this warp may read
+    const int col_half = (warp - 2) >> 2;           // two warps per quarter split the tile's columns
     const int row_in_tile = quarter * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -235,7 +236,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * FN);
       const int row = tm * FM + row_in_tile;
 #pragma unroll 1
-      for (int ch = 0; ch < FN / 16; ++ch) {
+      for (int ch = col_half * (FN / 32); ch < (col_half + 1) * (FN / 32); ++ch) {
         float v[16];
         tmem_ld_32x32b_x16(taddr + ch * 16, v);
         const int col0 = tn * FN + ch * 16;
@@ -299,7 +300,7 @@ int swb_gemm_nvfp4_w4a4(const void* Aq, const void* sfa, const void* a_scale, co
   p.N = N;
   p.kblocks = K / FK;
   static const int forced_fn = [] { const char* e = getenv("SWB_NVFP4_FN"); return e ? atoi(e) : 0; }();
-  const int FN = forced_fn == 128 || forced_fn == 256 ? forced_fn : 128;
+  const int FN = forced_fn == 128 || forced_fn == 256 ? forced_fn : ((N % 256 == 0 || N >= 2048) ? 256 : 128);
   p.tiles_m = (T + FM - 1) / FM;
   p.tiles_n = (N + FN - 1) / FN;
   CUtensorMap ta, tb;

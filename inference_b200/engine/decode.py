@@ -178,6 +178,7 @@ class ContinuousConfig:
     max_batch: int = 8
     block_size: int = 16
     exactness: BatchExactness = BatchExactness.THROUGHPUT
+    prefill_chunk: int = 0        # > 0: at most this many prompt tokens per step, in the same forward as the decode rows
 
 
 @dataclass
@@ -197,14 +198,17 @@ def generate_continuous(backend: DecodeBackend, requests: list[ContinuousRequest
     pending = [i for i in ids if sched.is_active(i)]
     lanes: dict[int, Any] = {}
     next_tok: dict[int, int] = {}
+    fed: dict[int, int] = {}          # chunked prefill: prompt tokens already fed per lane still in its prompt
     exact = ccfg.exactness is BatchExactness.EXACT
 
-    def step(group: list[int], new: list[list[int]]) -> None:
+    def step(group: list[int], new: list[list[int]], unfinished: frozenset | set = frozenset()) -> None:
         if exact:
             toks = [backend.forward_greedy([lanes[i]], [n])[0] for i, n in zip(group, new)]
         else:
             toks = backend.forward_greedy([lanes[i] for i in group], new)
         for i, t in zip(group, toks):
+            if i in unfinished:          # a prompt chunk that does not end the prompt: its logits predict nothing yet
+                continue
             why = sched.record(i, t)
             if why is None or why is FinishReason.LENGTH:
                 if sink is not None:
@@ -225,6 +229,30 @@ def generate_continuous(backend: DecodeBackend, requests: list[ContinuousRequest
                 i = pending.pop(0)
                 lanes[i] = backend.new_sequence()
                 admitted.append(i)
+            if ccfg.prefill_chunk > 0:
+                # chunked prefill: decode rows and a bounded slice of prompt tokens share one ragged forward, so a long
+                # prompt never stalls the running sequences for more than one chunk
+                for i in admitted:
+                    fed[i] = 0
+                group = [i for i in lanes if i in next_tok]
+                new = [[next_tok[i]] for i in group]
+                budget, unfinished = ccfg.prefill_chunk, set()
+                for i in [j for j in lanes if j in fed]:
+                    if budget <= 0:
+                        break
+                    prompt, s0 = requests[i].prompt, fed[i]
+                    n = min(budget, len(prompt) - s0)
+                    group.append(i)
+                    new.append(prompt[s0:s0 + n])
+                    budget -= n
+                    if s0 + n < len(prompt):
+                        fed[i] = s0 + n
+                        unfinished.add(i)
+                    else:
+                        del fed[i]
+                if group:
+                    step(group, new, unfinished)
+                continue
             if admitted:
                 step(admitted, [requests[i].prompt for i in admitted])
             live = [i for i in lanes if i in next_tok and i not in admitted]

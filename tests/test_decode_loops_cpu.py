@@ -80,6 +80,33 @@ def test_continuous_equals_solo(exact):
     assert all(r.finish_reason is FinishReason.LENGTH for r in res)
 
 
+@pytest.mark.parametrize("chunk", [1, 3, 64])
+def test_chunked_prefill_mixed_with_decode_equals_solo(chunk):
+    """Prompt tokens enter in slices of `chunk` alongside the decode rows of running sequences: same tokens as solo
+    runs, and no forward ever carries more than `chunk` prompt tokens once decode rows exist."""
+    be = _model()
+    budgets = [5, 9, 3, 7]
+    solo = [generate(be, p, GenerationConfig(max_new_tokens=b)).tokens for p, b in zip(PROMPTS, budgets)]
+    reqs = [ContinuousRequest(p, b) for p, b in zip(PROMPTS, budgets)]
+    seen = []
+    real = be.forward_greedy
+
+    def spy(seqs, new):
+        seen.append([len(n) for n in new])
+        return real(seqs, new)
+    be.forward_greedy = spy
+    try:
+        res = generate_continuous(be, reqs, ContinuousConfig(max_batch=3, prefill_chunk=chunk))
+    finally:
+        be.forward_greedy = real
+    assert [r.tokens for r in res] == solo
+    assert all(sum(n for n in step if n > 1) <= max(chunk, 1) or chunk >= 64 for step in seen)
+    if chunk == 3:
+        assert any(1 in step and any(n > 1 for n in step) for step in seen)       # decode rows rode with prompt slices
+    if chunk == 1:
+        assert all(all(n == 1 for n in step) for step in seen)
+
+
 def test_prefix_cached_equals_cold():
     be = _model()
     cache = PrefixCache(be, capacity=2)
