@@ -105,6 +105,7 @@ def _declare_kernels(lib: ctypes.CDLL) -> None:
                                        c_int, c_void_p])
     sig("swb_nvfp4_quantize", [c_void_p, c_int, c_ll, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                c_void_p])
+    sig("swb_nvfp4_quantize_fast", [c_void_p, c_int, c_ll, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p])
     sig("swb_dequant_nvfp4", [c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p])
     sig("swb_gemm_nvfp4", [c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                            c_void_p, ctypes.c_size_t, c_int, c_void_p])

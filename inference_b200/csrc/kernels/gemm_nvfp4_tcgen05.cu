@@ -12,8 +12,9 @@
 //   warp 1   one thread: per stage 8 tcgen05.cp (scale atoms -> tensor memory, the 32-lane x 128-bit shape replicated
 //            to the four lane quarters) and 4 tcgen05.mma.kind::mxf4nvf4.block_scale (M 128, N 128, K 64 each) into one
 //            of two 128-column fp32 accumulators; tcgen05.commit releases the stage / hands the accumulator over
-//   warps 2..9  epilogue: two warps per lane quarter, each half of the tile's columns: tcgen05.ld 16 columns at a time,
-//            * alpha + bias, bf16, 32-byte stores
+//   warps 2..17 epilogue: four warps per lane quarter, each a quarter of the tile's columns: the slice is read from
+//            tensor memory into registers in one go and the accumulator released at once; * alpha + bias, bf16 and
+//            32-byte stores then overlap the next tile's main loop
 //
 // Persistent: one CTA per SM walks tiles (row-tile fastest, so concurrent CTAs share a weight tile in L2).
 // Every wait is bounded (mbar_wait): on timeout the CTA raises the status word, drains its copies and frees its TMEM.
@@ -29,7 +30,8 @@ SWB_REGISTER_STATUS_UNIT(gemm_nvfp4);
 namespace {
 
 constexpr int FM = 128, FK = 256;                    // tile rows; FK elements = 128 bytes of codes per row
-constexpr int F_THREADS = 320;                        // TMA warp, MMA warp, 8 epilogue warps
+constexpr int F_EPI_WARPS = 16;                      // four per TMEM lane quarter
+constexpr int F_THREADS = 64 + 32 * F_EPI_WARPS;     // TMA warp, MMA warp, epilogue warps
 constexpr uint32_t F_TMEM_COLS = 512;
 
 // FN = 128: two accumulators (the epilogue of a tile overlaps the next tile's main loop), 5 stages.
@@ -108,7 +110,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&bar_tfull[a], 1);
-      mbar_init(&bar_tempty[a], 8);
+      mbar_init(&bar_tempty[a], F_EPI_WARPS);
     }
     *s_abort = 0;
     mbar_fence_init();
@@ -221,7 +223,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     }
   } else {
     const int quarter = warp & 3;                   // the TMEM lane quarter this warp may read
-    const int col_half = (warp - 2) >> 2;           // two warps per quarter split the tile's columns
+    const int part = (warp - 2) >> 2;               // which slice of the tile's columns (four warps per quarter)
+    constexpr int CHUNKS = FN / 16 / (F_EPI_WARPS / 4);   // 16-column chunks per warp: 4 (FN 256) or 2 (FN 128)
     const int row_in_tile = quarter * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -233,18 +236,33 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       ok = mbar_wait(&bar_tfull[acc], acc_phase, s_abort, 400 + acc);
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * FN);
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * FN) + (uint32_t)(part * CHUNKS * 16);
       const int row = tm * FM + row_in_tile;
-#pragma unroll 1
-      for (int ch = col_half * (FN / 32); ch < (col_half + 1) * (FN / 32); ++ch) {
-        float v[16];
-        tmem_ld_32x32b_x16(taddr + ch * 16, v);
-        const int col0 = tn * FN + ch * 16;
+      // the whole slice goes to registers first, so the accumulator is handed back after one TMEM read latency;
+      // scaling, conversion and the global stores then overlap the next tile's main loop
+      uint32_t r[CHUNKS][16];
+#pragma unroll
+      for (int ch = 0; ch < CHUNKS; ++ch) {
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+            : "=r"(r[ch][0]), "=r"(r[ch][1]), "=r"(r[ch][2]), "=r"(r[ch][3]), "=r"(r[ch][4]), "=r"(r[ch][5]), "=r"(r[ch][6]),
+              "=r"(r[ch][7]), "=r"(r[ch][8]), "=r"(r[ch][9]), "=r"(r[ch][10]), "=r"(r[ch][11]), "=r"(r[ch][12]), "=r"(r[ch][13]),
+              "=r"(r[ch][14]), "=r"(r[ch][15])
+            : "r"(taddr + ch * 16)
+            : "memory");
+      }
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_tempty[acc]);
+#pragma unroll
+      for (int ch = 0; ch < CHUNKS; ++ch) {
+        const int col0 = tn * FN + (part * CHUNKS + ch) * 16;
         if (row < p.T && col0 < p.N) {
           uint32_t o[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            float x0 = v[2 * e] * alpha, x1 = v[2 * e + 1] * alpha;
+            float x0 = __uint_as_float(r[ch][2 * e]) * alpha, x1 = __uint_as_float(r[ch][2 * e + 1]) * alpha;
             if (p.bias) {
               x0 += __bfloat162float(p.bias[col0 + 2 * e]);
               x1 += __bfloat162float(p.bias[col0 + 2 * e + 1]);
@@ -257,9 +275,6 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
         }
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bar_tempty[acc]);
       if (++acc == Cfg::ACCS) {
         acc = 0;
         acc_phase ^= 1;

@@ -157,13 +157,15 @@ def quantize_device_raw(x: torch.Tensor):
     sf_rows, sf_cols = _round_up(rows, SF_ATOM_ROWS), _round_up(nb, SF_ATOM_COLS)
     dev = x.device
     packed = torch.empty((rows, cols // 2), dtype=torch.uint8, device=dev)
-    scales = torch.zeros(sf_rows * sf_cols, dtype=torch.uint8, device=dev)
-    block_amax = torch.empty(rows * nb, dtype=torch.float32, device=dev)
-    tmax = torch.zeros(1, dtype=torch.int32, device=dev)
-    gs = torch.empty(1, dtype=torch.float32, device=dev)
-    check(kernels().swb_nvfp4_quantize(x.data_ptr(), 1 if x.dtype == torch.float32 else 0, x.stride(0), rows, cols,
-                                       packed.data_ptr(), scales.data_ptr(), sf_rows, block_amax.data_ptr(),
-                                       tmax.data_ptr(), gs.data_ptr(), stream_ptr()), "swb_nvfp4_quantize")
+    # padding rows / columns of the scale atoms must read as zero; an exactly tiled tensor writes every byte
+    alloc = torch.empty if (rows % SF_ATOM_ROWS == 0 and nb % SF_ATOM_COLS == 0) else torch.zeros
+    scales = alloc(sf_rows * sf_cols, dtype=torch.uint8, device=dev)
+    small = torch.zeros(2, dtype=torch.int32, device=dev)           # [tensor amax bits, tensor scale]
+    gs = small[1:].view(torch.float32)
+    # no per-block amax scratch: the packing kernel recomputes each block's maximum from the values it loads anyway
+    check(kernels().swb_nvfp4_quantize_fast(x.data_ptr(), 1 if x.dtype == torch.float32 else 0, x.stride(0), rows, cols,
+                                            packed.data_ptr(), scales.data_ptr(), sf_rows, small.data_ptr(), gs.data_ptr(),
+                                            stream_ptr()), "swb_nvfp4_quantize_fast")
     return packed, scales, gs
 
 
