@@ -132,8 +132,20 @@ class FaceDetection:
 
 
 class FaceEmbedder(abc.ABC):
+    """Face detection + identity embedding (gen-core/src/face.rs:40-61). Results are ordered largest face first."""
     @abc.abstractmethod
-    def detect(self, image: Image) -> list[FaceDetection]: ...
+    def detect(self, image: Image) -> list[FaceDetection]:
+        """Boxes and landmarks only (embeddings stay None): the cheap path."""
+
+    def analyze(self, image: Image) -> list[FaceDetection]:
+        """Every face with its raw embedding."""
+        raise NotImplementedError
+
+    def largest_face(self, image: Image) -> FaceDetection:
+        faces = self.analyze(image)
+        if not faces:
+            raise InferenceError("no face detected")
+        return faces[0]
 
 
 class ControlBranch(abc.ABC):
