@@ -91,6 +91,9 @@ def _openvoice_registration(backend: str) -> Registration:
 
 
 def register_providers(b: ProviderRegistryBuilder, backend: str) -> ProviderRegistryBuilder:
+    from . import kokoro
+
+    b.register_generators([kokoro.registration(backend)])
     b.register("transcriber", _whisper_registration(backend))
     b.register("voice_embedder", _chatterbox_ve_registration(backend))
     b.register("audio_embedder", _clap_registration(backend))
@@ -103,7 +106,9 @@ def provider_registry(backend: str = "b200") -> ProviderRegistry:
 
 
 def weight_licenses() -> list[WeightLicenseEntry]:
-    return [WeightLicenseEntry("whisper", WHISPER_LICENSE), WeightLicenseEntry("chatterbox_ve", CHATTERBOX_LICENSE),
+    from .kokoro import KOKORO_LICENSE
+
+    return [WeightLicenseEntry("kokoro_82m", KOKORO_LICENSE), WeightLicenseEntry("whisper", WHISPER_LICENSE), WeightLicenseEntry("chatterbox_ve", CHATTERBOX_LICENSE),
             WeightLicenseEntry("clap_htsat_unfused", CLAP_LICENSE), WeightLicenseEntry("openvoice_v2", OPENVOICE_LICENSE)]
 
 
@@ -114,4 +119,6 @@ def weight_licenses_manifest() -> str:
 def can_prepare(files: list[str]) -> bool:
     """A Whisper snapshot ships config.json, tokenizer.json and safetensors weights."""
     names = {f.rsplit("/", 1)[-1] for f in files}
+    if "config.json" in names and ("kokoro-v1_0.pth" in names or "kokoro.safetensors" in names):
+        return True                      # Kokoro snapshots carry no tokenizer.json: validated passthrough
     return "config.json" in names and "tokenizer.json" in names and any(n.endswith(".safetensors") for n in names)
