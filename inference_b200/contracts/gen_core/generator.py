@@ -40,6 +40,12 @@ class ConditioningKind(enum.Enum):
     AUDIO_EDIT = "audio_edit"
     VIDEO_SYNC = "video_sync"
     VOICE_REFERENCE = "voice_reference"
+    REFERENCE_AUDIO = "reference_audio"
+    VOICE_EMBEDDING = "voice_embedding"
+    REDUX_REFS = "redux_refs"
+    VIDEO_CLIP = "video_clip"                 # frames of a source clip (video -> video, upscaling)
+    CONTROL_CLIP = "control_clip"             # frames of a control signal (pose / depth video)
+    CONVERSATION_HISTORY = "conversation_history"
 
 
 @dataclass

@@ -163,20 +163,27 @@ class WanDiT:
         c = context.to(self.device, self.dtype)
         return self._lin(F.gelu(self._lin(c, t + "linear_1").float(), approximate="tanh").to(self.dtype), t + "linear_2")
 
-    def forward_grad(self, z, timestep, context, embedded: bool = False):
-        """z [B, C, F, H, W] latents, timestep [B] (sigma * 1000), context [B, L, text_dim] (or embed_text(...) with
-        embedded=True) -> velocity [B, C, F, H, W]."""
+    def patch_embed_tokens(self, z: torch.Tensor) -> tuple[torch.Tensor, tuple[int, int, int]]:
+        """Latents [B, C, F, H, W] -> (tokens [B, S, dim], the (frames, rows, columns) token grid)."""
+        pt, ph, pw = self.cfg.patch_size
+        _, _, Fr, H, W = z.shape
+        return self._lin(self.patchify(z.to(self.device, self.dtype)), "patch_embedding"), (Fr // pt, H // ph, W // pw)
+
+    def grid_rope(self, grid: tuple[int, int, int]) -> tuple[torch.Tensor, torch.Tensor]:
+        return rope_table(video_position_ids(*grid, self.device), self.cfg.rope_axes, 10000.0)
+
+    def forward_tokens(self, x, timestep, ctx, rope):
+        """The block stack and the output head on an already embedded token sequence: x [B, S, dim], timestep [B]
+        (sigma * 1000), ctx = embed_text(...), rope (cos, sin) [S, head_dim / 2] -> [B, S, pt * ph * pw * C]. Packed
+        conditioning (several clips on one token axis, each with its own rotary table) enters here
+        (candle-gen-wan/src/transformer.rs `forward_packed`)."""
         cfg = self.cfg
         dev, dt = self.device, self.dtype
-        B, _, Fr, H, W = z.shape
-        pt, ph, pw = cfg.patch_size
-        x = self._lin(self.patchify(z.to(dev, dt)), "patch_embedding")
-        rope = rope_table(video_position_ids(Fr // pt, H // ph, W // pw, dev), cfg.rope_axes, 10000.0)
+        B = x.shape[0]
         c = "condition_embedder."
         te = timestep_embedding(timestep.to(dev).float(), cfg.freq_dim, time_factor=1.0).to(dt)
         temb = self._lin(F.silu(self._lin(te, c + "time_embedder.linear_1").float()).to(dt), c + "time_embedder.linear_2")
         tproj = self._lin(F.silu(temb.float()).to(dt), c + "time_proj").float().view(B, 6, cfg.dim)
-        ctx = context.to(dev, dt) if embedded else self.embed_text(context)
         for i in range(cfg.num_layers):
             p = f"blocks.{i}"
             sh1, sc1, g1, sh2, sc2, g2 = (self.w[p + ".scale_shift_table"].float() + tproj).unsqueeze(2).unbind(1)
@@ -189,8 +196,15 @@ class WanDiT:
             f = self._lin(F.gelu(self._lin(h, p + ".ffn.net.0.proj").float(), approximate="tanh").to(dt), p + ".ffn.net.2")
             x = (x.float() + f.float() * g2).to(dt)
         shift, scale = (self.w["scale_shift_table"].float() + temb.float()[:, None]).unsqueeze(2).unbind(1)
-        out = self._lin((self._ln(x) * (1 + scale) + shift).to(dt), "proj_out")
-        return self.unpatchify(out, Fr, H, W)
+        return self._lin((self._ln(x) * (1 + scale) + shift).to(dt), "proj_out")
+
+    def forward_grad(self, z, timestep, context, embedded: bool = False):
+        """z [B, C, F, H, W] latents, timestep [B] (sigma * 1000), context [B, L, text_dim] (or embed_text(...) with
+        embedded=True) -> velocity [B, C, F, H, W]."""
+        _, _, Fr, H, W = z.shape
+        x, grid = self.patch_embed_tokens(z)
+        ctx = context.to(self.device, self.dtype) if embedded else self.embed_text(context)
+        return self.unpatchify(self.forward_tokens(x, timestep, ctx, self.grid_rope(grid)), Fr, H, W)
 
     @torch.no_grad()
     def forward(self, z, timestep, context, embedded: bool = False):
