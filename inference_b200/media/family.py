@@ -246,7 +246,7 @@ def family_descriptor(v: Variant, backend: str, prefix: str = "") -> ModelDescri
             supports_negative_prompt=v.uses_cfg and not v.extra.get("no_negative"), supports_guidance=v.default_guidance is not None,
             supports_true_cfg=v.uses_cfg,
             conditioning=list(v.conditioning), supports_lora=v.supports_lora, supports_lokr=v.supports_lokr,
-            samplers=[] if v.fixed_sampler else list(SOLVERS), schedulers=[] if v.fixed_sampler else list(SCHEDULERS),
+            samplers=[] if v.fixed_sampler else list(v.extra.get("samplers", SOLVERS)), schedulers=[] if v.fixed_sampler else list(SCHEDULERS),
             supported_guidance_methods=[], min_size=v.min_size,
             max_size=v.max_size, max_count=v.max_count, supports_sequential_offload=True),
         required_components=[])

@@ -253,3 +253,17 @@ def interleaved_mrope_table(positions: torch.Tensor, inv_freq: torch.Tensor, sec
     axis[(j % 3 == 2) & (j < 3 * section[2])] = 2
     ang = positions.to(inv_freq.device).float()[axis, :].t() * inv_freq.float()[None, :]          # [S, n]
     return ang.cos(), ang.sin()
+
+
+def language_model_config(j: dict):
+    """The language tower of a Qwen3-VL checkpoint as a plain Qwen3 decoder configuration (for callers that use the
+    tower as a text / instruction encoder): the `text_config` block, dense or mixture-of-experts, with its rotary
+    parameters (the three M-RoPE sections coincide on text-only prompts)."""
+    from .config import ModelConfig
+
+    t = dict(j.get("text_config", j))
+    moe = bool(t.get("num_experts"))
+    t["architectures"] = ["Qwen3MoeForCausalLM" if moe else "Qwen3ForCausalLM"]
+    t["model_type"] = "qwen3_moe" if moe else "qwen3"
+    t.setdefault("tie_word_embeddings", j.get("tie_word_embeddings", False))
+    return ModelConfig.from_json(t)
