@@ -1,0 +1,25 @@
+"""Audio generators on the sm_100a backend against the fp32 oracle backend."""
+import pytest
+
+
+@pytest.mark.gpu
+def test_moss_sfx_on_device_tracks_the_oracle_backend(tmp_path):
+    """The text-to-audio generator on the sm_100a backend (bf16 DiT on the tensor-core kernels, fp32 decoder) against the
+    fp32 oracle backend: same snapshot, seed and request."""
+    import numpy as np
+
+    from inference_b200.audio import moss_sfx
+    from inference_b200.audio.catalog import provider_registry
+    from inference_b200.contracts.gen_core import GenerationRequest, LoadSpec
+    from inference_b200.contracts.gen_core.generator import AudioParams
+
+    snap = moss_sfx.write_synthetic_snapshot(tmp_path / "sfx", sample_rate=4800)
+    req = dict(prompt="rain on a tin roof", steps=2, seed=3, guidance=2.0, audio=AudioParams(target_duration=1.0))
+    out = {}
+    for backend, prefix in (("b200", ""), ("cpu", "cpu_")):
+        g = provider_registry(backend).load(prefix + "moss_sfx_v2", LoadSpec.from_dir(snap))
+        t = g.generate(GenerationRequest(**req)).audio
+        out[backend] = np.asarray(t.samples, dtype=np.float32)
+    assert out["b200"].shape == out["cpu"].shape == (4800,)
+    denom = float(np.abs(out["cpu"]).mean()) + 1e-6
+    assert float(np.abs(out["b200"] - out["cpu"]).mean()) / denom < 0.25

@@ -155,6 +155,8 @@ FAMILY_TABLE = {
     "ideogram": ("ideogram_4", {"guidance": 2.0}),
     "anima": ("anima_base", {"guidance": 2.0, "negative_prompt": "blurry", "width": 512, "height": 512}),
     "mochi": ("mochi_1", {"guidance": 2.0, "negative_prompt": "blurry", "frames": 7}),
+    "boogu": ("boogu_image", {"guidance": 2.0}),
+    "bernini": ("bernini_renderer", {"guidance": 2.0, "frames": 5, "width": 64, "height": 64, "sampler": "euler"}),
 }
 
 
