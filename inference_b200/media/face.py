@@ -340,3 +340,125 @@ def random_face_weights(seed: int = 0, width: int = 8) -> tuple[dict[str, torch.
     a["fc.weight"], a["fc.bias"] = rn(512, cin * 7 * 7) / math.sqrt(cin * 49), rn(512) * 0.05
     a["features.scale"], a["features.shift"] = 1.0 + rn(512) * 0.05, rn(512) * 0.05
     return s, a
+
+
+# ---- face parsing (BiSeNet) ---------------------------------------------------------------------------------------------
+BG_LABELS = (0, 16, 18, 7, 8, 9, 14, 15)           # background, cloth, hat, ears, ear-ring, neck-lace, neck: whitened
+PARSE_MEAN, PARSE_STD = (0.485, 0.456, 0.406), (0.229, 0.224, 0.225)
+BISENET_FILE = "bisenet_parsing.safetensors"
+
+
+def upsample_bilinear_align_corners(x: torch.Tensor, out_h: int, out_w: int) -> torch.Tensor:
+    """[B, C, h, w] -> [B, C, out_h, out_w] with corner-aligned bilinear weights, as two interpolation matrices."""
+    def mat(n_in, n_out):
+        m = torch.zeros(n_out, n_in, device=x.device)
+        denom = float(max(n_out, 2) - 1)
+        for i in range(n_out):
+            src = i * (n_in - 1) / denom
+            x0 = int(math.floor(src))
+            x1 = min(x0 + 1, n_in - 1)
+            f = src - x0
+            m[i, x0] += 1.0 - f
+            m[i, x1] += f
+        return m
+
+    return mat(x.shape[2], out_h) @ x @ mat(x.shape[3], out_w).t()
+
+
+class BiSeNet(_ConvNet):
+    """19-class face parsing (parity: candle-gen-face/src/bisenet.rs): ResNet-18 trunk, two attention-refinement
+    modules and a global-context vector on the 1/16 and 1/32 features, feature fusion with a squeeze-excite gate at 1/8,
+    a 3x3 + 1x1 head, corner-aligned bilinear upsampling to the input size. Batch norms are folded into the
+    convolutions of the checkpoint."""
+
+    def _block(self, x, p, stride, down):
+        r = self.conv(self.conv(x, p + ".conv1", stride, 1, relu=True), p + ".conv2", 1, 1)
+        return F.relu(r + (self.conv(x, p + ".downsample", stride, 0) if down else x))
+
+    def _arm(self, x, p):
+        feat = self.conv(x, p + ".conv", 1, 1, relu=True)
+        return feat * torch.sigmoid(self.conv(feat.mean((2, 3), keepdim=True), p + ".conv_atten", 1, 0))
+
+    def _conv_w(self, x, name):
+        return F.conv2d(x, self.w[name + ".weight"])
+
+    @torch.no_grad()
+    def parse_logits(self, x: torch.Tensor) -> torch.Tensor:
+        """[B, 3, H, W] ImageNet-normalised -> [B, 19, H, W]."""
+        H, W = x.shape[2:]
+        h = F.max_pool2d(self.conv(x.to(self.device), "resnet.conv1", 2, 3, relu=True), 3, 2, 1)
+        feats = []
+        for layer, stride in ((1, 1), (2, 2), (3, 2), (4, 2)):
+            h = self._block(h, f"resnet.layer{layer}.0", stride, layer > 1)
+            h = self._block(h, f"resnet.layer{layer}.1", 1, False)
+            feats.append(h)
+        _, f8, f16, f32 = feats
+        avg = self.conv(f32.mean((2, 3), keepdim=True), "conv_avg", 1, 0, relu=True)
+        s32 = self._arm(f32, "arm32") + avg
+        cp16 = self.conv(F.interpolate(s32, size=f16.shape[2:], mode="nearest"), "conv_head32", 1, 1, relu=True)
+        s16 = self._arm(f16, "arm16") + cp16
+        cp8 = self.conv(F.interpolate(s16, size=f8.shape[2:], mode="nearest"), "conv_head16", 1, 1, relu=True)
+        feat = self.conv(torch.cat([f8, cp8], 1), "ffm.convblk", 1, 0, relu=True)
+        att = torch.sigmoid(self._conv_w(F.relu(self._conv_w(feat.mean((2, 3), keepdim=True), "ffm.conv1")), "ffm.conv2"))
+        fuse = feat * att + feat
+        out = self._conv_w(self.conv(fuse, "conv_out.conv", 1, 1, relu=True), "conv_out.conv_out")
+        return upsample_bilinear_align_corners(out, H, W)
+
+    def parse_mask(self, x: torch.Tensor) -> torch.Tensor:
+        return self.parse_logits(x).argmax(1)
+
+
+def face_features_image(rgb01: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+    """[B, 3, H, W] in [0, 1] and a label mask [B, H, W] -> the identity encoder's input: background labels white, the
+    rest the luma 0.299 R + 0.587 G + 0.114 B on all three channels."""
+    gray = 0.299 * rgb01[:, 0] + 0.587 * rgb01[:, 1] + 0.114 * rgb01[:, 2]
+    bg = torch.zeros_like(mask, dtype=torch.bool)
+    for lab in BG_LABELS:
+        bg |= mask == lab
+    v = torch.where(bg.to(gray.device), torch.ones_like(gray), gray)
+    return v[:, None].expand(-1, 3, -1, -1).contiguous()
+
+
+def face_features_for(analysis: FaceAnalysis, parser: BiSeNet, image: Image, face: FaceDetection) -> torch.Tensor:
+    """The 512 x 512 aligned crop of `face`, parsed and background-whitened: [1, 3, 512, 512] in [0, 1]."""
+    crop = align_face_512(image.pixels, image.height, image.width, face.landmarks)
+    rgb01 = torch.from_numpy(crop.astype(np.float32) / 255.0).permute(2, 0, 1)[None].contiguous()
+    mean, std = torch.tensor(PARSE_MEAN).view(1, 3, 1, 1), torch.tensor(PARSE_STD).view(1, 3, 1, 1)
+    mask = parser.parse_mask((rgb01 - mean) / std).cpu()
+    return face_features_image(rgb01, mask)
+
+
+def random_bisenet_weights(seed: int = 0, width: int = 8) -> dict[str, torch.Tensor]:
+    """Random parser weights in the checkpoint's [out, kh, kw, in] layout; `width` scales every channel count
+    (64 in the published network)."""
+    g = torch.Generator().manual_seed(seed)
+    w: dict[str, torch.Tensor] = {}
+
+    def conv(name, o, i, k, bias=True):
+        w[name + ".weight"] = torch.randn(o, k, k, i, generator=g) * (1.0 / math.sqrt(i * k * k))
+        if bias:
+            w[name + ".bias"] = torch.randn(o, generator=g) * 0.01
+
+    c = [width, width, 2 * width, 4 * width, 8 * width]
+    conv("resnet.conv1", c[0], 3, 7)
+    for layer in range(1, 5):
+        cin, cout = c[layer - 1] if layer > 1 else c[0], c[layer]
+        conv(f"resnet.layer{layer}.0.conv1", cout, cin, 3)
+        conv(f"resnet.layer{layer}.0.conv2", cout, cout, 3)
+        if layer > 1:
+            conv(f"resnet.layer{layer}.0.downsample", cout, cin, 1)
+        conv(f"resnet.layer{layer}.1.conv1", cout, cout, 3)
+        conv(f"resnet.layer{layer}.1.conv2", cout, cout, 3)
+    m = 2 * width
+    for name, cin in (("arm16", c[3]), ("arm32", c[4])):
+        conv(name + ".conv", m, cin, 3)
+        conv(name + ".conv_atten", m, m, 1)
+    conv("conv_head32", m, m, 3)
+    conv("conv_head16", m, m, 3)
+    conv("conv_avg", m, c[4], 1)
+    conv("ffm.convblk", 2 * m, c[2] + m, 1)
+    conv("ffm.conv1", m // 2, 2 * m, 1, bias=False)
+    conv("ffm.conv2", 2 * m, m // 2, 1, bias=False)
+    conv("conv_out.conv", 2 * m, 2 * m, 3)
+    conv("conv_out.conv_out", 19, 2 * m, 1, bias=False)
+    return w

@@ -187,6 +187,7 @@ class OracleFluxDiT:
         M = self._modulations(timesteps, y, guidance, img.dtype)
         ln = lambda x: F.layer_norm(x, (Hs,), eps=1e-6)  # noqa: E731
         T = txt.shape[1]
+        inj = getattr(self, "injector", None)      # image-stream residual hooks (identity adapters): see FluxDiTGpu.injector
         for i in range(cfg.depth):
             mods = {}
             for s in ("img", "txt"):
@@ -210,6 +211,9 @@ class OracleFluxDiT:
                               f"double_blocks.{i}.{s}_mlp.2")
                 outs[s] = x + g2 * h
             img, txt = outs["img"], outs["txt"]
+            r = inj.after_double(i, img) if inj is not None else None
+            if r is not None:
+                img = img + r.to(img.dtype)
         x = torch.cat([txt, img], 1)
         for i in range(cfg.depth_single):
             p = f"single_blocks.{i}"
@@ -220,6 +224,9 @@ class OracleFluxDiT:
             q, k, v = self._qkv(qkv, None, p + ".norm")
             attn = self._attn(q, k, v, cos, sin)
             x = x + g * self._lin(torch.cat([attn, F.gelu(mlp, approximate="tanh")], -1), p + ".linear2")
+            r = inj.after_single(i, x[:, T:]) if inj is not None else None
+            if r is not None:
+                x = torch.cat([x[:, :T], x[:, T:] + r.to(x.dtype)], 1)
         img = x[:, T:]
         sh, sc = M["final_layer.adaLN_modulation.1"][:, None, :].chunk(2, dim=-1)
         return self._lin((1 + sc) * ln(img) + sh, "final_layer.linear")
@@ -236,6 +243,9 @@ class FluxDiTGpu:
         self.device = device or self.comm.device
         self.w: dict[str, torch.Tensor] = {}
         self.launches = 0
+        # Optional image-stream hooks (candle-gen-flux `DitImageInjector`): an object with after_double(i, img) and
+        # after_single(i, img_tokens), each returning a residual [B, S_img, hidden] or None. Single-GPU eager path only.
+        self.injector = None
 
     def load_state_dict(self, weights: dict[str, torch.Tensor]) -> "FluxDiTGpu":
         self.w = {k: v.to(device=self.device, dtype=torch.bfloat16).contiguous() for k, v in weights.items()}
@@ -333,6 +343,7 @@ class FluxDiTGpu:
         x_img = self._lin(img.reshape(B * Si, -1), "img_in").view(B, Si, H)
         x_txt = self._lin(txt.reshape(B * St, -1), "txt_in").view(B, St, H)
         scale = D ** -0.5
+        inj = self.injector
         qkv = torch.empty((B, S, 3 * H), dtype=torch.bfloat16, device=dev)
         attn = torch.empty((B, S, H), dtype=torch.bfloat16, device=dev)
 
@@ -382,6 +393,9 @@ class FluxDiTGpu:
                 new[s] = ops.gated_residual(x, h2, mods[s][5], rows_per_batch=n)
                 self.launches += 3
             x_img, x_txt = new["img"], new["txt"]
+            r = inj.after_double(i, x_img) if inj is not None else None
+            if r is not None:
+                x_img = x_img + r.to(x_img.dtype)
 
         x = torch.cat([x_txt, x_img], 1).contiguous()
         buf2 = torch.empty((B, S, H + M), dtype=torch.bfloat16, device=dev)
@@ -397,6 +411,9 @@ class FluxDiTGpu:
             out = self._lin(buf2.view(B * S, H + M), p + ".linear2").view(B, S, H)
             x = ops.gated_residual(x, out, g, rows_per_batch=S)
             self.launches += 2
+            r = inj.after_single(i, x[:, St:]) if inj is not None else None
+            if r is not None:
+                x[:, St:] += r.to(x.dtype)
         x_img = x[:, St:].contiguous()
         m = mod["final_layer.adaLN_modulation.1"]
         xm = ops.layernorm_mod(x_img, scale=m[:, H:], shift=m[:, :H], rows_per_batch=Si)
@@ -410,6 +427,8 @@ class FluxDiTGpu:
     def forward_graphed(self, img, img_ids, txt, txt_ids, timesteps, y, guidance=None, rope=None):
         """Same result as forward(); the first call for a shape runs eagerly once (allocations, tensor maps,
         symmetric-memory rendezvous) and captures, later calls copy the inputs into static buffers and replay."""
+        if self.injector is not None:           # the hooks read per-request tensors: no capture
+            return self.forward(img, img_ids, txt, txt_ids, timesteps, y, guidance, rope)
         key = (tuple(img.shape), tuple(txt.shape), guidance is not None)
         st = getattr(self, "_graphs", None)
         if st is None:

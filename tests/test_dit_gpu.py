@@ -95,6 +95,38 @@ def test_flux_dit_matches_oracle(batch):
         assert torch.equal(eager, replay)
 
 
+def test_flux_dit_image_stream_hooks_match_oracle():
+    """The identity-adapter seam: perceiver cross-attention residuals added to the image stream after double / single
+    blocks give the same velocity on the device model (eager and through forward_graphed) as on the fp32 oracle."""
+    from inference_b200.media.pulid import IdFormerConfig, PulidCa, random_pulid_weights
+    from inference_b200.models.dit_flux import FluxConfig, FluxDiTGpu, OracleFluxDiT, make_ids, random_flux_weights
+
+    cfg = FluxConfig(in_channels=64, vec_in_dim=64, context_in_dim=128, hidden_size=256, num_heads=2, depth=2,
+                     depth_single=2)
+    w = {k: v.bfloat16().float() for k, v in random_flux_weights(cfg, seed=0, std=0.05).items()}
+    oracle = OracleFluxDiT(cfg, w, device="cuda")
+    model = FluxDiTGpu(cfg, device=torch.device("cuda")).load_state_dict(w)
+    pw = random_pulid_weights(IdFormerConfig(dim=16, depth=5, heads=2, dim_head=8, output_dim=24), 256, 2, 3)
+    pw["swb_ca_config"] = torch.tensor([2, 8])
+    g = torch.Generator(device="cuda").manual_seed(5)
+    emb = torch.randn(1, 4, 24, device="cuda", generator=g)
+    hh, ww, St = 6, 5, 19
+    img = torch.randn(1, hh * ww, 64, device="cuda", generator=g).bfloat16()
+    txt = torch.randn(1, St, 128, device="cuda", generator=g).bfloat16()
+    y = torch.randn(1, 64, device="cuda", generator=g).bfloat16()
+    t, gd = torch.full((1,), 0.7, device="cuda"), torch.full((1,), 3.5, device="cuda")
+    txt_ids, img_ids = make_ids(hh, ww, St, "cuda")
+    plain = model.forward(img, img_ids, txt, txt_ids, t, y, gd).float()
+    oracle.injector = model.injector = PulidCa(pw, emb, 1.0, cfg.depth, cfg.depth_single, "cuda")
+    ref = oracle.forward(img.float(), img_ids, txt.float(), txt_ids, t, y.float(), gd)
+    out = model.forward(img, img_ids, txt, txt_ids, t, y, gd).float()
+    assert (out - ref).abs().max().item() < 0.06 * max(1.0, ref.abs().max().item())
+    assert (out - plain).abs().max().item() > 1e-2
+    assert torch.equal(model.forward_graphed(img, img_ids, txt, txt_ids, t, y, gd).float(), out)
+    model.injector = None
+    assert torch.equal(model.forward(img, img_ids, txt, txt_ids, t, y, gd).float(), plain)
+
+
 def test_vae_decoder_matches_oracle():
     from inference_b200.models.vae import OracleVaeDecoder, VaeConfig, VaeDecoderGpu, random_vae_weights
 
