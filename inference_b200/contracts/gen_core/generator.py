@@ -55,6 +55,7 @@ class Conditioning:
     image: Image | None = None
     images: list[Image] = field(default_factory=list)
     frames: list[Image] = field(default_factory=list)
+    mask_frames: list[Image] = field(default_factory=list)        # CONTROL_CLIP: one mask per frame (white = generate)
     audio: AudioTrack | None = None
     strength: float | None = None
     frame_index: int | None = None

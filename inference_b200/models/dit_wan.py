@@ -172,29 +172,40 @@ class WanDiT:
     def grid_rope(self, grid: tuple[int, int, int]) -> tuple[torch.Tensor, torch.Tensor]:
         return rope_table(video_position_ids(*grid, self.device), self.cfg.rope_axes, 10000.0)
 
-    def forward_tokens(self, x, timestep, ctx, rope):
+    def _time(self, timestep, B):
+        """timestep [B] -> (embedding [B, dim], the six per-block modulation vectors [B, 6, dim] in fp32)."""
+        cfg, dt = self.cfg, self.dtype
+        c = "condition_embedder."
+        te = timestep_embedding(timestep.to(self.device).float(), cfg.freq_dim, time_factor=1.0).to(dt)
+        temb = self._lin(F.silu(self._lin(te, c + "time_embedder.linear_1").float()).to(dt), c + "time_embedder.linear_2")
+        return temb, self._lin(F.silu(temb.float()).to(dt), c + "time_proj").float().view(B, 6, cfg.dim)
+
+    def _block(self, x, p, tproj, ctx, rope):
+        """One transformer block with checkpoint prefix `p` (`blocks.<i>`, or a control branch's `vace_blocks.<j>`)."""
+        cfg, dt = self.cfg, self.dtype
+        sh1, sc1, g1, sh2, sc2, g2 = (self.w[p + ".scale_shift_table"].float() + tproj).unsqueeze(2).unbind(1)
+        h = (self._ln(x) * (1 + sc1) + sh1).to(dt)
+        x = (x.float() + self._attention(h, h, p + ".attn1", rope).float() * g1).to(dt)
+        n2 = F.layer_norm(x.float(), (cfg.dim,), self.w[p + ".norm2.weight"].float(), self.w[p + ".norm2.bias"].float(),
+                          cfg.eps).to(dt)
+        x = x + self._attention(n2, ctx, p + ".attn2", None)
+        h = (self._ln(x) * (1 + sc2) + sh2).to(dt)
+        f = self._lin(F.gelu(self._lin(h, p + ".ffn.net.0.proj").float(), approximate="tanh").to(dt), p + ".ffn.net.2")
+        return (x.float() + f.float() * g2).to(dt)
+
+    def forward_tokens(self, x, timestep, ctx, rope, hints: dict | None = None):
         """The block stack and the output head on an already embedded token sequence: x [B, S, dim], timestep [B]
         (sigma * 1000), ctx = embed_text(...), rope (cos, sin) [S, head_dim / 2] -> [B, S, pt * ph * pw * C]. Packed
         conditioning (several clips on one token axis, each with its own rotary table) enters here
-        (candle-gen-wan/src/transformer.rs `forward_packed`)."""
+        (candle-gen-wan/src/transformer.rs `forward_packed`). `hints` maps a block index to a residual added after that
+        block (control branches)."""
         cfg = self.cfg
         dev, dt = self.device, self.dtype
-        B = x.shape[0]
-        c = "condition_embedder."
-        te = timestep_embedding(timestep.to(dev).float(), cfg.freq_dim, time_factor=1.0).to(dt)
-        temb = self._lin(F.silu(self._lin(te, c + "time_embedder.linear_1").float()).to(dt), c + "time_embedder.linear_2")
-        tproj = self._lin(F.silu(temb.float()).to(dt), c + "time_proj").float().view(B, 6, cfg.dim)
+        temb, tproj = self._time(timestep, x.shape[0])
         for i in range(cfg.num_layers):
-            p = f"blocks.{i}"
-            sh1, sc1, g1, sh2, sc2, g2 = (self.w[p + ".scale_shift_table"].float() + tproj).unsqueeze(2).unbind(1)
-            h = (self._ln(x) * (1 + sc1) + sh1).to(dt)
-            x = (x.float() + self._attention(h, h, p + ".attn1", rope).float() * g1).to(dt)
-            n2 = F.layer_norm(x.float(), (cfg.dim,), self.w[p + ".norm2.weight"].float(), self.w[p + ".norm2.bias"].float(),
-                              cfg.eps).to(dt)
-            x = x + self._attention(n2, ctx, p + ".attn2", None)
-            h = (self._ln(x) * (1 + sc2) + sh2).to(dt)
-            f = self._lin(F.gelu(self._lin(h, p + ".ffn.net.0.proj").float(), approximate="tanh").to(dt), p + ".ffn.net.2")
-            x = (x.float() + f.float() * g2).to(dt)
+            x = self._block(x, f"blocks.{i}", tproj, ctx, rope)
+            if hints is not None and i in hints:
+                x = (x.float() + hints[i].float()).to(dt)
         shift, scale = (self.w["scale_shift_table"].float() + temb.float()[:, None]).unsqueeze(2).unbind(1)
         return self._lin((self._ln(x) * (1 + scale) + shift).to(dt), "proj_out")
 

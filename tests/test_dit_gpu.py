@@ -188,6 +188,7 @@ FAMILY_TABLE = {
     "anima": ("anima_base", {"guidance": 2.0, "negative_prompt": "blurry", "width": 512, "height": 512}),
     "mochi": ("mochi_1", {"guidance": 2.0, "negative_prompt": "blurry", "frames": 7}),
     "boogu": ("boogu_image", {"guidance": 2.0}),
+    "wan_vace": ("wan_vace", {"guidance": 2.0, "sampler": "euler", "conditioning": "vace"}),
     "bernini": ("bernini_renderer", {"guidance": 2.0, "frames": 5, "width": 64, "height": 64, "sampler": "euler"}),
 }
 
@@ -236,6 +237,13 @@ def test_generator_providers_on_device_track_the_oracle_backend(tmp_path, family
         mid, extra = "z_image", {"guidance": 2.0, "negative_prompt": "blurry"}
     snap = write_synthetic_snapshot(tmp_path / family)
     req = {**dict(prompt="a lighthouse at dusk", width=256, height=256, steps=2, seed=11), **extra}
+    if req.get("conditioning") == "vace":
+        from inference_b200.contracts.gen_core.generator import Conditioning, ConditioningKind
+        from inference_b200.contracts.gen_core.media import Image
+
+        fr = [Image(64, 64, bytes((i * k) % 256 for i in range(64 * 64 * 3))) for k in (3, 5, 7, 11, 13)]
+        mk = [Image(64, 64, bytes([255 * (j >= 2)]) * (64 * 64 * 3)) for j in range(5)]
+        req["conditioning"] = [Conditioning(ConditioningKind.CONTROL_CLIP, frames=fr, mask_frames=mk)]
     imgs = {}
     for backend, prefix in (("b200", ""), ("cpu", "cpu_")):
         g = provider_registry(backend).load(prefix + mid, LoadSpec.from_dir(snap))
