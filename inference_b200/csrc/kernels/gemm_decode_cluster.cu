@@ -108,6 +108,40 @@ __device__ __forceinline__ bool ld_lines(const uint4* src, uint32_t epoch, uint4
     }
   }
 }
+// Batched form for the rank that sums: the lines of four peers for one 16-byte group are requested together, so the
+// wait costs one memory round trip per four peers once the data has landed instead of one per peer. `bases[r]` is the
+// first line of peer first_peer + r (unused where bit r of `need` is clear); the data words land in u[r].
+__device__ __forceinline__ bool ld_lines_all(const uint4* const* bases, uint32_t need, uint32_t epoch, uint4* u, int where,
+                                             int rank, int first_peer) {
+  uint64_t t0 = 0;
+  uint32_t pending = need;
+  for (uint32_t it = 0; pending; ++it) {
+    uint4 a[4], b[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      if (pending & (1u << r)) {
+        a[r] = ld_line(bases[r]);
+        b[r] = ld_line(bases[r] + 1);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      if ((pending & (1u << r)) && a[r].y == epoch && a[r].w == epoch && b[r].y == epoch && b[r].w == epoch) {
+        u[r] = make_uint4(a[r].x, a[r].z, b[r].x, b[r].z);
+        pending &= ~(1u << r);
+      }
+    }
+    if (pending && (it & 0x3F) == 0x3F) {
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > g_wait_limit_ns) {
+        report_error(SWB_ERR_PEER_TIMEOUT, where, rank, first_peer + __ffs(pending) - 1);
+        return false;
+      }
+    }
+  }
+  return true;
+}
 // sum of squares -> 2^-24 fixed point (integer accumulation is order independent, so every rank and every replay
 // gets the same bits)
 __device__ __forceinline__ unsigned long long ssq_fixed(float ss) {
@@ -408,19 +442,31 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
 #pragma unroll
           for (int j = 0; j < 8; ++j) acc[j] = 0.f;
 #pragma unroll
-          for (int r = 0; r < 8; ++r) {
-            if (r < q.world && !failed) {
-              uint4 u = own[it];
-              if (r != q.rank) {
-                const uint4* src = q.slots[q.rank] + (((size_t)r * q.cap + tok) * ld8 + (feat >> 3)) * 2;
-                failed = !ld_lines(src, epoch, u, 1100, q.rank, r);
-              }
-              const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&u);
+          for (int h = 0; h < 2; ++h) {        // peers 0-3, then 4-7: the sum runs in rank order on every rank
+            if (h * 4 < q.world && !failed) {
+              uint4 u[4];
+              const uint4* bases[4];
+              uint32_t need = 0;
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float2 t = __bfloat1622float2(uh[j]);
-                acc[2 * j] += t.x;
-                acc[2 * j + 1] += t.y;
+              for (int k = 0; k < 4; ++k) {
+                const int r = h * 4 + k;
+                bases[k] = q.slots[q.rank] + (((size_t)r * q.cap + tok) * ld8 + (feat >> 3)) * 2;
+                if (r < q.world && r != q.rank) need |= 1u << k;
+              }
+              failed = !ld_lines_all(bases, need, epoch, u, 1100, q.rank, h * 4);
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const int r = h * 4 + k;
+                if (r < q.world && !failed) {
+                  const uint4 v = (r == q.rank) ? own[it] : u[k];
+                  const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const float2 t = __bfloat1622float2(uh[j]);
+                    acc[2 * j] += t.x;
+                    acc[2 * j + 1] += t.y;
+                  }
+                }
               }
             }
           }

@@ -17,8 +17,13 @@ from .kv_pool import PagedKvPool, PagedSequence
 
 
 def _splits_for(batch: int, kv_heads: int, max_kv: int, sms: int = 148) -> int:
+    """KV splits of the decode attention: enough CTAs for `SWB_ATTN_CTAS_PER_SM` (default 2) per SM, never below one
+    64-key tile per split."""
+    import os
+
     tiles = max(1, (max_kv + 63) // 64)
-    want = max(1, (2 * sms) // max(1, batch * kv_heads))
+    per_sm = max(1, int(os.environ.get("SWB_ATTN_CTAS_PER_SM", "2")))
+    want = max(1, (per_sm * sms) // max(1, batch * kv_heads))
     s = 1
     while s * 2 <= min(want, tiles, 32):
         s *= 2
