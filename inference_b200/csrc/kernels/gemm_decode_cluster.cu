@@ -154,7 +154,8 @@ __device__ __forceinline__ float act_apply(float x, int act) {
   return x;
 }
 
-template <int BLOCK_N, int CLUSTER, int STAGES_>
+// PEER instantiates the cross-rank epilogue (its batched peer loads need more registers than the plain store path).
+template <int BLOCK_N, int CLUSTER, int STAGES_, bool PEER>
 __global__ void __launch_bounds__(THREADS, STAGES_ > 4 ? 1 : 2)
 gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                            const GemmParams p) {
@@ -371,7 +372,7 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
     const int e = (warp - 2) * 32 + lane;
     if (e < 64) p.ssq_zero[e] = 0ull;
   }
-  if (warp >= 2 && p.peer.mode) {
+  if (PEER && warp >= 2) {
     // ---- cross-rank sum over peer memory, flag-in-data lines: no barrier, no fence, one NVLink hop per shot ----
     const int et = (warp - 2) * 32 + lane;  // 0 .. EPI_THREADS - 1
     const GemmPeerReduce& q = p.peer;
@@ -640,10 +641,10 @@ gemm_decode_cluster_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
   if (tr && threadIdx.x == 0) tr[7] = global_timer_ns();
 }
 
-template <int BLOCK_N, int CLUSTER, int STAGES_>
+template <int BLOCK_N, int CLUSTER, int STAGES_, bool PEER>
 int launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t stream) {
   using Cfg = DecCfg<BLOCK_N, STAGES_>;
-  auto kern = gemm_decode_cluster_kernel<BLOCK_N, CLUSTER, STAGES_>;
+  auto kern = gemm_decode_cluster_kernel<BLOCK_N, CLUSTER, STAGES_, PEER>;
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -679,13 +680,22 @@ int launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p
 
 template <int BLOCK_N, int STAGES_>
 int launch_cluster(int cluster, const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, cudaStream_t s) {
+  if (p.peer.mode) {          // the cross-rank epilogue runs with 1, 2, 4 or 8 members (see the launch checks)
+    switch (cluster) {
+      case 1: return launch_one<BLOCK_N, 1, STAGES_, true>(tw, tx, p, s);
+      case 2: return launch_one<BLOCK_N, 2, STAGES_, true>(tw, tx, p, s);
+      case 4: return launch_one<BLOCK_N, 4, STAGES_, true>(tw, tx, p, s);
+      case 8: return launch_one<BLOCK_N, 8, STAGES_, true>(tw, tx, p, s);
+    }
+    return -2;
+  }
   switch (cluster) {
-    case 1: return launch_one<BLOCK_N, 1, STAGES_>(tw, tx, p, s);
-    case 2: return launch_one<BLOCK_N, 2, STAGES_>(tw, tx, p, s);
-    case 3: return launch_one<BLOCK_N, 3, STAGES_>(tw, tx, p, s);
-    case 4: return launch_one<BLOCK_N, 4, STAGES_>(tw, tx, p, s);
-    case 6: return launch_one<BLOCK_N, 6, STAGES_>(tw, tx, p, s);
-    case 8: return launch_one<BLOCK_N, 8, STAGES_>(tw, tx, p, s);
+    case 1: return launch_one<BLOCK_N, 1, STAGES_, false>(tw, tx, p, s);
+    case 2: return launch_one<BLOCK_N, 2, STAGES_, false>(tw, tx, p, s);
+    case 3: return launch_one<BLOCK_N, 3, STAGES_, false>(tw, tx, p, s);
+    case 4: return launch_one<BLOCK_N, 4, STAGES_, false>(tw, tx, p, s);
+    case 6: return launch_one<BLOCK_N, 6, STAGES_, false>(tw, tx, p, s);
+    case 8: return launch_one<BLOCK_N, 8, STAGES_, false>(tw, tx, p, s);
   }
   return -2;
 }

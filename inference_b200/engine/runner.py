@@ -22,8 +22,8 @@ def _splits_for(batch: int, kv_heads: int, max_kv: int, sms: int = 148) -> int:
     import os
 
     tiles = max(1, (max_kv + 63) // 64)
-    per_sm = max(1, int(os.environ.get("SWB_ATTN_CTAS_PER_SM", "2")))
-    want = max(1, (per_sm * sms) // max(1, batch * kv_heads))
+    per_sm = max(0.25, float(os.environ.get("SWB_ATTN_CTAS_PER_SM", "2")))
+    want = max(1, int(per_sm * sms) // max(1, batch * kv_heads))
     s = 1
     while s * 2 <= min(want, tiles, 32):
         s *= 2
