@@ -6,7 +6,7 @@ from ..contracts.gen_core.registry import ProviderRegistry, ProviderRegistryBuil
 
 
 def provider_registry(backend: str = "b200") -> ProviderRegistry:
-    from . import anima, bernini, boogu, chroma, wan_vace, flux, flux2, ideogram, kolors, mochi, krea, qwen_image, sana, sd3, sdxl, svd, wan, z_image
+    from . import anima, bernini, boogu, chroma, wan_ti2v, wan_vace, flux, flux2, ideogram, kolors, mochi, krea, qwen_image, sana, sd3, sdxl, svd, wan, z_image
 
     b = ProviderRegistryBuilder()
     b.register_generators(flux.registrations(backend))
@@ -17,6 +17,7 @@ def provider_registry(backend: str = "b200") -> ProviderRegistry:
     b.register_generators(sdxl.registrations(backend))
     b.register_generators(kolors.registrations(backend))
     b.register_generators(wan.registrations(backend))
+    b.register_generators([wan_ti2v.registration(backend)])
     b.register_generators([wan_vace.registration(backend)])
     b.register_generators([bernini.registration(backend)])
     b.register_generators(boogu.registrations(backend))

@@ -54,6 +54,8 @@ class WanVariant:
     guidance_high: float
     guidance_low: float
     i2v: bool = False
+    stride: int = 8             # spatial compression of the autoencoder (16 for the z48 autoencoder of the 5B model)
+    fps: int = DEFAULT_FPS
 
 
 T2V_14B = WanVariant(MODEL_ID, BOUNDARY, FLOW_SHIFT, GUIDANCE_HIGH, GUIDANCE_LOW)
@@ -264,9 +266,9 @@ class WanPipeline:
         steps = req.steps or DEFAULT_STEPS
         frames = req.frames or DEFAULT_FRAMES
         base_seed = req.seed if req.seed is not None else default_seed()
-        lt, lh, lw = (frames - 1) // 4 + 1, req.height // 8, req.width // 8
-        dev, dt = self.device, self.dtype
         var = self.variant
+        lt, lh, lw = (frames - 1) // 4 + 1, req.height // var.stride, req.width // var.stride
+        dev, dt = self.device, self.dtype
         sigmas = wan_sigmas(steps, float(req.scheduler_shift) if req.scheduler_shift else var.shift)
         y = None
         if var.i2v:
@@ -365,7 +367,7 @@ class WanGenerator(Generator):
         self.validate(req)
         videos = self.residency.run(req.cancel, on_progress, lambda text: self.pipe.encode(text, req),
                                     lambda heavy, cond: self.pipe.render(heavy, cond, req, on_progress))
-        return GenerationOutput(video_frames=videos[0], fps=req.fps or DEFAULT_FPS)
+        return GenerationOutput(video_frames=videos[0], fps=req.fps or self.pipe.variant.fps)
 
 
 def _load(backend: str, prefix: str, variant: WanVariant = T2V_14B) -> Callable[[LoadSpec], WanGenerator]:

@@ -307,3 +307,135 @@ class WanVaeEncoder(WanVaeDecoder):
         h = self._conv(F.silu(self._norm(h, "encoder.norm_out")), "encoder.conv_out", 1)
         mu = self._conv(h, "quant_conv", 0)[:, : cfg.z_dim].float()
         return (mu - self.mean) / self.std
+
+
+# ---- Wan2.2 z48 residual autoencoder (decode side) -----------------------------------------------------------------------
+LATENTS48_MEAN = (-0.2289, -0.0052, -0.1323, -0.2339, -0.2799, 0.0174, 0.1838, 0.1557, -0.1382, 0.0542, 0.2813, 0.0891, 0.157,
+                  -0.0098, 0.0375, -0.1825, -0.2246, -0.1207, -0.0698, 0.5109, 0.2665, -0.2108, -0.2158, 0.2502, -0.2055, -0.0322,
+                  0.1109, 0.1567, -0.0729, 0.0899, -0.2799, -0.123, -0.0313, -0.1649, 0.0117, 0.0723, -0.2839, -0.2083, -0.052,
+                  0.3748, 0.0152, 0.1957, 0.1433, -0.2944, 0.3573, -0.0548, -0.1681, -0.0667)
+LATENTS48_STD = (0.4765, 1.0364, 0.4514, 1.1677, 0.5313, 0.499, 0.4818, 0.5013, 0.8158, 1.0344, 0.5894, 1.0901, 0.6885, 0.6165,
+                 0.8454, 0.4978, 0.5759, 0.3523, 0.7135, 0.6804, 0.5833, 1.4146, 0.8986, 0.5659, 0.7069, 0.5338, 0.4889, 0.4917,
+                 0.4069, 0.4999, 0.6866, 0.4093, 0.5709, 0.6065, 0.6415, 0.4944, 0.5726, 1.2042, 0.5458, 1.6887, 0.3971, 1.06,
+                 0.3943, 0.5537, 0.5444, 0.4089, 0.7468, 0.7744)
+
+
+@dataclass
+class Wan22VaeConfig:
+    z_dim: int = 48
+    base_dim: int = 256
+    num_res_blocks: int = 2
+    patch_size: int = 2
+    out_channels: int = 3
+
+    @property
+    def dims(self) -> tuple[int, ...]:
+        b = self.base_dim
+        return (4 * b, 4 * b, 4 * b, 2 * b, b)
+
+
+class Wan22VaeDecoder(WanVaeDecoder):
+    """Decode side of the Wan2.2 residual autoencoder (parity: candle-gen-wan/src/vae.rs): latents [B, 48, T, h, w] ->
+    video [B, 3, 1 + 4 (T - 1), 16 h, 16 w]. Four up blocks of three residual units; the first two double time and
+    space, the third space only, and each of those three adds a parameter-free shortcut: the block input with its
+    channels repeated and folded into the (time, row, column) factors (the leading frame of a time-doubling fold is
+    dropped, matching the first-frame rule of the learned path). The output convolution emits 12 channels that unfold
+    2 x 2 into RGB."""
+
+    def __init__(self, cfg: Wan22VaeConfig, weights: dict[str, torch.Tensor], dtype=torch.float32, device="cpu"):
+        self.cfg, self.dtype, self.device = cfg, dtype, torch.device(device)
+        self.w = {}
+        for k, v in weights.items():
+            if k.startswith(("decoder.", "post_quant_conv.")):
+                if k.endswith(".gamma"):
+                    v = v.reshape(1, -1, 1, 1, 1)
+                elif k.endswith(".weight") and v.dim() == 4:
+                    v = v[:, :, None]
+                self.w[k] = v.to(device=self.device, dtype=dtype).contiguous()
+        n = cfg.z_dim
+        self.mean = torch.tensor((LATENTS48_MEAN * (n // 48 + 1))[:n], device=self.device, dtype=dtype).view(1, -1, 1, 1, 1)
+        self.std = torch.tensor((LATENTS48_STD * (n // 48 + 1))[:n], device=self.device, dtype=dtype).view(1, -1, 1, 1, 1)
+
+    @staticmethod
+    def dup_shortcut(x: torch.Tensor, out_c: int, ft: int, fs: int) -> torch.Tensor:
+        B, C, T, H, W = x.shape
+        rep = out_c * ft * fs * fs // C
+        y = x[:, :, None].expand(B, C, rep, T, H, W).reshape(B, out_c, ft, fs, fs, T, H, W)
+        y = y.permute(0, 1, 5, 2, 6, 3, 7, 4).reshape(B, out_c, T * ft, H * fs, W * fs)
+        return y[:, :, ft - 1:] if ft > 1 else y
+
+    def _up(self, x, p, temporal: bool):
+        B, C, T, H, W = x.shape
+        if temporal:
+            if T > 1:
+                y = self._conv(x[:, :, 1:], p + ".time_conv", 0)
+                y = torch.stack((y[:, :C], y[:, C:]), 3).reshape(B, C, 2 * (T - 1), H, W)
+                x = torch.cat([x[:, :, :1], y], 2)
+            else:
+                x = x[:, :, :1]
+        T2 = x.shape[2]
+        fr = F.interpolate(x.permute(0, 2, 1, 3, 4).reshape(B * T2, C, H, W), scale_factor=2, mode="nearest")
+        return self._conv(fr.reshape(B, T2, C, 2 * H, 2 * W).permute(0, 2, 1, 3, 4), p + ".resample.1", 1)
+
+    @torch.no_grad()
+    def decode(self, latents: torch.Tensor) -> torch.Tensor:
+        cfg, dims = self.cfg, self.cfg.dims
+        z = latents.to(self.device, self.dtype) * self.std + self.mean
+        h = self._conv(self._conv(z, "post_quant_conv", 0), "decoder.conv_in", 1)
+        h = self._res(h, "decoder.mid_block.resnets.0")
+        h = self._attention(h, "decoder.mid_block.attentions.0")
+        h = self._res(h, "decoder.mid_block.resnets.1")
+        for i in range(4):
+            x0 = h
+            for j in range(cfg.num_res_blocks + 1):
+                h = self._res(h, f"decoder.up_blocks.{i}.resnets.{j}")
+            if i != 3:
+                h = self._up(h, f"decoder.up_blocks.{i}.upsampler", temporal=i < 2)
+                h = h + self.dup_shortcut(x0, dims[i + 1], 2 if i < 2 else 1, 2)
+        h = self._conv(F.silu(self._norm(h, "decoder.norm_out")), "decoder.conv_out", 1)       # [B, 3 p p, T', 8h, 8w]
+        B, _, T, H, W = h.shape
+        p, c = cfg.patch_size, cfg.out_channels
+        return h.reshape(B, c, p, p, T, H, W).permute(0, 1, 4, 5, 3, 6, 2).reshape(B, c, T, H * p, W * p)
+
+
+def random_wan22_vae_weights(cfg: Wan22VaeConfig, seed: int = 0, std: float = 0.05) -> dict[str, torch.Tensor]:
+    g = torch.Generator().manual_seed(seed)
+    w: dict[str, torch.Tensor] = {}
+
+    def conv3(name, o, i, k):
+        w[name + ".weight"] = torch.randn(o, i, *k, generator=g) * std
+        w[name + ".bias"] = torch.randn(o, generator=g) * 0.01
+
+    def gamma(name, c, dims=3):
+        w[name + ".gamma"] = 1 + torch.randn(c, *([1] * dims), generator=g) * 0.05
+
+    def res(p, cin, cout):
+        gamma(p + ".norm1", cin)
+        conv3(p + ".conv1", cout, cin, (3, 3, 3))
+        gamma(p + ".norm2", cout)
+        conv3(p + ".conv2", cout, cout, (3, 3, 3))
+        if cin != cout:
+            conv3(p + ".conv_shortcut", cout, cin, (1, 1, 1))
+
+    d = cfg.dims
+    conv3("post_quant_conv", cfg.z_dim, cfg.z_dim, (1, 1, 1))
+    conv3("decoder.conv_in", d[0], cfg.z_dim, (3, 3, 3))
+    res("decoder.mid_block.resnets.0", d[0], d[0])
+    res("decoder.mid_block.resnets.1", d[0], d[0])
+    a = "decoder.mid_block.attentions.0"
+    gamma(a + ".norm", d[0], 2)
+    w[a + ".to_qkv.weight"], w[a + ".to_qkv.bias"] = torch.randn(3 * d[0], d[0], 1, 1, generator=g) * std, torch.zeros(3 * d[0])
+    w[a + ".proj.weight"], w[a + ".proj.bias"] = torch.randn(d[0], d[0], 1, 1, generator=g) * std, torch.zeros(d[0])
+    for i in range(4):
+        cur = d[i]
+        for j in range(cfg.num_res_blocks + 1):
+            res(f"decoder.up_blocks.{i}.resnets.{j}", cur, d[i + 1])
+            cur = d[i + 1]
+        if i != 3:
+            u = f"decoder.up_blocks.{i}.upsampler"
+            if i < 2:
+                conv3(u + ".time_conv", 2 * cur, cur, (3, 1, 1))
+            w[u + ".resample.1.weight"], w[u + ".resample.1.bias"] = torch.randn(cur, cur, 3, 3, generator=g) * std, torch.zeros(cur)
+    gamma("decoder.norm_out", d[4])
+    conv3("decoder.conv_out", cfg.out_channels * cfg.patch_size ** 2, d[4], (3, 3, 3))
+    return w
