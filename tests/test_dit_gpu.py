@@ -190,6 +190,7 @@ FAMILY_TABLE = {
     "boogu": ("boogu_image", {"guidance": 2.0}),
     "wan_ti2v": ("wan2_2_ti2v_5b", {"guidance": 2.0, "sampler": "euler", "frames": 5, "width": 480, "height": 512}),
     "wan_vace": ("wan_vace", {"guidance": 2.0, "sampler": "euler", "conditioning": "vace"}),
+    "scail2": ("scail2_14b", {"guidance": 2.0, "sampler": "euler", "width": 64, "height": 64, "conditioning": "scail2"}),
     "bernini": ("bernini_renderer", {"guidance": 2.0, "frames": 5, "width": 64, "height": 64, "sampler": "euler"}),
 }
 
@@ -245,6 +246,14 @@ def test_generator_providers_on_device_track_the_oracle_backend(tmp_path, family
         fr = [Image(64, 64, bytes((i * k) % 256 for i in range(64 * 64 * 3))) for k in (3, 5, 7, 11, 13)]
         mk = [Image(64, 64, bytes([255 * (j >= 2)]) * (64 * 64 * 3)) for j in range(5)]
         req["conditioning"] = [Conditioning(ConditioningKind.CONTROL_CLIP, frames=fr, mask_frames=mk)]
+    if req.get("conditioning") == "scail2":
+        from inference_b200.contracts.gen_core.generator import Conditioning, ConditioningKind
+        from inference_b200.contracts.gen_core.media import Image
+
+        im = lambda k: Image(64, 64, bytes((i * k) % 256 for i in range(64 * 64 * 3)))      # noqa: E731
+        req["conditioning"] = [Conditioning(ConditioningKind.REFERENCE, image=im(17)), Conditioning(ConditioningKind.MASK, image=im(19)),
+                               Conditioning(ConditioningKind.CONTROL_CLIP, frames=[im(k) for k in (3, 5, 7, 11, 13)],
+                                            mask_frames=[im(k + 1) for k in (3, 5, 7, 11, 13)])]
     imgs = {}
     for backend, prefix in (("b200", ""), ("cpu", "cpu_")):
         g = provider_registry(backend).load(prefix + mid, LoadSpec.from_dir(snap))
