@@ -590,14 +590,15 @@ int swb_attn_dense(const void* q, long long q_stride_tok, int q_stride_head, con
                    int q_len, int kv_len, int Hq, int Hkv, int D, float scale, int causal, void* stream) {
   using namespace swb;
   if (batch <= 0 || q_len <= 0) return 0;
-  if (D != HD || Hq % Hkv != 0) return -3;
+  if ((D != HD && D != 64) || Hq % Hkv != 0) return -3;
   if (kv_len <= 0) return -3;
-  if (g_dense_impl == 0 && (!causal || q_len == kv_len) &&
+  if ((g_dense_impl == 0 || D == 64) && (!causal || q_len == kv_len) &&
       attn_dense_tcgen05_supported(q, k, v, q_stride_tok, q_stride_head, kv_stride_tok, kv_stride_head, out_stride_tok, D,
                                    causal))
     return attn_dense_tcgen05_launch(q, q_stride_tok, q_stride_head, k, v, kv_stride_tok, kv_stride_head, out,
                                      out_stride_tok, batch, q_len, kv_len, Hq, Hkv, scale,
-                                     reinterpret_cast<cudaStream_t>(stream), nullptr, 0, 0, 0, 0, 0, causal);
+                                     reinterpret_cast<cudaStream_t>(stream), nullptr, 0, 0, 0, 0, 0, causal, nullptr, 0, D);
+  if (D != HD) return -3;            // 64-wide heads exist on the tcgen05 kernel only
   int rc = configure_once();
   if (rc) return rc;
   AttnParams p{};

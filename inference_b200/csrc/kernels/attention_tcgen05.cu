@@ -29,18 +29,25 @@ SWB_REGISTER_STATUS_UNIT(attention_tcgen05);
 
 namespace {
 
-constexpr int HD = 128;          // head dim
 constexpr int BM = 128;          // query rows per tile (two tiles per CTA)
 constexpr int BN = 128;          // keys per tile
 constexpr int KV_STAGES = 2;
 constexpr int THREADS = 320;
-constexpr uint32_t TILE_BYTES = BM * HD * 2;       // 32 KB: two 64-column swizzle atoms of 16 KB
-constexpr uint32_t ATOM_BYTES = BM * 64 * 2;       // 16 KB
-constexpr uint32_t SMEM_Q = 0;                     // 2 tiles
-constexpr uint32_t SMEM_K = 2 * TILE_BYTES;        // KV_STAGES tiles
-constexpr uint32_t SMEM_V = SMEM_K + KV_STAGES * TILE_BYTES;
-constexpr uint32_t SMEM_BAR = SMEM_V + KV_STAGES * TILE_BYTES;
-constexpr size_t SMEM_BYTES = SMEM_BAR + 256 + 1024 /*alignment slack*/;
+constexpr uint32_t ATOM_BYTES = BM * 64 * 2;       // 16 KB: 128 rows of one 64-column swizzle atom
+// Head dim 128 (two swizzle atoms per tile) or 64 (one atom: half the shared memory and half the MMA work of the padded path).
+template <int HD>
+struct FaCfg {
+  static_assert(HD == 64 || HD == 128, "head dim 64 or 128");
+  static constexpr int ATOMS = HD / 64;
+  static constexpr uint32_t TILE_BYTES = BM * HD * 2;
+  static constexpr uint32_t SMEM_Q = 0;                                   // 2 tiles
+  static constexpr uint32_t SMEM_K = 2 * TILE_BYTES;                      // KV_STAGES tiles
+  static constexpr uint32_t SMEM_V = SMEM_K + KV_STAGES * TILE_BYTES;
+  static constexpr uint32_t SMEM_BAR = SMEM_V + KV_STAGES * TILE_BYTES;
+  static constexpr size_t SMEM_BYTES = SMEM_BAR + 256 + 1024 /*alignment slack*/;
+  static constexpr int ROW_BYTES = HD * 2;                                // one output row of one head
+  static constexpr int CHUNKS = ROW_BYTES / 16;                           // 16-byte chunks per row
+};
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_S0 = 0, COL_O0 = 128, COL_S1 = 256, COL_O1 = 384;
 constexpr float RESCALE_THRESHOLD = 8.f;           // in log2 units
@@ -144,9 +151,13 @@ struct Barriers {
   int abort;
 };
 
+template <int HD>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_dense_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                           const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
+  using C = FaCfg<HD>;
+  constexpr uint32_t TILE_BYTES = C::TILE_BYTES, SMEM_Q = C::SMEM_Q, SMEM_K = C::SMEM_K, SMEM_V = C::SMEM_V, SMEM_BAR = C::SMEM_BAR;
+  constexpr int ATOMS = C::ATOMS, ROW_BYTES = C::ROW_BYTES, CHUNKS = C::CHUNKS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   Barriers* bars = reinterpret_cast<Barriers*>(smem + SMEM_BAR);
@@ -201,7 +212,7 @@ attn_dense_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
     if (lane == 0) {
       mbar_arrive_expect_tx(&bars->q_full, p.tiles * TILE_BYTES);
       for (int q = 0; q < p.tiles; ++q)
-        for (int a = 0; a < 2; ++a)
+        for (int a = 0; a < ATOMS; ++a)
           tma_load_4d(smem + SMEM_Q + q * TILE_BYTES + a * ATOM_BYTES, &tmap_q, &bars->q_full, a * 64, head,
                       tok0 + q_base + q * BM, batch);
       bool ok = true;
@@ -212,14 +223,14 @@ attn_dense_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
         ok = mbar_wait(&bars->k_empty[s], ph ^ 1, abort_flag, 10);
         if (!ok) break;
         mbar_arrive_expect_tx(&bars->k_full[s], TILE_BYTES);
-        for (int a = 0; a < 2; ++a)
+        for (int a = 0; a < ATOMS; ++a)
           tma_load_4d(smem + SMEM_K + s * TILE_BYTES + a * ATOM_BYTES, &tmap_k, &bars->k_full[s], a * 64, kv_head,
                       tok0 + j * BN, batch);
         issued_k = j + 1;
         ok = mbar_wait(&bars->v_empty[s], ph ^ 1, abort_flag, 11);
         if (!ok) break;
         mbar_arrive_expect_tx(&bars->v_full[s], TILE_BYTES);
-        for (int a = 0; a < 2; ++a)
+        for (int a = 0; a < ATOMS; ++a)
           tma_load_4d(smem + SMEM_V + s * TILE_BYTES + a * ATOM_BYTES, &tmap_v, &bars->v_full[s], a * 64, kv_head,
                       tok0 + j * BN, batch);
         issued_v = j + 1;
@@ -342,6 +353,9 @@ attn_dense_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       }
       const float neg_m = -m_used * p.scale_log2;
       float l0 = 0.f, l1 = 0.f;
+      // (Measured alternatives for this loop, all slower on B200: every 4th / 2nd exponential as a cubic on the FMA pipe
+      // -8 % / -17 %; pairs of exponentials as one bf16x2 special-function operation -6 %; three-input max with
+      // two-lane fp32 multiply-add and add -30 %, from register-pair moves and spills. The loop is issue-bound.)
 #pragma unroll
       for (int i = 0; i < BN; i += 2) {   // packed P overwrites the row in place (index i/2 <= i)
         const float e0 = ex2(fmaf(__uint_as_float(s[i]), p.scale_log2, neg_m));
@@ -361,10 +375,10 @@ attn_dense_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
     if (ok && my_tiles > 0) {
       tc_fence_after_sync();
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      // Stage this warp's 32 rows x 128 columns in the (now idle) Q region, then write every row's 256 bytes with
-      // 16 lanes x 16 bytes: contiguous runs for local stores and for stores that cross NVLink alike.
+      // Stage this warp's 32 rows x HD columns in the (now idle) Q region, then write every row's HD * 2 bytes with
+      // HD / 8 lanes x 16 bytes: contiguous runs for local stores and for stores that cross NVLink alike.
       // 16-byte chunk c of row r sits at c ^ (r & 7).
-      uint8_t* slab = smem + SMEM_Q + warp * (32 * 256);
+      uint8_t* slab = smem + SMEM_Q + warp * (32 * ROW_BYTES);
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t o[32];
@@ -377,17 +391,17 @@ attn_dense_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
           u.y = pack_bf16x2(__uint_as_float(o[v * 8 + 2]) * inv, __uint_as_float(o[v * 8 + 3]) * inv);
           u.z = pack_bf16x2(__uint_as_float(o[v * 8 + 4]) * inv, __uint_as_float(o[v * 8 + 5]) * inv);
           u.w = pack_bf16x2(__uint_as_float(o[v * 8 + 6]) * inv, __uint_as_float(o[v * 8 + 7]) * inv);
-          *reinterpret_cast<uint4*>(slab + lane * 256 + (((c * 4 + v) ^ (lane & 7)) << 4)) = u;
+          *reinterpret_cast<uint4*>(slab + lane * ROW_BYTES + (((c * 4 + v) ^ (lane & 7)) << 4)) = u;
         }
       }
       __syncwarp();
       const int row0 = q_base + q * BM + (warp & 3) * 32;
 #pragma unroll 4
-      for (int it = 0; it < 16; ++it) {
-        const int r = 2 * it + (lane >> 4), ch = lane & 15;
+      for (int it = 0; it < CHUNKS; ++it) {            // CHUNKS lanes write one row: 32 / CHUNKS rows per pass
+        const int r = (32 / CHUNKS) * it + lane / CHUNKS, ch = lane % CHUNKS;
         const int grow = row0 + r;
         if (grow < q_len) {
-          const uint4 val = *reinterpret_cast<const uint4*>(slab + r * 256 + ((ch ^ (r & 7)) << 4));
+          const uint4 val = *reinterpret_cast<const uint4*>(slab + r * ROW_BYTES + ((ch ^ (r & 7)) << 4));
           bf16* dst = p.out + ((long long)batch * p.q_len + tok0 + grow) * p.out_stride_tok + (long long)head * HD;
           if (p.scatter.enabled) {
             const OutScatter& sc = p.scatter;
@@ -430,11 +444,11 @@ struct Map4Hash {
 
 // bf16 [batch, tokens, heads, 128] with element strides (tok, head, batch): dims (128, heads, tokens, batch),
 // box (64, 1, 128, 1), 128-byte swizzle, zero fill outside.
-int make_tmap_heads(CUtensorMap* out, const void* ptr, int heads, int tokens, int batch, long long stride_head,
+int make_tmap_heads(CUtensorMap* out, const void* ptr, int hd, int heads, int tokens, int batch, long long stride_head,
                     long long stride_tok, long long stride_batch) {
   static std::mutex mu;
   static std::unordered_map<Map4Key, CUtensorMap, Map4Hash> cache;
-  Map4Key key{ptr, stride_head, stride_tok, stride_batch, heads, tokens, batch};
+  Map4Key key{ptr, stride_head, stride_tok, stride_batch, heads * 1024 + hd, tokens, batch};
   {
     std::lock_guard<std::mutex> g(mu);
     auto it = cache.find(key);
@@ -452,7 +466,7 @@ int make_tmap_heads(CUtensorMap* out, const void* ptr, int heads, int tokens, in
       return -1;
     encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
   }
-  cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)heads, (cuuint64_t)tokens, (cuuint64_t)batch};
+  cuuint64_t dims[4] = {(cuuint64_t)hd, (cuuint64_t)heads, (cuuint64_t)tokens, (cuuint64_t)batch};
   cuuint64_t strides[3] = {(cuuint64_t)stride_head * 2, (cuuint64_t)stride_tok * 2, (cuuint64_t)stride_batch * 2};
   cuuint32_t box[4] = {64u, 1u, (cuuint32_t)BM, 1u};
   cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
@@ -475,7 +489,7 @@ void attn_dense_tcgen05_set_tiles(int tiles) { g_force_tiles = tiles; }
 int attn_dense_tcgen05_supported(const void* q, const void* k, const void* v, long long q_stride_tok, int q_stride_head,
                                  long long kv_stride_tok, int kv_stride_head, long long out_stride_tok, int D,
                                  int causal) {
-  if (D != HD) return 0;
+  if (D != 128 && D != 64) return 0;
   (void)causal;   // causal problems are supported when queries and keys cover the same positions (checked by callers)
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) return 0;
   if ((q_stride_tok | q_stride_head | kv_stride_tok | kv_stride_head | out_stride_tok) % 8) return 0;
@@ -486,25 +500,29 @@ int attn_dense_tcgen05_launch(const void* q, long long q_stride_tok, int q_strid
                               long long kv_stride_tok, int kv_stride_head, void* out, long long out_stride_tok,
                               int batch, int q_len, int kv_len, int Hq, int Hkv, float scale, cudaStream_t stream,
                               void* const* peers, int world, int split, int n0, int n1, int col_offset, int causal,
-                              const int* cu_q, int total_tokens) {
+                              const int* cu_q, int total_tokens, int head_dim) {
+  if (head_dim != 64 && head_dim != 128) return -3;
   CUtensorMap tq, tk, tv;
   // packed batches address one flat token axis (batch = the number of sequences only sizes the grid)
   const int map_q_tokens = cu_q ? total_tokens : q_len, map_kv_tokens = cu_q ? total_tokens : kv_len;
   const int map_batch = cu_q ? 1 : batch;
-  int rc = make_tmap_heads(&tq, q, Hq, map_q_tokens, map_batch, q_stride_head, q_stride_tok, q_stride_tok * map_q_tokens);
+  int rc = make_tmap_heads(&tq, q, head_dim, Hq, map_q_tokens, map_batch, q_stride_head, q_stride_tok, q_stride_tok * map_q_tokens);
   if (rc) return rc;
-  rc = make_tmap_heads(&tk, k, Hkv, map_kv_tokens, map_batch, kv_stride_head, kv_stride_tok,
+  rc = make_tmap_heads(&tk, k, head_dim, Hkv, map_kv_tokens, map_batch, kv_stride_head, kv_stride_tok,
                        kv_stride_tok * map_kv_tokens);
   if (rc) return rc;
-  rc = make_tmap_heads(&tv, v, Hkv, map_kv_tokens, map_batch, kv_stride_head, kv_stride_tok,
+  rc = make_tmap_heads(&tv, v, head_dim, Hkv, map_kv_tokens, map_batch, kv_stride_head, kv_stride_tok,
                        kv_stride_tok * map_kv_tokens);
   if (rc) return rc;
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(attn_dense_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(attn_dense_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)FaCfg<128>::SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_dense_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)FaCfg<64>::SMEM_BYTES);
     if (e != cudaSuccess) return -(int)e;
     configured[dev] = true;
   }
@@ -534,7 +552,9 @@ int attn_dense_tcgen05_launch(const void* q, long long q_stride_tok, int q_strid
   const double t2 = (double)((c2 + sms - 1) / sms), t1 = 0.85 * (double)((c1 + sms - 1) / sms);
   p.tiles = (g_force_tiles == 1 || g_force_tiles == 2) ? g_force_tiles : (t1 < t2 ? 1 : 2);
   dim3 grid((q_len + p.tiles * BM - 1) / (p.tiles * BM), Hq, batch);
-  return launch_kernel(attn_dense_tcgen05_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, tq, tk, tv, p);
+  if (head_dim == 64)
+    return launch_kernel(attn_dense_tcgen05_kernel<64>, grid, dim3(THREADS), FaCfg<64>::SMEM_BYTES, stream, tq, tk, tv, p);
+  return launch_kernel(attn_dense_tcgen05_kernel<128>, grid, dim3(THREADS), FaCfg<128>::SMEM_BYTES, stream, tq, tk, tv, p);
 }
 
 }  // namespace swb

@@ -74,7 +74,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float
     if on_device(q) and mask is None and D <= 128 and D % 8 == 0 and (not causal or Sq == k.shape[1]):
         from .. import ops
 
-        if D == 128:
+        if D == 128 or (D == 64 and not causal):
             kc, vc = k.contiguous(), v.contiguous()
             return ops.dense_attention(q.contiguous(), kc, vc, scale=scale, causal=causal)
         if not causal:

@@ -52,7 +52,8 @@ def paged_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
 
 def dense_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float, causal: bool = False,
                     out: torch.Tensor | None = None) -> torch.Tensor:
-    """q [B, Sq, Hq, 128], k/v [B, Skv, Hkv, 128] (k and v share strides) -> out [B, Sq, Hq*128]."""
+    """q [B, Sq, Hq, D], k/v [B, Skv, Hkv, D] (k and v share strides), D = 128 or 64 -> out [B, Sq, Hq*D]. Both widths
+    run on the tcgen05 kernel (64-wide heads: one swizzle atom per tile, half the shared memory and MMA work)."""
     require_cuda(q, k, v)
     B, Sq, Hq, D = q.shape
     Skv, Hkv = k.shape[1], k.shape[2]
@@ -68,20 +69,22 @@ def dense_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale:
 
 
 def narrow_heads_on_kernel() -> bool:
-    """Heads narrower than 128 run zero-padded on the tcgen05 kernel unless SWB_NARROW_ATTN=library selects the
-    framework's scaled-dot-product call (measured on SD3.5-Large at 1024 x 1024: 4.66 s / image padded, 3.99 s through
-    the library call, whose kernels are specialised for 64-wide heads)."""
+    """Heads narrower than 128 run on the tcgen05 kernel (64 natively, other widths zero-padded to 128) unless
+    SWB_NARROW_ATTN=library selects the framework's scaled-dot-product call. SWB_NARROW_ATTN=padded forces the
+    zero-padded path for 64-wide heads too (comparison runs)."""
     import os
 
     return os.environ.get("SWB_NARROW_ATTN", "kernel") != "library"
 
 
 def dense_attention_padded(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: float) -> torch.Tensor:
-    """dense_attention for head widths below 128 (64 in SD3 / SDXL blocks, 72 in the Qwen3-VL tower): q, k and v are
-    zero-padded to 128 per head, which changes neither q . k nor the first D output columns, so the tcgen05 kernel
-    serves them at twice the arithmetic. q [B, Sq, H, D], k / v [B, Skv, Hkv, D] bf16 -> [B, Sq, H * D]."""
+    """dense_attention for head widths below 128. 64 (SD3 / SDXL blocks) runs natively; other widths (72 in the Qwen3-VL
+    tower, 120 in Boogu) are zero-padded to 128 per head, which changes neither q . k nor the first D output columns.
+    q [B, Sq, H, D], k / v [B, Skv, Hkv, D] bf16 -> [B, Sq, H * D]."""
+    import os
+
     B, Sq, H, D = q.shape
-    if D == 128:
+    if D == 128 or (D == 64 and os.environ.get("SWB_NARROW_ATTN", "kernel") != "padded"):
         return dense_attention(q.contiguous(), k.contiguous(), v.contiguous(), scale=scale)
     assert D < 128
     pad = (0, 128 - D)
