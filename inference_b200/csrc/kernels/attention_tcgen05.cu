@@ -151,6 +151,8 @@ struct Barriers {
   int abort;
 };
 
+// 168 registers per thread is the cap for ten warps: two of the four scheduler partitions hold three warps, and a
+// partition's file is 16 K registers (a build with 200 registers per thread does not launch).
 template <int HD>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_dense_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
