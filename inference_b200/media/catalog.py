@@ -6,7 +6,7 @@ from ..contracts.gen_core.registry import ProviderRegistry, ProviderRegistryBuil
 
 
 def provider_registry(backend: str = "b200") -> ProviderRegistry:
-    from . import anima, bernini, boogu, chroma, scail2, wan_ti2v, wan_vace, flux, flux2, ideogram, kolors, mochi, krea, qwen_image, sana, sd3, sdxl, svd, wan, z_image
+    from . import anima, bernini, boogu, chroma, scail2, sensenova, wan_ti2v, wan_vace, flux, flux2, ideogram, kolors, mochi, krea, qwen_image, sana, sd3, sdxl, svd, wan, z_image
 
     b = ProviderRegistryBuilder()
     b.register_generators(flux.registrations(backend))
@@ -22,6 +22,7 @@ def provider_registry(backend: str = "b200") -> ProviderRegistry:
     b.register_generators([bernini.registration(backend)])
     b.register_generators([scail2.registration(backend)])
     b.register_generators(boogu.registrations(backend))
+    b.register_generators(sensenova.registrations(backend))
     b.register_generators(krea.registrations(backend))
     b.register_generators(flux2.registrations(backend))
     b.register_generators(sana.registrations(backend))

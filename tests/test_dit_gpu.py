@@ -188,6 +188,7 @@ FAMILY_TABLE = {
     "anima": ("anima_base", {"guidance": 2.0, "negative_prompt": "blurry", "width": 512, "height": 512}),
     "mochi": ("mochi_1", {"guidance": 2.0, "negative_prompt": "blurry", "frames": 7}),
     "boogu": ("boogu_image", {"guidance": 2.0}),
+    "sensenova": ("sensenova_u1_8b", {"guidance": 2.0}),
     "wan_ti2v": ("wan2_2_ti2v_5b", {"guidance": 2.0, "sampler": "euler", "frames": 5, "width": 480, "height": 512}),
     "wan_vace": ("wan_vace", {"guidance": 2.0, "sampler": "euler", "conditioning": "vace"}),
     "scail2": ("scail2_14b", {"guidance": 2.0, "sampler": "euler", "width": 64, "height": 64, "conditioning": "scail2"}),

@@ -30,7 +30,7 @@ def test_registry_lists_both_variants(registry):
     assert provider_registry("b200").ids() == ["flux1_schnell", "flux1_dev", "chroma1_hd", "chroma1_base", "chroma1_flash",
                                              "z_image", "z_image_turbo", "sd3_5_large", "sd3_5_large_turbo",
                                              "sd3_5_medium", "qwen_image", "sdxl", "kolors", "wan2_2_t2v_14b", "wan2_2_i2v_14b",
-                                             "wan2_2_ti2v_5b", "wan_vace", "bernini_renderer", "scail2_14b", "boogu_image", "boogu_image_turbo", "boogu_image_edit",
+                                             "wan2_2_ti2v_5b", "wan_vace", "bernini_renderer", "scail2_14b", "boogu_image", "boogu_image_turbo", "boogu_image_edit", "sensenova_u1_8b", "sensenova_u1_8b_fast",
                                              "krea_2_turbo", "krea_2_raw", "flux2_klein_9b", "flux2_dev", "sana_1600m",
                                              "sana_sprint_1600m", "ideogram_4", "ideogram_4_turbo", "mochi_1", "anima_base",
                                              "anima_aesthetic", "anima_turbo", "svd_xt"]
