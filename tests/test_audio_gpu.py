@@ -23,3 +23,34 @@ def test_moss_sfx_on_device_tracks_the_oracle_backend(tmp_path):
     assert out["b200"].shape == out["cpu"].shape == (4800,)
     denom = float(np.abs(out["cpu"]).mean()) + 1e-6
     assert float(np.abs(out["b200"] - out["cpu"]).mean()) / denom < 0.25
+
+
+@pytest.mark.gpu
+def test_acestep_on_device_tracks_the_oracle_backend(tmp_path):
+    """Text-to-music and a region edit on the sm_100a backend (bf16 condition encoder and DiT on the tensor-core
+    kernels, fp32 autoencoder) against the fp32 oracle backend: same snapshot, seed and request."""
+    import numpy as np
+    import torch
+
+    from inference_b200.audio import acestep
+    from inference_b200.audio.catalog import provider_registry
+    from inference_b200.contracts.gen_core import GenerationRequest, LoadSpec
+    from inference_b200.contracts.gen_core.generator import AudioParams, Conditioning, ConditioningKind
+    from inference_b200.contracts.gen_core.media import AudioTrack
+
+    snap = acestep.write_synthetic_snapshot(tmp_path / "ace")
+    src = torch.randn(480, 2, generator=torch.Generator().manual_seed(9)) * 0.2
+    edit = Conditioning(ConditioningKind.AUDIO_EDIT, audio=AudioTrack(48_000, 2, src.reshape(-1).tolist()), mode="inpaint",
+                        region=(0.0025, 0.0075))
+    reqs = {"t2m": dict(prompt="calm piano", steps=2, seed=3, audio=AudioParams(target_duration=0.1, lyrics="la la", bpm=90.0)),
+            "inpaint": dict(prompt="calm piano", steps=2, seed=3, audio=AudioParams(), conditioning=[edit])}
+    for name, req in reqs.items():
+        out = {}
+        for backend, prefix in (("b200", ""), ("cpu", "cpu_")):
+            g = provider_registry(backend).load(prefix + "acestep_v15_turbo", LoadSpec.from_dir(snap))
+            out[backend] = np.asarray(g.generate(GenerationRequest(**req)).audio.samples, dtype=np.float32)
+        assert out["b200"].shape == out["cpu"].shape, name
+        denom = float(np.abs(out["cpu"]).mean()) + 1e-6
+        assert float(np.abs(out["b200"] - out["cpu"]).mean()) / denom < 0.25, name
+    keep = out["b200"].reshape(-1, 2)[:120]
+    assert np.array_equal(keep, src.numpy()[:120])                     # outside the window the source survives bit for bit
