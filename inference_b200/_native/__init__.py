@@ -96,6 +96,8 @@ def _declare_kernels(lib: ctypes.CDLL) -> None:
     sig("swb_attn_dense_set_tiles", [c_int], None)
     sig("swb_attn_varlen_causal", [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_ll, c_int, c_void_p, c_ll, c_void_p, c_int,
                                    c_int, c_int, c_int, c_int, c_float, c_void_p])
+    sig("swb_attn_paged_prefill_tc", [c_void_p, c_ll, c_int, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                      c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
     sig("swb_attn_dense_scatter", [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_ll, c_int, c_void_p, c_int,
                                    c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                    c_void_p])

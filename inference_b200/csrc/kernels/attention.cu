@@ -579,6 +579,26 @@ int swb_attn_varlen_causal(const void* q, long long q_stride_tok, int q_stride_h
                                    reinterpret_cast<cudaStream_t>(stream), nullptr, 0, 0, 0, 0, 0, 1, cu_q, total_tokens);
 }
 
+// Prefill over paged keys / values on the tcgen05 kernel: sequence s has query tokens [cu_q[s], cu_q[s + 1]) of the flat
+// q / out token axis (total_tokens rows) and kv_lens[s] keys (earlier context + these tokens, already in the cache) in
+// pages block_table[s, :]; its queries sit at the last positions (bottom-right aligned causal mask). Caches:
+// [num_blocks, Hkv, block_size, 128] contiguous, block_size a multiple of 8 dividing 128. Returns -3 when the problem
+// is outside the kernel's reach (the caller then takes swb_attn_paged).
+int swb_attn_paged_prefill_tc(const void* q, long long q_stride_tok, int q_stride_head, void* out, long long out_stride_tok,
+                              const void* kcache, const void* vcache, const int* block_table, int max_blocks,
+                              int block_size, int num_blocks, const int* cu_q, const int* kv_lens, int num_seqs,
+                              int max_q_len, int total_tokens, int Hq, int Hkv, float scale, int causal, void* stream) {
+  using namespace swb;
+  if (num_seqs <= 0 || total_tokens <= 0) return 0;
+  if (g_dense_impl != 0 || !cu_q || !kv_lens || !block_table || max_q_len <= 0 || Hq % Hkv != 0) return -3;
+  if (!attn_dense_tcgen05_supported(q, kcache, vcache, q_stride_tok, q_stride_head, 128, 128, out_stride_tok, 128, causal))
+    return -3;
+  return attn_dense_tcgen05_launch(q, q_stride_tok, q_stride_head, kcache, vcache, 128, 128, out, out_stride_tok,
+                                   num_seqs, max_q_len, max_q_len, Hq, Hkv, scale, reinterpret_cast<cudaStream_t>(stream),
+                                   nullptr, 0, 0, 0, 0, 0, causal, cu_q, total_tokens, 128, kv_lens, block_table,
+                                   max_blocks, block_size, num_blocks);
+}
+
 // 0: pick the tcgen05 kernel whenever it supports the problem; 1: always the mma.sync kernel (comparison runs).
 void swb_attn_dense_set_impl(int impl) { swb::g_dense_impl = impl; }
 // 0: pick the number of query tiles per CTA per problem; 1 / 2: fixed (comparison runs).

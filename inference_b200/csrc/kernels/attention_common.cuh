@@ -84,5 +84,6 @@ int attn_dense_tcgen05_launch(const void* q, long long q_stride_tok, int q_strid
                               int batch, int q_len, int kv_len, int Hq, int Hkv, float scale, cudaStream_t stream,
                               void* const* peers = nullptr, int world = 0, int split = 0, int n0 = 0, int n1 = 0,
                               int col_offset = 0, int causal = 0, const int* cu_q = nullptr, int total_tokens = 0,
-                              int head_dim = 128);
+                              int head_dim = 128, const int* kv_lens = nullptr, const int* block_table = nullptr,
+                              int max_blocks = 0, int block_size = 0, int num_blocks = 0);
 }  // namespace swb

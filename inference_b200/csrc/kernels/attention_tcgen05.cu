@@ -69,6 +69,12 @@ struct FaParams {
   int tiles;   // query tiles per CTA: 2 (MMAs of one tile overlap the softmax of the other) or 1 (twice the CTAs)
   int causal;  // key j attends to query i only if j <= i (sequences start at position 0: fresh prefill)
   const int* cu_q;   // optional [num_seqs + 1] token offsets: blockIdx.z is then a sequence of a packed batch
+  // Paged keys / values (prefill on top of earlier context): tmap_k / tmap_v then describe the page pool
+  // [page, kv head, row in page, d]; sequence z owns pages block_table[z * max_blocks + i] and kv_lens[z] keys, and
+  // its queries are the last q_len of those positions (bottom-right aligned causal mask). Needs cu_q.
+  const int* kv_lens;
+  const int* block_table;
+  int max_blocks, block_size;
 };
 
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* tmap, uint64_t* bar, int c0, int c1, int c2,
@@ -169,11 +175,13 @@ attn_dense_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
   // packed variable-length batch: this CTA's sequence covers tokens [tok0, tok0 + q_len) of one flat token axis
   const int tok0 = p.cu_q ? p.cu_q[blockIdx.z] : 0;
   const int q_len = p.cu_q ? p.cu_q[blockIdx.z + 1] - tok0 : p.q_len;
-  const int kv_len = p.cu_q ? q_len : p.kv_len;
+  const bool paged = p.block_table != nullptr;
+  const int kv_len = paged ? p.kv_lens[blockIdx.z] : (p.cu_q ? q_len : p.kv_len);
+  const int coff = paged ? max(kv_len - q_len, 0) : 0;   // position of query 0 among the sequence's keys
   const int batch = p.cu_q ? 0 : blockIdx.z;
-  if (q_base >= q_len) return;   // uniform for the whole CTA, before any barrier or TMEM allocation
+  if (q_base >= q_len || kv_len <= 0) return;   // uniform for the whole CTA, before any barrier or TMEM allocation
   const int kv_head = head / (p.Hq / p.Hkv);
-  const int kv_end = p.causal ? min(kv_len, q_base + p.tiles * BM) : kv_len;
+  const int kv_end = p.causal ? min(kv_len, q_base + p.tiles * BM + coff) : kv_len;
   const int n_tiles = (kv_end + BN - 1) / BN;
   volatile int* abort_flag = &bars->abort;
 
@@ -219,22 +227,35 @@ attn_dense_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
                       tok0 + q_base + q * BM, batch);
       bool ok = true;
       int issued_k = 0, issued_v = 0;
+      // paged: a tile is BN / block_size pages, each a box of block_size rows that lands at its place in the swizzled
+      // tile (a page is a whole number of 8-row swizzle groups); tiles past the last page repeat it, masked below
+      const int* pages = paged ? p.block_table + (long long)blockIdx.z * p.max_blocks : nullptr;
+      const int per_tile = paged ? BN / p.block_size : 1, last_page = paged ? (kv_len - 1) / p.block_size : 0;
+      const uint32_t page_bytes = paged ? (uint32_t)p.block_size * 128u : 0u;
+      auto load_tile = [&](uint32_t dst_off, const CUtensorMap* map, uint64_t* bar, int j) {
+        if (!paged) {
+          for (int a = 0; a < ATOMS; ++a)
+            tma_load_4d(smem + dst_off + a * ATOM_BYTES, map, bar, a * 64, kv_head, tok0 + j * BN, batch);
+          return;
+        }
+        for (int g = 0; g < per_tile; ++g) {
+          const int page = pages[min(j * per_tile + g, last_page)];
+          for (int a = 0; a < ATOMS; ++a)
+            tma_load_4d(smem + dst_off + a * ATOM_BYTES + g * page_bytes, map, bar, a * 64, 0, kv_head, page);
+        }
+      };
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j % KV_STAGES;
         const uint32_t ph = (j / KV_STAGES) & 1;
         ok = mbar_wait(&bars->k_empty[s], ph ^ 1, abort_flag, 10);
         if (!ok) break;
         mbar_arrive_expect_tx(&bars->k_full[s], TILE_BYTES);
-        for (int a = 0; a < ATOMS; ++a)
-          tma_load_4d(smem + SMEM_K + s * TILE_BYTES + a * ATOM_BYTES, &tmap_k, &bars->k_full[s], a * 64, kv_head,
-                      tok0 + j * BN, batch);
+        load_tile(SMEM_K + s * TILE_BYTES, &tmap_k, &bars->k_full[s], j);
         issued_k = j + 1;
         ok = mbar_wait(&bars->v_empty[s], ph ^ 1, abort_flag, 11);
         if (!ok) break;
         mbar_arrive_expect_tx(&bars->v_full[s], TILE_BYTES);
-        for (int a = 0; a < ATOMS; ++a)
-          tma_load_4d(smem + SMEM_V + s * TILE_BYTES + a * ATOM_BYTES, &tmap_v, &bars->v_full[s], a * 64, kv_head,
-                      tok0 + j * BN, batch);
+        load_tile(SMEM_V + s * TILE_BYTES, &tmap_v, &bars->v_full[s], j);
         issued_v = j + 1;
       }
       if (!ok) {
@@ -319,8 +340,8 @@ attn_dense_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       tmem_ld_wait();
       // keys past the sequence (zero fill, or the next sequence of a packed batch) and, when causal, keys after the
       // query position never contribute
-      if ((j + 1) * BN > kv_len || (p.causal && (j + 1) * BN > q_base + q * BM)) {
-        const int last_key = p.causal ? min(kv_len - 1, row) : kv_len - 1;
+      if ((j + 1) * BN > kv_len || (p.causal && (j + 1) * BN > q_base + q * BM + coff)) {
+        const int last_key = p.causal ? min(kv_len - 1, row + coff) : kv_len - 1;
 #pragma unroll
         for (int i = 0; i < BN; ++i)
           if (j * BN + i > last_key) s[i] = __float_as_uint(-INFINITY);
@@ -446,10 +467,18 @@ struct Map4Hash {
 
 // bf16 [batch, tokens, heads, 128] with element strides (tok, head, batch): dims (128, heads, tokens, batch),
 // box (64, 1, 128, 1), 128-byte swizzle, zero fill outside.
+// With page_rows > 0 the tensor is a page pool [batch = pages, heads, page_rows, 128] (contiguous): dims
+// (128, page_rows, heads, pages), box (64, page_rows, 1, 1); `tokens` and the strides are then unused.
 int make_tmap_heads(CUtensorMap* out, const void* ptr, int hd, int heads, int tokens, int batch, long long stride_head,
-                    long long stride_tok, long long stride_batch) {
+                    long long stride_tok, long long stride_batch, int page_rows = 0) {
   static std::mutex mu;
   static std::unordered_map<Map4Key, CUtensorMap, Map4Hash> cache;
+  if (page_rows > 0) {
+    tokens = -page_rows;
+    stride_head = (long long)page_rows * hd;
+    stride_tok = hd;
+    stride_batch = (long long)heads * page_rows * hd;
+  }
   Map4Key key{ptr, stride_head, stride_tok, stride_batch, heads * 1024 + hd, tokens, batch};
   {
     std::lock_guard<std::mutex> g(mu);
@@ -471,6 +500,14 @@ int make_tmap_heads(CUtensorMap* out, const void* ptr, int hd, int heads, int to
   cuuint64_t dims[4] = {(cuuint64_t)hd, (cuuint64_t)heads, (cuuint64_t)tokens, (cuuint64_t)batch};
   cuuint64_t strides[3] = {(cuuint64_t)stride_head * 2, (cuuint64_t)stride_tok * 2, (cuuint64_t)stride_batch * 2};
   cuuint32_t box[4] = {64u, 1u, (cuuint32_t)BM, 1u};
+  if (page_rows > 0) {
+    dims[1] = (cuuint64_t)page_rows;
+    dims[2] = (cuuint64_t)heads;
+    strides[0] = (cuuint64_t)stride_tok * 2;
+    strides[1] = (cuuint64_t)stride_head * 2;
+    box[1] = (cuuint32_t)page_rows;
+    box[2] = 1u;
+  }
   cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
   CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -502,19 +539,24 @@ int attn_dense_tcgen05_launch(const void* q, long long q_stride_tok, int q_strid
                               long long kv_stride_tok, int kv_stride_head, void* out, long long out_stride_tok,
                               int batch, int q_len, int kv_len, int Hq, int Hkv, float scale, cudaStream_t stream,
                               void* const* peers, int world, int split, int n0, int n1, int col_offset, int causal,
-                              const int* cu_q, int total_tokens, int head_dim) {
+                              const int* cu_q, int total_tokens, int head_dim, const int* kv_lens,
+                              const int* block_table, int max_blocks, int block_size, int num_blocks) {
   if (head_dim != 64 && head_dim != 128) return -3;
+  const bool paged = block_table != nullptr;
+  if (paged && (head_dim != 128 || !cu_q || !kv_lens || block_size < 8 || block_size % 8 || BN % block_size ||
+                num_blocks <= 0 || max_blocks <= 0 || peers))
+    return -3;
   CUtensorMap tq, tk, tv;
   // packed batches address one flat token axis (batch = the number of sequences only sizes the grid)
   const int map_q_tokens = cu_q ? total_tokens : q_len, map_kv_tokens = cu_q ? total_tokens : kv_len;
   const int map_batch = cu_q ? 1 : batch;
   int rc = make_tmap_heads(&tq, q, head_dim, Hq, map_q_tokens, map_batch, q_stride_head, q_stride_tok, q_stride_tok * map_q_tokens);
   if (rc) return rc;
-  rc = make_tmap_heads(&tk, k, head_dim, Hkv, map_kv_tokens, map_batch, kv_stride_head, kv_stride_tok,
-                       kv_stride_tok * map_kv_tokens);
+  rc = make_tmap_heads(&tk, k, head_dim, Hkv, map_kv_tokens, paged ? num_blocks : map_batch, kv_stride_head,
+                       kv_stride_tok, kv_stride_tok * map_kv_tokens, paged ? block_size : 0);
   if (rc) return rc;
-  rc = make_tmap_heads(&tv, v, head_dim, Hkv, map_kv_tokens, map_batch, kv_stride_head, kv_stride_tok,
-                       kv_stride_tok * map_kv_tokens);
+  rc = make_tmap_heads(&tv, v, head_dim, Hkv, map_kv_tokens, paged ? num_blocks : map_batch, kv_stride_head,
+                       kv_stride_tok, kv_stride_tok * map_kv_tokens, paged ? block_size : 0);
   if (rc) return rc;
   static bool configured[64] = {false};
   int dev = 0;
@@ -538,6 +580,10 @@ int attn_dense_tcgen05_launch(const void* q, long long q_stride_tok, int q_strid
   p.scale_log2 = scale * 1.4426950408889634f;
   p.causal = causal;
   p.cu_q = cu_q;
+  p.kv_lens = kv_lens;
+  p.block_table = block_table;
+  p.max_blocks = max_blocks;
+  p.block_size = block_size;
   if (cu_q) p.q_len = 0;   // rows are addressed by their flat token index
   if (peers) {
     if (world < 1 || world > 8 || batch != 1 || n1 <= 0 || (split > 0 && n0 <= 0) || (col_offset % 8) != 0) return -3;

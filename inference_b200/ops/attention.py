@@ -1,6 +1,8 @@
 """Paged and dense attention wrappers (head_dim 128)."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .._native import kernels
@@ -27,7 +29,9 @@ def paged_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
     """q: [T, Hq, 128] (any token/head strides, unit inner stride); caches [blocks, Hkv, block_size, 128];
     block_table int32 [num_seqs, max_blocks]; kv_lens int32 [num_seqs] (context length including the new
     tokens); cu_q int32 [num_seqs + 1] or None when every sequence has exactly max_q_len query tokens.
-    Bottom-right aligned causal mask like the reference SDPA (candle-llm/src/primitives/attention.rs:154-186)."""
+    Bottom-right aligned causal mask like the reference SDPA (candle-llm/src/primitives/attention.rs:154-186).
+    Prefill (decode=False) with page sizes that divide 128 and no soft cap runs on the tcgen05 kernel, which reads the
+    pages through TMA; SWB_PAGED_PREFILL=legacy keeps the mma.sync kernel (comparison runs)."""
     require_cuda(q, kcache, vcache, block_table, kv_lens)
     T, Hq, D = q.shape
     Hkv, bs = kcache.shape[1], kcache.shape[2]
@@ -36,6 +40,18 @@ def paged_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
     num_seqs = kv_lens.numel()
     if out is None:
         out = torch.empty((T, Hq * D), dtype=q.dtype, device=q.device)
+    if (not decode and D == 128 and softcap == 0.0 and use_tma and bs % 8 == 0 and 128 % bs == 0
+            and os.environ.get("SWB_PAGED_PREFILL", "tcgen05") != "legacy"):
+        if cu_q is None:
+            cu_q = torch.arange(num_seqs + 1, dtype=torch.int32, device=q.device) * max_q_len
+        rc = kernels().swb_attn_paged_prefill_tc(q.data_ptr(), q.stride(0), q.stride(1), out.data_ptr(), out.stride(0),
+                                                 kcache.data_ptr(), vcache.data_ptr(), block_table.data_ptr(),
+                                                 block_table.stride(0), bs, kcache.shape[0], cu_q.data_ptr(),
+                                                 kv_lens.data_ptr(), num_seqs, max_q_len, T, Hq, Hkv, scale,
+                                                 1 if causal else 0, stream_ptr())
+        if rc != -3:
+            check(rc, "swb_attn_paged_prefill_tc")
+            return out
     ws_ptr, ws_bytes = None, 0
     if decode and num_splits > 1:
         need = kernels().swb_attn_decode_workspace_bytes(num_seqs, Hkv, num_splits)

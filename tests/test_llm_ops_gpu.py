@@ -190,6 +190,46 @@ def test_paged_prefill(Hq, Hkv):
         o += n
 
 
+@pytest.mark.parametrize("bs", [8, 16, 32, 128])
+def test_paged_prefill_tcgen05_against_reference_and_mma_sync(bs, monkeypatch):
+    """Prefill on top of earlier context, pages read through TMA: several page sizes, contexts that end mid page and
+    mid tile, one sequence with no earlier context, uniform query lengths without cu_q, and the non-causal form."""
+    from inference_b200 import ops
+
+    D, Hq, Hkv = 128, 8, 2
+    q_lens = [300, 17, 128, 256]
+    kv_lens = [1500, 401, 128, 257]
+    kc, vc, table, ks, vs = _build_paged(kv_lens, Hkv, D, bs=bs)
+    T = sum(q_lens)
+    q = torch.randn(T, Hq, D, device="cuda").bfloat16()
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    kvl = torch.tensor(kv_lens, dtype=torch.int32, device="cuda")
+    scale = 1 / math.sqrt(D)
+    for causal in (True, False):
+        out = ops.paged_attention(q, kc, vc, table, kvl, cu_q=cu, max_q_len=max(q_lens), scale=scale, causal=causal)
+        o = 0
+        for i, n in enumerate(q_lens):
+            ref = _ref_attn(q[o:o + n], ks[i], vs[i], scale, causal)
+            err = (out[o:o + n].float() - ref).abs().max().item()
+            assert err < 3e-2, (causal, i, err)
+            o += n
+    if bs == 16:
+        monkeypatch.setenv("SWB_PAGED_PREFILL", "legacy")
+        old = ops.paged_attention(q, kc, vc, table, kvl, cu_q=cu, max_q_len=max(q_lens), scale=scale, causal=True)
+        monkeypatch.setenv("SWB_PAGED_PREFILL", "tcgen05")
+        new = ops.paged_attention(q, kc, vc, table, kvl, cu_q=cu, max_q_len=max(q_lens), scale=scale, causal=True)
+        assert (old.float() - new.float()).abs().max().item() < 3e-2
+    # uniform query lengths, no cu_q
+    kv2 = [200, 136, 264]
+    kc, vc, table, ks, vs = _build_paged(kv2, Hkv, D, bs=bs)
+    q = torch.randn(3 * 136, Hq, D, device="cuda").bfloat16()
+    out = ops.paged_attention(q, kc, vc, table, torch.tensor(kv2, dtype=torch.int32, device="cuda"), cu_q=None, max_q_len=136,
+                              scale=scale, causal=True)
+    for i in range(3):
+        ref = _ref_attn(q[i * 136:(i + 1) * 136], ks[i], vs[i], scale, True)
+        assert (out[i * 136:(i + 1) * 136].float() - ref).abs().max().item() < 3e-2, i
+
+
 @pytest.mark.parametrize("use_tma", [True, False])
 @pytest.mark.parametrize("splits", [1, 3, 8])
 @pytest.mark.parametrize("q_len", [1, 3])
