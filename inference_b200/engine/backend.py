@@ -40,9 +40,19 @@ def set_embed_override(seq: Any, positions: list[int], values: torch.Tensor) -> 
 
 def set_mrope_override(seq: Any, positions: torch.Tensor, next_position: int, rows: torch.Tensor,
                        taps: list[torch.Tensor]) -> None:
-    """Qwen3-VL prompts (oracle backend): the next forward on `seq` uses the three-axis positions [3, S] of its new
-    tokens and adds the DeepStack taps at `rows`; later tokens continue at `next_position`."""
+    """Qwen3-VL prompts: the next forward on `seq` uses the three-axis positions [3, S] of its new tokens and adds the
+    DeepStack taps at `rows`; later tokens continue at `next_position`."""
     seq.pending_mrope = (positions, int(next_position), rows, taps)
+
+
+def _take_mrope(seqs) -> list | None:
+    mr = [getattr(s, "pending_mrope", None) for s in seqs]
+    if not any(m is not None for m in mr):
+        return None
+    for s in seqs:
+        if getattr(s, "pending_mrope", None) is not None:
+            s.pending_mrope = None
+    return mr
 
 
 def _take_overrides(seqs) -> list | None:
@@ -71,12 +81,12 @@ class GpuBackend:
         return all(len(t) == 1 for t in new_tokens) and len(seqs) <= self.runner.max_batch
 
     def forward(self, seqs, new_tokens, all_positions=False):
-        ov = _take_overrides(seqs)
-        if ov is None and not all_positions and self._is_decode(seqs, new_tokens):
+        ov, mr = _take_overrides(seqs), _take_mrope(seqs)
+        if ov is None and mr is None and not all_positions and self._is_decode(seqs, new_tokens):
             logits = self.runner.decode(seqs, [t[0] for t in new_tokens], want_logits=True)
             return [logits[i] for i in range(len(seqs))]
         logits = self.runner.prefill(seqs, new_tokens, want_logits=True, all_positions=all_positions,
-                                     embed_overrides=ov)
+                                     embed_overrides=ov, mrope_overrides=mr)
         if not all_positions:
             return [logits[i] for i in range(len(seqs))]
         out, o = [], 0
@@ -86,10 +96,10 @@ class GpuBackend:
         return out
 
     def forward_greedy(self, seqs, new_tokens):
-        ov = _take_overrides(seqs)
-        if ov is None and self._is_decode(seqs, new_tokens):
+        ov, mr = _take_overrides(seqs), _take_mrope(seqs)
+        if ov is None and mr is None and self._is_decode(seqs, new_tokens):
             return [int(x) for x in self.runner.decode(seqs, [t[0] for t in new_tokens]).tolist()]
-        return [int(x) for x in self.runner.prefill(seqs, new_tokens, embed_overrides=ov).tolist()]
+        return [int(x) for x in self.runner.prefill(seqs, new_tokens, embed_overrides=ov, mrope_overrides=mr).tolist()]
 
     def truncate(self, seq, length):
         seq.truncate(length)
@@ -97,7 +107,10 @@ class GpuBackend:
     def fork(self, seq, n_tokens):
         bs = self.runner.pool.block_size
         whole = (n_tokens // bs) * bs
-        return PagedSequence.seeded(self.runner.pool, seq.shareable_prefix_blocks(whole), whole)
+        f = PagedSequence.seeded(self.runner.pool, seq.shareable_prefix_blocks(whole), whole)
+        if getattr(seq, "rope_delta", 0):
+            f.rope_delta = seq.rope_delta
+        return f
 
     def release(self, seq):
         seq.release()

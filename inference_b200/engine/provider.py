@@ -5,6 +5,7 @@ tool-call segmentation, stop strings, incremental detokenisation, typed cancel, 
 from __future__ import annotations
 
 import json
+import os
 from pathlib import Path
 from typing import Callable
 
@@ -468,8 +469,12 @@ class Qwen3VlProvider(LlamaProvider):
         if on_gpu and not torch.cuda.is_available():
             raise LoadError("the b200 backend needs a CUDA device (use the cpu runtime bundle on hosts without one)")
         dev, dtype = ("cuda", torch.bfloat16) if on_gpu else ("cpu", torch.float32)
-        backend = OracleBackend(OracleLlama(cfg, text, dtype=dtype, device=dev),
-                                max_context=cfg.max_position_embeddings or 8192)
+        if on_gpu and _supported_on_gpu(cfg) and os.environ.get("SWB_QWEN3_VL_DECODER", "paged") != "oracle":
+            # the paged sm_100a decoder: per-token three-axis rotary table and DeepStack taps ride on the prefill step
+            backend = _build_backend(cfg, text, backend_name, comm)
+        else:
+            backend = OracleBackend(OracleLlama(cfg, text, dtype=dtype, device=dev),
+                                    max_context=cfg.max_position_embeddings or 8192)
         caps = TextLlmCapabilities(max_context_tokens=backend.max_context, max_new_tokens=0, supports_system_prompt=True,
                                    supports_vision=True, supports_video=False, supports_thinking=thinking,
                                    supports_tools=tools, supported_constraints=[Constraint.JSON])

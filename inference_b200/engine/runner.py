@@ -89,11 +89,15 @@ class ModelRunner:
 
     # ---- prefill (eager, ragged) ------------------------------------------------------------------
     def prefill(self, seqs: list[PagedSequence], new_tokens: list[list[int]], *, want_logits: bool = False,
-                all_positions: bool = False, embed_overrides: list[tuple[list[int], torch.Tensor] | None] | None = None):
+                all_positions: bool = False, embed_overrides: list[tuple[list[int], torch.Tensor] | None] | None = None,
+                mrope_overrides: list | None = None):
         """Appends new_tokens[i] to seqs[i] (any mix of lengths, including chunked / prefix-seeded sequences)
         and returns greedy next tokens [num_seqs] (or fp32 logits when want_logits). embed_overrides[i] =
         (positions within new_tokens[i], vectors [len(positions), hidden]) replaces those tokens' embeddings (the
-        image placeholders of a vision-language prompt)."""
+        image placeholders of a vision-language prompt). mrope_overrides[i] = (positions [3, len(new_tokens[i])], next
+        position, rows within new_tokens[i], taps) gives those tokens three-axis rotary positions and adds taps[l] to
+        the residual stream at `rows` after decoder layer l; the sequence's later tokens continue at `next position`
+        (kept on the sequence as `rope_delta`)."""
         dev = self.model.device
         ids, pos, slots, cu, kvl, rows = [], [], [], [0], [], []
         fresh = all(s.length == 0 for s in seqs)     # no earlier context: attention can read K / V from the QKV buffer
@@ -101,7 +105,8 @@ class ModelRunner:
             start = s.length
             sl = s.reserve(len(toks))
             ids += toks
-            pos += list(range(start, start + len(toks)))
+            delta = getattr(s, "rope_delta", 0)
+            pos += list(range(start + delta, start + delta + len(toks)))
             slots += sl
             cu.append(cu[-1] + len(toks))
             kvl.append(s.length)
@@ -131,12 +136,39 @@ class ModelRunner:
             if er:
                 inp.embed_rows = torch.tensor(er, dtype=torch.int64, device=dev)
                 inp.embed_values = torch.cat(ev, dim=0)
+        if mrope_overrides is not None and any(m is not None for m in mrope_overrides):
+            self._apply_mrope(inp, seqs, mrope_overrides, cu)
         with tracing.span("runner.prefill", tokens=len(ids), seqs=len(seqs)):
             hidden = self.model.forward_hidden(inp, self.pool.data)
             self.launches_last = self.model.launches
             if want_logits or all_positions:
                 return self.model.logits(hidden)
             return self.model.greedy_tokens(hidden)
+
+    def _apply_mrope(self, inp: StepInputs, seqs, overrides, cu: list[int]) -> None:
+        """Per-token rotary table for a step in which some sequences carry three-axis positions (the others keep their
+        scalar positions on all three axes), the flat DeepStack rows, and each such sequence's `rope_delta`."""
+        from ..models.qwen3_vl import interleaved_mrope_table
+
+        m = self.model
+        pos3 = inp.positions.to(torch.int64)[None, :].repeat(3, 1)
+        rows, levels = [], []
+        for i, (s, ov) in enumerate(zip(seqs, overrides)):
+            if ov is None:
+                continue
+            p3, nxt, r, taps = ov
+            pos3[:, cu[i]:cu[i + 1]] = p3.to(pos3.device)
+            s.rope_delta = int(nxt) - s.length
+            if len(taps):
+                rows.append(r.to(pos3.device, torch.int64) + cu[i])
+                levels.append(taps)
+        inv = torch.tensor(m._inv_freq, dtype=torch.float32, device=pos3.device) if not torch.is_tensor(m._inv_freq) \
+            else m._inv_freq.to(pos3.device, torch.float32)
+        cos, sin = interleaved_mrope_table(pos3, inv, m.cfg.mrope_section_resolved())
+        inp.rope_table = (cos.float().contiguous(), sin.float().contiguous())
+        if rows:
+            depth = min(len(t) for t in levels)
+            inp.deepstack = (torch.cat(rows), [torch.cat([t[l].to(pos3.device) for t in levels], dim=0) for l in range(depth)])
 
     # ---- decode (graph-captured, one token per sequence) ---------------------------------------------
     def _fill_decode_meta(self, seqs: list[PagedSequence], tokens: list[int], pad_to: int = 0) -> int:
@@ -154,7 +186,7 @@ class ModelRunner:
             p = s.length
             slot = s.reserve(1)[0]
             h[i] = tokens[i]
-            h[MB + i] = p
+            h[MB + i] = p + getattr(s, "rope_delta", 0)
             h[2 * MB + i] = slot
             h[3 * MB + i] = p + 1
             if p + 1 > max_kv:

@@ -39,6 +39,10 @@ class StepInputs:
     fresh_prefill: bool = False        # every sequence starts at position 0 (context == this step's tokens)
     embed_rows: torch.Tensor | None = None    # int64 [R]: rows of the flat batch whose embedding is replaced ...
     embed_values: torch.Tensor | None = None  # ... by these [R, H] vectors (projected image features of a VLM prompt)
+    rope_table: tuple[torch.Tensor, torch.Tensor] | None = None   # fp32 cos / sin [T, rot_dim / 2], one row per token of
+    #                                           this step: replaces the position-indexed table (three-axis rotary phases)
+    deepstack: tuple[torch.Tensor, list[torch.Tensor]] | None = None   # (int64 rows [R], taps): taps[l] [R, H] is added
+    #                                           to the residual stream at those rows after decoder layer l (Qwen3-VL)
 
 
 @dataclass
@@ -362,11 +366,17 @@ class LlamaGpu:
         D = cfg.head_dim
         eps, woff = cfg.rms_norm_eps, cfg.norm_weight_offset
         T = inp.input_ids.numel()
-        if self._use_tp_prefill(T) and inp.embed_rows is None:
+        if self._use_tp_prefill(T) and inp.embed_rows is None and inp.rope_table is None and inp.deepstack is None:
             return self._forward_hidden_tp_prefill(inp, kv_pool)
+        rope_pos, rope_cos, rope_sin = inp.positions, self.cos, self.sin
+        if inp.rope_table is not None:
+            rope_cos, rope_sin = inp.rope_table
+            rope_pos = torch.arange(T, dtype=torch.int32, device=self.device)
+        taps = inp.deepstack[1] if inp.deepstack is not None else []
         # decode-sized steps of a dense model: the norms are folded into a chain of GEMM epilogues
         chain = (self._chain_ok and inp.decode and T <= 64 and self.quant_format is None and
                  os.environ.get("SWB_NORM_CHAIN", "1") != "0")
+        chain = chain and not taps
         fc = self.comm.fused if self.comm.is_parallel else None
         if chain and self.comm.is_parallel:
             chain = fc is not None and T <= fc.chain_tokens and stage_in is None
@@ -400,7 +410,7 @@ class LlamaGpu:
                 qkv = ops.gemm_bf16_normed(res, L.qkv, bias=L.qkv_bias, ssq_in=ssq_prev, norm_dim=H, eps=eps)
             else:
                 qkv = ops.linear_any(h, L.qkv, bias=L.qkv_bias)
-            ops.rope_kv_write(qkv, inp.positions, inp.slot_mapping, self.cos, self.sin, kv_pool[li, 0], kv_pool[li, 1],
+            ops.rope_kv_write(qkv, rope_pos, inp.slot_mapping, rope_cos, rope_sin, kv_pool[li, 0], kv_pool[li, 1],
                               self.hq, self.hkv, D, rot_dim=self.rot_dim, interleaved=self.rope_interleaved,
                               q_norm=L.q_norm, k_norm=L.k_norm, norm_eps=eps, norm_w_offset=woff,
                               block_size=block_size)
@@ -438,7 +448,7 @@ class LlamaGpu:
                 n += 6 + (1 if h is not None else 0)
                 continue
             fused = self.comm.fused if (self.comm.fused is not None and T <= self.comm.fused.max_tokens and
-                                        L.post_attn_ln is None) else None
+                                        L.post_attn_ln is None and li >= len(taps)) else None
             if fused is not None:
                 h = fused.gemm_allreduce_rmsnorm(attn, L.o, res, L.ln2, eps, woff)
             else:
@@ -453,6 +463,8 @@ class LlamaGpu:
                 pending_h = None
                 branch = self.comm.all_reduce(self._moe_ffn(h, L.moe))
                 n += 9
+                if li < len(taps):      # the stream after this layer is res + branch: the tap joins the pending branch
+                    branch.index_add_(0, inp.deepstack[0], taps[li].to(branch.dtype))
                 continue
             act = self._gated_mlp_in(h, L.gate_up)
             if fused is not None and L.post_mlp_ln is None:
@@ -467,6 +479,8 @@ class LlamaGpu:
                 if L.post_mlp_ln is not None:
                     branch = ops.rmsnorm(branch, L.post_mlp_ln, eps, w_offset=woff)
                     n += 1
+            if li < len(taps):
+                branch.index_add_(0, inp.deepstack[0], taps[li].to(branch.dtype))
             n += 7 + self._mlp_in_launches
         self.launches = n
         if not last_stage:

@@ -370,3 +370,78 @@ def test_qwen3_vl_provider_on_the_device(tmp_path):
     finally:
         Q3.image_to_patches = orig
     assert res.usage.generated_tokens >= 1
+
+
+def test_qwen3_vl_paged_decoder_matches_the_oracle_decoder(tmp_path, monkeypatch):
+    """Qwen3-VL with 128-wide heads runs on the paged sm_100a decoder: the image prompt's three-axis rotary table and
+    DeepStack taps ride on the prefill step, later tokens continue at the shifted position. Same snapshot and request
+    through the oracle decoder (bf16, framework ops): the first-step logits agree and greedy decoding emits the same
+    tokens; a text-only request on the same provider still decodes."""
+    import json
+    import sys
+    from pathlib import Path
+
+    sys.path.insert(0, str(Path(__file__).parent))
+    from test_qwen3_vl_cpu import _hf
+
+    import inference_b200.models.qwen3_vl as Q3
+    from inference_b200.bundles import runtime_b200
+    from inference_b200.contracts.core_llm import LoadSpec, Message, Role, TextLlmRequest
+    from inference_b200.contracts.core_llm.message import ImageRef, Text
+    from inference_b200.contracts.core_llm.request import Sampling
+    from inference_b200.engine.backend import GpuBackend, OracleBackend
+    from inference_b200.io.safetensors_io import save_file
+    from inference_b200.testkit.synthetic import wordlevel_tokenizer_json
+
+    cfg, hf = _hf(seed=5, head_dim=128, mrope_section=(24, 20, 20))
+    top = cfg.to_dict()
+    top["model_type"], top["architectures"] = "qwen3_vl", ["Qwen3VLForConditionalGeneration"]
+    (tmp_path / "config.json").write_text(json.dumps(top))
+    save_file({k: v.contiguous() for k, v in hf.state_dict().items()}, tmp_path / "model.safetensors")
+    tok = json.loads(wordlevel_tokenizer_json(200))
+    special = {150: "<|image_pad|>", 151: "<|video_pad|>", 152: "<|vision_start|>", 153: "<|vision_end|>"}
+    tok["model"]["vocab"] = {special.get(i, w): i for w, i in tok["model"]["vocab"].items()}
+    tok["added_tokens"] = tok.get("added_tokens", []) + [
+        {"id": i, "content": c, "single_word": False, "lstrip": False, "rstrip": False, "normalized": False, "special": True}
+        for i, c in special.items()]
+    (tmp_path / "tokenizer.json").write_text(json.dumps(tok))
+    (tmp_path / "tokenizer_config.json").write_text(json.dumps({"eos_token": "<|im_end|>"}))
+    g = torch.Generator().manual_seed(5)
+    raw = bytes(torch.randint(0, 256, (16 * 24 * 3,), generator=g, dtype=torch.uint8).tolist())
+    req = lambda: TextLlmRequest(messages=[Message(Role.USER, [ImageRef(24, 16, raw), Text("the cat sat on the mat")])],   # noqa: E731
+                                 max_new_tokens=6, seed=0, sampling=Sampling(temperature=0.0))
+    orig = Q3.image_to_patches
+    monkeypatch.setattr(Q3, "image_to_patches", lambda rgb, vc_, **kw: orig(rgb, vc_, min_pixels=16, max_pixels=10 ** 6))
+    out, first = {}, {}
+    for mode, kind in (("paged", GpuBackend), ("oracle", OracleBackend)):
+        monkeypatch.setenv("SWB_QWEN3_VL_DECODER", mode)
+        llm = runtime_b200.catalog().text().load_for_model(LoadSpec.dense(str(tmp_path)))
+        assert isinstance(llm.backend, kind), mode
+        r = req()
+        res = llm.generate(r, on_event=lambda e: None)
+        out[mode] = res.text
+        assert res.usage.generated_tokens >= 1
+        # first-step logits through the backend itself
+        prompt_ids, seq = llm._splice_media(r, _prompt_ids(llm, r))
+        first[mode] = llm.backend.forward([seq], [prompt_ids])[0].float().cpu()
+        nxt = int(first[mode].argmax())
+        second = llm.backend.forward([seq], [[nxt]])[0].float().cpu()       # the decode step continues at the shifted position
+        first[mode + "2"] = second
+        llm.backend.release(seq)
+        if mode == "paged":
+            plain = llm.generate(TextLlmRequest(messages=[Message(Role.USER, [Text("the cat sat")])], max_new_tokens=3, seed=0,
+                                                sampling=Sampling(temperature=0.0)), on_event=lambda e: None)
+            assert plain.usage.generated_tokens >= 1
+        del llm
+    for k in ("paged", "paged2"):
+        ref = first[k.replace("paged", "oracle")]
+        assert (first[k] - ref).abs().max().item() < 0.06 * max(1.0, ref.abs().max().item()), k
+    assert out["paged"] == out["oracle"]
+
+
+def _prompt_ids(llm, req):
+    """The provider's own prompt rendering, without running a generation."""
+    from inference_b200.contracts.core_llm import RenderOptions
+
+    prompt = llm.template.render_with(llm._render_messages(req), RenderOptions(True, req.enable_thinking_kwarg(), req.tools))
+    return llm.tokenizer.encode(prompt, add_special_tokens=False)

@@ -9,14 +9,15 @@ from inference_b200.models import qwen3_vl as V
 transformers = pytest.importorskip("transformers")
 
 
-def _hf(seed=0):
+def _hf(seed=0, head_dim=32, mrope_section=(6, 5, 5)):
     from transformers import Qwen3VLConfig, Qwen3VLForConditionalGeneration
 
     cfg = Qwen3VLConfig(
         text_config=dict(hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
-                         num_key_value_heads=2, head_dim=32, vocab_size=200, max_position_embeddings=512,
-                         rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [6, 5, 5],
-                                          "mrope_interleaved": True}, tie_word_embeddings=False),
+                         num_key_value_heads=2, head_dim=head_dim, vocab_size=200, max_position_embeddings=512,
+                         rope_parameters={"rope_type": "default", "rope_theta": 10000.0,
+                                          "mrope_section": list(mrope_section), "mrope_interleaved": True},
+                         tie_word_embeddings=False),
         vision_config=dict(depth=4, hidden_size=48, num_heads=4, intermediate_size=96, patch_size=4, temporal_patch_size=2,
                            spatial_merge_size=2, out_hidden_size=64, num_position_embeddings=36,
                            deepstack_visual_indexes=[0, 1, 2]),
