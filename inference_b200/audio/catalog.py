@@ -91,10 +91,10 @@ def _openvoice_registration(backend: str) -> Registration:
 
 
 def register_providers(b: ProviderRegistryBuilder, backend: str) -> ProviderRegistryBuilder:
-    from . import acestep, kokoro, moss_sfx, moss_ttsd
+    from . import acestep, kokoro, moss_sfx, moss_tts_realtime, moss_ttsd
 
     b.register_generators([kokoro.registration(backend), moss_sfx.registration(backend), moss_ttsd.registration(backend),
-                           acestep.registration(backend)])
+                           acestep.registration(backend), moss_tts_realtime.registration(backend)])
     b.register("transcriber", _whisper_registration(backend))
     b.register("voice_embedder", _chatterbox_ve_registration(backend))
     b.register("audio_embedder", _clap_registration(backend))
@@ -110,9 +110,10 @@ def weight_licenses() -> list[WeightLicenseEntry]:
     from .kokoro import KOKORO_LICENSE
     from .acestep import ACESTEP_LICENSE
     from .moss_sfx import MOSS_SFX_LICENSE
+    from .moss_tts_realtime import MOSS_TTS_REALTIME_LICENSE
     from .moss_ttsd import MOSS_TTSD_LICENSE
 
-    return [WeightLicenseEntry("kokoro_82m", KOKORO_LICENSE), WeightLicenseEntry("moss_sfx_v2", MOSS_SFX_LICENSE), WeightLicenseEntry("moss_ttsd_v05", MOSS_TTSD_LICENSE), WeightLicenseEntry("acestep_v15_turbo", ACESTEP_LICENSE), WeightLicenseEntry("whisper", WHISPER_LICENSE), WeightLicenseEntry("chatterbox_ve", CHATTERBOX_LICENSE),
+    return [WeightLicenseEntry("kokoro_82m", KOKORO_LICENSE), WeightLicenseEntry("moss_sfx_v2", MOSS_SFX_LICENSE), WeightLicenseEntry("moss_ttsd_v05", MOSS_TTSD_LICENSE), WeightLicenseEntry("acestep_v15_turbo", ACESTEP_LICENSE), WeightLicenseEntry("moss_tts_realtime", MOSS_TTS_REALTIME_LICENSE), WeightLicenseEntry("whisper", WHISPER_LICENSE), WeightLicenseEntry("chatterbox_ve", CHATTERBOX_LICENSE),
             WeightLicenseEntry("clap_htsat_unfused", CLAP_LICENSE), WeightLicenseEntry("openvoice_v2", OPENVOICE_LICENSE)]
 
 

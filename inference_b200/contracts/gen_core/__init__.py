@@ -1,10 +1,11 @@
 """Tensor-free media contracts: generator trait and request model, load types, registries, the unified sampler
 framework, guidance, tiling and memory policy (parity target: crates/contracts/gen-core)."""
 from ..errors import Canceled, InferenceError, InvalidRequest, LoadError, Unsupported  # noqa: F401
-from .generator import (AudioParams, Capabilities, Conditioning, ConditioningKind, GenerationOutput,  # noqa: F401
-                        GenerationPhase, GenerationRequest, Generator, Modality, ModelDescriptor)
+from .generator import (AudioParams, Capabilities, Conditioning, ConditioningKind, ConversationSession,  # noqa: F401
+                        ConversationTurn, GenerationOutput, GenerationPhase, GenerationRequest, Generator, Modality,
+                        ModelDescriptor)
 from .guidance import GUIDANCE_METHODS, GuidanceMethod, MomentumBuffer, apg, apg_delta, cfg, cfg_rescale  # noqa: F401
-from .media import AudioTrack, Image  # noqa: F401
+from .media import AudioChunk, AudioTrack, Image  # noqa: F401
 from .registry import (ModelRegistration, PerComponentBytes, ProviderRegistry, ProviderRegistryBuilder,  # noqa: F401
                        Registration, model_descriptor_errors)
 from .runtime import (AdapterKind, AdapterSpec, CancelFlag, LoadPhase, LoadSpec, OffloadPolicy, Precision,  # noqa: F401

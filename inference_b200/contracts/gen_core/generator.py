@@ -61,6 +61,28 @@ class Conditioning:
     frame_index: int | None = None
     mode: str | None = None
     region: tuple[float, float | None] | None = None   # (start_secs, end_secs)
+    turns: list = field(default_factory=list)           # CONVERSATION_HISTORY: list[ConversationTurn]
+
+
+@dataclass
+class ConversationTurn:
+    """One turn of a multi-turn conversation: role "user" or "assistant", its text, and its audio when the turn is
+    provided context (a user turn always carries audio; an assistant turn without audio is synthesised)."""
+    role: str = "assistant"
+    text: str = ""
+    audio: AudioTrack | None = None
+
+
+class ConversationSession(abc.ABC):
+    """Stateful counterpart of a CONVERSATION_HISTORY request: the model's cross-turn state stays live, each `step`
+    advances by one turn and returns that turn's audio. For the same conversation and seed a session emits the samples
+    a single request carrying all turns emits (gen-core/src/generator.rs:120-168)."""
+
+    @abc.abstractmethod
+    def step(self, turn: ConversationTurn, on_chunk=lambda c: None, on_progress=lambda p: None) -> AudioTrack: ...
+
+    def finish(self) -> None:
+        return None
 
 
 @dataclass
@@ -282,6 +304,18 @@ class Capabilities:
                         msg(f"audio edit region start {start}s must be >= 0")
                     if end is not None and end <= start:
                         msg(f"audio edit region end {end}s must be > start {start}s")
+            if c.kind is ConditioningKind.CONVERSATION_HISTORY:
+                if not self.supports_conversation_history:
+                    gap("conversation histories are not supported")
+                if not c.turns:
+                    msg("a conversation history must carry at least one turn")
+                for i, t in enumerate(c.turns):
+                    if t.role not in ("user", "assistant"):
+                        msg(f"conversation turn {i}: unknown role {t.role!r}")
+                    if not t.text.strip():
+                        msg(f"conversation turn {i}: empty text")
+                    if t.role == "user" and t.audio is None:
+                        msg(f"conversation turn {i}: a user turn must carry its audio")
             if c.kind is ConditioningKind.VIDEO_SYNC and not c.frames:
                 msg("VideoSync conditioning carries no frames - a video->audio clip must have at least one frame")
 
@@ -314,5 +348,7 @@ class Generator(abc.ABC):
             on_chunk(out.audio)
         return out
 
-    def open_conversation(self) -> Any:
+    def open_conversation(self, req: GenerationRequest | None = None) -> ConversationSession:
+        """`req` carries what stays constant across the conversation (seed, audio knobs, a reference voice, the cancel
+        flag); the turns arrive through the session's `step`."""
         raise Unsupported(f"{self.descriptor().id}: conversation sessions are not supported")

@@ -23,3 +23,12 @@ class AudioTrack:
     sample_rate: int
     channels: int
     samples: list[float] = field(default_factory=list)  # interleaved f32 PCM in [-1, 1]
+
+
+@dataclass
+class AudioChunk:
+    """One block of a streamed track: chunks arrive in `index` order and concatenate to the returned track."""
+    sample_rate: int
+    channels: int
+    samples: list[float] = field(default_factory=list)
+    index: int = 0

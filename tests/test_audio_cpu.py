@@ -177,8 +177,8 @@ def test_audio_catalog_registers_whisper_and_licenses(tmp_path):
     reg = catalog.provider_registry("cpu")
     assert reg.ids("transcriber") == ["whisper"] and reg.descriptor_conformance_errors() == []
     manifest = json.loads(catalog.weight_licenses_manifest())
-    assert [r["provider_id"] for r in manifest["model_weight_licenses"]] == ["acestep_v15_turbo", "chatterbox_ve", "clap_htsat_unfused", "kokoro_82m", "moss_sfx_v2", "moss_ttsd_v05", "openvoice_v2", "whisper"]
-    assert reg.ids() == ["cpu_kokoro_82m", "cpu_moss_sfx_v2", "cpu_moss_ttsd_v05", "cpu_acestep_v15_turbo"] and catalog.can_prepare(["k/config.json", "k/kokoro-v1_0.pth", "k/voices/af_heart.pt"])
+    assert [r["provider_id"] for r in manifest["model_weight_licenses"]] == ["acestep_v15_turbo", "chatterbox_ve", "clap_htsat_unfused", "kokoro_82m", "moss_sfx_v2", "moss_tts_realtime", "moss_ttsd_v05", "openvoice_v2", "whisper"]
+    assert reg.ids() == ["cpu_kokoro_82m", "cpu_moss_sfx_v2", "cpu_moss_ttsd_v05", "cpu_acestep_v15_turbo", "cpu_moss_tts_realtime"] and catalog.can_prepare(["k/config.json", "k/kokoro-v1_0.pth", "k/voices/af_heart.pt"])
     assert catalog.can_prepare(["a/config.json", "a/tokenizer.json", "a/model.safetensors"])
     assert not catalog.can_prepare(["a/config.json", "a/model.safetensors"])
     hc, hf = _tiny_whisper()

@@ -54,3 +54,35 @@ def test_acestep_on_device_tracks_the_oracle_backend(tmp_path):
         assert float(np.abs(out["b200"] - out["cpu"]).mean()) / denom < 0.25, name
     keep = out["b200"].reshape(-1, 2)[:120]
     assert np.array_equal(keep, src.numpy()[:120])                     # outside the window the source survives bit for bit
+
+
+@pytest.mark.gpu
+def test_moss_tts_realtime_on_device(tmp_path):
+    """The streaming text-to-speech generator on the sm_100a backend: the codec (bf16 stages through the tensor-core GEMM)
+    tracks the fp32 codec on the same frames in both directions' shapes, and a streamed request yields chunks that
+    concatenate to the returned track (sampled tokens are not compared across precisions: one flipped draw changes the
+    rest of the utterance)."""
+    import torch
+
+    from inference_b200.audio import moss_tts_realtime as M
+    from inference_b200.audio.catalog import provider_registry
+    from inference_b200.contracts.gen_core import GenerationRequest, LoadSpec
+    from inference_b200.contracts.gen_core.generator import AudioParams
+    from inference_b200.contracts.gen_core.runtime import WeightsSource
+
+    model, codec = M.write_synthetic_snapshot(tmp_path / "m")
+    frames = torch.randint(0, 8, (20, 4), generator=torch.Generator().manual_seed(0)).tolist()
+    ref = M.MossAudioCodec(codec, 4, "cpu").decode_frames(frames)
+    dev = M.MossAudioCodec(codec, 4, "cuda")
+    got = dev.decode_frames(frames)
+    assert got.shape == ref.shape == (20 * 24,)
+    assert float((got - ref).abs().mean()) / (float(ref.abs().mean()) + 1e-6) < 0.1
+    assert len(dev.encode(ref, 24_000)) == 20
+    spec = LoadSpec.from_dir(model)
+    spec.components["codec"] = WeightsSource.dir(codec)
+    gen = provider_registry("b200").load("moss_tts_realtime", spec)
+    chunks = []
+    track = gen.generate_streaming(GenerationRequest(prompt="hello there how are you", seed=3, audio=AudioParams(target_duration=1.6)),
+                                   lambda p: None, chunks.append).audio
+    assert track.sample_rate == 24_000 and len(track.samples) > 0 and len(track.samples) % 24 == 0
+    assert sum((c.samples for c in chunks), []) == track.samples

@@ -26,7 +26,7 @@ def test_catalogs_validate_and_snapshot():
         assert snap["backend"] == backend and snap["text_llm_ids"] == [llm, llm.replace("llama", "llava"), llm.replace("llama", "qwen3-vl")]
         assert snap["snapshot_preparer_backends"] == [backend] and len(snap["generator_ids"]) == 37
         assert snap["audio_backend"] == backend and snap["audio_transcriber_ids"] == ["whisper"]
-        assert snap["audio_generator_ids"] == [("" if backend == "b200" else "cpu_") + n for n in ("kokoro_82m", "moss_sfx_v2", "moss_ttsd_v05", "acestep_v15_turbo")]
+        assert snap["audio_generator_ids"] == [("" if backend == "b200" else "cpu_") + n for n in ("kokoro_82m", "moss_sfx_v2", "moss_ttsd_v05", "acestep_v15_turbo", "moss_tts_realtime")]
 
 
 def test_catalog_rejects_mixed_backends_and_missing_preparer():
