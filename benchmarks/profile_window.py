@@ -8,6 +8,7 @@ with cudaProfilerStart/Stop so that `ncu --profile-from-start off` sees only tho
   --what quant    one Q4_K dequant-GEMM (T from --shape "Tx..", N=28672, K=4096: the gate/up projection)
   --what attn     one split-KV decode attention launch (batch 64, 8 KV heads, context 2048)
   --what attn_dense one dense non-causal attention launch (S=4608, 24 heads)
+  --what vae      one FLUX-class VAE decode, 128 x 128 latents -> 1024 x 1024 (about 115 launches, 1.3 GB live)
 """
 import argparse
 import os
@@ -78,6 +79,12 @@ def main():
         S, H = 4608, 24
         q, k, v = (torch.randn(1, S, H, 128, device=dev, generator=g).bfloat16() for _ in range(3))
         window(lambda: ops.dense_attention(q, k, v, scale=128 ** -0.5, causal=False), reps=args.reps)
+    elif args.what == "vae":
+        from inference_b200.models.vae import VaeConfig, VaeDecoderGpu
+
+        dec = VaeDecoderGpu(VaeConfig(), device=dev).init_random(0)
+        z = torch.randn(1, 16, 128, 128, device=dev, generator=g)
+        window(lambda: dec.decode(z), reps=args.reps)
     elif args.what == "dit":
         from inference_b200.contracts.gen_core.sampling import build_flow_sigmas, compute_mu, image_seq_len
         from inference_b200.models.dit_flux import FluxConfig, FluxDiTGpu, make_ids, rope_table

@@ -135,6 +135,8 @@ def _declare_kernels(lib: ctypes.CDLL) -> None:
     sig("swb_dequant_rows", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
     sig("swb_peer_barrier", [c_void_p, c_void_p, c_int, c_int, c_void_p])
     sig("swb_im2col3x3", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    sig("swb_conv3x3_nhwc", [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                             c_int, c_int, c_void_p])
     sig("swb_softmax_rows", [c_void_p, c_void_p, c_int, c_int, c_ll, c_ll, c_float, c_void_p])
     sig("swb_rgb8", [c_void_p, c_void_p, c_ll, c_int, c_void_p])
     sig("swb_comm_max_ctas", [])

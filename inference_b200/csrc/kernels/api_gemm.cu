@@ -43,6 +43,40 @@ int swb_gemm_bf16(const void* A, int lda, const void* W, int ldw, void* D, int l
   return swb::gemm_bf16_launch(a, reinterpret_cast<cudaStream_t>(stream));
 }
 
+// 3x3 convolution, stride 1, zero padding 1, over an NHWC bf16 activation x [n, h, w, c] as an implicit GEMM on the
+// tcgen05 kernel: no patch matrix is written; each reduction block is one window tap over one 64-channel slab, fetched
+// by a 4-D TMA box at the tile's pixel origin shifted by the tap (zero fill outside the image is the padding).
+// W [cout, (ky, kx, cin)] bf16 rows of 9 c; out [n h w, cout] bf16 (= NHWC); optional bias [cout] and residual
+// [n h w, cout]. Needs c % 64 == 0, h w % 128 == 0 and w a multiple or a divisor of 128; returns -3 otherwise.
+int swb_conv3x3_nhwc(const void* x, int n, int h, int w, int c, const void* W, int ldw, int cout, void* out, int ldd,
+                     const void* bias, const void* residual, int ld_res, int act, void* stream) {
+  swb::GemmArgs a;
+  a.A = x;
+  a.lda = c;
+  a.W = W;
+  a.ldw = ldw;
+  a.D = out;
+  a.ldd = ldd;
+  a.T = n * h * w;
+  a.N = cout;
+  a.K = 9 * c;
+  a.bias = bias;
+  a.residual = residual;
+  a.ld_res = ld_res;
+  a.act = act;
+  a.out_fp32 = 0;
+  a.workspace = nullptr;
+  a.workspace_bytes = 0;
+  a.force_mode = 0;
+  a.force_block_n = 0;
+  a.force_ctas = -1;
+  a.conv_n = n;
+  a.conv_h = h;
+  a.conv_w = w;
+  a.conv_c = c;
+  return swb::gemm_bf16_launch(a, reinterpret_cast<cudaStream_t>(stream));
+}
+
 // GEMM whose epilogue dispatches the output head-sharded to peers (see GemmScatter): D is not written locally.
 // peers: `world` device pointers to every rank's receive buffer [global rows, N / (heads * 128), heads_per_rank, 128].
 int swb_gemm_bf16_scatter(const void* A, int lda, const void* W, int ldw, int T, int N, int K, const void* bias,

@@ -3,6 +3,7 @@
 // softmax and the final RGB8 quantisation. They replace chains of elementwise launches in the reference:
 // candle-gen/src/sampler.rs:36-59 (scale / add / axpy), candle-gen-flux/src/vae/native.rs:163-222 (GroupNorm ->
 // SiLU, nearest upsample) and candle-gen/src/lib.rs:56-62 (round_rgb8, nearest-even).
+#include <algorithm>
 #include "common.cuh"
 
 namespace swb {
@@ -93,9 +94,10 @@ __global__ void __launch_bounds__(256) groupnorm_stats_kernel(const bf16* __rest
   }
 }
 
-// Narrow groups (C / G in {1, 2, 4}: a 16-byte vector spans several groups). One CTA covers `chunk` pixels of one
-// sample over all channels; thread t owns vector column t % (C/8) and walks pixels with stride 256 / (C/8).
-// Requires C/8 to divide 256 and G <= 512.
+// Row-coalesced statistics: one CTA covers `chunk` pixels of one sample over all channels; thread t owns vector column
+// t % (C/8) and walks pixels with stride 256 / (C/8), so a warp reads whole contiguous pixel rows. Groups may be narrower
+// than a 16-byte vector (C / G in {1, 2, 4}: the vector spans several groups) or a multiple of it (the vector's eight
+// channels fall in one group). Requires C/8 to divide 256 and G <= 512.
 __global__ void __launch_bounds__(256) groupnorm_stats_narrow_kernel(const bf16* __restrict__ x, float* stats, int HW,
                                                                     int C, int G, int chunk) {
   pdl_launch_dependents();
@@ -119,21 +121,77 @@ __global__ void __launch_bounds__(256) groupnorm_stats_narrow_kernel(const bf16*
       ss[j] += f[j] * f[j];
     }
   }
+  if (cpg >= 8) {
+    float st = 0.f, sst = 0.f;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const int g = (v * 8 + j) / cpg;
-    atomicAdd(&acc[2 * g], s[j]);
-    atomicAdd(&acc[2 * g + 1], ss[j]);
+    for (int j = 0; j < 8; ++j) {
+      st += s[j];
+      sst += ss[j];
+    }
+    const int g = (v * 8) / cpg;
+    atomicAdd(&acc[2 * g], st);
+    atomicAdd(&acc[2 * g + 1], sst);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int g = (v * 8 + j) / cpg;
+      atomicAdd(&acc[2 * g], s[j]);
+      atomicAdd(&acc[2 * g + 1], ss[j]);
+    }
   }
   __syncthreads();
   for (int i = threadIdx.x; i < 2 * G; i += blockDim.x) atomicAdd(&stats[(size_t)n * G * 2 + i], acc[i]);
 }
 
-// y = silu?((x - mean) * rstd * gamma + beta), NHWC bf16, 8 channels per thread.
+// y = silu?((x - mean) * rstd * gamma + beta), NHWC bf16. A thread owns one 8-channel vector column (C / 8 divides the
+// CTA's 256 threads) and walks pixels with a grid stride, so the per-channel scale and shift (folded from the group
+// statistics and gamma / beta) are computed once per sample instead of once per element, and the index arithmetic is
+// 32-bit. Launch with a grid whose thread count is a multiple of C / 8.
 __global__ void __launch_bounds__(256) groupnorm_apply_kernel(const bf16* __restrict__ x, const float* __restrict__ stats,
                                                              const bf16* __restrict__ gamma,
-                                                             const bf16* __restrict__ beta, bf16* out, long long n8,
-                                                             int HW, int C, int G, float eps, int silu) {
+                                                             const bf16* __restrict__ beta, bf16* out, int N, int HW,
+                                                             int C, int G, float eps, int silu) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const unsigned c8 = C / 8, cpg = C / G;
+  const unsigned tid = blockIdx.x * blockDim.x + threadIdx.x, threads = gridDim.x * blockDim.x;
+  const unsigned v = tid % c8, c = v * 8;
+  const unsigned pix_step = threads / c8;
+  const float cnt = (float)HW * cpg;
+  float ga[8], be[8];
+  unpack8(__ldg(reinterpret_cast<const uint4*>(gamma + c)), ga);
+  unpack8(__ldg(reinterpret_cast<const uint4*>(beta + c)), be);
+  for (int n = 0; n < N; ++n) {
+    float sc[8], sh[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const unsigned g = (c + j) / cpg;
+      const float mean = stats[((size_t)n * G + g) * 2] / cnt;
+      const float var = fmaxf(stats[((size_t)n * G + g) * 2 + 1] / cnt - mean * mean, 0.f);
+      const float rstd = rsqrtf(var + eps);
+      sc[j] = rstd * ga[j];
+      sh[j] = be[j] - mean * sc[j];
+    }
+    const uint4* xin = reinterpret_cast<const uint4*>(x) + (size_t)n * HW * c8 + v;
+    uint4* yout = reinterpret_cast<uint4*>(out) + (size_t)n * HW * c8 + v;
+    for (unsigned p = tid / c8; p < (unsigned)HW; p += pix_step) {
+      float f[8], o[8];
+      unpack8(xin[(size_t)p * c8], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float t = fmaf(f[j], sc[j], sh[j]);
+        o[j] = silu ? silu_f(t) : t;
+      }
+      yout[(size_t)p * c8] = pack8(o);
+    }
+  }
+}
+
+// Fallback for channel counts whose vector columns do not divide the CTA: one 8-channel vector per thread.
+__global__ void __launch_bounds__(256) groupnorm_apply_any_kernel(const bf16* __restrict__ x, const float* __restrict__ stats,
+                                                                 const bf16* __restrict__ gamma,
+                                                                 const bf16* __restrict__ beta, bf16* out, long long n8,
+                                                                 int HW, int C, int G, float eps, int silu) {
   pdl_launch_dependents();
   pdl_wait();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -144,27 +202,17 @@ __global__ void __launch_bounds__(256) groupnorm_apply_kernel(const bf16* __rest
   const int n = (int)(pix / HW);
   const int cpg = C / G;
   const float cnt = (float)HW * cpg;
-  float mean[8], rstd[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const int g = (c + j) / cpg;
-    if (j == 0 || (cpg < 8 && (c + j) % cpg == 0)) {
-      mean[j] = stats[((size_t)n * G + g) * 2] / cnt;
-      const float var = fmaxf(stats[((size_t)n * G + g) * 2 + 1] / cnt - mean[j] * mean[j], 0.f);
-      rstd[j] = rsqrtf(var + eps);
-    } else {
-      mean[j] = mean[j - 1];
-      rstd[j] = rstd[j - 1];
-    }
-  }
   float f[8], ga[8], be[8], o[8];
   unpack8(reinterpret_cast<const uint4*>(x)[i], f);
   unpack8(__ldg(reinterpret_cast<const uint4*>(gamma + c)), ga);
   unpack8(__ldg(reinterpret_cast<const uint4*>(beta + c)), be);
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    const float v = (f[j] - mean[j]) * rstd[j] * ga[j] + be[j];
-    o[j] = silu ? silu_f(v) : v;
+    const int g = (c + j) / cpg;
+    const float mean = stats[((size_t)n * G + g) * 2] / cnt;
+    const float var = fmaxf(stats[((size_t)n * G + g) * 2 + 1] / cnt - mean * mean, 0.f);
+    const float t = (f[j] - mean) * rsqrtf(var + eps) * ga[j] + be[j];
+    o[j] = silu ? silu_f(t) : t;
   }
   reinterpret_cast<uint4*>(out)[i] = pack8(o);
 }
@@ -283,12 +331,14 @@ int swb_groupnorm(const void* x, void* stats, const void* gamma, const void* bet
   if (N <= 0 || HW <= 0) return 0;
   if (C % G != 0 || C % 8 != 0) return -3;
   const int cpg = C / G;
-  const bool narrow = cpg % 8 != 0;
-  if (narrow && (8 % cpg != 0 || 256 % (C / 8) != 0 || G > 512)) return -3;
+  const bool rows_ok = 256 % (C / 8) == 0 && G <= 512 && (cpg % 8 == 0 || 8 % cpg == 0);
+  const bool narrow = cpg % 8 != 0 || rows_ok;      // the row-coalesced kernel whenever the shape allows it
+  if (cpg % 8 != 0 && !rows_ok) return -3;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   cudaError_t e = cudaMemsetAsync(stats, 0, (size_t)N * G * 2 * sizeof(float), s);
   if (e != cudaSuccess) return -(int)e;
-  const int chunk = 1024;
+  // enough CTAs to cover the SMs twice on small feature maps, at most 1024 pixels per CTA on large ones
+  const int chunk = narrow ? std::max(64, std::min(1024, (HW + 295) / 296)) : 1024;
   dim3 grid((HW + chunk - 1) / chunk, G, N);
   int rc = narrow ? launch_kernel(groupnorm_stats_narrow_kernel, dim3((HW + chunk - 1) / chunk, N), dim3(256), 0, s,
                                   reinterpret_cast<const bf16*>(x), reinterpret_cast<float*>(stats), HW, C, G, chunk)
@@ -296,7 +346,15 @@ int swb_groupnorm(const void* x, void* stats, const void* gamma, const void* bet
                                   reinterpret_cast<float*>(stats), HW, C, G, chunk);
   if (rc) return rc;
   const long long n8 = (long long)N * HW * C / 8;
-  return launch_kernel(groupnorm_apply_kernel, dim3(blocks_for(n8)), dim3(256), 0, s, reinterpret_cast<const bf16*>(x),
+  if (256 % (C / 8) == 0) {
+    // about four vectors per thread, at most eight CTAs per SM's worth of blocks
+    const long long per_sample = (long long)HW * (C / 8);
+    const int blocks = (int)std::max<long long>(1, std::min<long long>((per_sample + 1023) / 1024, 148 * 8));
+    return launch_kernel(groupnorm_apply_kernel, dim3(blocks), dim3(256), 0, s, reinterpret_cast<const bf16*>(x),
+                         reinterpret_cast<const float*>(stats), reinterpret_cast<const bf16*>(gamma),
+                         reinterpret_cast<const bf16*>(beta), reinterpret_cast<bf16*>(out), N, HW, C, G, eps, silu);
+  }
+  return launch_kernel(groupnorm_apply_any_kernel, dim3(blocks_for(n8)), dim3(256), 0, s, reinterpret_cast<const bf16*>(x),
                        reinterpret_cast<const float*>(stats), reinterpret_cast<const bf16*>(gamma),
                        reinterpret_cast<const bf16*>(beta), reinterpret_cast<bf16*>(out), n8, HW, C, G, eps, silu);
 }

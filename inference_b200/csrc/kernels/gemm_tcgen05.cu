@@ -374,7 +374,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           if (!ok) break;
           outstanding &= ~(1u << stage);
           mbar_arrive_expect_tx(&bar_full[stage], Cfg::STAGE_BYTES);
-          tma_load_2d_hint(sa, &tmap_a, &bar_full[stage], kb * BK, c.tm * BM, pol_a);
+          if (p.conv_c) {
+            // implicit 3x3 convolution: this k-block is one tap of the window over one 64-channel slab
+            const int slabs = p.conv_c / BK, tap = kb / slabs, c0 = (kb - tap * slabs) * BK;
+            const int hw = p.conv_h * p.conv_w, m0 = c.tm * BM, img = m0 / hw, rem = m0 - img * hw;
+            const int y0 = rem / p.conv_w, x0 = rem - y0 * p.conv_w;
+            tma_load_4d_hint(sa, &tmap_a, &bar_full[stage], c0, x0 + tap % 3 - 1, y0 + tap / 3 - 1, img, pol_a);
+          } else {
+            tma_load_2d_hint(sa, &tmap_a, &bar_full[stage], kb * BK, c.tm * BM, pol_a);
+          }
           tma_load_2d_hint(sb, &tmap_b, &bar_full[stage], kb * BK, b_row, pol_b);
           outstanding |= 1u << stage;
           issue_phase_bits = (issue_phase_bits & ~(1u << stage)) | (phase << stage);
@@ -665,6 +673,21 @@ int make_tmap_u32_3d(CUtensorMap* out, const void* ptr, const unsigned long long
   return r == CUDA_SUCCESS ? 0 : -(int)r - 1000;
 }
 
+// NHWC bf16 activation [n, h, w, c] (contiguous): dims (c, w, h, n), box (64, box_w, box_h, 1), 128-byte swizzle, zero
+// fill outside (rows of the box land in (y, x) order, 128 bytes each: the K-major A tile the MMA descriptor expects).
+int make_tmap_bf16_nhwc(CUtensorMap* out, const void* ptr, int n, int h, int w, int c, int box_w, int box_h) {
+  auto encode = get_encode_fn();
+  if (!encode) return -1;
+  cuuint64_t dims[4] = {(cuuint64_t)c, (cuuint64_t)w, (cuuint64_t)h, (cuuint64_t)n};
+  cuuint64_t strides[3] = {(cuuint64_t)c * 2, (cuuint64_t)w * c * 2, (cuuint64_t)h * w * c * 2};
+  cuuint32_t box[4] = {(cuuint32_t)BK, (cuuint32_t)box_w, (cuuint32_t)box_h, 1u};
+  cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+  CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -(int)r - 1000;
+}
+
 int device_sm_count() {
   static int sms[64] = {0};
   int dev = 0;
@@ -734,6 +757,16 @@ int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
     if (a.scatter || a.groups <= 0 || a.bias || a.residual) return -3;
     swapped = 0;
   }
+  if (a.conv_c > 0) {
+    // implicit 3x3 convolution: tokens-as-M only; a 128-pixel tile is a run of one image row or whole rows
+    const long hw = (long)a.conv_h * a.conv_w;
+    if (a.scatter || a.group_of_mtile || a.ssq_in || a.ssq_out || (a.peer && a.peer->mode) || a.act >= SWB_ACT_SWIGLU_PAIRS)
+      return -3;
+    if (a.conv_n <= 0 || a.conv_h <= 0 || a.conv_w <= 0 || (a.conv_c % BK) != 0 || a.K != 9 * a.conv_c ||
+        (long)a.T != hw * a.conv_n || (hw % BM) != 0 || !((a.conv_w % BM) == 0 || (BM % a.conv_w) == 0))
+      return -3;
+    swapped = 0;
+  }
   if (swapped < 0) swapped = (a.T <= 256) ? 1 : 0;
   if (a.peer && a.peer->mode) {   // cross-rank sum in the epilogue: decode cluster kernel only, any K
     if (a.scatter || a.group_of_mtile || !gemm_decode_cluster_supported(a.T)) return -3;
@@ -750,7 +783,7 @@ int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
   if (pairs && (a.scatter || a.group_of_mtile || a.residual || a.out_fp32 || (a.N & 1) || a.force_mode == 0 ||
                 a.force_mode == 1 || !gemm_bf16_gated_supported(a.T, a.N, a.K)))
     return -3;
-  if (!a.scatter && !a.group_of_mtile && (a.force_mode == 2 || (a.force_mode < 0 && gemm_decode_cluster_supported(a.T) && (a.N + BM - 1) / BM <= 2 * sms &&
+  if (!a.scatter && !a.group_of_mtile && !a.conv_c && (a.force_mode == 2 || (a.force_mode < 0 && gemm_decode_cluster_supported(a.T) && (a.N + BM - 1) / BM <= 2 * sms &&
                             (a.K + BK - 1) / BK >= 8))) {
     if (!gemm_decode_cluster_supported(a.T)) return -4;
     return gemm_decode_cluster_launch(a, a.force_mode == 2 ? a.force_ctas : 0, stream);
@@ -815,7 +848,16 @@ int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream) {
     p.stream_a = 0;
     p.tiles_m = (a.T + BM - 1) / BM;
     p.tiles_n = (a.N + block_n - 1) / block_n;
-    int r = make_tmap_bf16_2d(&ta, a.A, a.T, a.K, a.lda, BM);
+    int r;
+    if (a.conv_c > 0) {
+      const int box_w = a.conv_w >= BM ? BM : a.conv_w;
+      r = make_tmap_bf16_nhwc(&ta, a.A, a.conv_n, a.conv_h, a.conv_w, a.conv_c, box_w, BM / box_w);
+      p.conv_h = a.conv_h;
+      p.conv_w = a.conv_w;
+      p.conv_c = a.conv_c;
+    } else {
+      r = make_tmap_bf16_2d(&ta, a.A, a.T, a.K, a.lda, BM);
+    }
     if (r) return r;
     r = make_tmap_bf16_2d(&tb, a.W, a.group_of_mtile ? a.groups * a.N : a.N, a.K, a.ldw, block_n);
     if (r) return r;

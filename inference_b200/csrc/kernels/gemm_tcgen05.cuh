@@ -97,6 +97,11 @@ struct GemmParams {
   int norm_dim;
   float norm_eps;
   GemmPeerReduce peer;   // decode cluster kernel only
+  // 3x3 convolution as an implicit GEMM (conv_c > 0): A is an NHWC activation [n, conv_h, conv_w, conv_c] behind a 4-D
+  // tensor map with a box of 64 channels x (tile of 128 pixels); reduction block kb is tap kb / (conv_c / 64) (row
+  // major over the 3 x 3 window) and channel slab kb % (conv_c / 64), loaded at the tile's pixel origin shifted by the
+  // tap, zero filled outside the image (= the convolution's padding). Weights are [out, (ky, kx, in)].
+  int conv_h, conv_w, conv_c;
 };
 
 // User-level problem: D[T, N] = act(A[T, K] * W[N, K]^T + bias[N]) + residual[T, N].
@@ -127,6 +132,7 @@ struct GemmArgs {
   int norm_dim = 0;
   float norm_eps = 0.f;
   const GemmPeerReduce* peer = nullptr;  // see GemmPeerReduce (decode cluster kernel only)
+  int conv_n = 0, conv_h = 0, conv_w = 0, conv_c = 0;   // see GemmParams: A = NHWC activation, T = n h w, K = 9 c
 };
 
 int gemm_bf16_launch(const GemmArgs& a, cudaStream_t stream);
@@ -134,6 +140,7 @@ int gemm_bf16_gated_supported(int T, int N, int K);
 int gemm_decode_cluster_supported(int T);
 int gemm_decode_cluster_launch(const GemmArgs& a, int force_cluster, cudaStream_t stream);
 int make_tmap_bf16_2d(CUtensorMap* out, const void* ptr, int rows, int cols, int ld, int box_rows);
+int make_tmap_bf16_nhwc(CUtensorMap* out, const void* ptr, int n, int h, int w, int c, int box_w, int box_h);
 int make_tmap_u32_3d(CUtensorMap* out, const void* ptr, const unsigned long long dims[3], const unsigned long long strides[2],
                      const unsigned box[3]);
 int make_tmap_u16_2d(CUtensorMap* out, const void* ptr, long long cols, long long rows, long long row_pitch_bytes,

@@ -209,12 +209,8 @@ class VaeDecoderGpu:
         return self.load_state_dict(random_vae_weights(self.cfg, seed, device=self.device))
 
     def _conv3(self, x, name, residual=None):
-        N, H, W, C = x.shape
-        cols = ops.im2col3x3_nhwc(x)
-        res = residual.reshape(N * H * W, -1) if residual is not None else None
-        y = ops.gemm_bf16(cols, self.w[name + ".weight"], bias=self.w[name + ".bias"], residual=res)
-        self.launches += 2
-        return y.view(N, H, W, -1)
+        self.launches += 1 if ops.conv3x3_supported(x) else 2
+        return ops.conv3x3_nhwc(x, self.w[name + ".weight"], self.w[name + ".bias"], residual)
 
     def _conv1(self, x, name, residual=None):
         N, H, W, C = x.shape

@@ -31,6 +31,16 @@ def test_media_kernels():
         ref = torch.nn.functional.silu(torch.nn.functional.group_norm(a2.float().permute(0, 3, 1, 2), G, g2.float(),
                                                                       b2.float(), 1e-6))
         assert torch.allclose(out.float(), ref.permute(0, 2, 3, 1), atol=4e-2, rtol=2e-2)
+    # wide groups on the row-coalesced statistics kernel, small and large maps, several samples; and a channel count
+    # whose vector columns do not divide the CTA (the one-vector-per-thread kernels)
+    for N, H, W, C, G in ((2, 64, 64, 256, 32), (1, 16, 16, 512, 32), (3, 5, 7, 512, 32), (1, 9, 11, 192, 8)):
+        a2 = (torch.randn(N, H, W, C, device="cuda") * 2 + 0.5).bfloat16()
+        g2 = (torch.rand(C, device="cuda") + 0.5).bfloat16()
+        b2 = (torch.randn(C, device="cuda") * 0.1).bfloat16()
+        out = ops.groupnorm_nhwc(a2, g2, b2, groups=G, eps=1e-6, silu=True)
+        ref = torch.nn.functional.silu(torch.nn.functional.group_norm(a2.float().permute(0, 3, 1, 2), G, g2.float(),
+                                                                      b2.float(), 1e-6))
+        assert torch.allclose(out.float(), ref.permute(0, 2, 3, 1), atol=4e-2, rtol=2e-2), (N, H, W, C, G)
     a3 = torch.randn(1, 5, 6, 16, device="cuda").bfloat16()
     cols = ops.im2col3x3_nhwc(a3)
     ref = torch.nn.functional.unfold(a3.float().permute(0, 3, 1, 2), 3, padding=1)      # [1, C*9, L], (c, kh, kw)
@@ -125,6 +135,44 @@ def test_flux_dit_image_stream_hooks_match_oracle():
     assert torch.equal(model.forward_graphed(img, img_ids, txt, txt_ids, t, y, gd).float(), out)
     model.injector = None
     assert torch.equal(model.forward(img, img_ids, txt, txt_ids, t, y, gd).float(), plain)
+
+
+@pytest.mark.parametrize("shape", [(1, 16, 16, 64, 128), (2, 32, 32, 128, 64), (1, 64, 64, 256, 256), (1, 128, 128, 128, 128),
+                                   (1, 8, 256, 64, 8), (3, 4, 32, 64, 16)])
+def test_implicit_conv3x3_matches_conv2d(shape, monkeypatch):
+    """3x3 convolution as an implicit GEMM (TMA-shifted taps, zero fill as padding) against F.conv2d in fp32: tiles
+    that are part of a row, whole rows and stacks of rows; bias, activation and residual epilogues; several images
+    per batch (a tile never straddles two images); and agreement with the patch-gather path."""
+    import torch.nn.functional as F
+
+    from inference_b200 import ops
+
+    N, H, W, C, Co = shape
+    g = torch.Generator(device="cuda").manual_seed(H * W + C)
+    x = torch.randn(N, H, W, C, device="cuda", generator=g).bfloat16()
+    w4 = (torch.randn(Co, C, 3, 3, device="cuda", generator=g) / (9 * C) ** 0.5).bfloat16()
+    b = torch.randn(Co, device="cuda", generator=g).bfloat16()
+    r = torch.randn(N, H, W, Co, device="cuda", generator=g).bfloat16()
+    wk = w4.permute(0, 2, 3, 1).reshape(Co, 9 * C).contiguous()
+    assert ops.conv3x3_supported(x)
+    ref = F.conv2d(x.float().permute(0, 3, 1, 2), w4.float(), b.float(), padding=1).permute(0, 2, 3, 1)
+    got = ops.conv3x3_nhwc(x, wk, b)
+    assert got.shape == (N, H, W, Co)
+    assert (got.float() - ref).abs().max().item() < 0.03 * max(1.0, ref.abs().max().item())
+    got = ops.conv3x3_nhwc(x, wk, b, residual=r, act="silu")
+    want = F.silu(ref) + r.float()
+    assert (got.float() - want).abs().max().item() < 0.03 * max(1.0, want.abs().max().item())
+    monkeypatch.setenv("SWB_CONV3X3", "im2col")
+    old = ops.conv3x3_nhwc(x, wk, b)
+    assert (old.float() - ops.conv3x3_nhwc(x, wk, b).float()).abs().max().item() == 0.0
+    monkeypatch.setenv("SWB_CONV3X3", "implicit")
+    assert (old.float() - ops.conv3x3_nhwc(x, wk, b).float()).abs().max().item() < 0.02 * max(1.0, ref.abs().max().item())
+    narrow = torch.randn(1, 16, 16, 16, device="cuda", generator=g).bfloat16()          # 16 channels: the gather path
+    assert not ops.conv3x3_supported(narrow)
+    wn = (torch.randn(32, 16, 3, 3, device="cuda", generator=g) / 12).bfloat16()
+    out = ops.conv3x3_nhwc(narrow, wn.permute(0, 2, 3, 1).reshape(32, 144).contiguous())
+    refn = F.conv2d(narrow.float().permute(0, 3, 1, 2), wn.float(), padding=1).permute(0, 2, 3, 1)
+    assert (out.float() - refn).abs().max().item() < 0.03 * max(1.0, refn.abs().max().item())
 
 
 def test_vae_decoder_matches_oracle():
