@@ -424,3 +424,34 @@ def test_padded_dense_attention_serves_narrow_heads(D, Sq, Skv, B):
                                                            v.float().transpose(1, 2)).transpose(1, 2).reshape(B, Sq, 5 * D)
     assert out.shape == ref.shape
     assert (out.float() - ref).abs().max().item() < 0.03
+
+
+def test_flux_control_branch_on_device_tracks_the_oracle():
+    """The ControlNet branch on the sm_100a model class (fused checkpoint layout, tcgen05 GEMM / attention) against the
+    fp32 oracle class carrying the same converted weights, and the controlled base forward against its fp32 twin."""
+    from inference_b200.media import flux_control as C
+    from inference_b200.models.dit_flux import FluxConfig, FluxDiTGpu, OracleFluxDiT, make_ids, random_flux_weights
+
+    base_cfg = FluxConfig.tiny()
+    sd = C.random_control_weights(base_cfg, layers=2, seed=1, std=0.05)
+    g = torch.Generator().manual_seed(0)
+    ht, wt, St = 8, 8, 16
+    img, cond = torch.randn(1, ht * wt, base_cfg.in_channels, generator=g), torch.randn(1, ht * wt, base_cfg.in_channels, generator=g)
+    txt, y = torch.randn(1, St, base_cfg.context_in_dim, generator=g), torch.randn(1, base_cfg.vec_in_dim, generator=g)
+    txt_ids, img_ids = make_ids(ht, wt, St)
+    t, gd = torch.tensor([0.7]), torch.tensor([3.5])
+    ref_branch = C.FluxControlNet(base_cfg, sd, "cpu")
+    ref = ref_branch.forward(img, cond, img_ids, txt, txt_ids, t, y, gd)
+    dev_branch = C.FluxControlNet(base_cfg, sd, "cuda")
+    cu = lambda x: x.cuda().bfloat16() if x.is_floating_point() else x.cuda()                 # noqa: E731
+    got = dev_branch.forward(cu(img), cu(cond), img_ids.cuda(), cu(txt), txt_ids.cuda(), t.cuda(), cu(y), gd.cuda())
+    assert len(got) == 2
+    for a, b in zip(got, ref):
+        assert (a.float().cpu() - b).abs().max().item() < 0.06 * max(1.0, b.abs().max().item())
+    bw = random_flux_weights(base_cfg, 2, std=0.05)
+    want = C.ControlledDit(OracleFluxDiT(base_cfg, bw), ref_branch, cond, 0.7).forward(img, img_ids, txt, txt_ids, t, y, gd)
+    base = FluxDiTGpu(base_cfg).load_state_dict(bw)
+    out = C.ControlledDit(base, dev_branch, cu(cond), 0.7).forward_graphed(cu(img), img_ids.cuda(), cu(txt), txt_ids.cuda(), t.cuda(),
+                                                                         cu(y), gd.cuda())
+    assert base.injector is None
+    assert (out.float().cpu() - want).abs().max().item() < 0.06 * max(1.0, want.abs().max().item())
