@@ -198,6 +198,8 @@ class OracleFluxDiT:
                 xm = (1 + sc1) * ln(x) + sh1
                 qkvs[s] = self._qkv(self._lin(xm, f"double_blocks.{i}.{s}_attn.qkv"), None,
                                     f"double_blocks.{i}.{s}_attn.norm")
+            if inj is not None and hasattr(inj, "on_img_query"):
+                inj.on_img_query(i, qkvs["img"][0])          # [B, S_img, heads, head_dim]: after the q norm, before rotation
             q = torch.cat([qkvs["txt"][0], qkvs["img"][0]], 1)
             k = torch.cat([qkvs["txt"][1], qkvs["img"][1]], 1)
             v = torch.cat([qkvs["txt"][2], qkvs["img"][2]], 1)
@@ -367,6 +369,12 @@ class FluxDiTGpu:
                 for b in range(B):
                     self._lin(xm[b], f"double_blocks.{i}.{s}_attn.qkv", out=qkv[b, lo:lo + n])
                 self.launches += 1
+            if inj is not None and hasattr(inj, "on_img_query"):
+                # adapters that attend from the image query want it after the q norm and before rotation; the fused
+                # norm + rotation below works in place, so this copy is normalised on its own
+                inj.on_img_query(i, ops.rmsnorm(qkv[:, St:, :H].reshape(B * Si * NH, D).contiguous(),
+                                                self.w[f"double_blocks.{i}.img_attn.norm.query_norm.scale"], 1e-6)
+                                 .view(B, Si, NH, D))
             # per-stream QK norms differ: rotate each row range with its own norm weights
             for s, lo, n in (("txt", 0, St), ("img", St, Si)):
                 nw = (self.w[f"double_blocks.{i}.{s}_attn.norm.query_norm.scale"],

@@ -455,3 +455,43 @@ def test_flux_control_branch_on_device_tracks_the_oracle():
                                                                          cu(y), gd.cuda())
     assert base.injector is None
     assert (out.float().cpu() - want).abs().max().item() < 0.06 * max(1.0, want.abs().max().item())
+
+
+def test_flux_ip_adapter_seam_on_device_tracks_the_oracle():
+    """The IP-Adapter on the sm_100a model: the image query handed to the seam is the normalised, un-rotated query (its
+    own norm launch next to the fused norm + rotation), and the adapted forward tracks the fp32 twin; scale 0 leaves
+    the device forward unchanged."""
+    from inference_b200.media import flux_ip as P
+    from inference_b200.models.dit_flux import FluxConfig, FluxDiTGpu, OracleFluxDiT, make_ids, random_flux_weights
+
+    cfg = FluxConfig.tiny()
+    bw = random_flux_weights(cfg, 2, std=0.05)
+    g = torch.Generator().manual_seed(0)
+    ht, wt, St = 8, 8, 16
+    img, txt = torch.randn(1, ht * wt, cfg.in_channels, generator=g), torch.randn(1, St, cfg.context_in_dim, generator=g)
+    y = torch.randn(1, cfg.vec_in_dim, generator=g)
+    txt_ids, img_ids = make_ids(ht, wt, St)
+    t, gd = torch.tensor([0.6]), torch.tensor([3.5])
+    aw = P.random_ip_adapter_weights(cfg.depth, cfg.hidden_size, 24, seed=4)
+    emb = torch.randn(1, 24, generator=g)
+    ref_ad = P.FluxIpAdapter(aw, "cpu")
+    oracle = OracleFluxDiT(cfg, bw)
+    oracle.injector = P.FluxIpInjector(ref_ad, ref_ad.tokens(emb), 0.7)
+    want = oracle.forward(img, img_ids, txt, txt_ids, t, y, gd)
+    oracle.injector = None
+    plain = oracle.forward(img, img_ids, txt, txt_ids, t, y, gd)
+    assert (want - plain).abs().max().item() > 1e-3
+    dev_ad = P.FluxIpAdapter(aw, "cuda")
+    model = FluxDiTGpu(cfg).load_state_dict(bw)
+    cu = lambda x: x.cuda().bfloat16() if x.is_floating_point() else x.cuda()                 # noqa: E731
+    args = (cu(img), img_ids.cuda(), cu(txt), txt_ids.cuda(), t.cuda(), cu(y), gd.cuda())
+    base_out = model.forward(*args).float().cpu()
+    model.injector = P.FluxIpInjector(dev_ad, dev_ad.tokens(emb), 0.7)
+    got = model.forward(*args).float().cpu()
+    model.injector = P.FluxIpInjector(dev_ad, dev_ad.tokens(emb), 0.0)
+    off = model.forward(*args).float().cpu()
+    model.injector = None
+    tol = 0.06 * max(1.0, want.abs().max().item())
+    assert (got - want).abs().max().item() < tol and (base_out - plain).abs().max().item() < tol
+    assert torch.equal(off, base_out)
+    assert ((got - base_out) - (want - plain)).abs().max().item() < tol           # the adapter's effect itself agrees
