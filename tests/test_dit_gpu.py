@@ -495,3 +495,23 @@ def test_flux_ip_adapter_seam_on_device_tracks_the_oracle():
     assert (got - want).abs().max().item() < tol and (base_out - plain).abs().max().item() < tol
     assert torch.equal(off, base_out)
     assert ((got - base_out) - (want - plain)).abs().max().item() < tol           # the adapter's effect itself agrees
+
+
+def test_pid_network_on_device_tracks_the_oracle():
+    """The PiD network on the sm_100a backend (bf16 projections on the tcgen05 GEMM, 64-wide-head attention on the 64-wide
+    attention kernel, fp32 adapter trunk) against the fp32 backend carrying the same weights, v1.5 adapter."""
+    from inference_b200.media import pid as P
+
+    cfg = P.PidConfig(num_groups=2, hidden_size=128, pixel_hidden_size=8, pixel_attn_hidden_size=128, pixel_num_groups=2, patch_depth=3,
+                      pixel_depth=1, patch_size=4, txt_embed_dim=32, txt_max_length=12, rope_ref_h=32, rope_ref_w=32,
+                      lq_latent_channels=4, lq_hidden_dim=16, lq_num_res_blocks=1, lq_interval=2, sr_scale=2,
+                      latent_spatial_down_factor=8, lq_replicate_padding=True, pit_lq_inject=True)
+    w = P.random_pid_weights(cfg, seed=1)
+    g = torch.Generator().manual_seed(0)
+    x, y = torch.randn(1, 3, 64, 64, generator=g), torch.randn(1, 12, 32, generator=g)
+    lq, t, sig = torch.randn(1, 4, 4, 4, generator=g), torch.tensor([634.0]), torch.tensor([0.3])
+    want = P.PidNet(w, cfg, "cpu").forward(x, t, y, lq, sig)
+    got = P.PidNet(w, cfg, "cuda").forward(x, t, y, lq, sig).float().cpu()
+    assert got.shape == want.shape == (1, 3, 64, 64)
+    assert (got - want).abs().max().item() < 0.08 * max(1.0, want.abs().max().item())
+    assert float((got - want).abs().mean()) / (float(want.abs().mean()) + 1e-6) < 0.05
