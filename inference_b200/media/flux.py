@@ -114,6 +114,8 @@ class FluxPipeline:
         self.text_kind = "t5_clip"
         self.random_init = None
         self.adapters: list = []
+        self.pid_spec: tuple[Path, Path] | None = None       # (PiD checkpoint file, Gemma-2 snapshot directory)
+        self._pid_engine = None
         # when set to a dict, render() records device-timed phases of the last image into it:
         # "step_ms" (one entry per model evaluation) and "vae_ms" (CUDA events; read after the image is on the host)
         self.timings: dict | None = None
@@ -180,6 +182,17 @@ class FluxPipeline:
             vae = OracleVaeDecoder(self.vae_cfg, vae_w, device=self.device)
         return _Heavy(dit, vae, self.device, self.dtype)
 
+    def pid_engine(self, use_pid: bool):
+        """The super-resolving pixel decoder of this latent space, loaded the first time a request asks for it (a spec
+        the caller passed is never read by requests that do not use it)."""
+        if not use_pid or self.pid_spec is None:
+            return None
+        if self._pid_engine is None:
+            from .pid import PidEngine
+
+            self._pid_engine = PidEngine.load(self.pid_spec[0], self.pid_spec[1], "flux", self.backend)
+        return self._pid_engine
+
     # ---- phases --------------------------------------------------------------------------------------
     def encode(self, text, prompt: str) -> TextConditioning:
         return text.encode(prompt, self.variant.t5_max_len)
@@ -218,6 +231,12 @@ class FluxPipeline:
         c_lat = self.vae_cfg.z_channels
 
         events = [] if (self.timings is not None and self.backend == "b200") else None
+        from .pid import check_pid_request, resolve_pid_decoder
+
+        pid = self.pid_engine(req.use_pid)
+        if req.use_pid:
+            check_pid_request(pid, req, v.model_id)       # no engine / capture not wired / over budget: refused before any step
+        pid_for = lambda seed: resolve_pid_decoder(pid, req, seed, v.model_id)                 # noqa: E731
 
         def one_image(seed: int) -> Image:
             if events is not None:
@@ -257,6 +276,10 @@ class FluxPipeline:
                 raise Canceled(f"{v.model_id}: cancelled before decode")
             on_progress(ProgressDecoding())
             z = unpatchify(x.float(), lh, lw)
+            if pid is not None:                      # the same latent the VAE would get; the image comes out `scale` x larger
+                px = pid_for(seed).decode(z.cpu())[0].permute(1, 2, 0)
+                host = torch.round((px.clamp(-1, 1) + 1) * 127.5).to(torch.uint8).contiguous()
+                return Image(width=host.shape[1], height=host.shape[0], pixels=host.numpy().tobytes())
             if self.backend == "b200":
                 if events is not None:
                     v0, v1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -310,7 +333,13 @@ def _load(variant: Variant, backend: str, prefix: str) -> Callable[[LoadSpec], F
             raise Unsupported(f"{mid}: needs a snapshot directory (single-file checkpoints are not supported)")
         if spec.quantize is not None:
             raise Unsupported(f"{mid}: quantised loading ({spec.quantize.name}) is not supported")
-        reject_unknown_components(spec.components, [], mid)
+        reject_unknown_components(spec.components, ["pid_gemma"], mid)
+        pid_spec = None
+        if spec.pid is not None or "pid_gemma" in spec.components:
+            if spec.pid is None or not spec.pid.is_file or "pid_gemma" not in spec.components or spec.components["pid_gemma"].is_file:
+                raise LoadError(f"{mid}: the pixel decoder needs LoadSpec.pid (the converted checkpoint file) and the "
+                                "'pid_gemma' component (a Gemma-2 snapshot directory)")
+            pid_spec = (Path(spec.pid.path), Path(spec.components["pid_gemma"].path))
         if spec.control or spec.extra_controls or spec.ip_adapter:
             raise Unsupported(f"{mid}: control branches / IP adapters are not supported by this provider")
         for ad in spec.adapters:
@@ -324,6 +353,7 @@ def _load(variant: Variant, backend: str, prefix: str) -> Callable[[LoadSpec], F
             device = torch.device("cpu")
         pipe = FluxPipeline(variant, Path(spec.weights.path), backend, device)    # lazy: paths only
         pipe.adapters = list(spec.adapters)
+        pipe.pid_spec = pid_spec
         return FluxGenerator(variant, pipe, flux_descriptor(variant, backend, prefix), spec.offload_policy)
     return load
 

@@ -617,6 +617,39 @@ class PidEngine:
         return PidDecoder(self.net, self.sampler, self.caption.encode(caption), sigma, seed, cancel, tile)
 
 
+def resolve_pid_decoder(engine: "PidEngine | None", req, base_seed: int, model_id: str, capture_sigma: float = 0.0,
+                        capture_wired: bool = False, safe_gib: float | None = None) -> "PidDecoder | None":
+    """The request's decoder, or None when it did not ask for PiD. Asking without a loaded engine is an error; so is an
+    early-stop capture on a latent space whose generator does not hand over noisy latents (`capture_wired`). The output
+    is `scale` times the requested size, so the memory guard and the tile plan are sized for that."""
+    if not req.use_pid:
+        return None
+    safe_gib = check_pid_request(engine, req, model_id, capture_wired, safe_gib)
+    f = engine.vae_compression
+    return engine.decoder(req.prompt, capture_sigma, base_seed, req.cancel.is_cancelled, safe_gib, max(req.count, 1),
+                          (req.height // f, req.width // f))
+
+
+def check_pid_request(engine: "PidEngine | None", req, model_id: str, capture_wired: bool = False,
+                      safe_gib: float | None = None) -> float:
+    """The refusals of a request that asks for PiD, before any work is done -> the memory budget in GiB."""
+    if req.pid_capture_sigma is not None and not capture_wired:
+        raise InferenceError(f"{model_id}: pid_capture_sigma (early stop on a noisy latent) is not wired for this latent space")
+    if engine is None:
+        raise InferenceError(f"{model_id}: use_pid was requested but no PiD decoder is loaded (load with LoadSpec.pid)")
+    if safe_gib is None:
+        safe_gib = float(os.environ.get("PID_DECODE_BUDGET_GIB", "0")) or _device_budget_gib(engine.device)
+    guard(model_id, req.count, req.width, req.height, engine.scale, engine.cfg, safe_gib)
+    return safe_gib
+
+
+def _device_budget_gib(device: torch.device) -> float:
+    """0.85 of the device's memory; 16 GiB on a host without one."""
+    if device.type == "cuda":
+        return torch.cuda.get_device_properties(device).total_memory * 0.85 / GIB
+    return 16.0
+
+
 # ---- synthetic checkpoint ---------------------------------------------------------------------------------------------------
 def random_pid_weights(cfg: PidConfig, seed: int = 0, proj_in: int | None = None) -> dict[str, torch.Tensor]:
     g = torch.Generator().manual_seed(seed)

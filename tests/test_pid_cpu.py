@@ -299,3 +299,46 @@ def test_caption_and_engine_end_to_end(tmp_path):
     assert P.flow_capture_for_request(True, 0.6, sig, 0) == (0.5, 3)
     assert P.flow_capture_for_request(False, 0.6, sig, 0) == (0.0, 5) and P.flow_capture_for_request(True, None, sig, 0) == (0.0, 5)
     assert P.flow_capture_for_request(True, 0.6, sig, 2) == (0.0, 5) and P.flow_capture_for_request(True, 0.1, sig, 0) == (0.0, 5)
+
+
+def test_flux_generator_decodes_through_pid(tmp_path):
+    """`use_pid` on a FLUX generator loaded with the pixel decoder: same denoising, the latent goes to PiD instead of the
+    VAE and the image comes back `scale` times larger; requests that do not ask for it never touch the decoder."""
+    from inference_b200.contracts.errors import InferenceError, LoadError
+    from inference_b200.contracts.gen_core import GenerationRequest
+    from inference_b200.contracts.gen_core.runtime import LoadSpec, WeightsSource
+    from inference_b200.io.safetensors_io import save_file
+    from inference_b200.media import flux
+    from inference_b200.media.catalog import provider_registry
+
+    snap = flux.write_synthetic_snapshot(tmp_path / "flux", flux.Variant.SCHNELL)
+    _write_gemma(tmp_path / "gemma")
+    cfg = P.PidConfig(**{**TINY, "txt_embed_dim": 32, "txt_max_length": 300, "lq_latent_channels": 16, "sr_scale": 4, "patch_size": 16,
+                         "patch_depth": 2, "rope_ref_h": 256, "rope_ref_w": 256})
+    save_file(P.random_pid_weights(cfg, seed=2), tmp_path / "pid.safetensors")
+    reg = provider_registry("cpu")
+    plain_gen = reg.load("cpu_flux1_schnell", LoadSpec.from_dir(snap))
+    req = lambda **kw: GenerationRequest(prompt="a red fox", width=256, height=256, steps=2, seed=5, **kw)      # noqa: E731
+    with pytest.raises(InferenceError, match="no PiD decoder is loaded"):
+        plain_gen.generate(req(use_pid=True))
+    spec = LoadSpec.from_dir(snap)
+    spec.pid = WeightsSource.file(tmp_path / "pid.safetensors")
+    with pytest.raises(LoadError):
+        reg.load("cpu_flux1_schnell", spec)                                # the caption encoder is missing
+    spec.components["pid_gemma"] = WeightsSource.dir(tmp_path / "gemma")
+    gen = reg.load("cpu_flux1_schnell", spec)
+    import inference_b200.media.pid as pid_mod
+    orig = pid_mod.PidEngine.load
+    pid_mod.PidEngine.load = staticmethod(lambda ck, gd, bb, be="b200", base_cfg=None: orig(ck, gd, bb, be, cfg))   # the tiny topology
+    try:
+        base = gen.generate(req()).images[0]
+        assert gen.pipe._pid_engine is None and base.pixels == plain_gen.generate(req()).images[0].pixels
+        events = []
+        big = gen.generate(req(use_pid=True), events.append).images[0]
+        assert (big.width, big.height) == (1024, 1024) and len(big.pixels) == 1024 * 1024 * 3 and gen.pipe._pid_engine is not None
+        assert gen.pipe._pid_engine.spec.latent_space == "flux" and len(events) == 3
+        assert gen.generate(req(use_pid=True)).images[0].pixels == big.pixels
+        with pytest.raises(InferenceError, match="pid_capture_sigma"):
+            gen.generate(req(use_pid=True, pid_capture_sigma=0.3))
+    finally:
+        pid_mod.PidEngine.load = orig
