@@ -39,9 +39,10 @@ def provider_registry(backend: str = "b200") -> ProviderRegistry:
     from .train import sdxl_trainer_registration
 
     b.register("trainer", sdxl_trainer_registration(backend))
-    from .train import wan_trainer_registration
+    from .train import krea_trainer_registration, wan_trainer_registration
 
     b.register("trainer", wan_trainer_registration(backend))
+    b.register("trainer", krea_trainer_registration(backend))
     from . import vision_providers
 
     for kind, regs in vision_providers.registrations(backend).items():

@@ -335,6 +335,59 @@ def wan_trainer_registration(backend: str):
     return Registration(descriptor=lambda: SimpleDescriptor(tid, "wan", backend, {"adapters": ["lora"]}), load=load)
 
 
+KREA_TARGETS = ("attn.to_q", "attn.to_k", "attn.to_v", "attn.to_out.0")
+
+
+class KreaLoraTrainer(FluxLoraTrainer):
+    """The same loop on the Krea DiT (candle-gen-krea/src/training.rs:20-160, train_dit.rs:60): adapters on the q / k / v /
+    output projections of every block's attention (the gate projection and the modulation table stay frozen); the model
+    sees the raw flow time sigma and its raw output is regressed towards eps - x0 (no 1 - sigma, no negation). Items
+    hold `latent` [C, h, w] and `txt` [L, layers, text_hidden] (the stacked encoder layers the text fusion consumes).
+    The oracle-backend model keeps q / k / v separate, which is what the adapter names address."""
+    family, target_suffixes, item_keys = "krea", KREA_TARGETS, ("latent", "txt")
+
+    def __init__(self, cfg, weights: dict[str, torch.Tensor], backend: str = "cpu", device="cpu"):
+        from ..models.dit_krea import KreaDiT
+
+        self.cfg, self.backend, self.device = cfg, backend, torch.device("cpu")   # fp32 autograd through the unfused layout
+        self.model = KreaDiT(cfg, weights, dtype=torch.float32, device=self.device)
+        self.model.w = self.model.bag.w
+        for t in self.model.w.values():
+            t.requires_grad_(False)
+
+    def descriptor(self) -> SimpleDescriptor:
+        return SimpleDescriptor("krea_lora_trainer" if self.backend != "cpu" else "cpu_krea_lora_trainer", "krea", self.backend,
+                                {"adapters": ["lora", "lokr"], "targets": list(KREA_TARGETS)})
+
+    def loss_on(self, item, t: float, noise: torch.Tensor) -> torch.Tensor:
+        x0, eps = item["latent"][None], noise[None]
+        xt = (1.0 - t) * x0 + t * eps
+        out = self.model.forward_grad(xt, torch.full((1,), t, device=self.device), item["txt"][None])
+        return torch.mean((out.float() - (eps - x0)) ** 2)
+
+
+def krea_trainer_registration(backend: str):
+    """`krea_lora_trainer` (kind "trainer"): loads the DiT of a Krea snapshot directory."""
+    from ..contracts.gen_core.registry import Registration
+    from ..contracts.gen_core.runtime import LoadSpec
+
+    tid = "krea_lora_trainer" if backend != "cpu" else "cpu_krea_lora_trainer"
+
+    def load(spec: LoadSpec) -> KreaLoraTrainer:
+        from ..io.safetensors_io import load_dir
+        from .krea import KreaPipeline, VARIANTS
+
+        if spec.weights is None or spec.weights.is_file:
+            raise InferenceError(f"{tid}: needs a snapshot directory")
+        root = Path(spec.weights.path)
+        if not (root / "transformer").is_dir():
+            raise LoadError(f"{tid}: missing {root / 'transformer'}")
+        pipe = KreaPipeline(VARIANTS[0], root, "cpu", torch.device("cpu"))
+        return KreaLoraTrainer(pipe.dit_cfg, load_dir(root / "transformer"), backend, "cpu")
+
+    return Registration(descriptor=lambda: SimpleDescriptor(tid, "krea", backend, {"adapters": ["lora", "lokr"]}), load=load)
+
+
 SDXL_TARGETS = ("attn1.to_q", "attn1.to_k", "attn1.to_v", "attn1.to_out.0", "attn2.to_q", "attn2.to_k", "attn2.to_v",
                 "attn2.to_out.0")
 

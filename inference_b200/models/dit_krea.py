@@ -148,6 +148,7 @@ class KreaDiT:
         # "RMS scale": weight = scale + 1 (stored as the offset of the norm kernel)
         self._rope_cache: dict[tuple[int, int, int, int], tuple[torch.Tensor, torch.Tensor]] = {}
         self.nvfp4 = None            # name -> packed projection after quantize_nvfp4()
+        self.lora = None             # training: {module name: (A [r, in], B [out, r], scale)}, added to the projection's output
         if self.device.type == "cuda":
             # one GEMM for q / k / v / gate and one for the SwiGLU gate / up pair of every block
             for p in self._block_prefixes():
@@ -171,7 +172,10 @@ class KreaDiT:
     def _proj(self, x: torch.Tensor, name: str) -> torch.Tensor:
         if self.nvfp4 is not None and name in self.nvfp4:
             return self.nvfp4[name](x)
-        return self.bag.lin(x, name)
+        y = self.bag.lin(x, name)
+        if self.lora is not None and name in self.lora:
+            y = y + nd.adapter_residual(self.lora[name], x)
+        return y
 
     def _rms(self, x: torch.Tensor, key: str) -> torch.Tensor:
         return nd.rms_norm(x, self.bag[key], self.cfg.norm_eps, offset=1.0)
