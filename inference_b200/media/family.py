@@ -79,6 +79,7 @@ class FamilyPipeline:
 
     latent_channels = 16
     latent_downscale = 8
+    pid_space: str | None = None       # the PiD latent space of this family's VAE: `use_pid` then decodes through media/pid.py
 
     def __init__(self, variant: Variant, root: Path, backend: str, device: torch.device):
         self.variant, self.root, self.backend, self.device = variant, Path(root), backend, device
@@ -90,7 +91,19 @@ class FamilyPipeline:
         self.text_kind = self.raw.get("text", "model")
         self.random_init = self.raw.get("random_init")
         self.adapters: list = []
+        self.pid_spec: tuple[Path, Path] | None = None        # (PiD checkpoint file, Gemma-2 snapshot directory)
+        self._pid_engine = None
         self.timings: dict | None = None      # set to a dict to collect device-timed "step_ms" / "decode_ms"
+
+    def pid_engine(self, use_pid: bool):
+        """The super-resolving pixel decoder of this family's latent space, loaded by the first request that asks."""
+        if not use_pid or self.pid_spec is None or self.pid_space is None:
+            return None
+        if self._pid_engine is None:
+            from .pid import PidEngine
+
+            self._pid_engine = PidEngine.load(self.pid_spec[0], self.pid_spec[1], self.pid_space, self.backend)
+        return self._pid_engine
 
     # ---- hooks ---------------------------------------------------------------------------------------------------
     def load_text(self):
@@ -161,6 +174,11 @@ class FamilyPipeline:
         sigmas = self.sigmas(steps, req)
         solver, ops, ms = get_solver(req.sampler or "euler"), TorchLatentOps(), FlowModelSampling()
         events = [] if (self.timings is not None and dev.type == "cuda") else None
+        pid = self.pid_engine(req.use_pid)
+        if req.use_pid:
+            from .pid import check_pid_request, resolve_pid_decoder
+
+            check_pid_request(pid, req, v.id)     # no engine / capture not wired / over budget: refused before any step
 
         def one_image(seed: int):
             if events is not None:
@@ -195,7 +213,11 @@ class FamilyPipeline:
             if events is not None:
                 d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 d0.record()
-            out = self.decode(heavy, x.float(), req)
+            if pid is not None:          # the latent the VAE would get; the image comes back `scale` x larger
+                px = resolve_pid_decoder(pid, req, seed, v.id).decode(x.float().cpu())
+                out = [rgb8_image(px[0], px.shape[3], px.shape[2])]
+            else:
+                out = self.decode(heavy, x.float(), req)
             if events is not None:
                 d1.record()
                 torch.cuda.synchronize()
@@ -263,7 +285,16 @@ def family_registrations(variants: list[Variant], pipeline_cls: Callable[..., Fa
                 raise Unsupported(f"{mid}: needs a snapshot directory")
             if spec.quantize is not None and not v.extra.get("quants"):
                 raise Unsupported(f"{mid}: quantised loading ({spec.quantize.name}) is not supported")
-            reject_unknown_components(spec.components, [], mid)
+            has_pid = getattr(pipeline_cls, "pid_space", None) is not None
+            reject_unknown_components(spec.components, ["pid_gemma"] if has_pid else [], mid)
+            pid_spec = None
+            if spec.pid is not None or "pid_gemma" in spec.components:
+                if not has_pid:
+                    raise Unsupported(f"{mid}: no pixel decoder exists for this family's latent space")
+                if spec.pid is None or not spec.pid.is_file or "pid_gemma" not in spec.components or spec.components["pid_gemma"].is_file:
+                    raise LoadError(f"{mid}: the pixel decoder needs LoadSpec.pid (the converted checkpoint file) and the "
+                                    "'pid_gemma' component (a Gemma-2 snapshot directory)")
+                pid_spec = (Path(spec.pid.path), Path(spec.components["pid_gemma"].path))
             if spec.control or spec.extra_controls or spec.ip_adapter:
                 raise Unsupported(f"{mid}: control branches and IP adapters are not supported by this provider")
             for ad in spec.adapters:
@@ -278,6 +309,7 @@ def family_registrations(variants: list[Variant], pipeline_cls: Callable[..., Fa
                 device = torch.device("cpu")
             pipe = pipeline_cls(v, Path(spec.weights.path), backend, device)
             pipe.adapters = list(spec.adapters)
+            pipe.pid_spec = pid_spec
             pipe.quantize = spec.quantize
             return FamilyGenerator(pipe, family_descriptor(v, backend, prefix), spec.offload_policy)
         return load

@@ -91,6 +91,8 @@ class _Heavy:
 
 
 class KreaPipeline(FamilyPipeline):
+    pid_space = "qwenimage"            # the Qwen-Image autoencoder's latent space
+
     def __init__(self, variant, root, backend, device):
         super().__init__(variant, root, backend, device)
         self.dit_cfg, self.vae_cfg = KreaConfig(), QwenVaeConfig()

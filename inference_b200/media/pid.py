@@ -499,7 +499,7 @@ class CaptionEncoder:
     """Gemma-2 states of (instruction prefix + caption): padded to prefix length + 298 tokens, padding masked as keys,
     final norm applied; kept are position 0 and the last 299 positions."""
 
-    def __init__(self, gemma_dir: Path, device="cpu", chi_prompt: str = CHI_PROMPT):
+    def __init__(self, gemma_dir: Path, device="cpu", chi_prompt: str | None = None):
         import json
 
         from ..contracts.gen_core.tokenizer import TextTokenizer, TokenizerConfig
@@ -517,8 +517,8 @@ class CaptionEncoder:
         dt = torch.bfloat16 if self.device.type == "cuda" else torch.float32
         self.lm = OracleLlama(cfg, w, dt, self.device)
         self.tok = TextTokenizer.from_file(tk, TokenizerConfig(max_length=4096))
-        self.chi_prompt = chi_prompt
-        self.num_chi_tokens = len(self.tok.encode_ids(chi_prompt, True))
+        self.chi_prompt = chi_prompt if chi_prompt is not None else CHI_PROMPT
+        self.num_chi_tokens = len(self.tok.encode_ids(self.chi_prompt, True))
 
     def token_ids(self, caption: str) -> tuple[list[int], int]:
         max_len = self.num_chi_tokens + MODEL_MAX_LENGTH - 2

@@ -265,8 +265,11 @@ def _write_gemma(d):
     save_file(random_llama_weights(ModelConfig.from_json(cj), 3, std=0.1), d / "model.safetensors")
 
 
-def test_caption_and_engine_end_to_end(tmp_path):
+def test_caption_and_engine_end_to_end(tmp_path, monkeypatch):
     from inference_b200.contracts.errors import LoadError
+
+    assert P.CHI_PROMPT.startswith("Given a user prompt") and P.CHI_PROMPT.endswith("User Prompt: ")
+    monkeypatch.setattr(P, "CHI_PROMPT", "Enhance the prompt. User Prompt: ")       # a short prefix keeps the toy encoder quick
     from inference_b200.io.safetensors_io import save_file
 
     assert P.select_index(555) == [0] + list(range(256, 555)) and len(P.select_index(555)) == 300
@@ -301,7 +304,7 @@ def test_caption_and_engine_end_to_end(tmp_path):
     assert P.flow_capture_for_request(True, 0.6, sig, 2) == (0.0, 5) and P.flow_capture_for_request(True, 0.1, sig, 0) == (0.0, 5)
 
 
-def test_flux_generator_decodes_through_pid(tmp_path):
+def test_flux_generator_decodes_through_pid(tmp_path, monkeypatch):
     """`use_pid` on a FLUX generator loaded with the pixel decoder: same denoising, the latent goes to PiD instead of the
     VAE and the image comes back `scale` times larger; requests that do not ask for it never touch the decoder."""
     from inference_b200.contracts.errors import InferenceError, LoadError
@@ -311,6 +314,7 @@ def test_flux_generator_decodes_through_pid(tmp_path):
     from inference_b200.media import flux
     from inference_b200.media.catalog import provider_registry
 
+    monkeypatch.setattr(P, "CHI_PROMPT", "Enhance the prompt. User Prompt: ")
     snap = flux.write_synthetic_snapshot(tmp_path / "flux", flux.Variant.SCHNELL)
     _write_gemma(tmp_path / "gemma")
     cfg = P.PidConfig(**{**TINY, "txt_embed_dim": 32, "txt_max_length": 300, "lq_latent_channels": 16, "sr_scale": 4, "patch_size": 16,
@@ -342,3 +346,49 @@ def test_flux_generator_decodes_through_pid(tmp_path):
             gen.generate(req(use_pid=True, pid_capture_sigma=0.3))
     finally:
         pid_mod.PidEngine.load = orig
+
+
+def test_family_scaffolding_decodes_through_pid(tmp_path, monkeypatch):
+    """The shared family pipeline: a family that names its PiD latent space (Krea: the Qwen-Image autoencoder's) accepts
+    the decoder at load and routes `use_pid` requests through it; a family without one refuses the components."""
+    from inference_b200.contracts.errors import InferenceError, Unsupported
+    from inference_b200.contracts.gen_core import GenerationRequest
+    from inference_b200.contracts.gen_core.runtime import LoadSpec, WeightsSource
+    from inference_b200.io.safetensors_io import save_file
+    from inference_b200.media import krea, sana
+    from inference_b200.media.catalog import provider_registry
+
+    monkeypatch.setattr(P, "CHI_PROMPT", "Enhance the prompt. User Prompt: ")
+    snap = krea.write_synthetic_snapshot(tmp_path / "krea")
+    _write_gemma(tmp_path / "gemma")
+    reg = provider_registry("cpu")
+    plain = reg.load("cpu_krea_2_turbo", LoadSpec.from_dir(snap))
+    ch = plain.pipe.latent_channels
+    cfg = P.PidConfig(**{**TINY, "txt_embed_dim": 32, "txt_max_length": 300, "lq_latent_channels": ch, "sr_scale": 4, "patch_size": 16,
+                         "patch_depth": 2, "rope_ref_h": 256, "rope_ref_w": 256})
+    save_file(P.random_pid_weights(cfg, seed=2), tmp_path / "pid.safetensors")
+    spec = LoadSpec.from_dir(snap)
+    spec.pid = WeightsSource.file(tmp_path / "pid.safetensors")
+    spec.components["pid_gemma"] = WeightsSource.dir(tmp_path / "gemma")
+    gen = reg.load("cpu_krea_2_turbo", spec)
+    orig = P.PidEngine.load
+    monkeypatch.setattr(P.PidEngine, "load", staticmethod(lambda ck, gd, bb, be="b200", base_cfg=None: orig(ck, gd, bb, be, replace_channels(cfg, bb))))
+    req = lambda **kw: GenerationRequest(prompt="a red fox", width=256, height=256, steps=2, seed=5, **kw)      # noqa: E731
+    with pytest.raises(InferenceError, match="no PiD decoder is loaded"):
+        plain.generate(req(use_pid=True))
+    assert gen.generate(req()).images[0].pixels == plain.generate(req()).images[0].pixels and gen.pipe._pid_engine is None
+    big = gen.generate(req(use_pid=True)).images[0]
+    assert (big.width, big.height) == (1024, 1024) and gen.pipe._pid_engine.spec.latent_space == "qwenimage"
+    with pytest.raises(InferenceError, match="pid_capture_sigma"):
+        gen.generate(req(use_pid=True, pid_capture_sigma=0.3))
+    other = LoadSpec.from_dir(sana.write_synthetic_snapshot(tmp_path / "sana"))
+    other.pid = WeightsSource.file(tmp_path / "pid.safetensors")
+    other.components["pid_gemma"] = WeightsSource.dir(tmp_path / "gemma")
+    with pytest.raises(Unsupported):
+        reg.load("cpu_" + sana.VARIANTS[0].id, other)
+
+
+def replace_channels(cfg, backbone):
+    from dataclasses import replace
+
+    return replace(cfg, lq_latent_channels=P.lookup(backbone).latent_channels)
