@@ -8,6 +8,8 @@ with cudaProfilerStart/Stop so that `ncu --profile-from-start off` sees only tho
   --what quant    one Q4_K dequant-GEMM (T from --shape "Tx..", N=28672, K=4096: the gate/up projection)
   --what attn     one split-KV decode attention launch (batch 64, 8 KV heads, context 2048)
   --what attn_dense one dense non-causal attention launch (S=4608, 24 heads)
+  --what conv     one implicit-GEMM 3x3 convolution, 512 x 512 x 256 -> 256 channels (134 MB in, 134 MB out)
+  --what paged_prefill  one prefill-attention launch over paged K / V: 2048 new tokens on 8192 of context, 32 / 8 heads
   --what vae      one FLUX-class VAE decode, 128 x 128 latents -> 1024 x 1024 (about 115 launches, 1.3 GB live)
 """
 import argparse
@@ -79,6 +81,21 @@ def main():
         S, H = 4608, 24
         q, k, v = (torch.randn(1, S, H, 128, device=dev, generator=g).bfloat16() for _ in range(3))
         window(lambda: ops.dense_attention(q, k, v, scale=128 ** -0.5, causal=False), reps=args.reps)
+    elif args.what == "conv":
+        x = torch.randn(1, 512, 512, 256, device=dev, generator=g).bfloat16()
+        w = (torch.randn(256, 9 * 256, device=dev, generator=g) / 48).bfloat16()
+        b = torch.randn(256, device=dev, generator=g).bfloat16()
+        window(lambda: ops.conv3x3_nhwc(x, w, b), reps=args.reps)
+    elif args.what == "paged_prefill":
+        Hq, Hkv, D, bs, q_len, ctx = 32, 8, 128, 16, 2048, 8192
+        per = (ctx + q_len) // bs
+        kc = torch.randn(per + 4, Hkv, bs, D, device=dev, generator=g).bfloat16()
+        vc = torch.randn(per + 4, Hkv, bs, D, device=dev, generator=g).bfloat16()
+        table = torch.randperm(per, device=dev, generator=g).to(torch.int32).view(1, per).contiguous()
+        q = torch.randn(q_len, Hq, D, device=dev, generator=g).bfloat16()
+        cu = torch.tensor([0, q_len], dtype=torch.int32, device=dev)
+        kvl = torch.tensor([ctx + q_len], dtype=torch.int32, device=dev)
+        window(lambda: ops.paged_attention(q, kc, vc, table, kvl, cu_q=cu, max_q_len=q_len, scale=D ** -0.5, causal=True), reps=args.reps)
     elif args.what == "vae":
         from inference_b200.models.vae import VaeConfig, VaeDecoderGpu
 
