@@ -38,6 +38,8 @@ def main():
     ap.add_argument("--new-tokens", type=int, default=512)
     ap.add_argument("--max-batch", type=int, default=128)
     ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--prefill-chunk", type=int, default=0,
+                    help="> 0: at most this many prompt tokens per step, in the same forward as the decode rows")
     args = ap.parse_args()
     from inference_b200 import ops
     from inference_b200.engine.backend import GpuBackend
@@ -77,7 +79,7 @@ def main():
     def sink(i: int, tok: int) -> None:
         if i not in first:
             first[i] = time.perf_counter() - t0
-    res = generate_continuous(backend, reqs, ContinuousConfig(max_batch=args.max_batch,
+    res = generate_continuous(backend, reqs, ContinuousConfig(max_batch=args.max_batch, prefill_chunk=args.prefill_chunk,
                                                               exactness=BatchExactness.THROUGHPUT), sink=sink)
     torch.cuda.synchronize()
     comm.barrier()
@@ -92,7 +94,7 @@ def main():
                 "value": round(generated / total_s, 1), "unit": "generated tokens/s (whole job, prefill included)",
                 "decode_phase_tok_s": round((generated - args.requests) / max(1e-9, total_s - last_first), 1),
                 "ttft_s_p50": round(statistics.median(first.values()), 3), "ttft_s_max": round(last_first, 3),
-                "dtype": "bf16", "data": "synthetic random ids, random-init weights",
+                "prefill_chunk": args.prefill_chunk, "dtype": "bf16", "data": "synthetic random ids, random-init weights",
                 "kv_pool_gb": round(eng.pool.data.numel() * 2 / 1e9, 2)}
         if invalid:
             line["invalid"] = invalid
