@@ -9,6 +9,8 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+import os
+
 import torch
 
 from ..models.llama import LlamaGpu, StepInputs
@@ -82,6 +84,9 @@ class ModelRunner:
         self._graphs: dict[tuple[int, int, bool], _DecodeGraph] = {}
         self._meta_copy_done = None
         self.pad_batches = self.use_graphs      # decode batches are padded to a bucket so graphs are reused
+        # SWB_DECODE_SPLIT=n runs a decode batch of more than n rows as consecutive sub-steps of at most n rows, so
+        # that every sub-step stays inside the row limit of the chained (folded-norm, GEMM + cross-rank sum) path
+        self.decode_split = int(os.environ.get("SWB_DECODE_SPLIT", "0"))
         self.captures = 0
         self.h2d_bytes_last = 0
         self.d2h_bytes_last = 0
@@ -232,10 +237,17 @@ class ModelRunner:
 
     def _decode_body(self, B: int, splits: int, want_logits: bool, feedback: bool = False):
         self._unpack_meta(B, skip_ids=feedback, multi=feedback and self.model.device.type == "cuda")
-        inp = StepInputs(input_ids=self._ids[:B], positions=self._pos[:B], slot_mapping=self._slots[:B],
-                         block_table=self._table[:B], kv_lens=self._kvl[:B], cu_q=None, max_q_len=1, num_seqs=B,
-                         decode=True, attn_splits=splits, logits_rows=None)
-        hidden = self.model.forward_hidden(inp, self.pool.data)
+        cap = self.decode_split if 0 < self.decode_split < B else B
+        parts = []
+        for r0 in range(0, B, cap):
+            r1 = min(B, r0 + cap)
+            inp = StepInputs(input_ids=self._ids[r0:r1], positions=self._pos[r0:r1], slot_mapping=self._slots[r0:r1],
+                             block_table=self._table[r0:r1], kv_lens=self._kvl[r0:r1], cu_q=None, max_q_len=1,
+                             num_seqs=r1 - r0, decode=True, attn_splits=splits, logits_rows=None)
+            part = self.model.forward_hidden(inp, self.pool.data)
+            # the model may hand back a view of a workspace that the next sub-step reuses
+            parts.append(part.clone() if cap < B else part)
+        hidden = parts[0] if len(parts) == 1 else torch.cat(parts, dim=0)
         if want_logits:
             return None, self.model.logits(hidden)
         toks = self.model.greedy_tokens(hidden)

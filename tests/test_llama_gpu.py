@@ -445,3 +445,34 @@ def _prompt_ids(llm, req):
 
     prompt = llm.template.render_with(llm._render_messages(req), RenderOptions(True, req.enable_thinking_kwarg(), req.tools))
     return llm.tokenizer.encode(prompt, add_special_tokens=False)
+
+
+def test_split_decode_steps_match_whole_steps():
+    """A decode batch run as consecutive sub-steps of at most `decode_split` rows (the knob that keeps a
+    large batch inside the row limit of the chained path) gives the logits of the whole-batch step, with
+    and without graphs, and leaves the caches in the same state for the following step."""
+    from inference_b200.engine.kv_pool import PagedKvPool, PagedSequence
+    from inference_b200.engine.runner import ModelRunner
+
+    cfg = _small_cfg()
+    _, model, _, _ = _build(cfg, seed=6)
+    outs = []
+    for split, graphs in ((0, False), (4, False), (4, True)):
+        pool = PagedKvPool(cfg.num_layers, 512, model.hkv, cfg.head_dim, 16, device="cuda")
+        runner = ModelRunner(model, pool, max_batch=32, max_seq_len=256, use_graphs=graphs)
+        runner.decode_split = split
+        g = torch.Generator().manual_seed(2)
+        prompts = [torch.randint(0, cfg.vocab_size, (4 + 2 * i,), generator=g).tolist() for i in range(11)]
+        seqs = [PagedSequence(pool) for _ in prompts]
+        toks = runner.prefill(seqs, prompts).tolist()
+        steps = []
+        for _ in range(3):
+            lg = runner.decode(seqs, toks, want_logits=True).float().clone()
+            steps.append(lg.cpu())
+            toks = outs[0][1][len(steps) - 1] if outs else lg.argmax(-1).tolist()
+        outs.append((steps, [s.argmax(-1).tolist() for s in steps]))
+    ref = outs[0][0]
+    for steps, _ in outs[1:]:
+        for a, b in zip(steps, ref):
+            assert a.shape == b.shape
+            assert (a - b).abs().max().item() < 0.03 * max(1.0, b.abs().max().item())
